@@ -1,0 +1,107 @@
+"""Paged KV cache: fixed 64-token pages, ref-counted so prefix-cache hits can share pages.
+
+The reference keeps a per-sequence ring buffer per layer and *copies* cached prefix blocks back
+in on a hit (reference: src/v2/kernels/cuda/kvcache/CUDARingKVCache.cu, src/v2/execution/
+prefix_cache/PrefixStateCache.h).  Here a sequence is a list of page ids; a prefix hit just
+appends the cached page ids to the new sequence's table and bumps their reference counts.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+PAGE_SIZE = 64
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PageAllocator:
+    """Free-list allocator with reference counts (host side, O(1) per page)."""
+
+    def __init__(self, n_pages: int, reserved: int = 1):
+        # page 0 is kept as a scratch page that padded batch lanes point at
+        self.n_pages = n_pages
+        self.reserved = reserved
+        self.free = list(range(n_pages - 1, reserved - 1, -1))
+        self.refs = [0] * n_pages
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise OutOfPages("KV cache exhausted")
+        p = self.free.pop()
+        self.refs[p] = 1
+        return p
+
+    def retain(self, page: int) -> None:
+        assert self.refs[page] > 0
+        self.refs[page] += 1
+
+    def release(self, page: int) -> None:
+        assert self.refs[page] > 0, f"double free of page {page}"
+        self.refs[page] -= 1
+        if self.refs[page] == 0:
+            self.free.append(page)
+
+    @property
+    def n_free(self) -> int:
+        return len(self.free)
+
+
+@dataclass
+class SequenceKV:
+    """Page table of one sequence."""
+    pages: list[int] = field(default_factory=list)
+    length: int = 0                  # tokens whose K/V are in the cache
+
+    def capacity(self) -> int:
+        return len(self.pages) * PAGE_SIZE
+
+
+class PagedKVCache:
+    def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, n_pages: int, device, dtype=torch.bfloat16):
+        self.n_layers, self.n_kv_heads, self.head_dim, self.n_pages = n_layers, n_kv_heads, head_dim, n_pages
+        self.device = torch.device(device)
+        # zero-filled: masked-out positions are multiplied by zero probabilities, so they must stay finite
+        self.layers = [torch.zeros(n_pages, 2, n_kv_heads, PAGE_SIZE, head_dim, dtype=dtype, device=device)
+                       for _ in range(n_layers)]
+        self.allocator = PageAllocator(n_pages)
+
+    @staticmethod
+    def bytes_per_page(n_layers: int, n_kv_heads: int, head_dim: int, itemsize: int = 2) -> int:
+        return n_layers * 2 * n_kv_heads * PAGE_SIZE * head_dim * itemsize
+
+    def ensure_capacity(self, seq: SequenceKV, n_tokens: int) -> None:
+        """Grow the page table so that ``n_tokens`` positions fit."""
+        while seq.capacity() < n_tokens:
+            seq.pages.append(self.allocator.alloc())
+
+    def free_sequence(self, seq: SequenceKV) -> None:
+        for p in seq.pages:
+            self.allocator.release(p)
+        seq.pages.clear()
+        seq.length = 0
+
+    def truncate(self, seq: SequenceKV, n_tokens: int) -> None:
+        """Roll a sequence back to ``n_tokens`` (speculative-decode rejection); frees whole spare pages."""
+        keep = (n_tokens + PAGE_SIZE - 1) // PAGE_SIZE
+        while len(seq.pages) > max(keep, 0):
+            self.allocator.release(seq.pages.pop())
+        seq.length = min(seq.length, n_tokens)
+
+    def fork_prefix(self, pages: list[int], n_tokens: int) -> SequenceKV:
+        """New sequence that shares the given full pages (prefix-cache hit)."""
+        assert n_tokens == len(pages) * PAGE_SIZE
+        for p in pages:
+            self.allocator.retain(p)
+        return SequenceKV(list(pages), n_tokens)
+
+    # -- page payload movement for the RAM / disk prefix tiers -------------------------------
+    def export_page(self, page: int) -> torch.Tensor:
+        return torch.stack([l[page] for l in self.layers]).to("cpu", non_blocking=False)
+
+    def import_page(self, page: int, payload: torch.Tensor) -> None:
+        for i, l in enumerate(self.layers):
+            l[page].copy_(payload[i].to(self.device, non_blocking=True))

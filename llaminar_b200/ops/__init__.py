@@ -1,0 +1,181 @@
+"""Python surface of the sm_100a kernels.
+
+Everything here launches hand-written CUDA from ``csrc/`` on the current torch stream.  There is
+no silent fallback: on a machine with a GPU the extension must load, otherwise these calls raise.
+The pure-PyTorch execution path used on CPU lives in :mod:`llaminar_b200.models.reference`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import build as _build
+from .layout import FMT_IDS, PackedWeight, can_pack, pack_experts, pack_matrix  # noqa: F401
+
+EPI_STORE, EPI_RESID, EPI_SWIGLU = 0, 1, 2
+GEMV_MAX_ROWS = 4
+PAGE_SIZE = 64
+
+_launches = 0          # kernels of this extension launched by the current process (bench evidence)
+
+
+def ext():
+    return _build.load()
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+@dataclass
+class Scratch:
+    """Per-device reusable scratch: split-K accumulators, arrival counters, attention split partials.
+
+    All buffers are returned to zero by the kernels that use them, so they can be shared by every
+    call on one stream (calls on different streams need separate instances).
+    """
+    accum: torch.Tensor
+    tickets: torch.Tensor
+    part_o: torch.Tensor
+    part_ml: torch.Tensor
+    attn_tickets: torch.Tensor
+    status: torch.Tensor
+
+    @staticmethod
+    def create(device, accum_rows: int = 256, accum_cols: int = 65536, attn_slots: int = 1 << 22) -> "Scratch":
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)
+        return Scratch(accum=z(accum_rows, accum_cols), tickets=z(8192, dt=torch.int32),
+                       part_o=z(attn_slots), part_ml=z(attn_slots // 32), attn_tickets=z(8192, dt=torch.int32),
+                       status=z(4, dt=torch.int32))
+
+
+_scratch: dict[str, Scratch] = {}
+
+
+def scratch_for(device) -> Scratch:
+    key = str(device)
+    if key not in _scratch:
+        _scratch[key] = Scratch.create(device)
+    return _scratch[key]
+
+
+def _accum_args(pw: PackedWeight, rows: int, sc: Scratch | None):
+    if sc is None or pw.n_tiles * 128 > sc.accum.shape[1] or rows > sc.accum.shape[0]:
+        return None, None
+    return sc.accum, sc.tickets
+
+
+def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
+         epi: int = EPI_STORE, bias: torch.Tensor | None = None, scratch: Scratch | None = None, ksplit: int = 0) -> None:
+    """out[m, :] (+)= x[m, :] @ W^T for m <= 4 rows.  x: fp32 residual rows when ``norm_w`` is given, else bf16."""
+    rows = x.shape[0]
+    assert 1 <= rows <= GEMV_MAX_ROWS
+    accum, tickets = _accum_args(pw, rows, scratch)
+    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1)
+    _count()
+
+
+def gemv_experts(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor, slots_per_row: int, *,
+                 epi: int = EPI_STORE, scratch: Scratch | None = None) -> None:
+    """One GEMV per (token, expert slot): out[z] = W[expert_ids[z]] @ x[z // slots_per_row]."""
+    z = expert_ids.numel()
+    accum, tickets = _accum_args(pw, z, scratch)
+    if tickets is not None and z * pw.n_tiles > tickets.numel():
+        accum, tickets = None, None
+    stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
+    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, None, 0.0, out, epi, None, accum, tickets, 0, expert_ids, stride,
+               slots_per_row, 1, z)
+    _count()
+
+
+def gemm(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, epi: int = EPI_STORE, bias: torch.Tensor | None = None,
+         scratch: Scratch | None = None, ksplit: int = 0) -> None:
+    """Tensor-core path: out[M, N] (+)= x[M, K] @ dequant(W)^T, any M."""
+    accum, tickets = _accum_args(pw, x.shape[0], scratch)
+    ext().gemm_tc(pw.data, pw.fmt, pw.n, pw.k, x, out, epi, bias, accum, tickets, ksplit if accum is not None else 1,
+                  scratch.status if scratch is not None else None)
+    _count()
+
+
+def dequant(pw: PackedWeight, out: torch.Tensor | None = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(pw.n, pw.k, dtype=torch.bfloat16, device=pw.data.device)
+    ext().dequant(pw.data, pw.fmt, pw.n, pw.k, out)
+    _count()
+    return out
+
+
+def gather_rows(pw: PackedWeight, rows: torch.Tensor, out: torch.Tensor) -> None:
+    ext().gather_rows(pw.data, pw.fmt, pw.k, rows, out)
+    _count()
+
+
+def rmsnorm(h: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    ext().rmsnorm(h, w, out, eps)
+    _count()
+
+
+def rope_kv(qkv, q_out, kv, q_norm, k_norm, positions, seq_ids, block_table, n_heads, n_kv_heads, head_dim, theta, eps) -> None:
+    ext().rope_kv(qkv, q_out, kv, q_norm, k_norm, positions, seq_ids, block_table, n_heads, n_kv_heads, head_dim, theta, eps)
+    _count()
+
+
+def attn_decode(q, kv, out, block_table, seq_lens, n_heads, n_kv_heads, head_dim, rows_per_seq, scale, n_splits,
+                scratch: Scratch) -> None:
+    ext().attn_decode(q, kv, out, block_table, seq_lens, scratch.part_o, scratch.part_ml, scratch.attn_tickets,
+                      n_heads, n_kv_heads, head_dim, rows_per_seq, scale, n_splits)
+    _count()
+
+
+def attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len) -> None:
+    ext().attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len)
+    _count()
+
+
+def swiglu_tiled(gu, out) -> None:
+    ext().swiglu_tiled(gu, out)
+    _count()
+
+
+def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
+    ext().argmax(logits, tokens)
+    _count()
+
+
+def sample(logits, temperature, top_k, top_p, seeds, step, tokens, probs_out=None) -> None:
+    ext().sample(logits, temperature, top_k, top_p, seeds, step, tokens, probs_out)
+    _count()
+
+
+def penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency) -> None:
+    ext().penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency)
+    _count()
+
+
+def nan_scan(x: torch.Tensor) -> tuple[int, int]:
+    counts = torch.zeros(2, dtype=torch.int32, device=x.device)
+    ext().nan_scan(x.contiguous(), counts)
+    _count()
+    c = counts.tolist()
+    return c[0], c[1]
+
+
+def spec_verify_greedy(draft, target, n_accept, out_tokens) -> None:
+    ext().spec_verify_greedy(draft, target, n_accept, out_tokens)
+    _count()
+
+
+def spec_verify_reject(p_target, p_draft, draft, seeds, step, n_accept, out_tokens) -> None:
+    ext().spec_verify_reject(p_target, p_draft, draft, seeds, step, n_accept, out_tokens)
+    _count()
+
+
+def moe_topk(logits, k, renorm, ids, weights, counts=None) -> None:
+    ext().moe_topk(logits, k, renorm, ids, weights, counts)
+    _count()

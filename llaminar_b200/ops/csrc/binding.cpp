@@ -1,0 +1,267 @@
+// pybind11 surface of the CUDA extension: thin argument checking + launch on the current torch stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "gemm_tc.h"
+#include "gemv.h"
+#include "ops.h"
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+#define LLM_CUDA_CHECK(expr)                                                                         \
+    do {                                                                                             \
+        cudaError_t e__ = (expr);                                                                    \
+        TORCH_CHECK(e__ == cudaSuccess, #expr " failed: ", cudaGetErrorString(e__));                 \
+    } while (0)
+
+static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+template <class T> static const T* cptr(const OptTensor& t) { return t.has_value() ? static_cast<const T*>(t->data_ptr()) : nullptr; }
+template <class T> static T* mptr(const OptTensor& t) { return t.has_value() ? static_cast<T*>(t->data_ptr()) : nullptr; }
+static void check_cuda(const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.is_contiguous() || t.stride(-1) == 1, name, " must have unit inner stride");
+}
+
+static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, const OptTensor& norm_w, double eps,
+                 Tensor out, int64_t epi, const OptTensor& bias, const OptTensor& accum, const OptTensor& tickets,
+                 int64_t ksplit, const OptTensor& expert_ids, int64_t expert_stride, int64_t z_per_x, int64_t m_tile, int64_t z) {
+    check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(k % 256 == 0, "k must be a multiple of 256");
+    llm::GemvParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr());
+    p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.n_tiles = (int)((n + 127) / 128); p.k_blocks = (int)(k / 256);
+    p.x = x.data_ptr(); p.x_stride = (int)x.stride(0); p.z_per_x = (int)std::max<int64_t>(z_per_x, 1);
+    if (norm_w.has_value()) {
+        TORCH_CHECK(x.scalar_type() == torch::kFloat32, "fused-norm GEMV takes the fp32 residual stream");
+        TORCH_CHECK(norm_w->scalar_type() == torch::kFloat32, "norm gain must be fp32");
+    } else {
+        TORCH_CHECK(x.scalar_type() == torch::kBFloat16, "GEMV input must be bf16");
+    }
+    p.norm_w = cptr<float>(norm_w); p.eps = (float)eps;
+    p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets);
+    p.accum_stride = accum.has_value() ? (int)accum->stride(0) : 0;
+    if (accum.has_value()) {
+        TORCH_CHECK(accum->size(0) >= m_tile * z && accum->stride(0) >= p.n_tiles * 128, "split-K scratch too small");
+        TORCH_CHECK(tickets.has_value() && tickets->numel() >= z * p.n_tiles, "ticket scratch too small");
+    }
+    p.ksplit = (int)ksplit; p.epi = (int)epi;
+    p.out = out.data_ptr(); p.out_stride = (int)out.stride(0);
+    p.out_f32 = out.scalar_type() == torch::kFloat32;
+    if (epi == llm::EPI_RESID) TORCH_CHECK(p.out_f32, "residual epilogue updates an fp32 stream");
+    if (epi == llm::EPI_SWIGLU) TORCH_CHECK(!p.out_f32, "SwiGLU epilogue writes bf16");
+    p.bias = cptr<float>(bias);
+    p.expert_ids = cptr<int>(expert_ids); p.expert_stride = (size_t)expert_stride;
+    LLM_CUDA_CHECK(llm::launch_gemv(p, (int)m_tile, (int)z, cur_stream()));
+}
+
+static void dequant(const Tensor& w, int64_t fmt, int64_t n, int64_t k, Tensor out) {
+    check_cuda(w, "w"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(w.device());
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.numel() >= n * k);
+    LLM_CUDA_CHECK(llm::launch_dequant((int)fmt, static_cast<const uint8_t*>(w.data_ptr()), (int)n, (int)k,
+                                       static_cast<__nv_bfloat16*>(out.data_ptr()), cur_stream()));
+}
+
+static void gather_rows(const Tensor& w, int64_t fmt, int64_t k, const Tensor& rows, Tensor out) {
+    check_cuda(w, "w"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(w.device());
+    TORCH_CHECK(rows.scalar_type() == torch::kInt32);
+    const bool f32 = out.scalar_type() == torch::kFloat32;
+    LLM_CUDA_CHECK(llm::launch_gather_rows((int)fmt, static_cast<const uint8_t*>(w.data_ptr()), (int)k,
+                                           static_cast<const int*>(rows.data_ptr()), (int)rows.numel(),
+                                           f32 ? static_cast<float*>(out.data_ptr()) : nullptr,
+                                           f32 ? nullptr : static_cast<__nv_bfloat16*>(out.data_ptr()), (int)out.stride(0), cur_stream()));
+}
+
+static void rmsnorm(const Tensor& h, const Tensor& w, Tensor out, double eps) {
+    check_cuda(h, "h");
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.scalar_type() == torch::kFloat32 && out.scalar_type() == torch::kBFloat16 && h.is_contiguous() && out.is_contiguous());
+    LLM_CUDA_CHECK(llm::launch_rmsnorm(static_cast<const float*>(h.data_ptr()), static_cast<const float*>(w.data_ptr()),
+                                       static_cast<__nv_bfloat16*>(out.data_ptr()), (int)h.size(0), (int)h.size(1), (float)eps, cur_stream()));
+}
+
+static void rope_kv(Tensor qkv, Tensor q_out, Tensor kv, const OptTensor& q_norm, const OptTensor& k_norm, const Tensor& positions,
+                    const Tensor& seq_ids, const Tensor& block_table, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
+                    double theta, double eps) {
+    check_cuda(qkv, "qkv");
+    const c10::cuda::CUDAGuard guard(qkv.device());
+    TORCH_CHECK(qkv.is_contiguous() && q_out.is_contiguous() && kv.is_contiguous());
+    TORCH_CHECK(positions.scalar_type() == torch::kInt32 && seq_ids.scalar_type() == torch::kInt32 && block_table.scalar_type() == torch::kInt32);
+    llm::RopeKVParams p{};
+    p.qkv = static_cast<__nv_bfloat16*>(qkv.data_ptr()); p.q_out = static_cast<__nv_bfloat16*>(q_out.data_ptr());
+    p.kv = static_cast<__nv_bfloat16*>(kv.data_ptr());
+    p.q_norm = cptr<float>(q_norm); p.k_norm = cptr<float>(k_norm);
+    p.positions = static_cast<const int*>(positions.data_ptr()); p.seq_ids = static_cast<const int*>(seq_ids.data_ptr());
+    p.block_table = static_cast<const int*>(block_table.data_ptr());
+    p.n_tokens = (int)qkv.size(0); p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim;
+    p.max_pages = (int)block_table.size(1); p.theta = (float)theta; p.eps = (float)eps;
+    LLM_CUDA_CHECK(llm::launch_rope_kv(p, cur_stream()));
+}
+
+static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Tensor& block_table, const Tensor& seq_lens,
+                        const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& tickets, int64_t n_heads,
+                        int64_t n_kv_heads, int64_t head_dim, int64_t rows_per_seq, double scale, int64_t n_splits) {
+    check_cuda(q, "q");
+    const c10::cuda::CUDAGuard guard(q.device());
+    const int batch = (int)seq_lens.numel();
+    llm::AttnDecodeParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q.data_ptr()); p.kv = static_cast<const __nv_bfloat16*>(kv.data_ptr());
+    p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+    p.block_table = static_cast<const int*>(block_table.data_ptr()); p.seq_lens = static_cast<const int*>(seq_lens.data_ptr());
+    p.part_o = mptr<float>(part_o); p.part_ml = mptr<float>(part_ml); p.tickets = mptr<unsigned>(tickets);
+    p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim; p.max_pages = (int)block_table.size(1);
+    p.rows_per_seq = (int)rows_per_seq; p.scale = (float)scale;
+    if (n_splits > 1) {
+        TORCH_CHECK(part_o.has_value() && part_ml.has_value() && tickets.has_value(), "split decode needs scratch");
+        TORCH_CHECK(part_o->numel() >= (int64_t)batch * n_kv_heads * n_splits * 16 * head_dim, "part_o too small");
+        TORCH_CHECK(part_ml->numel() >= (int64_t)batch * n_kv_heads * n_splits * 32, "part_ml too small");
+        TORCH_CHECK(tickets->numel() >= (int64_t)batch * n_kv_heads, "tickets too small");
+    }
+    LLM_CUDA_CHECK(llm::launch_attn_decode(p, batch, (int)n_splits, cur_stream()));
+}
+
+static void attn_prefill(const Tensor& q, const Tensor& kv, Tensor out, const Tensor& block_table, const Tensor& cu_q,
+                         const Tensor& ctx_lens, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim, double scale, int64_t max_q_len) {
+    check_cuda(q, "q");
+    const c10::cuda::CUDAGuard guard(q.device());
+    llm::AttnPrefillParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q.data_ptr()); p.kv = static_cast<const __nv_bfloat16*>(kv.data_ptr());
+    p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+    p.block_table = static_cast<const int*>(block_table.data_ptr()); p.cu_q = static_cast<const int*>(cu_q.data_ptr());
+    p.ctx_lens = static_cast<const int*>(ctx_lens.data_ptr());
+    p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim; p.max_pages = (int)block_table.size(1);
+    p.scale = (float)scale;
+    LLM_CUDA_CHECK(llm::launch_attn_prefill(p, (int)ctx_lens.numel(), (int)max_q_len, cur_stream()));
+}
+
+static void swiglu_tiled(const Tensor& gu, Tensor out) {
+    const c10::cuda::CUDAGuard guard(gu.device());
+    TORCH_CHECK(gu.is_contiguous() && out.is_contiguous() && gu.size(1) == 2 * out.size(1) && out.size(1) % 64 == 0);
+    LLM_CUDA_CHECK(llm::launch_swiglu_tiled(static_cast<const __nv_bfloat16*>(gu.data_ptr()), static_cast<__nv_bfloat16*>(out.data_ptr()),
+                                            (int)out.size(0), (int)out.size(1), cur_stream()));
+}
+
+static void add_bf16_to_f32(Tensor h, const Tensor& x) {
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.is_contiguous() && x.is_contiguous() && h.numel() == x.numel());
+    LLM_CUDA_CHECK(llm::launch_add_bf16_to_f32(static_cast<float*>(h.data_ptr()), static_cast<const __nv_bfloat16*>(x.data_ptr()),
+                                               (size_t)h.numel(), cur_stream()));
+}
+
+static void argmax(const Tensor& logits, Tensor tokens) {
+    const c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && tokens.scalar_type() == torch::kInt32);
+    LLM_CUDA_CHECK(llm::launch_argmax(static_cast<const float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1),
+                                      (int)logits.stride(0), static_cast<int*>(tokens.data_ptr()), nullptr, nullptr, cur_stream()));
+}
+
+static void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p, const Tensor& seeds,
+                   const Tensor& step, Tensor tokens, const OptTensor& probs_out) {
+    const c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && tokens.scalar_type() == torch::kInt32);
+    TORCH_CHECK(seeds.scalar_type() == torch::kInt64 && step.scalar_type() == torch::kInt32 && top_k.scalar_type() == torch::kInt32);
+    llm::SampleParams p{};
+    p.logits = static_cast<const float*>(logits.data_ptr()); p.rows = (int)logits.size(0); p.vocab = (int)logits.size(1);
+    p.stride = (int)logits.stride(0);
+    p.temperature = static_cast<const float*>(temperature.data_ptr()); p.top_k = static_cast<const int*>(top_k.data_ptr());
+    p.top_p = static_cast<const float*>(top_p.data_ptr()); p.seeds = static_cast<const uint64_t*>(seeds.data_ptr());
+    p.step = static_cast<const int*>(step.data_ptr()); p.tokens = static_cast<int*>(tokens.data_ptr());
+    p.probs_out = mptr<float>(probs_out);
+    LLM_CUDA_CHECK(llm::launch_sample(p, cur_stream()));
+}
+
+static void penalties(Tensor logits, const Tensor& hist_tokens, const Tensor& hist_counts, const Tensor& hist_offsets,
+                      const Tensor& presence, const Tensor& frequency) {
+    const c10::cuda::CUDAGuard guard(logits.device());
+    LLM_CUDA_CHECK(llm::launch_penalties(static_cast<float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1), (int)logits.stride(0),
+                                         static_cast<const int*>(hist_tokens.data_ptr()), static_cast<const int*>(hist_counts.data_ptr()),
+                                         static_cast<const int*>(hist_offsets.data_ptr()), static_cast<const float*>(presence.data_ptr()),
+                                         static_cast<const float*>(frequency.data_ptr()), cur_stream()));
+}
+
+static void nan_scan(const Tensor& x, Tensor counts) {
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.is_contiguous() && counts.scalar_type() == torch::kInt32 && counts.numel() >= 2);
+    const int dt = x.scalar_type() == torch::kFloat32 ? 0 : 1;
+    TORCH_CHECK(dt == 0 || x.scalar_type() == torch::kBFloat16, "nan_scan: fp32 or bf16 only");
+    LLM_CUDA_CHECK(llm::launch_nan_scan(x.data_ptr(), (size_t)x.numel(), dt, static_cast<int*>(counts.data_ptr()), cur_stream()));
+}
+
+static void spec_verify_greedy(const Tensor& draft, const Tensor& target, Tensor n_accept, Tensor out_tokens) {
+    const c10::cuda::CUDAGuard guard(draft.device());
+    TORCH_CHECK(draft.scalar_type() == torch::kInt32 && target.scalar_type() == torch::kInt32);
+    LLM_CUDA_CHECK(llm::launch_spec_verify_greedy(static_cast<const int*>(draft.data_ptr()), static_cast<const int*>(target.data_ptr()),
+                                                  (int)draft.size(0), (int)draft.size(1), static_cast<int*>(n_accept.data_ptr()),
+                                                  static_cast<int*>(out_tokens.data_ptr()), cur_stream()));
+}
+
+static void spec_verify_reject(const Tensor& p_target, const Tensor& p_draft, const Tensor& draft, const Tensor& seeds, const Tensor& step,
+                               Tensor n_accept, Tensor out_tokens) {
+    const c10::cuda::CUDAGuard guard(draft.device());
+    TORCH_CHECK(p_target.is_contiguous() && p_draft.is_contiguous() && draft.is_contiguous());
+    llm::SpecRejectParams p{};
+    p.p_target = static_cast<const float*>(p_target.data_ptr()); p.p_draft = static_cast<const float*>(p_draft.data_ptr());
+    p.draft = static_cast<const int*>(draft.data_ptr()); p.seeds = static_cast<const uint64_t*>(seeds.data_ptr());
+    p.step = static_cast<const int*>(step.data_ptr());
+    p.batch = (int)draft.size(0); p.depth = (int)draft.size(1); p.vocab = (int)p_target.size(-1);
+    p.n_accept = static_cast<int*>(n_accept.data_ptr()); p.out_tokens = static_cast<int*>(out_tokens.data_ptr());
+    LLM_CUDA_CHECK(llm::launch_spec_verify_reject(p, cur_stream()));
+}
+
+static void moe_topk(const Tensor& logits, int64_t k, bool renorm, Tensor ids, Tensor weights, const OptTensor& counts) {
+    const c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous());
+    LLM_CUDA_CHECK(llm::launch_moe_topk(static_cast<const float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1), (int)k,
+                                        renorm ? 1 : 0, static_cast<int*>(ids.data_ptr()), static_cast<float*>(weights.data_ptr()),
+                                        mptr<int>(counts), cur_stream()));
+}
+
+// tensor-core GEMM: out[M, N] (+)= x[M, K] * dequant(W)[N, K]^T
+static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, Tensor out, int64_t epi, const OptTensor& bias,
+                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status) {
+    check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "gemm_tc input must be contiguous bf16");
+    llm::GemmTcParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr()); p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.m = (int)x.size(0);
+    p.x = static_cast<const __nv_bfloat16*>(x.data_ptr());
+    p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
+    p.epi = (int)epi; p.bias = cptr<float>(bias); p.status = mptr<int>(status);
+    p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets); p.ksplit = (int)ksplit;
+    p.accum_stride = accum.has_value() ? (int)accum->stride(0) : 0;
+    if (epi == llm::EPI_RESID) TORCH_CHECK(p.out_f32, "residual epilogue updates an fp32 stream");
+    if (accum.has_value()) {
+        int bm = 0, ks = 0;
+        llm::gemm_tc_plan(p.m, p.n, p.k, p.ksplit, &bm, &ks);
+        const int64_t n_tiles = (n + 127) / 128, m_tiles = (p.m + bm - 1) / bm;
+        TORCH_CHECK(ks == 1 || (accum->size(0) >= p.m && accum->stride(0) >= n_tiles * 128), "split-K scratch too small");
+        TORCH_CHECK(ks == 1 || (tickets.has_value() && tickets->numel() >= n_tiles * m_tiles), "ticket scratch too small");
+    }
+    LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("gemv", &gemv);
+    m.def("gemm_tc", &gemm_tc);
+    m.def("dequant", &dequant);
+    m.def("gather_rows", &gather_rows);
+    m.def("rmsnorm", &rmsnorm);
+    m.def("rope_kv", &rope_kv);
+    m.def("attn_decode", &attn_decode);
+    m.def("attn_prefill", &attn_prefill);
+    m.def("swiglu_tiled", &swiglu_tiled);
+    m.def("add_bf16_to_f32", &add_bf16_to_f32);
+    m.def("argmax", &argmax);
+    m.def("sample", &sample);
+    m.def("penalties", &penalties);
+    m.def("nan_scan", &nan_scan);
+    m.def("spec_verify_greedy", &spec_verify_greedy);
+    m.def("spec_verify_reject", &spec_verify_reject);
+    m.def("moe_topk", &moe_topk);
+    m.def("attn_decode_pick_splits", &llm::attn_decode_pick_splits);
+    m.def("gemv_pick_ksplit", &llm::gemv_pick_ksplit);
+}

@@ -1,0 +1,63 @@
+// Shared device helpers for the sm_100a kernels of this extension.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLM_DEVICE __device__ __forceinline__
+
+namespace llm {
+
+constexpr int TILE_N = 128;   // rows per weight chunk
+constexpr int TILE_K = 256;   // columns per weight chunk
+
+// Status codes a kernel may leave in a caller-provided status word (never traps).
+enum KernelStatus : int { STATUS_OK = 0, STATUS_TIMEOUT = 1, STATUS_BAD_ARG = 2 };
+
+LLM_DEVICE float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+LLM_DEVICE float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+LLM_DEVICE float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+LLM_DEVICE float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+LLM_DEVICE uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+LLM_DEVICE float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+LLM_DEVICE uint4 ldg_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+LLM_DEVICE uint2 ldg_nc_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+LLM_DEVICE uint32_t ldg_nc_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+LLM_DEVICE uint16_t ldg_nc_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+LLM_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+LLM_DEVICE float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+}  // namespace llm

@@ -1,0 +1,439 @@
+// out[M, N] = x[M, K] * dequant(W)[N, K]^T on the 5th-generation tensor cores, weights decoded in the main loop.
+//
+// Roles inside one CTA (320 threads):
+//   warps 0-7  dequant producers: lane == weight row; each warp owns a 32-row group and every other
+//              256-column chunk.  Packed bytes go global -> registers (next chunk prefetched), are
+//              converted to bf16 and stored into the 128B-swizzled K-major operand tile of the ring
+//              stage, one 64-column "atom" (16 KB) at a time.  Afterwards they run the epilogue.
+//   warp 8     TMA producer: the activation tile (BM tokens x 64 columns) of each atom, SWIZZLE_128B.
+//   warp 9     allocates TMEM, issues tcgen05.mma (A = weights, 128 rows; B = activations, BM columns),
+//              releases ring stages with tcgen05.commit.
+// The accumulator is D[n, m] in TMEM (128 lanes x BM fp32 columns): weights sit in the MMA M dimension
+// so a batch-32 decode step wastes nothing, and the same kernel serves prefill with BM = 256.
+// Skinny problems add split-K over blockIdx.z (fp32 atomics into scratch, last CTA runs the epilogue).
+// Every mbarrier wait is bounded; on a timeout the kernel raises the status word and tears down cleanly.
+//
+// Replaces nativeVnniTC_BK64/BK256 + splitk_reduce/streamk_* (mma.sync int8 with in-smem dequant) of the
+// reference: src/v2/kernels/cuda/gemm/CUDANativeVNNIPrefillKernels.cu:141-3219.
+#include <cuda.h>
+
+#include "formats.cuh"
+#include "gemm_tc.h"
+#include "gemv.h"
+
+namespace llm {
+
+namespace tc {
+
+constexpr int A_ATOM_BYTES = 128 * 128;          // 128 weight rows x 64 bf16
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+LLM_DEVICE void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+LLM_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+LLM_DEVICE void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false once the limit is hit or another thread has raised the abort flag.
+LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 256) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+LLM_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+LLM_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+LLM_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// K-major, 128-byte swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+LLM_DEVICE uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);          // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+LLM_DEVICE void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+LLM_DEVICE void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+LLM_DEVICE void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BM> struct Cfg {
+    static constexpr int B_ATOM_BYTES = BM * 128;
+    static constexpr int STAGE_BYTES = A_ATOM_BYTES + B_ATOM_BYTES;
+    static constexpr int STAGES = BM <= 64 ? 8 : (BM <= 128 ? 6 : 4);
+    static constexpr int TMEM_COLS = BM < 32 ? 32 : BM;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;     // + slack for 1024-byte alignment
+};
+
+// Sink of the dequant warps: acquires ring stages atom by atom and publishes them to the MMA warp.
+template <int STAGES>
+struct RingSink {
+    uint32_t smem_base;      // first stage
+    int stage_bytes;
+    uint32_t full_bar, empty_bar;    // arrays of 8-byte barriers
+    int it0;                 // atom index of this chunk's first atom, counted from the CTA's first chunk
+    int row, lane;
+    volatile int* abort_flag;
+    bool ok;
+    LLM_DEVICE void begin(int a, int n) {
+        for (int i = 0; i < n; ++i) {
+            const int it = it0 + a + i;
+            const int stage = it % STAGES, phase = (it / STAGES) & 1;
+            if (ok) ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
+        }
+    }
+    LLM_DEVICE void emit(int kg, uint4 v) {
+        const int stage = (it0 + (kg >> 3)) % STAGES;
+        const uint32_t dst = smem_base + stage * stage_bytes + row * 128 + ((((kg & 7) ^ row) & 7) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+    LLM_DEVICE void end(int a, int n) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            for (int i = 0; i < n; ++i) mbar_arrive(full_bar + ((it0 + a + i) % STAGES) * 8);
+        }
+    }
+};
+
+template <int FMT, int BM>
+__global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmTcParams p) {
+    using C = Cfg<BM>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[C::STAGES];
+    __shared__ __align__(8) uint64_t s_empty[C::STAGES];
+    __shared__ __align__(8) uint64_t s_accum;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    __shared__ int s_last;
+    __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int k_blocks = p.k / 256;
+    const int per = (k_blocks + gridDim.z - 1) / gridDim.z;
+    const int kb0 = blockIdx.z * per, kb1 = min(k_blocks, kb0 + per);
+    const int n_it = max(kb1 - kb0, 0) * 4;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full_bar = smem_u32(s_full), empty_bar = smem_u32(s_empty), accum_bar = smem_u32(&s_accum);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar + s * 8, 5); mbar_init(empty_bar + s * 8, 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (FMT == FMT_IQ3_S) {
+        for (int i = tid; i < 512; i += blockDim.x) s_grid[i] = g_iq3s_grid[i];
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp < 8) {
+        // ------------------------------ dequant producers ------------------------------
+        const int g = warp & 3, set = warp >> 2;
+        const uint8_t* wtile = p.w + (size_t)tile_n * k_blocks * FmtTraits<FMT>::CHUNK;
+        RingSink<C::STAGES> sink{smem_base, C::STAGE_BYTES, full_bar, empty_bar, 0, g * 32 + lane, lane, abort_flag, true};
+        int kb = kb0 + set;
+        typename DequantBlock<FMT>::Regs regs;
+        if (kb < kb1) regs = DequantBlock<FMT>::load(wtile + (size_t)kb * FmtTraits<FMT>::CHUNK, g, lane);
+        for (; kb < kb1; kb += 2) {
+            typename DequantBlock<FMT>::Regs nxt = regs;
+            if (kb + 2 < kb1) nxt = DequantBlock<FMT>::load(wtile + (size_t)(kb + 2) * FmtTraits<FMT>::CHUNK, g, lane);
+            sink.it0 = (kb - kb0) * 4;
+            if constexpr (FMT == FMT_IQ3_S) DequantBlock<FMT>::process(regs, sink, s_grid);
+            else DequantBlock<FMT>::process(regs, sink);
+            regs = nxt;
+        }
+    } else if (warp == 8) {
+        // ------------------------------ TMA producer (activations) ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int stage = it % C::STAGES, phase = (it / C::STAGES) & 1;
+                ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_arrive_expect_tx(full_bar + stage * 8, C::B_ATOM_BYTES);
+                tma_load_2d(smem_base + stage * C::STAGE_BYTES + A_ATOM_BYTES, &tmap_x, kb0 * 256 + it * 64, tile_m * BM,
+                            full_bar + stage * 8);
+            }
+        }
+    } else {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BM);
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int stage = it % C::STAGES, phase = (it / C::STAGES) & 1;
+                ok = mbar_wait(full_bar + stage * 8, phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + stage * C::STAGE_BYTES;
+                const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + A_ATOM_BYTES);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    // advance 16 columns = 32 bytes inside the swizzle atom: +2 in the (addr >> 4) field
+                    mma_f16(tmem_base, adesc + 2 * k4, bdesc + 2 * k4, idesc, (it > 0 || k4 > 0) ? 1u : 0u);
+                }
+                mma_commit(empty_bar + stage * 8);
+            }
+            if (ok) mma_commit(accum_bar);
+        }
+    }
+
+    // ------------------------------ epilogue (warps 0-7) ------------------------------
+    bool live = warp < 8;
+    if (live && n_it > 0) live = mbar_wait(accum_bar, 0, abort_flag);
+    if (*abort_flag) live = false;
+    tc_fence_after();
+    const int q = warp & 3, half = (warp >> 2) & 1;
+    const int row_in_tile = q * 32 + lane;
+    const int n_row = tile_n * 128 + row_in_tile;
+    constexpr int HALF_COLS = BM / 2;
+    constexpr int CHUNKS = HALF_COLS / 16;
+    const bool split = gridDim.z > 1;
+    float* exch = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));   // reuse ring memory: [2][64][17]
+
+    auto finish = [&](int c0, float (&v)[16]) {
+        // v[i]: value for token m0 + c0 + i, output row n_row
+        const int m_base = tile_m * BM + c0;
+        if (p.epi == EPI_SWIGLU) {
+            float* ex = exch + half * 64 * 17;
+            if (q >= 2) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) ex[(row_in_tile - 64) * 17 + i] = v[i];
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (q < 2) {
+                const int col = tile_n * 64 + row_in_tile;
+                if (col < p.n / 2) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = m_base + i;
+                        if (m < p.m)
+                            static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] =
+                                __float2bfloat16(silu(v[i]) * ex[row_in_tile * 17 + i]);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            return;
+        }
+        if (n_row >= p.n) return;
+        const float b = p.bias ? p.bias[n_row] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int m = m_base + i;
+            if (m >= p.m) continue;
+            const size_t idx = (size_t)m * p.out_stride + n_row;
+            const float o = v[i] + b;
+            if (p.epi == EPI_RESID) { float* h = static_cast<float*>(p.out); h[idx] += o; }
+            else if (p.out_f32) static_cast<float*>(p.out)[idx] = o;
+            else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(o);
+        }
+    };
+
+    if (warp < 8 && !split) {
+        // SwiGLU needs every epilogue warp at its named barrier, so a dead pipeline still walks the loop
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int c0 = half * HALF_COLS + c * 16;
+            float v[16];
+            if (live && n_it > 0) {
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+            if (live || p.epi == EPI_SWIGLU) finish(c0, v);
+        }
+    }
+    if (split) {
+        if (warp < 8 && live && n_it > 0) {
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int c0 = half * HALF_COLS + c * 16;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int m = tile_m * BM + c0 + i;
+                    if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], __uint_as_float(r[i]));
+                }
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned t = atomicAdd(&p.tickets[tile_m * gridDim.x + tile_n], 1u);
+            s_last = (t == gridDim.z - 1);
+            if (s_last) p.tickets[tile_m * gridDim.x + tile_n] = 0u;
+        }
+        __syncthreads();
+        if (s_last && warp < 8) {
+            __threadfence();
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int c0 = half * HALF_COLS + c * 16;
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int m = tile_m * BM + c0 + i;
+                    v[i] = 0.f;
+                    if (m < p.m) {
+                        float* a = &p.accum[(size_t)m * p.accum_stride + n_row];
+                        v[i] = __ldcg(a);
+                        __stcg(a, 0.f);
+                    }
+                }
+                finish(c0, v);
+            }
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0 && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
+        // give copies that are still in flight time to land before this CTA's shared memory is handed on
+        for (int i = 0; i < 2000; ++i) __nanosleep(100);
+        __syncthreads();
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+template <int FMT, int BM>
+static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st) {
+    using C = Cfg<BM>;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.k * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.x), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    dim3 grid((p.n + 127) / 128, (p.m + BM - 1) / BM, ksplit);
+    gemm_tc_kernel<FMT, BM><<<grid, 320, C::SMEM_BYTES, st>>>(tmap, p);
+    return cudaGetLastError();
+}
+
+}  // namespace tc
+
+void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* ksplit) {
+    const int bm = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+    const int tiles = ((n + 127) / 128) * ((m + bm - 1) / bm);
+    const int kb = k / 256;
+    int ks = ksplit_hint;
+    if (ks <= 0) {
+        ks = 1;
+        if (tiles < 148) {
+            ks = (148 + tiles - 1) / tiles;
+            const int cap = kb / 2 > 0 ? kb / 2 : 1;      // at least two chunks per CTA
+            if (ks > cap) ks = cap;
+        }
+    }
+    if (ks > kb) ks = kb;
+    if (ks < 1) ks = 1;
+    *block_m = bm;
+    *ksplit = ks;
+}
+
+template <int FMT>
+static cudaError_t launch_fmt(const GemmTcParams& p, int bm, int ks, cudaStream_t st) {
+    switch (bm) {
+        case 32: return tc::launch_one<FMT, 32>(p, ks, st);
+        case 64: return tc::launch_one<FMT, 64>(p, ks, st);
+        case 128: return tc::launch_one<FMT, 128>(p, ks, st);
+        case 256: return tc::launch_one<FMT, 256>(p, ks, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
+    if (p.m <= 0) return cudaSuccess;
+    if (p.k % 256 || (reinterpret_cast<uintptr_t>(p.x) & 15)) return cudaErrorInvalidValue;
+    int bm, ks;
+    gemm_tc_plan(p.m, p.n, p.k, p.ksplit, &bm, &ks);
+    if (ks > 1 && (!p.accum || !p.tickets)) ks = 1;
+    switch (p.fmt) {
+        case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(p, bm, ks, st);
+        case FMT_Q5_K: return launch_fmt<FMT_Q5_K>(p, bm, ks, st);
+        case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(p, bm, ks, st);
+        case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(p, bm, ks, st);
+        case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(p, bm, ks, st);
+        case FMT_IQ3_S: return launch_fmt<FMT_IQ3_S>(p, bm, ks, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace llm

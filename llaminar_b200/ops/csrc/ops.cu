@@ -1,0 +1,542 @@
+// Memory-bound glue kernels: RMSNorm, fused QK-norm + RoPE + paged KV append, SwiGLU, sampling
+// (argmax, top-k/top-p, penalties), speculative-decode verification, MoE routing, NaN/Inf scan.
+// Reference counterparts: src/v2/kernels/cuda/ops/CUDARMSNormKernels.cu, CUDARoPEKernels.cu,
+// CUDAFusedOpsKernels.cu, CUDASamplingKernels.cu, src/v2/kernels/cuda/kvcache/CUDARingKVCache.cu
+// (ring append; here the cache is paged), src/v2/kernels/cuda/moe/CUDAMoEKernels.cu (softmax_topk),
+// src/v2/backends/cuda/CUDATensorValidation.cu.
+#include "common.cuh"
+#include "ops.h"
+
+namespace llm {
+
+constexpr int PAGE = 64;
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm: fp32 residual stream in, bf16 out
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ h, const float* __restrict__ w,
+                                                      __nv_bfloat16* __restrict__ out, int d, float eps) {
+    __shared__ float s_part[8];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float4* x4 = reinterpret_cast<const float4*>(h + (size_t)row * d);
+    float ss = 0.f;
+    for (int i = tid; i < d / 4; i += 256) {
+        const float4 v = x4[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    const float r = rsqrtf(tot / d + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    uint2* o2 = reinterpret_cast<uint2*>(out + (size_t)row * d);
+    for (int i = tid; i < d / 4; i += 256) {
+        const float4 v = x4[i], g = w4[i];
+        o2[i] = make_uint2(pack_bf16(v.x * r * g.x, v.y * r * g.y), pack_bf16(v.z * r * g.z, v.w * r * g.w));
+    }
+}
+
+cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    if (d % 4) return cudaErrorInvalidValue;
+    rmsnorm_kernel<<<rows, 256, 0, st>>>(h, w, out, d, eps);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// per-head QK RMSNorm + split-half RoPE + paged KV append: one warp per (token, head)
+// ------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKVParams p) {
+    constexpr int EPL = D / 64;                          // elements per lane in each half
+    const int lane = threadIdx.x & 31;
+    const int heads_total = p.n_heads + 2 * p.n_kv_heads;
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= p.n_tokens * heads_total) return;
+    const int t = item / heads_total, hh = item % heads_total;
+    const __nv_bfloat16* src = p.qkv + (size_t)t * heads_total * D + (size_t)hh * D;
+    const int pos = p.positions[t];
+    float a[EPL], b[EPL];                                // a: first half, b: second half
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        a[e] = __bfloat162float(src[lane * EPL + e]);
+        b[e] = __bfloat162float(src[D / 2 + lane * EPL + e]);
+    }
+    const bool is_q = hh < p.n_heads, is_k = !is_q && hh < p.n_heads + p.n_kv_heads;
+    if (is_q || is_k) {
+        const float* nw = is_q ? p.q_norm : p.k_norm;
+        if (nw) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) ss += a[e] * a[e] + b[e] * b[e];
+            ss = warp_sum(ss);
+            const float r = rsqrtf(ss / D + p.eps);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                a[e] *= r * nw[lane * EPL + e];
+                b[e] *= r * nw[D / 2 + lane * EPL + e];
+            }
+        }
+        const float l2t = log2f(p.theta);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            const int i = lane * EPL + e;
+            const float inv = exp2f(-(2.0f * i / D) * l2t);
+            float sn, cs;
+            sincosf(pos * inv, &sn, &cs);
+            const float x1 = a[e], x2 = b[e];
+            a[e] = x1 * cs - x2 * sn;
+            b[e] = x2 * cs + x1 * sn;
+        }
+    }
+    __nv_bfloat16* dst;
+    if (is_q) {
+        dst = p.q_out + ((size_t)t * p.n_heads + hh) * D;
+    } else {
+        const int kvh = is_k ? hh - p.n_heads : hh - p.n_heads - p.n_kv_heads;
+        const int seq = p.seq_ids[t];
+        const size_t page = (size_t)p.block_table[(size_t)seq * p.max_pages + pos / PAGE];
+        dst = p.kv + ((page * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)(pos % PAGE) * D;
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        dst[lane * EPL + e] = __float2bfloat16(a[e]);
+        dst[D / 2 + lane * EPL + e] = __float2bfloat16(b[e]);
+    }
+}
+
+cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st) {
+    const int items = p.n_tokens * (p.n_heads + 2 * p.n_kv_heads);
+    if (items == 0) return cudaSuccess;
+    const int grid = (items + 3) / 4;
+    if (p.head_dim == 128) rope_kv_kernel<128><<<grid, 128, 0, st>>>(p);
+    else if (p.head_dim == 64) rope_kv_kernel<64><<<grid, 128, 0, st>>>(p);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU over the tile-interleaved gate|up GEMM output; residual add
+// ------------------------------------------------------------------------------------------------
+__global__ void swiglu_tiled_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int d_ff) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;     // one thread per 2 output columns
+    const int half = d_ff / 2;
+    if (i >= (size_t)rows * half) return;
+    const int r = i / half, c = (i % half) * 2;
+    const int tile = c / 64, off = c % 64;
+    const __nv_bfloat16* base = gu + (size_t)r * 2 * d_ff + tile * 128;
+    const uint32_t g = *reinterpret_cast<const uint32_t*>(base + off);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(base + 64 + off);
+    *reinterpret_cast<uint32_t*>(out + (size_t)r * d_ff + c) = pack_bf16(silu(bf16_lo(g)) * bf16_lo(u), silu(bf16_hi(g)) * bf16_hi(u));
+}
+cudaError_t launch_swiglu_tiled(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int d_ff, cudaStream_t st) {
+    const size_t n = (size_t)rows * d_ff / 2;
+    if (n == 0) return cudaSuccess;
+    swiglu_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(gu, out, rows, d_ff);
+    return cudaGetLastError();
+}
+
+__global__ void add_bf16_to_f32_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ x, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i + 1 < n) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(x + i);
+        float2 a = *reinterpret_cast<float2*>(h + i);
+        a.x += bf16_lo(v); a.y += bf16_hi(v);
+        *reinterpret_cast<float2*>(h + i) = a;
+    } else if (i < n) {
+        h[i] += __bfloat162float(x[i]);
+    }
+}
+cudaError_t launch_add_bf16_to_f32(float* h, const __nv_bfloat16* x, size_t n, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    add_bf16_to_f32_kernel<<<(unsigned)((n / 2 + 256) / 256), 256, 0, st>>>(h, x, n);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// sampling
+// ------------------------------------------------------------------------------------------------
+LLM_DEVICE uint32_t order_key(float f) {                 // monotone float -> uint map
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+LLM_DEVICE float key_to_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+LLM_DEVICE uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+LLM_DEVICE float uniform01(uint64_t seed, uint64_t ctr) {
+    return (splitmix64(seed ^ splitmix64(ctr)) >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int vocab, int stride, int* __restrict__ tokens) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const float* row = logits + (size_t)blockIdx.x * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += 1024) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = best; s_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = s_v[threadIdx.x]; bi = s_i[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) tokens[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, float*, int*, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, vocab, stride, tokens);
+    return cudaGetLastError();
+}
+
+// top-k (radix select) -> sort candidates -> softmax -> top-p cut -> inverse-CDF sample.  One CTA per row.
+constexpr int MAX_CAND = 1024;
+__global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
+    __shared__ unsigned s_hist[256];
+    __shared__ unsigned long long s_keys[MAX_CAND];
+    __shared__ float s_scan[MAX_CAND];
+    __shared__ unsigned s_prefix, s_need, s_count, s_eq_count;
+    __shared__ float s_warp[32];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* lg = p.logits + (size_t)row * p.stride;
+    const float temp = p.temperature ? p.temperature[row] : 1.0f;
+    int k = p.top_k ? p.top_k[row] : 0;
+    const float top_p = p.top_p ? p.top_p[row] : 1.0f;
+    const bool greedy = temp <= 0.f || k == 1;
+    if (k <= 0 || k > MAX_CAND) k = MAX_CAND;
+    if (k > p.vocab) k = p.vocab;
+    if (greedy) k = 1;
+    // ---- radix select of the k-th largest key ----
+    if (tid == 0) { s_prefix = 0; s_need = k; }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) s_hist[tid] = 0;
+        __syncthreads();
+        const unsigned prefix = s_prefix;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = tid; i < p.vocab; i += 1024) {
+            const unsigned key = order_key(lg[i]);
+            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 0xff], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned need = s_need, b = 255;
+            for (;; --b) {
+                const unsigned c = s_hist[b];
+                if (c >= need || b == 0) break;
+                need -= c;
+            }
+            s_prefix = prefix | (b << shift);
+            s_need = need;
+        }
+        __syncthreads();
+    }
+    const unsigned thr = s_prefix;              // key of the k-th largest element
+    const unsigned eq_quota = s_need;           // how many elements equal to thr are still needed
+    if (tid == 0) { s_count = 0; s_eq_count = 0; }
+    for (int i = tid; i < MAX_CAND; i += 1024) s_keys[i] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < p.vocab; i += 1024) {
+        const unsigned key = order_key(lg[i]);
+        bool take = key > thr;
+        if (key == thr) take = atomicAdd(&s_eq_count, 1u) < eq_quota;
+        if (take) {
+            const unsigned slot = atomicAdd(&s_count, 1u);
+            if (slot < MAX_CAND) s_keys[slot] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i);
+        }
+    }
+    __syncthreads();
+    // ---- bitonic sort, descending (largest key first; ties -> lower token id first) ----
+    for (int size = 2; size <= MAX_CAND; size <<= 1) {
+        for (int strd = size >> 1; strd > 0; strd >>= 1) {
+            const int i = tid, j = i ^ strd;
+            if (j > i) {
+                const unsigned long long a = s_keys[i], b = s_keys[j];
+                const bool desc = (i & size) == 0;
+                if ((a < b) == desc) { s_keys[i] = b; s_keys[j] = a; }
+            }
+            __syncthreads();
+        }
+    }
+    const int n = min((int)s_count, k);
+    if (p.probs_out) {
+        float* po = p.probs_out + (size_t)row * p.vocab;
+        for (int i = tid; i < p.vocab; i += 1024) po[i] = 0.f;
+    }
+    __syncthreads();
+    if (greedy) {
+        if (tid == 0) {
+            const int tok = (int)(0xffffffffu - (unsigned)(s_keys[0] & 0xffffffffu));
+            p.tokens[row] = tok;
+            if (p.probs_out) p.probs_out[(size_t)row * p.vocab + tok] = 1.0f;
+        }
+        return;
+    }
+    // ---- softmax over candidates (temperature applied here), inclusive scan ----
+    const float vmax = key_to_float((unsigned)(s_keys[0] >> 32));
+    float pr = 0.f;
+    if (tid < n) pr = __expf((key_to_float((unsigned)(s_keys[tid] >> 32)) - vmax) / temp);
+    float sc = pr;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, sc, o);
+        if ((tid & 31) >= o) sc += t;
+    }
+    if ((tid & 31) == 31) s_warp[tid >> 5] = sc;
+    __syncthreads();
+    if (tid < 32) {
+        float w = s_warp[tid];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, w, o);
+            if (tid >= o) w += t;
+        }
+        s_warp[tid] = w;
+    }
+    __syncthreads();
+    const float incl = sc + ((tid >> 5) > 0 ? s_warp[(tid >> 5) - 1] : 0.f);
+    const float total = s_warp[31];
+    // top-p: keep candidate i while the mass before it is < top_p * total (always keeps the first)
+    const float before = incl - pr;
+    const bool keep = tid < n && (top_p >= 1.0f || before < top_p * total || tid == 0);
+    s_scan[tid] = keep ? incl : -1.0f;
+    __syncthreads();
+    // kept candidates form a prefix; its last inclusive value is the new normaliser
+    __shared__ float s_z;
+    __shared__ int s_nkeep;
+    if (tid < n && keep && (tid == n - 1 || s_scan[tid + 1] < 0.f)) { s_z = incl; s_nkeep = tid + 1; }
+    __syncthreads();
+    const float z = s_z;
+    const int nkeep = s_nkeep;
+    if (p.probs_out && tid < nkeep) {
+        const int tok = (int)(0xffffffffu - (unsigned)(s_keys[tid] & 0xffffffffu));
+        p.probs_out[(size_t)row * p.vocab + tok] = pr / z;
+    }
+    const float u = uniform01(p.seeds ? p.seeds[row] : 0ull, (uint64_t)(p.step ? p.step[row] : 0)) * z;
+    // first kept candidate whose inclusive mass reaches u
+    __shared__ int s_pick;
+    if (tid == 0) s_pick = nkeep - 1;
+    __syncthreads();
+    if (tid < nkeep && incl >= u && (tid == 0 || before < u)) atomicMin(&s_pick, tid);
+    __syncthreads();
+    if (tid == 0) p.tokens[row] = (int)(0xffffffffu - (unsigned)(s_keys[s_pick] & 0xffffffffu));
+}
+cudaError_t launch_sample(const SampleParams& p, cudaStream_t st) {
+    if (p.rows == 0) return cudaSuccess;
+    sample_kernel<<<p.rows, 1024, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+__global__ void penalties_kernel(float* logits, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
+                                 const int* hist_offsets, const float* presence, const float* frequency) {
+    const int row = blockIdx.x;
+    const int b = hist_offsets[row], e = hist_offsets[row + 1];
+    const float pp = presence ? presence[row] : 0.f, fp = frequency ? frequency[row] : 0.f;
+    for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+        const int tok = hist_tokens[i];
+        if (tok >= 0 && tok < vocab) logits[(size_t)row * stride + tok] -= pp + fp * hist_counts[i];
+    }
+}
+cudaError_t launch_penalties(float* logits, int rows, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
+                             const int* hist_offsets, const float* presence, const float* frequency, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    penalties_kernel<<<rows, 256, 0, st>>>(logits, vocab, stride, hist_tokens, hist_counts, hist_offsets, presence, frequency);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// NaN / Inf scan
+// ------------------------------------------------------------------------------------------------
+__global__ void nan_scan_kernel(const void* x, size_t n, int dtype, int* counts) {
+    int nn = 0, ni = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = dtype == 0 ? static_cast<const float*>(x)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]);
+        nn += isnan(v) ? 1 : 0;
+        ni += isinf(v) ? 1 : 0;
+    }
+    nn = __reduce_add_sync(0xffffffffu, nn);
+    ni = __reduce_add_sync(0xffffffffu, ni);
+    if ((threadIdx.x & 31) == 0) {
+        if (nn) atomicAdd(&counts[0], nn);
+        if (ni) atomicAdd(&counts[1], ni);
+    }
+}
+cudaError_t launch_nan_scan(const void* x, size_t n, int dtype, int* counts, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    const unsigned grid = (unsigned)min((size_t)1184, (n + 255) / 256);
+    nan_scan_kernel<<<grid, 256, 0, st>>>(x, n, dtype, counts);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// speculative decoding verification
+// ------------------------------------------------------------------------------------------------
+__global__ void spec_verify_greedy_kernel(const int* draft, const int* target, int batch, int depth, int* n_accept, int* out_tokens) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    int n = 0;
+    while (n < depth && draft[b * depth + n] == target[b * (depth + 1) + n]) ++n;
+    n_accept[b] = n;
+    for (int i = 0; i <= depth; ++i) out_tokens[b * (depth + 1) + i] = i <= n ? target[b * (depth + 1) + i] : -1;
+}
+cudaError_t launch_spec_verify_greedy(const int* draft, const int* target, int batch, int depth, int* n_accept,
+                                      int* out_tokens, cudaStream_t st) {
+    if (batch == 0) return cudaSuccess;
+    spec_verify_greedy_kernel<<<(batch + 63) / 64, 64, 0, st>>>(draft, target, batch, depth, n_accept, out_tokens);
+    return cudaGetLastError();
+}
+
+// block-wide inverse-CDF sample from w[i] = max(a[i] - b[i], 0) (b may be null); returns the index to all threads
+LLM_DEVICE int block_sample_residual(const float* a, const float* b, int vocab, float u01, float* s_buf /*[blockDim.x + 1]*/) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int seg = (vocab + nt - 1) / nt;
+    const int lo = min(tid * seg, vocab), hi = min(lo + seg, vocab);
+    float s = 0.f;
+    for (int i = lo; i < hi; ++i) s += fmaxf(a[i] - (b ? b[i] : 0.f), 0.f);
+    s_buf[tid] = s;
+    __syncthreads();
+    if (tid == 0) {                    // serial scan over <= 1024 partials: negligible next to the vocab pass
+        float run = 0.f;
+        for (int t = 0; t < nt; ++t) { const float v = s_buf[t]; s_buf[t] = run; run += v; }
+        s_buf[nt] = run;
+    }
+    __syncthreads();
+    const float total = s_buf[nt];
+    __shared__ int s_idx;
+    if (tid == 0) s_idx = -1;
+    __syncthreads();
+    if (total > 0.f) {
+        const float target = u01 * total;
+        const float mine = s_buf[tid];
+        const float next = (tid + 1 < nt) ? s_buf[tid + 1] : total;
+        if (hi > lo && target >= mine && (target < next || tid == nt - 1 || next >= total)) {
+            float run = mine;
+            int pick = -1;
+            for (int i = lo; i < hi; ++i) {
+                const float w = fmaxf(a[i] - (b ? b[i] : 0.f), 0.f);
+                run += w;
+                if (w > 0.f) { pick = i; if (run > target) break; }
+            }
+            if (pick >= 0) atomicMax(&s_idx, pick);
+        }
+    }
+    __syncthreads();
+    int r = s_idx;
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(1024) spec_verify_reject_kernel(const SpecRejectParams p) {
+    __shared__ float s_buf[1025];
+    const int b = blockIdx.x;
+    const uint64_t seed = p.seeds ? p.seeds[b] : 0ull;
+    const uint64_t step = p.step ? (uint64_t)p.step[b] : 0ull;
+    int n = 0;
+    for (; n < p.depth; ++n) {
+        const int x = p.draft[b * p.depth + n];
+        const float pt = p.p_target[((size_t)b * (p.depth + 1) + n) * p.vocab + x];
+        const float pd = p.p_draft[((size_t)b * p.depth + n) * p.vocab + x];
+        const float r = uniform01(seed, step * 64 + 2 * n + 1);
+        const bool accept = pd <= 0.f ? pt > 0.f : r * pd < pt;        // r < min(1, pt / pd)
+        if (!accept) break;
+        if (threadIdx.x == 0) p.out_tokens[b * (p.depth + 1) + n] = x;
+    }
+    const float* pt = p.p_target + ((size_t)b * (p.depth + 1) + n) * p.vocab;
+    const float* pd = n < p.depth ? p.p_draft + ((size_t)b * p.depth + n) * p.vocab : nullptr;
+    int tok = block_sample_residual(pt, pd, p.vocab, uniform01(seed, step * 64 + 2 * n + 2), s_buf);
+    if (tok < 0) tok = block_sample_residual(pt, nullptr, p.vocab, uniform01(seed, step * 64 + 2 * n + 2), s_buf);
+    if (threadIdx.x == 0) {
+        p.out_tokens[b * (p.depth + 1) + n] = tok < 0 ? 0 : tok;
+        for (int i = n + 1; i <= p.depth; ++i) p.out_tokens[b * (p.depth + 1) + i] = -1;
+        p.n_accept[b] = n;
+    }
+}
+cudaError_t launch_spec_verify_reject(const SpecRejectParams& p, cudaStream_t st) {
+    if (p.batch == 0) return cudaSuccess;
+    spec_verify_reject_kernel<<<p.batch, 1024, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// MoE router: softmax over all experts, top-k (ties -> lower id), optional renormalisation.
+// One warp per token, up to 256 experts.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int tokens, int n_experts, int k, int renorm,
+                                                       int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    constexpr int PER = 8;
+    float v[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = j * 32 + lane;
+        v[j] = e < n_experts ? logits[(size_t)t * n_experts + e] : -INFINITY;
+        mx = fmaxf(mx, v[j]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { v[j] = (j * 32 + lane) < n_experts ? __expf(v[j] - mx) : -1.0f; sum += fmaxf(v[j], 0.f); }
+    sum = warp_sum(sum);
+    float wsum = 0.f;
+    float my_w = 0.f;
+    int my_id = 0;
+    for (int s = 0; s < k; ++s) {
+        float best = -1.0f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int e = j * 32 + lane;
+            if (v[j] > best || (v[j] == best && e < bi)) { best = v[j]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) v[bi >> 5] = -2.0f;          // remove the winner
+        const float pw = best / sum;
+        wsum += pw;
+        if (lane == s) { my_w = pw; my_id = bi; }
+    }
+    if (lane < k) {
+        ids[(size_t)t * k + lane] = my_id;
+        weights[(size_t)t * k + lane] = renorm ? my_w / wsum : my_w;
+        if (counts) atomicAdd(&counts[my_id], 1);
+    }
+}
+cudaError_t launch_moe_topk(const float* logits, int tokens, int n_experts, int k, int renorm, int* ids, float* weights,
+                            int* counts, cudaStream_t st) {
+    if (tokens == 0) return cudaSuccess;
+    if (n_experts > 256 || k > 32) return cudaErrorInvalidValue;
+    moe_topk_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(logits, tokens, n_experts, k, renorm, ids, weights, counts);
+    return cudaGetLastError();
+}
+
+}  // namespace llm

@@ -1,0 +1,93 @@
+// Launchers of the non-GEMM kernels (attention, norms, RoPE + KV append, sampling, debug scans).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace llm {
+
+struct AttnDecodeParams {
+    const __nv_bfloat16* q;        // [batch * rows_per_seq, n_heads, head_dim]
+    const __nv_bfloat16* kv;       // [n_pages, 2, n_kv_heads, 64, head_dim]
+    __nv_bfloat16* out;            // same shape as q
+    const int* block_table;        // [batch, max_pages]
+    const int* seq_lens;           // [batch] tokens in the cache including the rows of this step
+    float* part_o;                 // split scratch [batch, n_kv_heads, splits, 16, head_dim]
+    float* part_ml;                // split scratch [batch, n_kv_heads, splits, 16, 2]
+    unsigned* tickets;             // [batch * n_kv_heads], zero between calls
+    int n_heads, n_kv_heads, head_dim, max_pages, rows_per_seq;
+    float scale;
+};
+
+struct AttnPrefillParams {
+    const __nv_bfloat16* q;        // [total_q, n_heads, head_dim]
+    const __nv_bfloat16* kv;
+    __nv_bfloat16* out;
+    const int* block_table;        // [n_seqs, max_pages]
+    const int* cu_q;               // [n_seqs + 1] prefix sums of query rows
+    const int* ctx_lens;           // [n_seqs] tokens already cached before this chunk
+    int n_heads, n_kv_heads, head_dim, max_pages;
+    float scale;
+};
+
+int attn_decode_pick_splits(int batch, int n_kv_heads, int max_pages_in_use);
+cudaError_t launch_attn_decode(const AttnDecodeParams& p, int batch, int n_splits, cudaStream_t st);
+cudaError_t launch_attn_prefill(const AttnPrefillParams& p, int n_seqs, int max_q_len, cudaStream_t st);
+
+struct RopeKVParams {
+    __nv_bfloat16* qkv;            // [T, (n_heads + 2 n_kv_heads) * head_dim]; Q part is rewritten in place
+    __nv_bfloat16* q_out;          // [T, n_heads, head_dim]
+    __nv_bfloat16* kv;             // paged cache of this layer
+    const float* q_norm;           // [head_dim] or nullptr
+    const float* k_norm;
+    const int* positions;          // [T]
+    const int* seq_ids;            // [T] row of block_table for each token
+    const int* block_table;        // [n_seqs, max_pages]
+    int n_tokens, n_heads, n_kv_heads, head_dim, max_pages;
+    float theta, eps;
+};
+cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st);
+
+// h (+= delta) ; out = RMSNorm(h) * w   (fp32 residual stream, bf16 normalised output)
+cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st);
+// out[t, c] = silu(gate) * up, reading a gate|up GEMM output whose 128-column tiles hold 64 gate + 64 up columns
+cudaError_t launch_swiglu_tiled(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int d_ff, cudaStream_t st);
+cudaError_t launch_add_bf16_to_f32(float* h, const __nv_bfloat16* x, size_t n, cudaStream_t st);
+
+// greedy: argmax of each row -> tokens[row]
+cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, float* scratch_val,
+                          int* scratch_idx, cudaStream_t st);
+struct SampleParams {
+    const float* logits; int rows, vocab, stride;
+    const float* temperature;      // [rows]
+    const int* top_k;              // [rows] (0 = off)
+    const float* top_p;            // [rows] (>= 1 = off)
+    const uint64_t* seeds;         // [rows]
+    const int* step;               // [rows] decode step counter mixed into the RNG
+    int* tokens;                   // [rows]
+    float* probs_out;              // optional [rows, vocab] final distribution (speculative sampling)
+};
+cudaError_t launch_sample(const SampleParams& p, cudaStream_t st);
+cudaError_t launch_penalties(float* logits, int rows, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
+                             const int* hist_offsets, const float* presence, const float* frequency, cudaStream_t st);
+// counts[0] = #NaN, counts[1] = #Inf
+cudaError_t launch_nan_scan(const void* x, size_t n, int dtype /*0 f32, 1 bf16*/, int* counts, cudaStream_t st);
+
+// speculative decoding: greedy verify. draft [B, d], target_tokens [B, d+1] -> n_accept[B], out_tokens [B, d+1]
+cudaError_t launch_spec_verify_greedy(const int* draft, const int* target, int batch, int depth, int* n_accept,
+                                      int* out_tokens, cudaStream_t st);
+struct SpecRejectParams {
+    const float* p_target;         // [B, d+1, vocab] target distributions
+    const float* p_draft;          // [B, d, vocab] draft distributions
+    const int* draft;              // [B, d]
+    const uint64_t* seeds; const int* step;
+    int batch, depth, vocab;
+    int* n_accept; int* out_tokens;   // [B], [B, d+1]
+};
+cudaError_t launch_spec_verify_reject(const SpecRejectParams& p, cudaStream_t st);
+
+// MoE router: logits [T, E] fp32 -> top-k ids / renormalised weights
+cudaError_t launch_moe_topk(const float* logits, int tokens, int n_experts, int k, int renorm, int* ids, float* weights,
+                            int* counts, cudaStream_t st);
+
+}  // namespace llm

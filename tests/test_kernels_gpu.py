@@ -1,0 +1,290 @@
+"""CUDA kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+from llaminar_b200.gguf import GGMLType, dequantize, quantize
+from llaminar_b200.models.reference import rmsnorm as ref_rmsnorm, rope_split_half
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FORMATS = [GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.IQ3_S]
+
+
+def _weight(qt, n, k, seed=0):
+    from llaminar_b200 import ops
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    w = torch.randn(n, k, generator=g, device=DEV) * 0.05
+    raw = quantize(w, qt)
+    wf = dequantize(raw, qt, (n, k))
+    return ops.pack_matrix(raw, qt, n, k), wf
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12)).item()
+
+
+@pytest.mark.parametrize("qt", FORMATS)
+def test_dequant_matches_codec(qt):
+    from llaminar_b200 import ops
+    pw, wf = _weight(qt, 200, 512)
+    out = ops.dequant(pw)
+    torch.cuda.synchronize()
+    assert _rel(out, wf) < 6e-3          # bf16 rounding only
+    rows = torch.tensor([3, 199, 128, 0, 77], dtype=torch.int32, device=DEV)
+    g32 = torch.empty(5, 512, dtype=torch.float32, device=DEV)
+    ops.gather_rows(pw, rows, g32)
+    assert _rel(g32, wf[rows.long()]) < 6e-3
+
+
+@pytest.mark.parametrize("qt", FORMATS)
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+def test_gemv_plain_and_norm(qt, m):
+    from llaminar_b200 import ops
+    n, k = 384, 1024
+    pw, wf = _weight(qt, n, k, seed=m)
+    sc = ops.scratch_for(DEV)
+    x = torch.randn(m, k, device=DEV)
+    xb = x.to(torch.bfloat16)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    bias = torch.randn(n, device=DEV)
+    for ks in (1, 0, 2):
+        ops.gemv(pw, xb, out, bias=bias, scratch=sc, ksplit=ks)
+        ref = xb.float() @ wf.T + bias
+        assert _rel(out, ref) < 2e-2, (qt, m, ks)
+    # fused RMSNorm prologue + residual epilogue
+    gain = torch.rand(k, device=DEV) + 0.5
+    h = torch.randn(m, n, device=DEV)
+    h0 = h.clone()
+    ops.gemv(pw, x, h, norm_w=gain, eps=1e-6, epi=ops.EPI_RESID, scratch=sc)
+    ref = h0 + ref_rmsnorm(x, gain, 1e-6) @ wf.T
+    assert _rel(h, ref) < 2e-2
+    assert int(sc.tickets.abs().sum()) == 0 and float(sc.accum.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("qt", [GGMLType.Q4_K, GGMLType.Q8_0])
+def test_gemv_swiglu(qt):
+    from llaminar_b200 import ops
+    from llaminar_b200.ops.layout import interleave_gate_up
+    d_ff, k = 256, 512
+    g = torch.Generator(device=DEV).manual_seed(5)
+    wg = torch.randn(d_ff, k, generator=g, device=DEV) * 0.05
+    wu = torch.randn(d_ff, k, generator=g, device=DEV) * 0.05
+    rg, ru = quantize(wg, qt), quantize(wu, qt)
+    raw, _, n2, _ = interleave_gate_up(rg, ru, qt, d_ff, k)
+    pw = ops.pack_matrix(raw, qt, n2, k)
+    x = torch.randn(2, k, device=DEV).to(torch.bfloat16)
+    out = torch.empty(2, d_ff, dtype=torch.bfloat16, device=DEV)
+    ops.gemv(pw, x, out, epi=ops.EPI_SWIGLU, scratch=ops.scratch_for(DEV))
+    gf, uf = dequantize(rg, qt, (d_ff, k)), dequantize(ru, qt, (d_ff, k))
+    ref = torch.nn.functional.silu(x.float() @ gf.T) * (x.float() @ uf.T)
+    assert _rel(out, ref) < 3e-2
+
+
+@pytest.mark.parametrize("qt", FORMATS)
+@pytest.mark.parametrize("m", [5, 32, 100, 300])
+def test_gemm_tc(qt, m):
+    from llaminar_b200 import ops
+    n, k = 384, 1024
+    pw, wf = _weight(qt, n, k, seed=7)
+    sc = ops.scratch_for(DEV)
+    sc.status.zero_()
+    x = (torch.randn(m, k, device=DEV)).to(torch.bfloat16)
+    ref = x.float() @ wf.T
+    for ks in (1, 2, 0):
+        out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.gemm(pw, x, out, scratch=sc, ksplit=ks)
+        torch.cuda.synchronize()
+        assert int(sc.status[0]) == 0, "pipeline wait timed out"
+        assert _rel(out, ref) < 1.2e-2, (qt, m, ks)
+    h = torch.randn(m, n, device=DEV)
+    h0 = h.clone()
+    bias = torch.randn(n, device=DEV)
+    ops.gemm(pw, x, h, epi=ops.EPI_RESID, bias=bias, scratch=sc)
+    assert _rel(h, h0 + ref + bias) < 1.2e-2
+    assert int(sc.tickets.abs().sum()) == 0 and float(sc.accum.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("m", [16, 200])
+def test_gemm_tc_swiglu_large_k(m):
+    from llaminar_b200 import ops
+    from llaminar_b200.ops.layout import interleave_gate_up
+    qt, d_ff, k = GGMLType.Q4_K, 512, 4096
+    g = torch.Generator(device=DEV).manual_seed(11)
+    wg = torch.randn(d_ff, k, generator=g, device=DEV) * 0.03
+    wu = torch.randn(d_ff, k, generator=g, device=DEV) * 0.03
+    rg, ru = quantize(wg, qt), quantize(wu, qt)
+    raw, _, n2, _ = interleave_gate_up(rg, ru, qt, d_ff, k)
+    pw = ops.pack_matrix(raw, qt, n2, k)
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    out = torch.empty(m, d_ff, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(pw, x, out, epi=ops.EPI_SWIGLU, scratch=ops.scratch_for(DEV))
+    gf, uf = dequantize(rg, qt, (d_ff, k)), dequantize(ru, qt, (d_ff, k))
+    ref = torch.nn.functional.silu(x.float() @ gf.T) * (x.float() @ uf.T)
+    assert _rel(out, ref) < 2e-2
+
+
+def test_rmsnorm_and_swiglu():
+    from llaminar_b200 import ops
+    h = torch.randn(37, 1024, device=DEV)
+    w = torch.rand(1024, device=DEV) + 0.5
+    out = torch.empty(37, 1024, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(h, w, out, 1e-6)
+    assert _rel(out, ref_rmsnorm(h, w, 1e-6)) < 5e-3
+    gu = torch.randn(9, 256, device=DEV).to(torch.bfloat16)
+    o = torch.empty(9, 128, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu_tiled(gu, o)
+    t = gu.float().view(9, 2, 2, 64)
+    ref = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(9, 128)
+    assert _rel(o, ref) < 1e-2
+
+
+def _paged_setup(B, ctx_lens, n_kv, D, extra_pages=3):
+    pages_per = [(c + 63) // 64 for c in ctx_lens]
+    max_pages = max(pages_per) + 1
+    n_pages = sum(pages_per) + extra_pages + B
+    perm = torch.randperm(n_pages)[: B * max_pages].reshape(B, max_pages).to(torch.int32).to(DEV)
+    kv = torch.zeros(n_pages, 2, n_kv, 64, D, dtype=torch.bfloat16, device=DEV)
+    return kv, perm, max_pages
+
+
+@pytest.mark.parametrize("D,nq,nkv", [(128, 32, 8), (64, 4, 2), (128, 64, 8)])
+def test_rope_kv_and_attention(D, nq, nkv):
+    from llaminar_b200 import ops
+    torch.manual_seed(0)
+    B = 3
+    q_lens = [70, 129, 5]
+    kv, btab, max_pages = _paged_setup(B, [l + 3 for l in q_lens], nkv, D)
+    T = sum(q_lens)
+    qkv = (torch.randn(T, (nq + 2 * nkv) * D, device=DEV) * 0.5).to(torch.bfloat16)
+    qn = torch.rand(D, device=DEV) + 0.5
+    kn = torch.rand(D, device=DEV) + 0.5
+    pos = torch.cat([torch.arange(l) for l in q_lens]).to(torch.int32).to(DEV)
+    sid = torch.cat([torch.full((l,), i) for i, l in enumerate(q_lens)]).to(torch.int32).to(DEV)
+    q_out = torch.empty(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    ops.rope_kv(qkv.clone(), q_out, kv, qn, kn, pos, sid, btab, nq, nkv, D, 1e6, 1e-6)
+    # reference
+    x = qkv.float().view(T, nq + 2 * nkv, D)
+    qr = rope_split_half(ref_rmsnorm(x[:, :nq], qn, 1e-6), pos, 1e6)
+    kr = rope_split_half(ref_rmsnorm(x[:, nq:nq + nkv], kn, 1e-6), pos, 1e6)
+    vr = x[:, nq + nkv:]
+    assert _rel(q_out, qr) < 6e-3
+    # prefill attention
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ctx = torch.zeros(B, dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    ops.attn_prefill(q_out, kv, out, btab, cu, ctx, nq, nkv, D, scale, max(q_lens))
+    g = nq // nkv
+    s0 = 0
+    for b, L in enumerate(q_lens):
+        qb, kb, vb = qr[s0:s0 + L], kr[s0:s0 + L].repeat_interleave(g, 1), vr[s0:s0 + L].repeat_interleave(g, 1)
+        sc = torch.einsum("thd,shd->hts", qb, kb) * scale
+        mask = torch.ones(L, L, device=DEV).tril().bool()
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        ref = torch.einsum("hts,shd->thd", sc.softmax(-1), vb)
+        assert _rel(out[s0:s0 + L], ref) < 2e-2, (b, L)
+        s0 += L
+    # decode: one new token per sequence on top of the cached prompt, R rows
+    for R in (1, 2 if g * 2 <= 16 else 1):
+        newq = (torch.randn(B * R, (nq + 2 * nkv) * D, device=DEV) * 0.5).to(torch.bfloat16)
+        pos2 = torch.cat([torch.arange(L, L + R) for L in q_lens]).to(torch.int32).to(DEV)
+        sid2 = torch.arange(B).repeat_interleave(R).to(torch.int32).to(DEV)
+        kv2 = kv.clone()
+        qd = torch.empty(B * R, nq, D, dtype=torch.bfloat16, device=DEV)
+        ops.rope_kv(newq.clone(), qd, kv2, qn, kn, pos2, sid2, btab, nq, nkv, D, 1e6, 1e-6)
+        seq_lens = torch.tensor([L + R for L in q_lens], dtype=torch.int32, device=DEV)
+        xd = newq.float().view(B * R, nq + 2 * nkv, D)
+        qd_ref = rope_split_half(ref_rmsnorm(xd[:, :nq], qn, 1e-6), pos2, 1e6)
+        kd_ref = rope_split_half(ref_rmsnorm(xd[:, nq:nq + nkv], kn, 1e-6), pos2, 1e6)
+        vd_ref = xd[:, nq + nkv:]
+        for splits in (1, 2, 3):
+            od = torch.empty(B * R, nq, D, dtype=torch.bfloat16, device=DEV)
+            ops.attn_decode(qd, kv2, od, btab, seq_lens, nq, nkv, D, R, scale, splits, ops.scratch_for(DEV))
+            s0 = 0
+            for b, L in enumerate(q_lens):
+                for r in range(R):
+                    K = torch.cat([kr[s0:s0 + L], kd_ref[b * R:b * R + r + 1]]).repeat_interleave(g, 1)
+                    V = torch.cat([vr[s0:s0 + L], vd_ref[b * R:b * R + r + 1]]).repeat_interleave(g, 1)
+                    sc = torch.einsum("hd,shd->hs", qd_ref[b * R + r], K) * scale
+                    ref = torch.einsum("hs,shd->hd", sc.softmax(-1), V)
+                    assert _rel(od[b * R + r], ref) < 2e-2, (R, splits, b, r)
+                s0 += L
+        assert int(ops.scratch_for(DEV).attn_tickets.abs().sum()) == 0
+
+
+def test_sampling_kernels():
+    from llaminar_b200 import ops
+    torch.manual_seed(0)
+    rows, vocab = 6, 5000
+    logits = torch.randn(rows, vocab, device=DEV) * 3
+    tok = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, tok)
+    assert tok.tolist() == logits.argmax(-1).tolist()
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.0, 1.0, 1.0], device=DEV)
+    top_k = torch.tensor([0, 1, 5, 50, 0, 40], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.5, 0.9, 0.9], device=DEV)
+    seeds = torch.arange(rows, dtype=torch.int64, device=DEV) + 123
+    probs = torch.empty(rows, vocab, device=DEV)
+    counts = torch.zeros(rows, vocab, device=DEV)
+    for step in range(200):
+        st = torch.full((rows,), step, dtype=torch.int32, device=DEV)
+        ops.sample(logits, temp, top_k, top_p, seeds, st, tok, probs)
+        counts[torch.arange(rows), tok.long()] += 1
+    am = logits.argmax(-1)
+    assert counts[0, am[0]] == 200 and counts[1, am[1]] == 200          # greedy rows
+    assert (counts[2] > 0).sum() <= 5                                   # top-k 5
+    top5 = logits[2].topk(5).indices
+    assert counts[2, top5].sum() == 200
+    # distribution returned for row 2 equals softmax over the top-5 at temperature 0.7
+    ref = torch.zeros(vocab, device=DEV)
+    ref[top5] = torch.softmax(logits[2, top5] / 0.7, -1)
+    assert torch.allclose(probs[2], ref, atol=1e-4)
+    assert abs(probs[3].sum().item() - 1) < 1e-4 and abs(probs[4].sum().item() - 1) < 1e-4
+    # top-p 0.5 over top-50: kept set is the smallest prefix reaching 0.5 mass
+    srt = torch.softmax(logits[3].topk(50).values, -1)
+    n_keep = int((srt.cumsum(0) - srt < 0.5).sum())
+    assert int((probs[3] > 0).sum()) == n_keep
+    emp = counts[5] / 200
+    assert (emp - probs[5]).abs().max() < 0.15
+
+
+def test_spec_verify_and_moe_topk_and_nan_scan():
+    from llaminar_b200 import ops
+    draft = torch.tensor([[5, 6], [5, 9], [1, 2]], dtype=torch.int32, device=DEV)
+    target = torch.tensor([[5, 6, 7], [5, 6, 7], [9, 9, 9]], dtype=torch.int32, device=DEV)
+    na = torch.empty(3, dtype=torch.int32, device=DEV)
+    ot = torch.empty(3, 3, dtype=torch.int32, device=DEV)
+    ops.spec_verify_greedy(draft, target, na, ot)
+    assert na.tolist() == [2, 1, 0]
+    assert ot.tolist() == [[5, 6, 7], [5, 6, -1], [9, -1, -1]]
+    # rejection sampling: identical distributions always accept; disjoint support always rejects
+    B, d, V = 4, 2, 300
+    pt = torch.softmax(torch.randn(B, d + 1, V, device=DEV), -1)
+    pd = pt[:, :d].clone().contiguous()
+    dr = pd.argmax(-1).to(torch.int32)
+    seeds = torch.arange(B, dtype=torch.int64, device=DEV)
+    step = torch.zeros(B, dtype=torch.int32, device=DEV)
+    na = torch.empty(B, dtype=torch.int32, device=DEV)
+    ot = torch.empty(B, d + 1, dtype=torch.int32, device=DEV)
+    ops.spec_verify_reject(pt.contiguous(), pd, dr, seeds, step, na, ot)
+    assert na.tolist() == [d] * B and (ot[:, :d] == dr).all() and (ot[:, d] >= 0).all()
+    pd2 = torch.zeros(B, d, V, device=DEV); pd2[:, :, 0] = 1.0
+    pt2 = torch.zeros(B, d + 1, V, device=DEV); pt2[:, :, 7] = 1.0
+    dr2 = torch.zeros(B, d, dtype=torch.int32, device=DEV)
+    ops.spec_verify_reject(pt2, pd2, dr2, seeds, step, na, ot)
+    assert na.tolist() == [0] * B and ot[:, 0].tolist() == [7] * B
+    # MoE router
+    from llaminar_b200.models.reference import moe_route
+    lg = torch.randn(33, 128, device=DEV)
+    lg[0, 5] = lg[0, 9] = 10.0          # tie -> lower id first
+    ids = torch.empty(33, 8, dtype=torch.int32, device=DEV)
+    wts = torch.empty(33, 8, device=DEV)
+    cnt = torch.zeros(128, dtype=torch.int32, device=DEV)
+    ops.moe_topk(lg, 8, True, ids, wts, cnt)
+    rid, rw = moe_route(lg, 8, True)
+    assert (ids.long() == rid).all() and torch.allclose(wts, rw, atol=1e-5) and int(cnt.sum()) == 33 * 8
+    x = torch.randn(1000, device=DEV); x[3] = float("nan"); x[10] = float("inf"); x[11] = -float("inf")
+    assert ops.nan_scan(x) == (1, 2)
+    assert ops.nan_scan(torch.ones(64, device=DEV).to(torch.bfloat16)) == (0, 0)
