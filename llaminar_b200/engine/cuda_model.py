@@ -1,0 +1,380 @@
+"""GPU model runner: GGUF weights in chunk layout + the per-layer kernel sequence.
+
+Per decoder layer (dense), small batches (<= 4 rows, the GEMV path) launch
+    QKV GEMV (RMSNorm fused in the prologue) -> QK-norm + RoPE + KV append -> paged attention
+    -> Wo GEMV (residual add in the epilogue) -> gate|up GEMV (RMSNorm prologue, SwiGLU epilogue)
+    -> down GEMV (residual epilogue)
+and larger batches / prefill run the same sequence on the tcgen05 GEMM with a separate RMSNorm.
+The order of operations is the one the reference graph builds (reference:
+src/v2/models/qwen/QwenStandardGraph.cpp:103-203, src/v2/models/qwen/QwenGraphBase.cpp:1974-2176);
+the residual stream is kept in fp32, activations in bf16.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..gguf.constants import GGMLType
+from ..models.config import ModelConfig
+from ..models.weights import ModelWeights, QTensor
+from ..ops.layout import PackedWeight, can_pack, interleave_gate_up, pack_experts, pack_matrix
+from .kv_cache import PAGE_SIZE, PagedKVCache
+
+
+@dataclass
+class ForwardBatch:
+    """Device-side description of one forward call (all int32 tensors on the model's device)."""
+    tokens: torch.Tensor            # [T]
+    positions: torch.Tensor         # [T]
+    seq_ids: torch.Tensor           # [T] row of block_table
+    block_table: torch.Tensor       # [B, max_pages]
+    # decode-style attention (few rows per sequence)
+    seq_lens: torch.Tensor | None = None     # [B] cache length including this step's rows
+    rows_per_seq: int = 1
+    n_splits: int = 1
+    # prefill-style attention
+    cu_q: torch.Tensor | None = None         # [B + 1]
+    ctx_lens: torch.Tensor | None = None     # [B]
+    max_q_len: int = 0
+    # which hidden rows get logits (None: all rows)
+    logit_rows: torch.Tensor | None = None
+    embeds: torch.Tensor | None = None       # optional fp32 [T, d] input instead of token embeddings
+
+    @property
+    def is_decode(self) -> bool:
+        return self.seq_lens is not None
+
+
+class QLinear:
+    """A (possibly multi-part) quantised linear layer: parts may differ in block format."""
+
+    def __init__(self, parts: list[tuple[PackedWeight | torch.Tensor, int]], n_out: int, k: int, bias: torch.Tensor | None = None):
+        self.parts = parts          # (weight, first output column); torch.Tensor = dense bf16 fallback [n, k]
+        self.n_out, self.k, self.bias = n_out, k, bias
+
+    @staticmethod
+    def from_qtensors(qts: list[QTensor], device, bias: torch.Tensor | None = None) -> "QLinear":
+        """Row-concatenate matrices; consecutive matrices of one format share a launch."""
+        parts, col = [], 0
+        i = 0
+        k = qts[0].shape[1]
+        while i < len(qts):
+            j = i
+            while j + 1 < len(qts) and qts[j + 1].qtype == qts[i].qtype:
+                j += 1
+            group = qts[i:j + 1]
+            n = sum(q.shape[0] for q in group)
+            qt = group[0].qtype
+            raw = torch.cat([q.raw.to(device).reshape(-1) for q in group]) if len(group) > 1 else group[0].raw.to(device)
+            if can_pack(qt, k):
+                parts.append((pack_matrix(raw, qt, n, k), col))          # rows are padded to whole 128-row tiles
+            else:
+                from ..gguf import dequantize
+                parts.append((dequantize(raw, qt, (n, k)).to(torch.bfloat16), col))
+            col += n
+            i = j + 1
+        return QLinear(parts, col, k, bias)
+
+    def nbytes(self) -> int:
+        return sum(p.nbytes() if isinstance(p, PackedWeight) else p.numel() * 2 for p, _ in self.parts)
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, *, norm_w=None, eps=1e-6, epi=ops.EPI_STORE, scratch=None,
+                 xn: torch.Tensor | None = None) -> None:
+        """x: bf16 rows, or the fp32 residual rows when ``norm_w`` is given (GEMV path only).
+        ``xn``: pre-normalised bf16 rows for the GEMM path."""
+        rows = x.shape[0]
+        for w, col in self.parts:
+            n = w.n if isinstance(w, PackedWeight) else w.shape[0]
+            if epi == ops.EPI_SWIGLU:
+                o = out
+            else:
+                o = out[:, col:col + n] if (col or n != out.shape[1]) else out
+            b = self.bias[col:col + n] if self.bias is not None else None
+            if not isinstance(w, PackedWeight):
+                src = xn if xn is not None else x
+                y = src.to(torch.bfloat16) @ w.T
+                if b is not None:
+                    y = y + b
+                if epi == ops.EPI_RESID:
+                    o += y.float()
+                else:
+                    o.copy_(y)
+                continue
+            if rows <= ops.GEMV_MAX_ROWS and xn is None:
+                ops.gemv(w, x, o, norm_w=norm_w, eps=eps, epi=epi, bias=b, scratch=scratch)
+            else:
+                ops.gemm(w, xn if xn is not None else x, o, epi=epi, bias=b, scratch=scratch)
+
+
+def _f32(t: QTensor | None, device) -> torch.Tensor | None:
+    return None if t is None else t.to_float().to(device=device, dtype=torch.float32).contiguous()
+
+
+class CudaLayer:
+    pass
+
+
+class CudaModel:
+    def __init__(self, weights: ModelWeights, device="cuda", max_tokens: int = 4096, tp=None, layer_range=None,
+                 with_head: bool = True, with_embed: bool = True):
+        self.cfg: ModelConfig = weights.config
+        self.device = torch.device(device)
+        self.tp = tp
+        self.max_tokens = max_tokens
+        c = self.cfg
+        self.scratch = ops.scratch_for(self.device)
+        dev = self.device
+        self.layer_ids = list(range(*layer_range)) if layer_range else list(range(c.n_layers))
+        # ---- tensor-parallel slicing plan (replicated when tp is None) ----
+        from ..parallel.tp_plan import TPPlan
+        self.plan = TPPlan.build(c, tp.size if tp else 1, tp.rank if tp else 0)
+        pl = self.plan
+        self.n_heads_local, self.n_kv_local = pl.n_heads_local, pl.n_kv_local
+        self.q_dim, self.kv_dim = pl.n_heads_local * c.head_dim, pl.n_kv_local * c.head_dim
+        self.qkv_dim = self.q_dim + 2 * self.kv_dim
+        self.ff_local = pl.ff_stop - pl.ff_start
+
+        if with_embed:
+            emb = weights["token_embd.weight"]
+            self.embed = self._pack_or_dense(emb)
+        else:
+            self.embed = None
+        self.head = None
+        if with_head:
+            self.out_norm = _f32(weights["output_norm.weight"], dev)
+            head_t = weights.get("output.weight") or weights["token_embd.weight"]
+            v0, v1 = pl.vocab_start, pl.vocab_stop
+            self.head = QLinear.from_qtensors([head_t.rows(v0, v1)], dev)
+            self.vocab_local = v1 - v0
+        self.layers = [self._build_layer(weights, i) for i in self.layer_ids]
+        self.mtp_layers = []
+        for j in range(c.nextn_layers):
+            i = c.n_layers + j
+            lay = self._build_layer(weights, i)
+            p = f"blk.{i}.nextn."
+            lay.eh_proj = QLinear.from_qtensors([weights[p + "eh_proj.weight"]], dev)
+            lay.enorm = _f32(weights[p + "enorm.weight"], dev)
+            lay.hnorm = _f32(weights[p + "hnorm.weight"], dev)
+            lay.shared_head_norm = _f32(weights[p + "shared_head_norm.weight"], dev)
+            self.mtp_layers.append(lay)
+        self._alloc_workspace(max_tokens)
+
+    # ---------------------------------------------------------------------------------------
+    def _pack_or_dense(self, t: QTensor):
+        n, k = t.shape
+        if can_pack(t.qtype, k):
+            return pack_matrix(t.raw.to(self.device), t.qtype, n, k)
+        return t.to_float().to(self.device)
+
+    def _build_layer(self, w: ModelWeights, i: int) -> CudaLayer:
+        c, dev, pl = self.cfg, self.device, self.plan
+        p = f"blk.{i}."
+        L = CudaLayer()
+        L.attn_norm = _f32(w[p + "attn_norm.weight"], dev)
+        L.ffn_norm = _f32(w[p + "ffn_norm.weight"], dev)
+        D = c.head_dim
+        q = w[p + "attn_q.weight"].rows(pl.q_head_start * D, pl.q_head_stop * D)
+        k = w[p + "attn_k.weight"].rows(pl.kv_head_start * D, pl.kv_head_stop * D)
+        v = w[p + "attn_v.weight"].rows(pl.kv_head_start * D, pl.kv_head_stop * D)
+        bias = None
+        if c.qkv_bias:
+            bq = _f32(w[p + "attn_q.bias"], dev)[pl.q_head_start * D:pl.q_head_stop * D]
+            bk = _f32(w[p + "attn_k.bias"], dev)[pl.kv_head_start * D:pl.kv_head_stop * D]
+            bv = _f32(w[p + "attn_v.bias"], dev)[pl.kv_head_start * D:pl.kv_head_stop * D]
+            bias = torch.cat([bq, bk, bv]).contiguous()
+        L.qkv = QLinear.from_qtensors([q, k, v], dev, bias)
+        L.q_norm = _f32(w.get(p + "attn_q_norm.weight"), dev) if c.qk_norm else None
+        L.k_norm = _f32(w.get(p + "attn_k_norm.weight"), dev) if c.qk_norm else None
+        L.wo = QLinear.from_qtensors([w[p + "attn_output.weight"].cols(pl.q_head_start * D, pl.q_head_stop * D)], dev)
+        if c.is_moe:
+            L.router = w[p + "ffn_gate_inp.weight"].to_float().to(dev).to(torch.bfloat16).contiguous()
+            e0, e1 = pl.expert_start, pl.expert_stop
+            L.experts = self._pack_expert_slab(w, p, e0, e1)
+            L.gate_up = L.down = None
+        else:
+            f0, f1 = pl.ff_start, pl.ff_stop
+            g = w[p + "ffn_gate.weight"].rows(f0, f1)
+            u = w[p + "ffn_up.weight"].rows(f0, f1)
+            L.gate_up = self._pack_gate_up(g, u)
+            L.down = QLinear.from_qtensors([w[p + "ffn_down.weight"].cols(f0, f1)], dev)
+        return L
+
+    def _pack_gate_up(self, g: QTensor, u: QTensor) -> QLinear:
+        dev = self.device
+        n, k = g.shape
+        if g.qtype == u.qtype and can_pack(g.qtype, k) and n % 64 == 0:
+            raw, qt, n2, _ = interleave_gate_up(g.raw.to(dev), u.raw.to(dev), g.qtype, n, k)
+            lin = QLinear([(pack_matrix(raw, qt, n2, k), 0)], n2, k)
+            lin.fused_swiglu = True
+            return lin
+        lin = QLinear.from_qtensors([g, u], dev)
+        lin.fused_swiglu = False
+        return lin
+
+    def _pack_expert_slab(self, w: ModelWeights, p: str, e0: int, e1: int):
+        dev = self.device
+        ge, ue, de = w[p + "ffn_gate_exps.weight"], w[p + "ffn_up_exps.weight"], w[p + "ffn_down_exps.weight"]
+        E, ff, d = ge.shape
+        slab = CudaLayer()
+        gu_parts = []
+        for e in range(e0, e1):
+            g, u = ge.expert(e), ue.expert(e)
+            raw, qt, n2, _ = interleave_gate_up(g.raw.to(dev), u.raw.to(dev), g.qtype, ff, d)
+            gu_parts.append(raw)
+        slab.gate_up = pack_experts(torch.cat(gu_parts), ge.qtype, e1 - e0, 2 * ff, d)
+        dn = torch.cat([de.expert(e).raw.to(dev) for e in range(e0, e1)])
+        slab.down = pack_experts(dn, de.qtype, e1 - e0, d, ff)
+        slab.e0, slab.n_local = e0, e1 - e0
+        return slab
+
+    def weight_bytes(self) -> int:
+        tot = 0
+        for L in self.layers + self.mtp_layers:
+            tot += L.qkv.nbytes() + L.wo.nbytes()
+            if L.gate_up is not None:
+                tot += L.gate_up.nbytes() + L.down.nbytes()
+            else:
+                tot += L.experts.gate_up.nbytes() + L.experts.down.nbytes()
+        if self.head is not None:
+            tot += self.head.nbytes()
+        return tot
+
+    def _alloc_workspace(self, T: int) -> None:
+        c, dev = self.cfg, self.device
+        bf, f32 = torch.bfloat16, torch.float32
+        e = lambda *s, dt=bf: torch.empty(*s, dtype=dt, device=dev)
+        self.ws_h = e(T, c.d_model, dt=f32)
+        self.ws_xn = e(T, c.d_model)
+        self.ws_qkv = e(T, self.qkv_dim)
+        self.ws_q = e(T, self.n_heads_local, c.head_dim)
+        self.ws_o = e(T, self.q_dim)
+        ff = max(self.ff_local, c.expert_ff if c.is_moe else 0)
+        self.ws_act = e(T, ff)
+        self.ws_gu = e(T, 2 * ff) if any(getattr(L.gate_up, "fused_swiglu", True) is False for L in self.layers if L.gate_up) else None
+        self.ws_partial = e(T, c.d_model, dt=f32) if self.tp is not None else None
+
+    # ---------------------------------------------------------------------------------------
+    def embed_tokens(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        if isinstance(self.embed, PackedWeight):
+            ops.gather_rows(self.embed, tokens, out)
+        else:
+            out.copy_(self.embed[tokens.long()])
+
+    def _attention(self, L: CudaLayer, fb: ForwardBatch, kv_layer: torch.Tensor, T: int) -> torch.Tensor:
+        c = self.cfg
+        qkv, q, o = self.ws_qkv[:T], self.ws_q[:T], self.ws_o[:T]
+        ops.rope_kv(qkv, q, kv_layer, L.q_norm, L.k_norm, fb.positions, fb.seq_ids, fb.block_table,
+                    self.n_heads_local, self.n_kv_local, c.head_dim, c.rope_theta, c.rms_eps)
+        scale = 1.0 / math.sqrt(c.head_dim)
+        o3 = o.view(T, self.n_heads_local, c.head_dim)
+        if fb.is_decode:
+            ops.attn_decode(q, kv_layer, o3, fb.block_table, fb.seq_lens, self.n_heads_local, self.n_kv_local,
+                            c.head_dim, fb.rows_per_seq, scale, fb.n_splits, self.scratch)
+        else:
+            ops.attn_prefill(q, kv_layer, o3, fb.block_table, fb.cu_q, fb.ctx_lens, self.n_heads_local,
+                             self.n_kv_local, c.head_dim, scale, fb.max_q_len)
+        return o
+
+    def _row_parallel_resid(self, lin: QLinear, x: torch.Tensor, h: torch.Tensor) -> None:
+        """h += x @ W^T, summed over tensor-parallel ranks."""
+        if self.tp is None or self.tp.size == 1:
+            lin(x, h, epi=ops.EPI_RESID, scratch=self.scratch, xn=x if x.shape[0] > ops.GEMV_MAX_ROWS else None)
+            return
+        self.tp.row_parallel_resid(lin, x, h, self)
+
+    def _layer(self, L: CudaLayer, fb: ForwardBatch, kv_layer: torch.Tensor, T: int) -> None:
+        c, sc = self.cfg, self.scratch
+        h = self.ws_h[:T]
+        small = T <= ops.GEMV_MAX_ROWS
+        qkv = self.ws_qkv[:T]
+        if small:
+            L.qkv(h, qkv, norm_w=L.attn_norm, eps=c.rms_eps, scratch=sc)
+        else:
+            xn = self.ws_xn[:T]
+            ops.rmsnorm(h, L.attn_norm, xn, c.rms_eps)
+            L.qkv(xn, qkv, scratch=sc, xn=xn)
+        o = self._attention(L, fb, kv_layer, T)
+        self._row_parallel_resid(L.wo, o, h)
+        if c.is_moe:
+            self._moe(L, h, T)
+            return
+        act = self.ws_act[:T, :self.ff_local]
+        if small:
+            if L.gate_up.fused_swiglu:
+                L.gate_up(h, act, norm_w=L.ffn_norm, eps=c.rms_eps, epi=ops.EPI_SWIGLU, scratch=sc)
+            else:
+                gu = self.ws_gu[:T, :2 * self.ff_local]
+                L.gate_up(h, gu, norm_w=L.ffn_norm, eps=c.rms_eps, scratch=sc)
+                act.copy_((torch.nn.functional.silu(gu[:, :self.ff_local].float()) * gu[:, self.ff_local:].float()).to(act.dtype))
+        else:
+            xn = self.ws_xn[:T]
+            ops.rmsnorm(h, L.ffn_norm, xn, c.rms_eps)
+            if L.gate_up.fused_swiglu:
+                L.gate_up(xn, act, epi=ops.EPI_SWIGLU, scratch=sc, xn=xn)
+            else:
+                gu = self.ws_gu[:T, :2 * self.ff_local]
+                L.gate_up(xn, gu, scratch=sc, xn=xn)
+                act.copy_((torch.nn.functional.silu(gu[:, :self.ff_local].float()) * gu[:, self.ff_local:].float()).to(act.dtype))
+        self._row_parallel_resid(L.down, act, h)
+
+    def _moe(self, L: CudaLayer, h: torch.Tensor, T: int) -> None:
+        from .moe import moe_forward
+        moe_forward(self, L, h, T)
+
+    def _final_logits(self, h_rows: torch.Tensor, out: torch.Tensor | None, norm_w: torch.Tensor) -> torch.Tensor:
+        rows = h_rows.shape[0]
+        if out is None:
+            out = torch.empty(rows, self.vocab_local, dtype=torch.float32, device=self.device)
+        if rows <= ops.GEMV_MAX_ROWS:
+            self.head(h_rows, out, norm_w=norm_w, eps=self.cfg.rms_eps, scratch=self.scratch)
+        else:
+            xn = torch.empty(rows, self.cfg.d_model, dtype=torch.bfloat16, device=self.device)
+            ops.rmsnorm(h_rows.contiguous(), norm_w, xn, self.cfg.rms_eps)
+            self.head(xn, out, scratch=self.scratch, xn=xn)
+        return out
+
+    @torch.no_grad()
+    def forward(self, fb: ForwardBatch, kv: PagedKVCache, logits_out: torch.Tensor | None = None,
+                want_logits: bool = True, kv_layer_offset: int = 0):
+        """Runs the layers of this model (stage) over the batch; returns (logits or None, hidden [T, d] fp32 view)."""
+        T = fb.tokens.shape[0] if fb.embeds is None else fb.embeds.shape[0]
+        assert T <= self.max_tokens, f"{T} tokens exceed the workspace ({self.max_tokens})"
+        h = self.ws_h[:T]
+        if fb.embeds is not None:
+            h.copy_(fb.embeds)
+        else:
+            self.embed_tokens(fb.tokens, h)
+        for li, L in enumerate(self.layers):
+            self._layer(L, fb, kv.layers[kv_layer_offset + li], T)
+        logits = None
+        if want_logits and self.head is not None:
+            rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())
+            logits = self._final_logits(rows, logits_out, self.out_norm)
+        return logits, h
+
+    @torch.no_grad()
+    def mtp_forward(self, fb: ForwardBatch, hidden: torch.Tensor, kv: PagedKVCache, depth: int = 0,
+                    logits_out: torch.Tensor | None = None):
+        """NextN head: fb.tokens are the *next* tokens, ``hidden`` the trunk's final hidden rows (fp32 [T, d]).
+        Uses KV layer ``n_layers + depth`` of the cache."""
+        c = self.cfg
+        L = self.mtp_layers[depth]
+        T = fb.tokens.shape[0]
+        emb = torch.empty(T, c.d_model, dtype=torch.float32, device=self.device)
+        self.embed_tokens(fb.tokens, emb)
+        cat = torch.empty(T, 2 * c.d_model, dtype=torch.bfloat16, device=self.device)
+        ops.rmsnorm(emb, L.enorm, self.ws_xn[:T], c.rms_eps)
+        cat[:, :c.d_model].copy_(self.ws_xn[:T])
+        ops.rmsnorm(hidden.contiguous(), L.hnorm, self.ws_xn[:T], c.rms_eps)
+        cat[:, c.d_model:].copy_(self.ws_xn[:T])
+        x0 = torch.empty(T, c.d_model, dtype=torch.float32, device=self.device)
+        L.eh_proj(cat, x0, scratch=self.scratch, xn=cat if T > ops.GEMV_MAX_ROWS else None)
+        h = self.ws_h[:T]
+        h.copy_(x0)
+        self._layer(L, fb, kv.layers[c.n_layers + depth], T)
+        rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())
+        logits = self._final_logits(rows, logits_out, L.shared_head_norm)
+        return logits, h

@@ -1,0 +1,523 @@
+"""Request scheduler + step loop: continuous batching over a paged KV cache.
+
+The reference serves one request at a time through `prefill` / `decodeStep`
+(reference: src/v2/execution/runner/OrchestrationRunner.cpp:1028-1297, :10910-11317); here the same
+two phases run over up to ``max_batch`` lanes.  Decode steps replay a CUDA graph captured per
+batch bucket (inputs live in one static int32 buffer that is refreshed with a single pinned
+host-to-device copy per step).  The first generated token is sampled from the prefill logits, as in
+the reference (OrchestrationRunner.cpp:1289-1294).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import ModelWeights
+from .cuda_model import ForwardBatch
+from .kv_cache import PAGE_SIZE, OutOfPages, PagedKVCache, SequenceKV
+from .sampling import SamplingParams, apply_penalties, sample_row
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128)
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: list[int]
+    params: SamplingParams
+    kv: SequenceKV = field(default_factory=SequenceKV)
+    output: list[int] = field(default_factory=list)
+    state: str = "waiting"              # waiting -> running -> finished
+    finish_reason: str | None = None
+    prefix_hit_tokens: int = 0
+    t_arrival: float = 0.0
+    t_first_token: float | None = None
+    forced: list[int] = field(default_factory=list)     # tokens to emit instead of sampling (forceDecodeToken)
+    hidden: torch.Tensor | None = None                   # last trunk hidden row (MTP input)
+    draft: list[int] = field(default_factory=list)
+    step_count: int = 0
+
+    @property
+    def all_tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+@dataclass
+class StepOutput:
+    rid: int
+    new_tokens: list[int]
+    finished: bool
+    finish_reason: str | None = None
+
+
+class LLMEngine:
+    def __init__(self, weights: ModelWeights, device: str | torch.device | None = None, max_batch: int = 32,
+                 max_context: int = 4096, kv_pages: int | None = None, max_prefill_tokens: int = 8192,
+                 use_graphs: bool = True, prefix_cache=None, mtp=None, tp=None, eos_token_id: int | None = None,
+                 model=None, kv_memory_fraction: float = 0.85):
+        self.cfg: ModelConfig = weights.config if weights is not None else model.cfg
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        self.max_batch, self.max_context = max_batch, max_context
+        self.max_prefill_tokens = max_prefill_tokens
+        self.tp = tp
+        self.eos_token_id = eos_token_id
+        c = self.cfg
+        if model is not None:
+            self.model = model
+        elif self.is_cuda:
+            from .cuda_model import CudaModel
+            self.model = CudaModel(weights, self.device, max_tokens=max(max_prefill_tokens, max_batch * 4), tp=tp)
+        else:
+            from .torch_model import TorchPagedModel
+            self.model = TorchPagedModel(weights, self.device, tp=tp)
+        self.max_pages_per_seq = (max_context + PAGE_SIZE - 1) // PAGE_SIZE + 1
+        n_kv_layers = c.n_layers + c.nextn_layers
+        if kv_pages is None:
+            need = max_batch * self.max_pages_per_seq + 64
+            if self.is_cuda:
+                free, _ = torch.cuda.mem_get_info(self.device)
+                per_page = PagedKVCache.bytes_per_page(n_kv_layers, self.model.n_kv_local, c.head_dim)
+                kv_pages = int(min(need * 2, max(need // 4, int(free * kv_memory_fraction) // per_page)))
+            else:
+                kv_pages = need
+        self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
+                               dtype=torch.bfloat16 if self.is_cuda else torch.float32)
+        self.use_graphs = use_graphs and self.is_cuda
+        self._graphs: dict = {}
+        self.launches_per_graph: dict = {}      # kernels of this package inside each captured decode graph
+        self.step_events = None                 # optional list of (start, end) CUDA events, one pair consumed per decode step
+        self._rid = itertools.count()
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self.requests: dict[int, Request] = {}
+        self.prefix_cache = prefix_cache
+        if prefix_cache is not None:
+            prefix_cache.attach(self)
+        self.mtp = mtp
+        if mtp is not None:
+            mtp.attach(self)
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
+                      "prefix_hit_tokens": 0, "graph_replays": 0}
+        self._vocab = c.vocab_size
+        if self.is_cuda:
+            self._init_static_buffers()
+
+    # -- construction helpers ------------------------------------------------------------------
+    @staticmethod
+    def from_gguf(path: str, **kw) -> "LLMEngine":
+        dev = kw.get("device") or ("cuda" if torch.cuda.is_available() else "cpu")
+        w = ModelWeights.from_gguf(path, device="cpu")
+        eng = LLMEngine(w, **kw)
+        eng.metadata = w.metadata
+        return eng
+
+    # -- static decode buffers ---------------------------------------------------------------------
+    def _init_static_buffers(self) -> None:
+        B, P = max(self.max_batch, 1), self.max_pages_per_seq
+        bmax = next(b for b in BUCKETS if b >= B) if B <= BUCKETS[-1] else B
+        self._bmax = bmax
+        R = 4                                   # up to 4 rows per sequence (speculative verify)
+        n_int = bmax * R * 2 + bmax + bmax * P + bmax * 3
+        self._dec_host = torch.zeros(n_int, dtype=torch.int32).pin_memory()
+        self._dec_dev = torch.zeros(n_int, dtype=torch.int32, device=self.device)
+        self._fl_host = torch.zeros(bmax * R * 2, dtype=torch.float32).pin_memory()
+        self._fl_dev = torch.zeros(bmax * R * 2, dtype=torch.float32, device=self.device)
+        self._seed_host = torch.zeros(bmax * R, dtype=torch.int64).pin_memory()
+        self._seed_dev = torch.zeros(bmax * R, dtype=torch.int64, device=self.device)
+        self._tok_dev = torch.zeros(bmax * R, dtype=torch.int32, device=self.device)
+        self._tok_host = torch.zeros(bmax * R, dtype=torch.int32).pin_memory()
+        self._logits = torch.empty(bmax * R, self.model.vocab_local, dtype=torch.float32, device=self.device)
+
+    def _dec_views(self, bucket: int, R: int):
+        """Slices of the static int buffer for a (bucket, rows-per-seq) decode shape."""
+        P = self.max_pages_per_seq
+        T = bucket * R
+        o = 0
+        d, h = self._dec_dev, self._dec_host
+        def take(n):
+            nonlocal o
+            s = slice(o, o + n)
+            o += n
+            return s
+        s_tok, s_pos, s_len, s_bt = take(T), take(T), take(bucket), take(bucket * P)
+        s_topk, s_step, s_sid = take(T), take(T), take(T)
+        return {"tok": s_tok, "pos": s_pos, "len": s_len, "bt": s_bt, "topk": s_topk, "step": s_step, "sid": s_sid, "n": o}
+
+    # -- public API ---------------------------------------------------------------------------------
+    def add_request(self, prompt: list[int], params: SamplingParams | None = None) -> Request:
+        if not prompt:
+            raise ValueError("empty prompt")
+        params = params or SamplingParams()
+        if len(prompt) + 1 > self.max_context:
+            raise ValueError(f"prompt of {len(prompt)} tokens exceeds the context window of {self.max_context}")
+        r = Request(next(self._rid), list(prompt), params, t_arrival=time.perf_counter())
+        self.requests[r.rid] = r
+        self.waiting.append(r)
+        return r
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def abort(self, rid: int) -> None:
+        r = self.requests.get(rid)
+        if r is None or r.state == "finished":
+            return
+        self._finish(r, "abort")
+        if r in self.waiting:
+            self.waiting.remove(r)
+
+    def force_token(self, rid: int, token: int) -> None:
+        """Make the next decode step of a request emit ``token`` instead of sampling (thinking-budget stop)."""
+        self.requests[rid].forced.append(token)
+
+    def clear_cache(self) -> None:
+        for r in list(self.running):
+            self._finish(r, "abort")
+        if self.prefix_cache is not None:
+            self.prefix_cache.clear()
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None) -> list[list[int]]:
+        plist = params if isinstance(params, list) else [params or SamplingParams()] * len(prompts)
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        while any(r.state != "finished" for r in reqs):
+            self.step()
+        outs = [r.output for r in reqs]
+        for r in reqs:
+            self.requests.pop(r.rid, None)
+        return outs
+
+    # -- scheduling -----------------------------------------------------------------------------------
+    def step(self) -> list[StepOutput]:
+        """One scheduler iteration: admit + prefill waiting requests if lanes are free, else one decode step."""
+        self.stats["steps"] += 1
+        if self.waiting and len(self.running) < self.max_batch:
+            batch, budget = [], self.max_prefill_tokens
+            while self.waiting and len(self.running) + len(batch) < self.max_batch:
+                r = self.waiting[0]
+                cost = len(r.prompt)
+                if batch and cost > budget:
+                    break
+                try:
+                    self._admit(r)
+                except OutOfPages:
+                    if not batch and not self.running:
+                        raise
+                    break
+                self.waiting.pop(0)
+                batch.append(r)
+                budget -= cost
+            if batch:
+                return self._prefill(batch)
+        if self.running:
+            if self.mtp is not None:
+                return self.mtp.decode_step(self, list(self.running))
+            return self._decode(list(self.running))
+        return []
+
+    def _admit(self, r: Request) -> None:
+        hit_pages, hit_tokens = [], 0
+        if self.prefix_cache is not None:
+            hit_pages, hit_tokens = self.prefix_cache.lookup(r.prompt)
+        if hit_tokens >= len(r.prompt):               # keep at least one token to run for the logits
+            drop = (hit_tokens - len(r.prompt)) // PAGE_SIZE + 1
+            hit_pages = hit_pages[:len(hit_pages) - drop]
+            hit_tokens = len(hit_pages) * PAGE_SIZE
+        r.kv = self.kv.fork_prefix(hit_pages, hit_tokens) if hit_pages else SequenceKV()
+        r.prefix_hit_tokens = hit_tokens
+        try:
+            self._ensure_pages(r, len(r.prompt) + 1)
+        except OutOfPages:
+            self.kv.free_sequence(r.kv)
+            raise
+        self.stats["prefix_hit_tokens"] += hit_tokens
+
+    def _ensure_pages(self, r: Request, n_tokens: int) -> None:
+        try:
+            self.kv.ensure_capacity(r.kv, n_tokens)
+        except OutOfPages:
+            if self.prefix_cache is None or not self.prefix_cache.evict_for(self, n_tokens - r.kv.capacity()):
+                raise
+            self.kv.ensure_capacity(r.kv, n_tokens)
+
+    def _finish(self, r: Request, reason: str) -> None:
+        if r.state == "finished":
+            return
+        if self.prefix_cache is not None and reason != "abort":
+            self.prefix_cache.insert(self, r)
+        r.state, r.finish_reason = "finished", reason
+        if r in self.running:
+            self.running.remove(r)
+        self.kv.free_sequence(r.kv)
+        if self.mtp is not None:
+            self.mtp.release(r)
+
+    def _check_stop(self, r: Request, tok: int) -> str | None:
+        p = r.params
+        if tok in p.stop_token_ids:
+            return "stop"
+        if not p.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
+            return "stop"
+        if len(r.output) >= p.max_tokens:
+            return "length"
+        if r.n_tokens + 1 >= self.max_context:
+            return "length"
+        return None
+
+    def _emit(self, r: Request, toks: list[int]) -> StepOutput:
+        new = []
+        for t in toks:
+            r.output.append(t)
+            new.append(t)
+            if r.t_first_token is None:
+                r.t_first_token = time.perf_counter()
+            reason = self._check_stop(r, t)
+            if reason:
+                self._finish(r, reason)
+                return StepOutput(r.rid, new, True, reason)
+        return StepOutput(r.rid, new, False)
+
+    # -- sampling -----------------------------------------------------------------------------------
+    def _sample_rows(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
+        """Eager sampling of one row per request (prefill tail, penalties, CPU backend)."""
+        logits = self._gather_vocab(logits)
+        out = []
+        all_greedy = all(r.params.is_greedy and not r.params.needs_penalties and not r.forced for r in reqs)
+        if all_greedy:
+            if self.is_cuda:
+                from .. import ops
+                tok = torch.empty(len(reqs), dtype=torch.int32, device=self.device)
+                ops.argmax(logits.contiguous(), tok)
+                return tok.tolist()
+            return logits.argmax(-1).tolist()
+        for i, r in enumerate(reqs):
+            if r.forced:
+                out.append(r.forced.pop(0))
+                continue
+            row = apply_penalties(logits[i], r.all_tokens, r.params)
+            if self.is_cuda and not r.params.is_greedy:
+                from .. import ops
+                dev = self.device
+                seed = r.params.seed if r.params.seed is not None else (r.rid * 7919 + 17)
+                tok = torch.empty(1, dtype=torch.int32, device=dev)
+                ops.sample(row.view(1, -1).contiguous(), torch.tensor([r.params.temperature], device=dev),
+                           torch.tensor([r.params.top_k], dtype=torch.int32, device=dev),
+                           torch.tensor([r.params.top_p], device=dev), torch.tensor([seed], dtype=torch.int64, device=dev),
+                           torch.tensor([len(r.output)], dtype=torch.int32, device=dev), tok)
+                out.append(int(tok))
+            else:
+                gen = None
+                if r.params.seed is not None:
+                    gen = torch.Generator().manual_seed(r.params.seed * 1000003 + len(r.output))
+                out.append(sample_row(row, r.params, gen))
+        return out
+
+    def _gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
+        """Vocab-parallel logits shards -> full rows (a no-op without tensor parallelism)."""
+        if self.tp is None or self.tp.size == 1:
+            return logits
+        return self.tp.all_gather_vocab(logits, self.cfg.vocab_size)
+
+    # -- prefill ---------------------------------------------------------------------------------------
+    def _prefill(self, batch: list[Request]) -> list[StepOutput]:
+        t0 = time.perf_counter()
+        dev = self.device
+        # split long prompts into chunks of at most max_prefill_tokens rows per forward
+        pending = {r.rid: r.prefix_hit_tokens for r in batch}
+        final_logits: dict[int, torch.Tensor] = {}
+        final_hidden: dict[int, torch.Tensor] = {}
+        while any(pending[r.rid] < len(r.prompt) for r in batch):
+            toks, pos, sid, cu, ctx, rows_for = [], [], [], [0], [], []
+            budget = self.max_prefill_tokens
+            btab_rows = []
+            for r in batch:
+                done = pending[r.rid]
+                if done >= len(r.prompt) or budget <= 0:
+                    continue
+                n = min(len(r.prompt) - done, budget)
+                budget -= n
+                b = len(ctx)
+                toks.extend(r.prompt[done:done + n])
+                pos.extend(range(done, done + n))
+                sid.extend([b] * n)
+                cu.append(cu[-1] + n)
+                ctx.append(done)
+                btab_rows.append(r.kv.pages)
+                pending[r.rid] = done + n
+                rows_for.append((r, cu[-1] - 1 if done + n == len(r.prompt) else None))
+            P = max(len(p) for p in btab_rows)
+            bt = torch.zeros(len(btab_rows), P, dtype=torch.int32)
+            for i, p in enumerate(btab_rows):
+                bt[i, :len(p)] = torch.tensor(p, dtype=torch.int32)
+            it = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+            logit_rows = [row for _, row in rows_for if row is not None]
+            fb = ForwardBatch(tokens=it(toks), positions=it(pos), seq_ids=it(sid), block_table=bt.to(dev), cu_q=it(cu),
+                              ctx_lens=it(ctx), max_q_len=max(cu[i + 1] - cu[i] for i in range(len(ctx))),
+                              logit_rows=it(logit_rows) if logit_rows else None)
+            logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
+            j = 0
+            for r, row in rows_for:
+                if row is not None:
+                    final_logits[r.rid] = logits[j]
+                    final_hidden[r.rid] = h[row].clone()
+                    j += 1
+            self.stats["prefill_tokens"] += len(toks)
+        outs = []
+        lg = torch.stack([final_logits[r.rid] for r in batch])
+        toks = self._sample_rows(lg, batch)
+        for r, t in zip(batch, toks):
+            r.kv.length = len(r.prompt)
+            r.hidden = final_hidden[r.rid]
+            r.state = "running"
+            self.running.append(r)
+            if self.prefix_cache is not None:
+                self.prefix_cache.insert(self, r)
+            outs.append(self._emit(r, [t]))
+        if self.is_cuda:
+            torch.cuda.synchronize(dev)
+        self.stats["prefill_s"] += time.perf_counter() - t0
+        return outs
+
+    # -- decode ----------------------------------------------------------------------------------------
+    def _decode(self, reqs: list[Request]) -> list[StepOutput]:
+        t0 = time.perf_counter()
+        for r in reqs:
+            self._ensure_pages(r, r.n_tokens)
+        eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced for r in reqs)
+        if self.is_cuda:
+            toks = self._decode_cuda(reqs, eager)
+        else:
+            toks = self._decode_eager(reqs)
+        outs = []
+        for r, t in zip(reqs, toks):
+            r.kv.length = r.n_tokens          # the fed token's K/V are now cached
+            r.step_count += 1
+            outs.append(self._emit(r, [t]))
+        self.stats["decode_tokens"] += len(reqs)
+        self.stats["decode_s"] += time.perf_counter() - t0
+        return outs
+
+    def _decode_batch_tensors(self, reqs: list[Request]):
+        dev = self.device
+        B = len(reqs)
+        it = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        P = max(len(r.kv.pages) for r in reqs)
+        bt = torch.zeros(B, P, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            bt[i, :len(r.kv.pages)] = torch.tensor(r.kv.pages, dtype=torch.int32)
+        return ForwardBatch(tokens=it([r.output[-1] for r in reqs]), positions=it([r.n_tokens - 1 for r in reqs]),
+                            seq_ids=it(list(range(B))), block_table=bt.to(dev), seq_lens=it([r.n_tokens for r in reqs]),
+                            rows_per_seq=1, n_splits=self._splits_for(B))
+
+    def _splits_for(self, bucket: int) -> int:
+        if not self.is_cuda:
+            return 1
+        s = max(1, min(16, 296 // max(1, bucket * self.model.n_kv_local)))
+        return min(s, max(1, self.max_pages_per_seq // 2))
+
+    def _decode_eager(self, reqs: list[Request]) -> list[int]:
+        fb = self._decode_batch_tensors(reqs)
+        logits, h = self.model.forward(fb, self.kv)
+        for i, r in enumerate(reqs):
+            r.hidden = h[i].clone()
+        return self._sample_rows(logits, reqs)
+
+    def _fill_decode_host(self, reqs: list[Request], bucket: int, v: dict) -> None:
+        h = self._dec_host
+        P = self.max_pages_per_seq
+        B = len(reqs)
+        tok, pos, ln = h[v["tok"]], h[v["pos"]], h[v["len"]]
+        bt = h[v["bt"]].view(bucket, P)
+        topk, step = h[v["topk"]], h[v["step"]]
+        temp, topp = self._fl_host[:bucket], self._fl_host[bucket:2 * bucket]
+        h[v["sid"]] = torch.arange(bucket, dtype=torch.int32)       # a decode batch uses block-table rows 0..bucket-1
+        for i, r in enumerate(reqs):
+            tok[i] = r.output[-1]
+            pos[i] = r.n_tokens - 1
+            ln[i] = r.n_tokens
+            npg = len(r.kv.pages)
+            bt[i, :npg] = torch.as_tensor(r.kv.pages, dtype=torch.int32)
+            topk[i] = r.params.top_k
+            step[i] = len(r.output)
+            temp[i] = 0.0 if r.params.is_greedy else r.params.temperature
+            topp[i] = r.params.top_p
+            self._seed_host[i] = r.params.seed if r.params.seed is not None else (r.rid * 7919 + 17)
+        if B < bucket:                                  # padded lanes point at the scratch page
+            tok[B:bucket] = 0
+            pos[B:bucket] = 0
+            ln[B:bucket] = 1
+            bt[B:bucket].zero_()
+            temp[B:bucket] = 0.0
+
+    def _decode_cuda(self, reqs: list[Request], eager: bool) -> list[int]:
+        from .. import ops
+        B = len(reqs)
+        bucket = next((b for b in BUCKETS if b >= B), B)
+        if eager or bucket > self._bmax:
+            return self._decode_eager(reqs)
+        v = self._dec_views(bucket, 1)
+        self._fill_decode_host(reqs, bucket, v)
+        greedy = all(r.params.is_greedy for r in reqs)
+        n = v["n"]
+        self._dec_dev[:n].copy_(self._dec_host[:n], non_blocking=True)
+        if not greedy:
+            self._fl_dev[:2 * bucket].copy_(self._fl_host[:2 * bucket], non_blocking=True)
+            self._seed_dev[:bucket].copy_(self._seed_host[:bucket], non_blocking=True)
+        key = (bucket, greedy)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._capture_decode(bucket, greedy, v)
+            self._graphs[key] = g
+        evp = self.step_events.pop() if self.step_events else None
+        if evp:
+            evp[0].record()
+        g.replay()
+        if evp:
+            evp[1].record()
+        self.stats["graph_replays"] += 1
+        self._tok_host[:bucket].copy_(self._tok_dev[:bucket], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self._tok_host[:B].tolist()
+
+    def _decode_body(self, bucket: int, greedy: bool, v: dict) -> None:
+        from .. import ops
+        d = self._dec_dev
+        P = self.max_pages_per_seq
+        fb = ForwardBatch(tokens=d[v["tok"]], positions=d[v["pos"]], seq_ids=d[v["sid"]],
+                          block_table=d[v["bt"]].view(bucket, P), seq_lens=d[v["len"]], rows_per_seq=1,
+                          n_splits=self._splits_for(bucket))
+        logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
+        if self.tp is not None and self.tp.size > 1:
+            logits = self.tp.all_gather_vocab(logits, self.cfg.vocab_size)
+        if greedy:
+            ops.argmax(logits, self._tok_dev[:bucket])
+        else:
+            ops.sample(logits, self._fl_dev[:bucket], d[v["topk"]], self._fl_dev[bucket:2 * bucket],
+                       self._seed_dev[:bucket], d[v["step"]], self._tok_dev[:bucket])
+
+    def _capture_decode(self, bucket: int, greedy: bool, v: dict):
+        torch.cuda.synchronize(self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):                          # warm-up: lazy initialisation must not happen in capture
+                self._decode_body(bucket, greedy, v)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        from .. import ops
+        n0 = ops.launch_count()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._decode_body(bucket, greedy, v)
+        self.launches_per_graph[(bucket, greedy)] = ops.launch_count() - n0
+        return g

@@ -95,11 +95,11 @@ def gemv_experts(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, expert_id
 
 
 def gemm(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, epi: int = EPI_STORE, bias: torch.Tensor | None = None,
-         scratch: Scratch | None = None, ksplit: int = 0) -> None:
+         scratch: Scratch | None = None, ksplit: int = 0, debug_ptr: int = 0, flags: int = 0) -> None:
     """Tensor-core path: out[M, N] (+)= x[M, K] @ dequant(W)^T, any M."""
     accum, tickets = _accum_args(pw, x.shape[0], scratch)
     ext().gemm_tc(pw.data, pw.fmt, pw.n, pw.k, x, out, epi, bias, accum, tickets, ksplit if accum is not None else 1,
-                  scratch.status if scratch is not None else None)
+                  scratch.status if scratch is not None else None, debug_ptr, flags)
     _count()
 
 

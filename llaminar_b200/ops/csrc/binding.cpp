@@ -222,7 +222,7 @@ static void moe_topk(const Tensor& logits, int64_t k, bool renorm, Tensor ids, T
 
 // tensor-core GEMM: out[M, N] (+)= x[M, K] * dequant(W)[N, K]^T
 static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, Tensor out, int64_t epi, const OptTensor& bias,
-                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status) {
+                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status, int64_t debug_ptr, int64_t flags) {
     check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "gemm_tc input must be contiguous bf16");
@@ -232,6 +232,7 @@ static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Te
     p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
     p.epi = (int)epi; p.bias = cptr<float>(bias); p.status = mptr<int>(status);
     p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets); p.ksplit = (int)ksplit;
+    p.debug = reinterpret_cast<int*>(debug_ptr); p.flags = (int)flags;
     p.accum_stride = accum.has_value() ? (int)accum->stride(0) : 0;
     if (epi == llm::EPI_RESID) TORCH_CHECK(p.out_f32, "residual epilogue updates an fp32 stream");
     if (accum.has_value()) {

@@ -2,7 +2,7 @@
 //
 // Roles inside one CTA (320 threads):
 //   warps 0-7  dequant producers: lane == weight row; each warp owns a 32-row group and every other
-//              256-column chunk.  Packed bytes go global -> registers (next chunk prefetched), are
+//              256-column chunk (warps 0-3 and 4-7 form two sets, each with its own half of the ring).  Packed bytes go global -> registers (next chunk prefetched), are
 //              converted to bf16 and stored into the 128B-swizzled K-major operand tile of the ring
 //              stage, one 64-column "atom" (16 KB) at a time.  Afterwards they run the epilogue.
 //   warp 8     TMA producer: the activation tile (BM tokens x 64 columns) of each atom, SWIZZLE_128B.
@@ -97,6 +97,22 @@ template <int BM> struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;     // + slack for 1024-byte alignment
 };
 
+// Atom `it` (64 columns; counted from the CTA's first chunk, 4 per chunk) -> ring stage and mbarrier phase.
+// The two dequant warp sets take alternate chunks.  Each set owns one half of the ring and steps through it
+// with its own atom counter, so every waiter (either set, the TMA lane, the MMA lane) comes back to a stage
+// exactly one revolution later.  That is what keeps the 1-bit phase parity of mbarrier waits unambiguous: a
+// set that shared one ring with the other would revisit a stage only every second revolution and its parity
+// wait would be satisfied by a stale phase.
+template <int STAGES>
+LLM_DEVICE void ring_slot(int it, int& stage, int& phase) {
+    constexpr int D = STAGES / 2;
+    static_assert(STAGES % 2 == 0 && D >= 2, "each warp set needs at least two stages");
+    const int set = (it >> 2) & 1;
+    const int j = ((it >> 3) << 2) | (it & 3);      // atom index within the set's own sequence
+    stage = set * D + j % D;
+    phase = (j / D) & 1;
+}
+
 // Sink of the dequant warps: acquires ring stages atom by atom and publishes them to the MMA warp.
 template <int STAGES>
 struct RingSink {
@@ -109,13 +125,14 @@ struct RingSink {
     bool ok;
     LLM_DEVICE void begin(int a, int n) {
         for (int i = 0; i < n; ++i) {
-            const int it = it0 + a + i;
-            const int stage = it % STAGES, phase = (it / STAGES) & 1;
+            int stage, phase;
+            ring_slot<STAGES>(it0 + a + i, stage, phase);
             if (ok) ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
         }
     }
     LLM_DEVICE void emit(int kg, uint4 v) {
-        const int stage = (it0 + (kg >> 3)) % STAGES;
+        int stage, phase;
+        ring_slot<STAGES>(it0 + (kg >> 3), stage, phase);
         const uint32_t dst = smem_base + stage * stage_bytes + row * 128 + ((((kg & 7) ^ row) & 7) << 4);
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
     }
@@ -123,7 +140,11 @@ struct RingSink {
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            for (int i = 0; i < n; ++i) mbar_arrive(full_bar + ((it0 + a + i) % STAGES) * 8);
+            for (int i = 0; i < n; ++i) {
+                int stage, phase;
+                ring_slot<STAGES>(it0 + a + i, stage, phase);
+                mbar_arrive(full_bar + stage * 8);
+            }
         }
     }
 };
@@ -161,13 +182,27 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     }
     if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (!(p.flags & 1)) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = &s_abort;
+    const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    auto trace = [&](int slot, int value) {
+        if (p.debug) {
+            volatile int* d = p.debug + (size_t)cta_lin * 8;
+            d[slot] = value;
+            __threadfence_system();
+        }
+    };
+    if (tid == 0) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        trace(0, (int)smid + 1);
+        trace(1, (int)tmem_base);
+    }
 
     if (warp < 8) {
         // ------------------------------ dequant producers ------------------------------
@@ -190,12 +225,14 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         if (lane == 0) {
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
-                const int stage = it % C::STAGES, phase = (it / C::STAGES) & 1;
+                int stage, phase;
+                ring_slot<C::STAGES>(it, stage, phase);
                 ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
                 if (!ok) break;
                 mbar_arrive_expect_tx(full_bar + stage * 8, C::B_ATOM_BYTES);
                 tma_load_2d(smem_base + stage * C::STAGE_BYTES + A_ATOM_BYTES, &tmap_x, kb0 * 256 + it * 64, tile_m * BM,
                             full_bar + stage * 8);
+                trace(3, it + 1);
             }
         }
     } else {
@@ -204,7 +241,8 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
             constexpr uint32_t idesc = instr_desc(BM);
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
-                const int stage = it % C::STAGES, phase = (it / C::STAGES) & 1;
+                int stage, phase;
+                ring_slot<C::STAGES>(it, stage, phase);
                 ok = mbar_wait(full_bar + stage * 8, phase, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -216,8 +254,10 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
                     mma_f16(tmem_base, adesc + 2 * k4, bdesc + 2 * k4, idesc, (it > 0 || k4 > 0) ? 1u : 0u);
                 }
                 mma_commit(empty_bar + stage * 8);
+                trace(2, it + 1);
             }
             if (ok) mma_commit(accum_bar);
+            trace(2, ok ? 1000 + n_it : -1);
         }
     }
 
@@ -332,8 +372,10 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     }
 
     // ------------------------------ teardown ------------------------------
+    if (tid == 0) trace(6, live ? 1 : -1);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) trace(6, *abort_flag ? -2 : 2);
     if (*abort_flag) {
         if (tid == 0 && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
         // give copies that are still in flight time to land before this CTA's shared memory is handed on
@@ -341,7 +383,9 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         __syncthreads();
     }
     if (warp == 9) {
+        if (p.flags & 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+        if (lane == 0) trace(7, 1);
     }
 }
 

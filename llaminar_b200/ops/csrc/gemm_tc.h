@@ -21,6 +21,8 @@ struct GemmTcParams {
     int accum_stride;
     int ksplit;                // 0 = automatic
     int* status;               // optional device word: set to STATUS_TIMEOUT if a pipeline wait gave up
+    int* debug;                // optional host-mapped trace buffer: 8 ints per CTA (progress markers)
+    int flags;                 // bit 0: relinquish the TMEM allocation permit at teardown instead of right after alloc
 };
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);

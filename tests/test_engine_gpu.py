@@ -1,0 +1,95 @@
+"""GPU engine (kernels + CUDA graphs) against the fp32 oracle on small random models."""
+import pytest
+import torch
+
+from llaminar_b200.engine.engine import LLMEngine
+from llaminar_b200.engine.sampling import SamplingParams
+from llaminar_b200.models.config import SHAPES
+from llaminar_b200.models.reference import ReferenceModel
+from llaminar_b200.models.synth import synthesize
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompt(n, seed, vocab=1024):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0).item()
+
+
+@pytest.mark.parametrize("shape,recipe", [("tiny-qwen3", "Q8_0"), ("tiny-qwen2", "Q4_K_M"), ("tiny-qwen3", "Q5_K"),
+                                          ("tiny-qwen3", "Q6_K"), ("tiny-qwen3", "Q4_0")])
+def test_prefill_and_decode_logits_match_oracle(shape, recipe):
+    from llaminar_b200.engine.cuda_model import CudaModel, ForwardBatch
+    from llaminar_b200.engine.kv_cache import PagedKVCache
+    w = synthesize(SHAPES[shape], recipe, seed=0)
+    cfg = w.config
+    model = CudaModel(w, "cuda", max_tokens=512)
+    kv = PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 32, "cuda")
+    ref = ReferenceModel(w)
+    prompt = _prompt(100, 1)
+    it = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    bt = it([[3, 7, 1, 0]])
+    fb = ForwardBatch(tokens=it(prompt), positions=it(list(range(100))), seq_ids=it([0] * 100), block_table=bt,
+                      cu_q=it([0, 100]), ctx_lens=it([0]), max_q_len=100)
+    logits, h = model.forward(fb, kv)
+    rl, rh, rkv = ref.forward(torch.tensor(prompt))
+    assert _cos(h.cpu(), rh) > 0.998
+    assert _cos(logits.cpu(), rl) > 0.995
+    # three GEMV-path decode steps
+    tok = int(rl[-1].argmax())
+    for step in range(3):
+        pos = 100 + step
+        fb = ForwardBatch(tokens=it([tok]), positions=it([pos]), seq_ids=it([0]), block_table=bt, seq_lens=it([pos + 1]),
+                          rows_per_seq=1, n_splits=2)
+        lg, _ = model.forward(fb, kv)
+        rl, _, rkv = ref.forward(torch.tensor([tok]), rkv)
+        assert _cos(lg.cpu(), rl) > 0.995, step
+        tok = int(rl[-1].argmax())
+
+
+def test_engine_graph_decode_equals_eager_and_batches():
+    w = synthesize(SHAPES["tiny-qwen3"], "Q4_K_M", seed=2)
+    prompts = [_prompt(n, n) for n in (5, 70, 33, 130, 64)]
+    p = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    e1 = LLMEngine(w, device="cuda", max_batch=4, max_context=256, use_graphs=True)
+    e2 = LLMEngine(w, device="cuda", max_batch=4, max_context=256, use_graphs=False)
+    o1, o2 = e1.generate(prompts, p), e2.generate(prompts, p)
+    assert o1 == o2
+    assert e1.stats["graph_replays"] > 0
+    singles = [LLMEngine(w, device="cuda", max_batch=1, max_context=256).generate([pr], p)[0] for pr in prompts[:2]]
+    # batch composition changes which kernels run (GEMV vs tensor-core GEMM), so allow rare near-tie flips
+    agree = sum(a == b for s, o in zip(singles, o1[:2]) for a, b in zip(s, o))
+    assert agree >= 16
+    assert e1.kv.allocator.n_free == e1.kv.n_pages - 1
+
+
+def test_engine_sampling_graph_and_seed_determinism():
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=4)
+    p = SamplingParams(temperature=0.9, top_k=50, top_p=0.95, seed=11, max_tokens=12, ignore_eos=True)
+    e = LLMEngine(w, device="cuda", max_batch=2, max_context=256)
+    a = e.generate([_prompt(20, 1)], p)[0]
+    b = e.generate([_prompt(20, 1)], p)[0]
+    assert a == b and len(set(a)) > 1
+
+
+def test_moe_engine_matches_oracle():
+    w = synthesize(SHAPES["tiny-qwen3moe"], "Q8_0", seed=5)
+    eng = LLMEngine(w, device="cuda", max_batch=2, max_context=256)
+    prompt = _prompt(40, 9)
+    from llaminar_b200.engine.cuda_model import ForwardBatch
+    ref = ReferenceModel(w)
+    rl, _, _ = ref.forward(torch.tensor(prompt))
+    r = eng.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    while r.state != "finished":
+        eng.step()
+    assert len(r.output) == 6
+    # teacher-forced check of the GPU tokens against oracle logits: each chosen token is near the oracle's top
+    seq = prompt + r.output
+    full, _, _ = ref.forward(torch.tensor(seq[:-1]))
+    for i, t in enumerate(r.output):
+        row = full[len(prompt) - 1 + i]
+        assert row[t] >= row.max() - 0.05 * (row.max() - row.min())

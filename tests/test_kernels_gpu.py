@@ -106,6 +106,24 @@ def test_gemm_tc(qt, m):
     assert int(sc.tickets.abs().sum()) == 0 and float(sc.accum.abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("qt,m,n,k,ks", [(GGMLType.Q4_K, 2048, 8192, 1024, 1), (GGMLType.Q6_K, 1024, 4096, 2048, 1),
+                                          (GGMLType.Q8_0, 600, 2048, 1024, 1), (GGMLType.Q4_K, 48, 4096, 4096, 0),
+                                          (GGMLType.IQ3_S, 130, 3072, 768, 0)])
+def test_gemm_tc_many_ctas_per_sm(qt, m, n, k, ks):
+    """Grids with several waves of CTAs: the producer sets run far ahead of the MMA consumer here."""
+    from llaminar_b200 import ops
+    pw, wf = _weight(qt, n, k, seed=3)
+    sc = ops.scratch_for(DEV)
+    sc.status.zero_()
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    for _ in range(3):
+        ops.gemm(pw, x, out, scratch=sc, ksplit=ks)
+    torch.cuda.synchronize()
+    assert int(sc.status[0]) == 0
+    assert _rel(out, x.float() @ wf.T) < 1.2e-2
+
+
 @pytest.mark.parametrize("m", [16, 200])
 def test_gemm_tc_swiglu_large_k(m):
     from llaminar_b200 import ops
