@@ -41,6 +41,7 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a valid bench)")
     ap.add_argument("--skip-extras", action="store_true", help="only the headline region (no bs1 / prefill / TTFT)")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one instead of replaying a graph")
     return ap.parse_args()
 
 
@@ -133,7 +134,8 @@ def main():
     t0 = time.time()
     weights = synthesize(cfg, recipe, seed=0, device=dev, with_tokenizer=False)
     t_build = time.time() - t0
-    engine = LLMEngine(weights, device=dev, max_batch=B, max_context=S + K + W + 96, max_prefill_tokens=8192, tp=tp)
+    engine = LLMEngine(weights, device=dev, max_batch=B, max_context=S + K + W + 96, max_prefill_tokens=8192, tp=tp,
+                       use_graphs=not args.no_graphs)
     del weights
     torch.cuda.empty_cache()
     gen = torch.Generator().manual_seed(1)
@@ -202,7 +204,6 @@ def main():
     for _ in range(W):
         engine.step()
     key = (next(b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b >= B), True)
-    graph = engine._graphs[key]
     sampler = ClockSampler(local)
     launches0 = ops.launch_count() + engine.stats["graph_replays"] * engine.launches_per_graph.get(key, 0)
     barrier()

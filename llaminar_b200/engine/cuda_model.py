@@ -205,7 +205,7 @@ class CudaModel:
     def _pack_gate_up(self, g: QTensor, u: QTensor) -> QLinear:
         dev = self.device
         n, k = g.shape
-        if g.qtype == u.qtype and can_pack(g.qtype, k) and n % 64 == 0:
+        if g.qtype == u.qtype and can_pack(g.qtype, k) and n % 16 == 0:
             raw, qt, n2, _ = interleave_gate_up(g.raw.to(dev), u.raw.to(dev), g.qtype, n, k)
             lin = QLinear([(pack_matrix(raw, qt, n2, k), 0)], n2, k)
             lin.fused_swiglu = True

@@ -427,7 +427,12 @@ class LLMEngine:
 
     def _decode_eager(self, reqs: list[Request]) -> list[int]:
         fb = self._decode_batch_tensors(reqs)
+        evp = self.step_events.pop() if self.step_events else None
+        if evp:
+            evp[0].record()
         logits, h = self.model.forward(fb, self.kv)
+        if evp:
+            evp[1].record()
         for i, r in enumerate(reqs):
             r.hidden = h[i].clone()
         return self._sample_rows(logits, reqs)

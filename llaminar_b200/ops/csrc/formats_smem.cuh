@@ -1,0 +1,229 @@
+// Per-atom dequantisation of a weight chunk that has been staged in shared memory.
+//
+// A chunk (128 rows x 256 columns) splits into four 64-column "atoms", the K extent of one swizzled
+// MMA operand tile.  DequantAtom<FMT, A>::run converts atom A of one row (lane == row inside the
+// 32-row group g) to bf16 and hands it to the sink as eight 16-byte groups of 8 consecutive columns:
+//     sink.emit(c, v)   c = 0..7 -> columns 64*A + 8*c .. + 7
+// `raw` is the shared-memory address of the chunk; plane offsets are those of FmtTraits.
+#pragma once
+#include "formats.cuh"
+
+namespace llm {
+
+LLM_DEVICE uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+LLM_DEVICE uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+LLM_DEVICE uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+LLM_DEVICE uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+LLM_DEVICE uint32_t unit_off(int plane, int U, int g, int u, int lane) { return plane + ((((g * U + u) << 5) + lane) << 4); }
+
+template <int F, int A> struct DequantAtom;
+
+template <int A> struct DequantAtom<FMT_Q4_K, A> {
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
+        using T = FmtTraits<FMT_Q4_K>;
+        const uint4 meta = lds_v4(raw + T::P_META + (((g << 5) + lane) << 4));
+        const uint4 q0 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A, lane));
+        const uint4 q1 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A + 1, lane));
+        const float d = half_bits_to_float(meta.x & 0xffff), dmin = half_bits_to_float(meta.x >> 16);
+        int sc[8], mn[8];
+        unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
+        const __nv_bfloat162 off = __float2bfloat162_rn(128.0f);
+        const __nv_bfloat162 s_lo = __float2bfloat162_rn(d * sc[2 * A]), b_lo = __float2bfloat162_rn(-dmin * mn[2 * A]);
+        const __nv_bfloat162 s_hi = __float2bfloat162_rn(d * sc[2 * A + 1]), b_hi = __float2bfloat162_rn(-dmin * mn[2 * A + 1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 q = h ? q1 : q0;
+            uint4 o;
+            affine4(q.x & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y); affine4(q.y & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h, o);
+            affine4(q.z & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y); affine4(q.w & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h + 1, o);
+            affine4((q.x >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y); affine4((q.y >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h, o);
+            affine4((q.z >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y); affine4((q.w >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h + 1, o);
+        }
+    }
+};
+
+template <int A> struct DequantAtom<FMT_Q5_K, A> {
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
+        using T = FmtTraits<FMT_Q5_K>;
+        const uint4 meta = lds_v4(raw + T::P_META + (((g << 5) + lane) << 4));
+        const float d = half_bits_to_float(meta.x & 0xffff), dmin = half_bits_to_float(meta.x >> 16);
+        int sc[8], mn[8];
+        unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
+        const __nv_bfloat162 off = __float2bfloat162_rn(128.0f);
+        const __nv_bfloat162 s_lo = __float2bfloat162_rn(d * sc[2 * A]), b_lo = __float2bfloat162_rn(-dmin * mn[2 * A]);
+        const __nv_bfloat162 s_hi = __float2bfloat162_rn(d * sc[2 * A + 1]), b_hi = __float2bfloat162_rn(-dmin * mn[2 * A + 1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 q = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A + h, lane));
+            const uint4 hq = lds_v4(raw + unit_off(T::P_QH, 2, g, h, lane));
+            const uint32_t ws[4] = {q.x, q.y, q.z, q.w}, hs[4] = {hq.x, hq.y, hq.z, hq.w};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo[i] = (ws[i] & 0x0f0f0f0fu) | (((hs[i] >> (2 * A)) & 0x01010101u) << 4);
+                hi[i] = ((ws[i] >> 4) & 0x0f0f0f0fu) | (((hs[i] >> (2 * A + 1)) & 0x01010101u) << 4);
+            }
+            uint4 o;
+            affine4(lo[0], off, s_lo, b_lo, o.x, o.y); affine4(lo[1], off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h, o);
+            affine4(lo[2], off, s_lo, b_lo, o.x, o.y); affine4(lo[3], off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h + 1, o);
+            affine4(hi[0], off, s_hi, b_hi, o.x, o.y); affine4(hi[1], off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h, o);
+            affine4(hi[2], off, s_hi, b_hi, o.x, o.y); affine4(hi[3], off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h + 1, o);
+        }
+    }
+};
+
+template <int A> struct DequantAtom<FMT_Q6_K, A> {
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
+        using T = FmtTraits<FMT_Q6_K>;
+        constexpr int n = A >> 1, hi_half = A & 1;           // atom 2n: low nibbles, atom 2n+1: high nibbles
+        const int row = (g << 5) + lane;
+        const uint4 scw = lds_v4(raw + T::P_SC + (row << 4));
+        const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
+        const float d = half_bits_to_float((uint16_t)lds_u16(raw + T::P_D + (row << 1)));
+        const __nv_bfloat162 off = __float2bfloat162_rn(160.0f), zero = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int lh = 0; lh < 2; ++lh) {
+            const uint4 QA = lds_v4(raw + unit_off(T::P_QL, 8, g, 4 * n + lh, lane));
+            const uint4 QB = lds_v4(raw + unit_off(T::P_QL, 8, g, 4 * n + 2 + lh, lane));
+            const uint4 H = lds_v4(raw + unit_off(T::P_QH, 4, g, 2 * n + lh, lane));
+            const uint32_t as_[4] = {QA.x, QA.y, QA.z, QA.w}, bs_[4] = {QB.x, QB.y, QB.z, QB.w}, hs_[4] = {H.x, H.y, H.z, H.w};
+            constexpr int t0 = 2 * hi_half;                  // sub-block pair handled by this atom: t0, t0 + 1
+            const int s0 = 8 * n + lh + 2 * t0, s1 = s0 + 2;
+            const __nv_bfloat162 f0 = __float2bfloat162_rn(d * static_cast<int8_t>((scs[s0 >> 2] >> (8 * (s0 & 3))) & 0xff));
+            const __nv_bfloat162 f1 = __float2bfloat162_rn(d * static_cast<int8_t>((scs[s1 >> 2] >> (8 * (s1 & 3))) & 0xff));
+            uint32_t qa[4], qb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (hi_half == 0) {
+                    qa[i] = (as_[i] & 0x0f0f0f0fu) | ((hs_[i] << 4) & 0x30303030u);
+                    qb[i] = (bs_[i] & 0x0f0f0f0fu) | ((hs_[i] << 2) & 0x30303030u);
+                } else {
+                    qa[i] = ((as_[i] >> 4) & 0x0f0f0f0fu) | (hs_[i] & 0x30303030u);
+                    qb[i] = ((bs_[i] >> 4) & 0x0f0f0f0fu) | ((hs_[i] >> 2) & 0x30303030u);
+                }
+            }
+            uint4 o;
+            affine4(qa[0], off, f0, zero, o.x, o.y); affine4(qa[1], off, f0, zero, o.z, o.w);
+            sink.emit(2 * lh, o);
+            affine4(qa[2], off, f0, zero, o.x, o.y); affine4(qa[3], off, f0, zero, o.z, o.w);
+            sink.emit(2 * lh + 1, o);
+            affine4(qb[0], off, f1, zero, o.x, o.y); affine4(qb[1], off, f1, zero, o.z, o.w);
+            sink.emit(4 + 2 * lh, o);
+            affine4(qb[2], off, f1, zero, o.x, o.y); affine4(qb[3], off, f1, zero, o.z, o.w);
+            sink.emit(4 + 2 * lh + 1, o);
+        }
+    }
+};
+
+template <int A> struct DequantAtom<FMT_Q8_0, A> {
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
+        using T = FmtTraits<FMT_Q8_0>;
+        const uint4 dw = lds_v4(raw + T::P_D + (((g << 5) + lane) << 4));
+        const uint32_t ds[4] = {dw.x, dw.y, dw.z, dw.w};
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+            const int u = 4 * A + uu, b = u >> 1;
+            const uint4 q = lds_v4(raw + unit_off(T::P_QS, 16, g, u, lane));
+            const float d = half_bits_to_float((ds[b >> 1] >> (16 * (b & 1))) & 0xffff);
+            const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v0 = d * static_cast<int8_t>(ws[i] & 0xff), v1 = d * static_cast<int8_t>((ws[i] >> 8) & 0xff);
+                const float v2 = d * static_cast<int8_t>((ws[i] >> 16) & 0xff), v3 = d * static_cast<int8_t>(ws[i] >> 24);
+                o[2 * i] = pack_bf16(v0, v1);
+                o[2 * i + 1] = pack_bf16(v2, v3);
+            }
+            sink.emit(2 * uu, make_uint4(o[0], o[1], o[2], o[3]));
+            sink.emit(2 * uu + 1, make_uint4(o[4], o[5], o[6], o[7]));
+        }
+    }
+};
+
+template <int A> struct DequantAtom<FMT_Q4_0, A> {
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
+        using T = FmtTraits<FMT_Q4_0>;
+        const uint4 dw = lds_v4(raw + T::P_D + (((g << 5) + lane) << 4));
+        const uint32_t ds[4] = {dw.x, dw.y, dw.z, dw.w};
+        const __nv_bfloat162 off = __float2bfloat162_rn(136.0f), zero = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {
+            const int b = 2 * A + bb;
+            const uint4 q = lds_v4(raw + unit_off(T::P_QS, 8, g, b, lane));
+            const __nv_bfloat162 s = __float2bfloat162_rn(half_bits_to_float((ds[b >> 1] >> (16 * (b & 1))) & 0xffff));
+            uint4 o;
+            affine4(q.x & 0x0f0f0f0fu, off, s, zero, o.x, o.y); affine4(q.y & 0x0f0f0f0fu, off, s, zero, o.z, o.w);
+            sink.emit(4 * bb, o);
+            affine4(q.z & 0x0f0f0f0fu, off, s, zero, o.x, o.y); affine4(q.w & 0x0f0f0f0fu, off, s, zero, o.z, o.w);
+            sink.emit(4 * bb + 1, o);
+            affine4((q.x >> 4) & 0x0f0f0f0fu, off, s, zero, o.x, o.y); affine4((q.y >> 4) & 0x0f0f0f0fu, off, s, zero, o.z, o.w);
+            sink.emit(4 * bb + 2, o);
+            affine4((q.z >> 4) & 0x0f0f0f0fu, off, s, zero, o.x, o.y); affine4((q.w >> 4) & 0x0f0f0f0fu, off, s, zero, o.z, o.w);
+            sink.emit(4 * bb + 3, o);
+        }
+    }
+};
+
+template <int A> struct DequantAtom<FMT_IQ3_S, A> {
+    // `grid`: shared-memory copy of the 512-entry codebook
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink, const uint32_t* grid) {
+        using T = FmtTraits<FMT_IQ3_S>;
+        const int row = (g << 5) + lane;
+        const uint2 qh = lds_v2(raw + T::P_QH + (row << 3));
+        const uint32_t scw = lds_u32(raw + T::P_SC + (row << 2));
+        const float d = half_bits_to_float((uint16_t)lds_u16(raw + T::P_D + (row << 1)));
+        const uint4 q4 = lds_v4(raw + unit_off(T::P_QS, 4, g, A, lane));
+        const uint4 s4 = lds_v4(raw + unit_off(T::P_SIGNS, 2, g, A >> 1, lane));
+        const __nv_bfloat162 off = __float2bfloat162_rn(128.0f), zero = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            constexpr int dummy = 0; (void)dummy;
+            const int ib = 2 * A + k;
+            const uint32_t qa = k ? q4.z : q4.x, qb = k ? q4.w : q4.y;
+            const uint32_t hb = ((ib < 4 ? qh.x : qh.y) >> (8 * (ib & 3))) & 0xff;
+            const uint32_t sw = (ib & 3) == 0 ? s4.x : (ib & 3) == 1 ? s4.y : (ib & 3) == 2 ? s4.z : s4.w;
+            const __nv_bfloat162 db = __float2bfloat162_rn(d * (1 + 2 * ((scw >> (4 * ib)) & 0xf)));
+#pragma unroll
+            for (int l = 0; l < 4; ++l) {
+                const uint32_t pair = (l < 2 ? qa : qb) >> (16 * (l & 1));
+                const uint32_t i1 = (pair & 0xff) | ((hb << (8 - 2 * l)) & 256);
+                const uint32_t i2 = ((pair >> 8) & 0xff) | ((hb << (7 - 2 * l)) & 256);
+                const uint32_t sb = (sw >> (8 * l)) & 0xff;
+                uint4 o;
+                affine4(grid[i1], off, db, zero, o.x, o.y);
+                affine4(grid[i2], off, db, zero, o.z, o.w);
+                o.x ^= ((sb & 1) << 15) | ((sb & 2) << 30);
+                o.y ^= ((sb & 4) << 13) | ((sb & 8) << 28);
+                o.z ^= ((sb & 16) << 11) | ((sb & 32) << 26);
+                o.w ^= ((sb & 64) << 9) | ((sb & 128) << 24);
+                sink.emit(4 * k + l, o);
+            }
+        }
+    }
+};
+
+}  // namespace llm

@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     }
     if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
-        if (!(p.flags & 1)) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -272,31 +272,20 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     constexpr int HALF_COLS = BM / 2;
     constexpr int CHUNKS = HALF_COLS / 16;
     const bool split = gridDim.z > 1;
-    float* exch = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));   // reuse ring memory: [2][64][17]
 
     auto finish = [&](int c0, float (&v)[16]) {
         // v[i]: value for token m0 + c0 + i, output row n_row
         const int m_base = tile_m * BM + c0;
         if (p.epi == EPI_SWIGLU) {
-            float* ex = exch + half * 64 * 17;
-            if (q >= 2) {
+            // rows of a 32-row group: 16 gate rows then the 16 matching up rows -> pair lanes l and l + 16
+            const int col = tile_n * 64 + q * 16 + (lane & 15);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) ex[(row_in_tile - 64) * 17 + i] = v[i];
+            for (int i = 0; i < 16; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                const int m = m_base + i;
+                if (lane < 16 && m < p.m && col < p.n / 2)
+                    static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] = __float2bfloat16(silu(v[i]) * other);
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (q < 2) {
-                const int col = tile_n * 64 + row_in_tile;
-                if (col < p.n / 2) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int m = m_base + i;
-                        if (m < p.m)
-                            static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] =
-                                __float2bfloat16(silu(v[i]) * ex[row_in_tile * 17 + i]);
-                    }
-                }
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
             return;
         }
         if (n_row >= p.n) return;
@@ -314,7 +303,6 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     };
 
     if (warp < 8 && !split) {
-        // SwiGLU needs every epilogue warp at its named barrier, so a dead pipeline still walks the loop
         for (int c = 0; c < CHUNKS; ++c) {
             const int c0 = half * HALF_COLS + c * 16;
             float v[16];
@@ -327,7 +315,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0.f;
             }
-            if (live || p.epi == EPI_SWIGLU) finish(c0, v);
+            if (live) finish(c0, v);
         }
     }
     if (split) {
@@ -383,7 +371,6 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         __syncthreads();
     }
     if (warp == 9) {
-        if (p.flags & 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
         if (lane == 0) trace(7, 1);
     }
@@ -434,16 +421,19 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
 }  // namespace tc
 
 void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* ksplit) {
-    const int bm = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+    const int bm = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));     // 32: persistent small-batch kernel
     const int tiles = ((n + 127) / 128) * ((m + bm - 1) / bm);
     const int kb = k / 256;
     int ks = ksplit_hint;
     if (ks <= 0) {
+        // one CTA per SM: pick the split that minimises (waves of CTAs) x (chunks per CTA + fixed per-CTA cost)
         ks = 1;
-        if (tiles < 148) {
-            ks = (148 + tiles - 1) / tiles;
-            const int cap = kb / 2 > 0 ? kb / 2 : 1;      // at least two chunks per CTA
-            if (ks > cap) ks = cap;
+        long best = -1;
+        const int max_ks = kb < 16 ? kb : 16;
+        for (int c = 1; c <= max_ks; ++c) {
+            const long waves = ((long)tiles * c + 147) / 148;
+            const long cost = waves * ((kb + c - 1) / c + (c > 1 ? 3 : 2));
+            if (best < 0 || cost < best) { best = cost; ks = c; }
         }
     }
     if (ks > kb) ks = kb;
@@ -469,6 +459,7 @@ cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
     int bm, ks;
     gemm_tc_plan(p.m, p.n, p.k, p.ksplit, &bm, &ks);
     if (ks > 1 && (!p.accum || !p.tickets)) ks = 1;
+    if (bm == 32) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
     switch (p.fmt) {
         case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(p, bm, ks, st);
         case FMT_Q5_K: return launch_fmt<FMT_Q5_K>(p, bm, ks, st);

@@ -21,11 +21,13 @@ struct GemmTcParams {
     int accum_stride;
     int ksplit;                // 0 = automatic
     int* status;               // optional device word: set to STATUS_TIMEOUT if a pipeline wait gave up
-    int* debug;                // optional host-mapped trace buffer: 8 ints per CTA (progress markers)
-    int flags;                 // bit 0: relinquish the TMEM allocation permit at teardown instead of right after alloc
+    int* debug;                // optional trace buffer (progress markers / ns timestamps written by the kernels); nullptr in production
+    int flags;                 // bit 1 (set by the launcher): stream-K work split in the small-batch kernel
 };
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
+// small-batch kernel (block_m 32 or 64), implemented in gemm_tc_small.cu
+cudaError_t launch_gemm_tc_small(const GemmTcParams& p, int block_m, int ksplit, cudaStream_t st);
 // tokens per CTA tile and split factor the launcher would use (for sizing scratch)
 void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* ksplit);
 

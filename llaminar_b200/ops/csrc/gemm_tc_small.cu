@@ -1,0 +1,533 @@
+// Small-batch (5 <= M <= 64 rows) variant of the tcgen05 dequant GEMM: the weight-streaming, memory-bound regime
+// of batched decode.  out[M, N] = x[M, K] * dequant(W)[N, K]^T with weights in the MMA M dimension.
+//
+// Differences from the large-tile kernel in gemm_tc.cu:
+//   * raw weight chunks are fetched by ONE bulk copy each (cp.async.bulk, ~14-34 KB) into a deep shared-memory
+//     ring, so HBM latency is hidden by bytes in flight rather than by warps waiting on global loads;
+//   * 16 dequant warps cooperate on every chunk: warp (g, a) converts the 64-column atom `a` of row group `g`
+//     (lane == row), reading the packed bytes with ld.shared and storing the bf16 values straight into tensor
+//     memory (tcgen05.st), from where the MMA takes its A operand: no shared-memory round trip for the weights;
+//   * persistent CTAs (one per SM) walk a contiguous range of (tile, chunk) work ("stream-K"): every SM streams
+//     the same number of bytes, barriers / TMEM are set up once, and two TMEM accumulators let the MMAs of the
+//     next tile start while the previous tile's epilogue drains;
+//   * SwiGLU pairs gate and up rows inside one warp (16 + 16 rows), so the epilogue needs a shuffle only.
+// Warp roles: 0-15 dequant + epilogue, 16 raw-chunk bulk producer, 17 activation TMA producer, 18-19 MMA issuers
+// (18 also owns the TMEM allocation).
+// Every stage and raw slot is visited once per revolution by each waiter, so 1-bit mbarrier parities are exact.
+#include <cuda.h>
+
+#include "formats_smem.cuh"
+#include "gemm_tc.h"
+#include "gemv.h"
+
+namespace llm {
+namespace tcs {
+
+constexpr int A_ATOM_BYTES = 128 * 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int N_DQ_WARPS = 16;
+constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activation producer, two MMA issuers
+
+LLM_DEVICE void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+LLM_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+LLM_DEVICE void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 512) {
+            if (*abort_flag) return false;
+            __nanosleep(40);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+LLM_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+LLM_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+LLM_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+LLM_DEVICE void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+LLM_DEVICE uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+LLM_DEVICE void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+LLM_DEVICE void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+LLM_DEVICE void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int FMT, int BM> struct Cfg {
+    static_assert(BM == 32, "the small-batch kernel is built for one 32-token tile");
+    static constexpr int B_ATOM_BYTES = BM * 128;         // activation tile: BM tokens x 64 columns, 128B-swizzled
+    static constexpr int N_B_STAGES = 8;                  // two chunks of four 64-column atoms
+    static constexpr int RING_BYTES = N_B_STAGES * B_ATOM_BYTES;
+    static constexpr int CHUNK = FmtTraits<FMT>::CHUNK;
+    static constexpr int BUDGET = 218 * 1024 - RING_BYTES;
+    static constexpr int RAW_SLOTS_ = BUDGET / CHUNK;
+    static constexpr int RAW_SLOTS = RAW_SLOTS_ > 8 ? 8 : RAW_SLOTS_;
+    static_assert(RAW_SLOTS >= 2, "not enough shared memory for the raw chunk ring");
+    static constexpr int SMEM_BYTES = RING_BYTES + RAW_SLOTS * CHUNK + 1024;
+    static constexpr int COLS_PER_WARP = BM / 4;          // epilogue: 4 column parts x 4 lane quarters
+    // Tensor memory map (512 columns x 128 lanes, all of it):
+    //   [0, 256)    accumulators.  Control overhead per barrier wait / tcgen05.commit (~0.1 us each) dwarfs a 128x32x16
+    //               MMA, so the pipeline synchronises per 256-column chunk (16 MMAs) and two issuer warps take alternate
+    //               chunks.  Each issuer accumulates into its own pair of regions (even / odd K steps); the epilogue adds
+    //               them up; the whole set is double-buffered so the MMAs of unit i + 1 overlap the epilogue of unit i.
+    //   [256, 512)  the dequantised weight operand (MMA "A from TMEM"): two chunks of 128 rows x 256 bf16 = 128 columns
+    //               each.  Lane == weight row == dequant lane, so the dequant warps store their registers straight into
+    //               TMEM (tcgen05.st) and the bf16 weights never pass through shared memory.
+    static constexpr int N_ISSUERS = 2;
+    static constexpr int ACC_PER_ISSUER = 2;
+    static constexpr int ACC_SET_COLS = N_ISSUERS * ACC_PER_ISSUER * BM;
+    static constexpr int A_COLS_OFFSET = 2 * ACC_SET_COLS;
+    static constexpr int A_CHUNK_COLS = 128;
+    static constexpr int TMEM_COLS = 512;
+    static_assert(A_COLS_OFFSET + 2 * A_CHUNK_COLS <= TMEM_COLS, "tensor memory map overflows");
+};
+
+// Sink of a dequant warp: 8 bf16 (one uint4) -> 4 TMEM columns of this lane's row.
+struct TmemSink {
+    uint32_t taddr;         // lane quarter | first column of this atom in the current chunk's A region
+    LLM_DEVICE void emit(int c, uint4 v) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr + c * 4), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+};
+
+// Work distribution.  The (n_tile, chunk) pairs are flattened tile-major.  With scratch for partial sums
+// (stream-K mode) CTA b takes the contiguous range [b*T/G, (b+1)*T/G) and therefore at most a few tiles, some
+// of them partially; a partially covered tile is reduced through fp32 atomics and finished by the last
+// contributor.  Without scratch every CTA takes whole tiles round-robin.
+struct Unit { int tile, kb0, nkb, contributors; };
+struct UnitIter {
+    int k_blocks, n_tiles, total, G, b, streamk;
+    int pos, end;
+    LLM_DEVICE void init(int kb, int nt, int grid, int cta, int sk) {
+        k_blocks = kb; n_tiles = nt; total = kb * nt; G = grid; b = cta; streamk = sk;
+        if (streamk) { pos = (int)(((long long)b * total) / G); end = (int)(((long long)(b + 1) * total) / G); }
+        else { pos = b; end = n_tiles; }
+    }
+    LLM_DEVICE int cta_of(int x) const { return (int)((((long long)(x + 1)) * G - 1) / total); }
+    LLM_DEVICE bool next(Unit& u) {
+        if (pos >= end) return false;
+        if (streamk) {
+            u.tile = pos / k_blocks;
+            u.kb0 = pos - u.tile * k_blocks;
+            u.nkb = min(k_blocks - u.kb0, end - pos);
+            u.contributors = cta_of(u.tile * k_blocks + k_blocks - 1) - cta_of(u.tile * k_blocks) + 1;
+            pos += u.nkb;
+        } else {
+            u.tile = pos; u.kb0 = 0; u.nkb = k_blocks; u.contributors = 1;
+            pos += G;
+        }
+        return true;
+    }
+};
+
+template <int FMT, int BM>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmTcParams p) {
+    using C = Cfg<FMT, BM>;
+    constexpr int R = C::RAW_SLOTS;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[2], s_empty[2], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort, s_last;
+    __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k_blocks = p.k / 256, n_tiles = (p.n + 127) / 128;
+    const int streamk = p.flags & 2;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t raw_base = smem_base + C::RING_BYTES;       // activation ring first, raw weight chunks behind it
+    const uint32_t full_bar = smem_u32(s_full), empty_bar = smem_u32(s_empty);
+    const uint32_t rawf_bar = smem_u32(s_raw_full), rawe_bar = smem_u32(s_raw_empty);
+    const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < 2; ++s) { mbar_init(full_bar + s * 8, N_DQ_WARPS + 1); mbar_init(empty_bar + s * 8, 1); }
+        for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, N_DQ_WARPS); }
+        for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
+        mbar_init(epi_bar, N_DQ_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (FMT == FMT_IQ3_S) {
+        for (int i = tid; i < 512; i += blockDim.x) s_grid[i] = g_iq3s_grid[i];
+    }
+    if (warp == N_DQ_WARPS + 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem;
+    volatile int* abort_flag = &s_abort;
+    // optional timeline trace of CTA 0: p.debug[role * 1024 + slot] = low 32 bits of the ns timer
+    auto stamp = [&](int role, int slot) {
+        if (p.debug && blockIdx.x == 0 && slot < 1024) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.debug[role * 1024 + slot] = (int)(t & 0x7fffffff);
+        }
+    };
+    // per-CTA start / end stamps: p.debug[4096 + 4 * cta + {0, 1, 2}] = start, end, end of dequant loop
+    auto cta_stamp = [&](int slot) {
+        if (p.debug) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.debug[4096 + 4 * blockIdx.x + slot] = (int)(t & 0x7fffffff);
+        }
+    };
+    if (tid == 0) cta_stamp(0);
+    UnitIter it;
+    it.init(k_blocks, n_tiles, gridDim.x, blockIdx.x, streamk);
+    Unit u;
+
+    // chunk counter cc -> half of the operand ring (stages set*4 .. set*4+3) and the phase of its barriers
+    auto set_of = [](int cc) { return cc & 1; };
+    auto sphase_of = [](int cc) { return (cc >> 1) & 1; };
+
+    if (warp < N_DQ_WARPS) {
+        // ---------------- dequant + epilogue: warp (g, a) converts atom a of row group g of every chunk ----------------
+        const int g = warp & 3, a = warp >> 2;
+        const int row = g * 32 + lane;
+        const int q = g, part = a;                         // epilogue: TMEM lane quarter q, column part `part`
+        constexpr int CW = C::COLS_PER_WARP;
+        TmemSink sink{0};
+        int cc = 0, ui = 0, epi_syncs = 0;
+        bool ok = true;
+        while (ok && it.next(u)) {
+            for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                const int slot = cc % R, rphase = (cc / R) & 1;
+                const int set = set_of(cc);
+                ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
+                if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
+                if (!ok) break;
+                const uint32_t raw = raw_base + slot * C::CHUNK;
+                sink.taddr = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS + a * 32;
+                if constexpr (FMT == FMT_IQ3_S) {
+                    switch (a) {
+                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink, s_grid); break;
+                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink, s_grid); break;
+                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink, s_grid); break;
+                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink, s_grid); break;
+                    }
+                } else {
+                    switch (a) {
+                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink); break;
+                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink); break;
+                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink); break;
+                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
+                    }
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_bar + set * 8);        // this warp's part of the chunk's weight operand is in TMEM
+                    mbar_arrive(rawe_bar + slot * 8);       // this warp no longer needs the raw chunk
+                    if (warp == 0) stamp(0, cc * 4 + 2);
+                }
+            }
+            if (!ok) break;
+            // ---- epilogue of this unit ----
+            const int buf = ui & 1;
+            if (warp == 0 && lane == 0) stamp(3, ui * 4 + 0);
+            ok = mbar_wait(accf_bar + buf * 8, (ui >> 1) & 1, abort_flag);
+            if (warp == 0 && lane == 0) stamp(3, ui * 4 + 1);
+            if (!ok) break;
+            tc_fence_after();
+            float v[CW];
+            const int c0 = part * CW;
+            // issuer w worked on this unit iff the unit has a chunk of parity w
+            const int cc0 = cc - u.nkb;
+            const bool has0 = u.nkb >= 2 || (cc0 & 1) == 0, has1 = u.nkb >= 2 || (cc0 & 1) == 1;
+#pragma unroll
+            for (int i = 0; i < CW; ++i) v[i] = 0.f;
+#pragma unroll
+            for (int acc = 0; acc < C::N_ISSUERS * C::ACC_PER_ISSUER; ++acc) {
+                const bool valid = (acc < C::ACC_PER_ISSUER) ? has0 : has1;
+                if (!valid) continue;
+#pragma unroll
+                for (int j = 0; j < CW / 8; ++j) {
+                    uint32_t r[8];
+                    tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + buf * C::ACC_SET_COLS + acc * BM + c0 + j * 8, r);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[j * 8 + i] += __uint_as_float(r[i]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar + buf * 8);   // accumulator may be overwritten by unit ui + 2
+            ++ui;
+            const int n_row = u.tile * 128 + row;
+            bool do_finish = true;
+            if (u.contributors > 1) {
+#pragma unroll
+                for (int i = 0; i < CW; ++i) {
+                    const int m = c0 + i;
+                    if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], v[i]);
+                }
+                __threadfence();
+                __syncwarp();
+                // all 16 epilogue warps meet (bounded) before and after the arrival ticket is taken
+                if (lane == 0) mbar_arrive(epi_bar);
+                ok = mbar_wait(epi_bar, epi_syncs & 1, abort_flag); ++epi_syncs;
+                if (!ok) break;
+                if (tid == 0) {
+                    const unsigned t = atomicAdd(&p.tickets[u.tile], 1u);
+                    s_last = (t == (unsigned)u.contributors - 1);
+                    if (s_last) p.tickets[u.tile] = 0u;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(epi_bar);
+                ok = mbar_wait(epi_bar, epi_syncs & 1, abort_flag); ++epi_syncs;
+                if (!ok) break;
+                do_finish = s_last != 0;
+                if (do_finish) {
+                    __threadfence();
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) {
+                        const int m = c0 + i;
+                        v[i] = 0.f;
+                        if (m < p.m) {
+                            float* acc = &p.accum[(size_t)m * p.accum_stride + n_row];
+                            v[i] = __ldcg(acc);
+                            __stcg(acc, 0.f);
+                        }
+                    }
+                }
+                // s_last is rewritten by the next split unit only after every warp passed the barrier above
+            }
+            if (do_finish) {
+                if (p.epi == EPI_SWIGLU) {
+                    // rows of a 32-row group: 16 gate rows then the 16 matching up rows -> pair lanes l and l + 16
+                    const int col = u.tile * 64 + g * 16 + (lane & 15);
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                        const int m = c0 + i;
+                        if (lane < 16 && m < p.m && col < p.n / 2)
+                            static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] = __float2bfloat16(silu(v[i]) * other);
+                    }
+                } else if (n_row < p.n) {
+                    const float b = p.bias ? p.bias[n_row] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) {
+                        const int m = c0 + i;
+                        if (m >= p.m) continue;
+                        const size_t idx = (size_t)m * p.out_stride + n_row;
+                        const float o = v[i] + b;
+                        if (p.epi == EPI_RESID) { float* h = static_cast<float*>(p.out); h[idx] += o; }
+                        else if (p.out_f32) static_cast<float*>(p.out)[idx] = o;
+                        else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(o);
+                    }
+                }
+            }
+        }
+    } else if (warp == N_DQ_WARPS) {
+        // ---------------- raw chunk producer: the whole warp streams each chunk with 16-byte cp.async ----------------
+        // (measured: one cp.async.bulk per chunk tops out near 10 GB/s per SM here, far below what LDGSTS sustains)
+        int cc = 0;
+        bool ok = true;
+        while (ok && it.next(u)) {
+            const uint8_t* wsrc = p.w + ((size_t)u.tile * k_blocks + u.kb0) * C::CHUNK;
+            for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                const int slot = cc % R, rphase = (cc / R) & 1;
+                ok = mbar_wait(rawe_bar + slot * 8, rphase ^ 1, abort_flag);
+                if (!ok) break;
+                const uint8_t* src = wsrc + (size_t)c * C::CHUNK + lane * 16;
+                const uint32_t dst = raw_base + slot * C::CHUNK + lane * 16;
+#pragma unroll 4
+                for (int i = 0; i < C::CHUNK / 512; ++i)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 512), "l"(src + i * 512) : "memory");
+                if constexpr (C::CHUNK % 512 != 0) {
+                    constexpr int full = (C::CHUNK / 512) * 512;
+                    if (lane < (C::CHUNK % 512) / 16)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + full), "l"(src + full) : "memory");
+                }
+                // the barrier receives one arrival per lane once that lane's copies have landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(rawf_bar + slot * 8) : "memory");
+                if (lane == 0) stamp(1, cc);
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == N_DQ_WARPS + 1) {
+        // ---------------- activation tile producer (TMA): the four 64-column tiles of a chunk on one barrier ----------------
+        if (lane == 0) {
+            int cc = 0;
+            bool ok = true;
+            while (ok && it.next(u)) {
+                for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                    const int set = set_of(cc);
+                    ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_bar + set * 8, 4 * C::B_ATOM_BYTES);
+#pragma unroll
+                    for (int a = 0; a < 4; ++a)
+                        tma_load_2d(smem_base + (set * 4 + a) * C::B_ATOM_BYTES, &tmap_x, (u.kb0 + c) * 256 + a * 64, 0,
+                                    full_bar + set * 8);
+                }
+            }
+        }
+    } else {
+        // ---------------- MMA issuers: warp w takes the chunks of parity w ----------------
+        const int w = warp - (N_DQ_WARPS + 2);
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BM);
+            int cc = 0, ui = 0;
+            bool ok = true;
+            while (ok && it.next(u)) {
+                const int buf = ui & 1;
+                ok = mbar_wait(acce_bar + buf * 8, ((ui >> 1) & 1) ^ 1, abort_flag);     // epilogue of unit ui - 2 has drained this accumulator set
+                if (!ok) break;
+                tc_fence_after();
+                bool first = true;
+                for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                    if (set_of(cc) != w) continue;
+                    ok = mbar_wait(full_bar + w * 8, sphase_of(cc), abort_flag);
+                    if (w == 0) stamp(2, cc * 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t acc_base = tmem_base + buf * C::ACC_SET_COLS + w * C::ACC_PER_ISSUER * BM;
+                    const uint32_t a_tmem = tmem_base + C::A_COLS_OFFSET + w * C::A_CHUNK_COLS;
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+                        const uint64_t bdesc = smem_desc_sw128(smem_base + (w * 4 + a) * C::B_ATOM_BYTES);
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4)      // 16 columns of K = 8 TMEM columns of A, 32 bytes of the swizzled B row
+                            mma_f16_ts(acc_base + (k4 & 1) * BM, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc,
+                                       (first && a == 0 && k4 < 2) ? 0u : 1u);
+                    }
+                    mma_commit(empty_bar + w * 8);
+                    if (w == 0) stamp(2, cc * 2 + 1);
+                    first = false;
+                }
+                if (ok) mma_commit(accf_bar + buf * 8);
+                ++ui;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    if (tid == 0) { stamp(3, 1023); cta_stamp(2); }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0 && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
+        for (int i = 0; i < 2000; ++i) __nanosleep(100);   // let copies still in flight land before the CTA's memory is reused
+        __syncthreads();
+    }
+    if (warp == N_DQ_WARPS + 2) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    }
+    if (tid == 0) cta_stamp(1);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+template <int FMT, int BM>
+static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st) {
+    using C = Cfg<FMT, BM>;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.k * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.x), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<FMT, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    // persistent: one CTA per SM (or fewer when there is less work than that)
+    GemmTcParams q = p;
+    const int n_tiles = (p.n + 127) / 128, k_blocks = p.k / 256;
+    const bool streamk = ksplit != 1 && p.accum && p.tickets;
+    q.flags = (p.flags & ~2) | (streamk ? 2 : 0);
+    const int units = streamk ? n_tiles * k_blocks : n_tiles;
+    static int cached_sms = 0;
+    if (!cached_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev); }
+    const int sms = cached_sms > 0 ? cached_sms : 148;
+    const int grid = units < sms ? units : sms;
+    gemm_tc_small_kernel<FMT, BM><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmap, q);
+    return cudaGetLastError();
+}
+
+template <int FMT>
+static cudaError_t launch_fmt(const GemmTcParams& p, int bm, int ks, cudaStream_t st) {
+    if (bm == 32) return launch_one<FMT, 32>(p, ks, st);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tcs
+
+cudaError_t launch_gemm_tc_small(const GemmTcParams& p, int bm, int ks, cudaStream_t st) {
+    switch (p.fmt) {
+        case FMT_Q4_K: return tcs::launch_fmt<FMT_Q4_K>(p, bm, ks, st);
+        case FMT_Q5_K: return tcs::launch_fmt<FMT_Q5_K>(p, bm, ks, st);
+        case FMT_Q6_K: return tcs::launch_fmt<FMT_Q6_K>(p, bm, ks, st);
+        case FMT_Q8_0: return tcs::launch_fmt<FMT_Q8_0>(p, bm, ks, st);
+        case FMT_Q4_0: return tcs::launch_fmt<FMT_Q4_0>(p, bm, ks, st);
+        case FMT_IQ3_S: return tcs::launch_fmt<FMT_IQ3_S>(p, bm, ks, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace llm

@@ -147,18 +147,14 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     }
     // ---- epilogue ----
     if (p.epi == EPI_SWIGLU) {
-        __syncthreads();
-        if (tid >= 64 && tid < 128) {
-#pragma unroll
-            for (int m = 0; m < M; ++m) s_red[m * 64 + (tid - 64)] = v[m];
-        }
-        __syncthreads();
-        const int col = tile * 64 + tid;
-        if (tid < 64 && col < p.n / 2) {
+        // a 32-row group holds 16 gate rows followed by the 16 matching up rows: pair lanes l and l + 16
+        if (tid < 128) {
+            const int col = tile * 64 + (tid >> 5) * 16 + (lane & 15);
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const float o = silu(v[m]) * s_red[m * 64 + tid];
-                static_cast<__nv_bfloat16*>(p.out)[(size_t)(m0 + m) * p.out_stride + col] = __float2bfloat16(o);
+                const float other = __shfl_xor_sync(0xffffffffu, v[m], 16);
+                if (lane < 16 && col < p.n / 2)
+                    static_cast<__nv_bfloat16*>(p.out)[(size_t)(m0 + m) * p.out_stride + col] = __float2bfloat16(silu(v[m]) * other);
             }
         }
         return;

@@ -119,17 +119,17 @@ cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// SwiGLU over the tile-interleaved gate|up GEMM output; residual add
+// SwiGLU over the 16-column-interleaved gate|up GEMM output; residual add
 // ------------------------------------------------------------------------------------------------
 __global__ void swiglu_tiled_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int d_ff) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;     // one thread per 2 output columns
     const int half = d_ff / 2;
     if (i >= (size_t)rows * half) return;
     const int r = i / half, c = (i % half) * 2;
-    const int tile = c / 64, off = c % 64;
-    const __nv_bfloat16* base = gu + (size_t)r * 2 * d_ff + tile * 128;
+    const int grp = c / 16, off = c % 16;                 // 32 fused columns = 16 gate + 16 up
+    const __nv_bfloat16* base = gu + (size_t)r * 2 * d_ff + grp * 32;
     const uint32_t g = *reinterpret_cast<const uint32_t*>(base + off);
-    const uint32_t u = *reinterpret_cast<const uint32_t*>(base + 64 + off);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(base + 16 + off);
     *reinterpret_cast<uint32_t*>(out + (size_t)r * d_ff + c) = pack_bf16(silu(bf16_lo(g)) * bf16_lo(u), silu(bf16_hi(g)) * bf16_hi(u));
 }
 cudaError_t launch_swiglu_tiled(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int d_ff, cudaStream_t st) {

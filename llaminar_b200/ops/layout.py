@@ -126,11 +126,14 @@ def concat_rows(parts: list[tuple[torch.Tensor, GGMLType, int, int]]) -> tuple[t
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, qtype: GGMLType, n: int, k: int):
-    """Row order for the fused SwiGLU epilogue: every 128-row tile = 64 gate rows then 64 up rows."""
-    if n % 64:
-        raise ValueError("gate/up row count must be a multiple of 64")
+    """Row order for the fused SwiGLU epilogue: 16 gate rows, then the 16 up rows of the same outputs.
+
+    A kernel warp owns 32 consecutive fused rows (lane == row), so gate and up of one output column
+    sit in lanes l and l + 16 of the same warp and are combined with one shuffle."""
+    if n % 16:
+        raise ValueError("gate/up row count must be a multiple of 16")
     e, b = BLOCK_GEOMETRY[qtype]
     rb = k // e * b
-    g = gate.reshape(n // 64, 64, rb)
-    u = up.reshape(n // 64, 64, rb)
+    g = gate.reshape(n // 16, 16, rb)
+    u = up.reshape(n // 16, 16, rb)
     return torch.stack([g, u], dim=1).reshape(-1), qtype, 2 * n, k

@@ -153,7 +153,7 @@ def test_rmsnorm_and_swiglu():
     gu = torch.randn(9, 256, device=DEV).to(torch.bfloat16)
     o = torch.empty(9, 128, dtype=torch.bfloat16, device=DEV)
     ops.swiglu_tiled(gu, o)
-    t = gu.float().view(9, 2, 2, 64)
+    t = gu.float().view(9, 8, 2, 16)
     ref = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(9, 128)
     assert _rel(o, ref) < 1e-2
 
