@@ -72,12 +72,14 @@ def _accum_args(pw: PackedWeight, rows: int, sc: Scratch | None):
 
 
 def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
-         epi: int = EPI_STORE, bias: torch.Tensor | None = None, scratch: Scratch | None = None, ksplit: int = 0) -> None:
-    """out[m, :] (+)= x[m, :] @ W^T for m <= 4 rows.  x: fp32 residual rows when ``norm_w`` is given, else bf16."""
+         epi: int = EPI_STORE, bias: torch.Tensor | None = None, scratch: Scratch | None = None, ksplit: int = 0,
+         tp: torch.Tensor | None = None) -> None:
+    """out[m, :] (+)= x[m, :] @ W^T for m <= 4 rows.  x: fp32 residual rows when ``norm_w`` is given, else bf16.
+    ``tp``: device copy of the tensor-parallel descriptor; with EPI_RESID the epilogue all-reduces across ranks."""
     rows = x.shape[0]
     assert 1 <= rows <= GEMV_MAX_ROWS
     accum, tickets = _accum_args(pw, rows, scratch)
-    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1)
+    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1, tp)
     _count()
 
 
@@ -90,16 +92,17 @@ def gemv_experts(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, expert_id
         accum, tickets = None, None
     stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
     ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, None, 0.0, out, epi, None, accum, tickets, 0, expert_ids, stride,
-               slots_per_row, 1, z)
+               slots_per_row, 1, z, None)
     _count()
 
 
 def gemm(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, epi: int = EPI_STORE, bias: torch.Tensor | None = None,
-         scratch: Scratch | None = None, ksplit: int = 0, debug_ptr: int = 0, flags: int = 0) -> None:
+         scratch: Scratch | None = None, ksplit: int = 0, debug_ptr: int = 0, flags: int = 0,
+         tp: torch.Tensor | None = None) -> None:
     """Tensor-core path: out[M, N] (+)= x[M, K] @ dequant(W)^T, any M."""
     accum, tickets = _accum_args(pw, x.shape[0], scratch)
     ext().gemm_tc(pw.data, pw.fmt, pw.n, pw.k, x, out, epi, bias, accum, tickets, ksplit if accum is not None else 1,
-                  scratch.status if scratch is not None else None, debug_ptr, flags)
+                  scratch.status if scratch is not None else None, debug_ptr, flags, tp)
     _count()
 
 

@@ -26,7 +26,8 @@ static void check_cuda(const Tensor& t, const char* name) {
 
 static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, const OptTensor& norm_w, double eps,
                  Tensor out, int64_t epi, const OptTensor& bias, const OptTensor& accum, const OptTensor& tickets,
-                 int64_t ksplit, const OptTensor& expert_ids, int64_t expert_stride, int64_t z_per_x, int64_t m_tile, int64_t z) {
+                 int64_t ksplit, const OptTensor& expert_ids, int64_t expert_stride, int64_t z_per_x, int64_t m_tile, int64_t z,
+                 const OptTensor& tp) {
     check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(k % 256 == 0, "k must be a multiple of 256");
@@ -54,6 +55,7 @@ static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tenso
     if (epi == llm::EPI_SWIGLU) TORCH_CHECK(!p.out_f32, "SwiGLU epilogue writes bf16");
     p.bias = cptr<float>(bias);
     p.expert_ids = cptr<int>(expert_ids); p.expert_stride = (size_t)expert_stride;
+    p.tp = tp.has_value() ? reinterpret_cast<const llm::TpFuse*>(tp->data_ptr()) : nullptr;
     LLM_CUDA_CHECK(llm::launch_gemv(p, (int)m_tile, (int)z, cur_stream()));
 }
 
@@ -222,7 +224,7 @@ static void moe_topk(const Tensor& logits, int64_t k, bool renorm, Tensor ids, T
 
 // tensor-core GEMM: out[M, N] (+)= x[M, K] * dequant(W)[N, K]^T
 static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, Tensor out, int64_t epi, const OptTensor& bias,
-                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status, int64_t debug_ptr, int64_t flags) {
+                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status, int64_t debug_ptr, int64_t flags, const OptTensor& tp) {
     check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "gemm_tc input must be contiguous bf16");
@@ -233,6 +235,8 @@ static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Te
     p.epi = (int)epi; p.bias = cptr<float>(bias); p.status = mptr<int>(status);
     p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets); p.ksplit = (int)ksplit;
     p.debug = reinterpret_cast<int*>(debug_ptr); p.flags = (int)flags;
+    p.tp = tp.has_value() ? reinterpret_cast<const llm::TpFuse*>(tp->data_ptr()) : nullptr;
+    if (tp.has_value()) TORCH_CHECK(p.m <= 32 && epi == llm::EPI_RESID, "fused tensor-parallel epilogue: residual mode, at most 32 rows");
     p.accum_stride = accum.has_value() ? (int)accum->stride(0) : 0;
     if (epi == llm::EPI_RESID) TORCH_CHECK(p.out_f32, "residual epilogue updates an fp32 stream");
     if (accum.has_value()) {

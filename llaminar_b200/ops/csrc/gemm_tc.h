@@ -6,6 +6,8 @@
 
 namespace llm {
 
+struct TpFuse;   // tp_fuse.cuh
+
 struct GemmTcParams {
     const uint8_t* w;          // weight chunks [n_tiles][k_blocks][chunk]
     int fmt;
@@ -22,6 +24,7 @@ struct GemmTcParams {
     int ksplit;                // 0 = automatic
     int* status;               // optional device word: set to STATUS_TIMEOUT if a pipeline wait gave up
     int* debug;                // optional trace buffer (progress markers / ns timestamps written by the kernels); nullptr in production
+    const TpFuse* tp;          // EPI_RESID in the small-batch kernel: fused cross-rank all-reduce of each tile (nullptr: off)
     int flags;                 // bit 1 (set by the launcher): stream-K work split in the small-batch kernel
 };
 

@@ -19,6 +19,7 @@
 #include "formats_smem.cuh"
 #include "gemm_tc.h"
 #include "gemv.h"
+#include "tp_fuse.cuh"
 
 namespace llm {
 namespace tcs {
@@ -164,7 +165,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[2], s_empty[2], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort, s_last;
+    __shared__ int s_abort, s_last, s_tp_ok;
+    __shared__ unsigned s_tp_epoch;
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -346,6 +348,47 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         const int m = c0 + i;
                         if (lane < 16 && m < p.m && col < p.n / 2)
                             static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] = __float2bfloat16(silu(v[i]) * other);
+                    }
+                } else if (p.tp != nullptr && p.epi == EPI_RESID) {
+                    // fused tensor-parallel all-reduce of this tile, then the residual add (see tp_fuse.cuh);
+                    // the 16 epilogue warps meet on the bounded mbarrier between the protocol steps
+                    const TpFuse& tp = *p.tp;
+                    auto epi_sync = [&]() {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(epi_bar);
+                        const bool r = mbar_wait(epi_bar, epi_syncs & 1, abort_flag);
+                        ++epi_syncs;
+                        return r;
+                    };
+                    if (tid == 0) s_tp_epoch = tp.epoch[u.tile];
+                    ok = epi_sync();
+                    if (!ok) break;
+                    const unsigned e = s_tp_epoch;
+                    auto row_of = [&](int i) { return (c0 + i) < p.m ? c0 + i : -1; };
+                    if (n_row < p.n) {
+                        if (p.bias && tp.rank == 0) {
+#pragma unroll
+                            for (int i = 0; i < CW; ++i) v[i] += p.bias[n_row];
+                        }
+                        tp_push<CW>(tp, e, n_row, v, row_of);
+                    }
+                    ok = epi_sync();
+                    if (!ok) break;
+                    if (tid < tp.size) tp_signal(tp, u.tile, tid);
+                    if (tid == 0) {
+                        s_tp_ok = tp_wait(tp, u.tile, e) ? 1 : 0;
+                        tp.epoch[u.tile] = e + 1;
+                    }
+                    ok = epi_sync();
+                    if (!ok) break;
+                    if (s_tp_ok && n_row < p.n) {
+                        tp_reduce<CW>(tp, e, n_row, v, row_of);
+                        float* h = static_cast<float*>(p.out);
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) {
+                            const int m = c0 + i;
+                            if (m < p.m) h[(size_t)m * p.out_stride + n_row] += v[i];
+                        }
                     }
                 } else if (n_row < p.n) {
                     const float b = p.bias ? p.bias[n_row] : 0.f;

@@ -12,6 +12,7 @@
 // src/v2/kernels/cuda/ops/CUDAFusedOpsKernels.cu:37).
 #include "formats.cuh"
 #include "gemv.h"
+#include "tp_fuse.cuh"
 
 namespace llm {
 
@@ -159,6 +160,37 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
         return;
     }
+    if (p.tp != nullptr && p.epi == EPI_RESID) {
+        // fused tensor-parallel all-reduce of this tile, then the residual add (see tp_fuse.cuh)
+        __shared__ unsigned s_epoch;
+        __shared__ int s_ok;
+        const TpFuse& tp = *p.tp;
+        if (tid == 0) s_epoch = tp.epoch[tile];
+        __syncthreads();
+        const unsigned e = s_epoch;
+        auto row_of = [&](int i) { return m0 + i; };
+        if (tid < 128 && row < p.n) {
+            if (p.bias && tp.rank == 0) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) v[m] += p.bias[row];
+            }
+            tp_push<M>(tp, e, row, v, row_of);
+        }
+        __syncthreads();
+        if (tid < tp.size) tp_signal(tp, tile, tid);
+        if (tid == 0) {
+            s_ok = tp_wait(tp, tile, e) ? 1 : 0;
+            tp.epoch[tile] = e + 1;
+        }
+        __syncthreads();
+        if (s_ok && tid < 128 && row < p.n) {
+            tp_reduce<M>(tp, e, row, v, row_of);
+            float* h = static_cast<float*>(p.out);
+#pragma unroll
+            for (int m = 0; m < M; ++m) h[(size_t)(m0 + m) * p.out_stride + row] += v[m];
+        }
+        return;
+    }
     if (tid < 128 && row < p.n) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -217,6 +249,7 @@ size_t gemv_smem_bytes(int m_tile, int k_blocks, int ksplit) {
 // m_tile rows per CTA (1..4), z = number of row groups (grid.z); rows total = m_tile * z.
 cudaError_t launch_gemv(const GemvParams& p, int m_tile, int z, cudaStream_t st) {
     if (m_tile < 1 || m_tile > 4 || z < 1) return cudaErrorInvalidValue;
+    if (p.tp && z != 1) return cudaErrorInvalidValue;      // the per-tile flag protocol serves one row group
     int ks = p.ksplit > 0 ? p.ksplit : gemv_pick_ksplit(p.n_tiles, p.k_blocks, z);
     if (!p.accum || !p.tickets) ks = 1;
     size_t smem = gemv_smem_bytes(m_tile, p.k_blocks, ks);

@@ -6,6 +6,8 @@
 
 namespace llm {
 
+struct TpFuse;   // tp_fuse.cuh
+
 enum GemvEpilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
 struct GemvParams {
@@ -28,6 +30,8 @@ struct GemvParams {
     const float* bias;         // optional [n]
     const int* expert_ids;     // optional [z]: weight matrix index per grid.z group
     size_t expert_stride;      // bytes between expert matrices
+    const TpFuse* tp;          // EPI_RESID only: device copy of the tensor-parallel descriptor -> the epilogue all-reduces
+                               // the tile across ranks before adding it to the residual (nullptr: single rank)
 };
 
 cudaError_t launch_gemv(const GemvParams& p, int m_tile, int z, cudaStream_t st);

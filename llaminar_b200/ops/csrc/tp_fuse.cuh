@@ -1,0 +1,91 @@
+// In-kernel all-reduce of one output tile across tensor-parallel ranks over NVLink peer memory.
+//
+// Used by the epilogues of the row-parallel GEMV / GEMM (attention output and FFN down projections): the CTA
+// that holds a finished partial tile pushes it into every rank's inbox with plain peer stores, bumps a per-tile
+// flag on every rank (red.release.sys), waits -- bounded -- until all ranks' contributions for this call have
+// arrived in its own inbox and then adds their sum to the local residual stream.  One kernel therefore does
+// GEMM + all-reduce + residual add; the reference runs GEMM, ncclAllReduce and an add kernel as three stages
+// (reference: src/v2/models/qwen/QwenGraphBase.cpp:2937-3014, src/v2/collective/LocalTPContext.cpp:726).
+//
+// Protocol per tile t (every rank runs the same sequence of fused calls, all with d_model / 128 tiles):
+//   e = epoch[t] (local call counter), parity = e & 1
+//   inbox[r][parity][my_rank][m][n]  <- my partial, for every rank r          (peer stores)
+//   __threadfence_system(); flags[r][t] += 1 on every rank r                  (release, system scope)
+//   spin (bounded) until flags[me][t] >= (e + 1) * size                        (acquire, system scope)
+//   h[m][n] += sum_src inbox[me][parity][src][m][n]  (src order fixed, so all ranks compute identical bits)
+// A rank can run at most one call ahead of a peer (it needs the peer's tiles of call c to finish call c), so two
+// inbox parities suffice and monotone flags are never satisfied early.  No TMA and no multicast is involved.
+#pragma once
+#include "common.cuh"
+
+namespace llm {
+
+constexpr int TP_MAX_RANKS = 8;
+
+struct TpFuse {
+    float* inbox[TP_MAX_RANKS];        // per rank: [2][size][rows_cap][n_cap] floats (symmetric memory)
+    unsigned* flags[TP_MAX_RANKS];     // per rank: [n_cap / 128] arrival counters (symmetric memory)
+    unsigned* epoch;                   // local: [n_cap / 128] call counters
+    int* status;                       // local: set to STATUS_TIMEOUT when a wait gives up
+    int rank, size, rows_cap, n_cap;
+    unsigned spin_limit;               // iterations of the bounded wait
+};
+
+LLM_DEVICE unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+LLM_DEVICE void red_release_sys_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Step 1: push.  v[i] is this thread's partial for (row m_first + i * m_step ... caller-defined), column n.
+// The caller passes a functor row_of(i) -> activation row index (or -1 to skip).
+template <int NV, class RowOf>
+LLM_DEVICE void tp_push(const TpFuse& tp, unsigned epoch_val, int n, const float (&v)[NV], RowOf row_of) {
+    const int parity = epoch_val & 1;
+    for (int r = 0; r < tp.size; ++r) {
+        float* base = tp.inbox[r] + ((size_t)(parity * tp.size + tp.rank) * tp.rows_cap) * tp.n_cap + n;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int m = row_of(i);
+            if (m >= 0) base[(size_t)m * tp.n_cap] = v[i];
+        }
+    }
+    __threadfence_system();
+}
+
+// Step 2 (one thread per peer, after every pushing thread passed a barrier): signal.
+LLM_DEVICE void tp_signal(const TpFuse& tp, int tile, int peer) { red_release_sys_add(tp.flags[peer] + tile, 1u); }
+
+// Step 3 (one thread): bounded wait for all ranks of this call.  Returns false on timeout.
+LLM_DEVICE bool tp_wait(const TpFuse& tp, int tile, unsigned epoch_val) {
+    const unsigned target = (epoch_val + 1u) * (unsigned)tp.size;
+    const unsigned* f = tp.flags[tp.rank] + tile;
+    for (unsigned i = 0; i < tp.spin_limit; ++i) {
+        // wrap-safe comparison of monotone counters
+        if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
+        if (i > 64) __nanosleep(100);
+    }
+    if (tp.status) atomicExch(tp.status, (int)STATUS_TIMEOUT);
+    return false;
+}
+
+// Step 4: reduce this thread's elements from the local inbox (L1 bypassed: peers wrote the data).
+template <int NV, class RowOf>
+LLM_DEVICE void tp_reduce(const TpFuse& tp, unsigned epoch_val, int n, float (&v)[NV], RowOf row_of) {
+    const int parity = epoch_val & 1;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = 0.f;
+    for (int src = 0; src < tp.size; ++src) {
+        const float* base = tp.inbox[tp.rank] + ((size_t)(parity * tp.size + src) * tp.rows_cap) * tp.n_cap + n;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int m = row_of(i);
+            if (m >= 0) v[i] += __ldcg(base + (size_t)m * tp.n_cap);
+        }
+    }
+}
+
+}  // namespace llm

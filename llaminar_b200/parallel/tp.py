@@ -1,0 +1,114 @@
+"""Tensor-parallel context: one process per GPU, `torch.distributed` for the plumbing.
+
+Two implementations of the row-parallel "GEMM + all-reduce + residual add" step exist side by side:
+
+* the baseline issues the partial GEMM/GEMV, an NCCL (or gloo, on CPU) all-reduce and an add, which is what
+  the reference does per layer (reference: src/v2/compute_stages/stages/TPAllreduceStage.cpp ->
+  src/v2/collective/LocalTPContext.cpp:726 -> ncclAllReduce; two [tokens x d_model] all-reduces per layer,
+  src/v2/models/qwen/QwenGraphBase.cpp:2992-3010, :2119-2139);
+* the fused path (GPU, `fused=True`) lets the GEMV/GEMM epilogue push its partial tile straight into every
+  peer's inbox over NVLink (peer stores on symmetric memory), signal a per-tile flag, wait (bounded) for the
+  other ranks' tiles and add the sum to the residual stream, all inside the one kernel.
+
+Logits are vocab-parallel; `all_gather_vocab` assembles full rows for sampling.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class TPContext:
+    group: object
+    rank: int
+    size: int
+    device: torch.device
+    fused: bool = False
+    symm: object = None                 # parallel.symm.SymmetricArena when fused kernels are available
+    stats: dict = field(default_factory=lambda: {"allreduce_calls": 0, "allreduce_bytes": 0, "fused_calls": 0})
+    order_check: object = None          # parallel.collective_check.CollectiveOrderChecker in debug mode
+
+    @staticmethod
+    def create(group=None, device=None, fused: bool | None = None) -> "TPContext":
+        group = group if group is not None else dist.group.WORLD
+        rank, size = dist.get_rank(group), dist.get_world_size(group)
+        device = torch.device(device if device is not None else "cpu")
+        ctx = TPContext(group, rank, size, device)
+        want_fused = fused if fused is not None else (device.type == "cuda" and size > 1
+                                                      and os.environ.get("LLAMINAR_TP_FUSED", "1") != "0")
+        if want_fused and device.type == "cuda" and size > 1:
+            from .symm import SymmetricArena
+            try:
+                ctx.symm = SymmetricArena.create(group, device)
+                ctx.fused = True
+            except Exception as exc:        # no peer access / symmetric memory unavailable: keep the NCCL path
+                if fused:
+                    raise
+                ctx.fused = False
+                ctx.stats["fused_unavailable"] = str(exc)
+        return ctx
+
+    # -- collectives (baseline) -------------------------------------------------------------------
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return x
+        if self.order_check is not None:
+            self.order_check.record("all_reduce", x)
+        dist.all_reduce(x, group=self.group)
+        self.stats["allreduce_calls"] += 1
+        self.stats["allreduce_bytes"] += x.numel() * x.element_size()
+        return x
+
+    def all_gather_vocab(self, logits: torch.Tensor, vocab: int) -> torch.Tensor:
+        """[rows, vocab_local] shards (rank order, last shard may be short) -> [rows, vocab]."""
+        if self.size == 1:
+            return logits
+        if self.order_check is not None:
+            self.order_check.record("all_gather_vocab", logits)
+        rows = logits.shape[0]
+        from .tp_plan import VOCAB_UNIT, _split
+        n_units = (vocab + VOCAB_UNIT - 1) // VOCAB_UNIT
+        widths = []
+        for r in range(self.size):
+            u0, u1 = _split(n_units, self.size, r)
+            widths.append(min(u1 * VOCAB_UNIT, vocab) - u0 * VOCAB_UNIT)
+        wmax = max(widths)
+        send = logits
+        if logits.shape[1] != wmax:
+            send = torch.zeros(rows, wmax, dtype=logits.dtype, device=logits.device)
+            send[:, :logits.shape[1]] = logits
+        flat = torch.empty(self.size * rows, wmax, dtype=logits.dtype, device=logits.device)
+        dist.all_gather_into_tensor(flat, send.contiguous(), group=self.group)
+        out = flat.view(self.size, rows, wmax)
+        if all(w == wmax for w in widths):
+            return out.permute(1, 0, 2).reshape(rows, self.size * wmax)
+        return torch.cat([out[r, :, :w] for r, w in enumerate(widths)], dim=1)
+
+    def broadcast_object(self, obj, src: int = 0):
+        box = [obj]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, src) if self.group is not dist.group.WORLD else src,
+                                   group=self.group)
+        return box[0]
+
+    def barrier(self) -> None:
+        if self.size > 1:
+            dist.barrier(group=self.group)
+
+    # -- row-parallel linear + all-reduce + residual ---------------------------------------------------
+    def row_parallel_resid(self, lin, x: torch.Tensor, h: torch.Tensor, model) -> None:
+        """h += sum over ranks of (x @ W_shard^T)."""
+        from .. import ops
+        T = x.shape[0]
+        small = T <= ops.GEMV_MAX_ROWS
+        if self.fused and self.symm is not None and self.symm.supports(lin, T):
+            self.symm.fused_row_parallel(lin, x, h, model, small)
+            self.stats["fused_calls"] += 1
+            return
+        part = model.ws_partial[:T]
+        lin(x, part, scratch=model.scratch, xn=None if small else x)
+        self.all_reduce(part)
+        h += part

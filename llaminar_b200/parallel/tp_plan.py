@@ -63,8 +63,8 @@ class TPPlan:
             errs.append(f"d_ff={cfg.d_ff} has fewer than tp={tp} blocks of {FF_UNIT} columns")
         if cfg.is_moe and cfg.n_experts < tp:
             errs.append(f"n_experts={cfg.n_experts} < tp={tp}")
-        if (cfg.q_dim // tp) % FF_UNIT and tp > 1:
-            errs.append(f"per-rank attention width {cfg.q_dim // tp} is not a multiple of {FF_UNIT}")
+        if (cfg.q_dim // tp) % 32 and tp > 1:
+            errs.append(f"per-rank attention width {cfg.q_dim // tp} is not a multiple of 32 (smallest quantisation block)")
         return errs
 
     @staticmethod

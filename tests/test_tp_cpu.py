@@ -1,0 +1,58 @@
+"""Tensor parallelism on CPU ranks (gloo): sharded runner + engine must reproduce the single-rank tokens."""
+import torch
+
+from llaminar_b200.models.config import SHAPES
+from llaminar_b200.parallel.tp_plan import TPPlan
+from tests.mp_utils import run_ranks
+
+
+def _tp_generate(rank, world, shape, recipe, n_new):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES[shape], recipe, seed=0)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=tp)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 40)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    return outs, tp.stats["allreduce_calls"]
+
+
+def _single(shape, recipe, n_new):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.synth import synthesize
+    w = synthesize(SHAPES[shape], recipe, seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 40)]
+    return eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+
+
+def test_tp2_dense_matches_single_rank():
+    ref = _single("tiny-qwen3", "Q8_0", 6)
+    res = run_ranks(_tp_generate, 2, "tiny-qwen3", "Q8_0", 6)
+    assert res[0][0] == ref and res[1][0] == ref
+    assert res[0][1] > 0                         # the row-parallel layers really all-reduced
+
+
+def test_tp2_moe_expert_parallel_matches_single_rank():
+    ref = _single("tiny-qwen3moe", "Q8_0", 5)
+    res = run_ranks(_tp_generate, 2, "tiny-qwen3moe", "Q8_0", 5)
+    assert res[0][0] == ref and res[1][0] == ref
+
+
+def test_tp_plan_rules():
+    c = SHAPES["qwen3-32b"]
+    plans = [TPPlan.build(c, 8, r) for r in range(8)]
+    assert [p.n_heads_local for p in plans] == [8] * 8 and [p.n_kv_local for p in plans] == [1] * 8
+    assert sum(p.ff_stop - p.ff_start for p in plans) == c.d_ff and all((p.ff_start % 256) == 0 for p in plans)
+    assert plans[-1].vocab_stop == c.vocab_size and plans[0].vocab_start == 0
+    moe = SHAPES["qwen3-30b-a3b"]
+    p = TPPlan.build(moe, 8, 5)
+    assert p.kv_replicas == 2 and p.n_kv_local == 1 and p.kv_head_start == 5 * 4 // 8      # 4 KV heads over 8 ranks
+    assert (p.expert_start, p.expert_stop) == (80, 96)
+    assert TPPlan.validate(SHAPES["qwen3-8b"], 3)        # 32 heads are not divisible by 3
+    assert not TPPlan.validate(SHAPES["qwen3-8b"], 8)
