@@ -119,7 +119,7 @@ class CudaLayer:
 
 class CudaModel:
     def __init__(self, weights: ModelWeights, device="cuda", max_tokens: int = 4096, tp=None, layer_range=None,
-                 with_head: bool = True, with_embed: bool = True):
+                 with_head: bool = True, with_embed: bool = True, with_mtp: bool = True):
         self.cfg: ModelConfig = weights.config
         self.device = torch.device(device)
         self.tp = tp
@@ -151,7 +151,9 @@ class CudaModel:
             self.vocab_local = v1 - v0
         self.layers = [self._build_layer(weights, i) for i in self.layer_ids]
         self.mtp_layers = []
-        for j in range(c.nextn_layers):
+        self.mtp_kv_base = len(self.layer_ids)          # the NextN layers' K/V follow this stage's own layers in the cache
+        self.n_kv_layers = len(self.layer_ids) + (c.nextn_layers if with_mtp else 0)
+        for j in range(c.nextn_layers if with_mtp else 0):
             i = c.n_layers + j
             lay = self._build_layer(weights, i)
             p = f"blk.{i}.nextn."
@@ -374,7 +376,7 @@ class CudaModel:
         L.eh_proj(cat, x0, scratch=self.scratch, xn=cat if T > ops.GEMV_MAX_ROWS else None)
         h = self.ws_h[:T]
         h.copy_(x0)
-        self._layer(L, fb, kv.layers[c.n_layers + depth], T)
+        self._layer(L, fb, kv.layers[self.mtp_kv_base + depth], T)
         rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())
         logits = self._final_logits(rows, logits_out, L.shared_head_norm)
         return logits, h

@@ -40,6 +40,7 @@ class Request:
     hidden: torch.Tensor | None = None                   # last trunk hidden row (MTP input)
     draft: list[int] = field(default_factory=list)
     step_count: int = 0
+    terminal: object = None                               # prefix-cache terminal state: the forward pass is skipped
 
     @property
     def all_tokens(self) -> list[int]:
@@ -82,7 +83,7 @@ class LLMEngine:
             from .torch_model import TorchPagedModel
             self.model = TorchPagedModel(weights, self.device, tp=tp)
         self.max_pages_per_seq = (max_context + PAGE_SIZE - 1) // PAGE_SIZE + 1
-        n_kv_layers = c.n_layers + c.nextn_layers
+        n_kv_layers = getattr(self.model, "n_kv_layers", c.n_layers + c.nextn_layers)
         if kv_pages is None:
             need = max_batch * self.max_pages_per_seq + 64
             if self.is_cuda:
@@ -228,6 +229,17 @@ class LLMEngine:
     def _admit(self, r: Request) -> None:
         hit_pages, hit_tokens = [], 0
         if self.prefix_cache is not None:
+            term = self.prefix_cache.lookup_terminal(r.prompt)
+            if term is not None:
+                try:
+                    if self.prefix_cache.restore_terminal(self, r, term):
+                        r.terminal, r.prefix_hit_tokens = term, len(r.prompt)
+                        self._ensure_pages(r, len(r.prompt) + 1)
+                        self.stats["prefix_hit_tokens"] += len(r.prompt)
+                        return
+                except OutOfPages:
+                    self.kv.free_sequence(r.kv)
+                    r.kv = SequenceKV()
             hit_pages, hit_tokens = self.prefix_cache.lookup(r.prompt)
         if hit_tokens >= len(r.prompt):               # keep at least one token to run for the logits
             drop = (hit_tokens - len(r.prompt)) // PAGE_SIZE + 1
@@ -259,6 +271,8 @@ class LLMEngine:
         if r in self.running:
             self.running.remove(r)
         self.kv.free_sequence(r.kv)
+        if self.prefix_cache is not None:
+            self.prefix_cache.trim()                  # pages the request pinned can now leave the device tier
         if self.mtp is not None:
             self.mtp.release(r)
 
@@ -324,7 +338,7 @@ class LLMEngine:
 
     def _gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         """Vocab-parallel logits shards -> full rows (a no-op without tensor parallelism)."""
-        if self.tp is None or self.tp.size == 1:
+        if self.tp is None or self.tp.size == 1 or getattr(self.model, "returns_full_vocab", False):
             return logits
         return self.tp.all_gather_vocab(logits, self.cfg.vocab_size)
 
@@ -336,8 +350,11 @@ class LLMEngine:
         pending = {r.rid: r.prefix_hit_tokens for r in batch}
         final_logits: dict[int, torch.Tensor] = {}
         final_hidden: dict[int, torch.Tensor] = {}
+        for r in batch:
+            if r.terminal is not None:            # exact repeat of a cached prompt: logits and hidden row come from the cache
+                final_logits[r.rid], final_hidden[r.rid] = r.terminal.logits, r.terminal.hidden
         while any(pending[r.rid] < len(r.prompt) for r in batch):
-            toks, pos, sid, cu, ctx, rows_for = [], [], [], [0], [], []
+            toks, pos, sid, cu, ctx, rows_for, chunks = [], [], [], [0], [], [], []
             budget = self.max_prefill_tokens
             btab_rows = []
             for r in batch:
@@ -354,6 +371,7 @@ class LLMEngine:
                 ctx.append(done)
                 btab_rows.append(r.kv.pages)
                 pending[r.rid] = done + n
+                chunks.append((r, done, n))
                 rows_for.append((r, cu[-1] - 1 if done + n == len(r.prompt) else None))
             P = max(len(p) for p in btab_rows)
             bt = torch.zeros(len(btab_rows), P, dtype=torch.int32)
@@ -365,11 +383,14 @@ class LLMEngine:
                               ctx_lens=it(ctx), max_q_len=max(cu[i + 1] - cu[i] for i in range(len(ctx))),
                               logit_rows=it(logit_rows) if logit_rows else None)
             logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
+            if self.mtp is not None:
+                keep = {r.rid: h[row].clone() for r, row in rows_for if row is not None}
+                self.mtp.on_prefill_chunk(self, fb, h, chunks)
             j = 0
             for r, row in rows_for:
                 if row is not None:
                     final_logits[r.rid] = logits[j]
-                    final_hidden[r.rid] = h[row].clone()
+                    final_hidden[r.rid] = keep[r.rid] if self.mtp is not None else h[row].clone()
                     j += 1
             self.stats["prefill_tokens"] += len(toks)
         outs = []
@@ -382,6 +403,10 @@ class LLMEngine:
             self.running.append(r)
             if self.prefix_cache is not None:
                 self.prefix_cache.insert(self, r)
+                if r.terminal is None:
+                    self.prefix_cache.store_terminal(self, r, final_logits[r.rid], final_hidden[r.rid])
+            if self.mtp is not None:
+                self.mtp.on_prefill_done(self, r, t, final_hidden[r.rid])
             outs.append(self._emit(r, [t]))
         if self.is_cuda:
             torch.cuda.synchronize(dev)
@@ -502,8 +527,7 @@ class LLMEngine:
                           block_table=d[v["bt"]].view(bucket, P), seq_lens=d[v["len"]], rows_per_seq=1,
                           n_splits=self._splits_for(bucket))
         logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
-        if self.tp is not None and self.tp.size > 1:
-            logits = self.tp.all_gather_vocab(logits, self.cfg.vocab_size)
+        logits = self._gather_vocab(logits)
         if greedy:
             ops.argmax(logits, self._tok_dev[:bucket])
         else:

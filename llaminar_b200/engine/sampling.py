@@ -114,3 +114,23 @@ def sample_row(logits: torch.Tensor, p: SamplingParams, gen: torch.Generator | N
         probs = probs / probs.sum()
     choice = torch.multinomial(probs.cpu(), 1, generator=gen)
     return int(idx[choice])
+
+
+def filtered_probs(logits: torch.Tensor, p: SamplingParams) -> torch.Tensor:
+    """The distribution `sample_row` draws from, as a dense [vocab] vector (speculative-sampling verification)."""
+    out = torch.zeros(logits.numel(), dtype=torch.float32, device=logits.device)
+    if p.is_greedy:
+        out[int(torch.argmax(logits))] = 1.0
+        return out
+    x = logits.float() / max(p.temperature, 1e-6)
+    k = p.top_k if 0 < p.top_k < x.numel() else min(x.numel(), 1024)
+    vals, idx = torch.topk(x, k)
+    probs = torch.softmax(vals, dim=-1)
+    if p.top_p < 1.0:
+        cum = torch.cumsum(probs, dim=-1)
+        keep = (cum - probs) < p.top_p
+        keep[0] = True
+        probs = torch.where(keep, probs, torch.zeros_like(probs))
+        probs = probs / probs.sum()
+    out[idx] = probs
+    return out

@@ -22,7 +22,7 @@ from .kv_cache import PAGE_SIZE, PagedKVCache
 
 class TorchPagedModel:
     def __init__(self, weights: ModelWeights, device="cpu", max_tokens: int = 4096, tp=None, layer_range=None,
-                 with_head: bool = True, with_embed: bool = True):
+                 with_head: bool = True, with_embed: bool = True, with_mtp: bool = True):
         self.cfg: ModelConfig = weights.config
         self.device = torch.device(device)
         self.tp = tp
@@ -66,7 +66,9 @@ class TorchPagedModel:
 
         self.layers = [layer(i) for i in self.layer_ids]
         self.mtp_layers = []
-        for j in range(c.nextn_layers):
+        self.mtp_kv_base = len(self.layer_ids)          # the NextN layers' K/V follow this stage's own layers in the cache
+        self.n_kv_layers = len(self.layer_ids) + (c.nextn_layers if with_mtp else 0)
+        for j in range(c.nextn_layers if with_mtp else 0):
             i = c.n_layers + j
             L = layer(i)
             p = f"blk.{i}.nextn."
@@ -165,6 +167,6 @@ class TorchPagedModel:
         e = rmsnorm(self.embed[fb.tokens.long()].float(), L["enorm"], c.rms_eps)
         hn = rmsnorm(hidden.float(), L["hnorm"], c.rms_eps)
         x = torch.cat([e, hn], dim=-1) @ L["eh_proj"].T
-        h = self._layer(L, x, fb, kv.layers[c.n_layers + depth])
+        h = self._layer(L, x, fb, kv.layers[self.mtp_kv_base + depth])
         rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())
         return self._logits(rows, L["shared_head_norm"], logits_out), h

@@ -1,0 +1,85 @@
+"""Command replication for multi-process serving: rank 0 owns the HTTP front end and the scheduler decisions,
+every other rank mirrors the engine calls so that all ranks issue identical kernels and collectives.
+
+The reference does the same with an `MPI_Bcast` of a command tag + payload and a worker loop on the non-root
+ranks (reference: src/v2/execution/runner/OrchestrationRunner.cpp:13352-13485, src/v2/app/modes/ServerMode.cpp:89-101).
+Here the control channel is a gloo broadcast of a small Python object; the data plane stays on NCCL / NVLink.
+"""
+from __future__ import annotations
+
+import torch.distributed as dist
+
+ADD, STEP, ABORT, FORCE, CLEAR, SHUTDOWN = "add", "step", "abort", "force", "clear", "shutdown"
+
+
+class ControlChannel:
+    def __init__(self, world_group=None, timeout_s: float = 1800.0):
+        import datetime
+        # a CPU (gloo) group over the same ranks carries the commands
+        self.group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+        self.rank = dist.get_rank()
+
+    def bcast(self, obj=None):
+        box = [obj]
+        dist.broadcast_object_list(box, src=0, group=self.group)
+        return box[0]
+
+
+class ReplicatedEngine:
+    """Rank-0 proxy: forwards each call to the local engine after broadcasting it to the workers."""
+
+    def __init__(self, engine, channel: ControlChannel):
+        self._e, self._ch = engine, channel
+
+    def __getattr__(self, name):
+        return getattr(self._e, name)
+
+    def add_request(self, prompt, params):
+        self._ch.bcast((ADD, list(prompt), params))
+        return self._e.add_request(prompt, params)
+
+    def step(self):
+        self._ch.bcast((STEP,))
+        return self._e.step()
+
+    def abort(self, rid):
+        self._ch.bcast((ABORT, rid))
+        return self._e.abort(rid)
+
+    def force_token(self, rid, token):
+        self._ch.bcast((FORCE, rid, token))
+        return self._e.force_token(rid, token)
+
+    def clear_cache(self):
+        self._ch.bcast((CLEAR,))
+        return self._e.clear_cache()
+
+    def shutdown_workers(self):
+        self._ch.bcast((SHUTDOWN,))
+
+
+def worker_loop(engine, channel: ControlChannel) -> None:
+    """Non-root ranks: replay the commands of rank 0 until told to stop."""
+    while True:
+        cmd = channel.bcast()
+        op = cmd[0]
+        if op == SHUTDOWN:
+            return
+        try:
+            if op == ADD:
+                engine.add_request(cmd[1], cmd[2])
+            elif op == STEP:
+                engine.step()
+                for rid in [r for r, q in engine.requests.items() if q.state == "finished"]:
+                    engine.requests.pop(rid, None)
+            elif op == ABORT:
+                engine.abort(cmd[1])
+                engine.requests.pop(cmd[1], None)
+            elif op == FORCE:
+                engine.force_token(cmd[1], cmd[2])
+            elif op == CLEAR:
+                engine.clear_cache()
+        except Exception:
+            # rank 0 hits the same error in the same call and fails the affected requests; stay in lock step
+            import traceback
+            traceback.print_exc()

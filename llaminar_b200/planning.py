@@ -1,0 +1,122 @@
+"""Placement and memory planning: which rank holds what, and whether it fits.
+
+A deterministic function of (model config, layout, limits), so `plan` / `--dry-run` / `--explain-placement`
+need no devices (reference: src/v2/execution/mpi_orchestration/ExecutionPlanBuilder.cpp, src/v2/planning/*.cpp,
+`validateMemoryPlan` src/v2/execution/runner/OrchestrationRunner.cpp:12310).
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field
+
+from .gguf.constants import BLOCK_GEOMETRY, GGMLType
+from .models.config import RECIPES, ModelConfig, QuantRecipe
+from .parallel.tp_plan import TPPlan
+
+B200_HBM_BYTES = 180 * 10 ** 9
+
+
+def _bytes(qt: GGMLType, n: int) -> float:
+    e, b = BLOCK_GEOMETRY[qt]
+    return n / e * b
+
+
+@dataclass
+class RankPlan:
+    rank: int
+    device: str
+    stage: int
+    tp_rank: int
+    first_layer: int
+    last_layer: int
+    has_embedding: bool
+    has_head: bool
+    tp: dict
+    weight_bytes: int = 0
+    kv_bytes: int = 0
+    activation_bytes: int = 0
+    workspace_bytes: int = 0
+
+    @property
+    def total_bytes(self) -> int:
+        return self.weight_bytes + self.kv_bytes + self.activation_bytes + self.workspace_bytes
+
+
+@dataclass
+class ExecutionPlan:
+    model: str
+    layout: dict
+    ranks: list[RankPlan] = field(default_factory=list)
+    errors: list[str] = field(default_factory=list)
+
+    def to_dict(self) -> dict:
+        return {"model": self.model, "pp": self.layout["pp"], "tp": self.layout["tp"], "world": self.layout["world"],
+                "ranks": [dict(asdict(r), total_bytes=r.total_bytes) for r in self.ranks], "errors": self.errors}
+
+    def table(self) -> str:
+        rows = [f"{'rank':>4} {'device':>8} {'stage':>5} {'layers':>9} {'weights':>10} {'kv':>10} {'act+ws':>10} {'total':>10}"]
+        gb = lambda x: f"{x / 1e9:8.2f}GB"
+        for r in self.ranks:
+            rows.append(f"{r.rank:>4} {r.device:>8} {r.stage:>5} {r.first_layer:>4}-{r.last_layer:<4} {gb(r.weight_bytes)} "
+                        f"{gb(r.kv_bytes)} {gb(r.activation_bytes + r.workspace_bytes)} {gb(r.total_bytes)}")
+        return "\n".join(rows)
+
+
+def layer_weight_bytes(cfg: ModelConfig, recipe: QuantRecipe, layer: int, tp: TPPlan) -> float:
+    d, D = cfg.d_model, cfg.head_dim
+    t = lambda name: recipe.for_tensor(f"blk.{layer}.{name}.weight", layer, cfg.n_layers)
+    tot = _bytes(t("attn_q"), tp.n_heads_local * D * d) + 2 * _bytes(t("attn_k"), tp.n_kv_local * D * d)
+    tot += _bytes(t("attn_output"), d * tp.n_heads_local * D)
+    if cfg.is_moe:
+        n_e = tp.expert_stop - tp.expert_start
+        tot += n_e * (2 * _bytes(t("ffn_gate_exps"), cfg.expert_ff * d) + _bytes(t("ffn_down_exps"), cfg.expert_ff * d))
+        tot += 2 * cfg.n_experts * d
+    else:
+        ff = tp.ff_stop - tp.ff_start
+        tot += 2 * _bytes(t("ffn_gate"), ff * d) + _bytes(t("ffn_down"), ff * d)
+    return tot + 4 * (2 * d + 2 * D)
+
+
+def build_plan(cfg: ModelConfig, layout: dict, recipe: QuantRecipe | str = "Q4_K_M", ctx_size: int = 4096,
+               batch_size: int = 1, max_prefill_tokens: int = 8192, hbm_bytes: int = B200_HBM_BYTES) -> ExecutionPlan:
+    if isinstance(recipe, str):
+        recipe = RECIPES[recipe]
+    plan = ExecutionPlan(cfg.name, layout)
+    tp_n = layout["tp"]
+    errs = TPPlan.validate(cfg, tp_n)
+    if errs:
+        plan.errors.extend(errs)
+        return plan
+    stages = layout["stages"]
+    n_stages = len(stages)
+    rank = 0
+    for si, (dom, devices, first, last) in enumerate(stages):
+        if last < 0:
+            # even split of the layers when the stage gives no explicit range
+            first = cfg.n_layers * si // n_stages
+            last = cfg.n_layers * (si + 1) // n_stages - 1
+        if last >= cfg.n_layers:
+            plan.errors.append(f"stage {si}: layer {last} beyond the model's {cfg.n_layers} layers")
+            last = cfg.n_layers - 1
+        for ti, dev in enumerate(devices):
+            tp = TPPlan.build(cfg, tp_n, ti)
+            rp = RankPlan(rank, dev, si, ti, first, last, si == 0, si == n_stages - 1, asdict(tp))
+            w = sum(layer_weight_bytes(cfg, recipe, l, tp) for l in range(first, last + 1))
+            if rp.has_embedding:
+                w += _bytes(recipe.for_tensor("token_embd.weight"), cfg.vocab_size * cfg.d_model)
+            if rp.has_head:
+                w += _bytes(recipe.for_tensor("output.weight"), (tp.vocab_stop - tp.vocab_start) * cfg.d_model)
+            rp.weight_bytes = int(w)
+            pages = batch_size * ((ctx_size + 63) // 64 + 1) + 64
+            rp.kv_bytes = int(pages * (last - first + 1) * 2 * tp.n_kv_local * 64 * cfg.head_dim * 2)
+            T = max(max_prefill_tokens, batch_size * 4)
+            ff = (tp.ff_stop - tp.ff_start) if not cfg.is_moe else cfg.expert_ff
+            rp.activation_bytes = int(T * (cfg.d_model * (4 + 2) + (tp.n_heads_local + 2 * tp.n_kv_local) * cfg.head_dim * 2
+                                           + 2 * tp.n_heads_local * cfg.head_dim * 2 + ff * 2))
+            rp.workspace_bytes = int(256 * 65536 * 4 + (1 << 22) * 4 + batch_size * 4 * (tp.vocab_stop - tp.vocab_start) * 4)
+            if rp.total_bytes > hbm_bytes * 0.95:
+                plan.errors.append(f"rank {rank} ({dev}): needs {rp.total_bytes / 1e9:.1f} GB, device has {hbm_bytes / 1e9:.0f} GB")
+            plan.ranks.append(rp)
+            rank += 1
+    if last != cfg.n_layers - 1 and not plan.errors:
+        plan.errors.append(f"pipeline stages end at layer {last}, model has {cfg.n_layers} layers")
+    return plan

@@ -1,0 +1,283 @@
+"""OpenAI-compatible `/v1/chat/completions` request handling: validation, sampling merge, chat-template
+encoding, context-window check, generation loop with stop tokens, reasoning / content split, thinking
+budget with forced stop-thinking injection, tool-call extraction, `usage` accounting, SSE chunks.
+
+Behaviour follows the reference handler (reference: src/v2/app/modes/ChatCompletionHandler.cpp:554 parse,
+:753 setup, :867 non-streaming, :1165 streaming, :1137-1145 response schema; error objects are
+`{"error": {"message", "type"}}` with 400 for invalid requests / context overflow and 500 for runtime failures).
+"""
+from __future__ import annotations
+
+import json
+import queue
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Iterator
+
+from ..engine.sampling import SamplingParams, merge_with_model_defaults
+from ..tokenizer.bpe import StreamDecoder
+from ..tokenizer.chat_template import ThinkSplitter
+from .tool_parser import parse_tool_calls
+
+SYSTEM_FINGERPRINT = "llaminar-b200"
+STOP_THINKING_TEXT = "\n\nConsidering the limited time by the user, I have to give the solution based on the thinking directly now.\n</think>\n\n"
+_SAMPLING_FIELDS = ("temperature", "top_p", "top_k", "seed", "presence_penalty", "frequency_penalty",
+                    "dry_multiplier", "dry_base", "dry_allowed_length")
+
+
+class RequestError(Exception):
+    def __init__(self, message: str, status: int = 400, err_type: str = "invalid_request_error", param: str | None = None):
+        super().__init__(message)
+        self.status, self.err_type, self.param = status, err_type, param
+
+    def body(self) -> dict:
+        e = {"message": str(self), "type": self.err_type}
+        if self.param:
+            e["param"] = self.param
+        return {"error": e}
+
+
+@dataclass
+class ChatRequest:
+    messages: list[dict]
+    max_tokens: int = -1
+    stream: bool = False
+    enable_thinking: bool = True
+    model: str = ""
+    sampling: dict = field(default_factory=dict)
+    thinking_budget_tokens: int = -1
+    tools: list | None = None
+    tool_choice: object = None
+    parallel_tool_calls: bool = True
+
+
+def parse_request(body_bytes: bytes) -> ChatRequest:
+    try:
+        body = json.loads(body_bytes)
+    except (json.JSONDecodeError, UnicodeDecodeError) as exc:
+        raise RequestError(f"Invalid JSON: {exc}") from exc
+    if not isinstance(body, dict):
+        raise RequestError("request body must be a JSON object")
+    msgs = body.get("messages")
+    if not isinstance(msgs, list) or not msgs:
+        raise RequestError('"messages" field is required and must be a non-empty array', param="messages")
+    for m in msgs:
+        if not isinstance(m, dict) or "role" not in m:
+            raise RequestError('Each message must have a "role" field')
+        role = m["role"]
+        if role == "assistant" and "tool_calls" in m:
+            continue
+        if role == "tool":
+            if "tool_call_id" not in m:
+                raise RequestError('Tool messages must have a "tool_call_id" field')
+            continue
+        if "content" not in m:
+            raise RequestError('Each message must have "role" and "content" fields')
+    req = ChatRequest(messages=[])
+    try:
+        if "max_tokens" in body:
+            req.max_tokens = int(body["max_tokens"])
+        elif "max_completion_tokens" in body:
+            req.max_tokens = int(body["max_completion_tokens"])
+        req.stream = bool(body.get("stream", False))
+        req.enable_thinking = bool(body.get("enable_thinking", True))
+        req.model = str(body.get("model", ""))
+        for k in _SAMPLING_FIELDS:
+            if k in body and body[k] is not None:
+                req.sampling[k] = int(body[k]) if k in ("top_k", "seed", "dry_allowed_length") else float(body[k])
+        if "thinking_budget_tokens" in body:
+            req.thinking_budget_tokens = int(body["thinking_budget_tokens"])
+    except (TypeError, ValueError) as exc:
+        raise RequestError(f"bad parameter value: {exc}") from exc
+    if isinstance(body.get("tools"), list):
+        req.tools = body["tools"]
+    req.tool_choice = body.get("tool_choice")
+    req.parallel_tool_calls = bool(body.get("parallel_tool_calls", True))
+    for m in msgs:
+        cm = {"role": str(m["role"]), "content": "" if m.get("content") is None else m.get("content")}
+        if isinstance(cm["content"], list):        # OpenAI content parts: keep the text parts
+            cm["content"] = "".join(p.get("text", "") for p in cm["content"] if isinstance(p, dict))
+        if isinstance(m.get("tool_calls"), list):
+            cm["tool_calls"] = m["tool_calls"]
+        for k in ("tool_call_id", "name"):
+            if k in m:
+                cm[k] = m[k]
+        req.messages.append(cm)
+    return req
+
+
+class ChatCompletionHandler:
+    def __init__(self, loop, tokenizer, template, arch: str, max_context: int, model_name: str = "llaminar",
+                 cli_sampling: SamplingParams | None = None, eos_ids: tuple[int, ...] = ()):
+        self.loop, self.tok, self.template = loop, tokenizer, template
+        self.arch, self.max_context, self.model_name = arch, max_context, model_name
+        self.cli_sampling = cli_sampling
+        self.eos_ids = tuple(eos_ids)
+
+    # -- shared setup ---------------------------------------------------------------------------------------
+    def _setup(self, req: ChatRequest):
+        text = self.template.render(req.messages, tools=req.tools, add_generation_prompt=True,
+                                    enable_thinking=req.enable_thinking)
+        ids = self.tok.encode(text, add_special=True)
+        if len(ids) + 1 >= self.max_context:
+            raise RequestError(f"prompt of {len(ids)} tokens does not fit the context window of {self.max_context}",
+                               err_type="context_length_exceeded")
+        budget = self.max_context - len(ids) - 1
+        max_tokens = budget if req.max_tokens < 0 else min(req.max_tokens, budget)
+        if max_tokens < 1:
+            raise RequestError("max_tokens must be at least 1")
+        sp = merge_with_model_defaults(self.arch, req.sampling, self.cli_sampling)
+        sp.max_tokens = max_tokens
+        sp.stop_token_ids = tuple(self.eos_ids)
+        starts_in_think = text.rstrip().endswith("<think>")
+        return ids, sp, starts_in_think
+
+    def _generate(self, req: ChatRequest) -> Iterator[tuple[str, object]]:
+        """Yields ("delta", (reasoning, content)) ... then ("end", info dict)."""
+        ids, sp, starts_in_think = self._setup(req)
+        ticket = self.loop.submit(ids, sp)
+        dec = StreamDecoder(self.tok, skip_special=True)
+        splitter = ThinkSplitter(starts_in_think) if self.template.expects_thinking else None
+        budget_on = req.thinking_budget_tokens >= 0 and req.enable_thinking and splitter is not None
+        stop_ids = self.tok.encode(STOP_THINKING_TEXT, parse_special=True) if budget_on else []
+        injected = False
+        thinking_tokens = 0
+        n_completion = 0
+        finish = "stop"
+        if budget_on and req.thinking_budget_tokens == 0 and stop_ids:
+            for t in stop_ids:
+                self.loop.force_token(ticket, t)
+            injected = True
+        try:
+            while True:
+                try:
+                    ev = ticket.events.get(timeout=600)
+                except queue.Empty:
+                    raise RequestError("generation timed out", 500, "server_error")
+                if ev[0] == "error":
+                    raise RequestError(ev[1], ev[2] if len(ev) > 2 else 500,
+                                       "invalid_request_error" if (len(ev) > 2 and ev[2] == 400) else "server_error")
+                if ev[0] == "done":
+                    finish = ev[1] or "stop"
+                    break
+                for tid in ev[1]:
+                    n_completion += 1
+                    if tid in self.eos_ids:
+                        continue
+                    piece = dec.push(tid)
+                    if splitter is None:
+                        if piece:
+                            yield "delta", ("", piece)
+                        continue
+                    was_thinking = splitter.in_think
+                    r, c = splitter.push(piece)
+                    if was_thinking:
+                        thinking_tokens += 1
+                    if r or c:
+                        yield "delta", (r, c)
+                    if budget_on and not injected and splitter.in_think and thinking_tokens >= req.thinking_budget_tokens:
+                        for t in stop_ids:
+                            self.loop.force_token(ticket, t)
+                        injected = True
+            tail = dec.flush()
+            if tail:
+                r, c = splitter.push(tail) if splitter else ("", tail)
+                if r or c:
+                    yield "delta", (r, c)
+            if splitter:
+                r, c = splitter.flush()
+                if r or c:
+                    yield "delta", (r, c)
+        except GeneratorExit:
+            self.loop.cancel(ticket)
+            raise
+        yield "end", {"prompt_tokens": len(ids), "completion_tokens": n_completion, "finish_reason": finish,
+                      "prefix_hit_tokens": ticket.prefix_hit_tokens}
+
+    def _usage(self, info: dict) -> dict:
+        p, c = info["prompt_tokens"], info["completion_tokens"]
+        u = {"prompt_tokens": p, "completion_tokens": c, "total_tokens": p + c, "context_window": self.max_context,
+             "context_used": p + c}
+        if info.get("prefix_hit_tokens"):
+            u["prompt_tokens_details"] = {"cached_tokens": info["prefix_hit_tokens"]}
+        return u
+
+    # -- non-streaming --------------------------------------------------------------------------------------
+    def handle(self, req: ChatRequest) -> dict:
+        reasoning, content, info = [], [], None
+        for kind, payload in self._generate(req):
+            if kind == "delta":
+                reasoning.append(payload[0])
+                content.append(payload[1])
+            else:
+                info = payload
+        text, think = "".join(content), "".join(reasoning)
+        finish = "length" if info["finish_reason"] == "length" else "stop"
+        message: dict = {"role": "assistant"}
+        if req.tools:
+            parsed = parse_tool_calls(text)
+            if parsed.has_tool_calls:
+                calls = parsed.tool_calls if req.parallel_tool_calls else parsed.tool_calls[:1]
+                message["content"] = parsed.content or None
+                message["tool_calls"] = calls
+                finish = "tool_calls"
+            else:
+                message["content"] = text
+        else:
+            message["content"] = text
+        if think:
+            message["reasoning_content"] = think
+        return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
+                "model": req.model or self.model_name, "system_fingerprint": SYSTEM_FINGERPRINT,
+                "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": self._usage(info)}
+
+    # -- streaming (server-sent events) -------------------------------------------------------------------------
+    def stream(self, req: ChatRequest) -> Iterator[bytes]:
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        model = req.model or self.model_name
+
+        def chunk(delta: dict, finish=None, usage=None) -> bytes:
+            obj = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
+                   "system_fingerprint": SYSTEM_FINGERPRINT,
+                   "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+            if usage is not None:
+                obj["usage"] = usage
+            return b"data: " + json.dumps(obj, ensure_ascii=False).encode() + b"\n\n"
+
+        gen = self._generate(req)          # raises RequestError before the first byte if setup fails
+        first = next(gen)
+        yield chunk({"role": "assistant", "content": ""})
+        content_all = []
+        info = None
+        for kind, payload in _chain(first, gen):
+            if kind == "delta":
+                r, c = payload
+                if r:
+                    yield chunk({"reasoning_content": r})
+                if c:
+                    content_all.append(c)
+                    if not req.tools:
+                        yield chunk({"content": c})
+            else:
+                info = payload
+        finish = "length" if info["finish_reason"] == "length" else "stop"
+        if req.tools:
+            parsed = parse_tool_calls("".join(content_all))
+            if parsed.has_tool_calls:
+                if parsed.content:
+                    yield chunk({"content": parsed.content})
+                calls = parsed.tool_calls if req.parallel_tool_calls else parsed.tool_calls[:1]
+                yield chunk({"tool_calls": [dict(c, index=i) for i, c in enumerate(calls)]})
+                finish = "tool_calls"
+            else:
+                yield chunk({"content": "".join(content_all)})
+        yield chunk({}, finish=finish, usage=self._usage(info))
+        yield b"data: [DONE]\n\n"
+
+
+def _chain(first, rest):
+    yield first
+    yield from rest
+

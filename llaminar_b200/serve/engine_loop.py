@@ -1,0 +1,118 @@
+"""Background thread that owns the engine: requests come in through a queue, tokens go out through per-request
+queues.  Several HTTP handlers can be in flight at once (up to `--batch-size` lanes decode together); the
+reference serialises requests behind one inference mutex (reference: src/v2/app/modes/ServerMode.cpp:126-160).
+A failure inside a step fails the requests that were running, is reported to their handlers, and leaves the
+loop alive for the next request.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import traceback
+from dataclasses import dataclass, field
+
+
+@dataclass
+class Ticket:
+    prompt: list[int]
+    params: object
+    events: "queue.Queue" = field(default_factory=queue.Queue)     # ("tokens", [ids]) / ("done", reason) / ("error", msg)
+    rid: int | None = None
+    cancelled: bool = False
+    prefix_hit_tokens: int = 0
+
+
+class EngineLoop:
+    def __init__(self, engine, on_step=None):
+        self.engine = engine
+        self._in: "queue.Queue" = queue.Queue()
+        self._tickets: dict[int, Ticket] = {}
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self.on_step = on_step
+        self.errors = 0
+        self._thread = threading.Thread(target=self._run, name="engine-loop", daemon=True)
+        self._thread.start()
+
+    # -- called from handler threads -----------------------------------------------------------------
+    def submit(self, prompt: list[int], params) -> Ticket:
+        t = Ticket(list(prompt), params)
+        self._in.put(("add", t))
+        self._wake.set()
+        return t
+
+    def force_token(self, ticket: Ticket, token: int) -> None:
+        self._in.put(("force", ticket, token))
+        self._wake.set()
+
+    def cancel(self, ticket: Ticket) -> None:
+        ticket.cancelled = True
+        self._in.put(("cancel", ticket))
+        self._wake.set()
+
+    def shutdown(self) -> None:
+        self._stop.set()
+        self._wake.set()
+        self._thread.join(timeout=10)
+
+    # -- engine thread ---------------------------------------------------------------------------------
+    def _drain_commands(self) -> None:
+        while True:
+            try:
+                cmd = self._in.get_nowait()
+            except queue.Empty:
+                return
+            kind, t = cmd[0], cmd[1]
+            if kind == "add":
+                try:
+                    r = self.engine.add_request(t.prompt, t.params)
+                    t.rid = r.rid
+                    self._tickets[r.rid] = t
+                except Exception as exc:                       # e.g. prompt longer than the context window
+                    t.events.put(("error", str(exc), 400))
+            elif kind == "force" and t.rid is not None:
+                self.engine.force_token(t.rid, cmd[2])
+            elif kind == "cancel" and t.rid is not None:
+                self.engine.abort(t.rid)
+                self._tickets.pop(t.rid, None)
+                self.engine.requests.pop(t.rid, None)
+
+    def _run(self) -> None:
+        eng = self.engine
+        while not self._stop.is_set():
+            self._drain_commands()
+            if not eng.has_unfinished():
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            try:
+                outs = eng.step()
+            except Exception as exc:                           # fail the running requests, keep serving
+                self.errors += 1
+                msg = f"{type(exc).__name__}: {exc}"
+                traceback.print_exc()
+                for rid, t in list(self._tickets.items()):
+                    t.events.put(("error", msg, 500))
+                    try:
+                        eng.abort(rid)
+                    except Exception:
+                        pass
+                    eng.requests.pop(rid, None)
+                self._tickets.clear()
+                eng.waiting.clear()
+                continue
+            for o in outs:
+                t = self._tickets.get(o.rid)
+                if t is None:
+                    continue
+                req = eng.requests.get(o.rid)
+                if req is not None:
+                    t.prefix_hit_tokens = req.prefix_hit_tokens
+                if o.new_tokens:
+                    t.events.put(("tokens", list(o.new_tokens)))
+                if o.finished:
+                    t.events.put(("done", o.finish_reason))
+                    self._tickets.pop(o.rid, None)
+                    eng.requests.pop(o.rid, None)
+            if self.on_step is not None:
+                self.on_step(outs)

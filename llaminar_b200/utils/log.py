@@ -1,0 +1,16 @@
+"""Rank-prefixed logging; level from LLAMINAR_LOG_LEVEL or -v (reference: src/v2/utils/Logger.h)."""
+import logging
+import os
+
+_configured = False
+
+
+def get_logger(name: str = "llaminar") -> logging.Logger:
+    global _configured
+    if not _configured:
+        level = os.environ.get("LLAMINAR_LOG_LEVEL", "INFO").upper()
+        rank = os.environ.get("RANK", "0")
+        logging.basicConfig(level=getattr(logging, level, logging.INFO),
+                            format=f"%(asctime)s [rank {rank}] %(levelname)s %(name)s: %(message)s", datefmt="%H:%M:%S")
+        _configured = True
+    return logging.getLogger(f"llaminar.{name}")

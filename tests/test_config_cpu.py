@@ -1,0 +1,121 @@
+"""Flag parsing, validation rules, the placement planner, the CLI commands and SPMD command replication."""
+import json
+import subprocess
+import sys
+
+import pytest
+
+from llaminar_b200.config.orchestration import ConfigError, parse_args
+from llaminar_b200.models.config import SHAPES
+from llaminar_b200.planning import build_plan
+from tests.mp_utils import run_ranks
+
+
+def test_defaults_and_explicit_set():
+    c = parse_args(["oneshot", "--synthetic", "tiny-qwen3", "-n", "7"])
+    assert c.command == "oneshot" and c.values["n_predict"] == 7 and "n_predict" in c.explicitly_set
+    assert c.layout()["world"] == 1 and c.layout()["pp"] == 1
+
+
+def test_yaml_config_and_cli_override(tmp_path):
+    p = tmp_path / "c.yaml"
+    p.write_text("synthetic: tiny-qwen3\nctx-size: 256\nbatch_size: 3\n")
+    c = parse_args(["serve", "--config", str(p), "-c", "128"])
+    assert c.values["ctx_size"] == 128 and c.values["batch_size"] == 3 and c.values["synthetic"] == "tiny-qwen3"
+    p.write_text("no_such_key: 1\n")
+    with pytest.raises(ConfigError):
+        parse_args(["serve", "--config", str(p)])
+
+
+def test_device_modes_are_mutually_exclusive():
+    with pytest.raises(ConfigError) as e:
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "-d", "cuda:0", "--tp-devices", "cuda:0,cuda:1"])
+    assert "mutually exclusive" in str(e.value)
+
+
+def test_pp_layout_and_rules():
+    argv = ["plan", "--synthetic", "qwen3-32b", "--define-domain", "a=cuda:0,cuda:1,cuda:2,cuda:3",
+            "--define-domain", "b=cuda:4,cuda:5,cuda:6,cuda:7", "--pp-stage", "0=a:0-31", "--pp-stage", "1=b:32-63"]
+    lay = parse_args(argv).layout()
+    assert lay["pp"] == 2 and lay["tp"] == 4 and lay["world"] == 8 and lay["stages"][1][2:] == (32, 63)
+    bad = argv[:-1] + ["1=b:40-63"]
+    with pytest.raises(ConfigError) as e:
+        parse_args(bad)
+    assert "must continue at 32" in str(e.value)
+    with pytest.raises(ConfigError):
+        parse_args(["plan", "--synthetic", "qwen3-32b", "--pp-stage", "0=a:0-31"])
+
+
+def test_unsupported_and_bad_values_are_named():
+    with pytest.raises(ConfigError) as e:
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--kv-cache-precision", "tq4"])
+    assert "quantised KV" in str(e.value)
+    with pytest.raises(ConfigError):
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--tp-devices", "rocm:0,rocm:1"])
+    with pytest.raises(ConfigError):
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--mtp-draft-tokens", "5"])
+    with pytest.raises(ConfigError):
+        parse_args(["oneshot"])
+
+
+def test_planner_memory_and_errors():
+    lay = {"pp": 2, "tp": 4, "world": 8, "stages": [("a", [f"cuda:{i}" for i in range(4)], 0, 31), ("b", [f"cuda:{i}" for i in range(4, 8)], 32, 63)]}
+    plan = build_plan(SHAPES["qwen3-32b"], lay, ctx_size=4096, batch_size=8)
+    assert not plan.errors and len(plan.ranks) == 8
+    assert all(2e9 < r.total_bytes < 30e9 for r in plan.ranks)
+    assert "stage" in plan.table()
+    lay3 = {"pp": 1, "tp": 3, "world": 3, "stages": [("d", ["cuda:0", "cuda:1", "cuda:2"], 0, -1)]}
+    assert build_plan(SHAPES["qwen3-8b"], lay3, ctx_size=4096, batch_size=1).errors
+
+
+def _cli(*args):
+    r = subprocess.run([sys.executable, "-m", "llaminar_b200", *args], capture_output=True, text=True, timeout=300)
+    return r.returncode, r.stdout, r.stderr
+
+
+def test_cli_oneshot_benchmark_plan_describe(tmp_path):
+    rc, out, err = _cli("oneshot", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0", "-d", "cpu", "-p", "hello", "-n", "5")
+    assert rc == 0, err
+    out_json = tmp_path / "b.json"
+    rc, out, err = _cli("benchmark", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0", "-d", "cpu", "--bench-runs", "1",
+                        "--bench-prompt-tokens", "64", "-n", "8", "--bench-json", str(out_json))
+    assert rc == 0, err
+    j = json.loads(out_json.read_text())
+    assert j["decode_tok_s"] > 0 and j["prefill_tok_s"] > 0 and j["ttft_ms_p50"] > 0
+    rc, out, err = _cli("plan", "--synthetic", "qwen3-8b", "--tp-devices", "cuda:0,cuda:1")
+    assert rc == 0 and "weight_bytes" in out
+    rc, out, err = _cli("describe")
+    assert rc == 0 and "cpu" in out
+    rc, out, err = _cli("oneshot", "--synthetic", "nope")
+    assert rc != 0 and "unknown shape" in (out + err)
+
+
+def _spmd_run(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.spmd import ControlChannel, ReplicatedEngine, worker_loop
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=tp)
+    ch = ControlChannel()
+    if rank != 0:
+        worker_loop(eng, ch)
+        return eng.stats["decode_tokens"]
+    drive = ReplicatedEngine(eng, ch)
+    r = drive.add_request(list(range(3, 20)), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    r2 = drive.add_request(list(range(30, 50)), SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True))
+    n = 0
+    while r.state != "finished":
+        drive.step()
+        n += 1
+        if n == 2:
+            drive.abort(r2.rid)
+    drive.shutdown_workers()
+    return eng.stats["decode_tokens"]
+
+
+def test_spmd_workers_mirror_rank0():
+    res = run_ranks(_spmd_run, 2)
+    assert res[0] == res[1] and res[0] > 0

@@ -1,0 +1,128 @@
+"""OpenAI-compatible server, chat handler, templates, tool parsing: in-process against a tiny CPU engine."""
+import http.client
+import json
+
+import pytest
+
+from llaminar_b200.engine.engine import LLMEngine
+from llaminar_b200.models.config import SHAPES
+from llaminar_b200.models.synth import synthesize
+from llaminar_b200.serve.chat_handler import ChatCompletionHandler, RequestError, parse_request
+from llaminar_b200.serve.engine_loop import EngineLoop
+from llaminar_b200.serve.server import Server
+from llaminar_b200.serve.tool_parser import parse_tool_calls
+from llaminar_b200.tokenizer.bpe import BPETokenizer
+from llaminar_b200.tokenizer.chat_template import ChatTemplate, ThinkSplitter
+
+
+@pytest.fixture(scope="module")
+def server():
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=4, max_context=512)
+    tok = BPETokenizer.from_metadata(w.metadata)
+    tpl = ChatTemplate.resolve(None, tok.chat_template)
+    loop = EngineLoop(eng)
+    chat = ChatCompletionHandler(loop, tok, tpl, "qwen3", 512, model_name="tiny", eos_ids=(tok.eos_id,) if tok.eos_id is not None else ())
+    srv = Server(chat, "127.0.0.1", 0)
+    srv.start_background()
+    yield srv
+    srv.stop()
+
+
+def _post(srv, body, path="/v1/chat/completions", raw=None):
+    c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=120)
+    data = raw if raw is not None else json.dumps(body).encode()
+    c.request("POST", path, body=data, headers={"Content-Type": "application/json"})
+    r = c.getresponse()
+    return r.status, r.read(), dict(r.getheaders())
+
+
+def test_health_and_models(server):
+    c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+    c.request("GET", "/health")
+    r = c.getresponse()
+    assert r.status == 200 and json.loads(r.read())["status"] == "ok"
+    c.request("GET", "/v1/models")
+    r = c.getresponse()
+    assert r.status == 200 and json.loads(r.read())["data"][0]["id"] == "tiny"
+    c.request("GET", "/nope")
+    r = c.getresponse()
+    assert r.status == 404
+    r.read()
+
+
+def test_completion_json_and_usage(server):
+    st, body, _ = _post(server, {"messages": [{"role": "user", "content": "hi there"}], "max_tokens": 6, "temperature": 0})
+    assert st == 200
+    j = json.loads(body)
+    assert j["object"] == "chat.completion" and j["choices"][0]["message"]["role"] == "assistant"
+    assert j["choices"][0]["finish_reason"] in ("length", "stop")
+    u = j["usage"]
+    assert u["completion_tokens"] <= 6 and u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"]
+    st2, body2, _ = _post(server, {"messages": [{"role": "user", "content": "hi there"}], "max_tokens": 6, "temperature": 0})
+    assert json.loads(body2)["choices"][0]["message"] == j["choices"][0]["message"]       # greedy is deterministic
+
+
+def test_streaming_sse(server):
+    st, body, hdr = _post(server, {"messages": [{"role": "user", "content": "stream"}], "max_tokens": 5, "temperature": 0,
+                                   "stream": True, "stream_options": {"include_usage": True}})
+    assert st == 200 and hdr["Content-Type"].startswith("text/event-stream")
+    events = [l[6:] for l in body.decode().split("\n") if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+    assert any(c["choices"] and c["choices"][0].get("finish_reason") for c in chunks)
+    assert any(c.get("usage") for c in chunks)
+
+
+def test_errors(server):
+    st, body, _ = _post(server, None, raw=b"{not json")
+    assert st == 400 and json.loads(body)["error"]["type"] == "invalid_request_error"
+    st, body, _ = _post(server, {"messages": []})
+    assert st == 400
+    st, body, _ = _post(server, {"messages": [{"role": "user", "content": "x " * 2000}]})
+    assert st == 400 and "context" in json.loads(body)["error"]["message"]
+    st, body, _ = _post(server, {"messages": [{"role": "user", "content": "x"}]}, path="/v1/other")
+    assert st == 404
+
+
+def test_parse_request_validation():
+    with pytest.raises(RequestError):
+        parse_request(b"[]")
+    with pytest.raises(RequestError):
+        parse_request(json.dumps({"messages": [{"role": "user", "content": "a"}], "temperature": "hot"}).encode())
+    r = parse_request(json.dumps({"messages": [{"role": "user", "content": [{"type": "text", "text": "a"}, {"type": "text", "text": "b"}]}],
+                                  "top_p": 0.5, "max_completion_tokens": 9}).encode())
+    assert r.messages[0]["content"] == "ab" and r.sampling["top_p"] == 0.5 and r.max_tokens == 9
+
+
+def test_think_splitter_handles_split_tags():
+    s = ThinkSplitter()
+    out = [s.push(p) for p in ["<th", "ink>plan", " more</thi", "nk>answer", " tail"]]
+    out.append(s.flush())
+    reasoning = "".join(o[0] for o in out)
+    content = "".join(o[1] for o in out)
+    assert reasoning == "plan more" and content == "answer tail"
+    s2 = ThinkSplitter(starts_in_thinking=True)
+    a = s2.push("deep</think>ok")
+    b = s2.flush()
+    assert a[0] + b[0] == "deep" and a[1] + b[1] == "ok"
+
+
+def test_tool_call_parser():
+    text = 'I will call.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>'
+    p = parse_tool_calls(text)
+    assert p.has_tool_calls and p.tool_calls[0]["function"]["name"] == "get_weather"
+    assert json.loads(p.tool_calls[0]["function"]["arguments"]) == {"city": "Paris"}
+    assert "tool_call" not in p.content
+    assert not parse_tool_calls("plain text").has_tool_calls
+    assert not parse_tool_calls("<tool_call>{broken</tool_call>").has_tool_calls
+
+
+def test_chat_template_renders_tools_and_thinking():
+    from llaminar_b200.models.synth import CHATML_TEMPLATE
+    t = ChatTemplate(CHATML_TEMPLATE)
+    s = t.render([{"role": "system", "content": "sys"}, {"role": "user", "content": "q"}])
+    assert "<|im_start|>system\nsys<|im_end|>" in s and s.rstrip().endswith("<|im_start|>assistant")
+    with pytest.raises(Exception):
+        ChatTemplate("{{ raise_exception('bad') }}").render([])
