@@ -158,7 +158,17 @@ def _spmd(engine, rank, world):
     if world == 1:
         return engine, None
     from .parallel.spmd import ControlChannel, ReplicatedEngine, worker_loop
+    from .parallel.watchdog import Heartbeat, StepWatchdog, abort_process_group
+    import torch.distributed as dist
     ch = ControlChannel()
+    # failure detection: heartbeats through the rendezvous store; a dead or failed peer aborts the communicators so
+    # that nobody stays blocked in a collective
+    def peer_failed(r, why):
+        log.error("rank %d reported dead or failed (%s); aborting the process group", r, why)
+        abort_process_group()
+    hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, on_failure=peer_failed).start()
+    engine.heartbeat = hb
+    engine.step_watchdog = StepWatchdog(heartbeat=hb)
     if rank == 0:
         return ReplicatedEngine(engine, ch), None
     return None, (lambda: worker_loop(engine, ch))

@@ -20,6 +20,8 @@ from ..models.weights import ModelWeights
 from .cuda_model import ForwardBatch
 from .kv_cache import PAGE_SIZE, OutOfPages, PagedKVCache, SequenceKV
 from .sampling import SamplingParams, apply_penalties, sample_row
+from ..utils.env import debug_env
+from ..utils.perfstats import perf_stats
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128)
 
@@ -94,7 +96,8 @@ class LLMEngine:
                 kv_pages = need
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
                                dtype=torch.bfloat16 if self.is_cuda else torch.float32)
-        self.use_graphs = use_graphs and self.is_cuda
+        self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
+        self.perf = perf_stats()
         self._graphs: dict = {}
         self.launches_per_graph: dict = {}      # kernels of this package inside each captured decode graph
         self.step_events = None                 # optional list of (start, end) CUDA events, one pair consumed per decode step
@@ -201,6 +204,16 @@ class LLMEngine:
     # -- scheduling -----------------------------------------------------------------------------------
     def step(self) -> list[StepOutput]:
         """One scheduler iteration: admit + prefill waiting requests if lanes are free, else one decode step."""
+        if not self.perf.enabled:
+            return self._step()
+        kind = "prefill" if self.waiting and len(self.running) < self.max_batch else "decode"
+        self.perf.set_phase(kind)
+        with self.perf.timer("engine", "step", device=str(self.device)), self.perf.cuda_timer("engine", "step_device", device=self.device):
+            outs = self._step()
+        self.perf.count("engine", "tokens", sum(len(o.new_tokens) for o in outs), device=str(self.device))
+        return outs
+
+    def _step(self) -> list[StepOutput]:
         self.stats["steps"] += 1
         if self.waiting and len(self.running) < self.max_batch:
             batch, budget = [], self.max_prefill_tokens
@@ -330,9 +343,9 @@ class LLMEngine:
                            torch.tensor([len(r.output)], dtype=torch.int32, device=dev), tok)
                 out.append(int(tok))
             else:
-                gen = None
-                if r.params.seed is not None:
-                    gen = torch.Generator().manual_seed(r.params.seed * 1000003 + len(r.output))
+                # never the global generator: every rank of a multi-process engine must draw the same token
+                seed = r.params.seed if r.params.seed is not None else (r.rid * 7919 + 17)
+                gen = torch.Generator().manual_seed(seed * 1000003 + len(r.output))
                 out.append(sample_row(row, r.params, gen))
         return out
 

@@ -40,7 +40,11 @@ class ReplicatedEngine:
 
     def step(self):
         self._ch.bcast((STEP,))
-        return self._e.step()
+        wd = getattr(self._e, "step_watchdog", None)
+        if wd is None:
+            return self._e.step()
+        with wd("engine step"):
+            return self._e.step()
 
     def abort(self, rid):
         self._ch.bcast((ABORT, rid))
@@ -69,7 +73,12 @@ def worker_loop(engine, channel: ControlChannel) -> None:
             if op == ADD:
                 engine.add_request(cmd[1], cmd[2])
             elif op == STEP:
-                engine.step()
+                wd = getattr(engine, "step_watchdog", None)
+                if wd is None:
+                    engine.step()
+                else:
+                    with wd("engine step"):
+                        engine.step()
                 for rid in [r for r, q in engine.requests.items() if q.state == "finished"]:
                     engine.requests.pop(rid, None)
             elif op == ABORT:

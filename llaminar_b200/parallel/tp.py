@@ -20,6 +20,8 @@ from dataclasses import dataclass, field
 import torch
 import torch.distributed as dist
 
+from ..utils.env import debug_env
+
 
 @dataclass
 class TPContext:
@@ -31,6 +33,7 @@ class TPContext:
     symm: object = None                 # parallel.symm.SymmetricArena when fused kernels are available
     stats: dict = field(default_factory=lambda: {"allreduce_calls": 0, "allreduce_bytes": 0, "fused_calls": 0})
     order_check: object = None          # parallel.collective_check.CollectiveOrderChecker in debug mode
+    skip_allreduce: bool = False        # debug switch LLAMINAR_SKIP_ALLREDUCE (isolates compute time; results are wrong)
 
     @staticmethod
     def create(group=None, device=None, fused: bool | None = None) -> "TPContext":
@@ -38,8 +41,12 @@ class TPContext:
         rank, size = dist.get_rank(group), dist.get_world_size(group)
         device = torch.device(device if device is not None else "cpu")
         ctx = TPContext(group, rank, size, device)
+        ctx.skip_allreduce = debug_env().skip_allreduce
+        if debug_env().collective_order_check:
+            from .collective_check import CollectiveOrderChecker
+            ctx.order_check = CollectiveOrderChecker(None)
         want_fused = fused if fused is not None else (device.type == "cuda" and size > 1
-                                                      and os.environ.get("LLAMINAR_TP_FUSED", "1") != "0")
+                                                      and debug_env().tp_fused)
         if want_fused and device.type == "cuda" and size > 1:
             from .symm import SymmetricArena
             try:
@@ -58,6 +65,8 @@ class TPContext:
             return x
         if self.order_check is not None:
             self.order_check.record("all_reduce", x)
+        if self.skip_allreduce:
+            return x
         dist.all_reduce(x, group=self.group)
         self.stats["allreduce_calls"] += 1
         self.stats["allreduce_bytes"] += x.numel() * x.element_size()
