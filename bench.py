@@ -5,8 +5,9 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
 
-One "step" is one decode step of the whole batch (32 sequences -> 32 tokens).  N = 1 runs the
-Qwen3-8B shape in Q4_K_M on one GPU; N > 1 runs the Qwen3-32B shape in Q4_K_S tensor-parallel over N GPUs.
+One "step" is one decode step of the whole batch (32 sequences -> 32 tokens).  Every N runs the Qwen3-32B shape
+in Q4_K_S tensor-parallel over N GPUs (strong scaling, 1024-token prompts); at N = 1 the Qwen3-8B shape in Q4_K_M
+(2048-token prompts) is measured too and reported under `other_models`.
 Weights are random-init (N(0, 0.02), seed 0) and quantised with this package's GGUF encoders; prompts
 are uniform-random token ids.  The timed region replays the captured decode graph K times; the weights
 streamed per step (several GB) are far larger than the 126 MB L2, so no explicit flush is needed.
@@ -35,10 +36,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default=None, help="shape name (default: qwen3-8b for 1 GPU, qwen3-32b for TP)")
+    ap.add_argument("--model", default=None, help="shape name (default: qwen3-32b)")
     ap.add_argument("--recipe", default=None)
     ap.add_argument("--batch", type=int, default=32)
-    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--prompt-len", type=int, default=0, help="0: the model's default (1024 for qwen3-32b, 2048 for qwen3-8b)")
+    ap.add_argument("--watchdog-s", type=int, default=1500, help="dump stacks and exit if the run takes longer than this")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a valid bench)")
     ap.add_argument("--skip-extras", action="store_true", help="only the headline region (no bs1 / prefill / TTFT)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one instead of replaying a graph")
@@ -100,10 +102,18 @@ def reference_arm(args):
     return 0
 
 
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
+def log(msg: str) -> None:
+    """Progress on stderr (the JSON line on stdout stays alone)."""
+    sys.stderr.write(f"[bench rank {os.environ.get('RANK', '0')} +{time.time() - T_START:7.1f}s] {msg}\n")
+    sys.stderr.flush()
+
+
+T_START = time.time()
+MODEL_DEFAULTS = {"qwen3-8b": ("Q4_K_M", 2048), "qwen3-32b": ("Q4_K_S", 1024)}
+
+
+def measure(model_name: str, recipe: str, S: int, args, tp, dev, world: int, rank: int, local: int, extras_on: bool) -> dict:
+    """Builds the engine for one model shape and measures TTFT / prefill / bs1 decode (extras) and the bs-B decode headline."""
     import torch
     import torch.distributed as dist
     from llaminar_b200 import ops
@@ -111,29 +121,15 @@ def main():
     from llaminar_b200.engine.sampling import SamplingParams
     from llaminar_b200.models.config import SHAPES
     from llaminar_b200.models.synth import synthesize
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus != world and world > 1:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    tp = None
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        from llaminar_b200.parallel.tp import TPContext
-        tp = TPContext.create(dist.group.WORLD, dev)
-    model_name = args.model or ("qwen3-8b" if world == 1 else "qwen3-32b")
-    recipe = args.recipe or ("Q4_K_M" if model_name == "qwen3-8b" else "Q4_K_S")
     cfg = SHAPES[model_name]
     if args.layers:
         cfg = cfg.with_(n_layers=args.layers)
-    B, S, K, W = args.batch, args.prompt_len, args.steps, max(args.warmup, 3)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
     t0 = time.time()
+    log(f"synthesising {model_name} ({recipe}), {cfg.n_layers} layers")
     weights = synthesize(cfg, recipe, seed=0, device=dev, with_tokenizer=False)
     t_build = time.time() - t0
+    log(f"weights ready in {t_build:.1f} s; building the engine")
     engine = LLMEngine(weights, device=dev, max_batch=B, max_context=S + K + W + 96, max_prefill_tokens=8192, tp=tp,
                        use_graphs=not args.no_graphs)
     del weights
@@ -155,8 +151,9 @@ def main():
         return float(t)
 
     extras = {}
-    # ---- TTFT / prefill (one 2048-token request at a time, then the batch) ----
-    if not args.skip_extras:
+    # ---- TTFT / prefill (one S-token request at a time), then batch-1 decode ----
+    if extras_on:
+        log("TTFT runs")
         ttfts = []
         for i in range(4):
             barrier()
@@ -171,7 +168,7 @@ def main():
                 ttfts.append(max_over_ranks(ev0.elapsed_time(ev1)))
         extras["ttft_p50_ms"] = statistics.median(ttfts)
         extras["prefill_tok_s_bs1"] = S / (extras["ttft_p50_ms"] / 1e3)
-        # ---- batch-1 decode ----
+        log("batch-1 decode")
         r = engine.add_request(prompts[0], greedy)
         engine.step()
         for _ in range(W):
@@ -188,8 +185,10 @@ def main():
         extras["decode_bs1_tok_s"] = K / (max_over_ranks(ev0.elapsed_time(ev1)) / 1e3)
         extras["decode_bs1_e2e_tok_s"] = K / max_over_ranks(t_w1 - t_w0)
         engine.abort(r.rid)
+        engine.check_health()
 
     # ---- batch prefill ----
+    log(f"batch prefill: {B} x {S} tokens")
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -201,15 +200,16 @@ def main():
     extras["prefill_tok_s"] = B * S / (max_over_ranks(ev0.elapsed_time(ev1)) / 1e3)
 
     # ---- headline: K decode steps of the whole batch ----
+    log(f"decode warm-up ({W} steps) and {K} timed steps at batch {B}")
     for _ in range(W):
         engine.step()
+    engine.check_health()
     key = (next(b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b >= B), True)
     sampler = ClockSampler(local)
     launches0 = ops.launch_count() + engine.stats["graph_replays"] * engine.launches_per_graph.get(key, 0)
     barrier()
     if rank == 0:
         sampler.start()
-    dev_ms = 0.0
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     engine.step_events = list(evs)    # the engine records one pair around the graph replay of each step
     barrier()
@@ -221,34 +221,86 @@ def main():
     barrier()
     engine.step_events = None
     clocks = sampler.stop() if rank == 0 else {}
-    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
-    dev_ms = max_over_ranks(dev_ms)
+    engine.check_health()
+    dev_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in evs))
     wall_s = max_over_ranks(t_w1 - t_w0)
     launches = ops.launch_count() + engine.stats["graph_replays"] * engine.launches_per_graph.get(key, 0) - launches0
-    value = B * K / (dev_ms / 1e3)
-    e2e = B * K / wall_s
     v = engine._dec_views(key[0], 1)
-    h2d = v["n"] * 4
-    d2h = key[0] * 4
     assert all(len(r.output) >= K for r in reqs)
+    res = {"value": B * K / (dev_ms / 1e3), "ms_per_step": dev_ms / K, "e2e": B * K / wall_s, "h2d": v["n"] * 4, "d2h": key[0] * 4,
+           "launches": int(launches), "clocks": clocks, "extras": extras, "build_s": t_build, "layers": cfg.n_layers,
+           "weight_bytes": engine.model.weight_bytes(), "B": B, "S": S, "K": K, "W": W,
+           "fused_tp_calls": tp.stats.get("fused_calls", 0) if tp is not None else 0}
+    log(f"{model_name}: {res['value']:.1f} tok/s device-timed, {res['e2e']:.1f} tok/s end to end")
+    for r in reqs:
+        engine.abort(r.rid)
+    del engine
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import datetime
+    import faulthandler
+    import torch
+    import torch.distributed as dist
+
+    # a run that stops making progress dumps every thread's stack and exits instead of idling on the GPUs
+    faulthandler.dump_traceback_later(args.watchdog_s, exit=True)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    tp = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        from llaminar_b200.parallel.tp import TPContext
+        tp = TPContext.create(dist.group.WORLD, dev)
+        log(f"tensor-parallel context: size {tp.size}, fused peer-memory epilogues {'on' if tp.fused else 'off'}")
+    # the headline model is the same at every N (strong scaling of the Qwen3-32B shape over TP=N); the single-GPU
+    # Qwen3-8B numbers ride along in `extras` at N = 1
+    model_name = args.model or "qwen3-32b"
+    recipe = args.recipe or MODEL_DEFAULTS.get(model_name, ("Q4_K_M", 2048))[0]
+    S = args.prompt_len or MODEL_DEFAULTS.get(model_name, ("Q4_K_M", 2048))[1]
+    res = measure(model_name, recipe, S, args, tp, dev, world, rank, local, extras_on=not args.skip_extras)
+    extra_models = {}
+    if world == 1 and not args.skip_extras and not args.model:
+        r8 = measure("qwen3-8b", "Q4_K_M", 2048, args, None, dev, 1, 0, local, extras_on=True)
+        extra_models["qwen3-8b (Q4_K_M, 2048-token prompts)"] = {
+            "decode_bs32_tok_s": round(r8["value"], 2), "decode_bs32_e2e_tok_s": round(r8["e2e"], 2),
+            "ms_per_step": round(r8["ms_per_step"], 4), **{k: round(v, 2) for k, v in r8["extras"].items()}}
     if rank == 0:
+        ex = res["extras"]
         out = {
-            "metric": "decode_tok_s_bs32", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "config": {"model": f"{model_name} ({recipe}, random-init N(0,0.02) seed 0)", "global_batch": B,
-                       "seq_len": S, "decode_ctx_start": S + 1 + W, "parallelism": f"tp{world}",
+            "metric": "decode_tok_s_bs32", "value": round(res["value"], 2), "unit": "tok/s", "n_gpus": world, "steps": res["K"],
+            "warmup": res["W"], "ms_per_step": round(res["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": f"{model_name} ({recipe}, random-init N(0,0.02) seed 0)", "global_batch": res["B"],
+                       "seq_len": res["S"], "decode_ctx_start": res["S"] + 1 + res["W"], "parallelism": f"tp{world}",
                        "kv_cache": "paged bf16, 64-token pages", "l2": "inputs larger than L2 (weights stream from HBM every step)",
-                       "layers": cfg.n_layers, "weight_bytes_per_gpu": engine.model.weight_bytes()},
-            "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
-            "extras": {k: round(v_, 2) for k, v_ in extras.items()},
-            "build_s": round(t_build, 1),
-            "published_nearest": {"what": "reference Qwen2.5-7B Q8_0 decode bs1 on RTX 3090", "value": 93.97,
-                                  "ours_bs1_ratio": round(extras.get("decode_bs1_tok_s", 0) / 93.97, 2) if extras else None},
+                       "layers": res["layers"], "weight_bytes_per_gpu": res["weight_bytes"],
+                       "fused_tp_calls": res["fused_tp_calls"]},
+            "e2e": {"value": round(res["e2e"], 2), "unit": "tok/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},
+            "gpu_launches": res["launches"],
+            "clocks": res["clocks"],
+            "extras": {k: round(v_, 2) for k, v_ in ex.items()},
+            "other_models": extra_models,
+            "build_s": round(res["build_s"], 1),
+            "published_nearest": {"what": "reference Qwen3.6-27B dense Q4_K_S decode bs1 on RTX 3090", "value": 44.46,
+                                  "ours_bs1_ratio": round(ex.get("decode_bs1_tok_s", 0) / 44.46, 2) if ex else None},
         }
         print(json.dumps(out))
+        sys.stdout.flush()
+    faulthandler.cancel_dump_traceback_later()
     if world > 1:
         dist.destroy_process_group()
     return 0

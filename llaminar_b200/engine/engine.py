@@ -170,6 +170,22 @@ class LLMEngine:
         self.waiting.append(r)
         return r
 
+    def check_health(self) -> None:
+        """Raise if a kernel reported a bounded wait that ran out (a peer rank stalled); the scratch is reset first."""
+        if not self.is_cuda:
+            return
+        sc = getattr(self.model, "scratch", None)
+        bad = sc is not None and int(sc.status[0]) != 0
+        symm = getattr(self.tp, "symm", None) if self.tp is not None else None
+        try:
+            if symm is not None:
+                symm.check_status()
+        finally:
+            if bad:
+                sc.reset()
+        if bad:
+            raise RuntimeError("a GEMM kernel gave up a bounded wait (status word set); scratch buffers were reset")
+
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 

@@ -7,6 +7,14 @@ src/v2/models/qwen35moe/Qwen35MoEGraphConfigBuilder.cpp:37-45).  Small batches r
 step stays graph-capturable); larger batches group tokens by expert and run the tensor-core GEMM per
 expert.  Under expert parallelism a rank only computes the slots routed to its experts and the
 partial outputs are summed across ranks.
+
+Decode-sized batches take the fused path: `moe_route` (RMSNorm + router + top-k + grouped work list, one launch),
+a grouped gate|up GEMV with SwiGLU epilogue and a grouped down GEMV whose last CTA per column tile does the weighted
+combine, the all-reduce across the expert-parallel ranks over peer memory and the residual add
+(the reference runs route, count, scan, scatter, per-expert GEMMs, gather-scale-add and an NCCL all-reduce as
+separate stages: src/v2/compute_stages/stages/MoEExpertComputeStage.cpp, src/v2/models/qwen35moe/Qwen35MoEGraph.cpp:1766-1779).
+Because the residual stream is replicated across the ranks of a tensor-parallel group, "dispatch" needs no transfer:
+every rank gathers the rows routed to its own experts from its local copy.
 """
 from __future__ import annotations
 
@@ -17,10 +25,74 @@ from .. import ops
 SMALL_SLOTS = 256
 
 
+FUSED_MAX_PAIRS = 4096        # tokens * top_k the in-kernel work-list builder accepts
+FUSED_MAX_TOKENS = 64         # rows of the peer-memory inbox used by the fused combine
+
+
+class _FusedWS:
+    """Persistent buffers of the fused decode path (allocated once per token count: CUDA-graph safe)."""
+
+    def __init__(self, model, T: int, n_local: int):
+        c, dev = model.cfg, model.device
+        k = c.n_experts_used
+        z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=dev)
+        self.z_max = n_local + (T * k + 3) // 4
+        self.ids, self.wts = z(T, k, dt=torch.int32), z(T, k, dt=torch.float32)
+        self.items = z(self.z_max * ops.MOE_ITEM_INTS, dt=torch.int32)
+        self.n_items, self.ticket = z(1, dt=torch.int32), z(1, dt=torch.int32)
+        self.counts = z(max(n_local, 1), dt=torch.int32)
+        self.act = z(T * k, c.expert_ff, dt=torch.bfloat16)
+        self.yslot = z(T * k, c.d_model, dt=torch.float32)
+        self.tile_tickets = z((c.d_model + 127) // 128, dt=torch.int32)
+
+
+def fused_supported(model, L, T: int) -> bool:
+    c = model.cfg
+    if not hasattr(ops, "moe_route") or T * c.n_experts_used > FUSED_MAX_PAIRS or c.n_experts > 256 or c.d_model % 256:
+        return False
+    ep = model.tp is not None and model.tp.size > 1
+    if ep:
+        symm = getattr(model.tp, "symm", None)
+        if not (model.tp.fused and symm is not None and T <= symm.rows_cap and c.d_model <= symm.n_cap):
+            return T <= FUSED_MAX_TOKENS * 4          # fused kernels + NCCL all-reduce of the combined rows
+    return True
+
+
+def moe_forward_fused(model, L, h: torch.Tensor, T: int) -> None:
+    """Three launches per layer: route (+ work list), grouped gate|up + SwiGLU, grouped down + combine + all-reduce + residual."""
+    c, sc = model.cfg, model.scratch
+    slab = L.experts
+    k = c.n_experts_used
+    cache = model.__dict__.setdefault("_moe_ws", {})
+    ws = cache.get(T)
+    if ws is None:
+        ws = cache[T] = _FusedWS(model, T, slab.n_local)
+    ops.moe_route(h, L.ffn_norm, c.rms_eps, L.router, k, c.norm_topk_prob, slab.e0, slab.n_local, ws.ids, ws.wts,
+                  ws.items, ws.n_items, ws.ticket, ws.counts)
+    ops.moe_gate_up(slab.gate_up, h, L.ffn_norm, c.rms_eps, ws.act, ws.items, ws.n_items, k, ws.z_max, scratch=sc)
+    ep = model.tp is not None and model.tp.size > 1
+    symm = getattr(model.tp, "symm", None) if ep else None
+    in_kernel = ep and model.tp.fused and symm is not None and T <= symm.rows_cap and c.d_model <= symm.n_cap
+    if ep and not in_kernel:
+        target = model.ws_partial[:T]
+        target.zero_()
+        ops.moe_down_combine(slab.down, ws.act, ws.yslot, ws.items, ws.n_items, ws.z_max, ws.ids, ws.wts, k, slab.e0, slab.n_local,
+                             target, ws.tile_tickets, scratch=sc)
+        model.tp.all_reduce(target)
+        h += target
+        return
+    ops.moe_down_combine(slab.down, ws.act, ws.yslot, ws.items, ws.n_items, ws.z_max, ws.ids, ws.wts, k, slab.e0, slab.n_local,
+                         h, ws.tile_tickets, scratch=sc, tp=symm.desc if in_kernel else None)
+    if in_kernel:
+        model.tp.stats["fused_calls"] += 1
+
+
 def moe_forward(model, L, h: torch.Tensor, T: int) -> None:
     c, sc = model.cfg, model.scratch
     dev = model.device
     k = c.n_experts_used
+    if T * k <= SMALL_SLOTS * 2 and fused_supported(model, L, T):
+        return moe_forward_fused(model, L, h, T)
     xn = model.ws_xn[:T]
     ops.rmsnorm(h, L.ffn_norm, xn, c.rms_eps)
     logits = (xn @ L.router.T).float()

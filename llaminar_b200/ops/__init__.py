@@ -13,7 +13,7 @@ import torch
 from . import build as _build
 from .layout import FMT_IDS, PackedWeight, can_pack, pack_experts, pack_matrix  # noqa: F401
 
-EPI_STORE, EPI_RESID, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_MOE_COMBINE = 0, 1, 2, 3
 GEMV_MAX_ROWS = 4
 PAGE_SIZE = 64
 
@@ -55,6 +55,12 @@ class Scratch:
                        status=z(4, dt=torch.int32))
 
 
+    def reset(self) -> None:
+        """Return the split-K accumulators and counters to zero (after a kernel reported a timed-out wait)."""
+        for t in (self.accum, self.tickets, self.attn_tickets, self.status):
+            t.zero_()
+
+
 _scratch: dict[str, Scratch] = {}
 
 
@@ -93,6 +99,39 @@ def gemv_experts(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, expert_id
     stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
     ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, None, 0.0, out, epi, None, accum, tickets, 0, expert_ids, stride,
                slots_per_row, 1, z, None)
+    _count()
+
+
+MOE_ITEM_INTS = 6          # struct MoeItem { int expert, m, slot[4]; }
+
+
+def moe_route(h, norm_w, eps, router, top_k, renorm, e0, n_local, ids, wts, items, n_items, ticket, counts=None) -> None:
+    """Fused RMSNorm + router projection + softmax top-k + grouped work list of the local experts."""
+    ext().moe_route(h, norm_w, eps, router, top_k, bool(renorm), e0, n_local, ids, wts, items, n_items, ticket, counts)
+    _count()
+
+
+def moe_gate_up(pw: PackedWeight, h, norm_w, eps, act, items, n_items, top_k, z_max, scratch: Scratch | None = None) -> None:
+    """Grouped expert gate|up GEMV with fused RMSNorm prologue and SwiGLU epilogue: act[pair] for every local pair."""
+    accum, tickets = _accum_args(pw, 4 * z_max, scratch)
+    if tickets is not None and z_max * pw.n_tiles > tickets.numel():
+        accum, tickets = None, None
+    stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
+    ext().moe_gemv(pw.data, pw.fmt, pw.n, pw.k, stride, h, norm_w, eps, act, EPI_SWIGLU, items, n_items, top_k, z_max,
+                   accum, tickets, None, None, top_k, 0, 0, None, None, None)
+    _count()
+
+
+def moe_down_combine(pw: PackedWeight, act, yslot, items, n_items, z_max, ids, wts, top_k, e0, n_local, h, tile_tickets,
+                     scratch: Scratch | None = None, tp=None) -> None:
+    """Grouped expert down GEMV; the last CTA of each column tile combines the weighted pairs, all-reduces the tile
+    across expert-parallel ranks over peer memory (when ``tp`` is given) and adds it to the residual stream."""
+    accum, tickets = _accum_args(pw, 4 * z_max, scratch)
+    if tickets is not None and z_max * pw.n_tiles > tickets.numel():
+        accum, tickets = None, None
+    stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
+    ext().moe_gemv(pw.data, pw.fmt, pw.n, pw.k, stride, act, None, 0.0, yslot, EPI_MOE_COMBINE, items, n_items, 1, z_max,
+                   accum, tickets, ids, wts, top_k, e0, n_local, h, tile_tickets, tp)
     _count()
 
 

@@ -59,6 +59,76 @@ static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tenso
     LLM_CUDA_CHECK(llm::launch_gemv(p, (int)m_tile, (int)z, cur_stream()));
 }
 
+// Router: RMSNorm + projection + softmax top-k + grouped work list of the local experts (moe_ep.cu).
+static void moe_route(const Tensor& h, const Tensor& norm_w, double eps, const Tensor& router, int64_t top_k, bool renorm,
+                      int64_t e0, int64_t n_local, Tensor ids, Tensor wts, Tensor items, Tensor n_items, Tensor ticket,
+                      const OptTensor& counts) {
+    check_cuda(h, "h"); check_cuda(router, "router");
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.scalar_type() == torch::kFloat32 && router.scalar_type() == torch::kBFloat16 && router.is_contiguous());
+    TORCH_CHECK(ids.scalar_type() == torch::kInt32 && wts.scalar_type() == torch::kFloat32 && items.scalar_type() == torch::kInt32);
+    llm::MoeRouteParams p{};
+    p.h = static_cast<const float*>(h.data_ptr()); p.h_stride = (int)h.stride(0);
+    p.norm_w = static_cast<const float*>(norm_w.data_ptr()); p.eps = (float)eps;
+    p.router = static_cast<const __nv_bfloat16*>(router.data_ptr());
+    p.tokens = (int)h.size(0); p.d = (int)router.size(1); p.n_experts = (int)router.size(0);
+    p.top_k = (int)top_k; p.renorm = renorm ? 1 : 0; p.e0 = (int)e0; p.n_local = (int)n_local;
+    TORCH_CHECK(ids.numel() >= p.tokens * p.top_k && wts.numel() >= p.tokens * p.top_k);
+    p.ids = static_cast<int*>(ids.data_ptr()); p.wts = static_cast<float*>(wts.data_ptr());
+    p.items = reinterpret_cast<llm::MoeItem*>(items.data_ptr());
+    p.max_items = (int)(items.numel() * 4 / sizeof(llm::MoeItem));
+    p.n_items = static_cast<int*>(n_items.data_ptr()); p.ticket = static_cast<unsigned*>(ticket.data_ptr());
+    p.counts = mptr<int>(counts);
+    LLM_CUDA_CHECK(llm::launch_moe_route(p, cur_stream()));
+}
+
+// Grouped expert GEMV over the router's work list: epi = EPI_SWIGLU (gate|up) or EPI_MOE_COMBINE (down + combine [+ all-reduce]).
+static void moe_gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, int64_t expert_stride, const Tensor& x, const OptTensor& norm_w,
+                     double eps, Tensor out, int64_t epi, const Tensor& items, const Tensor& n_items, int64_t x_div, int64_t z_max,
+                     const OptTensor& accum, const OptTensor& tickets, const OptTensor& ids, const OptTensor& wts, int64_t top_k,
+                     int64_t e0, int64_t n_local, const OptTensor& h, const OptTensor& tile_tickets, const OptTensor& tp) {
+    check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(k % 256 == 0, "k must be a multiple of 256");
+    llm::GemvParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr());
+    p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.n_tiles = (int)((n + 127) / 128); p.k_blocks = (int)(k / 256);
+    p.x = x.data_ptr(); p.x_stride = (int)x.stride(0); p.z_per_x = 1;
+    if (norm_w.has_value()) {
+        TORCH_CHECK(x.scalar_type() == torch::kFloat32, "fused-norm GEMV takes the fp32 residual stream");
+    } else {
+        TORCH_CHECK(x.scalar_type() == torch::kBFloat16, "GEMV input must be bf16");
+    }
+    p.norm_w = cptr<float>(norm_w); p.eps = (float)eps;
+    p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets);
+    p.accum_stride = accum.has_value() ? (int)accum->stride(0) : 0;
+    if (accum.has_value()) {
+        TORCH_CHECK(accum->size(0) >= 4 * z_max && accum->stride(0) >= p.n_tiles * 128, "split-K scratch too small");
+        TORCH_CHECK(tickets.has_value() && tickets->numel() >= z_max * p.n_tiles, "ticket scratch too small");
+    }
+    p.epi = (int)epi;
+    p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
+    p.expert_stride = (size_t)expert_stride;
+    p.items = reinterpret_cast<const llm::MoeItem*>(items.data_ptr());
+    p.n_items = static_cast<const int*>(n_items.data_ptr());
+    p.x_div = (int)x_div;
+    TORCH_CHECK(z_max * (int64_t)sizeof(llm::MoeItem) <= items.numel() * 4, "work list shorter than the grid");
+    if (epi == llm::EPI_MOE_COMBINE) {
+        TORCH_CHECK(ids.has_value() && wts.has_value() && h.has_value() && tile_tickets.has_value(), "combine needs ids, weights, h, tickets");
+        TORCH_CHECK(p.out_f32 && h->scalar_type() == torch::kFloat32);
+        p.moe.ids = cptr<int>(ids); p.moe.wts = cptr<float>(wts);
+        p.moe.tokens = (int)h->size(0); p.moe.top_k = (int)top_k; p.moe.e0 = (int)e0; p.moe.n_local = (int)n_local;
+        p.moe.yslot = static_cast<float*>(out.data_ptr()); p.moe.y_stride = (int)out.stride(0);
+        p.moe.tile_tickets = mptr<unsigned>(tile_tickets);
+        TORCH_CHECK(tile_tickets->numel() >= p.n_tiles);
+        p.moe.h = static_cast<float*>(h->data_ptr()); p.moe.h_stride = (int)h->stride(0);
+        p.tp = tp.has_value() ? reinterpret_cast<const llm::TpFuse*>(tp->data_ptr()) : nullptr;
+    } else {
+        TORCH_CHECK(epi == llm::EPI_SWIGLU && !p.out_f32, "grouped gate|up writes bf16 through the SwiGLU epilogue");
+    }
+    LLM_CUDA_CHECK(llm::launch_gemv(p, 4, (int)z_max, cur_stream()));
+}
+
 static void dequant(const Tensor& w, int64_t fmt, int64_t n, int64_t k, Tensor out) {
     check_cuda(w, "w"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(w.device());
@@ -251,6 +321,8 @@ static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Te
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemv", &gemv);
+    m.def("moe_route", &moe_route);
+    m.def("moe_gemv", &moe_gemv);
     m.def("gemm_tc", &gemm_tc);
     m.def("dequant", &dequant);
     m.def("gather_rows", &gather_rows);

@@ -40,15 +40,19 @@ LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// Bounded wait.  abort_flag[0]: some wait of this CTA gave up (everybody leaves).  abort_flag[1]: the epilogue is inside its
+// own bounded wait for a tensor-parallel peer; the pipeline behind it is legitimately stalled, so the count is held
+// meanwhile (the peer wait has its own limit and reports through the status word).
 LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 512) {
-            if (*abort_flag) return false;
+            if (abort_flag[0]) return false;
+            if (abort_flag[1]) i = 513;
             __nanosleep(40);
         }
     }
-    *abort_flag = 1;
+    abort_flag[0] = 1;
     return false;
 }
 LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -165,7 +169,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[2], s_empty[2], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort, s_last, s_tp_ok;
+    __shared__ int s_abort[2], s_last, s_tp_ok;
     __shared__ unsigned s_tp_epoch;
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi);
 
     if (tid == 0) {
-        s_abort = 0;
+        s_abort[0] = 0; s_abort[1] = 0;
         for (int s = 0; s < 2; ++s) { mbar_init(full_bar + s * 8, N_DQ_WARPS + 1); mbar_init(empty_bar + s * 8, 1); }
         for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, N_DQ_WARPS); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem;
-    volatile int* abort_flag = &s_abort;
+    volatile int* abort_flag = s_abort;
     // optional timeline trace of CTA 0: p.debug[role * 1024 + slot] = low 32 bits of the ns timer
     auto stamp = [&](int role, int slot) {
         if (p.debug && blockIdx.x == 0 && slot < 1024) {
@@ -376,7 +380,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     if (!ok) break;
                     if (tid < tp.size) tp_signal(tp, u.tile, tid);
                     if (tid == 0) {
+                        abort_flag[1] = 1;                     // hold the other warps' wait limits while the peer is awaited
                         s_tp_ok = tp_wait(tp, u.tile, e) ? 1 : 0;
+                        abort_flag[1] = 0;
                         tp.epoch[u.tile] = e + 1;
                     }
                     ok = epi_sync();

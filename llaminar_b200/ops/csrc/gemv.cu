@@ -17,7 +17,7 @@
 namespace llm {
 
 template <int M, int NORM>
-LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* acts, float* s_red, int m0) {
+LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* acts, float* s_red, const int (&xr)[M]) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float rms[M];
     if (NORM) {
@@ -26,7 +26,7 @@ LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* act
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             ss[m] = 0.f;
-            const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)(m0 + m) * p.x_stride);
+            const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)xr[m] * p.x_stride);
             for (int i = tid; i < p.k / 4; i += blockDim.x) {
                 const float4 v = x4[i];
                 ss[m] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -49,11 +49,11 @@ LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* act
             const int col = kb0 * 256 + qd * 4;
             float v0, v1, v2, v3;
             if (NORM) {
-                const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)(m0 + m) * p.x_stride + col);
+                const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)xr[m] * p.x_stride + col);
                 const float4 g = *reinterpret_cast<const float4*>(p.norm_w + col);
                 v0 = v.x * rms[m] * g.x; v1 = v.y * rms[m] * g.y; v2 = v.z * rms[m] * g.z; v3 = v.w * rms[m] * g.w;
             } else {
-                const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)(m0 + m) * p.x_stride + col);
+                const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)xr[m] * p.x_stride + col);
                 v0 = bf16_lo(v.x); v1 = bf16_hi(v.x); v2 = bf16_lo(v.y); v3 = bf16_hi(v.y);
             }
             float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
@@ -86,8 +86,20 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     const int kb0 = blockIdx.y * per;
     const int kb1 = min(p.k_blocks, kb0 + per);
     const int nkb = max(kb1 - kb0, 0);
-    const int m0 = blockIdx.z * M;                        // first output row of this CTA
-    const int mx0 = (blockIdx.z / p.z_per_x) * M;         // first activation row
+    // rows of this CTA: consecutive ones, or the (token, slot) pairs of a grouped-expert work item
+    int xr[M], orow[M], n_valid = M, expert = -1;
+    if (p.items) {
+        if ((int)blockIdx.z >= __ldg(p.n_items)) return;
+        const MoeItem it = p.items[blockIdx.z];
+        expert = it.expert;
+        n_valid = min(it.m, M);
+#pragma unroll
+        for (int m = 0; m < M; ++m) { orow[m] = it.slot[m]; xr[m] = it.slot[m] / p.x_div; }
+    } else {
+#pragma unroll
+        for (int m = 0; m < M; ++m) { orow[m] = blockIdx.z * M + m; xr[m] = (blockIdx.z / p.z_per_x) * M + m; }
+        if (p.expert_ids) expert = p.expert_ids[blockIdx.z];
+    }
 
     ActBlk* acts = reinterpret_cast<ActBlk*>(smem);
     float* s_red = reinterpret_cast<float*>(smem + (size_t)M * per * sizeof(ActBlk));   // [2][M][128] floats
@@ -95,10 +107,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     if (FMT == FMT_IQ3_S) {
         for (int i = tid; i < 512; i += blockDim.x) s_grid[i] = g_iq3s_grid[i];
     }
-    gemv_prologue<M, NORM>(p, kb0, nkb, acts, s_red, mx0);
+    gemv_prologue<M, NORM>(p, kb0, nkb, acts, s_red, xr);
 
     const uint8_t* wbase = p.w;
-    if (p.expert_ids) wbase += (size_t)p.expert_ids[blockIdx.z] * p.expert_stride;
+    if (expert >= 0) wbase += (size_t)expert * p.expert_stride;
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
@@ -154,9 +166,70 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[m], 16);
-                if (lane < 16 && col < p.n / 2)
-                    static_cast<__nv_bfloat16*>(p.out)[(size_t)(m0 + m) * p.out_stride + col] = __float2bfloat16(silu(v[m]) * other);
+                if (lane < 16 && col < p.n / 2 && m < n_valid)
+                    static_cast<__nv_bfloat16*>(p.out)[(size_t)orow[m] * p.out_stride + col] = __float2bfloat16(silu(v[m]) * other);
             }
+        }
+        return;
+    }
+    if (p.epi == EPI_MOE_COMBINE) {
+        // grouped expert down-projection: park this item's rows, and let the CTA that finishes the tile last do the
+        // weighted combine over the locally owned pairs, the all-reduce across expert-parallel ranks and the residual add
+        const MoeCombine& mc = p.moe;
+        __shared__ int s_last2, s_ok2;
+        __shared__ unsigned s_epoch2;
+        if (tid < 128 && row < p.n) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (m < n_valid) __stcg(&mc.yslot[(size_t)orow[m] * mc.y_stride + row], v[m]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned t = atomicAdd(&mc.tile_tickets[tile], 1u);
+            s_last2 = (t == (unsigned)__ldg(p.n_items) - 1u);
+            if (s_last2 && p.tp) s_epoch2 = p.tp->epoch[tile];
+        }
+        __syncthreads();
+        if (!s_last2) return;
+        __threadfence();
+        if (tid == 0) mc.tile_tickets[tile] = 0u;
+        const int col = tile * 128 + (tid & 127), half = tid >> 7;
+        const bool live = col < p.n;
+        const TpFuse* tp = p.tp;
+        const unsigned e = tp ? s_epoch2 : 0u;
+        const int parity = e & 1;
+        for (int t = half; t < mc.tokens; t += 2) {
+            float sum = 0.f;
+            if (live) {
+                for (int j = 0; j < mc.top_k; ++j) {
+                    const int pr = t * mc.top_k + j;
+                    const int ex = mc.ids[pr] - mc.e0;
+                    if ((unsigned)ex < (unsigned)mc.n_local) sum += mc.wts[pr] * __ldcg(&mc.yslot[(size_t)pr * mc.y_stride + col]);
+                }
+                if (!tp) {
+                    mc.h[(size_t)t * mc.h_stride + col] += sum;
+                } else {
+                    for (int r = 0; r < tp->size; ++r)
+                        tp->inbox[r][((size_t)(parity * tp->size + tp->rank) * tp->rows_cap + t) * tp->n_cap + col] = sum;
+                }
+            }
+        }
+        if (!tp) return;
+        __threadfence_system();
+        __syncthreads();
+        if (tid < tp->size) tp_signal(*tp, tile, tid);
+        if (tid == 0) {
+            s_ok2 = tp_wait(*tp, tile, e) ? 1 : 0;
+            tp->epoch[tile] = e + 1;
+        }
+        __syncthreads();
+        if (!s_ok2 || !live) return;
+        for (int t = half; t < mc.tokens; t += 2) {
+            float sum = 0.f;
+            for (int src = 0; src < tp->size; ++src)
+                sum += __ldcg(tp->inbox[tp->rank] + ((size_t)(parity * tp->size + src) * tp->rows_cap + t) * tp->n_cap + col);
+            mc.h[(size_t)t * mc.h_stride + col] += sum;
         }
         return;
     }
@@ -168,7 +241,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         if (tid == 0) s_epoch = tp.epoch[tile];
         __syncthreads();
         const unsigned e = s_epoch;
-        auto row_of = [&](int i) { return m0 + i; };
+        auto row_of = [&](int i) { return orow[i]; };
         if (tid < 128 && row < p.n) {
             if (p.bias && tp.rank == 0) {
 #pragma unroll
@@ -187,16 +260,17 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             tp_reduce<M>(tp, e, row, v, row_of);
             float* h = static_cast<float*>(p.out);
 #pragma unroll
-            for (int m = 0; m < M; ++m) h[(size_t)(m0 + m) * p.out_stride + row] += v[m];
+            for (int m = 0; m < M; ++m) h[(size_t)orow[m] * p.out_stride + row] += v[m];
         }
         return;
     }
     if (tid < 128 && row < p.n) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
+            if (m >= n_valid) break;
             float o = v[m];
             if (p.bias) o += p.bias[row];
-            const size_t idx = (size_t)(m0 + m) * p.out_stride + row;
+            const size_t idx = (size_t)orow[m] * p.out_stride + row;
             if (p.epi == EPI_RESID) {
                 float* h = static_cast<float*>(p.out);
                 h[idx] = h[idx] + o;
@@ -249,7 +323,9 @@ size_t gemv_smem_bytes(int m_tile, int k_blocks, int ksplit) {
 // m_tile rows per CTA (1..4), z = number of row groups (grid.z); rows total = m_tile * z.
 cudaError_t launch_gemv(const GemvParams& p, int m_tile, int z, cudaStream_t st) {
     if (m_tile < 1 || m_tile > 4 || z < 1) return cudaErrorInvalidValue;
-    if (p.tp && z != 1) return cudaErrorInvalidValue;      // the per-tile flag protocol serves one row group
+    if (p.tp && z != 1 && p.epi != EPI_MOE_COMBINE) return cudaErrorInvalidValue;   // the per-tile flag protocol serves one row group
+    if (p.items && (m_tile != 4 || !p.n_items || p.x_div < 1)) return cudaErrorInvalidValue;
+    if (p.epi == EPI_MOE_COMBINE && (!p.items || !p.moe.yslot || !p.moe.tile_tickets)) return cudaErrorInvalidValue;
     int ks = p.ksplit > 0 ? p.ksplit : gemv_pick_ksplit(p.n_tiles, p.k_blocks, z);
     if (!p.accum || !p.tickets) ks = 1;
     size_t smem = gemv_smem_bytes(m_tile, p.k_blocks, ks);

@@ -1,0 +1,173 @@
+// Mixture-of-experts routing for expert-parallel decode: RMSNorm + router projection + softmax + top-k (+ renormalise)
+// + the grouped work list of the experts this rank owns, in one launch.
+//
+// One CTA per token.  The token's residual row is normalised into shared memory, the eight warps split the router rows
+// (bf16 [experts, d], L2 resident), warp 0 takes softmax and the top-k (ties go to the lower expert id).  The CTA that
+// finishes last (ticket) turns the [tokens, top_k] expert ids into work items: for every local expert the pairs routed
+// to it, in token order, cut into groups of four.  The grouped GEMVs (gemv.cu, `GemvParams::items`) consume that list
+// without a host round trip, so a decode step stays CUDA-graph capturable.
+//
+// Replaces the reference's route_logits / softmax_topk / count_per_expert / exclusive_scan / scatter_tokens kernels and the
+// host-built expert lists between them (reference: src/v2/kernels/cuda/moe/CUDAMoEKernels.cu:66-700,
+// src/v2/kernels/cuda/moe/CUDAMoEKernel.cpp).
+#include "common.cuh"
+#include "gemv.h"
+
+namespace llm {
+
+constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_MAX_EXPERTS = 256;
+constexpr int ROUTE_MAX_PAIRS = 4096;      // tokens * top_k handled by the list builder
+
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRouteParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* xn = reinterpret_cast<float*>(smem_raw);                 // [d]
+    float* logits = xn + p.d;                                        // [ROUTE_MAX_EXPERTS]
+    __shared__ float s_part[ROUTE_THREADS / 32];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t = blockIdx.x;
+
+    // ---- RMSNorm of the token's row into shared memory ----
+    const float* hrow = p.h + (size_t)t * p.h_stride;
+    float ss = 0.f;
+    for (int i = tid * 4; i < p.d; i += ROUTE_THREADS * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(hrow + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROUTE_THREADS / 32; ++w) tot += s_part[w];
+    const float rms = rsqrtf(tot / p.d + p.eps);
+    for (int i = tid * 4; i < p.d; i += ROUTE_THREADS * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(hrow + i);
+        const float4 g = *reinterpret_cast<const float4*>(p.norm_w + i);
+        *reinterpret_cast<float4*>(xn + i) = make_float4(v.x * rms * g.x, v.y * rms * g.y, v.z * rms * g.z, v.w * rms * g.w);
+    }
+    __syncthreads();
+
+    // ---- router projection: warp w takes experts w, w + 8, ... ----
+    for (int e = warp; e < p.n_experts; e += ROUTE_THREADS / 32) {
+        const __nv_bfloat16* wrow = p.router + (size_t)e * p.d;
+        float acc = 0.f;
+        for (int i = lane * 8; i < p.d; i += 256) {
+            const uint4 w8 = *reinterpret_cast<const uint4*>(wrow + i);
+            const float4 a = *reinterpret_cast<const float4*>(xn + i);
+            const float4 b = *reinterpret_cast<const float4*>(xn + i + 4);
+            acc += bf16_lo(w8.x) * a.x + bf16_hi(w8.x) * a.y + bf16_lo(w8.y) * a.z + bf16_hi(w8.y) * a.w
+                 + bf16_lo(w8.z) * b.x + bf16_hi(w8.z) * b.y + bf16_lo(w8.w) * b.z + bf16_hi(w8.w) * b.w;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logits[e] = acc;
+    }
+    __syncthreads();
+
+    // ---- softmax over all experts, top-k with lower-id tie-break (warp 0) ----
+    if (warp == 0) {
+        constexpr int PER = ROUTE_MAX_EXPERTS / 32;
+        float v[PER];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int e = j * 32 + lane;
+            v[j] = e < p.n_experts ? logits[e] : -INFINITY;
+            mx = fmaxf(mx, v[j]);
+        }
+        mx = warp_max(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            v[j] = (j * 32 + lane) < p.n_experts ? __expf(v[j] - mx) : -1.0f;
+            sum += fmaxf(v[j], 0.f);
+        }
+        sum = warp_sum(sum);
+        float wsum = 0.f, my_w = 0.f;
+        int my_id = 0;
+        for (int s = 0; s < p.top_k; ++s) {
+            float best = -1.0f;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int e = j * 32 + lane;
+                if (v[j] > best || (v[j] == best && e < bi)) { best = v[j]; bi = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            }
+            if ((bi & 31) == lane) v[bi >> 5] = -2.0f;
+            const float pw = best / sum;
+            wsum += pw;
+            if (lane == s) { my_w = pw; my_id = bi; }
+        }
+        if (lane < p.top_k) {
+            p.ids[(size_t)t * p.top_k + lane] = my_id;
+            p.wts[(size_t)t * p.top_k + lane] = p.renorm ? my_w / wsum : my_w;
+        }
+    }
+    // ---- last CTA: build the grouped work list of the local experts ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(p.ticket, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    int* s_ids = reinterpret_cast<int*>(smem_raw);                   // reuse: [pairs]
+    __shared__ int s_cnt[ROUTE_MAX_EXPERTS], s_off[ROUTE_MAX_EXPERTS + 1];
+    const int pairs = p.tokens * p.top_k;
+    for (int i = tid; i < pairs; i += ROUTE_THREADS) s_ids[i] = __ldcg(p.ids + i);
+    __syncthreads();
+    if (tid < p.n_local) {
+        int c = 0;
+        const int e = p.e0 + tid;
+        for (int i = 0; i < pairs; ++i) c += (s_ids[i] == e);
+        s_cnt[tid] = c;
+        if (p.counts) p.counts[tid] = c;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int off = 0;
+        for (int e = 0; e < p.n_local; ++e) { s_off[e] = off; off += (s_cnt[e] + 3) >> 2; }
+        if (off == 0) {                                              // keep the combine protocol alive on an idle rank
+            p.items[0].expert = 0; p.items[0].m = 0;
+            p.items[0].slot[0] = p.items[0].slot[1] = p.items[0].slot[2] = p.items[0].slot[3] = 0;
+            off = 1;
+        }
+        s_off[p.n_local] = off;
+        *p.n_items = min(off, p.max_items);
+        *p.ticket = 0u;
+    }
+    __syncthreads();
+    if (tid < p.n_local && s_cnt[tid] > 0) {
+        const int e = p.e0 + tid;
+        int item = s_off[tid], m = 0;
+        for (int i = 0; i < pairs; ++i) {
+            if (s_ids[i] != e) continue;
+            if (item < p.max_items) {
+                MoeItem& it = p.items[item];
+                if (m == 0) { it.expert = tid; it.slot[1] = it.slot[2] = it.slot[3] = i; }
+                it.slot[m] = i;
+                it.m = m + 1;
+            }
+            if (++m == 4) { m = 0; ++item; }
+        }
+    }
+}
+
+cudaError_t launch_moe_route(const MoeRouteParams& p, cudaStream_t st) {
+    if (p.tokens == 0) return cudaSuccess;
+    if (p.n_experts > ROUTE_MAX_EXPERTS || p.top_k > 32 || p.n_local > ROUTE_MAX_EXPERTS || (p.d & 255) != 0 ||
+        p.tokens * p.top_k > ROUTE_MAX_PAIRS)
+        return cudaErrorInvalidValue;
+    const size_t dyn = max((size_t)(p.d + ROUTE_MAX_EXPERTS) * sizeof(float), (size_t)p.tokens * p.top_k * sizeof(int));
+    if (dyn > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+    moe_route_kernel<<<p.tokens, ROUTE_THREADS, dyn, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace llm

@@ -17,13 +17,15 @@ import struct
 import torch
 import torch.distributed as dist
 
-ROWS_CAP = 32
+ROWS_CAP = 64
 TP_MAX_RANKS = 8
 
 
 class SymmetricArena:
-    def __init__(self, group, device, n_cap: int, rows_cap: int = ROWS_CAP, spin_limit: int = 4_000_000):
+    def __init__(self, group, device, n_cap: int, rows_cap: int = ROWS_CAP, spin_limit: int | None = None):
         import torch.distributed._symmetric_memory as symm_mem
+        from ..utils.env import debug_env
+        spin_limit = debug_env().tp_spin_limit if spin_limit is None else spin_limit
         self.group, self.device = group, torch.device(device)
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
         if self.size > TP_MAX_RANKS:
@@ -71,4 +73,5 @@ class SymmetricArena:
     def check_status(self) -> None:
         s = int(self.status[0])
         if s != 0:
+            self.status.zero_()
             raise RuntimeError(f"a fused tensor-parallel kernel gave up waiting for a peer (status {s})")

@@ -306,3 +306,64 @@ def test_spec_verify_and_moe_topk_and_nan_scan():
     x = torch.randn(1000, device=DEV); x[3] = float("nan"); x[10] = float("inf"); x[11] = -float("inf")
     assert ops.nan_scan(x) == (1, 2)
     assert ops.nan_scan(torch.ones(64, device=DEV).to(torch.bfloat16)) == (0, 0)
+
+
+@pytest.mark.parametrize("tokens,qt_name", [(1, "IQ3_S"), (7, "IQ3_S"), (64, "IQ3_S"), (33, "Q4_K")])
+def test_moe_fused_route_gate_up_down_combine(tokens, qt_name):
+    """Router + grouped expert GEMVs + weighted combine against a plain fp32 restatement (single rank: no all-reduce)."""
+    from llaminar_b200 import ops
+    from llaminar_b200.models.reference import moe_route
+    from llaminar_b200.ops.layout import interleave_gate_up, pack_experts
+    dev = torch.device("cuda")
+    E, k, d, ff = 128, 8, 2048, 768
+    e0, n_local = 32, 48                                  # this "rank" owns experts 32..79
+    qt = GGMLType[qt_name]
+    g = torch.Generator(device=dev).manual_seed(7)
+    h = torch.randn(tokens, d, device=dev, generator=g)
+    norm_w = 1.0 + 0.1 * torch.randn(d, device=dev, generator=g)
+    router = (torch.randn(E, d, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wg = torch.randn(n_local, ff, d, device=dev, generator=g) * 0.05
+    wu = torch.randn(n_local, ff, d, device=dev, generator=g) * 0.05
+    wd = torch.randn(n_local, d, ff, device=dev, generator=g) * 0.05
+    gu_raw, dn_raw, wg_q, wu_q, wd_q = [], [], [], [], []
+    for e in range(n_local):
+        rg, ru, rd = quantize(wg[e], qt), quantize(wu[e], qt), quantize(wd[e], qt)
+        wg_q.append(dequantize(rg, qt, (ff, d))); wu_q.append(dequantize(ru, qt, (ff, d))); wd_q.append(dequantize(rd, qt, (d, ff)))
+        gu_raw.append(interleave_gate_up(rg, ru, qt, ff, d)[0])
+        dn_raw.append(rd)
+    gate_up = pack_experts(torch.cat(gu_raw), qt, n_local, 2 * ff, d)
+    down = pack_experts(torch.cat(dn_raw), qt, n_local, d, ff)
+    z_max = n_local + (tokens * k + 3) // 4
+    zi = lambda *s, dt=torch.int32: torch.zeros(*s, dtype=dt, device=dev)
+    ids, wts = zi(tokens, k), zi(tokens, k, dt=torch.float32)
+    items, n_items, ticket, counts = zi(z_max * ops.MOE_ITEM_INTS), zi(1), zi(1), zi(n_local)
+    act = zi(tokens * k, ff, dt=torch.bfloat16)
+    yslot = zi(tokens * k, d, dt=torch.float32)
+    tile_tickets = zi(d // 128)
+    sc = ops.scratch_for(dev)
+    eps = 1e-6
+    for rep in range(2):                                  # second pass: tickets and counters were returned to zero
+        hh = h.clone()
+        ops.moe_route(hh, norm_w, eps, router, k, True, e0, n_local, ids, wts, items, n_items, ticket, counts)
+        ops.moe_gate_up(gate_up, hh, norm_w, eps, act, items, n_items, k, z_max, scratch=sc)
+        ops.moe_down_combine(down, act, yslot, items, n_items, z_max, ids, wts, k, e0, n_local, hh, tile_tickets, scratch=sc)
+        torch.cuda.synchronize()
+        xn = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * norm_w
+        logits = xn @ router.float().T
+        rid, rw = moe_route(logits, k, True)
+        same = (rid.sort(-1).values == ids.long().sort(-1).values).float().mean().item()
+        assert same > 0.98                                # a near-tie at the k-th place may resolve differently
+        assert torch.allclose(wts.sum(-1), torch.ones(tokens, device=dev), atol=1e-4)
+        # expert math on the kernel's own routing
+        ref = h.clone()
+        for t in range(tokens):
+            for j in range(k):
+                e = int(ids[t, j]) - e0
+                if 0 <= e < n_local:
+                    a = torch.nn.functional.silu(wg_q[e] @ xn[t]) * (wu_q[e] @ xn[t])
+                    ref[t] += float(wts[t, j]) * (wd_q[e] @ a)
+        delta, rdelta = hh - h, ref - h
+        assert (delta - rdelta).norm() / rdelta.norm().clamp_min(1e-6) < 3e-2
+        local_pairs = int(((ids >= e0) & (ids < e0 + n_local)).sum())
+        assert int(counts.sum()) == local_pairs
+        assert int(n_items) >= max(1, (local_pairs + 3) // 4) and int(ticket) == 0 and int(tile_tickets.sum()) == 0
