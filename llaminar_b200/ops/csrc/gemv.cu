@@ -216,7 +216,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             }
         }
         if (!tp) return;
-        __threadfence_system();
         __syncthreads();
         if (tid < tp->size) tp_signal(*tp, tile, tid);
         if (tid == 0) {

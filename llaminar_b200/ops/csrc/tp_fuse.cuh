@@ -10,7 +10,7 @@
 // Protocol per tile t (every rank runs the same sequence of fused calls, all with d_model / 128 tiles):
 //   e = epoch[t] (local call counter), parity = e & 1
 //   inbox[r][parity][my_rank][m][n]  <- my partial, for every rank r          (peer stores)
-//   __threadfence_system(); flags[r][t] += 1 on every rank r                  (release, system scope)
+//   CTA barrier; flags[r][t] += 1 on every rank r                             (red.release.sys: cumulative release)
 //   spin (bounded) until flags[me][t] >= (e + 1) * size                        (acquire, system scope)
 //   h[m][n] += sum_src inbox[me][parity][src][m][n]  (src order fixed, so all ranks compute identical bits)
 // A rank can run at most one call ahead of a peer (it needs the peer's tiles of call c to finish call c), so two
@@ -53,7 +53,8 @@ LLM_DEVICE void tp_push(const TpFuse& tp, unsigned epoch_val, int n, const float
             if (m >= 0) base[(size_t)m * tp.n_cap] = v[i];
         }
     }
-    __threadfence_system();
+    // no fence here: the caller's CTA-wide barrier orders these stores before the signalling thread's
+    // red.release.sys, whose release is cumulative over everything that happened before the barrier
 }
 
 // Step 2 (one thread per peer, after every pushing thread passed a barrier): signal.
@@ -66,7 +67,7 @@ LLM_DEVICE bool tp_wait(const TpFuse& tp, int tile, unsigned epoch_val) {
     for (unsigned i = 0; i < tp.spin_limit; ++i) {
         // wrap-safe comparison of monotone counters
         if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
-        if (i > 64) __nanosleep(100);
+        if (i > 4096) __nanosleep(64);       // the peer is normally a few microseconds away: poll hard first
     }
     if (tp.status) atomicExch(tp.status, (int)STATUS_TIMEOUT);
     return false;

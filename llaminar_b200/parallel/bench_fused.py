@@ -1,0 +1,115 @@
+"""Microbenchmark of the fused row-parallel GEMM/GEMV + all-reduce against GEMM + NCCL all-reduce + add.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29533 \
+        -m llaminar_b200.parallel.bench_fused --rows 1 32 --shape 5120x8192 5120x25600
+
+Every number is the device time of one call (CUDA events on the launching stream, L2 made cold by rotating through
+weight copies larger than the cache), maximum over ranks.  The roofline printed beside it is the slower of the
+weight bytes over the measured HBM bandwidth and the bytes that must cross NVLink over the measured peer bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, nargs="+", default=[1, 4, 32])
+    ap.add_argument("--shape", nargs="+", default=["5120x8192", "5120x25600"], help="N x K of the full (unsharded) weight")
+    ap.add_argument("--fmt", default="Q4_K")
+    ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--hbm-gbs", type=float, default=6455.6)
+    ap.add_argument("--nvlink-gbs", type=float, default=770.0)
+    args = ap.parse_args()
+    from .. import ops
+    from ..gguf import GGMLType
+    from ..gguf.constants import BLOCK_GEOMETRY
+    from .tp import TPContext
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = TPContext.create(device=dev, fused=True) if world > 1 else None
+    qt = GGMLType[args.fmt]
+    elems, bpb = BLOCK_GEOMETRY[qt]
+    sc = ops.scratch_for(dev)
+    out = []
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn(0)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            fn(i)
+            b.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+        t = torch.tensor([ts[len(ts) // 2]], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    for shp in args.shape:
+        n, k_full = (int(v) for v in shp.split("x"))
+        k = k_full // world
+        wbytes = n * k // elems * bpb
+        copies = max(2, int(400e6 // wbytes) + 1)                   # rotate through > 3x the L2 capacity
+        g = torch.Generator(device=dev).manual_seed(1 + rank)
+        raws = [torch.randint(0, 256, (wbytes,), dtype=torch.uint8, device=dev, generator=g) for _ in range(copies)]
+        # random bytes are valid blocks for timing purposes except for fp16 scale fields that could decode to inf/nan;
+        # clear the exponent's top bit of every 16-bit word so all scales stay finite
+        pws = []
+        for r in raws:
+            r16 = r.view(torch.int16)
+            r16 &= 0x3FFF
+            pws.append(ops.pack_matrix(r, qt, n, k))
+        for rows in args.rows:
+            x = (torch.randn(rows, k, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+            h = torch.zeros(rows, n, device=dev)
+            part = torch.zeros(rows, n, device=dev)
+            small = rows <= ops.GEMV_MAX_ROWS
+            call = ops.gemv if small else ops.gemm
+
+            def plain(i):
+                call(pws[i % copies], x, h, epi=ops.EPI_RESID, scratch=sc)
+
+            def nccl(i):
+                call(pws[i % copies], x, part, epi=ops.EPI_STORE, scratch=sc)
+                dist.all_reduce(part)
+                h.add_(part)
+
+            def fused(i):
+                call(pws[i % copies], x, h, epi=ops.EPI_RESID, scratch=sc, tp=tp.symm.desc)
+
+            rec = {"shape": shp, "rows": rows, "fmt": args.fmt, "world": world, "k_local": k,
+                   "gemm_only_us": round(timed(plain, args.iters), 2)}
+            if world > 1:
+                rec["gemm_nccl_add_us"] = round(timed(nccl, args.iters), 2)
+                rec["fused_us"] = round(timed(fused, args.iters), 2)
+                tp.symm.check_status()
+                link_bytes = rows * n * 4 * (world - 1)              # this rank's partial tile rows go to every peer
+                roof = max(wbytes / (args.hbm_gbs * 1e3), link_bytes / (args.nvlink_gbs * 1e3))
+                rec["roofline_us"] = round(roof, 2)
+                rec["fused_frac_of_roofline"] = round(roof / rec["fused_us"], 3)
+                rec["speedup_vs_nccl"] = round(rec["gemm_nccl_add_us"] / rec["fused_us"], 2)
+            out.append(rec)
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

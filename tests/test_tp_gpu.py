@@ -82,3 +82,33 @@ def test_engine_tp2_fused_equals_nccl_baseline():
     assert fused[0][1]["fused_calls"] > 0 and base[0][1]["fused_calls"] == 0
     agree = sum(a == b for fo, bo in zip(fused[0][0], base[0][0]) for a, b in zip(fo, bo))
     assert agree >= 0.9 * 48            # different summation order may flip a near-tie
+
+
+def _moe_engine_tokens(rank, world, fused):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    dev = torch.device("cuda", rank)
+    cfg = SHAPES["tiny-qwen3moe"].with_(d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, expert_ff=256, n_experts=16,
+                                        n_experts_used=4, n_layers=2)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    tp = TPContext.create(device=dev, fused=fused)
+    eng = LLMEngine(w, device=dev, max_batch=8, max_context=256, tp=tp)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9, 70, 21, 64, 5)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    eng.check_health()
+    return outs, dict(tp.stats)
+
+
+def test_engine_moe_expert_parallel_fused_combine_2gpu():
+    """Expert parallelism over 2 GPUs: the grouped down-projection's epilogue combines and all-reduces over peer memory."""
+    _need(2)
+    fused = run_ranks_gpu(_moe_engine_tokens, 2, True)
+    base = run_ranks_gpu(_moe_engine_tokens, 2, False)
+    assert fused[0][0] == fused[1][0] and base[0][0] == base[1][0]
+    assert fused[0][1]["fused_calls"] > base[0][1]["fused_calls"]
+    agree = sum(a == b for fo, bo in zip(fused[0][0], base[0][0]) for a, b in zip(fo, bo))
+    assert agree >= 0.85 * 48
