@@ -368,10 +368,7 @@ class CudaModel:
         emb = torch.empty(T, c.d_model, dtype=torch.float32, device=self.device)
         self.embed_tokens(fb.tokens, emb)
         cat = torch.empty(T, 2 * c.d_model, dtype=torch.bfloat16, device=self.device)
-        ops.rmsnorm(emb, L.enorm, self.ws_xn[:T], c.rms_eps)
-        cat[:, :c.d_model].copy_(self.ws_xn[:T])
-        ops.rmsnorm(hidden.contiguous(), L.hnorm, self.ws_xn[:T], c.rms_eps)
-        cat[:, c.d_model:].copy_(self.ws_xn[:T])
+        ops.mtp_concat_norm(emb, hidden.float().contiguous(), L.enorm, L.hnorm, cat, c.rms_eps)
         x0 = torch.empty(T, c.d_model, dtype=torch.float32, device=self.device)
         L.eh_proj(cat, x0, scratch=self.scratch, xn=cat if T > ops.GEMV_MAX_ROWS else None)
         h = self.ws_h[:T]

@@ -142,6 +142,11 @@ class LLMEngine:
         self._tok_dev = torch.zeros(bmax * R, dtype=torch.int32, device=self.device)
         self._tok_host = torch.zeros(bmax * R, dtype=torch.int32).pin_memory()
         self._logits = torch.empty(bmax * R, self.model.vocab_local, dtype=torch.float32, device=self.device)
+        # per-shard argmax candidates (value bits, global index) and their all-gathered copies: greedy sampling over a
+        # vocabulary-sharded head exchanges 8 bytes per row instead of the logits
+        ws = self.tp.size if self.tp is not None else 1
+        self._pairs = torch.zeros(bmax * R, 2, dtype=torch.int32, device=self.device)
+        self._pairs_all = torch.zeros(ws, bmax * R, 2, dtype=torch.int32, device=self.device)
 
     def _dec_views(self, bucket: int, R: int):
         """Slices of the static int buffer for a (bucket, rows-per-seq) decode shape."""
@@ -333,9 +338,13 @@ class LLMEngine:
     # -- sampling -----------------------------------------------------------------------------------
     def _sample_rows(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
         """Eager sampling of one row per request (prefill tail, penalties, CPU backend)."""
+        all_greedy = all(r.params.is_greedy and not r.params.needs_penalties and not r.forced for r in reqs)
+        if all_greedy and self._sharded_vocab() and logits.shape[0] <= self._pairs.shape[0]:
+            tok = torch.empty(len(reqs), dtype=torch.int32, device=self.device)
+            self._sharded_argmax(logits.contiguous(), len(reqs), tok)
+            return tok.tolist()
         logits = self._gather_vocab(logits)
         out = []
-        all_greedy = all(r.params.is_greedy and not r.params.needs_penalties and not r.forced for r in reqs)
         if all_greedy:
             if self.is_cuda:
                 from .. import ops
@@ -364,6 +373,19 @@ class LLMEngine:
                 gen = torch.Generator().manual_seed(seed * 1000003 + len(r.output))
                 out.append(sample_row(row, r.params, gen))
         return out
+
+    def _sharded_vocab(self) -> bool:
+        return self.is_cuda and self.tp is not None and self.tp.size > 1 and not getattr(self.model, "returns_full_vocab", False)
+
+    def _sharded_argmax(self, logits: torch.Tensor, rows: int, tokens: torch.Tensor) -> None:
+        """Greedy token over a vocabulary-sharded head: per-shard argmax, all-gather of (value, index), merge."""
+        from .. import ops
+        ws = self.tp.size
+        pairs = self._pairs[:rows]
+        ops.argmax(logits, None, pairs=pairs, idx_offset=self.model.plan.vocab_start)
+        gathered = self._pairs_all.view(-1)[:ws * rows * 2].view(ws, rows, 2)
+        self.tp.all_gather_flat(gathered, pairs)
+        ops.argmax_merge(gathered, ws, rows, tokens)
 
     def _gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         """Vocab-parallel logits shards -> full rows (a no-op without tensor parallelism)."""
@@ -556,6 +578,9 @@ class LLMEngine:
                           block_table=d[v["bt"]].view(bucket, P), seq_lens=d[v["len"]], rows_per_seq=1,
                           n_splits=self._splits_for(bucket))
         logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
+        if greedy and self._sharded_vocab():
+            self._sharded_argmax(logits, bucket, self._tok_dev[:bucket])
+            return
         logits = self._gather_vocab(logits)
         if greedy:
             ops.argmax(logits, self._tok_dev[:bucket])

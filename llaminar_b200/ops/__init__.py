@@ -145,6 +145,13 @@ def gemm(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, epi: int = EPI
     _count()
 
 
+def gemm_allgather(pw: PackedWeight, m_total: int, out: torch.Tensor, desc: torch.Tensor, *, epi: int = EPI_STORE,
+                   bias: torch.Tensor | None = None, status: torch.Tensor | None = None) -> None:
+    """Column-parallel GEMM with the all-gather of its row-sharded input fused into the launch (see AgFuse in gemm_tc.h)."""
+    ext().gemm_tc_allgather(pw.data, pw.fmt, pw.n, pw.k, m_total, out, epi, bias, status, desc)
+    _count()
+
+
 def dequant(pw: PackedWeight, out: torch.Tensor | None = None) -> torch.Tensor:
     if out is None:
         out = torch.empty(pw.n, pw.k, dtype=torch.bfloat16, device=pw.data.device)
@@ -160,6 +167,12 @@ def gather_rows(pw: PackedWeight, rows: torch.Tensor, out: torch.Tensor) -> None
 
 def rmsnorm(h: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float) -> None:
     ext().rmsnorm(h, w, out, eps)
+    _count()
+
+
+def mtp_concat_norm(emb, hidden, enorm, hnorm, out, eps: float) -> None:
+    """out[row] = [RMSNorm(emb[row]) * enorm | RMSNorm(hidden[row]) * hnorm] in bf16 (input of the NextN eh_proj)."""
+    ext().mtp_concat_norm(emb, hidden, enorm, hnorm, out, eps)
     _count()
 
 
@@ -185,8 +198,16 @@ def swiglu_tiled(gu, out) -> None:
     _count()
 
 
-def argmax(logits: torch.Tensor, tokens: torch.Tensor) -> None:
-    ext().argmax(logits, tokens)
+def argmax(logits: torch.Tensor, tokens: torch.Tensor | None, pairs: torch.Tensor | None = None, idx_offset: int = 0) -> None:
+    """Row argmax (ties -> lower index).  ``pairs`` [rows, 2] int32 receives (value bits, idx_offset + index) for the
+    cross-rank merge of a vocabulary-sharded head."""
+    ext().argmax(logits, tokens, pairs, idx_offset)
+    _count()
+
+
+def argmax_merge(gathered: torch.Tensor, ranks: int, rows: int, tokens: torch.Tensor) -> None:
+    """gathered [ranks, rows, 2] int32 of per-shard (value bits, global index) -> tokens[rows]."""
+    ext().argmax_merge(gathered, ranks, rows, tokens)
     _count()
 
 

@@ -156,6 +156,18 @@ static void rmsnorm(const Tensor& h, const Tensor& w, Tensor out, double eps) {
                                        static_cast<__nv_bfloat16*>(out.data_ptr()), (int)h.size(0), (int)h.size(1), (float)eps, cur_stream()));
 }
 
+static void mtp_concat_norm(const Tensor& emb, const Tensor& hidden, const Tensor& enorm, const Tensor& hnorm, Tensor out, double eps) {
+    check_cuda(emb, "emb"); check_cuda(hidden, "hidden");
+    const c10::cuda::CUDAGuard guard(emb.device());
+    TORCH_CHECK(emb.scalar_type() == torch::kFloat32 && hidden.scalar_type() == torch::kFloat32 && out.scalar_type() == torch::kBFloat16);
+    TORCH_CHECK(emb.is_contiguous() && hidden.is_contiguous() && out.is_contiguous() && emb.sizes() == hidden.sizes());
+    TORCH_CHECK(out.size(0) == emb.size(0) && out.size(1) == 2 * emb.size(1));
+    LLM_CUDA_CHECK(llm::launch_mtp_concat_norm(static_cast<const float*>(emb.data_ptr()), static_cast<const float*>(hidden.data_ptr()),
+                                               static_cast<const float*>(enorm.data_ptr()), static_cast<const float*>(hnorm.data_ptr()),
+                                               static_cast<__nv_bfloat16*>(out.data_ptr()), (int)emb.size(0), (int)emb.size(1), (float)eps,
+                                               cur_stream()));
+}
+
 static void rope_kv(Tensor qkv, Tensor q_out, Tensor kv, const OptTensor& q_norm, const OptTensor& k_norm, const Tensor& positions,
                     const Tensor& seq_ids, const Tensor& block_table, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
                     double theta, double eps) {
@@ -224,11 +236,23 @@ static void add_bf16_to_f32(Tensor h, const Tensor& x) {
                                                (size_t)h.numel(), cur_stream()));
 }
 
-static void argmax(const Tensor& logits, Tensor tokens) {
+static void argmax(const Tensor& logits, const OptTensor& tokens, const OptTensor& pairs, int64_t idx_offset) {
+    check_cuda(logits, "logits");
     const c10::cuda::CUDAGuard guard(logits.device());
-    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && tokens.scalar_type() == torch::kInt32);
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && (tokens.has_value() || pairs.has_value()));
+    if (tokens.has_value()) TORCH_CHECK(tokens->scalar_type() == torch::kInt32 && tokens->numel() >= logits.size(0));
+    if (pairs.has_value()) TORCH_CHECK(pairs->scalar_type() == torch::kInt32 && pairs->numel() >= 2 * logits.size(0) && pairs->is_contiguous());
     LLM_CUDA_CHECK(llm::launch_argmax(static_cast<const float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1),
-                                      (int)logits.stride(0), static_cast<int*>(tokens.data_ptr()), nullptr, nullptr, cur_stream()));
+                                      (int)logits.stride(0), mptr<int>(tokens), mptr<int>(pairs), (int)idx_offset, cur_stream()));
+}
+
+static void argmax_merge(const Tensor& gathered, int64_t ranks, int64_t rows, Tensor tokens) {
+    check_cuda(gathered, "gathered");
+    const c10::cuda::CUDAGuard guard(gathered.device());
+    TORCH_CHECK(gathered.scalar_type() == torch::kInt32 && gathered.is_contiguous() && gathered.numel() >= ranks * rows * 2);
+    TORCH_CHECK(tokens.scalar_type() == torch::kInt32 && tokens.numel() >= rows);
+    LLM_CUDA_CHECK(llm::launch_argmax_merge(static_cast<const int*>(gathered.data_ptr()), (int)ranks, (int)rows,
+                                            static_cast<int*>(tokens.data_ptr()), cur_stream()));
 }
 
 static void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p, const Tensor& seeds,
@@ -319,20 +343,51 @@ static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Te
     LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
 }
 
+// Column-parallel GEMM whose activation rows are all-gathered from the ranks inside the launch (AgFuse in gemm_tc.h).
+// `desc` is a host int64 tensor: [src ptr x8, avail ptr x8, stage ptr, staged ptr, world, rank, rows_per_rank, copy_ctas, epoch, spin_limit].
+static void gemm_tc_allgather(const Tensor& w, int64_t fmt, int64_t n, int64_t k, int64_t m, Tensor out, int64_t epi, const OptTensor& bias,
+                              const OptTensor& status, const Tensor& desc) {
+    check_cuda(w, "w"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(desc.device().is_cpu() && desc.scalar_type() == torch::kInt64 && desc.numel() >= 24);
+    const int64_t* d = desc.data_ptr<int64_t>();
+    llm::GemmTcParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr()); p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.m = (int)m;
+    p.x = nullptr;
+    p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
+    p.epi = (int)epi; p.bias = cptr<float>(bias); p.status = mptr<int>(status);
+    p.ksplit = 1;
+    p.ag_on = 1;
+    for (int i = 0; i < 8; ++i) {
+        p.ag.src[i] = reinterpret_cast<const __nv_bfloat16*>(d[i]);
+        p.ag.avail[i] = reinterpret_cast<unsigned*>(d[8 + i]);
+    }
+    p.ag.stage = reinterpret_cast<__nv_bfloat16*>(d[16]);
+    p.ag.staged = reinterpret_cast<unsigned*>(d[17]);
+    p.ag.world = (int)d[18]; p.ag.rank = (int)d[19]; p.ag.rows_per_rank = (int)d[20]; p.ag.copy_ctas = (int)d[21];
+    p.ag.epoch = (unsigned)d[22]; p.ag.spin_limit = (unsigned)d[23];
+    TORCH_CHECK(m <= (int64_t)p.ag.world * p.ag.rows_per_rank, "more rows than the ranks hold");
+    if (epi == llm::EPI_RESID) TORCH_CHECK(p.out_f32, "residual epilogue updates an fp32 stream");
+    LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemv", &gemv);
     m.def("moe_route", &moe_route);
     m.def("moe_gemv", &moe_gemv);
     m.def("gemm_tc", &gemm_tc);
+    m.def("gemm_tc_allgather", &gemm_tc_allgather);
     m.def("dequant", &dequant);
     m.def("gather_rows", &gather_rows);
     m.def("rmsnorm", &rmsnorm);
+    m.def("mtp_concat_norm", &mtp_concat_norm);
     m.def("rope_kv", &rope_kv);
     m.def("attn_decode", &attn_decode);
     m.def("attn_prefill", &attn_prefill);
     m.def("swiglu_tiled", &swiglu_tiled);
     m.def("add_bf16_to_f32", &add_bf16_to_f32);
     m.def("argmax", &argmax);
+    m.def("argmax_merge", &argmax_merge);
     m.def("sample", &sample);
     m.def("penalties", &penalties);
     m.def("nan_scan", &nan_scan);

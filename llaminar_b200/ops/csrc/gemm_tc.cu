@@ -19,6 +19,7 @@
 
 #include "formats.cuh"
 #include "gemm_tc.h"
+#include "tp_fuse.cuh"
 #include "gemv.h"
 
 namespace llm {
@@ -40,15 +41,17 @@ LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false once the limit is hit or another thread has raised the abort flag.
+// abort_flag[1] holds the count while the TMA lane is inside its own bounded wait for staged rows (fused all-gather).
 LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 256) {
-            if (*abort_flag) return false;
+            if (abort_flag[0]) return false;
+            if (abort_flag[1]) i = 257;
             __nanosleep(64);
         }
     }
-    *abort_flag = 1;
+    abort_flag[0] = 1;
     return false;
 }
 LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -149,6 +152,68 @@ struct RingSink {
     }
 };
 
+LLM_DEVICE unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Copier CTA of the fused all-gather: stages slice `slice` of m-tile `tile_m` (rows of one or two source ranks).
+template <int BM>
+LLM_DEVICE void ag_copy_tile(const GemmTcParams& p, int tile_m, int slice, bool first_cta) {
+    const AgFuse& ag = p.ag;
+    const int tid = threadIdx.x;
+    __shared__ int s_ok;
+    // this rank's rows are complete (stream order): tell every peer once per launch
+    if (first_cta && tid < ag.world) red_release_sys_add(ag.avail[tid] + ag.rank, 1u);
+    const int r0 = tile_m * BM, r1 = min(r0 + BM, p.m);
+    if (tid == 0) {
+        int ok = 1;
+        const int s_first = r0 / ag.rows_per_rank, s_last = (r1 - 1) / ag.rows_per_rank;
+        for (int s = s_first; s <= s_last && ok; ++s) {
+            if (s == ag.rank) continue;
+            const unsigned* f = ag.avail[ag.rank] + s;
+            ok = 0;
+            for (unsigned i = 0; i < ag.spin_limit; ++i) {
+                if ((int)(ld_acquire_sys(f) - (ag.epoch + 1u)) >= 0) { ok = 1; break; }
+                if (i > 4096) __nanosleep(64);
+            }
+        }
+        if (!ok && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (s_ok) {
+        const int row_units = p.k >> 3;                         // 16-byte units per row
+        const int total = (r1 - r0) * row_units;
+        const int stride = ag.copy_ctas * blockDim.x;
+        for (int u = slice * blockDim.x + tid; u < total; u += 4 * stride) {
+            uint4 v[4];
+            int uu[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uu[j] = u + j * stride;
+                if (uu[j] < total) {
+                    const int row = r0 + uu[j] / row_units, c = uu[j] % row_units;
+                    const int s = row / ag.rows_per_rank;
+                    const uint4* src = reinterpret_cast<const uint4*>(ag.src[s] + (size_t)(row - s * ag.rows_per_rank) * p.k) + c;
+                    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src) : "memory");
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (uu[j] < total) {
+                    const int row = r0 + uu[j] / row_units, c = uu[j] % row_units;
+                    reinterpret_cast<uint4*>(ag.stage + (size_t)row * p.k)[c] = v[j];
+                }
+            }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(ag.staged + tile_m, 1u);             // counted even after a timeout so that nobody waits twice
+}
+
 template <int FMT, int BM>
 __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmTcParams p) {
     using C = Cfg<BM>;
@@ -157,12 +222,21 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     __shared__ __align__(8) uint64_t s_empty[C::STAGES];
     __shared__ __align__(8) uint64_t s_accum;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort;
+    __shared__ int s_abort[2];
     __shared__ int s_last;
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    // fused all-gather: the first `copy_ctas` CTAs of every grid row stage that row's m-tile and leave; the m-tiles are
+    // rotated so that the rows this rank owns come first
+    const int n_copy = p.ag_on ? p.ag.copy_ctas : 0;
+    const int tile_m = p.ag_on ? (int)((blockIdx.y + (unsigned)(p.ag.rank * p.ag.rows_per_rank) / BM) % gridDim.y) : (int)blockIdx.y;
+    if ((int)blockIdx.x < n_copy) {
+        if (blockIdx.z == 0) ag_copy_tile<BM>(p, tile_m, blockIdx.x, blockIdx.x == 0 && blockIdx.y == 0);
+        return;
+    }
+    const int tile_n = blockIdx.x - n_copy;
+    const int n_tiles_grid = gridDim.x - n_copy;
     const int k_blocks = p.k / 256;
     const int per = (k_blocks + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * per, kb1 = min(k_blocks, kb0 + per);
@@ -171,7 +245,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     const uint32_t full_bar = smem_u32(s_full), empty_bar = smem_u32(s_empty), accum_bar = smem_u32(&s_accum);
 
     if (tid == 0) {
-        s_abort = 0;
+        s_abort[0] = 0; s_abort[1] = 0;
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar + s * 8, 5); mbar_init(empty_bar + s * 8, 1); }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -188,8 +262,9 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem;
-    volatile int* abort_flag = &s_abort;
+    volatile int* abort_flag = s_abort;
     const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    (void)n_tiles_grid;
     auto trace = [&](int slot, int value) {
         if (p.debug) {
             volatile int* d = p.debug + (size_t)cta_lin * 8;
@@ -224,6 +299,21 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         // ------------------------------ TMA producer (activations) ------------------------------
         if (lane == 0) {
             bool ok = true;
+            if (p.ag_on) {
+                // wait (bounded) until the copier CTAs have staged this m-tile, then order their generic-proxy stores
+                // before this lane's async-proxy (TMA) reads
+                const unsigned target = (unsigned)n_copy;
+                const unsigned* f = p.ag.staged + tile_m;
+                ok = false;
+                abort_flag[1] = 1;                 // the rest of the pipeline is legitimately stalled meanwhile
+                for (unsigned i = 0; i < p.ag.spin_limit; ++i) {
+                    if ((int)(ld_acquire_gpu(f) - target) >= 0) { ok = true; break; }
+                    if (i > 1024) __nanosleep(64);
+                }
+                abort_flag[1] = 0;
+                if (!ok) abort_flag[0] = 1;
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
             for (int it = 0; it < n_it && ok; ++it) {
                 int stage, phase;
                 ring_slot<C::STAGES>(it, stage, phase);
@@ -334,9 +424,9 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         __threadfence();
         __syncthreads();
         if (tid == 0) {
-            const unsigned t = atomicAdd(&p.tickets[tile_m * gridDim.x + tile_n], 1u);
+            const unsigned t = atomicAdd(&p.tickets[tile_m * n_tiles_grid + tile_n], 1u);
             s_last = (t == gridDim.z - 1);
-            if (s_last) p.tickets[tile_m * gridDim.x + tile_n] = 0u;
+            if (s_last) p.tickets[tile_m * n_tiles_grid + tile_n] = 0u;
         }
         __syncthreads();
         if (s_last && warp < 8) {
@@ -399,11 +489,12 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;
+    const __nv_bfloat16* x_src = p.ag_on ? p.ag.stage : p.x;      // fused all-gather: the tensor map covers the local staging copy only
     const cuuint64_t dims[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
     const cuuint64_t strides[1] = {(cuuint64_t)p.k * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)BM};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.x), dims, strides, box, estr,
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(x_src), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -413,7 +504,11 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    dim3 grid((p.n + 127) / 128, (p.m + BM - 1) / BM, ksplit);
+    dim3 grid((p.n + 127) / 128 + (p.ag_on ? p.ag.copy_ctas : 0), (p.m + BM - 1) / BM, ksplit);
+    if (p.ag_on) {                                   // per-m-tile counters of staged slices start from zero in every launch
+        cudaError_t e = cudaMemsetAsync(p.ag.staged, 0, sizeof(unsigned) * grid.y, st);
+        if (e != cudaSuccess) return e;
+    }
     gemm_tc_kernel<FMT, BM><<<grid, 320, C::SMEM_BYTES, st>>>(tmap, p);
     return cudaGetLastError();
 }
@@ -455,9 +550,14 @@ static cudaError_t launch_fmt(const GemmTcParams& p, int bm, int ks, cudaStream_
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
     if (p.m <= 0) return cudaSuccess;
-    if (p.k % 256 || (reinterpret_cast<uintptr_t>(p.x) & 15)) return cudaErrorInvalidValue;
+    const void* xa = p.ag_on ? static_cast<const void*>(p.ag.stage) : static_cast<const void*>(p.x);
+    if (p.k % 256 || (reinterpret_cast<uintptr_t>(xa) & 15)) return cudaErrorInvalidValue;
     int bm, ks;
     gemm_tc_plan(p.m, p.n, p.k, p.ksplit, &bm, &ks);
+    if (p.ag_on) {
+        if (p.m <= 32) bm = 64;                    // the fused all-gather lives in the large-tile kernel
+        if (p.ag.world < 1 || p.ag.world > 8 || p.ag.copy_ctas < 1 || p.ag.rows_per_rank < 1) return cudaErrorInvalidValue;
+    }
     if (ks > 1 && (!p.accum || !p.tickets)) ks = 1;
     if (bm == 32) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
     switch (p.fmt) {

@@ -8,6 +8,22 @@ namespace llm {
 
 struct TpFuse;   // tp_fuse.cuh
 
+// All-gather fused into the activation path of the large-tile kernel (column-parallel QKV / gate|up on row-sharded
+// input).  Rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank) of x.  Copier CTAs of the same launch pull the
+// peers' rows over NVLink into a local staging copy with plain 16-byte loads, one m-tile at a time, while the other
+// CTAs already multiply the tiles that have landed; the tensor map reads only the local copy, so no TMA touches peer
+// memory.  m-tiles are visited starting with this rank's own rows.
+struct AgFuse {
+    const __nv_bfloat16* src[8];   // every rank's own-row buffer of this call's parity (symmetric memory; src[rank] is local)
+    unsigned* avail[8];            // per rank: [8] counters; avail[r][s] = calls whose rows rank s has published to rank r
+    __nv_bfloat16* stage;          // local [m, k] gathered copy that the tensor map reads
+    unsigned* staged;              // local [m_tiles] counters of finished copy slices (zeroed by the launcher)
+    int world, rank, rows_per_rank;
+    int copy_ctas;                 // copier CTAs per m-tile
+    unsigned epoch;                // earlier calls on this arena (identical on all ranks)
+    unsigned spin_limit;
+};
+
 struct GemmTcParams {
     const uint8_t* w;          // weight chunks [n_tiles][k_blocks][chunk]
     int fmt;
@@ -26,6 +42,8 @@ struct GemmTcParams {
     int* debug;                // optional trace buffer (progress markers / ns timestamps written by the kernels); nullptr in production
     const TpFuse* tp;          // EPI_RESID in the small-batch kernel: fused cross-rank all-reduce of each tile (nullptr: off)
     int flags;                 // bit 1 (set by the launcher): stream-K work split in the small-batch kernel
+    int ag_on;                 // large-tile kernel: x rows are gathered from the ranks of `ag` inside the launch
+    AgFuse ag;
 };
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);

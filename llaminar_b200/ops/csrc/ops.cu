@@ -47,6 +47,44 @@ cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, i
 }
 
 // ------------------------------------------------------------------------------------------------
+// Multi-token-prediction draft prologue: out[row] = [RMSNorm(embedding[row]; enorm) | RMSNorm(hidden[row]; hnorm)] as bf16,
+// the input of the NextN layer's eh_proj (reference: src/v2/kernels/cuda/ops/CUDARowSelectKernels.cu:74 mtpConcatFP32Kernel
+// after two RMSNorm stages, src/v2/models/qwen35/Qwen35Graph.cpp:403-507).  grid = (rows, 2): y selects the half.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) mtp_concat_norm_kernel(const float* __restrict__ emb, const float* __restrict__ hidden,
+                                                              const float* __restrict__ enorm, const float* __restrict__ hnorm,
+                                                              __nv_bfloat16* __restrict__ out, int d, float eps) {
+    __shared__ float s_part[8];
+    const int row = blockIdx.x, half = blockIdx.y, tid = threadIdx.x;
+    const float4* x4 = reinterpret_cast<const float4*>((half ? hidden : emb) + (size_t)row * d);
+    const float4* w4 = reinterpret_cast<const float4*>(half ? hnorm : enorm);
+    float ss = 0.f;
+    for (int i = tid; i < d / 4; i += 256) {
+        const float4 v = x4[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    const float r = rsqrtf(tot / d + eps);
+    uint2* o2 = reinterpret_cast<uint2*>(out + (size_t)row * 2 * d + (size_t)half * d);
+    for (int i = tid; i < d / 4; i += 256) {
+        const float4 v = x4[i], g = w4[i];
+        o2[i] = make_uint2(pack_bf16(v.x * r * g.x, v.y * r * g.y), pack_bf16(v.z * r * g.z, v.w * r * g.w));
+    }
+}
+cudaError_t launch_mtp_concat_norm(const float* emb, const float* hidden, const float* enorm, const float* hnorm,
+                                   __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    if (d % 4) return cudaErrorInvalidValue;
+    mtp_concat_norm_kernel<<<dim3(rows, 2), 256, 0, st>>>(emb, hidden, enorm, hnorm, out, d, eps);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
 // per-head QK RMSNorm + split-half RoPE + paged KV append: one warp per (token, head)
 // ------------------------------------------------------------------------------------------------
 template <int D>
@@ -176,7 +214,8 @@ LLM_DEVICE float uniform01(uint64_t seed, uint64_t ctr) {
     return (splitmix64(seed ^ splitmix64(ctr)) >> 40) * (1.0f / 16777216.0f);
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int vocab, int stride, int* __restrict__ tokens) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int vocab, int stride, int* __restrict__ tokens,
+                                                      int* __restrict__ pairs, int idx_offset) {
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const float* row = logits + (size_t)blockIdx.x * stride;
@@ -202,12 +241,39 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (threadIdx.x == 0) tokens[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+        if (threadIdx.x == 0) {
+            bi = bi == 0x7fffffff ? 0 : bi;
+            if (tokens) tokens[blockIdx.x] = bi;
+            if (pairs) {                       // (value bits, global index) for the cross-rank merge of a vocabulary-sharded head
+                pairs[2 * blockIdx.x] = __float_as_int(best);
+                pairs[2 * blockIdx.x + 1] = bi + idx_offset;
+            }
+        }
     }
 }
-cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, float*, int*, cudaStream_t st) {
+cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, int* pairs, int idx_offset, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, vocab, stride, tokens);
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, vocab, stride, tokens, pairs, idx_offset);
+    return cudaGetLastError();
+}
+
+// Merge of per-shard argmax candidates: gathered[rank][row] = (value bits, global index); larger value wins, ties go to
+// the lower index (the result equals the argmax over the full row).
+__global__ void argmax_merge_kernel(const int* __restrict__ gathered, int ranks, int rows, int* __restrict__ tokens) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < ranks; ++k) {
+        const float v = __int_as_float(gathered[((size_t)k * rows + r) * 2]);
+        const int i = gathered[((size_t)k * rows + r) * 2 + 1];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    tokens[r] = bi == 0x7fffffff ? 0 : bi;
+}
+cudaError_t launch_argmax_merge(const int* gathered, int ranks, int rows, int* tokens, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, st>>>(gathered, ranks, rows, tokens);
     return cudaGetLastError();
 }
 

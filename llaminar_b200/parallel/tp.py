@@ -97,6 +97,13 @@ class TPContext:
             return out.permute(1, 0, 2).reshape(rows, self.size * wmax)
         return torch.cat([out[r, :, :w] for r, w in enumerate(widths)], dim=1)
 
+    def all_gather_flat(self, out: torch.Tensor, inp: torch.Tensor) -> torch.Tensor:
+        """out[rank] = inp for every rank (small fixed-size records, e.g. per-shard argmax candidates)."""
+        if self.order_check is not None:
+            self.order_check.record("all_gather_flat", inp)
+        dist.all_gather_into_tensor(out, inp, group=self.group)
+        return out
+
     def broadcast_object(self, obj, src: int = 0):
         box = [obj]
         dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, src) if self.group is not dist.group.WORLD else src,

@@ -112,3 +112,41 @@ def test_engine_moe_expert_parallel_fused_combine_2gpu():
     assert fused[0][1]["fused_calls"] > base[0][1]["fused_calls"]
     agree = sum(a == b for fo, bo in zip(fused[0][0], base[0][0]) for a, b in zip(fo, bo))
     assert agree >= 0.85 * 48
+
+
+def _allgather_gemm(rank, world, qt_name, m_total, n, k):
+    """Column-parallel GEMM on row-sharded input: every rank must get gather(x) @ W_shard^T for all rows."""
+    import torch.distributed as dist
+    from llaminar_b200 import ops
+    from llaminar_b200.gguf import GGMLType, dequantize, quantize
+    from llaminar_b200.parallel.symm import AllGatherArena
+    dev = torch.device("cuda", rank)
+    qt = GGMLType[qt_name]
+    rows_per_rank = (m_total + world - 1) // world
+    arena = AllGatherArena(dist.group.WORLD, dev, rows_cap=rows_per_rank, k_cap=k, copy_ctas=4)
+    g = torch.Generator(device=dev).manual_seed(11)                  # same seed: every rank can build the reference
+    x_full = (torch.randn(m_total, k, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank)         # each rank owns different weight columns
+    w = torch.randn(n, k, device=dev, generator=g2) * 0.05
+    raw = quantize(w, qt)
+    pw = ops.pack_matrix(raw, qt, n, k)
+    wq = dequantize(raw, qt, (n, k))
+    errs = []
+    for call in range(4):                                            # parities alternate, epochs advance
+        xs = (x_full.float() * (1.0 + 0.25 * call)).to(torch.bfloat16)
+        r0, r1 = rank * rows_per_rank, min(m_total, (rank + 1) * rows_per_rank)
+        arena.own_rows(r1 - r0, k).copy_(xs[r0:r1])
+        out = torch.zeros(m_total, n, device=dev)
+        arena.gemm(pw, m_total, rows_per_rank, out)
+        torch.cuda.synchronize()
+        arena.check_status()
+        ref = xs.float() @ wq.T
+        errs.append(((out - ref).norm() / ref.norm()).item())
+    return max(errs)
+
+
+@pytest.mark.parametrize("qt_name,m_total,n,k", [("Q4_K", 512, 640, 1024), ("Q6_K", 333, 256, 512), ("Q4_K", 2048, 1280, 2048)])
+def test_allgather_gemm_2gpu(qt_name, m_total, n, k):
+    _need(2)
+    errs = run_ranks_gpu(_allgather_gemm, 2, qt_name, m_total, n, k)
+    assert max(errs) < 2e-2
