@@ -98,7 +98,7 @@ def reference_arm(args):
     # build needs OpenMPI, libnuma and network FetchContent of two libraries; none exist in this image.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a CMake/C++ binary needing OpenMPI + libnuma + network FetchContent; "
-                      "pip install of /root/reference fails: no setup.py or pyproject.toml"}))
+                      "pip install of the reference tree fails: no setup.py or pyproject.toml"}))
     return 0
 
 

@@ -158,60 +158,71 @@ LLM_DEVICE unsigned ld_acquire_gpu(const unsigned* p) {
     return v;
 }
 
-// Copier CTA of the fused all-gather: stages slice `slice` of m-tile `tile_m` (rows of one or two source ranks).
+// Copier CTA of the fused all-gather.  The `copy_ctas` copiers are the first CTAs of the grid and live for the whole
+// gather: each walks the m-tiles in the order the GEMM CTAs will need them (own rows first) and stages its slice of every
+// tile from the owners' row buffers (symmetric memory; peers over NVLink) into the local staging buffer, bumping the
+// tile's counter after each slice.  They never wait on the GEMM CTAs, so they cannot be starved by them.
 template <int BM>
-LLM_DEVICE void ag_copy_tile(const GemmTcParams& p, int tile_m, int slice, bool first_cta) {
+LLM_DEVICE void ag_copier(const GemmTcParams& p, int slice, int m_tiles) {
     const AgFuse& ag = p.ag;
     const int tid = threadIdx.x;
     __shared__ int s_ok;
     // this rank's rows are complete (stream order): tell every peer once per launch
-    if (first_cta && tid < ag.world) red_release_sys_add(ag.avail[tid] + ag.rank, 1u);
-    const int r0 = tile_m * BM, r1 = min(r0 + BM, p.m);
-    if (tid == 0) {
-        int ok = 1;
+    if (slice == 0 && tid < ag.world) red_release_sys_add(ag.avail[tid] + ag.rank, 1u);
+    const int rot = (ag.rank * ag.rows_per_rank) / BM;
+    const int row_units = p.k >> 3;                             // 16-byte units per row
+    const int stride = ag.copy_ctas * blockDim.x;
+    unsigned seen = 1u << ag.rank;                              // sources whose rows are known to be published
+    for (int i = 0; i < m_tiles; ++i) {
+        const int tile_m = (rot + i) % m_tiles;
+        const int r0 = tile_m * BM, r1 = min(r0 + BM, p.m);
         const int s_first = r0 / ag.rows_per_rank, s_last = (r1 - 1) / ag.rows_per_rank;
-        for (int s = s_first; s <= s_last && ok; ++s) {
-            if (s == ag.rank) continue;
-            const unsigned* f = ag.avail[ag.rank] + s;
-            ok = 0;
-            for (unsigned i = 0; i < ag.spin_limit; ++i) {
-                if ((int)(ld_acquire_sys(f) - (ag.epoch + 1u)) >= 0) { ok = 1; break; }
-                if (i > 4096) __nanosleep(64);
+        unsigned need = 0;
+        for (int s = s_first; s <= s_last; ++s) need |= 1u << s;
+        if (need & ~seen) {
+            if (tid == 0) {
+                int ok = 1;
+                for (int s = s_first; s <= s_last && ok; ++s) {
+                    if (seen & (1u << s)) continue;
+                    const unsigned* f = ag.avail[ag.rank] + s;
+                    ok = 0;
+                    for (unsigned it = 0; it < ag.spin_limit; ++it) {
+                        if ((int)(ld_acquire_sys(f) - (ag.epoch + 1u)) >= 0) { ok = 1; break; }
+                        if (it > 4096) __nanosleep(64);
+                    }
+                }
+                if (!ok && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
+                s_ok = ok;
             }
+            __syncthreads();
+            if (s_ok) seen |= need;
         }
-        if (!ok && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
-        s_ok = ok;
-    }
-    __syncthreads();
-    if (s_ok) {
-        const int row_units = p.k >> 3;                         // 16-byte units per row
-        const int total = (r1 - r0) * row_units;
-        const int stride = ag.copy_ctas * blockDim.x;
-        for (int u = slice * blockDim.x + tid; u < total; u += 4 * stride) {
-            uint4 v[4];
-            int uu[4];
+        if ((need & ~seen) == 0) {
+            constexpr int INFLIGHT = 8;                         // 16-byte loads each thread keeps in flight
+            const int total = (r1 - r0) * row_units;
+            for (int u = slice * blockDim.x + tid; u < total; u += INFLIGHT * stride) {
+                uint4 v[INFLIGHT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uu[j] = u + j * stride;
-                if (uu[j] < total) {
-                    const int row = r0 + uu[j] / row_units, c = uu[j] % row_units;
-                    const int s = row / ag.rows_per_rank;
-                    const uint4* src = reinterpret_cast<const uint4*>(ag.src[s] + (size_t)(row - s * ag.rows_per_rank) * p.k) + c;
-                    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src) : "memory");
+                for (int j = 0; j < INFLIGHT; ++j) {
+                    const int uu = u + j * stride;
+                    if (uu < total) {
+                        const int row = r0 + uu / row_units;
+                        const int sr = row / ag.rows_per_rank;
+                        const uint4* src = reinterpret_cast<const uint4*>(ag.src[sr] + (size_t)(row - sr * ag.rows_per_rank) * p.k) + uu % row_units;
+                        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src) : "memory");
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < INFLIGHT; ++j) {
+                    const int uu = u + j * stride;
+                    if (uu < total) reinterpret_cast<uint4*>(ag.stage + (size_t)(r0 + uu / row_units) * p.k)[uu % row_units] = v[j];
                 }
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (uu[j] < total) {
-                    const int row = r0 + uu[j] / row_units, c = uu[j] % row_units;
-                    reinterpret_cast<uint4*>(ag.stage + (size_t)row * p.k)[c] = v[j];
-                }
-            }
         }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(ag.staged + tile_m, 1u);         // counted even after a timeout so that nobody waits twice
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) atomicAdd(ag.staged + tile_m, 1u);             // counted even after a timeout so that nobody waits twice
 }
 
 template <int FMT, int BM>
@@ -227,16 +238,21 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // fused all-gather: the first `copy_ctas` CTAs of every grid row stage that row's m-tile and leave; the m-tiles are
-    // rotated so that the rows this rank owns come first
-    const int n_copy = p.ag_on ? p.ag.copy_ctas : 0;
-    const int tile_m = p.ag_on ? (int)((blockIdx.y + (unsigned)(p.ag.rank * p.ag.rows_per_rank) / BM) % gridDim.y) : (int)blockIdx.y;
-    if ((int)blockIdx.x < n_copy) {
-        if (blockIdx.z == 0) ag_copy_tile<BM>(p, tile_m, blockIdx.x, blockIdx.x == 0 && blockIdx.y == 0);
-        return;
+    // fused all-gather: a linear grid whose first `copy_ctas` CTAs stage the activation rows (ag_copier) and whose other
+    // CTAs take the output tiles n-fastest, with the m-tiles rotated so that the rows this rank owns come first
+    int tile_n = blockIdx.x, tile_m = blockIdx.y, n_tiles_grid = gridDim.x;
+    if (p.ag_on) {
+        const int n_copy = p.ag.copy_ctas;
+        const int m_tiles = (p.m + BM - 1) / BM;
+        n_tiles_grid = (p.n + 127) / 128;
+        if ((int)blockIdx.x < n_copy) {
+            if (blockIdx.z == 0) ag_copier<BM>(p, blockIdx.x, m_tiles);
+            return;
+        }
+        const int lin = blockIdx.x - n_copy;
+        tile_n = lin % n_tiles_grid;
+        tile_m = (lin / n_tiles_grid + (p.ag.rank * p.ag.rows_per_rank) / BM) % m_tiles;
     }
-    const int tile_n = blockIdx.x - n_copy;
-    const int n_tiles_grid = gridDim.x - n_copy;
     const int k_blocks = p.k / 256;
     const int per = (k_blocks + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * per, kb1 = min(k_blocks, kb0 + per);
@@ -264,7 +280,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = s_abort;
     const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    (void)n_tiles_grid;
+
     auto trace = [&](int slot, int value) {
         if (p.debug) {
             volatile int* d = p.debug + (size_t)cta_lin * 8;
@@ -302,7 +318,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
             if (p.ag_on) {
                 // wait (bounded) until the copier CTAs have staged this m-tile, then order their generic-proxy stores
                 // before this lane's async-proxy (TMA) reads
-                const unsigned target = (unsigned)n_copy;
+                const unsigned target = (unsigned)p.ag.copy_ctas;
                 const unsigned* f = p.ag.staged + tile_m;
                 ok = false;
                 abort_flag[1] = 1;                 // the rest of the pipeline is legitimately stalled meanwhile
@@ -504,10 +520,11 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    dim3 grid((p.n + 127) / 128 + (p.ag_on ? p.ag.copy_ctas : 0), (p.m + BM - 1) / BM, ksplit);
+    dim3 grid((p.n + 127) / 128, (p.m + BM - 1) / BM, ksplit);
     if (p.ag_on) {                                   // per-m-tile counters of staged slices start from zero in every launch
         cudaError_t e = cudaMemsetAsync(p.ag.staged, 0, sizeof(unsigned) * grid.y, st);
         if (e != cudaSuccess) return e;
+        grid = dim3(grid.x * grid.y + p.ag.copy_ctas, 1, ksplit);
     }
     gemm_tc_kernel<FMT, BM><<<grid, 320, C::SMEM_BYTES, st>>>(tmap, p);
     return cudaGetLastError();

@@ -9,17 +9,18 @@ namespace llm {
 struct TpFuse;   // tp_fuse.cuh
 
 // All-gather fused into the activation path of the large-tile kernel (column-parallel QKV / gate|up on row-sharded
-// input).  Rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank) of x.  Copier CTAs of the same launch pull the
-// peers' rows over NVLink into a local staging copy with plain 16-byte loads, one m-tile at a time, while the other
-// CTAs already multiply the tiles that have landed; the tensor map reads only the local copy, so no TMA touches peer
-// memory.  m-tiles are visited starting with this rank's own rows.
+// input).  Rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank) of x and keeps them in a symmetric-memory
+// buffer.  A few copier CTAs at the head of the same launch pull all rows from their owners (peers over NVLink) with
+// plain 16-byte loads into a local staging buffer, m-tile by m-tile in the order the other CTAs will need them (own
+// rows first), while those CTAs already multiply the tiles that have landed; the tensor map reads only the local
+// buffer, so no TMA touches peer memory.
 struct AgFuse {
     const __nv_bfloat16* src[8];   // every rank's own-row buffer of this call's parity (symmetric memory; src[rank] is local)
     unsigned* avail[8];            // per rank: [8] counters; avail[r][s] = calls whose rows rank s has published to rank r
-    __nv_bfloat16* stage;          // local [m, k] gathered copy that the tensor map reads
+    __nv_bfloat16* stage;          // local [m, k] staging buffer that the tensor map reads
     unsigned* staged;              // local [m_tiles] counters of finished copy slices (zeroed by the launcher)
     int world, rank, rows_per_rank;
-    int copy_ctas;                 // copier CTAs per m-tile
+    int copy_ctas;                 // copier CTAs at the head of the grid
     unsigned epoch;                // earlier calls on this arena (identical on all ranks)
     unsigned spin_limit;
 };

@@ -25,6 +25,11 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--hbm-gbs", type=float, default=6455.6)
     ap.add_argument("--nvlink-gbs", type=float, default=770.0)
+    ap.add_argument("--bf16-tflops", type=float, default=1428.7)
+    ap.add_argument("--mode", default="rowpar", choices=["rowpar", "allgather"],
+                    help="rowpar: GEMM -> all-reduce (+ residual); allgather: all-gather -> column-parallel GEMM")
+    ap.add_argument("--ag-rows", type=int, nargs="+", default=[2048, 8192], help="allgather mode: total rows over all ranks")
+    ap.add_argument("--copy-ctas", type=int, default=8)
     args = ap.parse_args()
     from .. import ops
     from ..gguf import GGMLType
@@ -60,6 +65,59 @@ def main() -> int:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
+    if args.mode == "allgather":
+        from .symm import AllGatherArena
+        for shp in args.shape:
+            n_full, k = (int(v) for v in shp.split("x"))
+            n = n_full // world                                      # column-parallel: this rank's output columns
+            wbytes = n * k // elems * bpb
+            g = torch.Generator(device=dev).manual_seed(1 + rank)
+            raw = torch.randint(0, 256, (wbytes,), dtype=torch.uint8, device=dev, generator=g)
+            raw.view(torch.int16).bitwise_and_(0x3FFF)
+            pw = ops.pack_matrix(raw, qt, n, k)
+            for m_total in args.ag_rows:
+                rpr = (m_total + world - 1) // world
+                arena = AllGatherArena(dist.group.WORLD, dev, rows_cap=rpr, k_cap=k, copy_ctas=args.copy_ctas)
+                x_own = (torch.randn(rpr, k, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+                x_all = torch.empty(world * rpr, k, dtype=torch.bfloat16, device=dev)
+                out = torch.empty(m_total, n, dtype=torch.bfloat16, device=dev)
+
+                def nccl(i):
+                    dist.all_gather_into_tensor(x_all, x_own)
+                    ops.gemm(pw, x_all[:m_total], out, scratch=sc)
+
+                def gemm_only(i):
+                    ops.gemm(pw, x_all[:m_total], out, scratch=sc)
+
+                def fused(i):
+                    arena.own_rows(rpr, k).copy_(x_own)              # stands for the producer writing its rows in place
+                    arena.gemm(pw, m_total, rpr, out)
+
+                def copy_only(i):
+                    arena.own_rows(rpr, k).copy_(x_own)
+
+                def gemm_symm(i):                                     # same GEMM, activations read from symmetric memory
+                    ops.gemm(pw, x_symm, out, scratch=sc)
+
+                arena.own_rows(rpr, k).copy_(x_own)
+                arena.gemm(pw, m_total, rpr, out)
+                x_symm = arena.gathered(m_total, k)
+                rec = {"mode": "allgather", "shape": shp, "n_local": n, "rows_total": m_total, "fmt": args.fmt, "world": world,
+                       "gemm_only_us": round(timed(gemm_only, args.iters), 1), "gemm_on_symmetric_memory_us": round(timed(gemm_symm, args.iters), 1),
+                       "allgather_then_gemm_us": round(timed(nccl, args.iters), 1),
+                       "fused_us": round(timed(fused, args.iters) - timed(copy_only, args.iters), 1)}
+                arena.check_status()
+                flops = 2.0 * m_total * n * k
+                link_bytes = (world - 1) * rpr * k * 2               # rows this rank must pull from its peers
+                roof = max(flops / (args.bf16_tflops * 1e6), link_bytes / (args.nvlink_gbs * 1e3), wbytes / (args.hbm_gbs * 1e3))
+                rec.update(roofline_us=round(roof, 1), fused_frac_of_roofline=round(roof / rec["fused_us"], 3),
+                           speedup_vs_nccl=round(rec["allgather_then_gemm_us"] / rec["fused_us"], 2),
+                           tflops_fused=round(flops / rec["fused_us"] / 1e6, 1))
+                if rank == 0:
+                    print(json.dumps(rec), flush=True)
+                del arena
+        dist.destroy_process_group()
+        return 0
     for shp in args.shape:
         n, k_full = (int(v) for v in shp.split("x"))
         k = k_full // world
@@ -71,8 +129,7 @@ def main() -> int:
         # clear the exponent's top bit of every 16-bit word so all scales stay finite
         pws = []
         for r in raws:
-            r16 = r.view(torch.int16)
-            r16 &= 0x3FFF
+            r.view(torch.int16).bitwise_and_(0x3FFF)
             pws.append(ops.pack_matrix(r, qt, n, k))
         for rows in args.rows:
             x = (torch.randn(rows, k, device=dev, generator=g) * 0.1).to(torch.bfloat16)

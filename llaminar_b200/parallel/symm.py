@@ -80,15 +80,17 @@ class SymmetricArena:
 class AllGatherArena:
     """Buffers of the fused all-gather -> GEMM (`ops.gemm_allgather`).
 
-    Symmetric (peer-visible) per rank: two parities of this rank's own activation rows ``[rows_cap, k_cap]`` bf16 and eight
-    arrival counters.  Local: the gathered staging copy ``[world * rows_cap, k_cap]`` and one counter per m-tile.  A call
-    uses parity ``epoch & 1``; a rank can run at most one call ahead of its peers (it needs their rows to finish a call),
-    so two parities suffice.  The epoch is a host counter passed as a kernel argument, so these launches are not meant
-    for CUDA-graph capture (prefill runs eagerly).  The reference has no counterpart: its column-parallel projections
-    read a replicated input (reference: src/v2/compute_stages/stages/FusedQKVGEMMStage.cpp).
+    Symmetric (peer-visible) per rank: eight arrival counters and two parities of the rows this rank owns,
+    ``[rows_cap, k_cap]`` bf16; the producer of the activations writes there (`own_rows`).  Local, ordinary device memory:
+    the staging buffer ``x[m, k]`` that the kernel's copier CTAs fill from all owners and that the GEMM's tensor map
+    reads (TMA reads of symmetric-memory mappings measured ~10 % slower, so the operand is staged in ordinary memory).
+    A call uses parity ``epoch & 1``; a rank can run at most one call ahead of its peers (it needs their rows to finish
+    a call), so two parities suffice.  The epoch is a host counter passed as a kernel argument, so these launches are
+    not meant for CUDA-graph capture (prefill runs eagerly).  The reference has no counterpart: its column-parallel
+    projections read a replicated input (reference: src/v2/compute_stages/stages/FusedQKVGEMMStage.cpp).
     """
 
-    def __init__(self, group, device, rows_cap: int, k_cap: int, copy_ctas: int = 8, spin_limit: int | None = None):
+    def __init__(self, group, device, rows_cap: int, k_cap: int, copy_ctas: int = 16, spin_limit: int | None = None):
         import torch.distributed._symmetric_memory as symm_mem
         from ..utils.env import debug_env
         self.group, self.device = group, torch.device(device)
@@ -102,7 +104,7 @@ class AllGatherArena:
         torch.cuda.synchronize(self.device)
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.stage = torch.zeros(self.size * rows_cap, k_cap, dtype=torch.bfloat16, device=self.device)
+        self.stage = torch.zeros(self.size * rows_cap * k_cap, dtype=torch.bfloat16, device=self.device)
         self.staged = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.epoch = 0
@@ -114,15 +116,19 @@ class AllGatherArena:
         off = self.flag_bytes + (self.epoch & 1) * self.row_bytes
         return self.buf[off:off + rows * k * 2].view(torch.bfloat16).view(rows, k)
 
+    def gathered(self, m_total: int, k: int) -> torch.Tensor:
+        """The staging buffer as [m_total, k] (all rows are present once a call has run)."""
+        return self.stage[:m_total * k].view(m_total, k)
+
     def gemm(self, pw, m_total: int, rows_per_rank: int, out: torch.Tensor, *, epi: int = 0, bias=None) -> None:
-        """out[m_total, n] = gather(own rows of every rank)[m_total, k] @ W^T; rank r holds rows [r * rows_per_rank, ...)."""
+        """out[m_total, n] = x[m_total, k] @ W^T where rank r owns (and has written) rows [r * rows_per_rank, ...) of x."""
         from .. import ops
+        assert pw.k <= self.k_cap and m_total <= self.size * rows_per_rank and rows_per_rank <= self.rows_cap
         par = self.epoch & 1
         src = [p + self.flag_bytes + par * self.row_bytes for p in self.ptrs] + [0] * (TP_MAX_RANKS - self.size)
         avail = list(self.ptrs) + [0] * (TP_MAX_RANKS - self.size)
         desc = torch.tensor(src + avail + [self.stage.data_ptr(), self.staged.data_ptr(), self.size, self.rank, rows_per_rank,
                                           self.copy_ctas, self.epoch, self.spin_limit], dtype=torch.int64)
-        assert pw.k <= self.k_cap and m_total <= self.size * self.rows_cap      # staging is used as a flat [m_total, k] buffer
         ops.gemm_allgather(pw, m_total, out, desc, epi=epi, bias=bias, status=self.status)
         self.epoch += 1
 

@@ -1,0 +1,105 @@
+"""GGUF container and block codecs on CPU: round trips, block geometry, agreement with the `gguf` Python package
+(ggml's reference dequantisers) when it is importable, and the checkpoint round trip of a whole model."""
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from llaminar_b200.gguf import GGMLType, GGUFFile, GGUFWriter, dequantize, quantize
+from llaminar_b200.gguf.constants import BLOCK_GEOMETRY
+from llaminar_b200.gguf.reader import GGUFError
+
+QUANT_TYPES = ["Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "IQ3_S"]
+DEQUANT_ONLY = ["Q4_1", "Q5_0", "Q5_1", "IQ4_NL", "Q2_K", "Q3_K", "IQ4_XS", "IQ3_XXS"]
+EXPECTED_BLOCKS = {"Q8_0": (32, 34), "Q4_0": (32, 18), "Q4_1": (32, 20), "Q5_0": (32, 22), "Q5_1": (32, 24), "IQ4_NL": (32, 18),
+                   "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210), "Q3_K": (256, 110), "Q2_K": (256, 84),
+                   "IQ4_XS": (256, 136), "IQ3_S": (256, 110), "IQ3_XXS": (256, 98)}
+
+
+def test_block_geometry_matches_ggml():
+    for name, geo in EXPECTED_BLOCKS.items():
+        assert BLOCK_GEOMETRY[GGMLType[name]] == geo, name
+
+
+@pytest.mark.parametrize("name", QUANT_TYPES)
+def test_quantize_dequantize_error_is_bounded(name):
+    qt = GGMLType[name]
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(8, 512, generator=g) * 0.02
+    raw = quantize(x, qt)
+    e, b = BLOCK_GEOMETRY[qt]
+    assert raw.numel() == x.numel() // e * b and raw.dtype == torch.uint8
+    y = dequantize(raw, qt, tuple(x.shape))
+    rel = ((y - x).norm() / x.norm()).item()
+    assert rel < {"Q8_0": 0.01, "Q6_K": 0.02, "Q5_K": 0.04, "Q4_K": 0.08, "Q4_0": 0.12, "IQ3_S": 0.2}[name]
+    assert torch.equal(quantize(y, qt), quantize(y, qt))           # deterministic
+
+
+@pytest.mark.parametrize("name", QUANT_TYPES + DEQUANT_ONLY)
+def test_dequantize_agrees_with_ggml_reference(name):
+    gq = pytest.importorskip("gguf.quants")
+    import gguf
+    qt = GGMLType[name]
+    gt = getattr(gguf.GGMLQuantizationType, name)
+    e, b = BLOCK_GEOMETRY[qt]
+    rng = np.random.default_rng(3)
+    raw = rng.integers(0, 256, size=(4, 512 // e * b), dtype=np.uint8)
+    # keep every fp16 scale field finite: clear the top exponent bit of all 16-bit words
+    raw16 = raw.view(np.uint16)
+    raw16 &= 0x3FFF
+    try:
+        ref = gq.dequantize(raw, gt)
+    except (NotImplementedError, KeyError):
+        pytest.skip(f"the gguf package has no reference dequantiser for {name}")
+    ours = dequantize(torch.from_numpy(raw.reshape(-1).copy()), qt, (4, 512)).numpy()
+    np.testing.assert_allclose(ours, ref.reshape(4, 512), rtol=1e-6, atol=1e-7)
+
+
+def test_container_round_trip_and_value_types(tmp_path):
+    w = GGUFWriter()
+    w.add("general.architecture", "qwen3")
+    w.add("qwen3.block_count", 2)
+    w.add("qwen3.rope.freq_base", 1e6)
+    w.add("flag", True)
+    w.add("tokenizer.ggml.tokens", ["a", "b", "çé"])
+    w.add("ints", [1, 2, 3])
+    x = torch.arange(2 * 256, dtype=torch.float32).view(2, 256) / 100
+    w.add_tensor("blk.0.attn_q.weight", x, GGMLType.Q8_0)
+    w.add_tensor("output_norm.weight", torch.ones(256), GGMLType.F32)
+    path = tmp_path / "m.gguf"
+    w.write(str(path))
+    data = path.read_bytes()
+    assert data[:4] == b"GGUF" and struct.unpack("<I", data[4:8])[0] == 3
+    f = GGUFFile(str(path))
+    assert f.architecture == "qwen3" and f.get("qwen3.block_count") == 2 and f.get("flag") is True
+    assert f.get("tokenizer.ggml.tokens") == ["a", "b", "çé"] and f.get("ints") == [1, 2, 3]
+    t = f["blk.0.attn_q.weight"]
+    assert tuple(t.shape) == (2, 256) and t.qtype == GGMLType.Q8_0           # dims are stored reversed on disk
+    assert torch.allclose(t.to_float(), x, atol=0.03)
+    assert (t.offset % 32) == 0                                               # data section alignment
+    f.close()
+
+
+def test_reader_rejects_bad_files(tmp_path):
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(b"NOPE" + b"\0" * 64)
+    with pytest.raises(GGUFError):
+        GGUFFile(str(p))
+    p.write_bytes(b"GGUF" + struct.pack("<I", 99) + b"\0" * 64)
+    with pytest.raises(GGUFError):
+        GGUFFile(str(p))
+
+
+def test_model_checkpoint_round_trip(tmp_path):
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.models.weights import ModelWeights
+    w = synthesize(SHAPES["tiny-qwen3moe"], "Q4_K_M", seed=3)
+    path = tmp_path / "tiny.gguf"
+    w.save_gguf(str(path))
+    r = ModelWeights.from_gguf(str(path))
+    assert r.config.n_experts == w.config.n_experts and r.config.d_model == w.config.d_model
+    for name in ("blk.0.ffn_gate_exps.weight", "blk.1.attn_q.weight", "token_embd.weight"):
+        assert r[name].qtype == w[name].qtype and torch.equal(r[name].raw.cpu(), w[name].raw.cpu())
+    assert "tokenizer.ggml.tokens" in r.metadata
