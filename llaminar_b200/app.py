@@ -250,17 +250,24 @@ def cmd_serve(cfg: OrchestrationConfig) -> int:
     return 0
 
 
-def run_benchmark(drive, vocab: int, prompt_tokens: int, decode_tokens: int, runs: int, batch: int = 1, is_cuda: bool = True) -> dict:
+def run_benchmark(drive, vocab: int, prompt_tokens: int, decode_tokens: int, runs: int, batch: int = 1, is_cuda: bool = True,
+                  shared_prefix: int = 0, keep_cache: bool = False) -> dict:
     """The reference protocol: built-in ~512-token prompt, 128 greedy decode tokens, 1 warm-up + N measured runs
     averaged, cache cleared between runs (reference: src/v2/utils/BenchmarkRunner.cpp:451-457, :1059-1065, :1125-1256)."""
     from .engine.sampling import SamplingParams
     g = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, vocab, (prompt_tokens,), generator=g).tolist() for _ in range(batch)]
+    common = torch.randint(0, vocab, (min(shared_prefix, prompt_tokens),), generator=g).tolist()
+    def make_prompts():                         # a fresh unique tail per run: only the common prefix can hit the prefix cache
+        return [common + torch.randint(0, vocab, (prompt_tokens - len(common),), generator=g).tolist() for _ in range(batch)]
+    prompts = make_prompts()
     sp = SamplingParams(temperature=0.0, max_tokens=decode_tokens, ignore_eos=True)
     sync = (lambda: torch.cuda.synchronize()) if is_cuda else (lambda: None)
     res = []
     for run in range(runs + 1):
-        drive.clear_cache()
+        if not keep_cache:                      # with keep_cache the prefix cache stays warm between runs
+            drive.clear_cache()
+        elif run > 0:
+            prompts = make_prompts()
         sync()
         t0 = time.perf_counter()
         reqs = [drive.add_request(p, sp) for p in prompts]
@@ -291,7 +298,8 @@ def cmd_benchmark(cfg: OrchestrationConfig) -> int:
         return 0
     v = cfg.values
     out = run_benchmark(drive, engine.cfg.vocab_size, v["bench_prompt_tokens"], v["n_predict"], v["bench_runs"],
-                        batch=v["batch_size"], is_cuda=engine.is_cuda)
+                        batch=v["batch_size"], is_cuda=engine.is_cuda, shared_prefix=v.get("bench_shared_prefix_tokens", 0),
+                        keep_cache=bool(v.get("prefix_cache")) and v.get("bench_shared_prefix_tokens", 0) > 0)
     out.update(model=engine.cfg.name, world=world, stats={k: (round(x, 4) if isinstance(x, float) else x) for k, x in engine.stats.items()})
     if getattr(engine, "prefix_cache", None) is not None:
         out["prefix_cache"] = engine.prefix_cache.stats()

@@ -105,6 +105,7 @@ OPTIONS: list[OptionSpec] = [
     # -- benchmark ------------------------------------------------------------------------------------------
     _o("--bench-runs", type=int, default=3, category="benchmark"),
     _o("--bench-prompt-tokens", type=int, default=512, category="benchmark"),
+    _o("--bench-shared-prefix-tokens", type=int, default=0, help="the first N prompt tokens are common to all requests of the batch", category="benchmark"),
     _o("--bench-json", help="write the benchmark result JSON here", category="benchmark"),
     # -- debugging --------------------------------------------------------------------------------------------
     _o("-v", "--verbose", dest="verbose", action="store_true", category="debug"),

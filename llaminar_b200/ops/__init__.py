@@ -46,13 +46,14 @@ class Scratch:
     part_ml: torch.Tensor
     attn_tickets: torch.Tensor
     status: torch.Tensor
+    partials: torch.Tensor          # small-batch GEMM: per-CTA slots for the partial sums of split tiles
 
     @staticmethod
     def create(device, accum_rows: int = 256, accum_cols: int = 65536, attn_slots: int = 1 << 22) -> "Scratch":
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)
         return Scratch(accum=z(accum_rows, accum_cols), tickets=z(8192, dt=torch.int32),
                        part_o=z(attn_slots), part_ml=z(attn_slots // 32), attn_tickets=z(8192, dt=torch.int32),
-                       status=z(4, dt=torch.int32))
+                       status=z(4, dt=torch.int32), partials=z(148 * 2 * 128 * 32))
 
 
     def reset(self) -> None:
@@ -141,7 +142,8 @@ def gemm(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, epi: int = EPI
     """Tensor-core path: out[M, N] (+)= x[M, K] @ dequant(W)^T, any M."""
     accum, tickets = _accum_args(pw, x.shape[0], scratch)
     ext().gemm_tc(pw.data, pw.fmt, pw.n, pw.k, x, out, epi, bias, accum, tickets, ksplit if accum is not None else 1,
-                  scratch.status if scratch is not None else None, debug_ptr, flags, tp)
+                  scratch.status if scratch is not None else None, debug_ptr, flags, tp,
+                  scratch.partials if scratch is not None else None)
     _count()
 
 

@@ -318,7 +318,8 @@ static void moe_topk(const Tensor& logits, int64_t k, bool renorm, Tensor ids, T
 
 // tensor-core GEMM: out[M, N] (+)= x[M, K] * dequant(W)[N, K]^T
 static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, Tensor out, int64_t epi, const OptTensor& bias,
-                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status, int64_t debug_ptr, int64_t flags, const OptTensor& tp) {
+                    const OptTensor& accum, const OptTensor& tickets, int64_t ksplit, const OptTensor& status, int64_t debug_ptr, int64_t flags, const OptTensor& tp,
+                    const OptTensor& partials) {
     check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "gemm_tc input must be contiguous bf16");
@@ -328,6 +329,7 @@ static void gemm_tc(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Te
     p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
     p.epi = (int)epi; p.bias = cptr<float>(bias); p.status = mptr<int>(status);
     p.accum = mptr<float>(accum); p.tickets = mptr<unsigned>(tickets); p.ksplit = (int)ksplit;
+    if (partials.has_value() && partials->numel() >= 148 * 2 * 128 * 32 && partials->scalar_type() == torch::kFloat32) p.partials = mptr<float>(partials);
     p.debug = reinterpret_cast<int*>(debug_ptr); p.flags = (int)flags;
     p.tp = tp.has_value() ? reinterpret_cast<const llm::TpFuse*>(tp->data_ptr()) : nullptr;
     if (tp.has_value()) TORCH_CHECK(p.m <= 32 && epi == llm::EPI_RESID, "fused tensor-parallel epilogue: residual mode, at most 32 rows");

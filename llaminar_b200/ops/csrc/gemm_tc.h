@@ -38,6 +38,7 @@ struct GemmTcParams {
     float* accum;              // split-K scratch fp32 [m_pad][accum_stride], zero between calls
     unsigned* tickets;         // split-K counters [n_tiles * m_tiles], zero between calls
     int accum_stride;
+    float* partials;           // small-batch kernel: [grid][2][32 tokens][128 rows] fp32 slots for split tiles (nullptr: atomics into accum)
     int ksplit;                // 0 = automatic
     int* status;               // optional device word: set to STATUS_TIMEOUT if a pipeline wait gave up
     int* debug;                // optional trace buffer (progress markers / ns timestamps written by the kernels); nullptr in production

@@ -98,7 +98,8 @@ LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 template <int FMT, int BM> struct Cfg {
     static_assert(BM == 32, "the small-batch kernel is built for one 32-token tile");
     static constexpr int B_ATOM_BYTES = BM * 128;         // activation tile: BM tokens x 64 columns, 128B-swizzled
-    static constexpr int N_B_STAGES = 8;                  // two chunks of four 64-column atoms
+    static constexpr int N_SETS = 3;                      // chunks in flight between the dequant warps and the MMA issuers
+    static constexpr int N_B_STAGES = 4 * N_SETS;         // per chunk four 64-column activation atoms
     static constexpr int RING_BYTES = N_B_STAGES * B_ATOM_BYTES;
     static constexpr int CHUNK = FmtTraits<FMT>::CHUNK;
     static constexpr int BUDGET = 218 * 1024 - RING_BYTES;
@@ -108,20 +109,23 @@ template <int FMT, int BM> struct Cfg {
     static constexpr int SMEM_BYTES = RING_BYTES + RAW_SLOTS * CHUNK + 1024;
     static constexpr int COLS_PER_WARP = BM / 4;          // epilogue: 4 column parts x 4 lane quarters
     // Tensor memory map (512 columns x 128 lanes, all of it):
-    //   [0, 256)    accumulators.  Control overhead per barrier wait / tcgen05.commit (~0.1 us each) dwarfs a 128x32x16
+    //   [0, 128)    accumulators.  Control overhead per barrier wait / tcgen05.commit (~0.1 us each) dwarfs a 128x32x16
     //               MMA, so the pipeline synchronises per 256-column chunk (16 MMAs) and two issuer warps take alternate
-    //               chunks.  Each issuer accumulates into its own pair of regions (even / odd K steps); the epilogue adds
-    //               them up; the whole set is double-buffered so the MMAs of unit i + 1 overlap the epilogue of unit i.
-    //   [256, 512)  the dequantised weight operand (MMA "A from TMEM"): two chunks of 128 rows x 256 bf16 = 128 columns
+    //               chunks, each into its own accumulator; the epilogue adds them up; the pair is double-buffered so the
+    //               MMAs of unit i + 1 overlap the epilogue of unit i.
+    //   [128, 512)  the dequantised weight operand (MMA "A from TMEM"): three chunks of 128 rows x 256 bf16 = 128 columns
     //               each.  Lane == weight row == dequant lane, so the dequant warps store their registers straight into
-    //               TMEM (tcgen05.st) and the bf16 weights never pass through shared memory.
+    //               TMEM (tcgen05.st) and the bf16 weights never pass through shared memory.  Issuing a chunk's 16 MMAs
+    //               takes one lane ~0.85 us, longer than the ~0.6 us the 16 dequant warps need for a chunk; with only
+    //               two operand slots the dequant warps waited for the slot of chunk c - 2 (period >= 0.8 us per
+    //               chunk in a per-CTA timeline), a third slot takes that wait off the critical path.
     static constexpr int N_ISSUERS = 2;
-    static constexpr int ACC_PER_ISSUER = 2;
+    static constexpr int ACC_PER_ISSUER = 1;
     static constexpr int ACC_SET_COLS = N_ISSUERS * ACC_PER_ISSUER * BM;
     static constexpr int A_COLS_OFFSET = 2 * ACC_SET_COLS;
     static constexpr int A_CHUNK_COLS = 128;
     static constexpr int TMEM_COLS = 512;
-    static_assert(A_COLS_OFFSET + 2 * A_CHUNK_COLS <= TMEM_COLS, "tensor memory map overflows");
+    static_assert(A_COLS_OFFSET + N_SETS * A_CHUNK_COLS <= TMEM_COLS, "tensor memory map overflows");
 };
 
 // Sink of a dequant warp: 8 bf16 (one uint4) -> 4 TMEM columns of this lane's row.
@@ -167,7 +171,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     using C = Cfg<FMT, BM>;
     constexpr int R = C::RAW_SLOTS;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[2], s_empty[2], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
+    __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort[2], s_last, s_tp_ok;
     __shared__ unsigned s_tp_epoch;
@@ -184,7 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
 
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
-        for (int s = 0; s < 2; ++s) { mbar_init(full_bar + s * 8, N_DQ_WARPS + 1); mbar_init(empty_bar + s * 8, 1); }
+        for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, N_DQ_WARPS + 1); mbar_init(empty_bar + s * 8, 1); }
         for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, N_DQ_WARPS); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
@@ -203,9 +207,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     tc_fence_after();
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = s_abort;
-    // optional timeline trace of CTA 0: p.debug[role * 1024 + slot] = low 32 bits of the ns timer
+    // optional timeline trace of CTA (flags >> 8): p.debug[role * 1024 + slot] = low 32 bits of the ns timer
     auto stamp = [&](int role, int slot) {
-        if (p.debug && blockIdx.x == 0 && slot < 1024) {
+        if (p.debug && (int)blockIdx.x == (p.flags >> 8) && slot < 1024) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             p.debug[role * 1024 + slot] = (int)(t & 0x7fffffff);
@@ -225,8 +229,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     Unit u;
 
     // chunk counter cc -> half of the operand ring (stages set*4 .. set*4+3) and the phase of its barriers
-    auto set_of = [](int cc) { return cc & 1; };
-    auto sphase_of = [](int cc) { return (cc >> 1) & 1; };
+    auto set_of = [](int cc) { return cc % C::N_SETS; };
+    auto sphase_of = [](int cc) { return (cc / C::N_SETS) & 1; };
 
     if (warp < N_DQ_WARPS) {
         // ---------------- dequant + epilogue: warp (g, a) converts atom a of row group g of every chunk ----------------
@@ -306,10 +310,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
             const int n_row = u.tile * 128 + row;
             bool do_finish = true;
             if (u.contributors > 1) {
+                // Split tile.  With a partials workspace every contributor parks its [32 tokens][128 rows] partial in its own
+                // slot (slot 0: the CTA's first unit, slot 1: any later one -- a CTA has at most one split unit at each end
+                // of its range) and the last arriver adds the slots up in CTA order; 4096 fp32 atomics per unit were
+                // measured to cost several microseconds when all CTAs reach their unit boundary together.
+                const bool use_slots = p.partials != nullptr;
+                if (use_slots) {
+                    float* mine = p.partials + ((size_t)blockIdx.x * 2 + (ui > 1 ? 1 : 0)) * (128 * BM);
 #pragma unroll
-                for (int i = 0; i < CW; ++i) {
-                    const int m = c0 + i;
-                    if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], v[i]);
+                    for (int i = 0; i < CW; ++i) __stcg(&mine[(c0 + i) * 128 + row], v[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) {
+                        const int m = c0 + i;
+                        if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], v[i]);
+                    }
                 }
                 __threadfence();
                 __syncwarp();
@@ -327,16 +342,65 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 ok = mbar_wait(epi_bar, epi_syncs & 1, abort_flag); ++epi_syncs;
                 if (!ok) break;
                 do_finish = s_last != 0;
+                if (warp == 0 && lane == 0) stamp(3, (ui - 1) * 4 + 2);
                 if (do_finish) {
                     __threadfence();
+                    if (use_slots) {
+                        // contributors are the CTAs that own a chunk of this tile, in order; sum in that order (own registers
+                        // at this CTA's place) so that the result does not depend on who arrived last
+                        const int c_first = it.cta_of(u.tile * k_blocks), c_last = it.cta_of(u.tile * k_blocks + k_blocks - 1);
+                        // all slots are requested before any is consumed (one L2 round trip instead of one per contributor);
+                        // a tile of k_blocks chunks spread over CTAs of >= 1 chunk has at most MAX_C contributors in practice
+                        constexpr int MAX_C = 4;
+                        float part[MAX_C][CW];
+                        const int nc = c_last - c_first + 1;
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) {
-                        const int m = c0 + i;
-                        v[i] = 0.f;
-                        if (m < p.m) {
-                            float* acc = &p.accum[(size_t)m * p.accum_stride + n_row];
-                            v[i] = __ldcg(acc);
-                            __stcg(acc, 0.f);
+                        for (int j = 0; j < MAX_C; ++j) {
+                            const int c = c_first + j;
+                            if (j < nc && c != (int)blockIdx.x) {
+                                const int c_pos = (int)(((long long)c * it.total) / it.G);
+                                const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
+#pragma unroll
+                                for (int i = 0; i < CW; ++i) part[j][i] = __ldcg(&theirs[(c0 + i) * 128 + row]);
+                            }
+                        }
+                        float sum[CW];
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) sum[i] = 0.f;
+#pragma unroll
+                        for (int j = 0; j < MAX_C; ++j) {
+                            if (j >= nc) break;
+                            if (c_first + j == (int)blockIdx.x) {
+#pragma unroll
+                                for (int i = 0; i < CW; ++i) sum[i] += v[i];
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < CW; ++i) sum[i] += part[j][i];
+                            }
+                        }
+                        for (int c = c_first + MAX_C; c <= c_last; ++c) {        // more contributors than that: one by one
+                            if (c == (int)blockIdx.x) {
+#pragma unroll
+                                for (int i = 0; i < CW; ++i) sum[i] += v[i];
+                            } else {
+                                const int c_pos = (int)(((long long)c * it.total) / it.G);
+                                const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
+#pragma unroll
+                                for (int i = 0; i < CW; ++i) sum[i] += __ldcg(&theirs[(c0 + i) * 128 + row]);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) v[i] = sum[i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) {
+                            const int m = c0 + i;
+                            v[i] = 0.f;
+                            if (m < p.m) {
+                                float* acc = &p.accum[(size_t)m * p.accum_stride + n_row];
+                                v[i] = __ldcg(acc);
+                                __stcg(acc, 0.f);
+                            }
                         }
                     }
                 }
@@ -410,6 +474,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     }
                 }
             }
+            if (warp == 0 && lane == 0) stamp(3, (ui - 1) * 4 + 3);
         }
     } else if (warp == N_DQ_WARPS) {
         // ---------------- raw chunk producer: the whole warp streams each chunk with 16-byte cp.async ----------------
@@ -470,22 +535,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 tc_fence_after();
                 bool first = true;
                 for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
-                    if (set_of(cc) != w) continue;
-                    ok = mbar_wait(full_bar + w * 8, sphase_of(cc), abort_flag);
+                    if ((cc & 1) != w) continue;
+                    const int set = set_of(cc);
+                    ok = mbar_wait(full_bar + set * 8, sphase_of(cc), abort_flag);
                     if (w == 0) stamp(2, cc * 2);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t acc_base = tmem_base + buf * C::ACC_SET_COLS + w * C::ACC_PER_ISSUER * BM;
-                    const uint32_t a_tmem = tmem_base + C::A_COLS_OFFSET + w * C::A_CHUNK_COLS;
+                    const uint32_t a_tmem = tmem_base + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
-                        const uint64_t bdesc = smem_desc_sw128(smem_base + (w * 4 + a) * C::B_ATOM_BYTES);
+                        const uint64_t bdesc = smem_desc_sw128(smem_base + (set * 4 + a) * C::B_ATOM_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)      // 16 columns of K = 8 TMEM columns of A, 32 bytes of the swizzled B row
-                            mma_f16_ts(acc_base + (k4 & 1) * BM, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc,
-                                       (first && a == 0 && k4 < 2) ? 0u : 1u);
+                            mma_f16_ts(acc_base, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc, (first && a == 0 && k4 == 0) ? 0u : 1u);
                     }
-                    mma_commit(empty_bar + w * 8);
+                    mma_commit(empty_bar + set * 8);
                     if (w == 0) stamp(2, cc * 2 + 1);
                     first = false;
                 }
@@ -555,6 +620,7 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     if (!cached_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev); }
     const int sms = cached_sms > 0 ? cached_sms : 148;
     const int grid = units < sms ? units : sms;
+    if (grid > 148) q.partials = nullptr;            // the slot workspace is sized for 148 CTAs
     gemm_tc_small_kernel<FMT, BM><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmap, q);
     return cudaGetLastError();
 }

@@ -306,9 +306,10 @@ static cudaError_t launch_f(const GemvParams& p, int mt, dim3 grid, size_t smem,
 }
 
 int gemv_pick_ksplit(int n_tiles, int k_blocks, int z) {
-    // aim for ~3 CTAs per SM in flight, at least 2 chunks (one per k-phase) per CTA
-    const int target = 148 * 3;
-    int ks = (target + n_tiles * z - 1) / (n_tiles * z);
+    // one full wave and no more: four CTAs fit an SM, and a second, mostly empty wave costs a whole CTA lifetime
+    // (measured on 51200 x 5120: 400 CTAs 34.9 us, 800 CTAs 42.6 us); at least 2 chunks (one per k-phase) per CTA
+    const int slots = 148 * 4;
+    int ks = slots / (n_tiles * z);
     ks = ks < 1 ? 1 : ks;
     const int max_ks = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
     return ks > max_ks ? max_ks : ks;

@@ -49,19 +49,38 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     }
     __syncthreads();
 
-    // ---- router projection: warp w takes experts w, w + 8, ... ----
-    for (int e = warp; e < p.n_experts; e += ROUTE_THREADS / 32) {
-        const __nv_bfloat16* wrow = p.router + (size_t)e * p.d;
-        float acc = 0.f;
-        for (int i = lane * 8; i < p.d; i += 256) {
-            const uint4 w8 = *reinterpret_cast<const uint4*>(wrow + i);
-            const float4 a = *reinterpret_cast<const float4*>(xn + i);
-            const float4 b = *reinterpret_cast<const float4*>(xn + i + 4);
-            acc += bf16_lo(w8.x) * a.x + bf16_hi(w8.x) * a.y + bf16_lo(w8.y) * a.z + bf16_hi(w8.y) * a.w
-                 + bf16_lo(w8.z) * b.x + bf16_hi(w8.z) * b.y + bf16_lo(w8.w) * b.z + bf16_hi(w8.w) * b.w;
+    // ---- router projection: warp w takes experts w, w + 8, ...; four experts at a time so that four independent weight
+    //      loads per lane are in flight for every read of the normalised row (a one-expert loop ran at L2 latency) ----
+    //      Every CTA walks the router rows from a different starting row: CTAs that read the same rows in lock step
+    //      pile up on the same L2 slices.
+    constexpr int NW = ROUTE_THREADS / 32, EB = 4;
+    const int rot = (int)((blockIdx.x * 37u) % (unsigned)p.n_experts);
+    for (int e0 = warp; e0 < p.n_experts; e0 += NW * EB) {
+        const __nv_bfloat16* wrow[EB];
+        float acc[EB];
+        int eid[EB];
+#pragma unroll
+        for (int j = 0; j < EB; ++j) {
+            const int e = e0 + j * NW;
+            eid[j] = e < p.n_experts ? (e + rot) % p.n_experts : -1;
+            wrow[j] = p.router + (size_t)(eid[j] < 0 ? 0 : eid[j]) * p.d;
+            acc[j] = 0.f;
         }
-        acc = warp_sum(acc);
-        if (lane == 0) logits[e] = acc;
+#pragma unroll 2
+        for (int i = lane * 4; i < p.d; i += 128) {            // consecutive lanes read consecutive 16 bytes of xn: no bank conflicts
+            uint2 w4[EB];
+#pragma unroll
+            for (int j = 0; j < EB; ++j) w4[j] = *reinterpret_cast<const uint2*>(wrow[j] + i);
+            const float4 a = *reinterpret_cast<const float4*>(xn + i);
+#pragma unroll
+            for (int j = 0; j < EB; ++j)
+                acc[j] += bf16_lo(w4[j].x) * a.x + bf16_hi(w4[j].x) * a.y + bf16_lo(w4[j].y) * a.z + bf16_hi(w4[j].y) * a.w;
+        }
+#pragma unroll
+        for (int j = 0; j < EB; ++j) {
+            const float r = warp_sum(acc[j]);
+            if (lane == 0 && eid[j] >= 0) logits[eid[j]] = r;
+        }
     }
     __syncthreads();
 
@@ -122,39 +141,85 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     const int pairs = p.tokens * p.top_k;
     for (int i = tid; i < pairs; i += ROUTE_THREADS) s_ids[i] = __ldcg(p.ids + i);
     __syncthreads();
-    if (tid < p.n_local) {
+    // pass 1: pairs per local expert (warp w counts experts w, w + 8, ... with ballots over 32 pairs at a time)
+    for (int el = warp; el < p.n_local; el += ROUTE_THREADS / 32) {
+        const int e = p.e0 + el;
         int c = 0;
-        const int e = p.e0 + tid;
-        for (int i = 0; i < pairs; ++i) c += (s_ids[i] == e);
-        s_cnt[tid] = c;
-        if (p.counts) p.counts[tid] = c;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int off = 0;
-        for (int e = 0; e < p.n_local; ++e) { s_off[e] = off; off += (s_cnt[e] + 3) >> 2; }
-        if (off == 0) {                                              // keep the combine protocol alive on an idle rank
-            p.items[0].expert = 0; p.items[0].m = 0;
-            p.items[0].slot[0] = p.items[0].slot[1] = p.items[0].slot[2] = p.items[0].slot[3] = 0;
-            off = 1;
+        for (int i0 = 0; i0 < pairs; i0 += 32) {
+            const int i = i0 + lane;
+            c += __popc(__ballot_sync(0xffffffffu, i < pairs && s_ids[i] == e));
         }
-        s_off[p.n_local] = off;
-        *p.n_items = min(off, p.max_items);
-        *p.ticket = 0u;
+        if (lane == 0) {
+            s_cnt[el] = c;
+            if (p.counts) p.counts[el] = c;
+        }
     }
     __syncthreads();
-    if (tid < p.n_local && s_cnt[tid] > 0) {
-        const int e = p.e0 + tid;
-        int item = s_off[tid], m = 0;
-        for (int i = 0; i < pairs; ++i) {
-            if (s_ids[i] != e) continue;
-            if (item < p.max_items) {
-                MoeItem& it = p.items[item];
-                if (m == 0) { it.expert = tid; it.slot[1] = it.slot[2] = it.slot[3] = i; }
-                it.slot[m] = i;
-                it.m = m + 1;
+    // item offsets: exclusive scan of ceil(count / 4) by warp 0 (up to 8 experts per lane)
+    if (warp == 0) {
+        constexpr int PER = ROUTE_MAX_EXPERTS / 32;
+        int loc[PER], sum = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int el = lane * PER + j;
+            loc[j] = el < p.n_local ? (s_cnt[el] + 3) >> 2 : 0;
+            sum += loc[j];
+        }
+        int incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        int run = incl - sum;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int el = lane * PER + j;
+            if (el < p.n_local) s_off[el] = run;
+            run += loc[j];
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        if (lane == 0) {
+            int n = total;
+            if (n == 0) {                                            // keep the combine protocol alive on an idle rank
+                p.items[0].expert = 0; p.items[0].m = 0;
+                p.items[0].slot[0] = p.items[0].slot[1] = p.items[0].slot[2] = p.items[0].slot[3] = 0;
+                n = 1;
             }
-            if (++m == 4) { m = 0; ++item; }
+            *p.n_items = min(n, p.max_items);
+            *p.ticket = 0u;
+        }
+    }
+    __syncthreads();
+    // pass 2: fill the items in token order; the pair of rank r within its expert goes to item off + r / 4, slot r % 4
+    for (int el = warp; el < p.n_local; el += ROUTE_THREADS / 32) {
+        const int cnt = s_cnt[el];
+        if (cnt == 0) continue;
+        const int e = p.e0 + el, off = s_off[el];
+        int seen = 0;
+        for (int i0 = 0; i0 < pairs && seen < cnt; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < pairs && s_ids[i] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int r = seen + __popc(mask & ((1u << lane) - 1u));
+                const int item = off + (r >> 2);
+                if (item < p.max_items) {
+                    MoeItem& it = p.items[item];
+                    it.slot[r & 3] = i;
+                    if ((r & 3) == 0) { it.expert = el; it.m = min(4, cnt - r); }
+                }
+            }
+            seen += __popc(mask);
+        }
+        __syncwarp();
+        // pad the unused slots of the expert's last item with its first pair (rows are computed but never stored)
+        const int last = off + ((cnt - 1) >> 2), used = ((cnt - 1) & 3) + 1;
+        if (lane == 0 && last < p.max_items && used < 4) {
+            __threadfence_block();
+            MoeItem& it = p.items[last];
+            const int first = it.slot[0];
+            for (int m = used; m < 4; ++m) it.slot[m] = first;
         }
     }
 }

@@ -119,8 +119,11 @@ def main() -> int:
             ops.moe_gate_up(gate_up, h, norm_w, 1e-6, act, items, n_items, kk, z_max, scratch=sc)
             ops.moe_down_combine(down, act, yslot, items, n_items, z_max, ids, wts, kk, 0, E, h, tt, scratch=sc)
         us = _time(fn, args.iters)
+        parts = [round(_time(lambda: ops.moe_route(h, norm_w, 1e-6, router, kk, True, 0, E, ids, wts, items, n_items, ticket), args.iters), 1),
+                 round(_time(lambda: ops.moe_gate_up(gate_up, h, norm_w, 1e-6, act, items, n_items, kk, z_max, scratch=sc), args.iters), 1),
+                 round(_time(lambda: ops.moe_down_combine(down, act, yslot, items, n_items, z_max, ids, wts, kk, 0, E, h, tt, scratch=sc), args.iters), 1)]
         touched = int(torch.unique(ids).numel())
-        rec.update(tokens=T, experts=E, top_k=kk, us_three_launches=round(us, 1), experts_touched=touched,
+        rec.update(tokens=T, experts=E, top_k=kk, us_three_launches=round(us, 1), us_route_gateup_down=parts, experts_touched=touched,
                    expert_weight_gbs=round((b1 + b2) * touched / E / us / 1e3, 1))
     print(json.dumps(rec), flush=True)
     return 0

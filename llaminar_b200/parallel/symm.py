@@ -56,7 +56,7 @@ class SymmetricArena:
 
     def supports(self, lin, rows: int) -> bool:
         from ..ops.layout import PackedWeight
-        if rows > self.rows_cap or len(lin.parts) != 1:
+        if rows > min(self.rows_cap, 32) or len(lin.parts) != 1:      # GEMV up to 4 rows, small-batch GEMM up to 32
             return False
         w = lin.parts[0][0]
         return isinstance(w, PackedWeight) and w.n_tiles * 128 <= self.n_cap
