@@ -20,8 +20,17 @@ PAGE_SIZE = 64
 _launches = 0          # kernels of this extension launched by the current process (bench evidence)
 
 
+_ext_ready = False
+
+
 def ext():
-    return _build.load()
+    global _ext_ready
+    mod = _build.load()
+    if not _ext_ready:
+        from ..utils.env import debug_env
+        mod.set_pdl(bool(debug_env().pdl))       # programmatic dependent launch of the decode-path kernels
+        _ext_ready = True
+    return mod
 
 
 def launch_count() -> int:

@@ -14,6 +14,7 @@
 // Replaces flash_attention_2_pipelined_kernel / flash_decoding_*_kernel (+ reduce) of the reference
 // (reference: src/v2/kernels/cuda/attention/CUDAFlashAttentionKernels.cu:348, :923-1181).
 #include "common.cuh"
+#include "launch.h"
 #include "ops.h"
 
 namespace llm {
@@ -92,6 +93,8 @@ struct DecodeSmem {
 template <int D>
 __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = blockIdx.x, split = blockIdx.y, seq = blockIdx.z;
     const int G = p.n_heads / p.n_kv_heads, R = p.rows_per_seq;
@@ -289,12 +292,12 @@ cudaError_t launch_attn_decode(const AttnDecodeParams& p, int batch, int n_split
         constexpr int smem = DecodeSmem<128>::BYTES;
         static bool once = false;
         if (!once) { cudaFuncSetAttribute(paged_attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
-        paged_attn_decode_kernel<128><<<grid, 128, smem, st>>>(p);
+        return launch_pdl(paged_attn_decode_kernel<128>, grid, dim3(128), smem, st, p);
     } else if (p.head_dim == 64) {
         constexpr int smem = DecodeSmem<64>::BYTES < 4 * 16 * 64 * 4 + 1024 ? 4 * 16 * 64 * 4 + 1024 : DecodeSmem<64>::BYTES;
         static bool once = false;
         if (!once) { cudaFuncSetAttribute(paged_attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
-        paged_attn_decode_kernel<64><<<grid, 128, smem, st>>>(p);
+        return launch_pdl(paged_attn_decode_kernel<64>, grid, dim3(128), smem, st, p);
     } else {
         return cudaErrorInvalidValue;
     }

@@ -6,6 +6,7 @@
 #include "gemm_tc.h"
 #include "gemv.h"
 #include "ops.h"
+#include "launch.h"
 
 using torch::Tensor;
 using OptTensor = c10::optional<Tensor>;
@@ -374,6 +375,7 @@ static void gemm_tc_allgather(const Tensor& w, int64_t fmt, int64_t n, int64_t k
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("set_pdl", [](bool on) { llm::pdl_enabled() = on; });
     m.def("gemv", &gemv);
     m.def("moe_route", &moe_route);
     m.def("moe_gemv", &moe_gemv);

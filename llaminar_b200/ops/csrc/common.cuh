@@ -56,6 +56,11 @@ LLM_DEVICE uint16_t ldg_nc_u16(const void* p) {
     return v;
 }
 
+// Programmatic dependent launch (see launch.h): trigger lets the next kernel of the stream start its prologue, wait blocks
+// until the previous kernel has completed and its memory is visible.  Both are no-ops for an ordinary launch.
+LLM_DEVICE void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+LLM_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 LLM_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 LLM_DEVICE float silu(float x) { return x / (1.0f + __expf(-x)); }

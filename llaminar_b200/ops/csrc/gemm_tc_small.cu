@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include "formats_smem.cuh"
+#include "launch.h"
 #include "gemm_tc.h"
 #include "gemv.h"
 #include "tp_fuse.cuh"
@@ -119,6 +120,11 @@ template <int FMT, int BM> struct Cfg {
     //               takes one lane ~0.85 us, longer than the ~0.6 us the 16 dequant warps need for a chunk; with only
     //               two operand slots the dequant warps waited for the slot of chunk c - 2 (period >= 0.8 us per
     //               chunk in a per-CTA timeline), a third slot takes that wait off the critical path.
+    // Dequant warp organisation: formats whose conversion is light (Q8_0) or latency-heavy (IQ3_S grid lookups) run as two
+    // sets of eight warps on alternate chunks (measured per-chunk period 1.59 -> 1.16 us and 2.20 -> 1.57 us); the
+    // ALU-bound k-quants keep all sixteen warps on one chunk (two sets: 0.91 -> 1.10 us for Q4_K).
+    static constexpr bool TWO_SETS = (FMT == FMT_Q8_0 || FMT == FMT_IQ3_S);
+    static constexpr int DQ_WARPS_PER_CHUNK = TWO_SETS ? N_DQ_WARPS / 2 : N_DQ_WARPS;
     static constexpr int N_ISSUERS = 2;
     static constexpr int ACC_PER_ISSUER = 1;
     static constexpr int ACC_SET_COLS = N_ISSUERS * ACC_PER_ISSUER * BM;
@@ -177,6 +183,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     __shared__ unsigned s_tp_epoch;
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k_blocks = p.k / 256, n_tiles = (p.n + 127) / 128;
     const int streamk = p.flags & 2;
@@ -188,8 +195,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
 
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
-        for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, N_DQ_WARPS + 1); mbar_init(empty_bar + s * 8, 1); }
-        for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, N_DQ_WARPS); }
+        for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, C::DQ_WARPS_PER_CHUNK + 1); mbar_init(empty_bar + s * 8, 1); }
+        for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -205,6 +212,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                     // everything above touched only this CTA's shared and tensor memory
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = s_abort;
     // optional timeline trace of CTA (flags >> 8): p.debug[role * 1024 + slot] = low 32 bits of the ns timer
@@ -233,16 +241,33 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     auto sphase_of = [](int cc) { return (cc / C::N_SETS) & 1; };
 
     if (warp < N_DQ_WARPS) {
-        // ---------------- dequant + epilogue: warp (g, a) converts atom a of row group g of every chunk ----------------
-        const int g = warp & 3, a = warp >> 2;
+        // ---------------- dequant + epilogue ----------------
+        // TWO_SETS: two sets of eight warps take alternate chunks; warp (g, ah) of a set converts atoms 2 * ah and 2 * ah + 1
+        // of row group g.  Otherwise all sixteen warps work on every chunk, warp (g, a) converting atom a.
+        const int g = warp & 3, ws = C::TWO_SETS ? (warp >> 3) : 0, ah = (warp >> 2) & 1, a1 = warp >> 2;
         const int row = g * 32 + lane;
-        const int q = g, part = a;                         // epilogue: TMEM lane quarter q, column part `part`
+        const int q = g, part = warp >> 2;                 // epilogue: TMEM lane quarter q, column part `part`
         constexpr int CW = C::COLS_PER_WARP;
         TmemSink sink{0};
         int cc = 0, ui = 0, epi_syncs = 0;
         bool ok = true;
+        // A chunk is published to the MMA issuers one step late: its TMEM stores complete while this warp already waits
+        // for the next chunk's raw bytes and operand slot, instead of being waited for on their own.
+        int pend_set = -1, pend_slot = -1;
+        auto publish = [&]() {
+            if (pend_set < 0) return;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full_bar + pend_set * 8);       // this warp's part of the chunk's weight operand is in TMEM
+                mbar_arrive(rawe_bar + pend_slot * 8);      // this warp no longer needs the raw chunk
+            }
+            pend_set = -1;
+        };
         while (ok && it.next(u)) {
             for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                if (C::TWO_SETS && (cc & 1) != ws) continue;
                 const int slot = cc % R, rphase = (cc / R) & 1;
                 const int set = set_of(cc);
                 ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
@@ -250,33 +275,42 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
                 if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
                 if (!ok) break;
+                publish();
                 const uint32_t raw = raw_base + slot * C::CHUNK;
-                sink.taddr = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS + a * 32;
-                if constexpr (FMT == FMT_IQ3_S) {
-                    switch (a) {
-                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink, s_grid); break;
-                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink, s_grid); break;
-                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink, s_grid); break;
-                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink, s_grid); break;
+                const uint32_t a_base = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
+                if constexpr (C::TWO_SETS) {
+                    if constexpr (FMT == FMT_IQ3_S) {
+                        if (ah == 0) {
+                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink, s_grid);
+                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink, s_grid);
+                        } else {
+                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink, s_grid);
+                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink, s_grid);
+                        }
+                    } else {
+                        if (ah == 0) {
+                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink);
+                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink);
+                        } else {
+                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink);
+                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink);
+                        }
                     }
                 } else {
-                    switch (a) {
+                    sink.taddr = a_base + a1 * 32;
+                    switch (a1) {
                         case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink); break;
                         case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink); break;
                         case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink); break;
                         default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
                     }
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full_bar + set * 8);        // this warp's part of the chunk's weight operand is in TMEM
-                    mbar_arrive(rawe_bar + slot * 8);       // this warp no longer needs the raw chunk
-                    if (warp == 0) stamp(0, cc * 4 + 2);
-                }
+                pend_set = set;
+                pend_slot = slot;
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
             }
             if (!ok) break;
+            publish();                                       // the unit's last chunk
             // ---- epilogue of this unit ----
             const int buf = ui & 1;
             if (warp == 0 && lane == 0) stamp(3, ui * 4 + 0);
@@ -621,8 +655,7 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     const int sms = cached_sms > 0 ? cached_sms : 148;
     const int grid = units < sms ? units : sms;
     if (grid > 148) q.partials = nullptr;            // the slot workspace is sized for 148 CTAs
-    gemm_tc_small_kernel<FMT, BM><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmap, q);
-    return cudaGetLastError();
+    return launch_pdl(gemm_tc_small_kernel<FMT, BM>, dim3(grid), dim3(THREADS), C::SMEM_BYTES, st, tmap, q);
 }
 
 template <int FMT>

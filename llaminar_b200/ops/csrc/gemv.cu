@@ -11,6 +11,7 @@
 // fused_swiglu_quantize_blockwise_kernel (reference: src/v2/kernels/cuda/gemm/CUDANativeVNNIGemvTuned.cu:332-1672,
 // src/v2/kernels/cuda/ops/CUDAFusedOpsKernels.cu:37).
 #include "formats.cuh"
+#include "launch.h"
 #include "gemv.h"
 #include "tp_fuse.cuh"
 
@@ -80,6 +81,8 @@ LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* act
 template <int FMT, int M, int NORM>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.x;
     const int per = (p.k_blocks + gridDim.y - 1) / gridDim.y;
@@ -286,10 +289,10 @@ template <int FMT, int M>
 static cudaError_t launch_fm(const GemvParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     if (p.norm_w) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_kernel<FMT, M, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gemv_kernel<FMT, M, 1><<<grid, 256, smem, st>>>(p);
+        return launch_pdl(gemv_kernel<FMT, M, 1>, grid, dim3(256), smem, st, p);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gemv_kernel<FMT, M, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gemv_kernel<FMT, M, 0><<<grid, 256, smem, st>>>(p);
+        return launch_pdl(gemv_kernel<FMT, M, 0>, grid, dim3(256), smem, st, p);
     }
     return cudaGetLastError();
 }
@@ -377,6 +380,8 @@ __global__ void __launch_bounds__(128) dequant_kernel(const uint8_t* w, int n, i
 template <int FMT>
 __global__ void __launch_bounds__(128) gather_rows_kernel(const uint8_t* w, int k_blocks, const int* rows, int n_rows,
                                                           float* out_f32, __nv_bfloat16* out_bf16, int out_stride) {
+    pdl_trigger();
+    pdl_wait();
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
     if (item >= n_rows * k_blocks) return;
     const int t = item / k_blocks, kb = item % k_blocks;
@@ -410,12 +415,12 @@ cudaError_t launch_gather_rows(int fmt, const uint8_t* w, int k, const int* rows
     const int grid = (items + 127) / 128;
     if (grid == 0) return cudaSuccess;
     switch (fmt) {
-        case FMT_Q4_K: gather_rows_kernel<FMT_Q4_K><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
-        case FMT_Q5_K: gather_rows_kernel<FMT_Q5_K><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
-        case FMT_Q6_K: gather_rows_kernel<FMT_Q6_K><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
-        case FMT_Q8_0: gather_rows_kernel<FMT_Q8_0><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
-        case FMT_Q4_0: gather_rows_kernel<FMT_Q4_0><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
-        case FMT_IQ3_S: gather_rows_kernel<FMT_IQ3_S><<<grid, 128, 0, st>>>(w, kb, rows, n_rows, out_f32, out_bf16, out_stride); break;
+        case FMT_Q4_K: return launch_pdl(gather_rows_kernel<FMT_Q4_K>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
+        case FMT_Q5_K: return launch_pdl(gather_rows_kernel<FMT_Q5_K>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
+        case FMT_Q6_K: return launch_pdl(gather_rows_kernel<FMT_Q6_K>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
+        case FMT_Q8_0: return launch_pdl(gather_rows_kernel<FMT_Q8_0>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
+        case FMT_Q4_0: return launch_pdl(gather_rows_kernel<FMT_Q4_0>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
+        case FMT_IQ3_S: return launch_pdl(gather_rows_kernel<FMT_IQ3_S>, dim3(grid), dim3(128), 0, st, w, kb, rows, n_rows, out_f32, out_bf16, out_stride);
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

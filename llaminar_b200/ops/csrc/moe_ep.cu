@@ -11,11 +11,12 @@
 // host-built expert lists between them (reference: src/v2/kernels/cuda/moe/CUDAMoEKernels.cu:66-700,
 // src/v2/kernels/cuda/moe/CUDAMoEKernel.cpp).
 #include "common.cuh"
+#include "launch.h"
 #include "gemv.h"
 
 namespace llm {
 
-constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_THREADS = 512;
 constexpr int ROUTE_MAX_EXPERTS = 256;
 constexpr int ROUTE_MAX_PAIRS = 4096;      // tokens * top_k handled by the list builder
 
@@ -24,6 +25,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     float* xn = reinterpret_cast<float*>(smem_raw);                 // [d]
     float* logits = xn + p.d;                                        // [ROUTE_MAX_EXPERTS]
     __shared__ float s_part[ROUTE_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = blockIdx.x;
@@ -49,11 +52,12 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     }
     __syncthreads();
 
-    // ---- router projection: warp w takes experts w, w + 8, ...; four experts at a time so that four independent weight
-    //      loads per lane are in flight for every read of the normalised row (a one-expert loop ran at L2 latency) ----
+    // ---- router projection: warp w takes experts w, w + 8, ...; eight experts at a time so that eight independent weight
+    //      loads per lane are in flight for every read of the normalised row (a one-expert loop ran at memory latency:
+    //      the expert weights of the layer before have flushed the router matrix out of L2 by the time it is needed) ----
     //      Every CTA walks the router rows from a different starting row: CTAs that read the same rows in lock step
     //      pile up on the same L2 slices.
-    constexpr int NW = ROUTE_THREADS / 32, EB = 4;
+    constexpr int NW = ROUTE_THREADS / 32, EB = 8;
     const int rot = (int)((blockIdx.x * 37u) % (unsigned)p.n_experts);
     for (int e0 = warp; e0 < p.n_experts; e0 += NW * EB) {
         const __nv_bfloat16* wrow[EB];
@@ -231,8 +235,7 @@ cudaError_t launch_moe_route(const MoeRouteParams& p, cudaStream_t st) {
         return cudaErrorInvalidValue;
     const size_t dyn = max((size_t)(p.d + ROUTE_MAX_EXPERTS) * sizeof(float), (size_t)p.tokens * p.top_k * sizeof(int));
     if (dyn > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
-    moe_route_kernel<<<p.tokens, ROUTE_THREADS, dyn, st>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(moe_route_kernel, dim3(p.tokens), dim3(ROUTE_THREADS), dyn, st, p);
 }
 
 }  // namespace llm

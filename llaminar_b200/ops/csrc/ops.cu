@@ -5,6 +5,7 @@
 // (ring append; here the cache is paged), src/v2/kernels/cuda/moe/CUDAMoEKernels.cu (softmax_topk),
 // src/v2/backends/cuda/CUDATensorValidation.cu.
 #include "common.cuh"
+#include "launch.h"
 #include "ops.h"
 
 namespace llm {
@@ -17,6 +18,8 @@ constexpr int PAGE = 64;
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ h, const float* __restrict__ w,
                                                       __nv_bfloat16* __restrict__ out, int d, float eps) {
     __shared__ float s_part[8];
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float4* x4 = reinterpret_cast<const float4*>(h + (size_t)row * d);
     float ss = 0.f;
@@ -42,8 +45,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
     if (d % 4) return cudaErrorInvalidValue;
-    rmsnorm_kernel<<<rows, 256, 0, st>>>(h, w, out, d, eps);
-    return cudaGetLastError();
+    return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, st, h, w, out, d, eps);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -90,6 +92,8 @@ cudaError_t launch_mtp_concat_norm(const float* emb, const float* hidden, const 
 template <int D>
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKVParams p) {
     constexpr int EPL = D / 64;                          // elements per lane in each half
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int heads_total = p.n_heads + 2 * p.n_kv_heads;
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -150,8 +154,8 @@ cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st) {
     const int items = p.n_tokens * (p.n_heads + 2 * p.n_kv_heads);
     if (items == 0) return cudaSuccess;
     const int grid = (items + 3) / 4;
-    if (p.head_dim == 128) rope_kv_kernel<128><<<grid, 128, 0, st>>>(p);
-    else if (p.head_dim == 64) rope_kv_kernel<64><<<grid, 128, 0, st>>>(p);
+    if (p.head_dim == 128) return launch_pdl(rope_kv_kernel<128>, dim3(grid), dim3(128), 0, st, p);
+    else if (p.head_dim == 64) return launch_pdl(rope_kv_kernel<64>, dim3(grid), dim3(128), 0, st, p);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
@@ -218,6 +222,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
                                                       int* __restrict__ pairs, int idx_offset) {
     __shared__ float s_v[32];
     __shared__ int s_i[32];
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * stride;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -253,8 +259,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 }
 cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, int* pairs, int idx_offset, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, vocab, stride, tokens, pairs, idx_offset);
-    return cudaGetLastError();
+    return launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, vocab, stride, tokens, pairs, idx_offset);
 }
 
 // Merge of per-shard argmax candidates: gathered[rank][row] = (value bits, global index); larger value wins, ties go to
