@@ -219,6 +219,71 @@ def cmd_oneshot(cfg: OrchestrationConfig) -> int:
     return 0
 
 
+def cmd_chat(cfg: OrchestrationConfig) -> int:
+    """Interactive multi-turn chat on the terminal: one line per user turn, `/reset` clears the history, `/exit` or
+    end-of-input leaves (the reference's interactive mode is a full-screen TUI: src/v2/app/modes/InteractiveChatMode.cpp;
+    this is its line-oriented equivalent)."""
+    from .tokenizer.bpe import StreamDecoder
+    from .tokenizer.chat_template import ThinkSplitter
+    engine, tok, template, rank, world = build_engine(cfg)
+    drive, worker = _spmd(engine, rank, world)
+    if worker:
+        worker()
+        return 0
+    if tok is None or template is None:
+        raise ConfigError(["the checkpoint has no embedded tokenizer; `chat` needs tokenizer.ggml.* metadata"])
+    v = cfg.values
+    history: list[dict] = []
+    if v.get("system_prompt"):
+        history.append({"role": "system", "content": v["system_prompt"]})
+    base = list(history)
+    eos = tuple(i for i in (tok.eos_id, tok.vocab.get("<|im_end|>"), tok.vocab.get("<|endoftext|>")) if i is not None)
+    while True:
+        try:
+            line = input("> ")
+        except EOFError:
+            break
+        line = line.strip()
+        if line in ("/exit", "/quit"):
+            break
+        if line == "/reset":
+            history = list(base)
+            drive.clear_cache()
+            continue
+        if not line:
+            continue
+        history.append({"role": "user", "content": line})
+        ids = tok.encode(template.render(history), add_special=True)
+        if len(ids) + 2 >= v["ctx_size"]:
+            print("[context window exhausted; /reset to start over]")
+            history.pop()
+            continue
+        sp = cli_sampling(cfg)
+        sp.max_tokens = min(sp.max_tokens, v["ctx_size"] - len(ids) - 1)
+        sp.stop_token_ids = tuple(dict.fromkeys(eos))
+        req = drive.add_request(ids, sp)
+        dec, split, answer = StreamDecoder(tok), ThinkSplitter(), []
+        while req.state != "finished":
+            for o in drive.step():
+                if o.rid != req.rid:
+                    continue
+                for t in o.new_tokens:
+                    _, content = split.push(dec.push(t))
+                    if content:
+                        answer.append(content)
+                        sys.stdout.write(content)
+                        sys.stdout.flush()
+        _, content = split.push(dec.flush())
+        tail = content + split.flush()[1]
+        answer.append(tail)
+        sys.stdout.write(tail + "\n")
+        drive.requests.pop(req.rid, None)
+        history.append({"role": "assistant", "content": "".join(answer)})
+    if world > 1:
+        drive.shutdown_workers()
+    return 0
+
+
 def cmd_serve(cfg: OrchestrationConfig) -> int:
     from .serve.chat_handler import ChatCompletionHandler
     from .serve.engine_loop import EngineLoop
@@ -372,7 +437,7 @@ def main(argv: list[str] | None = None) -> int:
     if rc is not None:
         return rc
     try:
-        return {"oneshot": cmd_oneshot, "serve": cmd_serve, "benchmark": cmd_benchmark, "plan": cmd_plan,
+        return {"oneshot": cmd_oneshot, "chat": cmd_chat, "serve": cmd_serve, "benchmark": cmd_benchmark, "plan": cmd_plan,
                 "describe": cmd_describe}[cfg.command](cfg)
     except ConfigError as exc:
         for e in exc.errors:

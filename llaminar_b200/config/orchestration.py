@@ -13,7 +13,7 @@ import re
 from dataclasses import dataclass, field
 from typing import Any
 
-SUBCOMMANDS = ("oneshot", "serve", "benchmark", "plan", "describe")
+SUBCOMMANDS = ("oneshot", "chat", "serve", "benchmark", "plan", "describe")
 
 
 @dataclass
@@ -104,6 +104,7 @@ OPTIONS: list[OptionSpec] = [
     _o("--mtp-force-accept", action="store_true", help="benchmark aid: treat every draft as accepted (random weights)", category="mtp"),
     # -- benchmark ------------------------------------------------------------------------------------------
     _o("--bench-runs", type=int, default=3, category="benchmark"),
+    _o("--system-prompt", default=None, help="system message of `chat` / `oneshot`", category="generation"),
     _o("--bench-prompt-tokens", type=int, default=512, category="benchmark"),
     _o("--bench-shared-prefix-tokens", type=int, default=0, help="the first N prompt tokens are common to all requests of the batch", category="benchmark"),
     _o("--bench-json", help="write the benchmark result JSON here", category="benchmark"),
@@ -348,7 +349,7 @@ def validate(cfg: OrchestrationConfig) -> list[str]:
         errs.append("--prefix-cache-disk-budget-mb needs --prefix-cache-disk-dir")
     if int(v.get("batch_size") or 1) < 1 or int(v.get("ctx_size") or 1) < 16:
         errs.append("--batch-size must be >= 1 and -c >= 16")
-    if cfg.command in ("oneshot", "serve", "benchmark") and not (v.get("model") or v.get("synthetic")) \
+    if cfg.command in ("oneshot", "chat", "serve", "benchmark") and not (v.get("model") or v.get("synthetic")) \
             and not (v.get("dry_run") or v.get("list_devices") or v.get("validate_only")):
         errs.append("a model is required (-m file.gguf, or --synthetic SHAPE)")
     return errs

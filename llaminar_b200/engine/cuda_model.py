@@ -322,6 +322,30 @@ class CudaModel:
                 act.copy_((torch.nn.functional.silu(gu[:, :self.ff_local].float()) * gu[:, self.ff_local:].float()).to(act.dtype))
         self._row_parallel_resid(L.down, act, h)
 
+    def _debug_hooks(self):
+        """Per-layer checks behind environment switches (never inside CUDA-graph capture):
+        LLAMINAR_VALIDATE_TENSORS scans the residual stream for NaN/Inf after every layer (reference: the stage verifier,
+        src/v2/graph/StageVerifier.cpp); LLAMINAR_STAGE_DUMP_DIR writes it to `<dir>/layer_<n>_call_<k>.pt`
+        (reference: src/v2/execution/debug/StageDumper.h)."""
+        from ..utils.env import debug_env
+        env = debug_env()
+        validate, dump_dir = env.validate_tensors, env.stage_dump_dir
+        if not (validate or dump_dir) or torch.cuda.is_current_stream_capturing():
+            return None
+        self._dump_calls = getattr(self, "_dump_calls", 0) + 1
+        call = self._dump_calls
+
+        def hook(layer: int, h: torch.Tensor) -> None:
+            if validate:
+                n_nan, n_inf = ops.nan_scan(h)
+                if n_nan or n_inf:
+                    raise FloatingPointError(f"layer {layer}: {n_nan} NaN and {n_inf} Inf values in the residual stream")
+            if dump_dir:
+                import os
+                os.makedirs(dump_dir, exist_ok=True)
+                torch.save(h.detach().float().cpu(), os.path.join(dump_dir, f"layer_{layer:03d}_call_{call:05d}.pt"))
+        return hook
+
     def _moe(self, L: CudaLayer, h: torch.Tensor, T: int) -> None:
         from .moe import moe_forward
         moe_forward(self, L, h, T)
@@ -349,8 +373,11 @@ class CudaModel:
             h.copy_(fb.embeds)
         else:
             self.embed_tokens(fb.tokens, h)
+        debug = self._debug_hooks()
         for li, L in enumerate(self.layers):
             self._layer(L, fb, kv.layers[kv_layer_offset + li], T)
+            if debug is not None:
+                debug(self.layer_ids[li], h)
         logits = None
         if want_logits and self.head is not None:
             rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())

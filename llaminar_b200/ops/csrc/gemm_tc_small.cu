@@ -653,7 +653,15 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     static int cached_sms = 0;
     if (!cached_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev); }
     const int sms = cached_sms > 0 ? cached_sms : 148;
-    const int grid = units < sms ? units : sms;
+    int grid = units < sms ? units : sms;
+    if (streamk) {
+        // small problems: at least four chunks per CTA (the per-CTA start-up and epilogue cost a few chunks' worth of
+        // time) and at most four contributors per tile (the finalizer fetches their partial sums in one round trip)
+        const int g1 = (units + 3) / 4, g2 = 4 * n_tiles;
+        int g = g1 < g2 ? g1 : g2;
+        if (g < 1) g = 1;
+        if (g < grid) grid = g;
+    }
     if (grid > 148) q.partials = nullptr;            // the slot workspace is sized for 148 CTAs
     return launch_pdl(gemm_tc_small_kernel<FMT, BM>, dim3(grid), dim3(THREADS), C::SMEM_BYTES, st, tmap, q);
 }

@@ -119,3 +119,11 @@ def _spmd_run(rank, world):
 def test_spmd_workers_mirror_rank0():
     res = run_ranks(_spmd_run, 2)
     assert res[0] == res[1] and res[0] > 0
+
+
+def test_cli_chat_reads_turns_from_stdin():
+    r = subprocess.run([sys.executable, "-m", "llaminar_b200", "chat", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0",
+                        "-d", "cpu", "-n", "4", "-c", "256", "--system-prompt", "be brief"],
+                       input="hello\n/reset\nagain\n/exit\n", capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.count("> ") >= 3

@@ -139,3 +139,17 @@ def test_prefix_cache_on_gpu_tiers_and_terminal_state(tmp_path):
     assert agree >= 0.9 * 32
     st = pc.stats()
     assert st["hit_tokens"] >= 128 and st["terminal_hits"] >= 1 and st["evicted_to_disk"] > 0 and st["promoted"] > 0
+
+
+def test_debug_switches_validate_and_dump(tmp_path, monkeypatch):
+    """LLAMINAR_VALIDATE_TENSORS / LLAMINAR_STAGE_DUMP_DIR: per-layer NaN scan and residual-stream dumps in eager mode."""
+    monkeypatch.setenv("LLAMINAR_VALIDATE_TENSORS", "1")
+    monkeypatch.setenv("LLAMINAR_STAGE_DUMP_DIR", str(tmp_path))
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cuda", max_batch=2, max_context=128, use_graphs=False)
+    out = eng.generate([_prompt(20, 1)], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    assert len(out[0]) == 3
+    files = sorted(p.name for p in tmp_path.iterdir())
+    assert "layer_000_call_00001.pt" in files and "layer_001_call_00001.pt" in files
+    h = torch.load(tmp_path / "layer_001_call_00001.pt")
+    assert h.shape == (20, SHAPES["tiny-qwen3"].d_model) and torch.isfinite(h).all()
