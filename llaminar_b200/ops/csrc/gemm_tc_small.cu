@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort[2], s_last, s_tp_ok;
-    __shared__ unsigned s_tp_epoch;
+    __shared__ unsigned s_tp_epoch, s_tp_epoch2;
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
     pdl_trigger();
@@ -462,11 +462,78 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         ++epi_syncs;
                         return r;
                     };
-                    if (tid == 0) s_tp_epoch = tp.epoch[u.tile];
+                    if (tid == 0) { s_tp_epoch = tp.epoch[u.tile]; s_tp_epoch2 = tp.epoch2[u.tile]; }
                     ok = epi_sync();
                     if (!ok) break;
                     const unsigned e = s_tp_epoch;
                     auto row_of = [&](int i) { return (c0 + i) < p.m ? c0 + i : -1; };
+                    if (tp.two_phase_min_rows > 0 && p.m >= tp.two_phase_min_rows) {
+                        // ---- reduce-scatter + all-gather (see tp_fuse.cuh) ----
+                        const int W = tp.size, slice = 128 / W, cols_rs = tp.n_cap / W;
+                        const unsigned e2 = s_tp_epoch2;
+                        const int par = e & 1, par2 = e2 & 1;
+                        {   // phase 1: this thread's feature `row` belongs to the slice of rank `d`
+                            const int d = row / slice, fo = row - d * slice;
+                            float* dst = tp.rs_inbox[d] + ((size_t)(par * W + tp.rank) * tp.rows_cap) * cols_rs + u.tile * slice + fo;
+                            const float b = (p.bias && tp.rank == 0 && n_row < p.n) ? p.bias[n_row] : 0.f;
+#pragma unroll
+                            for (int i = 0; i < CW; ++i) {
+                                const int m = c0 + i;
+                                if (m < p.m) dst[(size_t)m * cols_rs] = (n_row < p.n) ? v[i] + b : 0.f;
+                            }
+                        }
+                        ok = epi_sync();
+                        if (!ok) break;
+                        if (tid < W) tp_signal(tp, u.tile, tid);
+                        if (tid == 0) {
+                            abort_flag[1] = 1;
+                            s_tp_ok = tp_wait(tp, u.tile, e) ? 1 : 0;
+                            abort_flag[1] = 0;
+                            tp.epoch[u.tile] = e + 1;
+                        }
+                        ok = epi_sync();
+                        if (!ok) break;
+                        if (s_tp_ok) {
+                            // phase 2a: reduce this rank's slice over all sources (fixed order) and hand it to every rank
+                            const float* mine = tp.rs_inbox[tp.rank] + ((size_t)(par * W) * tp.rows_cap) * cols_rs + u.tile * slice;
+                            for (int j = tid; j < p.m * slice; j += N_DQ_WARPS * 32) {
+                                const int m = j / slice, fo = j - m * slice;
+                                float r = 0.f;
+                                for (int src = 0; src < W; ++src) r += __ldcg(mine + ((size_t)src * tp.rows_cap + m) * cols_rs + fo);
+                                const size_t o = ((size_t)par2 * tp.rows_cap + m) * tp.n_cap + u.tile * 128 + tp.rank * slice + fo;
+                                for (int dd = 0; dd < W; ++dd) tp.ag_inbox[dd][o] = r;
+                            }
+                        }
+                        ok = epi_sync();
+                        if (!ok) break;
+                        if (tid < W) red_release_sys_add(tp.flags2[tid] + u.tile, 1u);
+                        if (tid == 0) {
+                            abort_flag[1] = 1;
+                            const unsigned target = (e2 + 1u) * (unsigned)W;
+                            const unsigned* f2 = tp.flags2[tp.rank] + u.tile;
+                            int got = 0;
+                            for (unsigned it2 = 0; it2 < tp.spin_limit; ++it2) {
+                                if ((int)(ld_acquire_sys(f2) - target) >= 0) { got = 1; break; }
+                                if (it2 > 4096) __nanosleep(64);
+                            }
+                            if (!got && tp.status) atomicExch(tp.status, (int)STATUS_TIMEOUT);
+                            s_tp_ok = s_tp_ok && got;
+                            abort_flag[1] = 0;
+                            tp.epoch2[u.tile] = e2 + 1;
+                        }
+                        ok = epi_sync();
+                        if (!ok) break;
+                        if (s_tp_ok && n_row < p.n) {
+                            // phase 2b: the complete tile is in this rank's all-gather inbox
+                            const float* full = tp.ag_inbox[tp.rank] + ((size_t)par2 * tp.rows_cap) * tp.n_cap + u.tile * 128 + row;
+                            float* h = static_cast<float*>(p.out);
+#pragma unroll
+                            for (int i = 0; i < CW; ++i) {
+                                const int m = c0 + i;
+                                if (m < p.m) h[(size_t)m * p.out_stride + n_row] += __ldcg(full + (size_t)m * tp.n_cap);
+                            }
+                        }
+                    } else {
                     if (n_row < p.n) {
                         if (p.bias && tp.rank == 0) {
 #pragma unroll
@@ -493,6 +560,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             const int m = c0 + i;
                             if (m < p.m) h[(size_t)m * p.out_stride + n_row] += v[i];
                         }
+                    }
                     }
                 } else if (n_row < p.n) {
                     const float b = p.bias ? p.bias[n_row] : 0.f;

@@ -15,6 +15,11 @@
 //   h[m][n] += sum_src inbox[me][parity][src][m][n]  (src order fixed, so all ranks compute identical bits)
 // A rank can run at most one call ahead of a peer (it needs the peer's tiles of call c to finish call c), so two
 // inbox parities suffice and monotone flags are never satisfied early.  No TMA and no multicast is involved.
+//
+// Two-phase variant (small-batch GEMM, groups of 4 or 8 ranks, >= two_phase_min_rows rows): rank d owns the column slice
+// [d * 128 / size, (d + 1) * 128 / size) of every tile.  Phase 1 pushes each rank's partial of slice d into rs_inbox[d] and
+// bumps flags[d][t]; the owner waits for `size` arrivals, sums the slice in rank order, pushes the result into every
+// rank's ag_inbox and bumps flags2[.][t]; everyone waits for `size` arrivals there and adds the complete tile to h.
 #pragma once
 #include "common.cuh"
 
@@ -29,6 +34,13 @@ struct TpFuse {
     int* status;                       // local: set to STATUS_TIMEOUT when a wait gives up
     int rank, size, rows_cap, n_cap;
     unsigned spin_limit;               // iterations of the bounded wait
+    // Two-phase variant (reduce-scatter then all-gather) for wider groups and larger tiles: the one-shot exchange sends
+    // every partial tile to every rank (size x the tile bytes per rank), the two-phase one 2 x (size - 1) / size of them.
+    int two_phase_min_rows;            // use it when size >= 4, size divides 128 and the call has at least this many rows (0: never)
+    float* rs_inbox[TP_MAX_RANKS];     // per rank: [2][size src][rows_cap][n_cap / size]  partial column slices this rank reduces
+    float* ag_inbox[TP_MAX_RANKS];     // per rank: [2][rows_cap][n_cap]                   reduced tiles, all column slices
+    unsigned* flags2[TP_MAX_RANKS];    // per rank: [n_cap / 128] arrival counters of the all-gather phase
+    unsigned* epoch2;                  // local: [n_cap / 128] two-phase call counters
 };
 
 LLM_DEVICE unsigned ld_acquire_sys(const unsigned* p) {

@@ -34,19 +34,31 @@ class SymmetricArena:
         n_tiles = n_cap // 128
         self.flag_bytes = (n_tiles * 4 + 255) // 256 * 256
         self.inbox_bytes = 2 * self.size * rows_cap * n_cap * 4
-        total = self.flag_bytes + self.inbox_bytes
+        self.rs_bytes = 2 * rows_cap * n_cap * 4          # [2][size][rows_cap][n_cap / size]
+        self.ag_bytes = 2 * rows_cap * n_cap * 4          # [2][rows_cap][n_cap]
+        total = 2 * self.flag_bytes + self.inbox_bytes + self.rs_bytes + self.ag_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.epoch = torch.zeros(n_tiles, dtype=torch.int32, device=self.device)
+        self.epoch = torch.zeros(2 * n_tiles, dtype=torch.int32, device=self.device)      # one-shot counters, then two-phase counters
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        # struct TpFuse { float* inbox[8]; unsigned* flags[8]; unsigned* epoch; int* status; int rank, size, rows_cap, n_cap; unsigned spin_limit; }
-        inbox = [p + self.flag_bytes for p in ptrs] + [0] * (TP_MAX_RANKS - self.size)
-        flags = ptrs + [0] * (TP_MAX_RANKS - self.size)
-        blob = struct.pack("<8Q8QQQiiiiI4x", *inbox, *flags, self.epoch.data_ptr(), self.status.data_ptr(),
-                           self.rank, self.size, rows_cap, n_cap, spin_limit)
+        pad = [0] * (TP_MAX_RANKS - self.size)
+        o_inbox = 2 * self.flag_bytes
+        o_rs, o_ag = o_inbox + self.inbox_bytes, o_inbox + self.inbox_bytes + self.rs_bytes
+        inbox = [p + o_inbox for p in ptrs] + pad
+        flags = ptrs + pad
+        rs = [p + o_rs for p in ptrs] + pad
+        ag = [p + o_ag for p in ptrs] + pad
+        flags2 = [p + self.flag_bytes for p in ptrs] + pad
+        two_phase_min_rows = 16 if (self.size >= 4 and 128 % self.size == 0) else 0
+        # struct TpFuse { float* inbox[8]; unsigned* flags[8]; unsigned* epoch; int* status; int rank, size, rows_cap, n_cap;
+        #                 unsigned spin_limit; int two_phase_min_rows; float* rs_inbox[8]; float* ag_inbox[8]; unsigned* flags2[8];
+        #                 unsigned* epoch2; }
+        blob = struct.pack("<8Q8QQQiiiiIi8Q8Q8QQ", *inbox, *flags, self.epoch.data_ptr(), self.status.data_ptr(),
+                           self.rank, self.size, rows_cap, n_cap, spin_limit, two_phase_min_rows, *rs, *ag, *flags2,
+                           self.epoch.data_ptr() + n_tiles * 4)
         self.desc = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.device)
         dist.barrier(group=group)
 

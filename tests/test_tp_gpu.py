@@ -150,3 +150,11 @@ def test_allgather_gemm_2gpu(qt_name, m_total, n, k):
     _need(2)
     errs = run_ranks_gpu(_allgather_gemm, 2, qt_name, m_total, n, k)
     assert max(errs) < 2e-2
+
+
+@pytest.mark.parametrize("qt_name,rows", [("Q4_K", 32), ("Q6_K", 17), ("Q4_K", 2)])
+def test_fused_row_parallel_allreduce_4gpu_two_phase(qt_name, rows):
+    """Groups of four: batches of >= 16 rows take the reduce-scatter + all-gather epilogue, small ones the one-shot push."""
+    _need(4)
+    errs = run_ranks_gpu(_fused_kernels, 4, qt_name, rows)
+    assert max(errs) < 2e-2
