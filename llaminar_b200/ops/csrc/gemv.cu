@@ -82,13 +82,20 @@ template <int FMT, int M, int NORM>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_trigger();
-    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.x;
     const int per = (p.k_blocks + gridDim.y - 1) / gridDim.y;
     const int kb0 = blockIdx.y * per;
     const int kb1 = min(p.k_blocks, kb0 + per);
     const int nkb = max(kb1 - kb0, 0);
+    // The weights do not depend on the previous kernel: pull this CTA's chunks towards L2 before waiting for it, so that
+    // the HBM latency of the first loads overlaps the predecessor's tail and this kernel's activation prologue.
+    if (!p.items && !p.expert_ids && nkb > 0) {
+        const uint8_t* w0 = p.w + ((size_t)tile * p.k_blocks + kb0) * FmtTraits<FMT>::CHUNK;
+        const int lines = min(nkb * (FmtTraits<FMT>::CHUNK / 128), 2048);          // at most 256 KB per CTA
+        for (int i = tid; i < lines; i += 256) asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + (size_t)i * 128));
+    }
+    pdl_wait();
     // rows of this CTA: consecutive ones, or the (token, slot) pairs of a grouped-expert work item
     int xr[M], orow[M], n_valid = M, expert = -1;
     if (p.items) {
