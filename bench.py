@@ -262,7 +262,7 @@ def main():
     tp = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=600))
         from llaminar_b200.parallel.tp import TPContext
         tp = TPContext.create(dist.group.WORLD, dev)
         log(f"tensor-parallel context: size {tp.size}, fused peer-memory epilogues {'on' if tp.fused else 'off'}")
