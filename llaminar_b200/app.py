@@ -69,6 +69,8 @@ def init_distributed(cfg: OrchestrationConfig):
     backend = cfg.values.get("backend", "auto")
     fused = None if backend == "auto" else (backend == "fused")
     tp = TPContext.create(group, dev, fused=fused) if tp_size > 1 else None
+    if tp is not None:
+        tp.moe_mode = cfg.values.get("moe_expert_mode") or "expert-parallel"
     if tp is not None and cfg.values.get("check_collectives"):
         from .parallel.collective_check import CollectiveOrderChecker
         tp.order_check = CollectiveOrderChecker(group)

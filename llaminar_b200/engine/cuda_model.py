@@ -130,7 +130,7 @@ class CudaModel:
         self.layer_ids = list(range(*layer_range)) if layer_range else list(range(c.n_layers))
         # ---- tensor-parallel slicing plan (replicated when tp is None) ----
         from ..parallel.tp_plan import TPPlan
-        self.plan = TPPlan.build(c, tp.size if tp else 1, tp.rank if tp else 0)
+        self.plan = TPPlan.build(c, tp.size if tp else 1, tp.rank if tp else 0, getattr(tp, "moe_mode", "expert-parallel"))
         pl = self.plan
         self.n_heads_local, self.n_kv_local = pl.n_heads_local, pl.n_kv_local
         self.q_dim, self.kv_dim = pl.n_heads_local * c.head_dim, pl.n_kv_local * c.head_dim

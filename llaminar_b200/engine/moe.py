@@ -50,7 +50,7 @@ def fused_supported(model, L, T: int) -> bool:
     c = model.cfg
     if not hasattr(ops, "moe_route") or T * c.n_experts_used > FUSED_MAX_PAIRS or c.n_experts > 256 or c.d_model % 256:
         return False
-    ep = model.tp is not None and model.tp.size > 1
+    ep = model.tp is not None and model.tp.size > 1 and getattr(model.tp, "moe_mode", "expert-parallel") != "replicated"
     if ep:
         symm = getattr(model.tp, "symm", None)
         if not (model.tp.fused and symm is not None and T <= symm.rows_cap and c.d_model <= symm.n_cap):
@@ -70,7 +70,7 @@ def moe_forward_fused(model, L, h: torch.Tensor, T: int) -> None:
     ops.moe_route(h, L.ffn_norm, c.rms_eps, L.router, k, c.norm_topk_prob, slab.e0, slab.n_local, ws.ids, ws.wts,
                   ws.items, ws.n_items, ws.ticket, ws.counts)
     ops.moe_gate_up(slab.gate_up, h, L.ffn_norm, c.rms_eps, ws.act, ws.items, ws.n_items, k, ws.z_max, scratch=sc)
-    ep = model.tp is not None and model.tp.size > 1
+    ep = model.tp is not None and model.tp.size > 1 and getattr(model.tp, "moe_mode", "expert-parallel") != "replicated"
     symm = getattr(model.tp, "symm", None) if ep else None
     in_kernel = ep and model.tp.fused and symm is not None and T <= symm.rows_cap and c.d_model <= symm.n_cap
     if ep and not in_kernel:
@@ -104,7 +104,7 @@ def moe_forward(model, L, h: torch.Tensor, T: int) -> None:
     lids = torch.where(local, ids - slab.e0, torch.zeros_like(ids)).contiguous()
     w_eff = torch.where(local, wts, torch.zeros_like(wts))
     ff, d = c.expert_ff, c.d_model
-    ep = model.tp is not None and model.tp.size > 1
+    ep = model.tp is not None and model.tp.size > 1 and getattr(model.tp, "moe_mode", "expert-parallel") != "replicated"
     target = model.ws_partial[:T] if ep else h
     if ep:
         target.zero_()

@@ -28,7 +28,7 @@ class TorchPagedModel:
         self.tp = tp
         self.max_tokens = max_tokens
         c = self.cfg
-        pl = self.plan = TPPlan.build(c, tp.size if tp else 1, tp.rank if tp else 0)
+        pl = self.plan = TPPlan.build(c, tp.size if tp else 1, tp.rank if tp else 0, getattr(tp, "moe_mode", "expert-parallel"))
         self.n_heads_local, self.n_kv_local = pl.n_heads_local, pl.n_kv_local
         self.layer_ids = list(range(*layer_range)) if layer_range else list(range(c.n_layers))
         D = c.head_dim
@@ -139,8 +139,10 @@ class TorchPagedModel:
     def _layer(self, L, h, fb, kvl):
         c = self.cfg
         h = h + self._sum_ranks(self._attention(L, rmsnorm(h, L["attn_norm"], c.rms_eps), fb, kvl))
-        h = h + self._sum_ranks(self._ffn(L, rmsnorm(h, L["ffn_norm"], c.rms_eps)))
-        return h
+        y = self._ffn(L, rmsnorm(h, L["ffn_norm"], c.rms_eps))
+        if not (c.is_moe and getattr(self.tp, "moe_mode", "expert-parallel") == "replicated"):
+            y = self._sum_ranks(y)               # replicated experts: every rank already has the full sum
+        return h + y
 
     def _logits(self, h_rows, norm_w, out):
         lg = rmsnorm(h_rows, norm_w, self.cfg.rms_eps) @ self.head.T

@@ -33,6 +33,7 @@ class TPContext:
     symm: object = None                 # parallel.symm.SymmetricArena when fused kernels are available
     stats: dict = field(default_factory=lambda: {"allreduce_calls": 0, "allreduce_bytes": 0, "fused_calls": 0})
     order_check: object = None          # parallel.collective_check.CollectiveOrderChecker in debug mode
+    moe_mode: str = "expert-parallel"   # --moe-expert-mode: expert-parallel | replicated
     skip_allreduce: bool = False        # debug switch LLAMINAR_SKIP_ALLREDUCE (isolates compute time; results are wrong)
 
     @staticmethod

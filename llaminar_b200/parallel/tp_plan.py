@@ -68,7 +68,7 @@ class TPPlan:
         return errs
 
     @staticmethod
-    def build(cfg, tp: int = 1, rank: int = 0) -> "TPPlan":
+    def build(cfg, tp: int = 1, rank: int = 0, moe_mode: str = "expert-parallel") -> "TPPlan":
         errs = TPPlan.validate(cfg, tp)
         if errs:
             raise ValueError("; ".join(errs))
@@ -92,7 +92,13 @@ class TPPlan:
         n_vu = (cfg.vocab_size + VOCAB_UNIT - 1) // VOCAB_UNIT
         v0, v1 = _split(n_vu, tp, rank)
         vs, ve = v0 * VOCAB_UNIT, min(v1 * VOCAB_UNIT, cfg.vocab_size)
-        es, ee = _split(cfg.n_experts, tp, rank) if cfg.is_moe else (0, 0)
+        if moe_mode == "tensor-parallel":
+            raise ValueError("--moe-expert-mode tensor-parallel (every expert split across ranks) is not built; "
+                             "use expert-parallel or replicated")
+        if cfg.is_moe and moe_mode == "replicated":
+            es, ee = 0, cfg.n_experts           # every rank holds and computes all experts: no exchange after the MoE block
+        else:
+            es, ee = _split(cfg.n_experts, tp, rank) if cfg.is_moe else (0, 0)
         return TPPlan(tp, rank, qs, qe, ks, ke, rep, fs, fe, vs, ve, es, ee)
 
     def describe(self) -> str:

@@ -56,3 +56,31 @@ def test_tp_plan_rules():
     assert (p.expert_start, p.expert_stop) == (80, 96)
     assert TPPlan.validate(SHAPES["qwen3-8b"], 3)        # 32 heads are not divisible by 3
     assert not TPPlan.validate(SHAPES["qwen3-8b"], 8)
+
+
+def _tp_generate_replicated(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3moe"], "Q8_0", seed=0)
+    tp = TPContext.create(device="cpu")
+    tp.moe_mode = "replicated"
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=tp)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 40)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    return outs, eng.model.plan.expert_stop - eng.model.plan.expert_start
+
+
+def test_tp2_moe_replicated_experts_matches_single_rank():
+    ref = _single("tiny-qwen3moe", "Q8_0", 5)
+    res = run_ranks(_tp_generate_replicated, 2)
+    assert res[0][0] == ref and res[1][0] == ref
+    assert res[0][1] == SHAPES["tiny-qwen3moe"].n_experts
+
+
+def test_moe_tensor_parallel_mode_is_rejected_by_name():
+    import pytest
+    with pytest.raises(ValueError, match="tensor-parallel"):
+        TPPlan.build(SHAPES["tiny-qwen3moe"], 2, 0, "tensor-parallel")
