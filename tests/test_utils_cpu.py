@@ -1,0 +1,75 @@
+"""Perf-stats collector, environment-switch registry, collective-order checker, device inventory."""
+import json
+
+import pytest
+
+from llaminar_b200.utils.perfstats import PerfStats
+from tests.mp_utils import run_ranks
+
+
+def test_perfstats_records_export_and_filter():
+    p = PerfStats(enabled=True)
+    p.set_phase("prefill")
+    with p.timer("engine", "step", device="cpu", tags=("bs4",)):
+        sum(range(1000))
+    with p.timer("engine", "step", device="cpu", tags=("bs4",)):
+        pass
+    p.set_phase("decode")
+    p.count("kv", "pages_allocated", 3)
+    p.count("kv", "pages_allocated", 2)
+    p.gauge("kv", "free_pages", 17)
+    rows = p.rows()
+    step = next(r for r in rows if r["name"] == "step")
+    assert step["count"] == 2 and step["phase"] == "prefill" and step["tags"] == "bs4" and step["total_ms"] >= step["max_ms"] > 0
+    pages = next(r for r in rows if r["name"] == "pages_allocated")
+    assert pages["value"] == 5 and pages["phase"] == "decode"
+    assert json.loads(p.to_json("kv")) and all(r["domain"] == "kv" for r in json.loads(p.to_json("kv")))
+    csv = p.to_csv()
+    assert csv.splitlines()[0].startswith("domain,name,phase,device,tags") and "free_pages" in csv
+    assert "pages_allocated" in p.table()
+    off = PerfStats(enabled=False)
+    with off.timer("a", "b"):
+        pass
+    off.count("a", "c")
+    assert off.rows() == []
+
+
+def test_env_registry_types_and_unknown_names():
+    from llaminar_b200.utils.env import DebugEnv
+    env = DebugEnv({"LLAMINAR_PROFILING": "true", "LLAMINAR_TP_SPIN_LIMIT": "1000", "LLAMINAR_STAGE_DUMP_DIR": "/x"})
+    assert env.profiling is True and env.tp_spin_limit == 1000 and env.stage_dump_dir == "/x" and env.pdl is True
+    with pytest.raises(KeyError):
+        env.get("LLAMINAR_NOT_A_SWITCH")
+    with pytest.raises(ValueError):
+        DebugEnv({"LLAMINAR_TP_SPIN_LIMIT": "many"}).tp_spin_limit
+    assert "LLAMINAR_TP_FUSED" in env.describe()
+
+
+def _order_check(rank, world, diverge):
+    import torch
+    from llaminar_b200.parallel.collective_check import CollectiveOrderChecker, CollectiveOrderMismatch
+    chk = CollectiveOrderChecker(None, interval=1000)
+    x = torch.zeros(4, 8)
+    for i in range(5):
+        chk.record("all_reduce", x)
+    if diverge and rank == 1:
+        chk.record("all_gather_vocab", x[:, :4])       # rank 1 issues a different collective
+    else:
+        chk.record("all_reduce", x)
+    try:
+        chk.verify()
+        return "same"
+    except CollectiveOrderMismatch as exc:
+        return str(exc)
+
+
+def test_collective_order_checker_names_the_divergence():
+    assert run_ranks(_order_check, 2, False) == ["same", "same"]
+    res = run_ranks(_order_check, 2, True)
+    assert all("diverged" in r and "all_gather_vocab" in r for r in res)
+
+
+def test_device_inventory_shape():
+    from llaminar_b200.utils.devices import describe_devices as describe
+    d = describe()
+    assert "cpu" in d and "gpus" in d and isinstance(d["gpus"], list)
