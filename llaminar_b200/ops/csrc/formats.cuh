@@ -83,8 +83,6 @@ LLM_DEVICE int dp4a_s(uint32_t a, int b, int c) {   // both signed
 template <int F, int M> struct DotBlock;
 
 template <int M> struct DotBlock<FMT_Q4_K, M> {
-    // Activation words of this format are permuted by the GEMV prologue to match the pair words: for every eight columns
-    // x0..x7 the two int8x4 words are (x0, x4, x1, x5) and (x2, x6, x3, x7).
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q4_K>;
         const uint4 meta = ldg_nc_v4(chunk + T::P_META + ((g * 32 + lane) << 4));
@@ -95,23 +93,34 @@ template <int M> struct DotBlock<FMT_Q4_K, M> {
         int sc[8], mn[8];
         unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {                          // sub-block u: 32 weights, one scale / min
-            const uint32_t ws[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-            const float su = d * sc[u], mu = dmin * mn[u];
+        for (int j = 0; j < 4; ++j) {
+            int lo[M], hi[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) lo[m] = hi[m] = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 q = w[2 * j + h];
+                const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const ActBlk& ab = *reinterpret_cast<const ActBlk*>(reinterpret_cast<const uint8_t*>(act) + m * act_stride);
+                    const int4 al = *reinterpret_cast<const int4*>(&ab.a[16 * j + 4 * h]);
+                    const int4 ah = *reinterpret_cast<const int4*>(&ab.a[16 * j + 8 + 4 * h]);
+                    const int as_l[4] = {al.x, al.y, al.z, al.w}, as_h[4] = {ah.x, ah.y, ah.z, ah.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        lo[m] = dp4a_u(ws[i] & 0x0f0f0f0fu, as_l[i], lo[m]);
+                        hi[m] = dp4a_u((ws[i] >> 4) & 0x0f0f0f0fu, as_h[i], hi[m]);
+                    }
+                }
+            }
+            const float s_lo = d * sc[2 * j], s_hi = d * sc[2 * j + 1];
+            const float m_lo = dmin * mn[2 * j], m_hi = dmin * mn[2 * j + 1];
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const ActBlk& ab = *reinterpret_cast<const ActBlk*>(reinterpret_cast<const uint8_t*>(act) + m * act_stride);
-                const int4 a0 = *reinterpret_cast<const int4*>(&ab.a[8 * u]);
-                const int4 a1 = *reinterpret_cast<const int4*>(&ab.a[8 * u + 4]);
-                const int as_[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                int isum = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t un = __funnelshift_r(ws[k], ws[k], 3);          // undo the rotation: plain nibbles
-                    isum = dp4a_u(un & 0x0f0f0f0fu, as_[2 * k], isum);
-                    isum = dp4a_u((un >> 4) & 0x0f0f0f0fu, as_[2 * k + 1], isum);
-                }
-                acc[m] += su * (ab.d[u] * isum) - mu * (ab.ds16[2 * u] + ab.ds16[2 * u + 1]);
+                acc[m] += s_lo * (ab.d[2 * j] * lo[m]) - m_lo * (ab.ds16[4 * j] + ab.ds16[4 * j + 1]);
+                acc[m] += s_hi * (ab.d[2 * j + 1] * hi[m]) - m_hi * (ab.ds16[4 * j + 2] + ab.ds16[4 * j + 3]);
             }
         }
     }
@@ -338,22 +347,6 @@ LLM_DEVICE void affine4(uint32_t w, __nv_bfloat162 offset, __nv_bfloat162 scale,
     o1 = as_u32(__hfma2(__hsub2(as_bf162(magic_pair23(w)), offset), scale, bias));
 }
 
-// Q4_K pair words (see ops/layout.py): word w holds eight consecutive weights; pair j = (n_2j, n_2j+1) as the bf16 pair
-// (16 + n_2j, 16 + n_2j+1) is one rotate and one logic op away.
-LLM_DEVICE uint32_t q4k_pair(uint32_t w, int j) {
-    const uint32_t t = j == 0 ? w : __funnelshift_r(w, w, 4 * j);
-    return (t & 0x00780078u) | 0x41804180u;
-}
-// eight weights of one word -> four bf16 pairs, scaled: (16 + n) * scale + (bias - 16 * scale)
-LLM_DEVICE uint4 q4k_word(uint32_t w, __nv_bfloat162 scale, __nv_bfloat162 bias16) {
-    uint4 o;
-    o.x = as_u32(__hfma2(as_bf162(q4k_pair(w, 0)), scale, bias16));
-    o.y = as_u32(__hfma2(as_bf162(q4k_pair(w, 1)), scale, bias16));
-    o.z = as_u32(__hfma2(as_bf162(q4k_pair(w, 2)), scale, bias16));
-    o.w = as_u32(__hfma2(as_bf162(q4k_pair(w, 3)), scale, bias16));
-    return o;
-}
-
 template <int F> struct DequantBlock;
 // Each format offers
 //   Regs  load(chunk, g, lane)            the row's packed bytes, fetched into registers
@@ -377,18 +370,28 @@ template <> struct DequantBlock<FMT_Q4_K> {
         const float d = half_bits_to_float(r.meta.x & 0xffff), dmin = half_bits_to_float(r.meta.x >> 16);
         int sc[8], mn[8];
         unpack_k4_scales(r.meta.y, r.meta.z, r.meta.w, sc, mn);
+        const __nv_bfloat162 off = __float2bfloat162_rn(128.0f);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             sink.begin(j, 1);
+            const __nv_bfloat162 s_lo = __float2bfloat162_rn(d * sc[2 * j]), b_lo = __float2bfloat162_rn(-dmin * mn[2 * j]);
+            const __nv_bfloat162 s_hi = __float2bfloat162_rn(d * sc[2 * j + 1]), b_hi = __float2bfloat162_rn(-dmin * mn[2 * j + 1]);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {                      // unit 2j + h = sub-block 2j + h: 32 weights, one scale
-                const float sf = d * sc[2 * j + h];
-                const __nv_bfloat162 s2 = __float2bfloat162_rn(sf), b2 = __float2bfloat162_rn(-dmin * mn[2 * j + h] - 16.0f * sf);
+            for (int h = 0; h < 2; ++h) {
                 const uint4 q = r.q[2 * j + h];
-                sink.emit(8 * j + 4 * h + 0, q4k_word(q.x, s2, b2));
-                sink.emit(8 * j + 4 * h + 1, q4k_word(q.y, s2, b2));
-                sink.emit(8 * j + 4 * h + 2, q4k_word(q.z, s2, b2));
-                sink.emit(8 * j + 4 * h + 3, q4k_word(q.w, s2, b2));
+                uint4 o;
+                affine4(q.x & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y);
+                affine4(q.y & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+                sink.emit(8 * j + 2 * h, o);
+                affine4(q.z & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y);
+                affine4(q.w & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+                sink.emit(8 * j + 2 * h + 1, o);
+                affine4((q.x >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y);
+                affine4((q.y >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+                sink.emit(8 * j + 4 + 2 * h, o);
+                affine4((q.z >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y);
+                affine4((q.w >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+                sink.emit(8 * j + 4 + 2 * h + 1, o);
             }
             sink.end(j, 1);
         }

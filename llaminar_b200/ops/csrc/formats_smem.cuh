@@ -38,22 +38,27 @@ template <int A> struct DequantAtom<FMT_Q4_K, A> {
     template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, S& sink) {
         using T = FmtTraits<FMT_Q4_K>;
         const uint4 meta = lds_v4(raw + T::P_META + (((g << 5) + lane) << 4));
-        const uint4 q0 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A, lane));        // sub-block 2A: columns 64A .. 64A + 31
-        const uint4 q1 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A + 1, lane));    // sub-block 2A + 1
+        const uint4 q0 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A, lane));
+        const uint4 q1 = lds_v4(raw + unit_off(T::P_QS, 8, g, 2 * A + 1, lane));
         const float d = half_bits_to_float(meta.x & 0xffff), dmin = half_bits_to_float(meta.x >> 16);
         int sc[8], mn[8];
         unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
-        const float f_lo = d * sc[2 * A], f_hi = d * sc[2 * A + 1];
-        const __nv_bfloat162 s_lo = __float2bfloat162_rn(f_lo), b_lo = __float2bfloat162_rn(-dmin * mn[2 * A] - 16.0f * f_lo);
-        const __nv_bfloat162 s_hi = __float2bfloat162_rn(f_hi), b_hi = __float2bfloat162_rn(-dmin * mn[2 * A + 1] - 16.0f * f_hi);
-        sink.emit(0, q4k_word(q0.x, s_lo, b_lo));
-        sink.emit(1, q4k_word(q0.y, s_lo, b_lo));
-        sink.emit(2, q4k_word(q0.z, s_lo, b_lo));
-        sink.emit(3, q4k_word(q0.w, s_lo, b_lo));
-        sink.emit(4, q4k_word(q1.x, s_hi, b_hi));
-        sink.emit(5, q4k_word(q1.y, s_hi, b_hi));
-        sink.emit(6, q4k_word(q1.z, s_hi, b_hi));
-        sink.emit(7, q4k_word(q1.w, s_hi, b_hi));
+        const __nv_bfloat162 off = __float2bfloat162_rn(128.0f);
+        const __nv_bfloat162 s_lo = __float2bfloat162_rn(d * sc[2 * A]), b_lo = __float2bfloat162_rn(-dmin * mn[2 * A]);
+        const __nv_bfloat162 s_hi = __float2bfloat162_rn(d * sc[2 * A + 1]), b_hi = __float2bfloat162_rn(-dmin * mn[2 * A + 1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 q = h ? q1 : q0;
+            uint4 o;
+            affine4(q.x & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y); affine4(q.y & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h, o);
+            affine4(q.z & 0x0f0f0f0fu, off, s_lo, b_lo, o.x, o.y); affine4(q.w & 0x0f0f0f0fu, off, s_lo, b_lo, o.z, o.w);
+            sink.emit(2 * h + 1, o);
+            affine4((q.x >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y); affine4((q.y >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h, o);
+            affine4((q.z >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.x, o.y); affine4((q.w >> 4) & 0x0f0f0f0fu, off, s_hi, b_hi, o.z, o.w);
+            sink.emit(4 + 2 * h + 1, o);
+        }
     }
 };
 

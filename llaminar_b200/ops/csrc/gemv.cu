@@ -17,7 +17,7 @@
 
 namespace llm {
 
-template <int M, int NORM, bool PERM>
+template <int M, int NORM>
 LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* acts, float* s_red, const int (&xr)[M]) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float rms[M];
@@ -47,28 +47,15 @@ LLM_DEVICE void gemv_prologue(const GemvParams& p, int kb0, int nkb, ActBlk* act
     const int n_quads = nkb * 64;
     for (int m = 0; m < M; ++m) {
         for (int qd = tid; qd < n_quads; qd += blockDim.x) {
+            const int col = kb0 * 256 + qd * 4;
             float v0, v1, v2, v3;
-            if constexpr (PERM) {
-                // pair-word formats (Q4_K): the two words of every eight columns x0..x7 are (x0, x4, x1, x5) and (x2, x6, x3, x7)
-                const int col = kb0 * 256 + (qd >> 1) * 8 + (qd & 1) * 2;
-                if (NORM) {
-                    const float* xr_ = static_cast<const float*>(p.x) + (size_t)xr[m] * p.x_stride + col;
-                    const float* gw = p.norm_w + col;
-                    v0 = xr_[0] * rms[m] * gw[0]; v1 = xr_[4] * rms[m] * gw[4]; v2 = xr_[1] * rms[m] * gw[1]; v3 = xr_[5] * rms[m] * gw[5];
-                } else {
-                    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.x) + (size_t)xr[m] * p.x_stride + col;
-                    v0 = __bfloat162float(xb[0]); v1 = __bfloat162float(xb[4]); v2 = __bfloat162float(xb[1]); v3 = __bfloat162float(xb[5]);
-                }
+            if (NORM) {
+                const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)xr[m] * p.x_stride + col);
+                const float4 g = *reinterpret_cast<const float4*>(p.norm_w + col);
+                v0 = v.x * rms[m] * g.x; v1 = v.y * rms[m] * g.y; v2 = v.z * rms[m] * g.z; v3 = v.w * rms[m] * g.w;
             } else {
-                const int col = kb0 * 256 + qd * 4;
-                if (NORM) {
-                    const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)xr[m] * p.x_stride + col);
-                    const float4 g = *reinterpret_cast<const float4*>(p.norm_w + col);
-                    v0 = v.x * rms[m] * g.x; v1 = v.y * rms[m] * g.y; v2 = v.z * rms[m] * g.z; v3 = v.w * rms[m] * g.w;
-                } else {
-                    const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)xr[m] * p.x_stride + col);
-                    v0 = bf16_lo(v.x); v1 = bf16_hi(v.x); v2 = bf16_lo(v.y); v3 = bf16_hi(v.y);
-                }
+                const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)xr[m] * p.x_stride + col);
+                v0 = bf16_lo(v.x); v1 = bf16_hi(v.x); v2 = bf16_lo(v.y); v3 = bf16_hi(v.y);
             }
             float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -130,7 +117,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     if (FMT == FMT_IQ3_S) {
         for (int i = tid; i < 512; i += blockDim.x) s_grid[i] = g_iq3s_grid[i];
     }
-    gemv_prologue<M, NORM, FMT == FMT_Q4_K>(p, kb0, nkb, acts, s_red, xr);
+    gemv_prologue<M, NORM>(p, kb0, nkb, acts, s_red, xr);
 
     const uint8_t* wbase = p.w;
     if (expert >= 0) wbase += (size_t)expert * p.expert_stride;

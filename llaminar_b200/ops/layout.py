@@ -67,8 +67,6 @@ class PackedWeight:
 def _planes_of(qtype: GGMLType, blocks: torch.Tensor) -> list[torch.Tensor]:
     """blocks: [N, KB, bytes per 256 columns] -> list of [N, KB, R] planes."""
     n, kb, _ = blocks.shape
-    if qtype == GGMLType.Q4_K:
-        return [_q4k_pair_words(blocks[:, :, 16:144]), blocks[:, :, 0:16]]
     if qtype in _PLANES:
         return [blocks[:, :, off:off + r] for off, r in _PLANES[qtype]]
     if qtype == GGMLType.Q8_0:
@@ -78,28 +76,6 @@ def _planes_of(qtype: GGMLType, blocks: torch.Tensor) -> list[torch.Tensor]:
         v = blocks.reshape(n, kb, 8, 18)
         return [v[..., 2:].reshape(n, kb, 128), v[..., :2].reshape(n, kb, 16)]
     raise NotImplementedError(qtype)
-
-
-def _q4k_pair_words(qs: torch.Tensor) -> torch.Tensor:
-    """Q4_K nibbles [N, KB, 128 bytes] -> the same 128 bytes per row, regrouped for the kernels.
-
-    GGUF stores element i of sub-block 2j in the low nibble and element i of sub-block 2j + 1 in the high nibble of byte
-    32 j + i.  Here every sub-block (32 elements, one scale) becomes four 32-bit words of eight consecutive elements
-    n0..n7 each, laid out as ``rotl32(n0 | n2<<4 | n4<<8 | n6<<12 | n1<<16 | n3<<20 | n5<<24 | n7<<28, 3)``:
-    ``(rotr32(w, 4 j) & 0x00780078) | 0x41804180`` is then the bf16 pair (16 + n_2j, 16 + n_2j+1), one logic op per two
-    weights, and the 16 folds into the bias of the scale FMA (its bf16 rounding error is 1/32 of a quantisation step; with
-    the nibble in the low mantissa bits the magic number would be 128 and the error a quarter step).
-    """
-    n, kb, _ = qs.shape
-    g = qs.reshape(n, kb, 4, 32)
-    q = torch.stack([g & 0x0F, g >> 4], dim=3).reshape(n, kb, 8, 4, 8).to(torch.int64)       # [.., sub-block, word, element]
-    order = (0, 2, 4, 6, 1, 3, 5, 7)
-    packed = torch.zeros(n, kb, 8, 4, dtype=torch.int64, device=qs.device)
-    for slot, e in enumerate(order):
-        packed |= q[..., e] << (4 * slot)
-    rot = ((packed << 3) | (packed >> 29)) & 0xFFFFFFFF
-    b = torch.stack([(rot >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)     # little-endian bytes
-    return b.reshape(n, kb, 128)
 
 
 def can_pack(qtype: GGMLType, k: int) -> bool:

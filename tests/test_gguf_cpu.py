@@ -104,26 +104,3 @@ def test_model_checkpoint_round_trip(tmp_path):
         assert r[name].qtype == w[name].qtype and torch.equal(r[name].raw.cpu(), w[name].raw.cpu())
     assert "tokenizer.ggml.tokens" in r.metadata
 
-
-def test_q4k_pair_word_layout_decodes_to_the_same_weights():
-    """The load-time regrouping of Q4_K nibbles: (rotr(w, 4j) & 0x00780078) | 0x41804180 must be the bf16 pair (16 + n_2j, 16 + n_2j+1)."""
-    from llaminar_b200.ops.layout import _q4k_pair_words
-    g = torch.Generator().manual_seed(0)
-    n, k = 6, 768
-    raw = quantize(torch.randn(n, k, generator=g) * 0.02, GGMLType.Q4_K)
-    blocks = raw.reshape(n, k // 256, 144)
-    qs = blocks[:, :, 16:144]
-    words = _q4k_pair_words(qs).reshape(n, k // 256, 8, 4, 4).to(torch.int64)
-    w = words[..., 0] | (words[..., 1] << 8) | (words[..., 2] << 16) | (words[..., 3] << 24)          # [n, kb, sub-block, word]
-    got = torch.zeros(n, k // 256, 8, 4, 8, dtype=torch.int64)
-    for j in range(4):
-        t = ((w >> (4 * j)) | (w << (32 - 4 * j))) & 0xFFFFFFFF
-        pair = (t & 0x00780078) | 0x41804180
-        for half, shift in ((0, 0), (1, 16)):
-            bits = ((pair >> shift) & 0xFFFF) << 16                                                     # bf16 -> fp32 bit pattern
-            val = bits.to(torch.int32).view(torch.float32)
-            got[..., 2 * j + half] = (val - 16.0).round().to(torch.int64)
-    # reference nibbles: byte 32 j + i holds element i of sub-block 2j (low) and of sub-block 2j + 1 (high)
-    grp = qs.reshape(n, k // 256, 4, 32).to(torch.int64)
-    ref = torch.stack([grp & 0xF, grp >> 4], dim=3).reshape(n, k // 256, 8, 4, 8)
-    assert torch.equal(got, ref)
