@@ -232,6 +232,54 @@ class ChatCompletionHandler:
                 "model": req.model or self.model_name, "system_fingerprint": SYSTEM_FINGERPRINT,
                 "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": self._usage(info)}
 
+    # -- raw text completion (no chat template) ---------------------------------------------------------------
+    def complete(self, body_bytes: bytes) -> dict:
+        """`/v1/completions`: the prompt is tokenised as is (the reference's completion mode,
+        src/v2/app/modes/CompletionMode.cpp); returns the OpenAI text_completion object."""
+        try:
+            body = json.loads(body_bytes)
+        except Exception as exc:
+            raise RequestError(f"request body is not valid JSON: {exc}") from exc
+        if not isinstance(body, dict) or not isinstance(body.get("prompt"), str) or not body["prompt"]:
+            raise RequestError("`prompt` must be a non-empty string", param="prompt")
+        ids = self.tok.encode(body["prompt"], add_special=True)
+        if len(ids) + 1 >= self.max_context:
+            raise RequestError(f"prompt of {len(ids)} tokens does not fit the context window of {self.max_context}",
+                               err_type="context_length_exceeded")
+        given = {k: body[k] for k in ("temperature", "top_p", "top_k", "seed", "presence_penalty", "frequency_penalty") if k in body}
+        for k, v in given.items():
+            if not isinstance(v, (int, float)) or isinstance(v, bool):
+                raise RequestError(f"`{k}` must be a number", param=k)
+        sp = merge_with_model_defaults(self.arch, given, self.cli_sampling)
+        budget = self.max_context - len(ids) - 1
+        mt = body.get("max_tokens", 16)
+        if not isinstance(mt, int) or isinstance(mt, bool) or mt < 1:
+            raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
+        sp.max_tokens = min(mt, budget)
+        sp.stop_token_ids = tuple(self.eos_ids)
+        ticket = self.loop.submit(ids, sp)
+        dec = StreamDecoder(self.tok, skip_special=True)
+        parts, n, finish = [], 0, "stop"
+        while True:
+            try:
+                ev = ticket.events.get(timeout=600)
+            except queue.Empty:
+                raise RequestError("generation timed out", 500, "server_error")
+            if ev[0] == "error":
+                raise RequestError(ev[1], ev[2] if len(ev) > 2 else 500, "server_error")
+            if ev[0] == "done":
+                finish = ev[1] or "stop"
+                break
+            for tid in ev[1]:
+                n += 1
+                if tid not in self.eos_ids:
+                    parts.append(dec.push(tid))
+        parts.append(dec.flush())
+        return {"id": "cmpl-" + uuid.uuid4().hex[:24], "object": "text_completion", "created": int(time.time()),
+                "model": body.get("model") or self.model_name,
+                "choices": [{"index": 0, "text": "".join(parts), "finish_reason": "length" if finish == "length" else "stop"}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": n, "total_tokens": len(ids) + n}}
+
     # -- streaming (server-sent events) -------------------------------------------------------------------------
     def stream(self, req: ChatRequest) -> Iterator[bytes]:
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]

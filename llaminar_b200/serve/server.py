@@ -52,6 +52,18 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
                 self._send_json(404, {"error": {"message": f"unknown path {self.path}", "type": "invalid_request_error"}})
 
         def do_POST(self):
+            if self.path.rstrip("/") == "/v1/completions":
+                try:
+                    n = int(self.headers.get("Content-Length") or 0)
+                    if n <= 0 or n > MAX_BODY:
+                        raise RequestError("missing or oversized request body")
+                    self._send_json(200, chat.complete(self.rfile.read(n)))
+                    state["served"] += 1
+                except RequestError as exc:
+                    self._send_json(exc.status, exc.body())
+                except Exception as exc:
+                    self._send_json(500, {"error": {"message": f"{type(exc).__name__}: {exc}", "type": "server_error"}})
+                return
             if self.path.rstrip("/") != "/v1/chat/completions":
                 self._send_json(404, {"error": {"message": f"unknown path {self.path}", "type": "invalid_request_error"}})
                 return

@@ -126,3 +126,14 @@ def test_chat_template_renders_tools_and_thinking():
     assert "<|im_start|>system\nsys<|im_end|>" in s and s.rstrip().endswith("<|im_start|>assistant")
     with pytest.raises(Exception):
         ChatTemplate("{{ raise_exception('bad') }}").render([])
+
+
+def test_text_completion_endpoint(server):
+    st, body, _ = _post(server, {"prompt": "once upon a time", "max_tokens": 5, "temperature": 0}, path="/v1/completions")
+    assert st == 200
+    j = json.loads(body)
+    assert j["object"] == "text_completion" and j["usage"]["completion_tokens"] <= 5 and isinstance(j["choices"][0]["text"], str)
+    st, body, _ = _post(server, {"prompt": "", "max_tokens": 5}, path="/v1/completions")
+    assert st == 400 and json.loads(body)["error"]["param"] == "prompt"
+    st, body, _ = _post(server, {"prompt": "x", "max_tokens": 0}, path="/v1/completions")
+    assert st == 400
