@@ -514,31 +514,46 @@ class LLMEngine:
         return self._sample_rows(logits, reqs)
 
     def _fill_decode_host(self, reqs: list[Request], bucket: int, v: dict) -> None:
-        h = self._dec_host
+        """Writes the step's inputs into the pinned staging buffer (numpy views; one slice assignment per field).  Lanes
+        keep their contents between steps: while the set of running requests is unchanged only the token, position and
+        length of every lane, and the page-table rows that grew, are rewritten."""
+        import numpy as np
+        if getattr(self, "_np_dec", None) is None:
+            self._np_dec = self._dec_host.numpy()
+            self._np_fl = self._fl_host.numpy()
+            self._np_seed = self._seed_host.numpy()
+            self._lane_sig = None
+        h = self._np_dec
         P = self.max_pages_per_seq
         B = len(reqs)
         tok, pos, ln = h[v["tok"]], h[v["pos"]], h[v["len"]]
-        bt = h[v["bt"]].view(bucket, P)
-        topk, step = h[v["topk"]], h[v["step"]]
-        temp, topp = self._fl_host[:bucket], self._fl_host[bucket:2 * bucket]
-        h[v["sid"]] = torch.arange(bucket, dtype=torch.int32)       # a decode batch uses block-table rows 0..bucket-1
+        bt = h[v["bt"]].reshape(bucket, P)
+        n_tok = np.fromiter((r.n_tokens for r in reqs), dtype=np.int32, count=B)
+        tok[:B] = np.fromiter((r.output[-1] for r in reqs), dtype=np.int32, count=B)
+        pos[:B] = n_tok - 1
+        ln[:B] = n_tok
+        h[v["step"]][:B] = np.fromiter((len(r.output) for r in reqs), dtype=np.int32, count=B)
+        sig = (bucket, tuple(r.rid for r in reqs))
+        if sig != self._lane_sig:
+            self._lane_sig = sig
+            self._lane_pages = [0] * B
+            h[v["sid"]] = np.arange(bucket, dtype=np.int32)        # a decode batch uses block-table rows 0..bucket-1
+            h[v["topk"]][:B] = np.fromiter((r.params.top_k for r in reqs), dtype=np.int32, count=B)
+            temp, topp = self._np_fl[:bucket], self._np_fl[bucket:2 * bucket]
+            temp[:B] = [0.0 if r.params.is_greedy else r.params.temperature for r in reqs]
+            topp[:B] = [r.params.top_p for r in reqs]
+            self._np_seed[:B] = [r.params.seed if r.params.seed is not None else (r.rid * 7919 + 17) for r in reqs]
+            if B < bucket:                              # padded lanes point at the scratch page
+                tok[B:bucket] = 0
+                pos[B:bucket] = 0
+                ln[B:bucket] = 1
+                bt[B:bucket] = 0
+                temp[B:bucket] = 0.0
         for i, r in enumerate(reqs):
-            tok[i] = r.output[-1]
-            pos[i] = r.n_tokens - 1
-            ln[i] = r.n_tokens
             npg = len(r.kv.pages)
-            bt[i, :npg] = torch.as_tensor(r.kv.pages, dtype=torch.int32)
-            topk[i] = r.params.top_k
-            step[i] = len(r.output)
-            temp[i] = 0.0 if r.params.is_greedy else r.params.temperature
-            topp[i] = r.params.top_p
-            self._seed_host[i] = r.params.seed if r.params.seed is not None else (r.rid * 7919 + 17)
-        if B < bucket:                                  # padded lanes point at the scratch page
-            tok[B:bucket] = 0
-            pos[B:bucket] = 0
-            ln[B:bucket] = 1
-            bt[B:bucket].zero_()
-            temp[B:bucket] = 0.0
+            if npg != self._lane_pages[i]:
+                bt[i, :npg] = r.kv.pages
+                self._lane_pages[i] = npg
 
     def _decode_cuda(self, reqs: list[Request], eager: bool) -> list[int]:
         from .. import ops
