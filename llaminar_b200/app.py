@@ -127,6 +127,8 @@ def build_engine(cfg: OrchestrationConfig):
     eos = tok.eos_id if tok is not None else None
     kw = dict(device=dev, max_batch=v["batch_size"], max_context=v["ctx_size"], prefix_cache=prefix, mtp=mtp, tp=tp,
               eos_token_id=eos)
+    if torch.device(dev).type == "cpu" and "kv_cache_precision" in cfg.explicitly_set:
+        kw["kv_dtype"] = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[v["kv_cache_precision"]]
     if layout["pp"] > 1:
         from .parallel.pp import build_pipeline_engine
         engine = build_pipeline_engine(weights, layout, rank, **kw)

@@ -339,6 +339,12 @@ def validate(cfg: OrchestrationConfig) -> list[str]:
         errs.append("-tp must be >= 1")
     if v.get("backend") in ("mpi", "rccl", "host"):
         errs.append(f"--backend {v['backend']}: not supported on this build (NCCL / fused NVLink / gloo only)")
+    on_cpu = str(v.get("device") or "").startswith("cpu") or (cfg.tp_devices_list() and all(d.startswith("cpu") for d in cfg.tp_devices_list())) \
+        or (cfg.domains and all(dev.startswith("cpu") for d in cfg.domains for dev in d.devices))
+    if not on_cpu and v.get("kv_cache_precision") in ("fp16", "fp32") and "kv_cache_precision" in ex:
+        errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: the CUDA kernels keep the KV cache in bf16 (fp16 / fp32 are available with -d cpu)")
+    if not on_cpu and v.get("activation_precision") in ("fp16", "fp32") and "activation_precision" in ex:
+        errs.append(f"--activation-precision {v['activation_precision']}: the CUDA path uses bf16 GEMM operands with an fp32 residual stream (fp32 is available with -d cpu)")
     if v.get("kv_cache_precision") in ("q8_1", "tq4", "tq8"):
         errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: quantised KV caches are not built (bf16/fp16/fp32)")
     if not 1 <= int(v.get("mtp_draft_tokens") or 1) <= 3:

@@ -65,7 +65,7 @@ class LLMEngine:
     def __init__(self, weights: ModelWeights, device: str | torch.device | None = None, max_batch: int = 32,
                  max_context: int = 4096, kv_pages: int | None = None, max_prefill_tokens: int = 8192,
                  use_graphs: bool = True, prefix_cache=None, mtp=None, tp=None, eos_token_id: int | None = None,
-                 model=None, kv_memory_fraction: float = 0.85):
+                 model=None, kv_memory_fraction: float = 0.85, kv_dtype: torch.dtype | None = None):
         self.cfg: ModelConfig = weights.config if weights is not None else model.cfg
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -95,7 +95,7 @@ class LLMEngine:
             else:
                 kv_pages = need
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
-                               dtype=torch.bfloat16 if self.is_cuda else torch.float32)
+                               dtype=torch.bfloat16 if self.is_cuda else (kv_dtype or torch.float32))
         self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
         self.perf = perf_stats()
         self._graphs: dict = {}

@@ -127,3 +127,14 @@ def test_cli_chat_reads_turns_from_stdin():
                        input="hello\n/reset\nagain\n/exit\n", capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
     assert r.stdout.count("> ") >= 3
+
+
+def test_precision_flags_are_checked_against_the_device():
+    with pytest.raises(ConfigError) as e:
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--kv-cache-precision", "fp16"])
+    assert "bf16" in str(e.value)
+    c = parse_args(["oneshot", "--synthetic", "tiny-qwen3", "-d", "cpu", "--kv-cache-precision", "fp16"])
+    assert c.values["kv_cache_precision"] == "fp16"
+    rc, out, err = _cli("oneshot", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0", "-d", "cpu", "--kv-cache-precision", "bf16",
+                        "-p", "hi", "-n", "3")
+    assert rc == 0, err
