@@ -63,6 +63,7 @@ LLM_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); 
 
 LLM_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-LLM_DEVICE float silu(float x) { return x / (1.0f + __expf(-x)); }
+// branch-free: the approximate division has no slow path for huge or infinite denominators (they give 0, the right limit)
+LLM_DEVICE float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 }  // namespace llm

@@ -84,12 +84,21 @@ LLM_DEVICE void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_
 LLM_DEVICE void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-LLM_DEVICE void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+// 32 accumulator columns of this warp's 32 TMEM lanes; the values may be read only after tmem_wait_ld on the same array
+LLM_DEVICE void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
+}
+// Completes every tcgen05.ld of this thread; the empty statements tie the array to the wait so that no use of it is scheduled earlier.
+LLM_DEVICE void tmem_wait_ld(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]));
 }
 
 template <int BM> struct Cfg {
@@ -238,6 +247,8 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     __shared__ uint32_t s_grid[FMT == FMT_IQ3_S ? 512 : 1];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned long long t_entry;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_entry));
     // fused all-gather: a linear grid whose first `copy_ctas` CTAs stage the activation rows (ag_copier) and whose other
     // CTAs take the output tiles n-fastest, with the m-tiles rotated so that the rows this rank owns come first
     int tile_n = blockIdx.x, tile_m = blockIdx.y, n_tiles_grid = gridDim.x;
@@ -281,8 +292,16 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     volatile int* abort_flag = s_abort;
     const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
 
+    const bool timing = p.debug && (p.flags & 0x100);
+    auto ts = [&](int slot) {
+        if (timing) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            reinterpret_cast<unsigned long long*>(p.debug)[(size_t)cta_lin * 8 + slot] = t;
+        }
+    };
     auto trace = [&](int slot, int value) {
-        if (p.debug) {
+        if (p.debug && !timing) {
             volatile int* d = p.debug + (size_t)cta_lin * 8;
             d[slot] = value;
             __threadfence_system();
@@ -291,6 +310,9 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     if (tid == 0) {
         uint32_t smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        ts(1);
+        if (timing) reinterpret_cast<unsigned long long*>(p.debug)[(size_t)cta_lin * 8 + 0] = t_entry;
+        if (timing) reinterpret_cast<unsigned long long*>(p.debug)[(size_t)cta_lin * 8 + 7] = smid;
         trace(0, (int)smid + 1);
         trace(1, (int)tmem_base);
     }
@@ -351,6 +373,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
                 ring_slot<C::STAGES>(it, stage, phase);
                 ok = mbar_wait(full_bar + stage * 8, phase, abort_flag);
                 if (!ok) break;
+                if (it == 0) ts(2);
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + stage * C::STAGE_BYTES;
                 const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + A_ATOM_BYTES);
@@ -363,6 +386,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
                 trace(2, it + 1);
             }
             if (ok) mma_commit(accum_bar);
+            ts(3);
             trace(2, ok ? 1000 + n_it : -1);
         }
     }
@@ -371,71 +395,98 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     bool live = warp < 8;
     if (live && n_it > 0) live = mbar_wait(accum_bar, 0, abort_flag);
     if (*abort_flag) live = false;
+    live = __all_sync(0xffffffffu, live);          // warp-uniform: the epilogue exchanges values between lanes
+    if (tid == 0) ts(4);
     tc_fence_after();
     const int q = warp & 3, half = (warp >> 2) & 1;
     const int row_in_tile = q * 32 + lane;
     const int n_row = tile_n * 128 + row_in_tile;
     constexpr int HALF_COLS = BM / 2;
-    constexpr int CHUNKS = HALF_COLS / 16;
+    constexpr int LOADS = HALF_COLS / 32;          // TMEM loads of 32 columns per warp
+    static_assert(HALF_COLS % 32 == 0, "the epilogue reads the accumulator 32 columns at a time");
     const bool split = gridDim.z > 1;
+    const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF_COLS;
 
-    auto finish = [&](int c0, float (&v)[16]) {
+    auto finish = [&](int c0, const float (&v)[32]) {
         // v[i]: value for token m0 + c0 + i, output row n_row
         const int m_base = tile_m * BM + c0;
         if (p.epi == EPI_SWIGLU) {
-            // rows of a 32-row group: 16 gate rows then the 16 matching up rows -> pair lanes l and l + 16
+            // rows of a 32-row group: 16 gate rows then the 16 matching up rows.  Lanes l and l + 16 hold one output
+            // column; the lower lane finishes the even tokens and the upper lane the odd ones, so one exchange serves two.
             const int col = tile_n * 64 + q * 16 + (lane & 15);
+            const bool lower = lane < 16;
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)(m_base + (lower ? 0 : 1)) * p.out_stride + col;
+            const bool col_ok = col < p.n / 2;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                const int m = m_base + i;
-                if (lane < 16 && m < p.m && col < p.n / 2)
-                    static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.out_stride + col] = __float2bfloat16(silu(v[i]) * other);
+            for (int j = 0; j < 16; ++j) {
+                const float got = __shfl_xor_sync(0xffffffffu, lower ? v[2 * j + 1] : v[2 * j], 16);
+                const float gate = lower ? v[2 * j] : got, up = lower ? got : v[2 * j + 1];
+                if (col_ok && m_base + 2 * j + (lower ? 0 : 1) < p.m) o[(size_t)(2 * j) * p.out_stride] = __float2bfloat16(silu(gate) * up);
             }
             return;
         }
         if (n_row >= p.n) return;
         const float b = p.bias ? p.bias[n_row] : 0.f;
+        if (p.epi == EPI_RESID) {
+            float* h = static_cast<float*>(p.out) + (size_t)m_base * p.out_stride + n_row;
+            float old[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 32; ++i) old[i] = (m_base + i < p.m) ? h[(size_t)i * p.out_stride] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (m_base + i < p.m) h[(size_t)i * p.out_stride] = old[i] + v[i] + b;
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
             const int m = m_base + i;
             if (m >= p.m) continue;
             const size_t idx = (size_t)m * p.out_stride + n_row;
-            const float o = v[i] + b;
-            if (p.epi == EPI_RESID) { float* h = static_cast<float*>(p.out); h[idx] += o; }
-            else if (p.out_f32) static_cast<float*>(p.out)[idx] = o;
-            else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(o);
+            if (p.out_f32) static_cast<float*>(p.out)[idx] = v[i] + b;
+            else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(v[i] + b);
+        }
+    };
+    // Walks this warp's accumulator columns 32 at a time, the next load in flight while `use` works on the current one.
+    auto for_each_load = [&](auto&& use) {
+        uint32_t ra[32], rb[32];
+        tmem_ld32_issue(tmem_warp, ra);
+#pragma unroll
+        for (int c = 0; c < LOADS; c += 2) {
+            tmem_wait_ld(ra);
+            if (c + 1 < LOADS) tmem_ld32_issue(tmem_warp + (c + 1) * 32, rb);
+            use(half * HALF_COLS + c * 32, ra);
+            if (c + 1 < LOADS) {
+                tmem_wait_ld(rb);
+                if (c + 2 < LOADS) tmem_ld32_issue(tmem_warp + (c + 2) * 32, ra);
+                use(half * HALF_COLS + (c + 1) * 32, rb);
+            }
         }
     };
 
-    if (warp < 8 && !split) {
-        for (int c = 0; c < CHUNKS; ++c) {
-            const int c0 = half * HALF_COLS + c * 16;
-            float v[16];
-            if (live && n_it > 0) {
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+    if (warp < 8 && !split && live) {
+        if (n_it > 0) {
+            for_each_load([&](int c0, const uint32_t (&r)[32]) {
+                float v[32];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-            } else {
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                finish(c0, v);
+            });
+        } else {
+            float v[32];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
-            }
-            if (live) finish(c0, v);
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int c = 0; c < LOADS; ++c) finish(half * HALF_COLS + c * 32, v);
         }
     }
     if (split) {
         if (warp < 8 && live && n_it > 0) {
-            for (int c = 0; c < CHUNKS; ++c) {
-                const int c0 = half * HALF_COLS + c * 16;
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r);
+            for_each_load([&](int c0, const uint32_t (&r)[32]) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 32; ++i) {
                     const int m = tile_m * BM + c0 + i;
                     if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], __uint_as_float(r[i]));
                 }
-            }
+            });
         }
         __threadfence();
         __syncthreads();
@@ -447,11 +498,11 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         __syncthreads();
         if (s_last && warp < 8) {
             __threadfence();
-            for (int c = 0; c < CHUNKS; ++c) {
-                const int c0 = half * HALF_COLS + c * 16;
-                float v[16];
+            for (int c = 0; c < LOADS; ++c) {
+                const int c0 = half * HALF_COLS + c * 32;
+                float v[32];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 32; ++i) {
                     const int m = tile_m * BM + c0 + i;
                     v[i] = 0.f;
                     if (m < p.m) {
@@ -466,9 +517,10 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     }
 
     // ------------------------------ teardown ------------------------------
-    if (tid == 0) trace(6, live ? 1 : -1);
+    if (tid == 0) { trace(6, live ? 1 : -1); ts(5); }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) ts(6);
     if (tid == 0) trace(6, *abort_flag ? -2 : 2);
     if (*abort_flag) {
         if (tid == 0 && p.status) atomicExch(p.status, (int)STATUS_TIMEOUT);
@@ -557,7 +609,6 @@ void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* kspli
 template <int FMT>
 static cudaError_t launch_fmt(const GemmTcParams& p, int bm, int ks, cudaStream_t st) {
     switch (bm) {
-        case 32: return tc::launch_one<FMT, 32>(p, ks, st);
         case 64: return tc::launch_one<FMT, 64>(p, ks, st);
         case 128: return tc::launch_one<FMT, 128>(p, ks, st);
         case 256: return tc::launch_one<FMT, 256>(p, ks, st);

@@ -44,6 +44,9 @@ def main() -> int:
     ap.add_argument("--case", required=True, choices=["gemm_small", "gemv", "gemm_large", "attn_decode", "attn_prefill", "moe"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--fmt", default="Q4_K")
+    ap.add_argument("--m", type=int, default=0, help="rows of activations (GEMM cases; default: the case's own)")
+    ap.add_argument("--n", type=int, default=51200)
+    ap.add_argument("--k", type=int, default=5120)
     args = ap.parse_args()
     from .. import ops
     from ..gguf import GGMLType
@@ -53,8 +56,8 @@ def main() -> int:
     g = torch.Generator(device=dev).manual_seed(0)
     rec = {"case": args.case}
     if args.case in ("gemm_small", "gemv", "gemm_large"):
-        n, k = 51200, 5120                                  # gate|up of the Qwen3-32B shape: 147 MB of Q4_K, larger than L2
-        m = {"gemm_small": 32, "gemv": 1, "gemm_large": 1024}[args.case]
+        n, k = args.n, args.k                               # default: gate|up of the Qwen3-32B shape, 147 MB of Q4_K, larger than L2
+        m = args.m or {"gemm_small": 32, "gemv": 1, "gemm_large": 1024}[args.case]
         pws = [_rand_weight(ops, qt, n, k, dev, s) for s in (1, 2)]
         x = (torch.randn(m, k, device=dev, generator=g) * 0.1).to(torch.bfloat16)
         out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=dev)
