@@ -96,6 +96,13 @@ LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+LLM_DEVICE unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+LLM_DEVICE void red_release_gpu_add(unsigned* p, unsigned v) { asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+
 template <int FMT, int BM> struct Cfg {
     static_assert(BM == 32, "the small-batch kernel is built for one 32-token tile");
     static constexpr int B_ATOM_BYTES = BM * 128;         // activation tile: BM tokens x 64 columns, 128B-swizzled
@@ -177,7 +184,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     using C = Cfg<FMT, BM>;
     constexpr int R = C::RAW_SLOTS;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi;
+    __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi, s_sig;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort[2], s_last, s_tp_ok;
     __shared__ unsigned s_tp_epoch, s_tp_epoch2;
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     const uint32_t raw_base = smem_base + C::RING_BYTES;       // activation ring first, raw weight chunks behind it
     const uint32_t full_bar = smem_u32(s_full), empty_bar = smem_u32(s_empty);
     const uint32_t rawf_bar = smem_u32(s_raw_full), rawe_bar = smem_u32(s_raw_empty);
-    const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi);
+    const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi), sig_bar = smem_u32(&s_sig);
 
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
@@ -199,6 +206,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
+        mbar_init(sig_bar, N_DQ_WARPS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -265,63 +273,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
             }
             pend_set = -1;
         };
-        while (ok && it.next(u)) {
-            for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
-                if (C::TWO_SETS && (cc & 1) != ws) continue;
-                const int slot = cc % R, rphase = (cc / R) & 1;
-                const int set = set_of(cc);
-                ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
-                if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
-                if (!ok) break;
-                publish();
-                const uint32_t raw = raw_base + slot * C::CHUNK;
-                const uint32_t a_base = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
-                if constexpr (C::TWO_SETS) {
-                    if constexpr (FMT == FMT_IQ3_S) {
-                        if (ah == 0) {
-                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink, s_grid);
-                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink, s_grid);
-                        } else {
-                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink, s_grid);
-                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink, s_grid);
-                        }
-                    } else {
-                        if (ah == 0) {
-                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink);
-                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink);
-                        } else {
-                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink);
-                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink);
-                        }
-                    }
-                } else {
-                    sink.taddr = a_base + a1 * 32;
-                    switch (a1) {
-                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink); break;
-                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink); break;
-                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink); break;
-                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
-                    }
-                }
-                pend_set = set;
-                pend_slot = slot;
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
-            }
-            if (!ok) break;
-            publish();                                       // the unit's last chunk
-            // ---- epilogue of this unit ----
-            const int buf = ui & 1;
-            if (warp == 0 && lane == 0) stamp(3, ui * 4 + 0);
-            ok = mbar_wait(accf_bar + buf * 8, (ui >> 1) & 1, abort_flag);
-            if (warp == 0 && lane == 0) stamp(3, ui * 4 + 1);
-            if (!ok) break;
+        // Epilogue of unit `ui_` (accumulator set ui_ & 1; its first chunk had counter cc0).  Returns false after a timeout.
+        auto epilogue = [&](const Unit& u, int ui_, int cc0) -> bool {
+            const int buf = ui_ & 1;
+            if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 0);
+            if (!mbar_wait(accf_bar + buf * 8, (ui_ >> 1) & 1, abort_flag)) return false;
+            if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 1);
             tc_fence_after();
             float v[CW];
             const int c0 = part * CW;
             // issuer w worked on this unit iff the unit has a chunk of parity w
-            const int cc0 = cc - u.nkb;
             const bool has0 = u.nkb >= 2 || (cc0 & 1) == 0, has1 = u.nkb >= 2 || (cc0 & 1) == 1;
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = 0.f;
@@ -340,7 +301,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar + buf * 8);   // accumulator may be overwritten by unit ui + 2
-            ++ui;
             const int n_row = u.tile * 128 + row;
             bool do_finish = true;
             if (u.contributors > 1) {
@@ -350,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 // measured to cost several microseconds when all CTAs reach their unit boundary together.
                 const bool use_slots = p.partials != nullptr;
                 if (use_slots) {
-                    float* mine = p.partials + ((size_t)blockIdx.x * 2 + (ui > 1 ? 1 : 0)) * (128 * BM);
+                    float* mine = p.partials + ((size_t)blockIdx.x * 2 + (ui_ > 0 ? 1 : 0)) * (128 * BM);
 #pragma unroll
                     for (int i = 0; i < CW; ++i) __stcg(&mine[(c0 + i) * 128 + row], v[i]);
                 } else {
@@ -360,12 +320,45 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         if (m < p.m) atomicAdd(&p.accum[(size_t)m * p.accum_stride + n_row], v[i]);
                     }
                 }
+                if (use_slots) {
+                    // The tile's first contributor finishes it: its part of the tile is the tail of its own chunk range and
+                    // therefore the last to be computed, so it hardly ever waits.  The others hand their slot to the signal
+                    // lane (in the activation producer's warp), which pays for the device-scope release (~2 us of waiting
+                    // for the stores to be acknowledged) while these warps go back to converting weights.
+                    const int c_first = it.cta_of(u.tile * k_blocks);
+                    __syncwarp();
+                    if ((int)blockIdx.x != c_first) {
+                        if (lane == 0) mbar_arrive(sig_bar);
+                        do_finish = false;
+                    } else {
+                        const unsigned target = (unsigned)(N_DQ_WARPS * (u.contributors - 1));
+                        int got = 1;
+                        if (lane == 0) {
+                            got = 0;
+                            for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                                if (ld_acquire_gpu(&p.tickets[u.tile]) >= target) { got = 1; break; }
+                                if (i > 64) { if (abort_flag[0]) break; __nanosleep(32); }
+                            }
+                            if (!got) abort_flag[0] = 1;
+                        }
+                        got = __shfl_sync(0xffffffffu, got, 0);
+                        __syncwarp();
+                        if (!got) return false;
+                        // once every warp has seen the count, warp 0 puts the counter back for the next launch
+                        if (lane == 0) mbar_arrive(epi_bar);
+                        if (warp == 0) {
+                            if (!mbar_wait(epi_bar, epi_syncs & 1, abort_flag)) return false;
+                            if (lane == 0) p.tickets[u.tile] = 0u;
+                        }
+                        ++epi_syncs;
+                    }
+                } else {
                 __threadfence();
                 __syncwarp();
                 // all 16 epilogue warps meet (bounded) before and after the arrival ticket is taken
                 if (lane == 0) mbar_arrive(epi_bar);
                 ok = mbar_wait(epi_bar, epi_syncs & 1, abort_flag); ++epi_syncs;
-                if (!ok) break;
+                if (!ok) return false;
                 if (tid == 0) {
                     const unsigned t = atomicAdd(&p.tickets[u.tile], 1u);
                     s_last = (t == (unsigned)u.contributors - 1);
@@ -374,11 +367,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(epi_bar);
                 ok = mbar_wait(epi_bar, epi_syncs & 1, abort_flag); ++epi_syncs;
-                if (!ok) break;
+                if (!ok) return false;
                 do_finish = s_last != 0;
-                if (warp == 0 && lane == 0) stamp(3, (ui - 1) * 4 + 2);
+                }
+                if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 2);
                 if (do_finish) {
-                    __threadfence();
+                    if (!use_slots) __threadfence();
                     if (use_slots) {
                         // contributors are the CTAs that own a chunk of this tile, in order; sum in that order (own registers
                         // at this CTA's place) so that the result does not depend on who arrived last
@@ -464,7 +458,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     };
                     if (tid == 0) { s_tp_epoch = tp.epoch[u.tile]; s_tp_epoch2 = tp.epoch2[u.tile]; }
                     ok = epi_sync();
-                    if (!ok) break;
+                    if (!ok) return false;
                     const unsigned e = s_tp_epoch;
                     auto row_of = [&](int i) { return (c0 + i) < p.m ? c0 + i : -1; };
                     if (tp.two_phase_min_rows > 0 && p.m >= tp.two_phase_min_rows) {
@@ -483,7 +477,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             }
                         }
                         ok = epi_sync();
-                        if (!ok) break;
+                        if (!ok) return false;
                         if (tid < W) tp_signal(tp, u.tile, tid);
                         if (tid == 0) {
                             abort_flag[1] = 1;
@@ -492,7 +486,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             tp.epoch[u.tile] = e + 1;
                         }
                         ok = epi_sync();
-                        if (!ok) break;
+                        if (!ok) return false;
                         if (s_tp_ok) {
                             // phase 2a: reduce this rank's slice over all sources (fixed order) and hand it to every rank
                             const float* mine = tp.rs_inbox[tp.rank] + ((size_t)(par * W) * tp.rows_cap) * cols_rs + u.tile * slice;
@@ -505,7 +499,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             }
                         }
                         ok = epi_sync();
-                        if (!ok) break;
+                        if (!ok) return false;
                         if (tid < W) red_release_sys_add(tp.flags2[tid] + u.tile, 1u);
                         if (tid == 0) {
                             abort_flag[1] = 1;
@@ -522,7 +516,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             tp.epoch2[u.tile] = e2 + 1;
                         }
                         ok = epi_sync();
-                        if (!ok) break;
+                        if (!ok) return false;
                         if (s_tp_ok && n_row < p.n) {
                             // phase 2b: the complete tile is in this rank's all-gather inbox
                             const float* full = tp.ag_inbox[tp.rank] + ((size_t)par2 * tp.rows_cap) * tp.n_cap + u.tile * 128 + row;
@@ -542,7 +536,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         tp_push<CW>(tp, e, n_row, v, row_of);
                     }
                     ok = epi_sync();
-                    if (!ok) break;
+                    if (!ok) return false;
                     if (tid < tp.size) tp_signal(tp, u.tile, tid);
                     if (tid == 0) {
                         abort_flag[1] = 1;                     // hold the other warps' wait limits while the peer is awaited
@@ -551,7 +545,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         tp.epoch[u.tile] = e + 1;
                     }
                     ok = epi_sync();
-                    if (!ok) break;
+                    if (!ok) return false;
                     if (s_tp_ok && n_row < p.n) {
                         tp_reduce<CW>(tp, e, n_row, v, row_of);
                         float* h = static_cast<float*>(p.out);
@@ -576,8 +570,78 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     }
                 }
             }
-            if (warp == 0 && lane == 0) stamp(3, (ui - 1) * 4 + 3);
+            if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 3);
+            return true;
+        };
+        // The epilogue of a unit is run two chunks into the next unit: by then its MMAs have completed, so the dequant warps
+        // never sit out the drain of the operand ring, and the issuers work through those two chunks meanwhile.
+        constexpr int DEFER = 2;
+        Unit pu{};
+        int p_ui = -1, p_cc0 = 0;
+        auto flush = [&]() -> bool {
+            if (p_ui < 0) return true;
+            publish();
+            const bool r = epilogue(pu, p_ui, p_cc0);
+            p_ui = -1;
+            return r;
+        };
+        // chunks [c_begin, c_end) of unit u
+        auto convert = [&](int c_begin, int c_end) {
+            for (int c = c_begin; c < c_end && ok; ++c, ++cc) {
+                if (C::TWO_SETS && (cc & 1) != ws) continue;
+                const int slot = cc % R, rphase = (cc / R) & 1;
+                const int set = set_of(cc);
+                ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
+                if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
+                if (!ok) return;
+                publish();
+                const uint32_t raw = raw_base + slot * C::CHUNK;
+                const uint32_t a_base = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
+                if constexpr (C::TWO_SETS) {
+                    if constexpr (FMT == FMT_IQ3_S) {
+                        if (ah == 0) {
+                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink, s_grid);
+                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink, s_grid);
+                        } else {
+                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink, s_grid);
+                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink, s_grid);
+                        }
+                    } else {
+                        if (ah == 0) {
+                            sink.taddr = a_base;      DequantAtom<FMT, 0>::run(raw, g, lane, sink);
+                            sink.taddr = a_base + 32; DequantAtom<FMT, 1>::run(raw, g, lane, sink);
+                        } else {
+                            sink.taddr = a_base + 64; DequantAtom<FMT, 2>::run(raw, g, lane, sink);
+                            sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink);
+                        }
+                    }
+                } else {
+                    sink.taddr = a_base + a1 * 32;
+                    switch (a1) {
+                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink); break;
+                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink); break;
+                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink); break;
+                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
+                    }
+                }
+                pend_set = set;
+                pend_slot = slot;
+                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
+            }
+        };
+        while (ok && it.next(u)) {
+            const int cc0 = cc;
+            const int head = u.nkb < DEFER ? u.nkb : DEFER;
+            convert(0, head);
+            if (ok && p_ui >= 0) ok = flush();
+            convert(head, u.nkb);
+            if (!ok) break;
+            pu = u; p_ui = ui; p_cc0 = cc0;                 // this unit's epilogue is owed
+            ++ui;
         }
+        if (ok) ok = flush();
     } else if (warp == N_DQ_WARPS) {
         // ---------------- raw chunk producer: the whole warp streams each chunk with 16-byte cp.async ----------------
         // (measured: one cp.async.bulk per chunk tops out near 10 GB/s per SM here, far below what LDGSTS sustains)
@@ -607,6 +671,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == N_DQ_WARPS + 1) {
         // ---------------- activation tile producer (TMA): the four 64-column tiles of a chunk on one barrier ----------------
+        if (lane == 16 && streamk && p.partials != nullptr) {
+            // signal lane: once all dequant warps have parked their partial sums of a tile that another CTA finishes, one
+            // release (cumulative over the mbarrier) publishes them to that CTA
+            int n = 0;
+            while (it.next(u)) {
+                if (u.contributors > 1 && (int)blockIdx.x != it.cta_of(u.tile * k_blocks)) {
+                    if (!mbar_wait(sig_bar, n & 1, abort_flag)) break;
+                    red_release_gpu_add(&p.tickets[u.tile], (unsigned)N_DQ_WARPS);
+                    ++n;
+                }
+            }
+        }
         if (lane == 0) {
             int cc = 0;
             bool ok = true;
