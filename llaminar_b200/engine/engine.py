@@ -147,6 +147,13 @@ class LLMEngine:
         ws = self.tp.size if self.tp is not None else 1
         self._pairs = torch.zeros(bmax * R, 2, dtype=torch.int32, device=self.device)
         self._pairs_all = torch.zeros(ws, bmax * R, 2, dtype=torch.int32, device=self.device)
+        # top-k / top-p sampling over a sharded head: every rank contributes its SAMPLE_CANDIDATES best entries per row
+        # (the sampling kernel never looks beyond that many), 8 KB per row and rank instead of the logits
+        self._cand = self._cand_all = None
+        if ws > 1 and self.is_cuda:
+            kc = min(self.SAMPLE_CANDIDATES, self.model.vocab_local)
+            self._cand = torch.zeros(bmax * R, kc, 2, dtype=torch.int32, device=self.device)
+            self._cand_all = torch.zeros(ws * bmax * R * kc * 2, dtype=torch.int32, device=self.device)
 
     def _dec_views(self, bucket: int, R: int):
         """Slices of the static int buffer for a (bucket, rows-per-seq) decode shape."""
@@ -387,6 +394,21 @@ class LLMEngine:
         self.tp.all_gather_flat(gathered, pairs)
         ops.argmax_merge(gathered, ws, rows, tokens)
 
+    SAMPLE_CANDIDATES = 1024      # the sampling kernel's candidate cap (top_k = 0 means "the best 1024")
+
+    def _sharded_sample(self, logits: torch.Tensor, rows: int, temperature, top_k, top_p, seeds, step, tokens) -> None:
+        """Top-k / top-p sampling over a vocabulary-sharded head: per-shard candidates, all-gather, one merged draw.
+        Every rank draws the same token, and it is the token a single rank would draw from the gathered logits
+        (reference: DeviceSampler's per-shard candidate merge, src/v2/execution/local_execution/orchestrators/DeviceSampler.cpp)."""
+        from .. import ops
+        ws = self.tp.size
+        cand = self._cand[:rows]
+        kc = cand.shape[1]
+        ops.sample_candidates(logits, self.model.plan.vocab_start, cand)
+        gathered = self._cand_all[:ws * rows * kc * 2].view(ws, rows, kc, 2)
+        self.tp.all_gather_flat(gathered, cand)
+        ops.sample_merged(gathered, temperature, top_k, top_p, seeds, step, tokens)
+
     def _gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         """Vocab-parallel logits shards -> full rows (a no-op without tensor parallelism)."""
         if self.tp is None or self.tp.size == 1 or getattr(self.model, "returns_full_vocab", False):
@@ -595,6 +617,10 @@ class LLMEngine:
         logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
         if greedy and self._sharded_vocab():
             self._sharded_argmax(logits, bucket, self._tok_dev[:bucket])
+            return
+        if not greedy and self._sharded_vocab() and self._cand is not None:
+            self._sharded_sample(logits, bucket, self._fl_dev[:bucket], d[v["topk"]], self._fl_dev[bucket:2 * bucket],
+                                 self._seed_dev[:bucket], d[v["step"]], self._tok_dev[:bucket])
             return
         logits = self._gather_vocab(logits)
         if greedy:

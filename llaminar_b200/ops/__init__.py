@@ -227,6 +227,19 @@ def sample(logits, temperature, top_k, top_p, seeds, step, tokens, probs_out=Non
     _count()
 
 
+def sample_candidates(logits, idx_offset: int, pairs) -> None:
+    """Pass 1 of sampling over a vocabulary-sharded head: pairs[rows, k, 2] (int32) receive this shard's k best entries as
+    (float bits, global token id), best first."""
+    ext().sample_candidates(logits, idx_offset, pairs)
+    _count()
+
+
+def sample_merged(gathered, temperature, top_k, top_p, seeds, step, tokens) -> None:
+    """Pass 2: draw from the all-gathered pairs [ranks, rows, k, 2]; the token equals the one `sample` draws from the full row."""
+    ext().sample_merged(gathered, temperature, top_k, top_p, seeds, step, tokens)
+    _count()
+
+
 def penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency) -> None:
     ext().penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency)
     _count()

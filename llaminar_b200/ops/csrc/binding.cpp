@@ -271,6 +271,34 @@ static void sample(const Tensor& logits, const Tensor& temperature, const Tensor
     LLM_CUDA_CHECK(llm::launch_sample(p, cur_stream()));
 }
 
+// pass 1 of sampling over a vocabulary-sharded head: pairs[rows, k, 2] = this shard's k best (float bits, global token id)
+static void sample_candidates(const Tensor& logits, int64_t idx_offset, Tensor pairs) {
+    const c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && pairs.scalar_type() == torch::kInt32 && pairs.is_contiguous());
+    TORCH_CHECK(pairs.dim() == 3 && pairs.size(0) >= logits.size(0) && pairs.size(2) == 2 && pairs.size(1) >= 1 && pairs.size(1) <= 1024);
+    llm::SampleParams p{};
+    p.logits = static_cast<const float*>(logits.data_ptr()); p.rows = (int)logits.size(0); p.vocab = (int)logits.size(1);
+    p.stride = (int)logits.stride(0);
+    p.cand_out = static_cast<int*>(pairs.data_ptr()); p.cand_k = (int)pairs.size(1); p.idx_offset = (int)idx_offset;
+    LLM_CUDA_CHECK(llm::launch_sample(p, cur_stream()));
+}
+
+// pass 2: draw from the all-gathered pairs [ranks, rows, k, 2]
+static void sample_merged(const Tensor& gathered, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p, const Tensor& seeds,
+                          const Tensor& step, Tensor tokens) {
+    const c10::cuda::CUDAGuard guard(gathered.device());
+    TORCH_CHECK(gathered.scalar_type() == torch::kInt32 && gathered.is_contiguous() && gathered.dim() == 4 && gathered.size(3) == 2);
+    TORCH_CHECK(tokens.scalar_type() == torch::kInt32 && tokens.numel() >= gathered.size(1));
+    TORCH_CHECK(seeds.scalar_type() == torch::kInt64 && step.scalar_type() == torch::kInt32 && top_k.scalar_type() == torch::kInt32);
+    llm::SampleParams p{};
+    p.rows = (int)gathered.size(1); p.vocab = (int)(gathered.size(0) * gathered.size(2));
+    p.merge_pairs = static_cast<const int*>(gathered.data_ptr()); p.merge_ranks = (int)gathered.size(0); p.merge_k = (int)gathered.size(2);
+    p.temperature = static_cast<const float*>(temperature.data_ptr()); p.top_k = static_cast<const int*>(top_k.data_ptr());
+    p.top_p = static_cast<const float*>(top_p.data_ptr()); p.seeds = static_cast<const uint64_t*>(seeds.data_ptr());
+    p.step = static_cast<const int*>(step.data_ptr()); p.tokens = static_cast<int*>(tokens.data_ptr());
+    LLM_CUDA_CHECK(llm::launch_sample(p, cur_stream()));
+}
+
 static void penalties(Tensor logits, const Tensor& hist_tokens, const Tensor& hist_counts, const Tensor& hist_offsets,
                       const Tensor& presence, const Tensor& frequency) {
     const c10::cuda::CUDAGuard guard(logits.device());
@@ -393,6 +421,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax", &argmax);
     m.def("argmax_merge", &argmax_merge);
     m.def("sample", &sample);
+    m.def("sample_candidates", &sample_candidates);
+    m.def("sample_merged", &sample_merged);
     m.def("penalties", &penalties);
     m.def("nan_scan", &nan_scan);
     m.def("spec_verify_greedy", &spec_verify_greedy);

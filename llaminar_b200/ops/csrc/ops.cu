@@ -292,12 +292,22 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     __shared__ float s_warp[32];
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* lg = p.logits + (size_t)row * p.stride;
+    const bool merging = p.merge_pairs != nullptr;
+    const int n_items = merging ? p.merge_ranks * p.merge_k : p.vocab;
+    // entry i of this row: its value and the token id it stands for
+    auto pair_at = [&](int i) {
+        const int w = i / p.merge_k, j = i - w * p.merge_k;
+        return p.merge_pairs + (((size_t)w * p.rows + row) * p.merge_k + j) * 2;
+    };
+    auto val_at = [&](int i) { return merging ? __int_as_float(pair_at(i)[0]) : lg[i]; };
+    auto id_at = [&](int i) { return merging ? (unsigned)pair_at(i)[1] : (unsigned)(i + p.idx_offset); };
     const float temp = p.temperature ? p.temperature[row] : 1.0f;
     int k = p.top_k ? p.top_k[row] : 0;
     const float top_p = p.top_p ? p.top_p[row] : 1.0f;
-    const bool greedy = temp <= 0.f || k == 1;
+    const bool greedy = !p.cand_out && (temp <= 0.f || k == 1);
     if (k <= 0 || k > MAX_CAND) k = MAX_CAND;
-    if (k > p.vocab) k = p.vocab;
+    if (p.cand_out) k = p.cand_k;
+    if (k > n_items) k = n_items;
     if (greedy) k = 1;
     // ---- radix select of the k-th largest key ----
     if (tid == 0) { s_prefix = 0; s_need = k; }
@@ -308,8 +318,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
         __syncthreads();
         const unsigned prefix = s_prefix;
         const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = tid; i < p.vocab; i += 1024) {
-            const unsigned key = order_key(lg[i]);
+        for (int i = tid; i < n_items; i += 1024) {
+            const unsigned key = order_key(val_at(i));
             if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 0xff], 1u);
         }
         __syncthreads();
@@ -330,13 +340,13 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     if (tid == 0) { s_count = 0; s_eq_count = 0; }
     for (int i = tid; i < MAX_CAND; i += 1024) s_keys[i] = 0ull;
     __syncthreads();
-    for (int i = tid; i < p.vocab; i += 1024) {
-        const unsigned key = order_key(lg[i]);
+    for (int i = tid; i < n_items; i += 1024) {
+        const unsigned key = order_key(val_at(i));
         bool take = key > thr;
         if (key == thr) take = atomicAdd(&s_eq_count, 1u) < eq_quota;
         if (take) {
             const unsigned slot = atomicAdd(&s_count, 1u);
-            if (slot < MAX_CAND) s_keys[slot] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i);
+            if (slot < MAX_CAND) s_keys[slot] = ((unsigned long long)key << 32) | (0xffffffffu - id_at(i));
         }
     }
     __syncthreads();
@@ -353,6 +363,15 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
         }
     }
     const int n = min((int)s_count, k);
+    if (p.cand_out) {
+        // pass 1 of a sharded head: the best cand_k entries in order, padded with (-inf, no token)
+        for (int i = tid; i < p.cand_k; i += 1024) {
+            int* o = p.cand_out + ((size_t)row * p.cand_k + i) * 2;
+            o[0] = i < n ? __float_as_int(key_to_float((unsigned)(s_keys[i] >> 32))) : (int)0xff800000u;
+            o[1] = i < n ? (int)(0xffffffffu - (unsigned)(s_keys[i] & 0xffffffffu)) : 0x7fffffff;
+        }
+        return;
+    }
     if (p.probs_out) {
         float* po = p.probs_out + (size_t)row * p.vocab;
         for (int i = tid; i < p.vocab; i += 1024) po[i] = 0.f;

@@ -69,6 +69,12 @@ struct SampleParams {
     const int* step;               // [rows] decode step counter mixed into the RNG
     int* tokens;                   // [rows]
     float* probs_out;              // optional [rows, vocab] final distribution (speculative sampling)
+    // Vocabulary-sharded heads sample in two launches.  Pass 1 (cand_out set): every rank writes the cand_k best entries of
+    // its shard as (float bits, global token id) pairs [rows, cand_k, 2] and draws nothing.  Pass 2 (merge_pairs set): the
+    // all-gathered pairs [merge_ranks, rows, merge_k, 2] are the "vocabulary"; ties still go to the lower token id, so the
+    // token is the one a single launch over the full row would have drawn.
+    int* cand_out = nullptr; int cand_k = 0; int idx_offset = 0;
+    const int* merge_pairs = nullptr; int merge_ranks = 0, merge_k = 0;
 };
 cudaError_t launch_sample(const SampleParams& p, cudaStream_t st);
 cudaError_t launch_penalties(float* logits, int rows, int vocab, int stride, const int* hist_tokens, const int* hist_counts,

@@ -268,6 +268,35 @@ def test_sampling_kernels():
     assert (emp - probs[5]).abs().max() < 0.15
 
 
+def test_sharded_sampling_draws_the_same_token_as_the_full_row():
+    """Per-shard candidates + merged draw (what tensor-parallel ranks do) against one launch over the whole vocabulary."""
+    from llaminar_b200 import ops
+    torch.manual_seed(1)
+    rows, vocab, shards = 5, 6000, 4
+    logits = torch.randn(rows, vocab, device=DEV) * 2
+    logits[0, 17] = logits[0, 4000] = logits[0].max() + 1          # a tie across two shards: the lower token id must win
+    temp = torch.tensor([0.0, 1.0, 0.8, 1.0, 1.3], device=DEV)
+    top_k = torch.tensor([0, 0, 7, 50, 1000], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.6, 0.95], device=DEV)
+    seeds = torch.arange(rows, dtype=torch.int64, device=DEV) + 7
+    per = vocab // shards
+    kc = 1024
+    full, merged = torch.empty(rows, dtype=torch.int32, device=DEV), torch.empty(rows, dtype=torch.int32, device=DEV)
+    gathered = torch.zeros(shards, rows, kc, 2, dtype=torch.int32, device=DEV)
+    for step in range(40):
+        st = torch.full((rows,), step, dtype=torch.int32, device=DEV)
+        ops.sample(logits, temp, top_k, top_p, seeds, st, full)
+        for s in range(shards):
+            ops.sample_candidates(logits[:, s * per:(s + 1) * per], s * per, gathered[s])
+        ops.sample_merged(gathered, temp, top_k, top_p, seeds, st, merged)
+        assert merged.tolist() == full.tolist(), step
+    assert full[0].item() == 17
+    # the candidates of a shard are its best entries, best first, with global token ids
+    vals = gathered[1, 2, :, 0].view(torch.float32)
+    ref = logits[2, per:2 * per].topk(kc)
+    assert torch.equal(vals, ref.values) and gathered[1, 2, :8, 1].tolist() == (ref.indices[:8] + per).tolist()
+
+
 def test_spec_verify_and_moe_topk_and_nan_scan():
     from llaminar_b200 import ops
     draft = torch.tensor([[5, 6], [5, 9], [1, 2]], dtype=torch.int32, device=DEV)

@@ -84,6 +84,38 @@ def test_engine_tp2_fused_equals_nccl_baseline():
     assert agree >= 0.9 * 48            # different summation order may flip a near-tie
 
 
+def _engine_sampled_tokens(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    dev = torch.device("cuda", rank)
+    cfg = SHAPES["tiny-qwen3"].with_(d_model=1024, n_heads=8, n_kv_heads=2, head_dim=128, d_ff=2048, n_layers=2)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    tp = TPContext.create(device=dev, fused=True)
+    eng = LLMEngine(w, device=dev, max_batch=8, max_context=256, tp=tp)
+    calls = [0]
+    inner = eng._sharded_sample
+    def counted(*a, **k):
+        calls[0] += 1
+        return inner(*a, **k)
+    eng._sharded_sample = counted
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (30, 12, 50)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.9, top_k=40, top_p=0.95, seed=11, max_tokens=12, ignore_eos=True))
+    eng.check_health()
+    return outs, calls[0], cfg.vocab_size
+
+
+def test_engine_tp2_sampled_decode_uses_candidate_merge():
+    _need(2)
+    res = run_ranks_gpu(_engine_sampled_tokens, 2)
+    assert res[0][0] == res[1][0]                       # every rank drew the same tokens
+    assert res[0][1] > 0                                # through the per-shard candidate path (graph capture calls it)
+    assert all(0 <= t < res[0][2] for o in res[0][0] for t in o) and all(len(o) == 12 for o in res[0][0])
+
+
 def _moe_engine_tokens(rank, world, fused):
     from llaminar_b200.engine.engine import LLMEngine
     from llaminar_b200.engine.sampling import SamplingParams
