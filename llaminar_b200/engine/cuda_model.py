@@ -277,7 +277,7 @@ class CudaModel:
                             c.head_dim, fb.rows_per_seq, scale, fb.n_splits, self.scratch)
         else:
             ops.attn_prefill(q, kv_layer, o3, fb.block_table, fb.cu_q, fb.ctx_lens, self.n_heads_local,
-                             self.n_kv_local, c.head_dim, scale, fb.max_q_len)
+                             self.n_kv_local, c.head_dim, scale, fb.max_q_len, scratch=self.scratch)
         return o
 
     def _row_parallel_resid(self, lin: QLinear, x: torch.Tensor, h: torch.Tensor) -> None:

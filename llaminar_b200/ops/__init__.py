@@ -199,9 +199,29 @@ def attn_decode(q, kv, out, block_table, seq_lens, n_heads, n_kv_heads, head_dim
     _count()
 
 
-def attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len) -> None:
-    ext().attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len)
+def attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len,
+                 tensor_core: bool | None = None, scratch: "Scratch | None" = None) -> None:
+    """Causal GQA attention of a prefill chunk over the paged cache.  ``tensor_core`` picks the tcgen05 kernel (head_dim 128),
+    otherwise the mma.sync kernel runs.  Default: the tcgen05 kernel for chunks of at least ATTN_TC_MIN_ROWS query rows per
+    sequence (measured 283 vs 246 TFLOP/s at 2048 rows, 323 vs 234 at 4096, but 223 vs 237 at 1024, where its per-CTA
+    start-up weighs more); LLAMINAR_ATTN_TC=0 turns it off."""
+    if tensor_core is None:
+        tensor_core = head_dim == 128 and max_q_len >= ATTN_TC_MIN_ROWS and _attn_tc_default()
+    status = scratch.status if (tensor_core and scratch is not None) else None
+    ext().attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, head_dim, scale, max_q_len, bool(tensor_core), status)
     _count()
+
+
+ATTN_TC_MIN_ROWS = 1536
+_ATTN_TC = None
+
+
+def _attn_tc_default() -> bool:
+    global _ATTN_TC
+    if _ATTN_TC is None:
+        from ..utils.env import debug_env
+        _ATTN_TC = bool(debug_env().attn_tc)
+    return _ATTN_TC
 
 
 def swiglu_tiled(gu, out) -> None:

@@ -210,7 +210,8 @@ static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Ten
 }
 
 static void attn_prefill(const Tensor& q, const Tensor& kv, Tensor out, const Tensor& block_table, const Tensor& cu_q,
-                         const Tensor& ctx_lens, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim, double scale, int64_t max_q_len) {
+                         const Tensor& ctx_lens, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim, double scale, int64_t max_q_len,
+                         bool tensor_core, const OptTensor& status) {
     check_cuda(q, "q");
     const c10::cuda::CUDAGuard guard(q.device());
     llm::AttnPrefillParams p{};
@@ -220,7 +221,12 @@ static void attn_prefill(const Tensor& q, const Tensor& kv, Tensor out, const Te
     p.ctx_lens = static_cast<const int*>(ctx_lens.data_ptr());
     p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim; p.max_pages = (int)block_table.size(1);
     p.scale = (float)scale;
-    LLM_CUDA_CHECK(llm::launch_attn_prefill(p, (int)ctx_lens.numel(), (int)max_q_len, cur_stream()));
+    if (tensor_core) {
+        TORCH_CHECK(head_dim == 128, "the tcgen05 prefill attention is built for head_dim 128");
+        LLM_CUDA_CHECK(llm::launch_attn_prefill_tc(p, (int)ctx_lens.numel(), (int)max_q_len, mptr<int>(status), cur_stream()));
+    } else {
+        LLM_CUDA_CHECK(llm::launch_attn_prefill(p, (int)ctx_lens.numel(), (int)max_q_len, cur_stream()));
+    }
 }
 
 static void swiglu_tiled(const Tensor& gu, Tensor out) {

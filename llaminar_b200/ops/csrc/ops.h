@@ -33,6 +33,8 @@ struct AttnPrefillParams {
 int attn_decode_pick_splits(int batch, int n_kv_heads, int max_pages_in_use);
 cudaError_t launch_attn_decode(const AttnDecodeParams& p, int batch, int n_splits, cudaStream_t st);
 cudaError_t launch_attn_prefill(const AttnPrefillParams& p, int n_seqs, int max_q_len, cudaStream_t st);
+// tcgen05 version (head_dim 128 only); `status` (optional) receives STATUS_TIMEOUT if a pipeline wait gave up
+cudaError_t launch_attn_prefill_tc(const AttnPrefillParams& p, int n_seqs, int max_q_len, int* status, cudaStream_t st);
 
 struct RopeKVParams {
     __nv_bfloat16* qkv;            // [T, (n_heads + 2 n_kv_heads) * head_dim]; Q part is rewritten in place

@@ -232,6 +232,54 @@ def test_rope_kv_and_attention(D, nq, nkv):
         assert int(ops.scratch_for(DEV).attn_tickets.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nq,nkv,q_lens,ctx_lens", [(8, 2, [70, 129, 5], [0, 0, 0]), (4, 4, [300, 128], [0, 64]),
+                                                     (16, 2, [257, 40, 1], [200, 131, 513])])
+def test_prefill_attention_tcgen05(nq, nkv, q_lens, ctx_lens):
+    """tcgen05 prefill attention (head_dim 128) against an fp32 reference, with and without a cached prefix."""
+    from llaminar_b200 import ops
+    torch.manual_seed(2)
+    D, B = 128, len(q_lens)
+    tot = [c + l for c, l in zip(ctx_lens, q_lens)]
+    max_pages = max((t + 63) // 64 for t in tot) + 1
+    n_pages = B * max_pages + 3
+    btab = torch.randperm(n_pages)[: B * max_pages].reshape(B, max_pages).to(torch.int32).to(DEV)
+    kv = torch.zeros(n_pages, 2, nkv, 64, D, dtype=torch.bfloat16, device=DEV)
+    # fill the cache with every sequence's keys / values (prefix and this chunk)
+    ks = [(torch.randn(t, nkv, D, device=DEV) * 0.7) for t in tot]
+    vs = [(torch.randn(t, nkv, D, device=DEV) * 0.7) for t in tot]
+    for b in range(B):
+        for t in range(tot[b]):
+            page = int(btab[b, t // 64])
+            kv[page, 0, :, t % 64] = ks[b][t].to(torch.bfloat16)
+            kv[page, 1, :, t % 64] = vs[b][t].to(torch.bfloat16)
+    T = sum(q_lens)
+    q = (torch.randn(T, nq, D, device=DEV) * 0.7).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    sc = ops.scratch_for(DEV)
+    out_tc = torch.zeros(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    out_old = torch.zeros_like(out_tc)
+    ops.attn_prefill(q, kv, out_tc, btab, cu, ctx, nq, nkv, D, scale, max(q_lens), tensor_core=True, scratch=sc)
+    ops.attn_prefill(q, kv, out_old, btab, cu, ctx, nq, nkv, D, scale, max(q_lens), tensor_core=False)
+    torch.cuda.synchronize()
+    assert int(sc.status[0]) == 0
+    g = nq // nkv
+    s0 = 0
+    for b, L in enumerate(q_lens):
+        C = ctx_lens[b]
+        kb = ks[b].to(torch.bfloat16).float().repeat_interleave(g, 1)
+        vb = vs[b].to(torch.bfloat16).float().repeat_interleave(g, 1)
+        qb = q[s0:s0 + L].float()
+        scr = torch.einsum("thd,shd->hts", qb, kb) * scale
+        mask = (torch.arange(C + L, device=DEV)[None, :] <= (C + torch.arange(L, device=DEV))[:, None])
+        scr = scr.masked_fill(~mask[None], float("-inf"))
+        ref = torch.einsum("hts,shd->thd", scr.softmax(-1), vb)
+        assert _rel(out_old[s0:s0 + L], ref) < 2e-2, ("mma.sync", b, L)
+        assert _rel(out_tc[s0:s0 + L], ref) < 2e-2, ("tcgen05", b, L, _rel(out_tc[s0:s0 + L], ref))
+        s0 += L
+
+
 def test_sampling_kernels():
     from llaminar_b200 import ops
     torch.manual_seed(0)
