@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
     const int head = blockIdx.y, seq = blockIdx.z;
     const int G = p.n_heads / p.n_kv_heads, kvh = head / G;
     const int q_start = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_start;
-    const int q0 = blockIdx.x * BQ;
+    // the last query tiles see the most keys: they go first so that the grid ends with the short CTAs
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ;
     if (q0 >= q_len) return;                               // uniform for the CTA, before any barrier or allocation
     const int ctx = p.ctx_lens[seq];                       // tokens already in the cache before this chunk
     const int rows = min(BQ, q_len - q0);
