@@ -233,13 +233,14 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             if (lane == 0) mbar_arrive(bar(O_EMPTY));
             return true;
         };
-        // Order per tile: [fold of the previous tile] -> second pass (P) -> first pass of the next tile, so that the P V MMAs
-        // of a tile run while these threads already look for the next tile's maxima.
-        ok = pass1(0);
-        for (int j = 0; j < nt && ok; ++j) {
+        // Order per tile: first pass (row maxima; the P V MMAs of the previous tile run meanwhile) -> fold of the previous tile
+        // (which also frees the P tile) -> second pass (P).  Every phase has exactly one call site: the unrolled 64-column
+        // loops are large and a second copy of each showed up as instruction-fetch stalls.
+        for (int j = 0; j <= nt && ok; ++j) {
             const int b = j & 1;
-            if (j > 0) ok = fold(j - 1);               // also frees the P tile
-            if (!ok) break;
+            if (j < nt) ok = pass1(j);
+            if (ok && j > 0) ok = fold(j - 1);
+            if (!ok || j == nt) break;
             const int key0 = j * BK + half * 64;
             const bool need_mask = key0 + 64 > lim;
             const uint32_t t_s = t_lane + b * 128;
@@ -282,9 +283,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             l = l * alpha + sum;
             m = m_new;
             alpha_prev = alpha;
-            if (j + 1 < nt) ok = pass1(j + 1);
         }
-        if (ok) ok = fold(nt - 1);
         // the row's normaliser is the sum over both column halves
         if (ok) {
             s_xchg[half][row] = l;

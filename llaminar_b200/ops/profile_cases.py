@@ -47,6 +47,7 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=0, help="rows of activations (GEMM cases; default: the case's own)")
     ap.add_argument("--n", type=int, default=51200)
     ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--seq", type=int, default=2048, help="tokens per sequence of the attn_prefill case")
     args = ap.parse_args()
     from .. import ops
     from ..gguf import GGMLType
@@ -84,7 +85,7 @@ def main() -> int:
         kv_bytes = B * ctx * 2 * nkv * D * 2
         rec.update(batch=B, ctx=ctx, heads=f"{nq}/{nkv}", us=round(us, 1), kv_gbs=round(kv_bytes / us / 1e3, 1))
     elif args.case == "attn_prefill":
-        B, L, nq, nkv, D = 4, 2048, 32, 8, 128
+        B, L, nq, nkv, D = 4, args.seq, 32, 8, 128
         pages = (L + 63) // 64
         kv = (torch.randn(B * pages + 1, 2, nkv, 64, D, device=dev, generator=g) * 0.3).to(torch.bfloat16)
         bt = (torch.arange(B * pages, dtype=torch.int32, device=dev) + 1).view(B, pages)
@@ -92,10 +93,12 @@ def main() -> int:
         out = torch.empty_like(q)
         cu = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=dev)
         ctxl = torch.zeros(B, dtype=torch.int32, device=dev)
-        fn = lambda: ops.attn_prefill(q, kv, out, bt, cu, ctxl, nq, nkv, D, 1.0 / math.sqrt(D), L)
-        us = _time(fn, args.iters)
         flops = 4.0 * B * nq * D * L * L / 2                 # causal: half of the score matrix
-        rec.update(batch=B, seq=L, heads=f"{nq}/{nkv}", us=round(us, 1), tflops=round(flops / us / 1e6, 1))
+        rec.update(batch=B, seq=L, heads=f"{nq}/{nkv}")
+        for name, tc in (("mma_sync", False), ("tcgen05", True)):
+            fn = lambda: ops.attn_prefill(q, kv, out, bt, cu, ctxl, nq, nkv, D, 1.0 / math.sqrt(D), L, tensor_core=tc)
+            us = _time(fn, args.iters)
+            rec[name] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1)}
     else:  # moe: Qwen3-30B-A3B layer, 64 tokens, all 128 experts local (259 MB of IQ3_S expert weights)
         from ..ops.layout import pack_experts
         from ..gguf.constants import BLOCK_GEOMETRY
