@@ -89,11 +89,15 @@ def _accum_args(pw: PackedWeight, rows: int, sc: Scratch | None):
 
 def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
          epi: int = EPI_STORE, bias: torch.Tensor | None = None, scratch: Scratch | None = None, ksplit: int = 0,
-         tp: torch.Tensor | None = None) -> None:
+         tp: torch.Tensor | None = None, tuned: bool = True) -> None:
     """out[m, :] (+)= x[m, :] @ W^T for m <= 4 rows.  x: fp32 residual rows when ``norm_w`` is given, else bf16.
-    ``tp``: device copy of the tensor-parallel descriptor; with EPI_RESID the epilogue all-reduces across ranks."""
+    ``tp``: device copy of the tensor-parallel descriptor; with EPI_RESID the epilogue all-reduces across ranks.
+    ``ksplit`` 0 lets the tuning table (``ops/tuning.py``), then the kernel's heuristic, pick the split-K factor."""
     rows = x.shape[0]
     assert 1 <= rows <= GEMV_MAX_ROWS
+    if ksplit == 0 and tuned:
+        from .tuning import table
+        ksplit = table().ksplit("gemv", pw.fmt, pw.n, pw.k, rows)
     accum, tickets = _accum_args(pw, rows, scratch)
     ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1, tp)
     _count()

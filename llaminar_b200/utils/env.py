@@ -32,6 +32,7 @@ REGISTRY: tuple[EnvVar, ...] = (
     EnvVar("LLAMINAR_VALIDATE_TENSORS", bool, False, "scan activations for NaN/Inf after every layer"),
     EnvVar("LLAMINAR_PDL", bool, True, "launch the decode-path kernels with programmatic dependent launch (prologues overlap the previous kernel)"),
     EnvVar("LLAMINAR_ATTN_TC", bool, True, "long prefill chunks (head_dim 128) run attention on the tcgen05 kernel instead of the mma.sync kernel"),
+    EnvVar("LLAMINAR_TUNING_FILE", str, "", "JSON table of measured kernel launch parameters (written by python -m llaminar_b200.ops.tuning)"),
     EnvVar("LLAMINAR_NO_CUDA_GRAPHS", bool, False, "run decode steps eagerly instead of replaying CUDA graphs"),
     EnvVar("LLAMINAR_HEARTBEAT_S", float, 2.0, "interval of the per-rank heartbeat"),
     EnvVar("LLAMINAR_WATCHDOG_TIMEOUT_S", float, 60.0, "a rank whose heartbeat is older than this is reported dead"),

@@ -73,3 +73,27 @@ def test_device_inventory_shape():
     from llaminar_b200.utils.devices import describe_devices as describe
     d = describe()
     assert "cpu" in d and "gpus" in d and isinstance(d["gpus"], list)
+
+
+def test_tuning_table_keeps_only_clear_wins_and_validates_files(tmp_path):
+    from llaminar_b200.ops import tuning
+    t = tuning.TuningTable()
+    assert t.ksplit("gemv", 0, 5120, 8192, 1) == 0                       # nothing measured: the kernel's heuristic decides
+    assert t.record("gemv", 0, 5120, 8192, 1, {0: 20.0, 2: 19.8, 4: 17.0}) is True
+    assert t.ksplit("gemv", 0, 5120, 8192, 1) == 4
+    assert t.record("gemv", 0, 10240, 5120, 1, {0: 20.0, 2: 19.8}) is False    # 1 % is noise, not a win
+    assert t.ksplit("gemv", 0, 10240, 5120, 1) == 0
+    f = tmp_path / "tune.json"
+    t.dump(f, {"device": "test"})
+    back = tuning.TuningTable.load(f)
+    assert back.entries == t.entries and back.ksplit("gemv", 0, 5120, 8192, 1) == 4
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"entries": {"gemv:0:1x1:m1": {"ksplit": -3}}}')
+    import pytest
+    with pytest.raises(ValueError):
+        tuning.TuningTable.load(bad)
+    with pytest.raises(FileNotFoundError):
+        tuning.TuningTable.load(tmp_path / "missing.json")
+    from llaminar_b200.models.config import SHAPES
+    shapes = dict((n, (a, b)) for n, a, b in tuning.projection_shapes(SHAPES["qwen3-32b"], tp=2))
+    assert shapes["qkv"] == (5120, 5120) and shapes["down"] == (5120, 12800) and shapes["gate_up"] == (25600, 5120)
