@@ -153,3 +153,35 @@ def test_debug_switches_validate_and_dump(tmp_path, monkeypatch):
     assert "layer_000_call_00001.pt" in files and "layer_001_call_00001.pt" in files
     h = torch.load(tmp_path / "layer_001_call_00001.pt")
     assert h.shape == (20, SHAPES["tiny-qwen3"].d_model) and torch.isfinite(h).all()
+
+
+def test_long_prompt_prefill_with_tcgen05_attention_matches_the_mma_sync_path():
+    """A 1800-token prompt (head_dim 128) runs its prefill attention on the tcgen05 kernel; the hidden state of the last
+    token must agree with the same forward on the mma.sync kernel."""
+    from llaminar_b200 import ops
+    from llaminar_b200.engine.cuda_model import CudaModel, ForwardBatch
+    from llaminar_b200.engine.kv_cache import PagedKVCache
+    cfg = SHAPES["tiny-qwen3"].with_(d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=1024, n_layers=2)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    n = 1800
+    assert n >= ops.ATTN_TC_MIN_ROWS
+    model = CudaModel(w, "cuda", max_tokens=2048)
+    prompt = _prompt(n, 4)
+    it = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    pages = (n + 63) // 64
+    outs = []
+    saved = ops._ATTN_TC
+    try:
+        for tc in (True, False):
+            ops._ATTN_TC = tc
+            kv = PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, pages + 2, "cuda")
+            fb = ForwardBatch(tokens=it(prompt), positions=it(list(range(n))), seq_ids=it([0] * n),
+                              block_table=it([list(range(1, pages + 1))]), cu_q=it([0, n]), ctx_lens=it([0]), max_q_len=n)
+            logits, h = model.forward(fb, kv)
+            outs.append((logits.float().clone(), h.float().clone()))
+    finally:
+        ops._ATTN_TC = saved
+    assert int(model.scratch.status[0]) == 0
+    assert _cos(outs[0][1], outs[1][1]) > 0.9995
+    same = (outs[0][0].argmax(-1) == outs[1][0].argmax(-1)).float().mean().item()
+    assert same > 0.97, same              # near-ties of a random model may flip between two bf16 attention kernels
