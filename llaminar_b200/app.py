@@ -395,7 +395,26 @@ def cmd_plan(cfg: OrchestrationConfig) -> int:
         gf = GGUFFile(v["model"])
         mcfg = ModelConfig.from_gguf(gf)
         gf.close()
-    plan = build_plan(mcfg, cfg.layout(), v.get("synthetic_recipe") or "Q4_K_M", v["ctx_size"], v["batch_size"])
+    recipe = v.get("synthetic_recipe") or "Q4_K_M"
+    if v.get("suggest_layout"):
+        from .planning import suggest_layout
+        layout, plan = suggest_layout(mcfg, int(v["suggest_layout"]), recipe, v["ctx_size"], v["batch_size"])
+        if layout is None:
+            for r in plan:
+                print(f"error: {r}", file=sys.stderr)
+            return 1
+        flags = []
+        if layout["pp"] == 1:
+            flags = ["--tp-devices", ",".join(layout["stages"][0][1])] if layout["tp"] > 1 else ["-d", "cuda:0"]
+        else:
+            for name, devs, first, last in layout["stages"]:
+                flags += ["--define-domain", f"{name}={','.join(devs)}"]
+            for i, (name, devs, first, last) in enumerate(layout["stages"]):
+                flags += ["--pp-stage", f"{i}={name}:{first}-{last}"]
+        print(f"suggested layout: pp={layout['pp']} x tp={layout['tp']} on {layout['world']} device(s)")
+        print("flags: " + " ".join(flags))
+    else:
+        plan = build_plan(mcfg, cfg.layout(), recipe, v["ctx_size"], v["batch_size"])
     print(plan.table())
     print(yaml.safe_dump(plan.to_dict(), sort_keys=False))
     return 1 if plan.errors else 0

@@ -72,6 +72,8 @@ OPTIONS: list[OptionSpec] = [
     _o("--dry-run", action="store_true", help="plan and validate, then exit", category="devices"),
     _o("--explain-placement", action="store_true", category="devices"),
     _o("--validate-only", action="store_true", category="devices"),
+    _o("--suggest-layout", type=int, default=None, category="devices",
+       help="plan: find the smallest pp x tp placement on up to N GPUs that fits their memory and print its flags"),
     # -- precision ------------------------------------------------------------------------------------------
     _o("--activation-precision", default="bf16", choices=("bf16", "fp32", "fp16"), category="precision"),
     _o("--kv-cache-precision", default="bf16", choices=("bf16", "fp16", "fp32", "q8_1", "tq4", "tq8"), category="precision"),

@@ -120,3 +120,40 @@ def build_plan(cfg: ModelConfig, layout: dict, recipe: QuantRecipe | str = "Q4_K
     if last != cfg.n_layers - 1 and not plan.errors:
         plan.errors.append(f"pipeline stages end at layer {last}, model has {cfg.n_layers} layers")
     return plan
+
+
+def suggest_layout(cfg: ModelConfig, n_devices: int, recipe: QuantRecipe | str = "Q4_K_M", ctx_size: int = 4096,
+                   batch_size: int = 1, hbm_bytes: int | list[int] = B200_HBM_BYTES, max_prefill_tokens: int = 8192):
+    """Smallest placement of ``cfg`` on up to ``n_devices`` identical GPUs that fits their memory.
+
+    Candidates are (pp, tp) with tp a degree the model can be split by and pp * tp <= n_devices; fewer devices win, then
+    tensor parallelism wins over pipeline stages (one NVSwitch domain: TP has the lower latency), then the plan with the
+    most head-room.  ``hbm_bytes`` may be a list (an inventory of device memories): every rank must fit the smallest
+    device it could land on.  Returns (layout, plan) or (None, reasons).  The reference's planner answers the same
+    question from a cluster inventory (src/v2/planning/, tests/v2/integration/orchestration/scenarios/).
+    """
+    caps = sorted(hbm_bytes)[::-1] if isinstance(hbm_bytes, (list, tuple)) else [hbm_bytes] * n_devices
+    n_devices = min(n_devices, len(caps))
+    reasons, best = [], None
+    for world in range(1, n_devices + 1):
+        cap = caps[world - 1]                                   # the smallest of the `world` largest devices
+        for pp in range(1, world + 1):
+            if world % pp:
+                continue
+            tp = world // pp
+            if TPPlan.validate(cfg, tp) or pp > cfg.n_layers:
+                continue
+            stages = [(f"s{i}", [f"cuda:{i * tp + j}" for j in range(tp)], cfg.n_layers * i // pp, cfg.n_layers * (i + 1) // pp - 1)
+                      for i in range(pp)]
+            layout = {"pp": pp, "tp": tp, "world": world, "stages": stages}
+            plan = build_plan(cfg, layout, recipe, ctx_size, batch_size, max_prefill_tokens, cap)
+            if plan.errors:
+                reasons.append(f"pp={pp} x tp={tp}: {plan.errors[0]}")
+                continue
+            head_room = cap - max(r.total_bytes for r in plan.ranks)
+            cand = (pp, -head_room, layout, plan)
+            if best is None or cand[:2] < best[:2]:
+                best = cand
+        if best is not None:
+            return best[2], best[3]
+    return None, reasons or [f"{cfg.name} cannot be split over 1..{n_devices} devices"]

@@ -138,3 +138,29 @@ def test_precision_flags_are_checked_against_the_device():
     rc, out, err = _cli("oneshot", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0", "-d", "cpu", "--kv-cache-precision", "bf16",
                         "-p", "hi", "-n", "3")
     assert rc == 0, err
+
+
+def test_suggest_layout_from_synthetic_inventories():
+    """Placement scenarios on made-up device inventories (no hardware): the planner is pure."""
+    from llaminar_b200.planning import suggest_layout
+    GB = 10 ** 9
+    # a 32B Q4_K_S model fits one 180 GB device
+    lay, plan = suggest_layout(SHAPES["qwen3-32b"], 8, "Q4_K_S", ctx_size=4096, batch_size=32)
+    assert (lay["pp"], lay["tp"], lay["world"]) == (1, 1, 1) and not plan.errors
+    # on 16 GB devices it needs several; tensor parallelism is preferred to pipeline stages when the heads divide
+    lay, plan = suggest_layout(SHAPES["qwen3-32b"], 8, "Q4_K_S", ctx_size=2048, batch_size=1, hbm_bytes=16 * GB)
+    assert lay is not None and lay["world"] in (2, 4) and lay["pp"] == 1 and max(r.total_bytes for r in plan.ranks) < 16 * GB
+    # three devices: 64 heads cannot be split three ways, so the answer is three pipeline stages (or fewer devices)
+    lay, plan = suggest_layout(SHAPES["qwen3-32b"], 3, "Q4_K_S", ctx_size=2048, batch_size=1, hbm_bytes=10 * GB)
+    assert lay is None or lay["tp"] in (1, 2)
+    # a mixed inventory: every rank must fit the smallest device that takes part
+    lay, plan = suggest_layout(SHAPES["qwen3-32b"], 4, "Q4_K_S", ctx_size=2048, batch_size=1, hbm_bytes=[180 * GB, 12 * GB, 12 * GB, 12 * GB])
+    assert lay["world"] == 1
+    # nothing fits: the reasons say why
+    lay, reasons = suggest_layout(SHAPES["qwen3-32b"], 2, "Q4_K_S", ctx_size=2048, batch_size=1, hbm_bytes=4 * GB)
+    assert lay is None and reasons and "GB" in reasons[0]
+    # the MoE model splits its experts
+    lay, plan = suggest_layout(SHAPES["qwen3-30b-a3b"], 8, "IQ3_S_MOE", ctx_size=1024, batch_size=64, hbm_bytes=8 * GB)
+    assert lay is not None and lay["world"] >= 2
+    rc, out, err = _cli("plan", "--synthetic", "qwen3-32b", "--synthetic-recipe", "Q4_K_S", "--suggest-layout", "8")
+    assert rc == 0 and "suggested layout: pp=1 x tp=1" in out and "flags: -d cuda:0" in out
