@@ -97,3 +97,19 @@ def test_tuning_table_keeps_only_clear_wins_and_validates_files(tmp_path):
     from llaminar_b200.models.config import SHAPES
     shapes = dict((n, (a, b)) for n, a, b in tuning.projection_shapes(SHAPES["qwen3-32b"], tp=2))
     assert shapes["qkv"] == (5120, 5120) and shapes["down"] == (5120, 12800) and shapes["gate_up"] == (25600, 5120)
+
+
+def test_perf_gate_flags_only_slowdowns_beyond_the_tolerance():
+    from llaminar_b200.ops import perf_gate
+    base = {"gemv": {"us": 40.0, "tolerance": 0.2}, "gemm_large": {"us": 500.0, "tolerance": 0.15}, "moe": {"us": 300.0}}
+    bad, notes = perf_gate.compare(base, {"gemv": 47.0, "gemm_large": 580.0, "moe": 250.0, "extra": 1.0})
+    assert len(bad) == 1 and bad[0].startswith("gemm_large") and "+16 %" in bad[0]
+    assert any(n.startswith("moe") and "faster" in n for n in notes) and any(n.startswith("extra") for n in notes)
+    bad, _ = perf_gate.compare(base, {"gemv": 40.0})
+    assert sorted(b.split(":")[0] for b in bad) == ["gemm_large", "moe"]
+    rec = {"mma_sync": {"us": 570.0, "tflops": 1.0}, "tcgen05": {"us": 480.0, "tflops": 1.0}}
+    assert perf_gate.extract_us("attn_prefill", rec) == {"attn_prefill.mma_sync": 570.0, "attn_prefill.tcgen05": 480.0}
+    assert perf_gate.extract_us("moe", {"us_three_launches": 315.0}) == {"moe": 315.0}
+    import json
+    doc = json.loads(perf_gate.BASELINE.read_text())
+    assert {"gemv", "gemm_small", "gemm_large", "attn_decode", "moe"} <= set(doc["cases"])
