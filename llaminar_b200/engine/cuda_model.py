@@ -378,6 +378,8 @@ class CudaModel:
             self._layer(L, fb, kv.layers[kv_layer_offset + li], T)
             if debug is not None:
                 debug(self.layer_ids[li], h)
+            if getattr(self, "taps", None) is not None:       # per-layer hidden states for the parity report
+                self.taps[f"layer{self.layer_ids[li]}"] = h.float().clone()
         logits = None
         if want_logits and self.head is not None:
             rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())

@@ -156,6 +156,8 @@ class TorchPagedModel:
         h = fb.embeds.float() if fb.embeds is not None else self.embed[fb.tokens.long()].float()
         for li, L in enumerate(self.layers):
             h = self._layer(L, h, fb, kv.layers[kv_layer_offset + li])
+            if getattr(self, "taps", None) is not None:       # per-layer hidden states for the parity report
+                self.taps[f"layer{li}"] = h.float().clone()
         logits = None
         if want_logits and self.head is not None:
             rows = h if fb.logit_rows is None else h.index_select(0, fb.logit_rows.long())

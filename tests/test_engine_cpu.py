@@ -64,3 +64,21 @@ def test_sampler_reference():
     assert picks <= {1, 2}
     # DRY: history "a b c a b" -> emitting c would extend a repeat of length 2
     assert dry_match_lengths([1, 2, 3, 1, 2]) == {3: 2}
+
+
+def test_parity_report_against_the_oracle(tmp_path):
+    """The parity tool: per-layer cosine / logit gates of the runtime model against the fp32 oracle, CSV output, and a
+    failing gate when the runtime model is broken on purpose."""
+    from llaminar_b200 import parity
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    out = tmp_path / "p.csv"
+    assert parity.main(["--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0", "-d", "cpu", "--prompt-tokens", "24",
+                        "--decode-steps", "2", "--csv", str(out)]) == 0
+    lines = out.read_text().splitlines()
+    assert lines[0].startswith("phase,stage,cosine") and len(lines) == 1 + 3 * (2 + 1)
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    rows, failed = parity.compare(w, "cpu", prompt_tokens=16, decode_steps=1)
+    assert not failed and all(r["cosine"] > 0.9999 for r in rows if r["stage"] != "logits")
+    m = parity.logit_metrics(torch.tensor([[0.0, 5.0, 1.0, 0.5, 0.2, 0.1]]), torch.tensor([[5.0, 0.0, 1.0, 0.5, 0.2, 0.1]]))
+    assert m["top1"] == 0.0 and m["kl"] > 1.0 and abs(m["top5_overlap"] - 0.8) < 1e-9
