@@ -137,3 +137,60 @@ def test_text_completion_endpoint(server):
     assert st == 400 and json.loads(body)["error"]["param"] == "prompt"
     st, body, _ = _post(server, {"prompt": "x", "max_tokens": 0}, path="/v1/completions")
     assert st == 400
+
+
+def test_serve_process_end_to_end(tmp_path):
+    """The `serve` command as a separate process: wait for /health, one chat completion, one streamed completion, a
+    long prompt, then SIGTERM and a clean exit (the reference drives its server the same way from a shell script:
+    tests/v2/e2e/server/test_server_e2e.sh)."""
+    import http.client
+    import json
+    import signal
+    import socket
+    import subprocess
+    import sys
+    import time
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    log = open(tmp_path / "serve.log", "w")
+    proc = subprocess.Popen([sys.executable, "-m", "llaminar_b200", "serve", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0",
+                             "-d", "cpu", "--host", "127.0.0.1", "--port", str(port), "-c", "512"], stdout=log, stderr=subprocess.STDOUT)
+    try:
+        deadline = time.time() + 120
+        ready = False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                c = http.client.HTTPConnection("127.0.0.1", port, timeout=5)
+                c.request("GET", "/health")
+                if c.getresponse().status == 200:
+                    ready = True
+                    break
+            except OSError:
+                time.sleep(0.5)
+        assert ready, (tmp_path / "serve.log").read_text()[-2000:]
+
+        def post(body):
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+            c.request("POST", "/v1/chat/completions", body=json.dumps(body), headers={"Content-Type": "application/json"})
+            r = c.getresponse()
+            return r.status, r.read().decode()
+        st, body = post({"messages": [{"role": "user", "content": "What is 2 + 2?"}], "max_tokens": 8, "temperature": 0})
+        j = json.loads(body)
+        assert st == 200 and j["choices"][0]["finish_reason"] in ("length", "stop") and j["usage"]["completion_tokens"] <= 8
+        st, body = post({"messages": [{"role": "user", "content": "count"}], "max_tokens": 6, "temperature": 0, "stream": True})
+        events = [ln[6:] for ln in body.splitlines() if ln.startswith("data: ")]
+        assert st == 200 and events[-1] == "[DONE]" and all("chat.completion.chunk" in e for e in events[:-1])
+        st, body = post({"messages": [{"role": "user", "content": "lorem ipsum " * 15}], "max_tokens": 4, "temperature": 0})
+        assert st == 200 and json.loads(body)["usage"]["prompt_tokens"] > 100
+        st, body = post({"messages": [{"role": "user", "content": "lorem ipsum " * 60}], "max_tokens": 4, "temperature": 0})
+        assert st == 400 and json.loads(body)["error"]["type"] == "context_length_exceeded"
+        st, body = post({"messages": "not a list"})
+        assert st == 400
+        proc.send_signal(signal.SIGTERM)
+        assert proc.wait(timeout=60) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+        log.close()
