@@ -95,7 +95,7 @@ def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.
     ``ksplit`` 0 lets the tuning table (``ops/tuning.py``), then the kernel's heuristic, pick the split-K factor."""
     rows = x.shape[0]
     assert 1 <= rows <= GEMV_MAX_ROWS
-    if ksplit == 0 and tuned:
+    if ksplit == 0 and tuned and tp is None:          # the fused all-reduce epilogue keeps the kernel's own choice
         from .tuning import table
         ksplit = table().ksplit("gemv", pw.fmt, pw.n, pw.k, rows)
     accum, tickets = _accum_args(pw, rows, scratch)
