@@ -107,6 +107,9 @@ def build_engine(cfg: OrchestrationConfig):
     t0 = time.time()
     weights = load_weights(cfg, dev)
     mcfg = weights.config
+    if v["ctx_size"] > mcfg.context_length:
+        # positions beyond the trained maximum are extrapolated RoPE angles: refuse rather than degrade silently
+        raise ConfigError([f"--ctx-size {v['ctx_size']} exceeds the model's trained context of {mcfg.context_length} tokens"])
     plan = build_plan(mcfg, layout, ctx_size=v["ctx_size"], batch_size=v["batch_size"])
     if plan.errors:
         raise ConfigError(plan.errors)

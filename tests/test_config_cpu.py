@@ -88,6 +88,8 @@ def test_cli_oneshot_benchmark_plan_describe(tmp_path):
     assert rc == 0 and "cpu" in out
     rc, out, err = _cli("oneshot", "--synthetic", "nope")
     assert rc != 0 and "unknown shape" in (out + err)
+    rc, out, err = _cli("oneshot", "--synthetic", "tiny-qwen3", "-d", "cpu", "-c", "8192", "-p", "x", "-n", "1")
+    assert rc != 0 and "trained context" in (out + err)
 
 
 def _spmd_run(rank, world):
