@@ -43,7 +43,9 @@ struct GemmTcParams {
     int* status;               // optional device word: set to STATUS_TIMEOUT if a pipeline wait gave up
     int* debug;                // optional trace buffer (progress markers / ns timestamps written by the kernels); nullptr in production
     const TpFuse* tp;          // EPI_RESID in the small-batch kernel: fused cross-rank all-reduce of each tile (nullptr: off)
-    int flags;                 // bit 1 (set by the launcher): stream-K work split in the small-batch kernel
+    int flags;                 // bit 1 (set by the launcher): stream-K work split in the small-batch kernel; with `debug`: 0x100 makes the
+                               // large-tile kernel write per-CTA ns timestamps (8 x u64 per CTA) instead of progress markers, bits 8.. select
+                               // the traced CTA of the small-batch kernel
     int ag_on;                 // large-tile kernel: x rows are gathered from the ranks of `ag` inside the launch
     AgFuse ag;
 };
