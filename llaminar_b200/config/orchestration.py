@@ -65,7 +65,9 @@ OPTIONS: list[OptionSpec] = [
     _o("--define-domain", action="append", default=[], help="name=dev,dev[;backend=nccl] : a named tensor-parallel domain", category="devices"),
     _o("--pp-stage", action="append", default=[], help="id=domain:first-last : a pipeline stage (layer range on a domain)", category="devices"),
     _o("--device-map", category="devices", unsupported="per-layer heterogeneous device maps are not built"),
-    _o("--topology", category="devices", unsupported="parallelism-tree topology strings are expressed with --define-domain/--pp-stage here"),
+    _o("--topology", category="devices",
+       help='parallelism tree, e.g. "PP(global, TP(a, cuda:0, cuda:1), TP(b, cuda:2, cuda:3))" or "TP(g, cuda:0, cuda:1)"; layers are split evenly'),
+    _o("--topology-file", category="devices", help="YAML file with a `topology:` tree (type pp/tp, name, children / devices)"),
     _o("--backend", default="auto", choices=("auto", "nccl", "fused", "gloo", "mpi", "rccl", "host"),
        help="collective backend: fused = in-kernel NVLink collectives (default on GPU), nccl = library baseline", category="devices"),
     _o("--list-devices", action="store_true", category="devices"),
@@ -186,6 +188,80 @@ class PPStageDefinition:
         return PPStageDefinition(sid, dom, a, b)
 
 
+def _topology_tokens(text: str) -> list[str]:
+    return re.findall(r"[A-Za-z_][\w.:-]*|[(),]", text)
+
+
+def parse_topology(text: str) -> dict:
+    """``KIND(name, child, ...)`` with KIND in {PP, TP} and children either nested nodes or devices -> a tree of dicts
+    {'type', 'name', 'children' | 'devices'} (the form the YAML file has).  Reference syntax:
+    src/v2/config/ParallelismTreeParser.h:25-28 (the reference parses the tree but does not run it yet)."""
+    toks = _topology_tokens(text)
+    if "".join(toks) != re.sub(r"\s+", "", text):
+        raise ValueError(f"--topology '{text}': unexpected characters")
+    pos = 0
+
+    def node() -> dict:
+        nonlocal pos
+        kind = toks[pos].lower() if pos < len(toks) else ""
+        if kind not in ("pp", "tp") or pos + 1 >= len(toks) or toks[pos + 1] != "(":
+            raise ValueError(f"--topology '{text}': expected PP(...) or TP(...) at token {pos}")
+        pos += 2
+        if pos >= len(toks) or toks[pos] in "(),":
+            raise ValueError(f"--topology '{text}': a node needs a name")
+        out = {"type": kind, "name": toks[pos], "children": [], "devices": []}
+        pos += 1
+        while pos < len(toks) and toks[pos] == ",":
+            pos += 1
+            if pos + 1 < len(toks) and toks[pos + 1] == "(":
+                out["children"].append(node())
+            elif pos < len(toks) and toks[pos] not in "(),":
+                out["devices"].append(toks[pos])
+                pos += 1
+            else:
+                raise ValueError(f"--topology '{text}': dangling ','")
+        if pos >= len(toks) or toks[pos] != ")":
+            raise ValueError(f"--topology '{text}': missing ')'")
+        pos += 1
+        return out
+
+    tree = node()
+    if pos != len(toks):
+        raise ValueError(f"--topology '{text}': trailing input after the root node")
+    return tree
+
+
+def topology_to_layout(tree: dict) -> tuple[list["DomainDefinition"], list["PPStageDefinition"]]:
+    """Domains and pipeline stages of a parallelism tree.  A TP root is one domain; a PP root has one stage per child
+    (a TP node, or a bare device = a stage of one GPU).  Stages carry no layer ranges: the layers are split evenly."""
+    kind = str(tree.get("type", "")).lower()
+    if kind == "tp":
+        if tree.get("children"):
+            raise ValueError(f"topology node '{tree.get('name')}': a TP node holds devices, not nodes")
+        devs = [str(d) for d in tree.get("devices") or []]
+        if not devs:
+            raise ValueError(f"topology node '{tree.get('name')}': a TP node needs devices")
+        dom = DomainDefinition(str(tree["name"]), devs)
+        if tree.get("backend"):
+            dom.backend = str(tree["backend"])
+        return [dom], []
+    if kind != "pp":
+        raise ValueError(f"topology node '{tree.get('name')}': type must be pp or tp")
+    domains, stages = [], []
+    kids = list(tree.get("children") or []) + [{"type": "tp", "name": f"{tree['name']}_{d.replace(':', '')}", "devices": [d]}
+                                               for d in tree.get("devices") or []]
+    if not kids:
+        raise ValueError(f"topology node '{tree.get('name')}': a PP node needs stages")
+    kids.sort(key=lambda k: k.get("rank", 0))                 # the YAML form may give explicit stage ranks; stable otherwise
+    for i, k in enumerate(kids):
+        if str(k.get("type", "")).lower() != "tp":
+            raise ValueError(f"topology node '{k.get('name')}': stages of a PP node must be TP nodes or devices")
+        d, _ = topology_to_layout(k)
+        domains += d
+        stages.append(PPStageDefinition(i, d[0].name, -1, -1))
+    return domains, stages
+
+
 @dataclass
 class OrchestrationConfig:
     command: str = "oneshot"
@@ -285,6 +361,16 @@ def parse_args(argv: list[str]) -> OrchestrationConfig:
     try:
         cfg.domains = [DomainDefinition.parse(t) for t in values.get("define_domain") or []]
         cfg.pp_stages = [PPStageDefinition.parse(t) for t in values.get("pp_stage") or []]
+        tree = None
+        if values.get("topology"):
+            tree = parse_topology(values["topology"])
+        elif values.get("topology_file"):
+            doc = _load_yaml(values["topology_file"])
+            tree = doc.get("topology", doc)
+        if tree is not None:
+            if cfg.domains or cfg.pp_stages:
+                raise ValueError("--topology cannot be combined with --define-domain / --pp-stage")
+            cfg.domains, cfg.pp_stages = topology_to_layout(tree)
     except ValueError as exc:
         raise ConfigError([str(exc)]) from exc
     errors = validate(cfg)
@@ -298,8 +384,9 @@ def validate(cfg: OrchestrationConfig) -> list[str]:
     v, ex = cfg.values, cfg.explicitly_set
     errs: list[str] = []
     modes = [name for name, on in (("-d", "device" in ex), ("-tp", "tp" in ex), ("--tp-devices", "tp_devices" in ex),
-                                   ("--define-domain", bool(cfg.domains)), ("--device-map", "device_map" in ex),
-                                   ("--topology", "topology" in ex)) if on]
+                                   ("--define-domain", bool(cfg.domains) and not ({"topology", "topology_file"} & ex)),
+                                   ("--device-map", "device_map" in ex), ("--topology", "topology" in ex),
+                                   ("--topology-file", "topology_file" in ex)) if on]
     if len(modes) > 1 and not (set(modes) == {"--define-domain"}):
         errs.append(f"device selection flags are mutually exclusive, got {' and '.join(modes)}")
     for o in OPTIONS:
@@ -316,10 +403,11 @@ def validate(cfg: OrchestrationConfig) -> list[str]:
             if s.domain not in names:
                 errs.append(f"--pp-stage {s.stage_id}: unknown domain '{s.domain}'")
         st = sorted(cfg.pp_stages, key=lambda s: s.stage_id)
+        implicit = all(s.last_layer < 0 for s in st)          # stages of a topology tree: layers are split evenly
         for a, b in zip(st, st[1:]):
-            if b.first_layer != a.last_layer + 1:
+            if not implicit and b.first_layer != a.last_layer + 1:
                 errs.append(f"--pp-stage {b.stage_id}: layers must continue at {a.last_layer + 1}, got {b.first_layer}")
-        if st and st[0].first_layer != 0:
+        if st and not implicit and st[0].first_layer != 0:
             errs.append("--pp-stage 0 must start at layer 0")
         sizes = {len(d.devices) for d in cfg.domains if d.name in {s.domain for s in cfg.pp_stages}}
         if len(sizes) > 1:

@@ -166,3 +166,30 @@ def test_suggest_layout_from_synthetic_inventories():
     assert lay is not None and lay["world"] >= 2
     rc, out, err = _cli("plan", "--synthetic", "qwen3-32b", "--synthetic-recipe", "Q4_K_S", "--suggest-layout", "8")
     assert rc == 0 and "suggested layout: pp=1 x tp=1" in out and "flags: -d cuda:0" in out
+
+
+def test_topology_tree_string_and_file(tmp_path):
+    """--topology / --topology-file: a parallelism tree becomes domains and evenly split pipeline stages."""
+    from llaminar_b200.config.orchestration import parse_topology, topology_to_layout
+    c = parse_args(["plan", "--synthetic", "qwen3-32b", "--topology", "PP(global, TP(a, cuda:0, cuda:1), TP(b, cuda:2, cuda:3))"])
+    lay = c.layout()
+    assert (lay["pp"], lay["tp"], lay["world"]) == (2, 2, 4) and [s[0] for s in lay["stages"]] == ["a", "b"]
+    plan = build_plan(SHAPES["qwen3-32b"], lay)
+    assert not plan.errors and [(r.first_layer, r.last_layer) for r in plan.ranks] == [(0, 31), (0, 31), (32, 63), (32, 63)]
+    lay = parse_args(["plan", "--synthetic", "qwen3-8b", "--topology", "tp(g, cuda:0, cuda:1, cuda:2, cuda:3)"]).layout()
+    assert (lay["pp"], lay["tp"]) == (1, 4)
+    lay = parse_args(["plan", "--synthetic", "qwen3-8b", "--topology", "PP(g, cuda:0, cuda:1, cuda:2)"]).layout()
+    assert (lay["pp"], lay["tp"], lay["world"]) == (3, 1, 3)
+    y = tmp_path / "t.yaml"
+    y.write_text("topology:\n  type: pp\n  name: global\n  children:\n    - {type: tp, name: s1, rank: 1, devices: ['cuda:2', 'cuda:3']}\n"
+                 "    - {type: tp, name: s0, rank: 0, backend: nccl, devices: ['cuda:0', 'cuda:1']}\n")
+    c = parse_args(["plan", "--synthetic", "qwen3-32b", "--topology-file", str(y)])
+    assert [s[0] for s in c.layout()["stages"]] == ["s0", "s1"] and c.domains[0].backend == "nccl"
+    for bad in ("PP(global", "XX(a, cuda:0)", "TP(a)", "PP(g, TP(a, cuda:0), TP(b, cuda:0))", "TP(a, cuda:0) junk", "TP(a, TP(b, cuda:0))",
+                "PP(g, TP(a, cuda:0, cuda:1), TP(b, cuda:2))"):
+        with pytest.raises(ConfigError):
+            parse_args(["plan", "--synthetic", "qwen3-32b", "--topology", bad])
+    with pytest.raises(ConfigError):
+        parse_args(["plan", "--synthetic", "qwen3-32b", "--topology", "TP(a, cuda:0, cuda:1)", "--tp-devices", "cuda:0,cuda:1"])
+    tree = parse_topology("PP(x, TP(y, cuda:0))")
+    assert tree["children"][0]["devices"] == ["cuda:0"] and topology_to_layout(tree)[1][0].domain == "y"
