@@ -64,7 +64,7 @@ OPTIONS: list[OptionSpec] = [
        unsupported="heterogeneous proportional splits are not built (homogeneous B200 ranks only)"),
     _o("--define-domain", action="append", default=[], help="name=dev,dev[;backend=nccl] : a named tensor-parallel domain", category="devices"),
     _o("--pp-stage", action="append", default=[], help="id=domain:first-last : a pipeline stage (layer range on a domain)", category="devices"),
-    _o("--device-map", category="devices", unsupported="per-layer heterogeneous device maps are not built"),
+    _o("--device-map", category="devices", help='explicit rank -> device mapping of one tensor-parallel group, e.g. "0=cuda:0,1=cuda:1"'),
     _o("--topology", category="devices",
        help='parallelism tree, e.g. "PP(global, TP(a, cuda:0, cuda:1), TP(b, cuda:2, cuda:3))" or "TP(g, cuda:0, cuda:1)"; layers are split evenly'),
     _o("--topology-file", category="devices", help="YAML file with a `topology:` tree (type pp/tp, name, children / devices)"),
@@ -188,6 +188,23 @@ class PPStageDefinition:
         return PPStageDefinition(sid, dom, a, b)
 
 
+def parse_device_map(text: str) -> list[str]:
+    """``rank=device,...`` -> devices in rank order (reference: --device-map, src/v2/config/OrchestrationConfigParser.cpp:1190).
+    Ranks must be 0..n-1 without gaps; the ranks form one tensor-parallel group, rank r on the r-th device."""
+    pairs = {}
+    for item in text.split(","):
+        m = re.match(r"^\s*(\d+)\s*=\s*([\w:.-]+)\s*$", item)
+        if not m:
+            raise ValueError(f"--device-map '{text}': expected rank=device, got '{item.strip()}'")
+        r = int(m.group(1))
+        if r in pairs:
+            raise ValueError(f"--device-map '{text}': rank {r} appears twice")
+        pairs[r] = m.group(2)
+    if sorted(pairs) != list(range(len(pairs))):
+        raise ValueError(f"--device-map '{text}': ranks must be 0..{len(pairs) - 1} without gaps")
+    return [pairs[r] for r in range(len(pairs))]
+
+
 def _topology_tokens(text: str) -> list[str]:
     return re.findall(r"[A-Za-z_][\w.:-]*|[(),]", text)
 
@@ -279,6 +296,8 @@ class OrchestrationConfig:
     # -- derived layout -------------------------------------------------------------------------------------
     def tp_devices_list(self) -> list[str]:
         v = self.values
+        if v.get("device_map"):
+            return parse_device_map(v["device_map"])
         if v.get("tp_devices"):
             return [d.strip() for d in v["tp_devices"].split(",") if d.strip()]
         if v.get("tp"):
@@ -361,6 +380,8 @@ def parse_args(argv: list[str]) -> OrchestrationConfig:
     try:
         cfg.domains = [DomainDefinition.parse(t) for t in values.get("define_domain") or []]
         cfg.pp_stages = [PPStageDefinition.parse(t) for t in values.get("pp_stage") or []]
+        if values.get("device_map"):
+            parse_device_map(values["device_map"])
         tree = None
         if values.get("topology"):
             tree = parse_topology(values["topology"])

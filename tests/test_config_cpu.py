@@ -193,3 +193,13 @@ def test_topology_tree_string_and_file(tmp_path):
         parse_args(["plan", "--synthetic", "qwen3-32b", "--topology", "TP(a, cuda:0, cuda:1)", "--tp-devices", "cuda:0,cuda:1"])
     tree = parse_topology("PP(x, TP(y, cuda:0))")
     assert tree["children"][0]["devices"] == ["cuda:0"] and topology_to_layout(tree)[1][0].domain == "y"
+
+
+def test_device_map_is_an_explicit_rank_to_device_mapping():
+    c = parse_args(["plan", "--synthetic", "qwen3-32b", "--device-map", "1=cuda:3, 0=cuda:2"])
+    assert c.layout()["stages"][0][1] == ["cuda:2", "cuda:3"] and c.layout()["tp"] == 2
+    for bad in ("0=cuda:0,2=cuda:1", "a=cuda:0", "0=cuda:0,0=cuda:1"):
+        with pytest.raises(ConfigError):
+            parse_args(["plan", "--synthetic", "qwen3-32b", "--device-map", bad])
+    with pytest.raises(ConfigError):
+        parse_args(["plan", "--synthetic", "qwen3-32b", "--device-map", "0=cuda:0", "-d", "cuda:0"])
