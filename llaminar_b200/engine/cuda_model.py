@@ -286,6 +286,9 @@ class CudaModel:
             lin(x, h, epi=ops.EPI_RESID, scratch=self.scratch, xn=x if x.shape[0] > ops.GEMV_MAX_ROWS else None)
             return
         self.tp.row_parallel_resid(lin, x, h, self)
+        if self.tp.verify_checksums and not torch.cuda.is_current_stream_capturing():
+            # debug: after the (fused or NCCL) reduction every rank must hold the same residual rows, bit for bit
+            self.tp.verify_replicated(h, "row-parallel projection + all-reduce")
 
     def _layer(self, L: CudaLayer, fb: ForwardBatch, kv_layer: torch.Tensor, T: int) -> None:
         c, sc = self.cfg, self.scratch

@@ -35,6 +35,7 @@ class TPContext:
     order_check: object = None          # parallel.collective_check.CollectiveOrderChecker in debug mode
     moe_mode: str = "expert-parallel"   # --moe-expert-mode: expert-parallel | replicated
     skip_allreduce: bool = False        # debug switch LLAMINAR_SKIP_ALLREDUCE (isolates compute time; results are wrong)
+    verify_checksums: bool = False      # debug switch LLAMINAR_VERIFY_COLLECTIVES: every rank must hold the same reduced values
 
     @staticmethod
     def create(group=None, device=None, fused: bool | None = None) -> "TPContext":
@@ -43,6 +44,7 @@ class TPContext:
         device = torch.device(device if device is not None else "cpu")
         ctx = TPContext(group, rank, size, device)
         ctx.skip_allreduce = debug_env().skip_allreduce
+        ctx.verify_checksums = debug_env().verify_collectives
         if debug_env().collective_order_check:
             from .collective_check import CollectiveOrderChecker
             ctx.order_check = CollectiveOrderChecker(None)
@@ -71,7 +73,28 @@ class TPContext:
         dist.all_reduce(x, group=self.group)
         self.stats["allreduce_calls"] += 1
         self.stats["allreduce_bytes"] += x.numel() * x.element_size()
+        if self.verify_checksums:
+            self.verify_replicated(x, "all_reduce")
         return x
+
+    def verify_replicated(self, x: torch.Tensor, what: str) -> None:
+        """Debug check that ``x`` is bit-identical on every rank of the group (an all-reduce result, or the residual
+        stream after a fused reduce epilogue): the ranks exchange a 64-bit checksum of the bytes plus NaN / Inf counts and
+        raise on a mismatch.  Counterpart of the reference's LLAMINAR_MPI_VERIFY_CHECKSUMS (src/v2/utils/DebugEnv.h)."""
+        flat = x.detach().contiguous().view(-1).view(torch.uint8).to(torch.int64)
+        weights = torch.arange(1, flat.numel() + 1, dtype=torch.int64, device=flat.device) % 65521
+        mine = torch.stack([(flat * weights).sum(), flat.sum(),
+                            torch.isnan(x).sum().to(torch.int64) if x.is_floating_point() else flat.new_zeros(()),
+                            torch.isinf(x).sum().to(torch.int64) if x.is_floating_point() else flat.new_zeros(())])
+        everyone = torch.empty(self.size * 4, dtype=torch.int64, device=mine.device)
+        dist.all_gather_into_tensor(everyone, mine, group=self.group)
+        everyone = everyone.view(self.size, 4).cpu()
+        self.stats["verified_collectives"] = self.stats.get("verified_collectives", 0) + 1
+        bad = [r for r in range(self.size) if not torch.equal(everyone[r, :2], everyone[0, :2])]
+        if bad:
+            raise RuntimeError(f"{what}: ranks {bad} hold different bytes than rank 0 (checksums {everyone[:, 0].tolist()})")
+        if int(everyone[0, 2]) or int(everyone[0, 3]):
+            raise RuntimeError(f"{what}: result has {int(everyone[0, 2])} NaN and {int(everyone[0, 3])} Inf values")
 
     def all_gather_vocab(self, logits: torch.Tensor, vocab: int) -> torch.Tensor:
         """[rows, vocab_local] shards (rank order, last shard may be short) -> [rows, vocab]."""

@@ -28,6 +28,7 @@ REGISTRY: tuple[EnvVar, ...] = (
     EnvVar("LLAMINAR_TP_FUSED", bool, True, "fuse the row-parallel GEMM with its all-reduce over peer memory"),
     EnvVar("LLAMINAR_TP_SPIN_LIMIT", int, 4_000_000, "iterations of the bounded in-kernel wait for a peer"),
     EnvVar("LLAMINAR_COLLECTIVE_ORDER_CHECK", bool, False, "audit that all ranks issue the same collectives in the same order"),
+    EnvVar("LLAMINAR_VERIFY_COLLECTIVES", bool, False, "after every all-reduce compare a checksum of the result across ranks (and count NaN/Inf)"),
     EnvVar("LLAMINAR_SKIP_ALLREDUCE", bool, False, "debug: skip tensor-parallel all-reduces (results are wrong; isolates compute time)"),
     EnvVar("LLAMINAR_VALIDATE_TENSORS", bool, False, "scan activations for NaN/Inf after every layer"),
     EnvVar("LLAMINAR_PDL", bool, True, "launch the decode-path kernels with programmatic dependent launch (prologues overlap the previous kernel)"),

@@ -84,3 +84,35 @@ def test_moe_tensor_parallel_mode_is_rejected_by_name():
     import pytest
     with pytest.raises(ValueError, match="tensor-parallel"):
         TPPlan.build(SHAPES["tiny-qwen3moe"], 2, 0, "tensor-parallel")
+
+
+def _verify_worker(rank, world):
+    from llaminar_b200.parallel.tp import TPContext
+    tp = TPContext.create(device="cpu")
+    tp.verify_checksums = True
+    x = torch.full((4, 8), float(rank + 1))
+    tp.all_reduce(x)                                    # verified inside: every rank holds 3.0
+    ok_calls = tp.stats["verified_collectives"]
+    diverged = torch.full((4, 8), 1.0)
+    if rank == 1:
+        diverged[2, 3] = 1.0000001                      # one rank differs in one element
+    caught = ""
+    try:
+        tp.verify_replicated(diverged, "residual stream")
+    except RuntimeError as exc:
+        caught = str(exc)
+    bad = torch.full((4,), float("nan"))
+    nan_msg = ""
+    try:
+        tp.verify_replicated(bad, "logits")
+    except RuntimeError as exc:
+        nan_msg = str(exc)
+    return float(x[0, 0]), ok_calls, caught, nan_msg
+
+
+def test_collective_checksum_verification_catches_divergence_and_nans():
+    res = run_ranks(_verify_worker, 2)
+    for val, calls, caught, nan_msg in res:
+        assert val == 3.0 and calls == 1
+        assert "ranks [1] hold different bytes" in caught and "residual stream" in caught
+        assert "4 NaN" in nan_msg
