@@ -107,6 +107,19 @@ def build_engine(cfg: OrchestrationConfig):
     t0 = time.time()
     weights = load_weights(cfg, dev)
     mcfg = weights.config
+    if v.get("moe_expert_placement"):
+        from .models.expert_placement import ExpertStats, apply_placement, range_loads
+        try:
+            loads = ExpertStats.load(v["moe_expert_placement"])
+            perms = apply_placement(weights, loads, layout["tp"])
+        except (OSError, ValueError) as exc:
+            raise ConfigError([f"--moe-expert-placement: {exc}"]) from exc
+        if rank == 0 and perms:
+            l0 = min(perms)
+            before = range_loads(loads[l0], list(range(mcfg.n_experts)), layout["tp"])
+            after = range_loads(loads[l0], perms[l0], layout["tp"])
+            log.info("expert placement from %s: %d layers renumbered; layer %d load per rank %s -> %s", v["moe_expert_placement"],
+                     len(perms), l0, [int(x) for x in before], [int(x) for x in after])
     if v["ctx_size"] > mcfg.context_length:
         # positions beyond the trained maximum are extrapolated RoPE angles: refuse rather than degrade silently
         raise ConfigError([f"--ctx-size {v['ctx_size']} exceeds the model's trained context of {mcfg.context_length} tokens"])
@@ -137,6 +150,14 @@ def build_engine(cfg: OrchestrationConfig):
         engine = build_pipeline_engine(weights, layout, rank, **kw)
     else:
         engine = LLMEngine(weights, **kw)
+    if v.get("moe_stats_out") and mcfg.is_moe and rank == 0:
+        import atexit
+        from .models.expert_placement import ExpertStats
+        stats = ExpertStats(mcfg.n_layers, mcfg.n_experts)
+        target = getattr(engine.model, "inner", engine.model)
+        target.expert_stats = stats
+        engine.use_graphs = False                      # the router hook reads the chosen experts on the host
+        atexit.register(lambda: stats.dump(v["moe_stats_out"], mcfg.name))
     template = None
     if tok is not None:
         template = ChatTemplate.resolve(v.get("chat_template"), tok.chat_template,

@@ -82,7 +82,11 @@ OPTIONS: list[OptionSpec] = [
     # -- MoE ------------------------------------------------------------------------------------------------
     _o("--moe-expert-mode", default="expert-parallel", choices=("expert-parallel", "tensor-parallel", "replicated"), category="moe"),
     _o("--moe-overlay", category="moe", unsupported="CPU/GPU expert overlay tiers are not built"),
-    _o("--moe-rebalance", action="store_true", category="moe", unsupported="dynamic expert rebalancing is not built"),
+    _o("--moe-rebalance", action="store_true", category="moe",
+       unsupported="experts are not moved while serving; measure with --moe-stats-out and place them with --moe-expert-placement"),
+    _o("--moe-stats-out", category="moe", help="write per-layer router statistics (tokens per expert) to this JSON file at exit"),
+    _o("--moe-expert-placement", category="moe",
+       help="statistics file of --moe-stats-out: renumber every layer's experts so that the expert-parallel ranks carry balanced load"),
     # -- prefix cache ---------------------------------------------------------------------------------------
     _o("--prefix-cache", action="store_true", category="prefix-cache"),
     _o("--prefix-cache-storage", default="tiered", choices=("ram", "device", "tiered"), category="prefix-cache"),

@@ -175,6 +175,7 @@ class CudaModel:
         c, dev, pl = self.cfg, self.device, self.plan
         p = f"blk.{i}."
         L = CudaLayer()
+        L.index = i
         L.attn_norm = _f32(w[p + "attn_norm.weight"], dev)
         L.ffn_norm = _f32(w[p + "ffn_norm.weight"], dev)
         D = c.head_dim

@@ -46,6 +46,13 @@ class _FusedWS:
         self.tile_tickets = z((c.d_model + 127) // 128, dt=torch.int32)
 
 
+def _record_routing(model, L, ids: torch.Tensor) -> None:
+    """Router statistics for the load-aware expert placement (models/expert_placement.py); eager steps only."""
+    stats = getattr(model, "expert_stats", None)
+    if stats is not None and not torch.cuda.is_current_stream_capturing():
+        stats.record(L.index, ids)
+
+
 def fused_supported(model, L, T: int) -> bool:
     c = model.cfg
     if not hasattr(ops, "moe_route") or T * c.n_experts_used > FUSED_MAX_PAIRS or c.n_experts > 256 or c.d_model % 256:
@@ -69,6 +76,7 @@ def moe_forward_fused(model, L, h: torch.Tensor, T: int) -> None:
         ws = cache[T] = _FusedWS(model, T, slab.n_local)
     ops.moe_route(h, L.ffn_norm, c.rms_eps, L.router, k, c.norm_topk_prob, slab.e0, slab.n_local, ws.ids, ws.wts,
                   ws.items, ws.n_items, ws.ticket, ws.counts)
+    _record_routing(model, L, ws.ids)
     ops.moe_gate_up(slab.gate_up, h, L.ffn_norm, c.rms_eps, ws.act, ws.items, ws.n_items, k, ws.z_max, scratch=sc)
     ep = model.tp is not None and model.tp.size > 1 and getattr(model.tp, "moe_mode", "expert-parallel") != "replicated"
     symm = getattr(model.tp, "symm", None) if ep else None
@@ -99,6 +107,7 @@ def moe_forward(model, L, h: torch.Tensor, T: int) -> None:
     ids = torch.empty(T, k, dtype=torch.int32, device=dev)
     wts = torch.empty(T, k, dtype=torch.float32, device=dev)
     ops.moe_topk(logits, k, c.norm_topk_prob, ids, wts)
+    _record_routing(model, L, ids)
     slab = L.experts
     local = (ids >= slab.e0) & (ids < slab.e0 + slab.n_local)
     lids = torch.where(local, ids - slab.e0, torch.zeros_like(ids)).contiguous()

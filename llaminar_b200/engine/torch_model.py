@@ -43,7 +43,7 @@ class TorchPagedModel:
 
         def layer(i):
             p = f"blk.{i}."
-            L = {"attn_norm": f(p + "attn_norm.weight"), "ffn_norm": f(p + "ffn_norm.weight")}
+            L = {"attn_norm": f(p + "attn_norm.weight"), "ffn_norm": f(p + "ffn_norm.weight"), "index": i}
             qs, qe, ks, ke = pl.q_head_start * D, pl.q_head_stop * D, pl.kv_head_start * D, pl.kv_head_stop * D
             L["wq"], L["wk"], L["wv"] = f(p + "attn_q.weight")[qs:qe], f(p + "attn_k.weight")[ks:ke], f(p + "attn_v.weight")[ks:ke]
             L["wo"] = f(p + "attn_output.weight")[:, qs:qe]
@@ -125,6 +125,8 @@ class TorchPagedModel:
         if not c.is_moe:
             return (F.silu(x @ L["wg"].T) * (x @ L["wu"].T)) @ L["wd"].T
         idx, wt = moe_route(x @ L["router"].T, c.n_experts_used, c.norm_topk_prob)
+        if getattr(self, "expert_stats", None) is not None:
+            self.expert_stats.record(L["index"], idx)
         out = torch.zeros_like(x)
         for e in range(L["e0"], L["e1"]):
             tok, slot = (idx == e).nonzero(as_tuple=True)

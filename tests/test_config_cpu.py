@@ -203,3 +203,16 @@ def test_device_map_is_an_explicit_rank_to_device_mapping():
             parse_args(["plan", "--synthetic", "qwen3-32b", "--device-map", bad])
     with pytest.raises(ConfigError):
         parse_args(["plan", "--synthetic", "qwen3-32b", "--device-map", "0=cuda:0", "-d", "cuda:0"])
+
+
+def test_cli_moe_stats_and_expert_placement(tmp_path):
+    stats = tmp_path / "stats.json"
+    base = ["oneshot", "--synthetic", "tiny-qwen3moe", "--synthetic-recipe", "Q8_0", "-d", "cpu", "-p", "hello world", "-n", "5"]
+    rc, out1, err = _cli(*base, "--moe-stats-out", str(stats))
+    assert rc == 0 and json.loads(stats.read_text())["n_experts"] == SHAPES["tiny-qwen3moe"].n_experts, err
+    rc, out2, err = _cli(*base, "--moe-expert-placement", str(stats))
+    assert rc == 0 and out2.strip().splitlines()[-1] == out1.strip().splitlines()[-1], err      # same model function
+    rc, out, err = _cli("oneshot", "--synthetic", "tiny-qwen3", "-d", "cpu", "-p", "x", "-n", "2", "--moe-expert-placement", str(stats))
+    assert rc != 0 and "mixture-of-experts" in (out + err)
+    rc, out, err = _cli(*base, "--moe-rebalance")
+    assert rc != 0 and "--moe-expert-placement" in (out + err)

@@ -95,6 +95,18 @@ def test_moe_engine_matches_oracle():
         assert row[t] >= row.max() - 0.05 * (row.max() - row.min())
 
 
+def test_router_statistics_on_the_gpu_model_count_every_routed_token():
+    from llaminar_b200.models.expert_placement import ExpertStats
+    cfg = SHAPES["tiny-qwen3moe"]
+    w = synthesize(cfg, "Q8_0", seed=5)
+    eng = LLMEngine(w, device="cuda", max_batch=2, max_context=256, use_graphs=False)
+    eng.model.expert_stats = ExpertStats(cfg.n_layers, cfg.n_experts)
+    eng.generate([_prompt(40, 9), _prompt(7, 3)], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    counts = eng.model.expert_stats.counts
+    rows = 40 + 7 + 2 * 4                                      # prompt rows plus one row per decode step after the first token
+    assert counts.sum(1).tolist() == [rows * cfg.n_experts_used] * cfg.n_layers and (counts >= 0).all()
+
+
 def _mtp_weights():
     import dataclasses
     return synthesize(dataclasses.replace(SHAPES["tiny-qwen3"], nextn_layers=1), "Q8_0", seed=1)

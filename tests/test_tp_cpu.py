@@ -116,3 +116,50 @@ def test_collective_checksum_verification_catches_divergence_and_nans():
         assert val == 3.0 and calls == 1
         assert "ranks [1] hold different bytes" in caught and "residual stream" in caught
         assert "4 NaN" in nan_msg
+
+
+def _placed_generate(rank, world, loads):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.expert_placement import apply_placement
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3moe"], "Q8_0", seed=0)
+    if loads is not None:
+        apply_placement(w, loads, world)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=tp)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 40)]
+    return eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+
+
+def test_expert_placement_balances_ranks_and_keeps_the_model_function(tmp_path):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.expert_placement import ExpertStats, balanced_permutation, range_loads
+    from llaminar_b200.models.synth import synthesize
+    cfg = SHAPES["tiny-qwen3moe"]
+    # 1. measure router statistics on one rank
+    w = synthesize(cfg, "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128)
+    eng.model.expert_stats = ExpertStats(cfg.n_layers, cfg.n_experts)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 40)]
+    base = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    f = tmp_path / "stats.json"
+    eng.model.expert_stats.dump(str(f), cfg.name)
+    loads = ExpertStats.load(str(f))
+    assert set(loads) == set(range(cfg.n_layers)) and sum(loads[0]) == (17 + 40 + 2 * 5) * cfg.n_experts_used
+    # 2. the permutation balances the two contiguous ranges at least as well as the checkpoint's numbering
+    perm = balanced_permutation(loads[0], 2)
+    assert sorted(perm) == list(range(cfg.n_experts))
+    before, after = range_loads(loads[0], list(range(cfg.n_experts)), 2), range_loads(loads[0], perm, 2)
+    assert max(after) - min(after) <= max(before) - min(before)
+    skew = [100.0, 90.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0]
+    p2 = balanced_permutation(skew, 2)
+    assert (0 in p2[:4]) != (1 in p2[:4]) and max(range_loads(skew, p2, 2)) < 110
+    # 3. renumbered experts compute the same function: same greedy tokens on 2 expert-parallel ranks
+    placed = run_ranks(_placed_generate, 2, loads)
+    plain = run_ranks(_placed_generate, 2, None)
+    assert placed[0] == placed[1] == plain[0] == base
