@@ -50,6 +50,47 @@ class ChatRequest:
     tools: list | None = None
     tool_choice: object = None
     parallel_tool_calls: bool = True
+    stop: list = field(default_factory=list)
+
+
+def parse_stop(value) -> list[str]:
+    """OpenAI ``stop``: a string or up to four strings (an extension of the reference's API, which stops on EOS only)."""
+    if value is None:
+        return []
+    items = [value] if isinstance(value, str) else value
+    if not isinstance(items, list) or len(items) > 4 or not all(isinstance(s, str) for s in items):
+        raise RequestError("`stop` must be a string or an array of at most 4 strings", param="stop")
+    return [s for s in items if s]
+
+
+class StopMatcher:
+    """Cuts generated text at the first stop sequence.  Text is released as soon as it can no longer be the beginning of
+    a stop sequence, so streaming stays incremental and never shows a part of the sequence itself."""
+
+    def __init__(self, stops: list[str]):
+        self.stops = stops
+        self.buf = ""
+        self.hit = False
+
+    def push(self, text: str) -> str:
+        if self.hit or not self.stops:
+            return "" if self.hit else text
+        self.buf += text
+        found = [i for i in (self.buf.find(s) for s in self.stops) if i >= 0]
+        if found:
+            out, self.buf, self.hit = self.buf[:min(found)], "", True
+            return out
+        hold = 0
+        for k in range(min(max(len(s) for s in self.stops) - 1, len(self.buf)), 0, -1):
+            if any(s.startswith(self.buf[-k:]) for s in self.stops):
+                hold = k
+                break
+        out, self.buf = self.buf[:len(self.buf) - hold], self.buf[len(self.buf) - hold:]
+        return out
+
+    def flush(self) -> str:
+        out, self.buf = ("" if self.hit else self.buf), ""
+        return out
 
 
 def parse_request(body_bytes: bytes) -> ChatRequest:
@@ -94,6 +135,7 @@ def parse_request(body_bytes: bytes) -> ChatRequest:
         req.tools = body["tools"]
     req.tool_choice = body.get("tool_choice")
     req.parallel_tool_calls = bool(body.get("parallel_tool_calls", True))
+    req.stop = parse_stop(body.get("stop"))
     for m in msgs:
         cm = {"role": str(m["role"]), "content": "" if m.get("content") is None else m.get("content")}
         if isinstance(cm["content"], list):        # OpenAI content parts: keep the text parts
@@ -145,6 +187,7 @@ class ChatCompletionHandler:
         thinking_tokens = 0
         n_completion = 0
         finish = "stop"
+        stopper = StopMatcher(req.stop)
         if budget_on and req.thinking_budget_tokens == 0 and stop_ids:
             for t in stop_ids:
                 self.loop.force_token(ticket, t)
@@ -161,34 +204,52 @@ class ChatCompletionHandler:
                 if ev[0] == "done":
                     finish = ev[1] or "stop"
                     break
+                if stopper.hit:
+                    continue                                  # tokens that were in flight when the stop sequence appeared
                 for tid in ev[1]:
                     n_completion += 1
                     if tid in self.eos_ids:
                         continue
                     piece = dec.push(tid)
                     if splitter is None:
+                        piece = stopper.push(piece)
                         if piece:
                             yield "delta", ("", piece)
+                        if stopper.hit:
+                            break
                         continue
                     was_thinking = splitter.in_think
                     r, c = splitter.push(piece)
+                    c = stopper.push(c) if c else c
                     if was_thinking:
                         thinking_tokens += 1
                     if r or c:
                         yield "delta", (r, c)
+                    if stopper.hit:
+                        break
                     if budget_on and not injected and splitter.in_think and thinking_tokens >= req.thinking_budget_tokens:
                         for t in stop_ids:
                             self.loop.force_token(ticket, t)
                         injected = True
-            tail = dec.flush()
-            if tail:
-                r, c = splitter.push(tail) if splitter else ("", tail)
-                if r or c:
-                    yield "delta", (r, c)
-            if splitter:
-                r, c = splitter.flush()
-                if r or c:
-                    yield "delta", (r, c)
+                if stopper.hit:
+                    self.loop.cancel(ticket)                  # the engine frees the sequence; a "done" event follows
+                    finish = "stop"
+                    break
+            if not stopper.hit:
+                tail = dec.flush()
+                if tail:
+                    r, c = splitter.push(tail) if splitter else ("", tail)
+                    c = stopper.push(c) if c else c
+                    if r or c:
+                        yield "delta", (r, c)
+                if splitter and not stopper.hit:
+                    r, c = splitter.flush()
+                    c = stopper.push(c) if c else c
+                    if r or c:
+                        yield "delta", (r, c)
+                rest = stopper.flush()
+                if rest:
+                    yield "delta", ("", rest)
         except GeneratorExit:
             self.loop.cancel(ticket)
             raise
@@ -257,6 +318,7 @@ class ChatCompletionHandler:
             raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
         sp.max_tokens = min(mt, budget)
         sp.stop_token_ids = tuple(self.eos_ids)
+        stopper = StopMatcher(parse_stop(body.get("stop")))
         ticket = self.loop.submit(ids, sp)
         dec = StreamDecoder(self.tok, skip_special=True)
         parts, n, finish = [], 0, "stop"
@@ -270,11 +332,21 @@ class ChatCompletionHandler:
             if ev[0] == "done":
                 finish = ev[1] or "stop"
                 break
+            if stopper.hit:
+                continue
             for tid in ev[1]:
                 n += 1
                 if tid not in self.eos_ids:
-                    parts.append(dec.push(tid))
-        parts.append(dec.flush())
+                    parts.append(stopper.push(dec.push(tid)))
+                if stopper.hit:
+                    self.loop.cancel(ticket)
+                    finish = "stop"
+                    break
+            if stopper.hit:
+                break
+        if not stopper.hit:
+            parts.append(stopper.push(dec.flush()))
+            parts.append(stopper.flush())
         return {"id": "cmpl-" + uuid.uuid4().hex[:24], "object": "text_completion", "created": int(time.time()),
                 "model": body.get("model") or self.model_name,
                 "choices": [{"index": 0, "text": "".join(parts), "finish_reason": "length" if finish == "length" else "stop"}],

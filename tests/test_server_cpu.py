@@ -194,3 +194,35 @@ def test_serve_process_end_to_end(tmp_path):
         if proc.poll() is None:
             proc.kill()
         log.close()
+
+
+def test_stop_sequences_cut_the_text_in_chat_stream_and_completions(server):
+    from llaminar_b200.serve.chat_handler import StopMatcher
+    m = StopMatcher(["END", "###"])
+    out = [m.push(t) for t in ("abc E", "N", "x EN", "D tail")]
+    assert "".join(out) == "abc ENx " and m.hit and m.flush() == ""          # held back "E", "EN" until they were settled
+    m2 = StopMatcher(["END"])
+    assert m2.push("no stop here E") == "no stop here " and m2.flush() == "E" and not m2.hit
+    msgs = [{"role": "user", "content": "hi there"}]
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 10, "temperature": 0})
+    full = json.loads(body)["choices"][0]["message"]["content"]
+    assert len(full) > 12
+    stop = full[len(full) // 2: len(full) // 2 + 5]
+    want = full[:full.find(stop)]
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 10, "temperature": 0, "stop": stop})
+    j = json.loads(body)
+    assert st == 200 and j["choices"][0]["message"]["content"] == want and j["choices"][0]["finish_reason"] == "stop"
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 10, "temperature": 0, "stop": ["zzzz", stop], "stream": True})
+    chunks = [json.loads(l[6:]) for l in body.decode().split("\n") if l.startswith("data: ") and l[6:] != "[DONE]"]
+    streamed = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+    assert streamed == want
+    st, body, _ = _post(server, {"messages": msgs, "stop": [1, 2]})
+    assert st == 400 and json.loads(body)["error"]["param"] == "stop"
+    st, body, _ = _post(server, {"prompt": "hi there", "max_tokens": 10, "temperature": 0}, path="/v1/completions")
+    text = json.loads(body)["choices"][0]["text"]
+    stop2 = text[len(text) // 2: len(text) // 2 + 5]
+    st, body, _ = _post(server, {"prompt": "hi there", "max_tokens": 10, "temperature": 0, "stop": stop2}, path="/v1/completions")
+    assert st == 200 and json.loads(body)["choices"][0]["text"] == text[:text.find(stop2)]
+    # the engine is still healthy after the cancellations
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 4, "temperature": 0})
+    assert st == 200
