@@ -31,6 +31,9 @@ class EngineLoop:
         self._wake = threading.Event()
         self.on_step = on_step
         self.errors = 0
+        # counters for /metrics (written by the engine thread only)
+        self.counters = {"requests_submitted": 0, "requests_finished": 0, "requests_cancelled": 0, "requests_rejected": 0,
+                         "prompt_tokens": 0, "generated_tokens": 0, "prefix_hit_tokens": 0, "engine_steps": 0}
         self._thread = threading.Thread(target=self._run, name="engine-loop", daemon=True)
         self._thread.start()
 
@@ -50,6 +53,17 @@ class EngineLoop:
         self._in.put(("cancel", ticket))
         self._wake.set()
 
+    def metrics(self) -> dict:
+        """Counters plus the current queue state (read from handler threads; plain ints, no locking needed)."""
+        m = dict(self.counters)
+        m["engine_errors"] = self.errors
+        m["requests_running"] = len(self._tickets)
+        m["requests_waiting"] = len(getattr(self.engine, "waiting", ()))
+        alloc = getattr(getattr(self.engine, "kv", None), "allocator", None)
+        if alloc is not None:
+            m["kv_pages_free"] = int(alloc.n_free)
+        return m
+
     def shutdown(self) -> None:
         self._stop.set()
         self._wake.set()
@@ -68,13 +82,17 @@ class EngineLoop:
                     r = self.engine.add_request(t.prompt, t.params)
                     t.rid = r.rid
                     self._tickets[r.rid] = t
+                    self.counters["requests_submitted"] += 1
+                    self.counters["prompt_tokens"] += len(t.prompt)
                 except Exception as exc:                       # e.g. prompt longer than the context window
+                    self.counters["requests_rejected"] += 1
                     t.events.put(("error", str(exc), 400))
             elif kind == "force" and t.rid is not None:
                 self.engine.force_token(t.rid, cmd[2])
             elif kind == "cancel" and t.rid is not None:
                 self.engine.abort(t.rid)
-                self._tickets.pop(t.rid, None)
+                if self._tickets.pop(t.rid, None) is not None:
+                    self.counters["requests_cancelled"] += 1
                 self.engine.requests.pop(t.rid, None)
 
     def _run(self) -> None:
@@ -87,6 +105,7 @@ class EngineLoop:
                 continue
             try:
                 outs = eng.step()
+                self.counters["engine_steps"] += 1
             except Exception as exc:                           # fail the running requests, keep serving
                 self.errors += 1
                 msg = f"{type(exc).__name__}: {exc}"
@@ -109,8 +128,11 @@ class EngineLoop:
                 if req is not None:
                     t.prefix_hit_tokens = req.prefix_hit_tokens
                 if o.new_tokens:
+                    self.counters["generated_tokens"] += len(o.new_tokens)
                     t.events.put(("tokens", list(o.new_tokens)))
                 if o.finished:
+                    self.counters["requests_finished"] += 1
+                    self.counters["prefix_hit_tokens"] += int(t.prefix_hit_tokens or 0)
                     t.events.put(("done", o.finish_reason))
                     self._tickets.pop(o.rid, None)
                     eng.requests.pop(o.rid, None)

@@ -46,6 +46,18 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
             if self.path.rstrip("/") == "/health":
                 self._send_json(200, {"status": "ok", "model": chat.model_name, "requests_served": state["served"],
                                       "engine_errors": chat.loop.errors})
+            elif self.path.rstrip("/") == "/metrics":
+                # Prometheus text exposition (the reference has no metrics endpoint; its counters live in log lines)
+                lines = []
+                for k, v in sorted(chat.loop.metrics().items()):
+                    kind = "gauge" if k.startswith(("requests_running", "requests_waiting", "kv_")) else "counter"
+                    lines += [f"# TYPE llaminar_{k} {kind}", f"llaminar_{k} {v}"]
+                body = ("\n".join(lines) + "\n").encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4; charset=utf-8")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
             elif self.path.rstrip("/") == "/v1/models":
                 self._send_json(200, {"object": "list", "data": [{"id": chat.model_name, "object": "model", "owned_by": "local"}]})
             else:

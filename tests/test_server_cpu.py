@@ -226,3 +226,22 @@ def test_stop_sequences_cut_the_text_in_chat_stream_and_completions(server):
     # the engine is still healthy after the cancellations
     st, body, _ = _post(server, {"messages": msgs, "max_tokens": 4, "temperature": 0})
     assert st == 200
+
+
+def test_metrics_endpoint_counts_requests_and_tokens(server):
+    def scrape():
+        c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+        c.request("GET", "/metrics")
+        r = c.getresponse()
+        text = r.read().decode()
+        assert r.status == 200 and r.getheader("Content-Type").startswith("text/plain")
+        return {ln.split()[0]: float(ln.split()[1]) for ln in text.splitlines() if ln and not ln.startswith("#")}, text
+    before, text = scrape()
+    assert "# TYPE llaminar_generated_tokens counter" in text and "# TYPE llaminar_requests_running gauge" in text
+    st, body, _ = _post(server, {"messages": [{"role": "user", "content": "count me"}], "max_tokens": 5, "temperature": 0})
+    used = json.loads(body)["usage"]
+    after, _ = scrape()
+    assert after["llaminar_requests_finished"] == before["llaminar_requests_finished"] + 1
+    assert after["llaminar_generated_tokens"] - before["llaminar_generated_tokens"] == used["completion_tokens"]
+    assert after["llaminar_prompt_tokens"] - before["llaminar_prompt_tokens"] == used["prompt_tokens"]
+    assert after["llaminar_requests_running"] == 0 and after["llaminar_kv_pages_free"] > 0
