@@ -17,11 +17,12 @@
 // Every mbarrier wait is bounded; on a timeout the kernel raises the status word and tears down cleanly.
 //
 // Replaces flash_attention_2_pipelined_kernel of the reference (src/v2/kernels/cuda/attention/CUDAFlashAttentionKernels.cu:348).
-#include "common.cuh"
 #include "ops.h"
+#include "tc_common.cuh"
 
 namespace llm {
 namespace atc {
+using namespace tc5;
 
 constexpr int D = 128, BQ = 128, BK = 128, PAGE = 64;
 constexpr int ATOM = 128 * 128;                    // 128 rows x 64 bf16: one swizzled operand atom
@@ -36,14 +37,6 @@ constexpr int OFF_P = OFF_VT + 4 * ATOM;           // 2 atoms (key halves), rows
 constexpr int OFF_VS = OFF_P + 2 * ATOM;           // staging of the two V pages of a key tile: 128 keys x 256 bytes
 constexpr int SMEM_BYTES = OFF_VS + BK * D * 2 + 1024;
 
-LLM_DEVICE void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-LLM_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -55,48 +48,13 @@ LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_fla
     *abort_flag = 1;
     return false;
 }
-LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-LLM_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-LLM_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 LLM_DEVICE void cp_async16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
 LLM_DEVICE void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 LLM_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 LLM_DEVICE void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
-// K-major, 128-byte swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
-LLM_DEVICE uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3fff);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 // bf16 x bf16 -> fp32, both operands K-major, M = 128, N = 128
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-LLM_DEVICE void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate) : "memory");
-}
-LLM_DEVICE void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-LLM_DEVICE void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-// Completes every tcgen05.ld of this thread; the empty statements tie the array to the wait so that no use of it is scheduled earlier.
-LLM_DEVICE void tmem_wait_ld(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]));
-}
+constexpr uint32_t IDESC = instr_desc(128);
 LLM_DEVICE float ex2(float x) {                    // 2^x, approximate; -inf -> 0
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -388,7 +346,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
                 mma_f16(tmem + b * 128, smem_desc_sw128(sQ + (ks >> 2) * ATOM) + 2 * (ks & 3),
-                        smem_desc_sw128(sK + (b * 2 + (ks >> 2)) * ATOM) + 2 * (ks & 3), ks > 0 ? 1u : 0u);
+                        smem_desc_sw128(sK + (b * 2 + (ks >> 2)) * ATOM) + 2 * (ks & 3), IDESC, ks > 0 ? 1u : 0u);
             mma_commit(bar(S_FULL + b));
             mma_commit(bar(K_EMPTY + b));
         };
@@ -404,7 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
                 mma_f16(tmem + 256, smem_desc_sw128(sP + (ks >> 2) * ATOM) + 2 * (ks & 3),
-                        smem_desc_sw128(sVT + (b * 2 + (ks >> 2)) * ATOM) + 2 * (ks & 3), ks > 0 ? 1u : 0u);
+                        smem_desc_sw128(sVT + (b * 2 + (ks >> 2)) * ATOM) + 2 * (ks & 3), IDESC, ks > 0 ? 1u : 0u);
             mma_commit(bar(O_FULL));
             mma_commit(bar(VT_EMPTY + b));
         }
