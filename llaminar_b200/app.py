@@ -451,7 +451,7 @@ def cmd_describe(cfg: OrchestrationConfig) -> int:
 
 
 def print_help() -> None:
-    print("usage: python -m llaminar_b200 {oneshot|serve|benchmark|plan|describe} [options]\n")
+    print("usage: python -m llaminar_b200 {oneshot|chat|serve|benchmark|plan|describe} [options]\n")
     for cat, opts in help_by_category().items():
         print(f"[{cat}]")
         for o in opts:

@@ -334,7 +334,7 @@ class ConfigError(ValueError):
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="llaminar_b200", add_help=True, allow_abbrev=False,
-                                 description="Blackwell-native GGUF inference engine (oneshot | serve | benchmark | plan | describe)")
+                                 description="Blackwell-native GGUF inference engine (oneshot | chat | serve | benchmark | plan | describe)")
     ap.add_argument("command", nargs="?", default="oneshot", choices=SUBCOMMANDS)
     groups: dict[str, Any] = {}
     for o in OPTIONS:
