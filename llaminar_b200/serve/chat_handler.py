@@ -51,6 +51,7 @@ class ChatRequest:
     tool_choice: object = None
     parallel_tool_calls: bool = True
     stop: list = field(default_factory=list)
+    n: int = 1
 
 
 def parse_stop(value) -> list[str]:
@@ -136,6 +137,12 @@ def parse_request(body_bytes: bytes) -> ChatRequest:
     req.tool_choice = body.get("tool_choice")
     req.parallel_tool_calls = bool(body.get("parallel_tool_calls", True))
     req.stop = parse_stop(body.get("stop"))
+    n = body.get("n", 1)
+    if not isinstance(n, int) or isinstance(n, bool) or not 1 <= n <= 8:
+        raise RequestError("`n` must be an integer between 1 and 8", param="n")
+    if n > 1 and req.stream:
+        raise RequestError("`n` > 1 is not supported together with `stream`", param="n")
+    req.n = n
     for m in msgs:
         cm = {"role": str(m["role"]), "content": "" if m.get("content") is None else m.get("content")}
         if isinstance(cm["content"], list):        # OpenAI content parts: keep the text parts
@@ -266,6 +273,33 @@ class ChatCompletionHandler:
 
     # -- non-streaming --------------------------------------------------------------------------------------
     def handle(self, req: ChatRequest) -> dict:
+        if req.n > 1:
+            return self._handle_many(req)
+        return self._handle_one(req)
+
+    def _handle_many(self, req: ChatRequest) -> dict:
+        """OpenAI ``n``: the choices are independent requests that run side by side in the engine's batch (and share the
+        prompt's prefix-cache blocks); choice i draws with seed + i when the request gives a seed."""
+        import copy
+        from concurrent.futures import ThreadPoolExecutor
+        reqs = []
+        for i in range(req.n):
+            r = copy.copy(req)
+            r.n = 1
+            r.sampling = dict(req.sampling)
+            if r.sampling.get("seed") is not None:
+                r.sampling["seed"] = int(r.sampling["seed"]) + i
+            reqs.append(r)
+        with ThreadPoolExecutor(max_workers=req.n) as pool:
+            outs = list(pool.map(self._handle_one, reqs))
+        first = outs[0]
+        first["choices"] = [dict(o["choices"][0], index=i) for i, o in enumerate(outs)]
+        u = first["usage"]
+        u["completion_tokens"] = sum(o["usage"]["completion_tokens"] for o in outs)
+        u["total_tokens"] = u["prompt_tokens"] + u["completion_tokens"]
+        return first
+
+    def _handle_one(self, req: ChatRequest) -> dict:
         reasoning, content, info = [], [], None
         for kind, payload in self._generate(req):
             if kind == "delta":

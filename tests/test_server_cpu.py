@@ -245,3 +245,20 @@ def test_metrics_endpoint_counts_requests_and_tokens(server):
     assert after["llaminar_generated_tokens"] - before["llaminar_generated_tokens"] == used["completion_tokens"]
     assert after["llaminar_prompt_tokens"] - before["llaminar_prompt_tokens"] == used["prompt_tokens"]
     assert after["llaminar_requests_running"] == 0 and after["llaminar_kv_pages_free"] > 0
+
+
+def test_n_choices_run_as_parallel_requests(server):
+    msgs = [{"role": "user", "content": "pick something"}]
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 6, "temperature": 1.0, "top_k": 0, "top_p": 1.0, "seed": 3, "n": 3})
+    j = json.loads(body)
+    assert st == 200 and [c["index"] for c in j["choices"]] == [0, 1, 2]
+    texts = [c["message"]["content"] for c in j["choices"]]
+    assert len(set(texts)) > 1                                   # different seeds: the draws differ
+    assert j["usage"]["completion_tokens"] <= 18 and j["usage"]["total_tokens"] == j["usage"]["prompt_tokens"] + j["usage"]["completion_tokens"]
+    # choice 0 is what a single request with the same seed returns
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 6, "temperature": 1.0, "top_k": 0, "top_p": 1.0, "seed": 3})
+    assert json.loads(body)["choices"][0]["message"]["content"] == texts[0]
+    st, body, _ = _post(server, {"messages": msgs, "n": 2, "stream": True})
+    assert st == 400 and json.loads(body)["error"]["param"] == "n"
+    st, body, _ = _post(server, {"messages": msgs, "n": 0})
+    assert st == 400
