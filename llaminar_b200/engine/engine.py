@@ -43,6 +43,7 @@ class Request:
     draft: list[int] = field(default_factory=list)
     step_count: int = 0
     terminal: object = None                               # prefix-cache terminal state: the forward pass is skipped
+    logprobs: list = field(default_factory=list)          # one (token, logprob, [(token, logprob), ...]) per output token
 
     @property
     def all_tokens(self) -> list[int]:
@@ -59,6 +60,7 @@ class StepOutput:
     new_tokens: list[int]
     finished: bool
     finish_reason: str | None = None
+    logprobs: list | None = None        # entries of Request.logprobs for new_tokens, when the request asked for them
 
 
 class LLMEngine:
@@ -177,6 +179,8 @@ class LLMEngine:
         params = params or SamplingParams()
         if len(prompt) + 1 > self.max_context:
             raise ValueError(f"prompt of {len(prompt)} tokens exceeds the context window of {self.max_context}")
+        if params.wants_logprobs and self.mtp is not None:
+            raise ValueError("log-probabilities are not available while speculative decoding (MTP) is on")
         r = Request(next(self._rid), list(prompt), params, t_arrival=time.perf_counter())
         self.requests[r.rid] = r
         self.waiting.append(r)
@@ -339,18 +343,47 @@ class LLMEngine:
             reason = self._check_stop(r, t)
             if reason:
                 self._finish(r, reason)
-                return StepOutput(r.rid, new, True, reason)
-        return StepOutput(r.rid, new, False)
+                return StepOutput(r.rid, new, True, reason, self._new_logprobs(r, len(new)))
+        return StepOutput(r.rid, new, False, None, self._new_logprobs(r, len(new)))
+
+    @staticmethod
+    def _new_logprobs(r: Request, n: int) -> list | None:
+        if not r.params.wants_logprobs:
+            return None
+        return r.logprobs[len(r.logprobs) - n:] if n else []
+
+    @staticmethod
+    def _record_logprobs(logits: torch.Tensor, reqs: list[Request], toks: list[int]) -> None:
+        """Log-probabilities of the model's own distribution (full-vocabulary rows, before penalties, temperature and
+        truncation) for the requests that asked: the emitted token and the k likeliest ones."""
+        rows = [i for i, r in enumerate(reqs) if r.params.wants_logprobs]
+        if not rows:
+            return
+        lp = torch.log_softmax(logits[rows].float(), dim=-1)
+        k = max(reqs[i].params.logprobs for i in rows)
+        chosen = lp.gather(1, torch.tensor([[toks[i]] for i in rows], device=lp.device)).view(-1).tolist()
+        top_v, top_i = (lp.topk(k, dim=-1) if k else (lp[:, :0], lp[:, :0].long()))
+        top_v, top_i = top_v.tolist(), top_i.tolist()
+        for j, i in enumerate(rows):
+            kk = reqs[i].params.logprobs
+            reqs[i].logprobs.append((int(toks[i]), float(chosen[j]), list(zip(top_i[j][:kk], top_v[j][:kk]))))
 
     # -- sampling -----------------------------------------------------------------------------------
     def _sample_rows(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
         """Eager sampling of one row per request (prefill tail, penalties, CPU backend)."""
         all_greedy = all(r.params.is_greedy and not r.params.needs_penalties and not r.forced for r in reqs)
-        if all_greedy and self._sharded_vocab() and logits.shape[0] <= self._pairs.shape[0]:
+        want_lp = any(r.params.wants_logprobs for r in reqs)
+        if all_greedy and not want_lp and self._sharded_vocab() and logits.shape[0] <= self._pairs.shape[0]:
             tok = torch.empty(len(reqs), dtype=torch.int32, device=self.device)
             self._sharded_argmax(logits.contiguous(), len(reqs), tok)
             return tok.tolist()
         logits = self._gather_vocab(logits)
+        out = self._sample_full_rows(logits, reqs, all_greedy)
+        if want_lp:
+            self._record_logprobs(logits, reqs, out)
+        return out
+
+    def _sample_full_rows(self, logits: torch.Tensor, reqs: list[Request], all_greedy: bool) -> list[int]:
         out = []
         if all_greedy:
             if self.is_cuda:
@@ -491,7 +524,7 @@ class LLMEngine:
         t0 = time.perf_counter()
         for r in reqs:
             self._ensure_pages(r, r.n_tokens)
-        eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced for r in reqs)
+        eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced or r.params.wants_logprobs for r in reqs)
         if self.is_cuda:
             toks = self._decode_cuda(reqs, eager)
         else:

@@ -26,6 +26,11 @@ class SamplingParams:
     max_tokens: int = 128
     stop_token_ids: tuple[int, ...] = ()
     ignore_eos: bool = False
+    logprobs: int = -1                  # -1 off; k >= 0: report the chosen token's log-probability and the k likeliest tokens
+
+    @property
+    def wants_logprobs(self) -> bool:
+        return self.logprobs >= 0
 
     @property
     def is_greedy(self) -> bool:

@@ -52,6 +52,8 @@ class ChatRequest:
     parallel_tool_calls: bool = True
     stop: list = field(default_factory=list)
     n: int = 1
+    logprobs: bool = False
+    top_logprobs: int = 0
 
 
 def parse_stop(value) -> list[str]:
@@ -143,6 +145,17 @@ def parse_request(body_bytes: bytes) -> ChatRequest:
     if n > 1 and req.stream:
         raise RequestError("`n` > 1 is not supported together with `stream`", param="n")
     req.n = n
+    lp, top = body.get("logprobs", False), body.get("top_logprobs")
+    if not isinstance(lp, bool):
+        raise RequestError("`logprobs` must be a boolean", param="logprobs")
+    if top is not None:
+        if not isinstance(top, int) or isinstance(top, bool) or not 0 <= top <= 20:
+            raise RequestError("`top_logprobs` must be an integer between 0 and 20", param="top_logprobs")
+        if not lp:
+            raise RequestError("`top_logprobs` needs `logprobs` to be true", param="top_logprobs")
+    if lp and req.stream:
+        raise RequestError("`logprobs` is not supported together with `stream`", param="logprobs")
+    req.logprobs, req.top_logprobs = lp, int(top or 0)
     for m in msgs:
         cm = {"role": str(m["role"]), "content": "" if m.get("content") is None else m.get("content")}
         if isinstance(cm["content"], list):        # OpenAI content parts: keep the text parts
@@ -179,6 +192,8 @@ class ChatCompletionHandler:
         sp = merge_with_model_defaults(self.arch, req.sampling, self.cli_sampling)
         sp.max_tokens = max_tokens
         sp.stop_token_ids = tuple(self.eos_ids)
+        if req.logprobs:
+            sp.logprobs = req.top_logprobs
         starts_in_think = text.rstrip().endswith("<think>")
         return ids, sp, starts_in_think
 
@@ -195,6 +210,7 @@ class ChatCompletionHandler:
         n_completion = 0
         finish = "stop"
         stopper = StopMatcher(req.stop)
+        token_logprobs: list = []
         if budget_on and req.thinking_budget_tokens == 0 and stop_ids:
             for t in stop_ids:
                 self.loop.force_token(ticket, t)
@@ -213,10 +229,12 @@ class ChatCompletionHandler:
                     break
                 if stopper.hit:
                     continue                                  # tokens that were in flight when the stop sequence appeared
-                for tid in ev[1]:
+                for k, tid in enumerate(ev[1]):
                     n_completion += 1
                     if tid in self.eos_ids:
                         continue
+                    if len(ev) > 2 and ev[2]:
+                        token_logprobs.append(ev[2][k])
                     piece = dec.push(tid)
                     if splitter is None:
                         piece = stopper.push(piece)
@@ -261,7 +279,15 @@ class ChatCompletionHandler:
             self.loop.cancel(ticket)
             raise
         yield "end", {"prompt_tokens": len(ids), "completion_tokens": n_completion, "finish_reason": finish,
-                      "prefix_hit_tokens": ticket.prefix_hit_tokens}
+                      "prefix_hit_tokens": ticket.prefix_hit_tokens, "logprobs": token_logprobs}
+
+    def _logprobs_object(self, entries: list) -> dict:
+        """OpenAI `choices[i].logprobs`: one item per generated token with its text, bytes and log-probability under the
+        model's distribution, and the `top_logprobs` likeliest alternatives (an extension of the reference's API)."""
+        def item(tid: int, lp: float) -> dict:
+            raw = self.tok.token_bytes(int(tid))
+            return {"token": raw.decode("utf-8", errors="replace"), "logprob": max(float(lp), -9999.0), "bytes": list(raw)}
+        return {"content": [dict(item(t, lp), top_logprobs=[item(a, b) for a, b in top]) for t, lp, top in entries]}
 
     def _usage(self, info: dict) -> dict:
         p, c = info["prompt_tokens"], info["completion_tokens"]
@@ -323,9 +349,12 @@ class ChatCompletionHandler:
             message["content"] = text
         if think:
             message["reasoning_content"] = think
+        choice = {"index": 0, "message": message, "finish_reason": finish}
+        if req.logprobs:
+            choice["logprobs"] = self._logprobs_object(info["logprobs"])
         return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
                 "model": req.model or self.model_name, "system_fingerprint": SYSTEM_FINGERPRINT,
-                "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": self._usage(info)}
+                "choices": [choice], "usage": self._usage(info)}
 
     # -- raw text completion (no chat template) ---------------------------------------------------------------
     def complete(self, body_bytes: bytes) -> dict:

@@ -16,7 +16,7 @@ from dataclasses import dataclass, field
 class Ticket:
     prompt: list[int]
     params: object
-    events: "queue.Queue" = field(default_factory=queue.Queue)     # ("tokens", [ids]) / ("done", reason) / ("error", msg)
+    events: "queue.Queue" = field(default_factory=queue.Queue)     # ("tokens", [ids], logprobs | None) / ("done", reason) / ("error", msg, status)
     rid: int | None = None
     cancelled: bool = False
     prefix_hit_tokens: int = 0
@@ -129,7 +129,7 @@ class EngineLoop:
                     t.prefix_hit_tokens = req.prefix_hit_tokens
                 if o.new_tokens:
                     self.counters["generated_tokens"] += len(o.new_tokens)
-                    t.events.put(("tokens", list(o.new_tokens)))
+                    t.events.put(("tokens", list(o.new_tokens), getattr(o, "logprobs", None)))
                 if o.finished:
                     self.counters["requests_finished"] += 1
                     self.counters["prefix_hit_tokens"] += int(t.prefix_hit_tokens or 0)

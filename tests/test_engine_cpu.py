@@ -82,3 +82,33 @@ def test_parity_report_against_the_oracle(tmp_path):
     assert not failed and all(r["cosine"] > 0.9999 for r in rows if r["stage"] != "logits")
     m = parity.logit_metrics(torch.tensor([[0.0, 5.0, 1.0, 0.5, 0.2, 0.1]]), torch.tensor([[5.0, 0.0, 1.0, 0.5, 0.2, 0.1]]))
     assert m["top1"] == 0.0 and m["kl"] > 1.0 and abs(m["top5_overlap"] - 0.8) < 1e-9
+
+
+def test_logprobs_follow_the_models_distribution():
+    """The chosen token's log-probability and the k likeliest alternatives, per output token, against the oracle's
+    logits; a request without the option in the same batch is unaffected."""
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=256)
+    prompt = _prompt(40, seed=4)
+    with_lp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3)
+    plain = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    a, b = eng.add_request(prompt, with_lp), eng.add_request(prompt, plain)
+    steps = []
+    while eng.has_unfinished():
+        steps += eng.step()
+    ref_tokens, ref_logits = ReferenceModel(w).generate_greedy(torch.tensor(prompt), 6)
+    assert a.output == ref_tokens and b.output == ref_tokens
+    assert b.logprobs == [] and all(o.logprobs is None for o in steps if o.rid == b.rid)
+    assert sum(len(o.logprobs) for o in steps if o.rid == a.rid) == 6
+    ref_lp = torch.log_softmax(ref_logits.float(), -1)
+    for i, (tok, lp, top) in enumerate(a.logprobs):
+        assert tok == ref_tokens[i] and abs(lp - float(ref_lp[i, tok])) < 2e-2
+        assert len(top) == 3 and top[0][0] == tok                      # greedy: the emitted token leads the list
+        assert [t for t, _ in top] == ref_lp[i].topk(3).indices.tolist()
+        assert all(x[1] >= y[1] for x, y in zip(top, top[1:]))
+    # sampled requests report the probability of the token that was drawn, not of the likeliest one
+    sp = SamplingParams(temperature=1.5, top_k=0, top_p=1.0, seed=11, max_tokens=8, ignore_eos=True, logprobs=0)
+    r = eng.add_request(prompt, sp)
+    while eng.has_unfinished():
+        eng.step()
+    assert [t for t, _, _ in r.logprobs] == r.output and all(top == [] and lp <= 0.0 for _, lp, top in r.logprobs)

@@ -197,3 +197,16 @@ def test_long_prompt_prefill_with_tcgen05_attention_matches_the_mma_sync_path():
     assert _cos(outs[0][1], outs[1][1]) > 0.9995
     same = (outs[0][0].argmax(-1) == outs[1][0].argmax(-1)).float().mean().item()
     assert same > 0.97, same              # near-ties of a random model may flip between two bf16 attention kernels
+
+
+def test_logprobs_on_the_gpu_engine_are_self_consistent():
+    """Requests that ask for log-probabilities take the eager sampling path; the numbers describe the emitted tokens."""
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cuda", max_batch=2, max_context=256)
+    r = eng.add_request(_prompt(40, 4), SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3))
+    while eng.has_unfinished():
+        eng.step()
+    assert [t for t, _, _ in r.logprobs] == r.output and len(r.output) == 6
+    for tok, lp, top in r.logprobs:
+        assert lp <= 1e-6 and len(top) == 3 and abs(top[0][1] - lp) < 1e-5      # greedy: the likeliest token was emitted
+        assert top[0][1] >= top[1][1] >= top[2][1]

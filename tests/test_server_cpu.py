@@ -262,3 +262,22 @@ def test_n_choices_run_as_parallel_requests(server):
     assert st == 400 and json.loads(body)["error"]["param"] == "n"
     st, body, _ = _post(server, {"messages": msgs, "n": 0})
     assert st == 400
+
+
+def test_logprobs_in_chat_completions(server):
+    msgs = [{"role": "user", "content": "count to three"}]
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 5, "temperature": 0, "presence_penalty": 0,
+                                 "logprobs": True, "top_logprobs": 2})
+    j = json.loads(body)
+    assert st == 200
+    items = j["choices"][0]["logprobs"]["content"]
+    assert 1 <= len(items) <= 5
+    for it in items:
+        assert it["logprob"] <= 0.0 and bytes(it["bytes"]).decode("utf-8", errors="replace") == it["token"]
+        assert len(it["top_logprobs"]) == 2 and it["top_logprobs"][0]["logprob"] >= it["top_logprobs"][1]["logprob"]
+        assert it["top_logprobs"][0]["token"] == it["token"]           # greedy, no penalties: the likeliest token is emitted
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 5, "temperature": 0})
+    assert "logprobs" not in json.loads(body)["choices"][0]
+    for bad in ({"logprobs": 1}, {"top_logprobs": 2}, {"logprobs": True, "top_logprobs": 21}, {"logprobs": True, "stream": True}):
+        st, body, _ = _post(server, dict({"messages": msgs}, **bad))
+        assert st == 400 and json.loads(body)["error"]["param"] in ("logprobs", "top_logprobs")
