@@ -16,7 +16,8 @@ from __future__ import annotations
 import torch
 
 from .constants import BLOCK_GEOMETRY, GGMLType
-from .iq_tables import IQ3_S_GRID, IQ3_XXS_GRID, IQ4_NL_VALUES
+from .iq_tables import (IQ1_DELTA, IQ1_LEVELS, IQ1S_GRID_CODES, IQ2_LEVELS, IQ2S_GRID_CODES, IQ2XS_GRID_CODES, IQ2XXS_GRID_CODES,
+                        IQ3_S_GRID, IQ3_XXS_GRID, IQ4_NL_VALUES, unpack_codes)
 
 _TABLE_CACHE: dict[tuple[str, str], torch.Tensor] = {}
 
@@ -31,6 +32,9 @@ def _table(name: str, device: torch.device) -> torch.Tensor:
             src = IQ3_S_GRID if name == "iq3s" else IQ3_XXS_GRID
             packed = torch.tensor(src, dtype=torch.int64, device=device)
             t = torch.stack([(packed >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.float32)
+        elif name in ("iq2xxs", "iq2xs", "iq2s", "iq1s"):
+            src = {"iq2xxs": IQ2XXS_GRID_CODES, "iq2xs": IQ2XS_GRID_CODES, "iq2s": IQ2S_GRID_CODES, "iq1s": IQ1S_GRID_CODES}[name]
+            t = torch.tensor(unpack_codes(src, IQ1_LEVELS if name == "iq1s" else IQ2_LEVELS), dtype=torch.float32, device=device)
         else:
             raise KeyError(name)
         _TABLE_CACHE[key] = t
@@ -379,6 +383,103 @@ def dequant_iq3_xxs(b: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------------------
+# 2-bit and 1-bit codebook formats (eight elements per codebook entry)
+# ----------------------------------------------------------------------------------------
+
+def _u16(b: torch.Tensor) -> torch.Tensor:
+    """uint8 [n, 2m] -> little-endian 16-bit words as int64 [n, m]."""
+    w = b.to(torch.int64)
+    return w[:, 0::2] | (w[:, 1::2] << 8)
+
+
+def _signs_from_7bit(s7: torch.Tensor) -> torch.Tensor:
+    """7 stored sign bits -> +-1.0 for eight elements [..., 8]; the eighth bit makes the number of set bits even."""
+    par = s7 ^ (s7 >> 4)
+    par = par ^ (par >> 2)
+    par = (par ^ (par >> 1)) & 1
+    return _signs_from_byte(s7 | (par << 7))
+
+
+def _signs_from_byte(s8: torch.Tensor) -> torch.Tensor:
+    bitpos = torch.arange(8, device=s8.device, dtype=torch.int64)
+    return 1.0 - 2.0 * ((s8[..., None] >> bitpos) & 1).to(torch.float32)
+
+
+def dequant_iq2_xxs(b: torch.Tensor) -> torch.Tensor:
+    """66 bytes: fp16 d, then per 32 elements two 32-bit words: four 8-bit codebook indices; 4 x 7 sign bits + 4-bit scale."""
+    n = b.shape[0]
+    d = _f16_at(b, 0)
+    w = _u16(b[:, 2:66]).reshape(n, 8, 4)
+    idx = torch.stack([w[:, :, 0] & 0xFF, w[:, :, 0] >> 8, w[:, :, 1] & 0xFF, w[:, :, 1] >> 8], dim=-1)       # [n, 8, 4]
+    hi = w[:, :, 2] | (w[:, :, 3] << 16)
+    db = d * (0.5 + (hi >> 28).to(torch.float32)) * 0.25                                                       # [n, 8]
+    l = torch.arange(4, device=b.device, dtype=torch.int64)
+    sign = _signs_from_7bit((hi[:, :, None] >> (7 * l)) & 127)                                                 # [n, 8, 4, 8]
+    return (db[:, :, None, None] * _table("iq2xxs", b.device)[idx] * sign).reshape(n, 256)
+
+
+def dequant_iq2_xs(b: torch.Tensor) -> torch.Tensor:
+    """74 bytes: fp16 d, 32 words (9-bit codebook index + 7 sign bits, one per 8 elements), 8 bytes of two 4-bit scales
+    (low nibble: first 16 elements of the group of 32, high nibble: the other 16)."""
+    n = b.shape[0]
+    d = _f16_at(b, 0)
+    q = _u16(b[:, 2:66]).reshape(n, 8, 4)
+    sc = b[:, 66:74].to(torch.int64)
+    ls = torch.stack([sc & 0xF, sc & 0xF, sc >> 4, sc >> 4], dim=-1).to(torch.float32)                         # [n, 8, 4]
+    db = d[:, :, None] * (0.5 + ls) * 0.25
+    return (db[..., None] * _table("iq2xs", b.device)[q & 511] * _signs_from_7bit(q >> 9)).reshape(n, 256)
+
+
+def dequant_iq2_s(b: torch.Tensor) -> torch.Tensor:
+    """82 bytes: fp16 d, 32 index low bytes, 32 full sign bytes, 8 bytes of index bits 8-9 (two per 8 elements), 8 bytes
+    of two 4-bit scales."""
+    n = b.shape[0]
+    d = _f16_at(b, 0)
+    lo = b[:, 2:34].to(torch.int64).reshape(n, 8, 4)
+    sg = b[:, 34:66].to(torch.int64).reshape(n, 8, 4)
+    qh = b[:, 66:74].to(torch.int64)
+    sc = b[:, 74:82].to(torch.int64)
+    l = torch.arange(4, device=b.device, dtype=torch.int64)
+    idx = lo | (((qh[:, :, None] >> (2 * l)) & 3) << 8)
+    ls = torch.stack([sc & 0xF, sc & 0xF, sc >> 4, sc >> 4], dim=-1).to(torch.float32)
+    db = d[:, :, None] * (0.5 + ls) * 0.25
+    return (db[..., None] * _table("iq2s", b.device)[idx] * _signs_from_byte(sg)).reshape(n, 256)
+
+
+def dequant_iq1_s(b: torch.Tensor) -> torch.Tensor:
+    """50 bytes: fp16 d, 32 index low bytes, 8 words: 4 x 3 index high bits, a 3-bit scale (bits 12-14) and the sign of the
+    common offset (bit 15).  Elements are d * (2 s + 1) * (codebook value +- 1/8)."""
+    n = b.shape[0]
+    d = _f16_at(b, 0)
+    lo = b[:, 2:34].to(torch.int64).reshape(n, 8, 4)
+    qh = _u16(b[:, 34:50])                                                                                      # [n, 8]
+    l = torch.arange(4, device=b.device, dtype=torch.int64)
+    idx = lo | (((qh[:, :, None] >> (3 * l)) & 7) << 8)
+    dl = d * (2.0 * ((qh >> 12) & 7).to(torch.float32) + 1.0)
+    delta = torch.where((qh & 0x8000) != 0, -IQ1_DELTA, IQ1_DELTA)
+    return (dl[:, :, None, None] * (_table("iq1s", b.device)[idx] + delta[:, :, None, None])).reshape(n, 256)
+
+
+def dequant_iq1_m(b: torch.Tensor) -> torch.Tensor:
+    """56 bytes, no separate d: 32 index low bytes; 16 bytes with, per nibble, 3 index high bits and an offset sign (one
+    nibble per 8 elements); 4 scale words whose top nibbles spell the fp16 super-block scale and whose low 12 bits hold
+    four 3-bit scales (one per 16 elements)."""
+    n = b.shape[0]
+    lo = b[:, 0:32].to(torch.int64).reshape(n, 16, 2)
+    qh = b[:, 32:48].to(torch.int64)                                                                            # [n, 16]
+    sc = _u16(b[:, 48:56])                                                                                      # [n, 4]
+    dbits = (sc[:, 0] >> 12) | ((sc[:, 1] >> 8) & 0x00F0) | ((sc[:, 2] >> 4) & 0x0F00) | (sc[:, 3] & 0xF000)
+    d = ((dbits ^ 0x8000) - 0x8000).to(torch.int16).view(torch.float16).to(torch.float32)[:, None]      # 16 bits -> fp16
+    nib = torch.stack([qh & 0xF, qh >> 4], dim=-1)                                                              # [n, 16, 2]
+    idx = lo | ((nib & 7) << 8)
+    delta = torch.where((nib & 8) != 0, -IQ1_DELTA, IQ1_DELTA)
+    sh = torch.arange(4, device=b.device, dtype=torch.int64) * 3
+    s3 = ((sc[:, :, None] >> sh) & 7).reshape(n, 16)                                                            # one per 16 elements
+    dl = d * (2.0 * s3.to(torch.float32) + 1.0)
+    return (dl[:, :, None, None] * (_table("iq1s", b.device)[idx] + delta[..., None])).reshape(n, 256)
+
+
+# ----------------------------------------------------------------------------------------
 # registry + tensor-level helpers
 # ----------------------------------------------------------------------------------------
 
@@ -388,6 +489,8 @@ _DEQUANT = {
     GGMLType.Q4_K: dequant_q4_k, GGMLType.Q5_K: dequant_q5_k, GGMLType.Q6_K: dequant_q6_k,
     GGMLType.Q2_K: dequant_q2_k, GGMLType.Q3_K: dequant_q3_k, GGMLType.IQ4_XS: dequant_iq4_xs,
     GGMLType.IQ3_S: dequant_iq3_s, GGMLType.IQ3_XXS: dequant_iq3_xxs,
+    GGMLType.IQ2_XXS: dequant_iq2_xxs, GGMLType.IQ2_XS: dequant_iq2_xs, GGMLType.IQ2_S: dequant_iq2_s,
+    GGMLType.IQ1_S: dequant_iq1_s, GGMLType.IQ1_M: dequant_iq1_m,
 }
 _QUANT = {
     GGMLType.Q8_0: quant_q8_0, GGMLType.Q4_0: quant_q4_0, GGMLType.Q4_K: quant_q4_k,

@@ -11,10 +11,11 @@ from llaminar_b200.gguf.constants import BLOCK_GEOMETRY
 from llaminar_b200.gguf.reader import GGUFError
 
 QUANT_TYPES = ["Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "IQ3_S"]
-DEQUANT_ONLY = ["Q4_1", "Q5_0", "Q5_1", "IQ4_NL", "Q2_K", "Q3_K", "IQ4_XS", "IQ3_XXS"]
+DEQUANT_ONLY = ["Q4_1", "Q5_0", "Q5_1", "IQ4_NL", "Q2_K", "Q3_K", "IQ4_XS", "IQ3_XXS", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ1_S", "IQ1_M"]
 EXPECTED_BLOCKS = {"Q8_0": (32, 34), "Q4_0": (32, 18), "Q4_1": (32, 20), "Q5_0": (32, 22), "Q5_1": (32, 24), "IQ4_NL": (32, 18),
                    "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210), "Q3_K": (256, 110), "Q2_K": (256, 84),
-                   "IQ4_XS": (256, 136), "IQ3_S": (256, 110), "IQ3_XXS": (256, 98)}
+                   "IQ4_XS": (256, 136), "IQ3_S": (256, 110), "IQ3_XXS": (256, 98), "IQ2_XXS": (256, 66), "IQ2_XS": (256, 74),
+                   "IQ2_S": (256, 82), "IQ1_S": (256, 50), "IQ1_M": (256, 56)}
 
 
 def test_block_geometry_matches_ggml():
@@ -104,3 +105,46 @@ def test_model_checkpoint_round_trip(tmp_path):
         assert r[name].qtype == w[name].qtype and torch.equal(r[name].raw.cpu(), w[name].raw.cpu())
     assert "tokenizer.ggml.tokens" in r.metadata
 
+
+
+def test_checkpoint_with_two_bit_and_one_bit_tensors_loads_and_runs(tmp_path):
+    """A file whose projections use the 2-bit / 1-bit codebook formats (no quantiser here: random valid blocks) goes
+    through the loader and the engine; the tokens are those of the fp32 oracle on the same decoded weights."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.reference import ReferenceModel
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.models.weights import ModelWeights, QTensor
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=1)
+    rng = np.random.default_rng(5)
+    swaps = {"blk.0.ffn_gate.weight": "IQ2_XXS", "blk.0.ffn_up.weight": "IQ2_XS", "blk.0.ffn_down.weight": "IQ2_S",
+             "blk.1.ffn_gate.weight": "IQ1_S", "blk.1.ffn_up.weight": "IQ1_M"}
+    for name, fmt in swaps.items():
+        qt = GGMLType[fmt]
+        n, k = w[name].shape
+        assert k % 256 == 0
+        e, b = BLOCK_GEOMETRY[qt]
+        raw = rng.integers(0, 256, size=(n * k // e, b), dtype=np.uint8)
+        raw16 = raw.view(np.uint16) if b % 2 == 0 else None
+        # small finite super-block scales: overwrite the fp16 field (IQ1_M spreads it over the scale words' top nibbles)
+        d = np.float16(0.002).view(np.uint16)
+        if fmt == "IQ1_M":
+            sc = raw[:, 48:56].copy().view(np.uint16)
+            for i in range(4):
+                sc[:, i] = (sc[:, i] & 0x0FFF) | (((d >> (4 * i)) & 0xF) << 12)
+            raw[:, 48:56] = sc.view(np.uint8)
+        else:
+            raw[:, 0:2] = np.array([d], dtype=np.uint16).view(np.uint8)
+        w.tensors[name] = QTensor(qt, (n, k), torch.from_numpy(raw.reshape(-1).copy()))
+    path = str(tmp_path / "lowbit.gguf")
+    w.save_gguf(path)
+    r = ModelWeights.from_gguf(path)
+    for name, fmt in swaps.items():
+        assert r[name].qtype == GGMLType[fmt]
+        t = r[name].to_float()
+        assert torch.isfinite(t).all() and 0 < t.abs().max() < 1.0
+    eng = LLMEngine.from_gguf(path, device="cpu", max_batch=1, max_context=128)
+    prompt = list(range(3, 35))
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0]
+    assert out == ReferenceModel(r).generate_greedy(torch.tensor(prompt), 8)[0]
