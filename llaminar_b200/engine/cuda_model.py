@@ -24,6 +24,23 @@ from ..ops.layout import PackedWeight, can_pack, interleave_gate_up, pack_expert
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
 
+def expert_tensors_for_packing(w: ModelWeights, prefix: str) -> tuple[QTensor, QTensor, QTensor]:
+    """Gate, up and down expert stacks of a layer in formats the grouped expert kernels can read.  The grouped kernels
+    have no dense path, so a stack whose format has no packed device layout (the 1- to 3-bit codebook formats, Q2_K, Q3_K,
+    ...) is re-encoded as Q8_0 once; gate and up must share a format because their rows are interleaved."""
+    ge, ue, de = (w[prefix + n] for n in ("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"))
+    _, ff, d = ge.shape
+    if not (can_pack(ge.qtype, d) and ge.qtype == ue.qtype):
+        for name, key in (("gate", "ffn_gate_exps.weight"), ("up", "ffn_up_exps.weight")):
+            t = w[prefix + key]
+            if t.qtype != GGMLType.Q8_0:
+                w.tensors[prefix + key] = t.transcoded(GGMLType.Q8_0)      # cached: expert-parallel slabs share the result
+        ge, ue = w[prefix + "ffn_gate_exps.weight"], w[prefix + "ffn_up_exps.weight"]
+    if not can_pack(de.qtype, ff):
+        w.tensors[prefix + "ffn_down_exps.weight"] = de = de.transcoded(GGMLType.Q8_0)
+    return ge, ue, de
+
+
 @dataclass
 class ForwardBatch:
     """Device-side description of one forward call (all int32 tensors on the model's device)."""
@@ -219,7 +236,7 @@ class CudaModel:
 
     def _pack_expert_slab(self, w: ModelWeights, p: str, e0: int, e1: int):
         dev = self.device
-        ge, ue, de = w[p + "ffn_gate_exps.weight"], w[p + "ffn_up_exps.weight"], w[p + "ffn_down_exps.weight"]
+        ge, ue, de = expert_tensors_for_packing(w, p)
         E, ff, d = ge.shape
         slab = CudaLayer()
         gu_parts = []

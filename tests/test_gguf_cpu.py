@@ -148,3 +148,31 @@ def test_checkpoint_with_two_bit_and_one_bit_tensors_loads_and_runs(tmp_path):
     prompt = list(range(3, 35))
     out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0]
     assert out == ReferenceModel(r).generate_greedy(torch.tensor(prompt), 8)[0]
+
+
+def test_expert_stacks_without_a_packed_layout_are_reencoded_for_the_grouped_kernels():
+    from llaminar_b200.engine.cuda_model import expert_tensors_for_packing
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.models.weights import QTensor
+    from llaminar_b200.ops.layout import can_pack
+    w = synthesize(SHAPES["tiny-qwen3moe"], "Q4_K_M", seed=2)
+    p = "blk.0."
+    before = [w[p + n] for n in ("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight")]
+    if before[0].qtype == before[1].qtype:
+        got = expert_tensors_for_packing(w, p)
+        assert all(a is b for a, b in zip(got, before))                  # packable formats pass through untouched
+    # a 2-bit gate stack: gate and up move to Q8_0 together, down stays as it is
+    E, ff, d = before[0].shape
+    rng = np.random.default_rng(7)
+    raw = rng.integers(0, 256, size=(E * ff * d // 256, 74), dtype=np.uint8)
+    raw[:, 0:2] = np.array([np.float16(0.003)], dtype=np.float16).view(np.uint8)
+    low = QTensor(GGMLType.IQ2_XS, (E, ff, d), torch.from_numpy(raw.reshape(-1).copy()))
+    w.tensors[p + "ffn_gate_exps.weight"] = low
+    ge, ue, de = expert_tensors_for_packing(w, p)
+    assert ge.qtype == ue.qtype == GGMLType.Q8_0 and can_pack(ge.qtype, d) and de is before[2]
+    assert w[p + "ffn_gate_exps.weight"] is ge                            # cached for the other expert-parallel slabs
+    a, b = low.to_float(), ge.to_float()
+    assert a.shape == b.shape and ((a - b).norm() / a.norm()).item() < 0.01
+    u0, u1 = before[1].to_float(), ue.to_float()
+    assert ((u0 - u1).norm() / u0.norm()).item() < 0.01
