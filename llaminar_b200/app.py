@@ -445,6 +445,10 @@ def cmd_plan(cfg: OrchestrationConfig) -> int:
 
 
 def cmd_describe(cfg: OrchestrationConfig) -> int:
+    if cfg.values.get("env"):
+        from .utils.env import debug_env
+        print(debug_env().describe())
+        return 0
     from .utils.devices import describe_devices
     print(json.dumps(describe_devices(), indent=2))
     return 0

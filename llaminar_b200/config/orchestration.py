@@ -73,6 +73,7 @@ OPTIONS: list[OptionSpec] = [
     _o("--list-devices", action="store_true", category="devices"),
     _o("--dry-run", action="store_true", help="plan and validate, then exit", category="devices"),
     _o("--explain-placement", action="store_true", category="devices"),
+    _o("--env", action="store_true", category="debug", help="describe: list the LLAMINAR_* environment switches instead of the devices"),
     _o("--validate-only", action="store_true", category="devices"),
     _o("--suggest-layout", type=int, default=None, category="devices",
        help="plan: find the smallest pp x tp placement on up to N GPUs that fits their memory and print its flags"),

@@ -216,3 +216,10 @@ def test_cli_moe_stats_and_expert_placement(tmp_path):
     assert rc != 0 and "mixture-of-experts" in (out + err)
     rc, out, err = _cli(*base, "--moe-rebalance")
     assert rc != 0 and "--moe-expert-placement" in (out + err)
+
+
+def test_describe_env_lists_the_switch_registry(capsys):
+    from llaminar_b200.app import main
+    assert main(["describe", "--env"]) == 0
+    out = capsys.readouterr().out
+    assert "LLAMINAR_TP_FUSED" in out and "LLAMINAR_ATTN_TC" in out
