@@ -281,3 +281,41 @@ def test_logprobs_in_chat_completions(server):
     for bad in ({"logprobs": 1}, {"top_logprobs": 2}, {"logprobs": True, "top_logprobs": 21}, {"logprobs": True, "stream": True}):
         st, body, _ = _post(server, dict({"messages": msgs}, **bad))
         assert st == 400 and json.loads(body)["error"]["param"] in ("logprobs", "top_logprobs")
+
+
+def test_no_kv_page_leak_across_request_kinds(server):
+    """Every way a request can end (length, stop sequence with cancellation, several choices, a client that goes away in
+    mid-stream, a rejected request) gives its KV pages back: the free-page gauge returns to its idle value."""
+    import time
+
+    def free_pages():
+        c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+        c.request("GET", "/metrics")
+        text = c.getresponse().read().decode()
+        vals = {ln.split()[0]: float(ln.split()[1]) for ln in text.splitlines() if ln and not ln.startswith("#")}
+        return vals["llaminar_kv_pages_free"], vals["llaminar_requests_running"]
+
+    def idle_free():
+        for _ in range(100):
+            free, running = free_pages()
+            if running == 0:
+                return free
+            time.sleep(0.05)
+        raise AssertionError("requests still running")
+
+    base = idle_free()
+    msgs = [{"role": "user", "content": "tell me a story about pages"}]
+    _post(server, {"messages": msgs, "max_tokens": 40, "temperature": 0})
+    _post(server, {"messages": msgs, "max_tokens": 40, "temperature": 1.0, "seed": 1, "n": 3})
+    first = json.loads(_post(server, {"messages": msgs, "max_tokens": 12, "temperature": 0})[1])["choices"][0]["message"]["content"]
+    if len(first) > 4:
+        _post(server, {"messages": msgs, "max_tokens": 40, "temperature": 0, "stop": [first[2:4]]})
+    # a streaming client that disconnects after the first chunk
+    c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+    c.request("POST", "/v1/chat/completions", body=json.dumps({"messages": msgs, "max_tokens": 200, "stream": True}).encode(),
+              headers={"Content-Type": "application/json"})
+    r = c.getresponse()
+    r.read(20)
+    c.close()
+    _post(server, {"messages": [{"role": "user", "content": "x " * 2000}], "max_tokens": 4})       # context overflow: 400
+    assert idle_free() == base
