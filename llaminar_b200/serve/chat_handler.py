@@ -153,8 +153,6 @@ def parse_request(body_bytes: bytes) -> ChatRequest:
             raise RequestError("`top_logprobs` must be an integer between 0 and 20", param="top_logprobs")
         if not lp:
             raise RequestError("`top_logprobs` needs `logprobs` to be true", param="top_logprobs")
-    if lp and req.stream:
-        raise RequestError("`logprobs` is not supported together with `stream`", param="logprobs")
     req.logprobs, req.top_logprobs = lp, int(top or 0)
     for m in msgs:
         cm = {"role": str(m["role"]), "content": "" if m.get("content") is None else m.get("content")}
@@ -198,7 +196,9 @@ class ChatCompletionHandler:
         return ids, sp, starts_in_think
 
     def _generate(self, req: ChatRequest) -> Iterator[tuple[str, object]]:
-        """Yields ("delta", (reasoning, content)) ... then ("end", info dict)."""
+        """Yields ("delta", (reasoning, content)) ... then ("end", info dict).  When the request asks for log-probabilities
+        the first event is ("logprobs", list): the live list that receives one entry per generated token (a streaming
+        consumer sends the entries added since its previous chunk); ``info["logprobs"]`` is the same list."""
         ids, sp, starts_in_think = self._setup(req)
         ticket = self.loop.submit(ids, sp)
         dec = StreamDecoder(self.tok, skip_special=True)
@@ -211,6 +211,8 @@ class ChatCompletionHandler:
         finish = "stop"
         stopper = StopMatcher(req.stop)
         token_logprobs: list = []
+        if req.logprobs:
+            yield "logprobs", token_logprobs              # the live list: a streaming consumer reads new entries from it
         if budget_on and req.thinking_budget_tokens == 0 and stop_ids:
             for t in stop_ids:
                 self.loop.force_token(ticket, t)
@@ -331,7 +333,7 @@ class ChatCompletionHandler:
             if kind == "delta":
                 reasoning.append(payload[0])
                 content.append(payload[1])
-            else:
+            elif kind == "end":
                 info = payload
         text, think = "".join(content), "".join(reasoning)
         finish = "length" if info["finish_reason"] == "length" else "stop"
@@ -421,16 +423,27 @@ class ChatCompletionHandler:
         created = int(time.time())
         model = req.model or self.model_name
 
+        live_lp: list | None = None
+        sent_lp = 0
+
         def chunk(delta: dict, finish=None, usage=None) -> bytes:
+            nonlocal sent_lp
+            choice = {"index": 0, "delta": delta, "finish_reason": finish}
+            if live_lp is not None and ("content" in delta or "reasoning_content" in delta) and "role" not in delta:
+                # the entries of the tokens generated since the previous chunk travel with this one
+                choice["logprobs"] = self._logprobs_object(live_lp[sent_lp:])
+                sent_lp = len(live_lp)
             obj = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
-                   "system_fingerprint": SYSTEM_FINGERPRINT,
-                   "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                   "system_fingerprint": SYSTEM_FINGERPRINT, "choices": [choice]}
             if usage is not None:
                 obj["usage"] = usage
             return b"data: " + json.dumps(obj, ensure_ascii=False).encode() + b"\n\n"
 
         gen = self._generate(req)          # raises RequestError before the first byte if setup fails
         first = next(gen)
+        if first[0] == "logprobs":
+            live_lp = first[1]
+            first = next(gen)
         yield chunk({"role": "assistant", "content": ""})
         content_all = []
         info = None
@@ -446,6 +459,8 @@ class ChatCompletionHandler:
             else:
                 info = payload
         finish = "length" if info["finish_reason"] == "length" else "stop"
+        if live_lp is not None and sent_lp < len(live_lp) and not req.tools:
+            yield chunk({"content": ""})               # tokens that produced no text of their own
         if req.tools:
             parsed = parse_tool_calls("".join(content_all))
             if parsed.has_tool_calls:

@@ -278,7 +278,17 @@ def test_logprobs_in_chat_completions(server):
         assert it["top_logprobs"][0]["token"] == it["token"]           # greedy, no penalties: the likeliest token is emitted
     st, body, _ = _post(server, {"messages": msgs, "max_tokens": 5, "temperature": 0})
     assert "logprobs" not in json.loads(body)["choices"][0]
-    for bad in ({"logprobs": 1}, {"top_logprobs": 2}, {"logprobs": True, "top_logprobs": 21}, {"logprobs": True, "stream": True}):
+    # streamed: the entries arrive with the chunks and add up to the same list
+    st, body, _ = _post(server, {"messages": msgs, "max_tokens": 5, "temperature": 0, "presence_penalty": 0,
+                                 "logprobs": True, "top_logprobs": 2, "stream": True})
+    assert st == 200
+    streamed = []
+    for ln in body.decode().splitlines():
+        if ln.startswith("data: {"):
+            ch = json.loads(ln[6:])["choices"][0]
+            streamed += (ch.get("logprobs") or {}).get("content", [])
+    assert streamed == items
+    for bad in ({"logprobs": 1}, {"top_logprobs": 2}, {"logprobs": True, "top_logprobs": 21}):
         st, body, _ = _post(server, dict({"messages": msgs}, **bad))
         assert st == 400 and json.loads(body)["error"]["param"] in ("logprobs", "top_logprobs")
 
