@@ -44,14 +44,15 @@ class Request:
     step_count: int = 0
     terminal: object = None                               # prefix-cache terminal state: the forward pass is skipped
     logprobs: list = field(default_factory=list)          # one (token, logprob, [(token, logprob), ...]) per output token
+    n_folded: int = 0                                     # leading output tokens that a preemption appended to `prompt`
 
     @property
     def all_tokens(self) -> list[int]:
-        return self.prompt + self.output
+        return self.prompt + self.output[self.n_folded:]
 
     @property
     def n_tokens(self) -> int:
-        return len(self.prompt) + len(self.output)
+        return len(self.prompt) + len(self.output) - self.n_folded
 
 
 @dataclass
@@ -114,7 +115,7 @@ class LLMEngine:
         if mtp is not None:
             mtp.attach(self)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
-                      "prefix_hit_tokens": 0, "graph_replays": 0}
+                      "prefix_hit_tokens": 0, "graph_replays": 0, "preemptions": 0}
         self._vocab = c.vocab_size
         if self.is_cuda:
             self._init_static_buffers()
@@ -272,6 +273,12 @@ class LLMEngine:
         return []
 
     def _admit(self, r: Request) -> None:
+        if r.n_folded and self.running:
+            # a preempted sequence comes back only when it fits with room to grow beside the running ones: re-admitting
+            # it into a full cache would recompute its whole prefix just to be preempted again
+            need = (r.n_tokens + PAGE_SIZE) // PAGE_SIZE + len(self.running) + 1
+            if self.kv.allocator.n_free < need:
+                raise OutOfPages("waiting for pages after a preemption")
         hit_pages, hit_tokens = [], 0
         if self.prefix_cache is not None:
             term = self.prefix_cache.lookup_terminal(r.prompt)
@@ -522,8 +529,7 @@ class LLMEngine:
     # -- decode ----------------------------------------------------------------------------------------
     def _decode(self, reqs: list[Request]) -> list[StepOutput]:
         t0 = time.perf_counter()
-        for r in reqs:
-            self._ensure_pages(r, r.n_tokens)
+        reqs = self._reserve_decode_pages(reqs)
         eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced or r.params.wants_logprobs for r in reqs)
         if self.is_cuda:
             toks = self._decode_cuda(reqs, eager)
@@ -537,6 +543,35 @@ class LLMEngine:
         self.stats["decode_tokens"] += len(reqs)
         self.stats["decode_s"] += time.perf_counter() - t0
         return outs
+
+    def _reserve_decode_pages(self, reqs: list[Request]) -> list[Request]:
+        """Gives every running sequence the page its next token needs.  When the cache is exhausted (and the prefix cache
+        has nothing left to evict) the most recently admitted sequences are preempted until the others fit; a single
+        sequence that does not fit, or an engine with speculative state per sequence, raises as before."""
+        live = list(reqs)
+        i = 0
+        while i < len(live):
+            try:
+                self._ensure_pages(live[i], live[i].n_tokens)
+                i += 1
+            except OutOfPages:
+                if len(live) == 1 or self.mtp is not None:
+                    raise
+                self._preempt(live.pop())
+        return live
+
+    def _preempt(self, r: Request) -> None:
+        """Recompute preemption: the sequence gives its pages back and returns to the head of the waiting queue with
+        its generated tokens appended to the prompt; the next prefill rebuilds the cache and samples the next token
+        with the same step index a decode step would have used, so the output continues where it stopped."""
+        self.running.remove(r)
+        self.kv.free_sequence(r.kv)
+        r.kv = SequenceKV()
+        r.prompt = r.prompt + r.output[r.n_folded:]
+        r.n_folded = len(r.output)
+        r.state, r.hidden, r.terminal, r.prefix_hit_tokens = "waiting", None, None, 0
+        self.waiting.insert(0, r)
+        self.stats["preemptions"] += 1
 
     def _decode_batch_tensors(self, reqs: list[Request]):
         dev = self.device

@@ -59,6 +59,7 @@ class EngineLoop:
         m["engine_errors"] = self.errors
         m["requests_running"] = len(self._tickets)
         m["requests_waiting"] = len(getattr(self.engine, "waiting", ()))
+        m["preemptions"] = int(getattr(self.engine, "stats", {}).get("preemptions", 0))
         alloc = getattr(getattr(self.engine, "kv", None), "allocator", None)
         if alloc is not None:
             m["kv_pages_free"] = int(alloc.n_free)

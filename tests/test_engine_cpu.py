@@ -112,3 +112,32 @@ def test_logprobs_follow_the_models_distribution():
     while eng.has_unfinished():
         eng.step()
     assert [t for t, _, _ in r.logprobs] == r.output and all(top == [] and lp <= 0.0 for _, lp, top in r.logprobs)
+
+
+def test_preemption_when_the_kv_cache_runs_out_continues_the_same_output():
+    """Three long generations in a cache that holds about half of them: the youngest sequences are preempted (pages freed,
+    tokens folded into the prompt, prefix recomputed later) instead of failing the step; greedy outputs equal those of an
+    engine with room for everything, logprobs stay aligned, and every page comes back."""
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    prompts = [_prompt(60, seed=s) for s in (1, 2, 3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=150, ignore_eos=True, logprobs=0)
+    big = LLMEngine(w, device="cpu", max_batch=3, max_context=256)
+    want = big.generate(prompts, sp)
+    assert big.stats["preemptions"] == 0
+    small = LLMEngine(w, device="cpu", max_batch=3, max_context=256, kv_pages=8)       # 7 usable pages of 64 tokens
+    reqs = [small.add_request(p, sp) for p in prompts]
+    while small.has_unfinished():
+        small.step()
+    assert small.stats["preemptions"] >= 1
+    for r, ref in zip(reqs, want):
+        assert r.output == ref and [t for t, _, _ in r.logprobs] == r.output and r.n_tokens == 60 + 150
+    assert small.kv.allocator.n_free == small.kv.n_pages - 1
+    # a single sequence that cannot fit still fails with the allocator's error
+    tiny = LLMEngine(w, device="cpu", max_batch=1, max_context=256, kv_pages=3)
+    tiny.add_request(prompts[0], sp)
+    try:
+        while tiny.has_unfinished():
+            tiny.step()
+        raise AssertionError("expected the cache to run out")
+    except RuntimeError as exc:
+        assert "exhausted" in str(exc)

@@ -147,3 +147,22 @@ def test_depth_controller_demotes_and_promotes():
         fixed.observe(0, 2)
         fixed.end_step()
     assert fixed.depth == 2
+
+
+def test_preemption_with_a_prefix_cache_keeps_outputs_and_page_accounting():
+    """Cache exhaustion with the prefix cache on: cached pages are evicted first, then sequences are preempted; the
+    outputs equal those of a roomy engine and no page is lost (free + held by the cache == all pages)."""
+    from llaminar_b200.engine.sampling import SamplingParams
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    g = torch.Generator().manual_seed(5)
+    shared = torch.randint(0, 1024, (64,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1024, (10 + i,), generator=g).tolist() for i in range(3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=140, ignore_eos=True)
+    want = LLMEngine(w, device="cpu", max_batch=3, max_context=256).generate(prompts, sp)
+    pc = PrefixCache(PrefixCacheConfig(terminal_state="off"), "fp")
+    eng = LLMEngine(w, device="cpu", max_batch=3, max_context=256, kv_pages=9, prefix_cache=pc)
+    got = eng.generate(prompts, sp)
+    assert got == want and eng.stats["preemptions"] >= 1
+    held = len(pc.device)
+    assert eng.kv.allocator.n_free + held == eng.kv.n_pages - 1
+    assert all(r <= 1 for r in eng.kv.allocator.refs)
