@@ -544,18 +544,18 @@ class LLMEngine:
         self.stats["decode_s"] += time.perf_counter() - t0
         return outs
 
-    def _reserve_decode_pages(self, reqs: list[Request]) -> list[Request]:
-        """Gives every running sequence the page its next token needs.  When the cache is exhausted (and the prefix cache
-        has nothing left to evict) the most recently admitted sequences are preempted until the others fit; a single
-        sequence that does not fit, or an engine with speculative state per sequence, raises as before."""
+    def _reserve_decode_pages(self, reqs: list[Request], extra: int = 0) -> list[Request]:
+        """Gives every running sequence the pages its next token (plus ``extra`` speculative rows) needs.  When the cache
+        is exhausted (and the prefix cache has nothing left to evict) the most recently admitted sequences are preempted
+        until the others fit; a single sequence that does not fit raises the allocator's error."""
         live = list(reqs)
         i = 0
         while i < len(live):
             try:
-                self._ensure_pages(live[i], live[i].n_tokens)
+                self._ensure_pages(live[i], live[i].n_tokens + extra)
                 i += 1
             except OutOfPages:
-                if len(live) == 1 or self.mtp is not None:
+                if len(live) == 1:
                     raise
                 self._preempt(live.pop())
         return live
@@ -566,7 +566,10 @@ class LLMEngine:
         with the same step index a decode step would have used, so the output continues where it stopped."""
         self.running.remove(r)
         self.kv.free_sequence(r.kv)
+        if self.mtp is not None:
+            self.mtp.release(r)
         r.kv = SequenceKV()
+        r.draft = []
         r.prompt = r.prompt + r.output[r.n_folded:]
         r.n_folded = len(r.output)
         r.state, r.hidden, r.terminal, r.prefix_hit_tokens = "waiting", None, None, 0

@@ -150,10 +150,10 @@ class MTPDecoder:
         k = 0 if special else self.ctl.depth
         k = min(k, min(engine.max_context - r.n_tokens - 2 for r in reqs))
         k = max(k, 0)
+        reqs = engine._reserve_decode_pages(reqs, extra=k + 1)     # may preempt the youngest sequences
         B = len(reqs)
         n0 = [r.n_tokens for r in reqs]
         for r in reqs:
-            engine._ensure_pages(r, r.n_tokens + k + 1)
             if r.rid not in self.seq:                      # admitted through a terminal-state hit: only the last row is known
                 self.seq[r.rid] = _SeqState([(r.n_tokens - 2, r.output[-1], r.hidden)])
         P = max(len(r.kv.pages) for r in reqs)

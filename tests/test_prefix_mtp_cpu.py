@@ -166,3 +166,15 @@ def test_preemption_with_a_prefix_cache_keeps_outputs_and_page_accounting():
     held = len(pc.device)
     assert eng.kv.allocator.n_free + held == eng.kv.n_pages - 1
     assert all(r <= 1 for r in eng.kv.allocator.refs)
+
+
+def test_preemption_under_speculative_decoding_stays_lossless(weights):
+    """Speculation reserves pages for its draft rows; when they run out the youngest sequence is preempted, its
+    speculative state dropped and rebuilt by the re-prefill: greedy outputs still equal plain decoding."""
+    sp = SamplingParams(max_tokens=120, temperature=0.0, ignore_eos=True)
+    prompts = _prompts()[:2] + [_prompts()[0][:40]]
+    ref = LLMEngine(weights, device="cpu", max_batch=3, max_context=512).generate(prompts, sp)
+    eng = LLMEngine(weights, device="cpu", max_batch=3, max_context=512, kv_pages=8, mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
+    got = eng.generate(prompts, sp)
+    assert eng.stats["preemptions"] >= 1 and got == ref
+    assert eng.kv.allocator.n_free == eng.kv.n_pages - 1 and not eng.mtp.seq
