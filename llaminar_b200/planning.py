@@ -15,7 +15,12 @@ from .parallel.tp_plan import TPPlan
 B200_HBM_BYTES = 180 * 10 ** 9
 
 
-def _bytes(qt: GGMLType, n: int) -> float:
+def _bytes(qt: GGMLType, n: int, expert: bool = False) -> float:
+    """Device-resident bytes of ``n`` weights stored as ``qt`` in the file: formats with a packed device layout stay as
+    they are; the others are decoded to bf16 at load (expert stacks: re-encoded as Q8_0), which is what has to fit."""
+    from .ops.layout import FMT_IDS
+    if qt not in FMT_IDS and qt not in (GGMLType.F32, GGMLType.F16, GGMLType.BF16):
+        return n * (34 / 32 if expert else 2.0)
     e, b = BLOCK_GEOMETRY[qt]
     return n / e * b
 
@@ -68,7 +73,7 @@ def layer_weight_bytes(cfg: ModelConfig, recipe: QuantRecipe, layer: int, tp: TP
     tot += _bytes(t("attn_output"), d * tp.n_heads_local * D)
     if cfg.is_moe:
         n_e = tp.expert_stop - tp.expert_start
-        tot += n_e * (2 * _bytes(t("ffn_gate_exps"), cfg.expert_ff * d) + _bytes(t("ffn_down_exps"), cfg.expert_ff * d))
+        tot += n_e * (2 * _bytes(t("ffn_gate_exps"), cfg.expert_ff * d, True) + _bytes(t("ffn_down_exps"), cfg.expert_ff * d, True))
         tot += 2 * cfg.n_experts * d
     else:
         ff = tp.ff_stop - tp.ff_start
