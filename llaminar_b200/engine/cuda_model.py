@@ -24,6 +24,20 @@ from ..ops.layout import PackedWeight, can_pack, interleave_gate_up, pack_expert
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
 
+_FLOAT_TYPES = (GGMLType.F32, GGMLType.F16, GGMLType.BF16)
+
+
+def for_kernels(t: QTensor) -> QTensor:
+    """A weight matrix in a format the quantised GEMV / GEMM kernels can read.  Block formats without a packed device
+    layout (Q2_K, Q3_K, Q4_1, Q5_0/1, IQ4_*, IQ3_XXS, IQ2_*, IQ1_*) are re-encoded as Q8_0 once at load: half the bytes
+    of a bf16 copy and the same kernels as every other layer.  Unquantised tensors, and matrices whose K is not a whole
+    number of 256-column chunks, are left alone and run as dense bf16."""
+    k = t.shape[-1]
+    if can_pack(t.qtype, k) or t.qtype in _FLOAT_TYPES or not can_pack(GGMLType.Q8_0, k):
+        return t
+    return t.transcoded(GGMLType.Q8_0)
+
+
 def expert_tensors_for_packing(w: ModelWeights, prefix: str) -> tuple[QTensor, QTensor, QTensor]:
     """Gate, up and down expert stacks of a layer in formats the grouped expert kernels can read.  The grouped kernels
     have no dense path, so a stack whose format has no packed device layout (the 1- to 3-bit codebook formats, Q2_K, Q3_K,
@@ -77,6 +91,7 @@ class QLinear:
         """Row-concatenate matrices; consecutive matrices of one format share a launch."""
         parts, col = [], 0
         i = 0
+        qts = [for_kernels(q) for q in qts]
         k = qts[0].shape[1]
         while i < len(qts):
             j = i
@@ -183,6 +198,7 @@ class CudaModel:
 
     # ---------------------------------------------------------------------------------------
     def _pack_or_dense(self, t: QTensor):
+        t = for_kernels(t)
         n, k = t.shape
         if can_pack(t.qtype, k):
             return pack_matrix(t.raw.to(self.device), t.qtype, n, k)
@@ -224,6 +240,7 @@ class CudaModel:
 
     def _pack_gate_up(self, g: QTensor, u: QTensor) -> QLinear:
         dev = self.device
+        g, u = for_kernels(g), for_kernels(u)
         n, k = g.shape
         if g.qtype == u.qtype and can_pack(g.qtype, k) and n % 16 == 0:
             raw, qt, n2, _ = interleave_gate_up(g.raw.to(dev), u.raw.to(dev), g.qtype, n, k)

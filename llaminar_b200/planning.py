@@ -17,10 +17,12 @@ B200_HBM_BYTES = 180 * 10 ** 9
 
 def _bytes(qt: GGMLType, n: int, expert: bool = False) -> float:
     """Device-resident bytes of ``n`` weights stored as ``qt`` in the file: formats with a packed device layout stay as
-    they are; the others are decoded to bf16 at load (expert stacks: re-encoded as Q8_0), which is what has to fit."""
+    they are, the other block formats are re-encoded as Q8_0 at load, and unquantised tensors become bf16."""
     from .ops.layout import FMT_IDS
-    if qt not in FMT_IDS and qt not in (GGMLType.F32, GGMLType.F16, GGMLType.BF16):
-        return n * (34 / 32 if expert else 2.0)
+    if qt in (GGMLType.F32, GGMLType.F16, GGMLType.BF16):
+        return n * 2.0
+    if qt not in FMT_IDS:
+        qt = GGMLType.Q8_0
     e, b = BLOCK_GEOMETRY[qt]
     return n / e * b
 

@@ -226,16 +226,16 @@ def test_describe_env_lists_the_switch_registry(capsys):
 
 
 def test_planner_counts_resident_bytes_for_formats_without_a_packed_layout():
-    """A 2-bit checkpoint is decoded to bf16 at load (expert stacks: Q8_0), so the plan must budget those bytes, not the
-    file's; packed formats are budgeted at their file size."""
+    """A 2-bit checkpoint is re-encoded as Q8_0 at load, so the plan must budget those bytes, not the file's; packed
+    formats are budgeted at their file size, unquantised tensors as bf16."""
     from llaminar_b200.gguf.constants import GGMLType
     from llaminar_b200.models.config import SHAPES, QuantRecipe
     from llaminar_b200.planning import _bytes, build_plan
     assert _bytes(GGMLType.Q4_K, 256) == 144 and _bytes(GGMLType.IQ3_S, 256) == 110
-    assert _bytes(GGMLType.IQ2_XS, 256) == 512 and _bytes(GGMLType.IQ2_XS, 256, expert=True) == 272
-    assert _bytes(GGMLType.BF16, 256) == 512 and _bytes(GGMLType.F32, 256) == 1024
+    assert _bytes(GGMLType.IQ2_XS, 256) == 272 and _bytes(GGMLType.IQ2_XS, 256, expert=True) == 272
+    assert _bytes(GGMLType.BF16, 256) == 512 and _bytes(GGMLType.F32, 256) == 512
     cfg = SHAPES["qwen3-32b"]
     layout = {"tp": 1, "stages": [("main", ["cuda:0"], 0, cfg.n_layers - 1)]}
     low = build_plan(cfg, layout, QuantRecipe(GGMLType.IQ2_XS, {}, "IQ2_XS"), 4096, 1)
     q4 = build_plan(cfg, layout, "Q4_K_S", 4096, 1)
-    assert low.ranks[0].weight_bytes > 3 * q4.ranks[0].weight_bytes
+    assert low.ranks[0].weight_bytes > 1.7 * q4.ranks[0].weight_bytes

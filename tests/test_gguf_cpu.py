@@ -176,3 +176,27 @@ def test_expert_stacks_without_a_packed_layout_are_reencoded_for_the_grouped_ker
     assert a.shape == b.shape and ((a - b).norm() / a.norm()).item() < 0.01
     u0, u1 = before[1].to_float(), ue.to_float()
     assert ((u0 - u1).norm() / u0.norm()).item() < 0.01
+
+
+def test_block_formats_without_a_packed_layout_are_reencoded_for_the_dense_kernels():
+    from llaminar_b200.engine.cuda_model import QLinear, for_kernels
+    from llaminar_b200.models.weights import QTensor, qtensor_from_float
+    from llaminar_b200.ops.layout import PackedWeight
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(128, 512, generator=g) * 0.02
+    packed = qtensor_from_float(x, GGMLType.Q4_K)
+    assert for_kernels(packed) is packed                                    # has a device layout: untouched
+    half = qtensor_from_float(x, GGMLType.F16)
+    assert for_kernels(half) is half                                        # unquantised: stays dense
+    rng = np.random.default_rng(1)
+    raw = rng.integers(0, 256, size=(128 * 512 // 256, 84), dtype=np.uint8)          # Q2_K: d and dmin are the last two fp16
+    raw[:, 80:84] = np.array([np.float16(0.01), np.float16(0.005)], dtype=np.float16).view(np.uint8)
+    low = QTensor(GGMLType.Q2_K, (128, 512), torch.from_numpy(raw.reshape(-1).copy()))
+    t = for_kernels(low)
+    assert t.qtype == GGMLType.Q8_0 and t.shape == (128, 512)
+    a, b = low.to_float(), t.to_float()
+    assert ((a - b).norm() / a.norm()).item() < 0.01
+    narrow = QTensor(GGMLType.Q5_0, (64, 128), quantize(torch.randn(64, 128, generator=g), GGMLType.Q8_0)[:64 * 128 // 32 * 22])
+    assert for_kernels(narrow) is narrow                                    # K is not a whole 256-column chunk: dense path
+    lin = QLinear.from_qtensors([packed, low], "cpu")
+    assert len(lin.parts) == 2 and all(isinstance(p, PackedWeight) for p, _ in lin.parts) and lin.n_out == 256
