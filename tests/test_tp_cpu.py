@@ -163,3 +163,28 @@ def test_expert_placement_balances_ranks_and_keeps_the_model_function(tmp_path):
     placed = run_ranks(_placed_generate, 2, loads)
     plain = run_ranks(_placed_generate, 2, None)
     assert placed[0] == placed[1] == plain[0] == base
+
+
+def _tp_preempt(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=3, max_context=256, kv_pages=7, tp=tp)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 1024, (50,), generator=g).tolist() for _ in range(3)]
+    sp = SamplingParams(temperature=0.7, top_k=20, top_p=0.9, seed=4, max_tokens=100, ignore_eos=True, logprobs=1)
+    reqs = [eng.add_request(p, sp) for p in prompts]
+    while eng.has_unfinished():
+        eng.step()
+    return [r.output for r in reqs], eng.stats["preemptions"], [[round(lp, 4) for _, lp, _ in r.logprobs] for r in reqs]
+
+
+def test_tp2_ranks_stay_in_step_through_preemptions_and_sampled_logprobs():
+    """Scheduling decisions (who is preempted, when it returns) depend only on replicated state, so both ranks issue
+    the same collectives in the same order and end with the same sampled tokens and log-probabilities."""
+    res = run_ranks(_tp_preempt, 2)
+    assert res[0] == res[1] and res[0][1] >= 1
+    assert all(len(o) == 100 for o in res[0][0])
