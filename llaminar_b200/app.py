@@ -123,7 +123,8 @@ def build_engine(cfg: OrchestrationConfig):
     if v["ctx_size"] > mcfg.context_length:
         # positions beyond the trained maximum are extrapolated RoPE angles: refuse rather than degrade silently
         raise ConfigError([f"--ctx-size {v['ctx_size']} exceeds the model's trained context of {mcfg.context_length} tokens"])
-    plan = build_plan(mcfg, layout, ctx_size=v["ctx_size"], batch_size=v["batch_size"])
+    from .planning import FileRecipe
+    plan = build_plan(mcfg, layout, FileRecipe.from_weights(weights), ctx_size=v["ctx_size"], batch_size=v["batch_size"])
     if plan.errors:
         raise ConfigError(plan.errors)
     if rank == 0:
@@ -412,14 +413,16 @@ def cmd_plan(cfg: OrchestrationConfig) -> int:
     from .models.config import SHAPES, ModelConfig
     from .planning import build_plan
     v = cfg.values
+    recipe = v.get("synthetic_recipe") or "Q4_K_M"
     if v.get("synthetic"):
         mcfg = SHAPES[v["synthetic"]]
     else:
         from .gguf import GGUFFile
+        from .planning import FileRecipe
         gf = GGUFFile(v["model"])
         mcfg = ModelConfig.from_gguf(gf)
+        recipe = FileRecipe(gf)                 # budget the formats the file really stores
         gf.close()
-    recipe = v.get("synthetic_recipe") or "Q4_K_M"
     if v.get("suggest_layout"):
         from .planning import suggest_layout
         layout, plan = suggest_layout(mcfg, int(v["suggest_layout"]), recipe, v["ctx_size"], v["batch_size"])

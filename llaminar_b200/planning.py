@@ -27,6 +27,35 @@ def _bytes(qt: GGMLType, n: int, expert: bool = False) -> float:
     return n / e * b
 
 
+class FileRecipe:
+    """The formats a parsed checkpoint really stores, in the shape of a quantisation recipe: the planner then budgets
+    the file that will be loaded instead of a nominal recipe (the reference's estimator reads the tensor types from the
+    GGUF header the same way; reference: src/v2/planning/WeightMemoryEstimator.cpp)."""
+
+    def __init__(self, gguf_file=None, entries=None):
+        """``gguf_file``: a parsed GGUFFile; or ``entries``: (name, qtype, n_dims, n_bytes) tuples."""
+        if entries is None:
+            entries = [(t.name, t.qtype, len(t.shape), t.nbytes) for t in gguf_file]
+        self.types = {name: qt for name, qt, _, _ in entries}
+        counts: dict = {}
+        for _, qt, nd, nb in entries:
+            if nd >= 2:
+                counts[qt] = counts.get(qt, 0) + nb
+        self.default = max(counts, key=counts.get) if counts else GGMLType.Q8_0
+        self.name = f"file ({self.default.name} mostly)"
+
+    @staticmethod
+    def from_weights(weights) -> "FileRecipe":
+        """The same view of weights that are already loaded (or synthesised)."""
+        return FileRecipe(entries=[(n, t.qtype, len(t.shape), t.raw.numel()) for n, t in weights.tensors.items()])
+
+    def for_tensor(self, tensor_name: str, layer: int | None = None, n_layers: int = 0) -> GGMLType:
+        qt = self.types.get(tensor_name)
+        if qt is None and tensor_name == "output.weight":          # tied head
+            qt = self.types.get("token_embd.weight")
+        return qt if qt is not None else self.default
+
+
 @dataclass
 class RankPlan:
     rank: int

@@ -239,3 +239,28 @@ def test_planner_counts_resident_bytes_for_formats_without_a_packed_layout():
     low = build_plan(cfg, layout, QuantRecipe(GGMLType.IQ2_XS, {}, "IQ2_XS"), 4096, 1)
     q4 = build_plan(cfg, layout, "Q4_K_S", 4096, 1)
     assert low.ranks[0].weight_bytes > 1.7 * q4.ranks[0].weight_bytes
+
+
+def test_plan_of_a_checkpoint_budgets_the_formats_in_the_file(tmp_path, capsys):
+    from llaminar_b200.app import main
+    from llaminar_b200.gguf import GGUFFile
+    from llaminar_b200.gguf.constants import GGMLType
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.planning import FileRecipe, build_plan
+    sizes = {}
+    for recipe in ("Q8_0", "Q4_K_M"):
+        path = str(tmp_path / f"{recipe}.gguf")
+        synthesize(SHAPES["tiny-qwen3"], recipe, seed=0).save_gguf(path)
+        gf = GGUFFile(path)
+        fr = FileRecipe(gf)
+        assert fr.for_tensor("blk.0.attn_q.weight") == gf["blk.0.attn_q.weight"].qtype
+        assert fr.for_tensor("blk.99.attn_q.weight") == fr.default and fr.default == (GGMLType.Q8_0 if recipe == "Q8_0" else GGMLType.Q4_K)
+        layout = {"tp": 1, "stages": [("main", ["cuda:0"], 0, SHAPES["tiny-qwen3"].n_layers - 1)]}
+        sizes[recipe] = build_plan(SHAPES["tiny-qwen3"], layout, fr).ranks[0].weight_bytes
+        nominal = build_plan(SHAPES["tiny-qwen3"], layout, recipe).ranks[0].weight_bytes
+        assert abs(sizes[recipe] - nominal) <= 0.1 * nominal      # a tied head takes the embedding's format, not the recipe's
+        gf.close()
+    assert sizes["Q8_0"] > 1.5 * sizes["Q4_K_M"]
+    assert main(["plan", "-m", str(tmp_path / "Q8_0.gguf"), "-d", "cuda:0"]) == 0
+    assert "weight" in capsys.readouterr().out
