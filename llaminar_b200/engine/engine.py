@@ -180,8 +180,6 @@ class LLMEngine:
         params = params or SamplingParams()
         if len(prompt) + 1 > self.max_context:
             raise ValueError(f"prompt of {len(prompt)} tokens exceeds the context window of {self.max_context}")
-        if params.wants_logprobs and self.mtp is not None:
-            raise ValueError("log-probabilities are not available while speculative decoding (MTP) is on")
         r = Request(next(self._rid), list(prompt), params, t_arrival=time.perf_counter())
         self.requests[r.rid] = r
         self.waiting.append(r)

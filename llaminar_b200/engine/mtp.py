@@ -143,7 +143,7 @@ class MTPDecoder:
         t0 = time.perf_counter()
         dev = engine.device
         it = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
-        special = any(r.forced or r.params.needs_penalties for r in reqs)
+        special = any(r.forced or r.params.needs_penalties or r.params.wants_logprobs for r in reqs)     # plain steps: one row each
         sampling = self.cfg.verify_mode == "speculative-sampling" and not all(r.params.is_greedy for r in reqs)
         if self.cfg.verify_mode == "greedy" and not all(r.params.is_greedy for r in reqs):
             special = True                                 # argmax verification would override the requested sampler

@@ -178,3 +178,19 @@ def test_preemption_under_speculative_decoding_stays_lossless(weights):
     got = eng.generate(prompts, sp)
     assert eng.stats["preemptions"] >= 1 and got == ref
     assert eng.kv.allocator.n_free == eng.kv.n_pages - 1 and not eng.mtp.seq
+
+
+def test_logprobs_under_speculative_decoding_fall_back_to_plain_steps(weights):
+    sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True, logprobs=2)
+    ref = LLMEngine(weights, device="cpu", max_batch=2, max_context=512)
+    a = ref.add_request(_prompts()[0], sp)
+    while ref.has_unfinished():
+        ref.step()
+    eng = LLMEngine(weights, device="cpu", max_batch=2, max_context=512, mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
+    b = eng.add_request(_prompts()[0], sp)
+    c = eng.add_request(_prompts()[1], GREEDY)                # rides along; speculation resumes once b is done
+    while eng.has_unfinished():
+        eng.step()
+    assert b.output == a.output and [t for t, _, _ in b.logprobs] == b.output
+    assert all(abs(x[1] - y[1]) < 1e-4 for x, y in zip(a.logprobs, b.logprobs))
+    assert len(c.output) == 12 and c.logprobs == [] and eng.mtp.stats()["drafted"] > 0
