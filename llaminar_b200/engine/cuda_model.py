@@ -78,6 +78,48 @@ class ForwardBatch:
     def is_decode(self) -> bool:
         return self.seq_lens is not None
 
+    def index_errors(self, vocab: int, n_pages: int, max_positions: int) -> list[str]:
+        """Every index the kernels will dereference, checked against its range on the host (one synchronisation; a debug
+        aid behind LLAMINAR_VALIDATE_TENSORS, never inside graph capture).  The kernels themselves trust these arrays: an
+        out-of-range page id or sequence id would be an out-of-bounds access on the device, so the check runs before any
+        launch and reports instead."""
+        errs = []
+
+        def rng(name, t, lo, hi):
+            if t is not None and t.numel():
+                mn, mx = int(t.min()), int(t.max())
+                if mn < lo or mx >= hi:
+                    errs.append(f"{name}: values in [{mn}, {mx}], allowed [{lo}, {hi})")
+
+        T = self.tokens.shape[0] if self.embeds is None else self.embeds.shape[0]
+        B, P = self.block_table.shape
+        if self.embeds is None:
+            rng("tokens", self.tokens, 0, vocab)
+        rng("positions", self.positions, 0, max_positions)
+        rng("seq_ids", self.seq_ids, 0, B)
+        rng("block_table", self.block_table, 0, n_pages)
+        if self.positions.shape[0] != T or self.seq_ids.shape[0] != T:
+            errs.append(f"positions / seq_ids have {self.positions.shape[0]} / {self.seq_ids.shape[0]} rows for {T} tokens")
+        cap = P * PAGE_SIZE
+        if self.is_decode:
+            rng("seq_lens", self.seq_lens, 1, cap + 1)
+            if self.seq_lens.shape[0] * self.rows_per_seq < T and self.seq_lens.shape[0] != B:
+                errs.append(f"seq_lens has {self.seq_lens.shape[0]} entries for {B} block-table rows")
+        else:
+            if self.cu_q is None or self.ctx_lens is None:
+                errs.append("prefill batch without cu_q / ctx_lens")
+            else:
+                cu = self.cu_q.tolist()
+                if cu[0] != 0 or cu[-1] != T or any(b < a for a, b in zip(cu, cu[1:])):
+                    errs.append(f"cu_q {cu[:4]}...{cu[-1]} is not a non-decreasing partition of {T} rows")
+                elif max(b - a for a, b in zip(cu, cu[1:])) > self.max_q_len:
+                    errs.append(f"max_q_len {self.max_q_len} is smaller than the longest query of the batch")
+                end = [c + (b - a) for c, a, b in zip(self.ctx_lens.tolist(), cu, cu[1:])]
+                if end and max(end) > cap:
+                    errs.append(f"context + query reaches {max(end)} tokens, the block table holds {cap}")
+        rng("logit_rows", self.logit_rows, 0, max(T, 1))
+        return errs
+
 
 class QLinear:
     """A (possibly multi-part) quantised linear layer: parts may differ in block format."""
@@ -406,12 +448,16 @@ class CudaModel:
         """Runs the layers of this model (stage) over the batch; returns (logits or None, hidden [T, d] fp32 view)."""
         T = fb.tokens.shape[0] if fb.embeds is None else fb.embeds.shape[0]
         assert T <= self.max_tokens, f"{T} tokens exceed the workspace ({self.max_tokens})"
+        debug = self._debug_hooks()
+        if debug is not None:
+            errs = fb.index_errors(self.cfg.vocab_size, kv.n_pages, self.cfg.context_length)
+            if errs:
+                raise IndexError("forward batch rejected before launch: " + "; ".join(errs))
         h = self.ws_h[:T]
         if fb.embeds is not None:
             h.copy_(fb.embeds)
         else:
             self.embed_tokens(fb.tokens, h)
-        debug = self._debug_hooks()
         for li, L in enumerate(self.layers):
             self._layer(L, fb, kv.layers[kv_layer_offset + li], T)
             if debug is not None:

@@ -30,7 +30,7 @@ REGISTRY: tuple[EnvVar, ...] = (
     EnvVar("LLAMINAR_COLLECTIVE_ORDER_CHECK", bool, False, "audit that all ranks issue the same collectives in the same order"),
     EnvVar("LLAMINAR_VERIFY_COLLECTIVES", bool, False, "after every all-reduce compare a checksum of the result across ranks (and count NaN/Inf)"),
     EnvVar("LLAMINAR_SKIP_ALLREDUCE", bool, False, "debug: skip tensor-parallel all-reduces (results are wrong; isolates compute time)"),
-    EnvVar("LLAMINAR_VALIDATE_TENSORS", bool, False, "scan activations for NaN/Inf after every layer"),
+    EnvVar("LLAMINAR_VALIDATE_TENSORS", bool, False, "check every index of a step's inputs on the host before launch; scan activations for NaN/Inf after every layer"),
     EnvVar("LLAMINAR_PDL", bool, True, "launch the decode-path kernels with programmatic dependent launch (prologues overlap the previous kernel)"),
     EnvVar("LLAMINAR_ATTN_TC", bool, True, "long prefill chunks (head_dim 128) run attention on the tcgen05 kernel instead of the mma.sync kernel"),
     EnvVar("LLAMINAR_TUNING_FILE", str, "", "JSON table of measured kernel launch parameters (written by python -m llaminar_b200.ops.tuning)"),

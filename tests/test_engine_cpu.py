@@ -141,3 +141,32 @@ def test_preemption_when_the_kv_cache_runs_out_continues_the_same_output():
         raise AssertionError("expected the cache to run out")
     except RuntimeError as exc:
         assert "exhausted" in str(exc)
+
+
+def test_forward_batch_index_check_names_every_out_of_range_input():
+    """The host-side check behind LLAMINAR_VALIDATE_TENSORS: well-formed prefill and decode batches pass; a page id, a
+    sequence id, a token, a length or a query partition outside its range is reported by name before anything launches."""
+    from llaminar_b200.engine.cuda_model import ForwardBatch
+    it = lambda x: torch.tensor(x, dtype=torch.int32)
+    ok_prefill = ForwardBatch(tokens=it([5, 6, 7, 8]), positions=it([64, 65, 0, 1]), seq_ids=it([0, 0, 1, 1]),
+                              block_table=it([[3, 4], [2, 0]]), cu_q=it([0, 2, 4]), ctx_lens=it([64, 0]), max_q_len=2,
+                              logit_rows=it([1, 3]))
+    assert ok_prefill.index_errors(vocab=1024, n_pages=8, max_positions=4096) == []
+    ok_decode = ForwardBatch(tokens=it([5, 6]), positions=it([70, 3]), seq_ids=it([0, 1]), block_table=it([[3, 4], [2, 0]]),
+                             seq_lens=it([71, 4]))
+    assert ok_decode.index_errors(1024, 8, 4096) == []
+    import dataclasses
+    bad = {
+        "tokens": dataclasses.replace(ok_decode, tokens=it([5, 1024])),
+        "block_table": dataclasses.replace(ok_decode, block_table=it([[3, 9], [2, 0]])),
+        "seq_ids": dataclasses.replace(ok_decode, seq_ids=it([0, 2])),
+        "seq_lens": dataclasses.replace(ok_decode, seq_lens=it([129, 4])),
+        "positions": dataclasses.replace(ok_prefill, positions=it([64, 65, 0, -1])),
+        "cu_q": dataclasses.replace(ok_prefill, cu_q=it([0, 3, 2])),
+        "max_q_len": dataclasses.replace(ok_prefill, max_q_len=1),
+        "context + query": dataclasses.replace(ok_prefill, ctx_lens=it([127, 0])),
+        "logit_rows": dataclasses.replace(ok_prefill, logit_rows=it([4])),
+    }
+    for name, fb in bad.items():
+        errs = fb.index_errors(1024, 8, 4096)
+        assert errs and any(name in e for e in errs), (name, errs)
