@@ -281,7 +281,8 @@ class ChatCompletionHandler:
             self.loop.cancel(ticket)
             raise
         yield "end", {"prompt_tokens": len(ids), "completion_tokens": n_completion, "finish_reason": finish,
-                      "prefix_hit_tokens": ticket.prefix_hit_tokens, "logprobs": token_logprobs}
+                      "prefix_hit_tokens": ticket.prefix_hit_tokens, "logprobs": token_logprobs,
+                      "reasoning_tokens": thinking_tokens if splitter is not None else None}
 
     def _logprobs_object(self, entries: list) -> dict:
         """OpenAI `choices[i].logprobs`: one item per generated token with its text, bytes and log-probability under the
@@ -297,6 +298,8 @@ class ChatCompletionHandler:
              "context_used": p + c}
         if info.get("prefix_hit_tokens"):
             u["prompt_tokens_details"] = {"cached_tokens": info["prefix_hit_tokens"]}
+        if info.get("reasoning_tokens") is not None:
+            u["completion_tokens_details"] = {"reasoning_tokens": info["reasoning_tokens"]}
         return u
 
     # -- non-streaming --------------------------------------------------------------------------------------

@@ -329,3 +329,12 @@ def test_no_kv_page_leak_across_request_kinds(server):
     c.close()
     _post(server, {"messages": [{"role": "user", "content": "x " * 2000}], "max_tokens": 4})       # context overflow: 400
     assert idle_free() == base
+
+
+def test_usage_reports_reasoning_tokens_for_thinking_templates(server):
+    st, body, _ = _post(server, {"messages": [{"role": "user", "content": "think about it"}], "max_tokens": 8, "temperature": 0})
+    u = json.loads(body)["usage"]
+    if server.chat.template.expects_thinking:
+        assert 0 <= u["completion_tokens_details"]["reasoning_tokens"] <= u["completion_tokens"]
+    else:
+        assert "completion_tokens_details" not in u
