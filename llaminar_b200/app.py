@@ -262,6 +262,15 @@ def cmd_chat(cfg: OrchestrationConfig) -> int:
     if tok is None or template is None:
         raise ConfigError(["the checkpoint has no embedded tokenizer; `chat` needs tokenizer.ggml.* metadata"])
     v = cfg.values
+    if v.get("tui"):
+        from .tui import ChatSession, run
+        session = ChatSession(drive, tok, template, v["ctx_size"], lambda: cli_sampling(cfg), v.get("system_prompt"))
+        try:
+            run(session, engine.cfg.name)
+        finally:
+            if world > 1:
+                drive.shutdown_workers()
+        return 0
     history: list[dict] = []
     if v.get("system_prompt"):
         history.append({"role": "system", "content": v["system_prompt"]})

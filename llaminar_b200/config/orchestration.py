@@ -113,6 +113,7 @@ OPTIONS: list[OptionSpec] = [
     _o("--mtp-force-accept", action="store_true", help="benchmark aid: treat every draft as accepted (random weights)", category="mtp"),
     # -- benchmark ------------------------------------------------------------------------------------------
     _o("--bench-runs", type=int, default=3, category="benchmark"),
+    _o("--tui", action="store_true", help="chat: full-screen interface (scroll-back, input history, status bar)", category="generation"),
     _o("--system-prompt", default=None, help="system message of `chat` / `oneshot`", category="generation"),
     _o("--bench-prompt-tokens", type=int, default=512, category="benchmark"),
     _o("--bench-shared-prefix-tokens", type=int, default=0, help="the first N prompt tokens are common to all requests of the batch", category="benchmark"),

@@ -113,3 +113,121 @@ def test_perf_gate_flags_only_slowdowns_beyond_the_tolerance():
     import json
     doc = json.loads(perf_gate.BASELINE.read_text())
     assert {"gemv", "gemm_small", "gemm_large", "attn_decode", "moe"} <= set(doc["cases"])
+
+
+def test_chat_view_wraps_scrolls_and_edits_without_a_terminal():
+    from llaminar_b200.tui import ChatView, LineEditor
+    v = ChatView(width=40, height=10)
+    v.add("user", "hello there")
+    v.append("assistant", "word " * 90)
+    v.append("assistant", "tail")
+    ls = v.lines()
+    assert ls[0][1].startswith("you   | hello") and ls[1][1].startswith("model | word")
+    assert all(len(t) <= 40 for _, t in ls) and len(v.entries) == 2 and "tail" in ls[-1][1]
+    assert len(v.visible()) == v.pane_height == 7 and v.visible()[-1] == ls[-1]          # follows the newest text
+    v.scroll_by(3)
+    assert v.visible()[-1] == ls[-4]
+    v.scroll_by(1000)
+    assert v.visible()[0] == ls[0]                                                      # clamped at the top
+    v.scroll_by(-1000)
+    assert v.scroll == 0
+    v.append("reasoning", "hmm")
+    assert v.entries[-1] == ["reasoning", "hmm"] and v.lines()[-1][1].startswith("think |")
+    assert len(v.status("m", 10, 100, 12.5, False)) == 39
+    v.resize(100, 10)
+    assert "generating" in v.status("m", 10, 100, 12.5, True) and "/reset" in v.status("m", 10, 100, 12.5, False)
+    e = LineEditor()
+    for ch in "helo":
+        e.key(ch)
+    e.key("LEFT"); e.key("l")
+    assert (e.buf, e.cur) == ("hello", 4)
+    e.key("HOME"); e.key("DELETE"); e.key("END"); e.key("BACKSPACE")
+    assert e.buf == "ell"
+    assert e.key("ENTER") == "ell" and e.buf == ""
+    e.key("x"); e.key("KILL")
+    assert e.buf == ""
+    e.key("UP")
+    assert e.buf == "ell"
+    e.key("DOWN")
+    assert e.buf == ""
+    e.buf, e.cur = "a" * 50, 50
+    text, col = e.window(10)
+    assert len(text) <= 10 and col == 9
+
+
+def test_chat_session_streams_answers_and_keeps_history():
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.tokenizer.bpe import BPETokenizer
+    from llaminar_b200.tokenizer.chat_template import ChatTemplate
+    from llaminar_b200.tui import ChatSession
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=1, max_context=256)
+    tok = BPETokenizer.from_metadata(w.metadata)
+    tpl = ChatTemplate.resolve(None, tok.chat_template)
+    s = ChatSession(eng, tok, tpl, 256, lambda: SamplingParams(temperature=0.0, max_tokens=6), "be brief")
+    pieces = list(s.ask("hi"))
+    assert all(k in ("reasoning", "content") for k, _ in pieces) and s.generated >= 1 and s.prompt_tokens > 0
+    assert [m["role"] for m in s.history] == ["system", "user", "assistant"]
+    assert s.history[-1]["content"] == "".join(p for k, p in pieces if k == "content")
+    list(s.ask("again"))
+    assert len(s.history) == 5 and s.context_used <= 256
+    import pytest
+    with pytest.raises(ValueError):
+        list(s.ask("x " * 400))
+    assert len(s.history) == 5                                   # the rejected turn left no trace
+    s.reset()
+    assert [m["role"] for m in s.history] == ["system"] and s.context_used == 0
+    assert not eng.has_unfinished() and eng.kv.allocator.n_free == eng.kv.n_pages - 1
+
+
+def test_full_screen_chat_runs_in_a_pseudo_terminal():
+    """`chat --tui` under a pty: a question is typed, an answer is drawn, /exit leaves with status 0."""
+    import os
+    import pty
+    import select
+    import subprocess
+    import sys
+    import time
+    master, slave = pty.openpty()
+    import fcntl, struct, termios
+    fcntl.ioctl(slave, termios.TIOCSWINSZ, struct.pack("HHHH", 24, 100, 0, 0))
+    env = dict(os.environ, TERM="xterm", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = subprocess.Popen([sys.executable, "-m", "llaminar_b200", "chat", "--tui", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0",
+                          "-d", "cpu", "-n", "6", "-c", "256"], stdin=slave, stdout=slave, stderr=subprocess.PIPE, env=env, close_fds=True)
+    os.close(slave)
+    seen = b""
+
+    def pump(until: bytes, limit: float) -> bool:
+        nonlocal seen
+        t0 = time.time()
+        while time.time() - t0 < limit:
+            r, _, _ = select.select([master], [], [], 0.2)
+            if r:
+                try:
+                    seen += os.read(master, 65536)
+                except OSError:
+                    return until in seen
+            if until in seen:
+                return True
+            if p.poll() is not None:
+                return until in seen
+        return False
+
+    try:
+        assert pump(b"full-screen chat", 120), p.stderr.read().decode()[-2000:] if p.poll() is not None else seen[-500:]
+        os.write(master, b"hello\r")
+        assert pump(b"you   | hello", 60)
+        assert pump(b"model |", 60)
+        time.sleep(1.0)
+        os.write(master, b"/exit\r")
+        t0 = time.time()
+        while p.poll() is None and time.time() - t0 < 60:
+            pump(b"\x00never", 0.3)
+        assert p.returncode == 0, p.stderr.read().decode()[-2000:]
+    finally:
+        if p.poll() is None:
+            p.kill()
+        os.close(master)
