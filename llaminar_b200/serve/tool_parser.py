@@ -2,7 +2,9 @@
 
 Supported layouts: Hermes-2-Pro / Qwen `<tool_call>{json}</tool_call>` blocks, bare JSON objects with
 `name` + `arguments`, and `[TOOL_CALLS] [...]` arrays (reference: src/v2/utils/ToolCallParser.cpp,
-src/v2/utils/ToolCallTypes.h).
+src/v2/utils/ToolCallTypes.h); and the tagged layout that the reference's own Qwen3.5 chat template writes for past
+calls (jinja/qwen/qwen35/template.jinja), which a model trained on that template emits:
+`<tool_call><function=NAME><parameter=KEY>VALUE</parameter>...</function></tool_call>`.
 """
 from __future__ import annotations
 
@@ -12,6 +14,27 @@ import uuid
 from dataclasses import dataclass, field
 
 _BLOCK = re.compile(r"<tool_call>\s*(.*?)\s*</tool_call>", re.S)
+_FUNCTION = re.compile(r"<function=([^>\s]+)>\s*(.*?)\s*</function>", re.S)
+_PARAMETER = re.compile(r"<parameter=([^>\s]+)>\n?(.*?)\n?</parameter>", re.S)
+
+
+def _tagged_calls(payload: str) -> list[dict]:
+    """`<function=name><parameter=key>value</parameter>...</function>` -> name / arguments objects.  A value that reads
+    as JSON (number, boolean, null, object, array) keeps its type; anything else is a string."""
+    out = []
+    for m in _FUNCTION.finditer(payload):
+        args = {}
+        for pm in _PARAMETER.finditer(m.group(2)):
+            raw = pm.group(2)
+            try:
+                val = json.loads(raw)
+                if isinstance(val, str):
+                    val = raw
+            except json.JSONDecodeError:
+                val = raw
+            args[pm.group(1)] = val
+        out.append({"name": m.group(1), "arguments": args})
+    return out
 
 
 @dataclass
@@ -42,7 +65,9 @@ def parse_tool_calls(text: str) -> ToolCallParse:
         try:
             obj = json.loads(payload)
         except json.JSONDecodeError:
-            return False
+            obj = _tagged_calls(payload)
+            if not obj:
+                return False
         items = obj if isinstance(obj, list) else [obj]
         got = [c for c in (_to_openai(o) for o in items) if c]
         calls.extend(got)

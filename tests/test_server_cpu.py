@@ -338,3 +338,18 @@ def test_usage_reports_reasoning_tokens_for_thinking_templates(server):
         assert 0 <= u["completion_tokens_details"]["reasoning_tokens"] <= u["completion_tokens"]
     else:
         assert "completion_tokens_details" not in u
+
+
+def test_tool_call_parser_reads_the_tagged_function_layout():
+    text = ("Let me check.\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n</parameter>\n"
+            "<parameter=opts>\n{\"units\": \"C\"}\n</parameter>\n</function>\n</tool_call>")
+    p = parse_tool_calls(text)
+    assert p.has_tool_calls and p.content == "Let me check."
+    fn = p.tool_calls[0]["function"]
+    assert fn["name"] == "get_weather" and json.loads(fn["arguments"]) == {"city": "Paris", "days": 3, "opts": {"units": "C"}}
+    # two calls in one block, a multi-line string value, and a block that is neither JSON nor tagged stays as text
+    two = parse_tool_calls("<tool_call><function=a><parameter=x>line1\nline2</parameter></function><function=b></function></tool_call>")
+    assert [c["function"]["name"] for c in two.tool_calls] == ["a", "b"]
+    assert json.loads(two.tool_calls[0]["function"]["arguments"]) == {"x": "line1\nline2"}
+    junk = parse_tool_calls("<tool_call>not a call</tool_call>")
+    assert not junk.has_tool_calls and junk.content == "<tool_call>not a call</tool_call>"
