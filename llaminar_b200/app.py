@@ -338,7 +338,7 @@ def cmd_serve(cfg: OrchestrationConfig) -> int:
     eos = tuple(i for i in (tok.eos_id, tok.vocab.get("<|im_end|>"), tok.vocab.get("<|endoftext|>")) if i is not None)
     chat = ChatCompletionHandler(loop, tok, template, engine.cfg.arch, v["ctx_size"], model_name=engine.cfg.name,
                                  cli_sampling=cli_sampling(cfg), eos_ids=tuple(dict.fromkeys(eos)))
-    srv = Server(chat, v["host"], v["port"], verbose=v.get("verbose", False))
+    srv = Server(chat, v["host"], v["port"], verbose=v.get("verbose", False), api_key=v.get("api_key"))
     try:
         import resource
         rss = resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 1024

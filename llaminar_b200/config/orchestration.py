@@ -49,6 +49,7 @@ OPTIONS: list[OptionSpec] = [
     # -- server ---------------------------------------------------------------------------------------------
     _o("--host", default="127.0.0.1", help="HTTP bind address", category="server"),
     _o("--port", type=int, default=8080, help="HTTP port", category="server"),
+    _o("--api-key", default=None, help="serve: require `Authorization: Bearer <key>` on the /v1 endpoints", category="server"),
     # -- sampling -------------------------------------------------------------------------------------------
     _o("-t", "--temperature", dest="temperature", type=float, default=0.8, category="sampling"),
     _o("--top-k", type=int, default=40, category="sampling"),

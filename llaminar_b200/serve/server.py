@@ -35,6 +35,23 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
             self.end_headers()
             self.wfile.write(body)
 
+        def _authorised(self) -> bool:
+            """With a key configured, the /v1 endpoints want `Authorization: Bearer <key>` (the reference has no
+            authentication; /health and /metrics stay open for probes)."""
+            key = state.get("api_key")
+            if not key:
+                return True
+            import hmac
+            given = self.headers.get("Authorization") or ""
+            if given.startswith("Bearer ") and hmac.compare_digest(given[7:].strip().encode(), key.encode()):
+                return True
+            n = int(self.headers.get("Content-Length") or 0)
+            if 0 < n <= MAX_BODY:
+                self.rfile.read(n)                      # keep the connection in step
+            self._send_json(401, {"error": {"message": "missing or invalid API key", "type": "invalid_request_error",
+                                            "code": "invalid_api_key"}})
+            return False
+
         def do_OPTIONS(self):
             self.send_response(204)
             for k, v in CORS.items():
@@ -59,11 +76,15 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
                 self.end_headers()
                 self.wfile.write(body)
             elif self.path.rstrip("/") == "/v1/models":
+                if not self._authorised():
+                    return
                 self._send_json(200, {"object": "list", "data": [{"id": chat.model_name, "object": "model", "owned_by": "local"}]})
             else:
                 self._send_json(404, {"error": {"message": f"unknown path {self.path}", "type": "invalid_request_error"}})
 
         def do_POST(self):
+            if self.path.startswith("/v1/") and not self._authorised():
+                return
             if self.path.rstrip("/") == "/v1/completions":
                 try:
                     n = int(self.headers.get("Content-Length") or 0)
@@ -117,8 +138,10 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
 
 
 class Server:
-    def __init__(self, chat: ChatCompletionHandler, host: str = "127.0.0.1", port: int = 8080, verbose: bool = False):
-        self.state = {"served": 0, "verbose": verbose}
+    def __init__(self, chat: ChatCompletionHandler, host: str = "127.0.0.1", port: int = 8080, verbose: bool = False,
+                 api_key: str | None = None, owns_loop: bool = True):
+        self.state = {"served": 0, "verbose": verbose, "api_key": api_key}
+        self.owns_loop = owns_loop                  # False: a second front end on an engine loop that someone else stops
         self.httpd = ThreadingHTTPServer((host, port), make_handler(chat, self.state))
         self.httpd.daemon_threads = True
         self.chat = chat
@@ -135,7 +158,8 @@ class Server:
             self.httpd.serve_forever(poll_interval=0.2)
         finally:
             self.httpd.server_close()
-            self.chat.loop.shutdown()
+            if self.owns_loop:
+                self.chat.loop.shutdown()
 
     def start_background(self) -> threading.Thread:
         t = threading.Thread(target=self.serve_forever, kwargs={"install_signals": False}, daemon=True)

@@ -353,3 +353,28 @@ def test_tool_call_parser_reads_the_tagged_function_layout():
     assert json.loads(two.tool_calls[0]["function"]["arguments"]) == {"x": "line1\nline2"}
     junk = parse_tool_calls("<tool_call>not a call</tool_call>")
     assert not junk.has_tool_calls and junk.content == "<tool_call>not a call</tool_call>"
+
+
+def test_api_key_guards_the_v1_endpoints(server):
+    srv = Server(server.chat, "127.0.0.1", 0, api_key="s3cret", owns_loop=False)
+    srv.start_background()
+    try:
+        body = json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0}).encode()
+
+        def call(method, path, headers, data=None):
+            c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+            c.request(method, path, body=data, headers=headers)
+            r = c.getresponse()
+            return r.status, r.read()
+
+        assert call("GET", "/health", {})[0] == 200                                    # probes stay open
+        st, out = call("POST", "/v1/chat/completions", {"Content-Type": "application/json"}, body)
+        assert st == 401 and json.loads(out)["error"]["code"] == "invalid_api_key"
+        assert call("POST", "/v1/chat/completions", {"Authorization": "Bearer wrong"}, body)[0] == 401
+        assert call("GET", "/v1/models", {})[0] == 401
+        st, out = call("POST", "/v1/chat/completions", {"Authorization": "Bearer s3cret", "Content-Type": "application/json"}, body)
+        assert st == 200 and json.loads(out)["object"] == "chat.completion"
+        assert call("GET", "/v1/models", {"Authorization": "Bearer s3cret"})[0] == 200
+    finally:
+        srv.stop()
+    assert _post(server, {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2})[0] == 200     # the shared loop lives on
