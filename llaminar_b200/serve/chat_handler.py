@@ -362,9 +362,10 @@ class ChatCompletionHandler:
                 "choices": [choice], "usage": self._usage(info)}
 
     # -- raw text completion (no chat template) ---------------------------------------------------------------
-    def complete(self, body_bytes: bytes) -> dict:
+    def complete(self, body_bytes: bytes):
         """`/v1/completions`: the prompt is tokenised as is (the reference's completion mode,
-        src/v2/app/modes/CompletionMode.cpp); returns the OpenAI text_completion object."""
+        src/v2/app/modes/CompletionMode.cpp).  Returns the OpenAI text_completion object, or with `"stream": true` an
+        iterator of server-sent-event chunks of the same shape (setup errors are raised before the first chunk)."""
         try:
             body = json.loads(body_bytes)
         except Exception as exc:
@@ -386,39 +387,78 @@ class ChatCompletionHandler:
             raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
         sp.max_tokens = min(mt, budget)
         sp.stop_token_ids = tuple(self.eos_ids)
-        stopper = StopMatcher(parse_stop(body.get("stop")))
+        stops = parse_stop(body.get("stop"))
+        rid, created, model = "cmpl-" + uuid.uuid4().hex[:24], int(time.time()), body.get("model") or self.model_name
+        pieces = self._complete_pieces(ids, sp, stops)
+
+        def obj(text: str, finish, usage=None) -> dict:
+            o = {"id": rid, "object": "text_completion", "created": created, "model": model,
+                 "choices": [{"index": 0, "text": text, "finish_reason": finish}]}
+            if usage is not None:
+                o["usage"] = usage
+            return o
+
+        def usage_of(n: int) -> dict:
+            return {"prompt_tokens": len(ids), "completion_tokens": n, "total_tokens": len(ids) + n}
+
+        if body.get("stream"):
+            first = next(pieces)                         # the request is in the engine (or has failed) before headers go out
+
+            def sse():
+                for kind, payload in _chain(first, pieces):
+                    if kind == "text":
+                        if payload:
+                            yield b"data: " + json.dumps(obj(payload, None), ensure_ascii=False).encode() + b"\n\n"
+                    else:
+                        n, finish = payload
+                        yield b"data: " + json.dumps(obj("", finish, usage_of(n)), ensure_ascii=False).encode() + b"\n\n"
+                yield b"data: [DONE]\n\n"
+            return sse()
+        parts, n, finish = [], 0, "stop"
+        for kind, payload in pieces:
+            if kind == "text":
+                parts.append(payload)
+            else:
+                n, finish = payload
+        return obj("".join(parts), finish, usage_of(n))
+
+    def _complete_pieces(self, ids: list[int], sp, stops: list[str]):
+        """Yields ("text", piece) while the completion streams, then ("end", (tokens generated, finish reason))."""
+        stopper = StopMatcher(stops)
         ticket = self.loop.submit(ids, sp)
         dec = StreamDecoder(self.tok, skip_special=True)
-        parts, n, finish = [], 0, "stop"
-        while True:
-            try:
-                ev = ticket.events.get(timeout=600)
-            except queue.Empty:
-                raise RequestError("generation timed out", 500, "server_error")
-            if ev[0] == "error":
-                raise RequestError(ev[1], ev[2] if len(ev) > 2 else 500, "server_error")
-            if ev[0] == "done":
-                finish = ev[1] or "stop"
-                break
-            if stopper.hit:
-                continue
-            for tid in ev[1]:
-                n += 1
-                if tid not in self.eos_ids:
-                    parts.append(stopper.push(dec.push(tid)))
-                if stopper.hit:
-                    self.loop.cancel(ticket)
-                    finish = "stop"
+        n, finish = 0, "stop"
+        try:
+            while True:
+                try:
+                    ev = ticket.events.get(timeout=600)
+                except queue.Empty:
+                    raise RequestError("generation timed out", 500, "server_error")
+                if ev[0] == "error":
+                    raise RequestError(ev[1], ev[2] if len(ev) > 2 else 500,
+                                       "invalid_request_error" if (len(ev) > 2 and ev[2] == 400) else "server_error")
+                if ev[0] == "done":
+                    finish = ev[1] or "stop"
                     break
-            if stopper.hit:
-                break
-        if not stopper.hit:
-            parts.append(stopper.push(dec.flush()))
-            parts.append(stopper.flush())
-        return {"id": "cmpl-" + uuid.uuid4().hex[:24], "object": "text_completion", "created": int(time.time()),
-                "model": body.get("model") or self.model_name,
-                "choices": [{"index": 0, "text": "".join(parts), "finish_reason": "length" if finish == "length" else "stop"}],
-                "usage": {"prompt_tokens": len(ids), "completion_tokens": n, "total_tokens": len(ids) + n}}
+                if stopper.hit:
+                    continue
+                for tid in ev[1]:
+                    n += 1
+                    if tid not in self.eos_ids:
+                        yield "text", stopper.push(dec.push(tid))
+                    if stopper.hit:
+                        self.loop.cancel(ticket)
+                        finish = "stop"
+                        break
+                if stopper.hit:
+                    break
+            if not stopper.hit:
+                yield "text", stopper.push(dec.flush())
+                yield "text", stopper.flush()
+        except GeneratorExit:
+            self.loop.cancel(ticket)
+            raise
+        yield "end", (n, "length" if finish == "length" else "stop")
 
     # -- streaming (server-sent events) -------------------------------------------------------------------------
     def stream(self, req: ChatRequest) -> Iterator[bytes]:

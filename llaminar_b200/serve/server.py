@@ -52,6 +52,28 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
                                             "code": "invalid_api_key"}})
             return False
 
+        def _send_stream(self, it) -> None:
+            """Server-sent events from an iterator of encoded chunks."""
+            first = next(it)                         # setup errors surface here, before headers go out
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            for k, v in CORS.items():
+                self.send_header(k, v)
+            self.end_headers()
+            try:
+                self.wfile.write(first)
+                self.wfile.flush()
+                for b in it:
+                    self.wfile.write(b)
+                    self.wfile.flush()
+            except (BrokenPipeError, ConnectionResetError):
+                it.close()                           # client went away: cancels the generation
+            except RequestError as exc:              # failure after the stream began: report in-band
+                self.wfile.write(b"data: " + json.dumps(exc.body()).encode() + b"\n\n")
+            self.close_connection = True
+
         def do_OPTIONS(self):
             self.send_response(204)
             for k, v in CORS.items():
@@ -90,7 +112,11 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
                     n = int(self.headers.get("Content-Length") or 0)
                     if n <= 0 or n > MAX_BODY:
                         raise RequestError("missing or oversized request body")
-                    self._send_json(200, chat.complete(self.rfile.read(n)))
+                    result = chat.complete(self.rfile.read(n))
+                    if isinstance(result, dict):
+                        self._send_json(200, result)
+                    else:
+                        self._send_stream(result)
                     state["served"] += 1
                 except RequestError as exc:
                     self._send_json(exc.status, exc.body())
@@ -106,26 +132,7 @@ def make_handler(chat: ChatCompletionHandler, state: dict):
                     raise RequestError("missing or oversized request body")
                 req = parse_request(self.rfile.read(n))
                 if req.stream:
-                    it = chat.stream(req)
-                    first = next(it)                 # setup errors surface here, before headers go out
-                    self.send_response(200)
-                    self.send_header("Content-Type", "text/event-stream")
-                    self.send_header("Cache-Control", "no-cache")
-                    self.send_header("Connection", "close")
-                    for k, v in CORS.items():
-                        self.send_header(k, v)
-                    self.end_headers()
-                    try:
-                        self.wfile.write(first)
-                        self.wfile.flush()
-                        for b in it:
-                            self.wfile.write(b)
-                            self.wfile.flush()
-                    except (BrokenPipeError, ConnectionResetError):
-                        it.close()                   # client went away: cancels the generation
-                    except RequestError as exc:      # failure after the stream began: report in-band
-                        self.wfile.write(b"data: " + json.dumps(exc.body()).encode() + b"\n\n")
-                    self.close_connection = True
+                    self._send_stream(chat.stream(req))
                 else:
                     self._send_json(200, chat.handle(req))
                 state["served"] += 1

@@ -378,3 +378,21 @@ def test_api_key_guards_the_v1_endpoints(server):
     finally:
         srv.stop()
     assert _post(server, {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2})[0] == 200     # the shared loop lives on
+
+
+def test_text_completion_streams_the_same_text(server):
+    req = {"prompt": "Once upon a time", "max_tokens": 8, "temperature": 0}
+    st, body, _ = _post(server, req, path="/v1/completions")
+    whole = json.loads(body)
+    assert st == 200
+    st, body, hdr = _post(server, dict(req, stream=True), path="/v1/completions")
+    assert st == 200 and hdr["Content-Type"].startswith("text/event-stream")
+    lines = [ln for ln in body.decode().splitlines() if ln.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(ln[6:]) for ln in lines[:-1]]
+    assert all(c["object"] == "text_completion" for c in chunks)
+    assert "".join(c["choices"][0]["text"] for c in chunks) == whole["choices"][0]["text"]
+    assert chunks[-1]["choices"][0]["finish_reason"] == whole["choices"][0]["finish_reason"]
+    assert chunks[-1]["usage"] == whole["usage"] and all(c["choices"][0]["finish_reason"] is None for c in chunks[:-1])
+    st, body, _ = _post(server, {"prompt": "", "stream": True}, path="/v1/completions")
+    assert st == 400                                              # setup errors arrive as JSON, not as a stream
