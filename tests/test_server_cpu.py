@@ -396,3 +396,17 @@ def test_text_completion_streams_the_same_text(server):
     assert chunks[-1]["usage"] == whole["usage"] and all(c["choices"][0]["finish_reason"] is None for c in chunks[:-1])
     st, body, _ = _post(server, {"prompt": "", "stream": True}, path="/v1/completions")
     assert st == 400                                              # setup errors arrive as JSON, not as a stream
+
+
+def test_load_generator_against_the_in_process_server(server, tmp_path):
+    from llaminar_b200.serve import loadgen
+    s = loadgen.run(f"http://127.0.0.1:{server.port}", concurrency=3, requests=6, prompt_tokens=24, max_tokens=5)
+    assert s["succeeded"] == 6 and s["failed"] == 0 and 6 <= s["output_tokens"] <= 30
+    assert s["ttft_ms"]["p50"] > 0 and s["ttft_ms"]["p99"] >= s["ttft_ms"]["p50"] and s["output_tok_per_s"] > 0
+    out = tmp_path / "lg.json"
+    assert loadgen.main(["--url", f"http://127.0.0.1:{server.port}", "--concurrency", "2", "--requests", "2", "--prompt-tokens", "16",
+                         "--max-tokens", "3", "--json", str(out)]) == 0
+    assert json.loads(out.read_text())["succeeded"] == 2
+    bad = loadgen.run("http://127.0.0.1:9", concurrency=1, requests=1, prompt_tokens=8, max_tokens=2, timeout=5)
+    assert bad["failed"] == 1 and bad["errors"]
+    assert loadgen.percentile([1.0, 2.0, 3.0, 4.0], 50) in (2.0, 3.0) and loadgen.percentile([], 99) == 0.0
