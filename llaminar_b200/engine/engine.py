@@ -299,10 +299,23 @@ class LLMEngine:
         r.prefix_hit_tokens = hit_tokens
         try:
             self._ensure_pages(r, len(r.prompt) + 1)
+            if self.running and self._available_pages() < len(self.running) + 1:
+                # admission watermark: every running sequence must still be able to take its next page, otherwise the
+                # newcomer's prefill would be thrown away by a preemption a few steps later
+                raise OutOfPages("admission would leave the running sequences no room to grow")
         except OutOfPages:
             self.kv.free_sequence(r.kv)
+            r.kv = SequenceKV()
+            r.prefix_hit_tokens = 0
             raise
         self.stats["prefix_hit_tokens"] += hit_tokens
+
+    def _available_pages(self) -> int:
+        """Free pages plus the pages that the prefix cache would give back on demand."""
+        n = self.kv.allocator.n_free
+        if self.prefix_cache is not None:
+            n += self.prefix_cache.evictable_pages()
+        return n
 
     def _ensure_pages(self, r: Request, n_tokens: int) -> None:
         try:

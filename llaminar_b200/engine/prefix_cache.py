@@ -243,6 +243,11 @@ class PrefixCache:
                 return True
         return False
 
+    def evictable_pages(self) -> int:
+        """Device pages that only the cache still holds (they can be handed back to the allocator on demand)."""
+        refs = self.engine.kv.allocator.refs
+        return sum(1 for page in self.device.values() if refs[page] == 1)
+
     def evict_for(self, engine, n_tokens: int) -> bool:
         """Free at least ceil(n_tokens / 64) pages held only by the cache.  Returns False if nothing could be freed."""
         need = (n_tokens + PAGE_SIZE - 1) // PAGE_SIZE
