@@ -254,7 +254,7 @@ class LLMEngine:
                 if batch and cost > budget:
                     break
                 try:
-                    self._admit(r)
+                    self._admit(r, len(batch))
                 except OutOfPages:
                     if not batch and not self.running:
                         raise
@@ -270,7 +270,9 @@ class LLMEngine:
             return self._decode(list(self.running))
         return []
 
-    def _admit(self, r: Request) -> None:
+    def _admit(self, r: Request, pending: int = 0) -> None:
+        """Pages for the prompt (shared with the prefix cache where it hits).  ``pending``: sequences admitted earlier in
+        the same scheduler step, which count as running for the watermark."""
         if r.n_folded and self.running:
             # a preempted sequence comes back only when it fits with room to grow beside the running ones: re-admitting
             # it into a full cache would recompute its whole prefix just to be preempted again
@@ -299,7 +301,8 @@ class LLMEngine:
         r.prefix_hit_tokens = hit_tokens
         try:
             self._ensure_pages(r, len(r.prompt) + 1)
-            if self.running and self._available_pages() < len(self.running) + 1:
+            others = len(self.running) + pending
+            if others and self._available_pages() < others + 1:
                 # admission watermark: every running sequence must still be able to take its next page, otherwise the
                 # newcomer's prefill would be thrown away by a preemption a few steps later
                 raise OutOfPages("admission would leave the running sequences no room to grow")
