@@ -579,6 +579,8 @@ class LLMEngine:
         its generated tokens appended to the prompt; the next prefill rebuilds the cache and samples the next token
         with the same step index a decode step would have used, so the output continues where it stopped."""
         self.running.remove(r)
+        if self.prefix_cache is not None:
+            self.prefix_cache.insert(self, r)          # its full pages stay reusable until someone needs the space
         self.kv.free_sequence(r.kv)
         if self.mtp is not None:
             self.mtp.release(r)
