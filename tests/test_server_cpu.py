@@ -410,3 +410,29 @@ def test_load_generator_against_the_in_process_server(server, tmp_path):
     bad = loadgen.run("http://127.0.0.1:9", concurrency=1, requests=1, prompt_tokens=8, max_tokens=2, timeout=5)
     assert bad["failed"] == 1 and bad["errors"]
     assert loadgen.percentile([1.0, 2.0, 3.0, 4.0], 50) in (2.0, 3.0) and loadgen.percentile([], 99) == 0.0
+
+
+def test_soak_under_kv_pressure_every_request_completes():
+    """Streamed requests at a concurrency the KV cache cannot hold (prefix cache on): admission waits, sequences are
+    preempted and resumed, and every request still gets its full answer; afterwards every page is either free or held
+    by the prefix cache alone."""
+    from llaminar_b200.engine.prefix_cache import PrefixCache, PrefixCacheConfig
+    from llaminar_b200.serve import loadgen
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    pc = PrefixCache(PrefixCacheConfig(), "fp")
+    eng = LLMEngine(w, device="cpu", max_batch=8, max_context=512, kv_pages=12, prefix_cache=pc)
+    tok = BPETokenizer.from_metadata(w.metadata)
+    loop = EngineLoop(eng)
+    chat = ChatCompletionHandler(loop, tok, ChatTemplate.resolve(None, tok.chat_template), "qwen3", 512, model_name="tiny", eos_ids=())
+    srv = Server(chat, "127.0.0.1", 0)
+    srv.start_background()
+    try:
+        s = loadgen.run(f"http://127.0.0.1:{srv.port}", concurrency=8, requests=12, prompt_tokens=30, max_tokens=200, temperature=0.8)
+        assert s["succeeded"] == 12 and s["failed"] == 0 and s["output_tokens"] == 12 * 200
+        assert loop.errors == 0 and eng.stats["preemptions"] >= 1
+        m = loop.metrics()
+        assert m["requests_finished"] == 12 and m["requests_running"] == 0 and m["requests_waiting"] == 0
+        assert eng.kv.allocator.n_free + len(pc.device) == eng.kv.n_pages - 1
+        assert all(r <= 1 for r in eng.kv.allocator.refs)
+    finally:
+        srv.stop()
