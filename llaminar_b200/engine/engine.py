@@ -114,6 +114,7 @@ class LLMEngine:
         self.mtp = mtp
         if mtp is not None:
             mtp.attach(self)
+        self._dropped: list[StepOutput] = []       # sequences that a decode step had to end because the cache is full
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
                       "prefix_hit_tokens": 0, "graph_replays": 0, "preemptions": 0}
         self._vocab = c.vocab_size
@@ -265,9 +266,9 @@ class LLMEngine:
             if batch:
                 return self._prefill(batch)
         if self.running:
-            if self.mtp is not None:
-                return self.mtp.decode_step(self, list(self.running))
-            return self._decode(list(self.running))
+            self._dropped = []
+            outs = self.mtp.decode_step(self, list(self.running)) if self.mtp is not None else self._decode(list(self.running))
+            return outs + self._dropped
         return []
 
     def _admit(self, r: Request, pending: int = 0) -> None:
@@ -544,6 +545,8 @@ class LLMEngine:
     def _decode(self, reqs: list[Request]) -> list[StepOutput]:
         t0 = time.perf_counter()
         reqs = self._reserve_decode_pages(reqs)
+        if not reqs:
+            return []
         eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced or r.params.wants_logprobs for r in reqs)
         if self.is_cuda:
             toks = self._decode_cuda(reqs, eager)
@@ -561,7 +564,7 @@ class LLMEngine:
     def _reserve_decode_pages(self, reqs: list[Request], extra: int = 0) -> list[Request]:
         """Gives every running sequence the pages its next token (plus ``extra`` speculative rows) needs.  When the cache
         is exhausted (and the prefix cache has nothing left to evict) the most recently admitted sequences are preempted
-        until the others fit; a single sequence that does not fit raises the allocator's error."""
+        until the others fit; a single sequence that does not fit is ended with finish reason "length"."""
         live = list(reqs)
         i = 0
         while i < len(live):
@@ -570,8 +573,13 @@ class LLMEngine:
                 i += 1
             except OutOfPages:
                 if len(live) == 1:
-                    raise
-                self._preempt(live.pop())
+                    # nobody left to preempt: the cache cannot hold this one sequence any further.  It ends here with
+                    # what it has produced (finish reason "length") instead of failing the step for every request.
+                    r = live.pop()
+                    self._finish(r, "length")
+                    self._dropped.append(StepOutput(r.rid, [], True, "length", [] if r.params.wants_logprobs else None))
+                else:
+                    self._preempt(live.pop())
         return live
 
     def _preempt(self, r: Request) -> None:

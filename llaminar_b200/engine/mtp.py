@@ -151,6 +151,8 @@ class MTPDecoder:
         k = min(k, min(engine.max_context - r.n_tokens - 2 for r in reqs))
         k = max(k, 0)
         reqs = engine._reserve_decode_pages(reqs, extra=k + 1)     # may preempt the youngest sequences
+        if not reqs:
+            return []
         B = len(reqs)
         n0 = [r.n_tokens for r in reqs]
         for r in reqs:
