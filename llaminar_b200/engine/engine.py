@@ -278,7 +278,7 @@ class LLMEngine:
             # a preempted sequence comes back only when it fits with room to grow beside the running ones: re-admitting
             # it into a full cache would recompute its whole prefix just to be preempted again
             need = (r.n_tokens + PAGE_SIZE) // PAGE_SIZE + len(self.running) + 1
-            if self.kv.allocator.n_free < need:
+            if self._available_pages() < need:
                 raise OutOfPages("waiting for pages after a preemption")
         hit_pages, hit_tokens = [], 0
         if self.prefix_cache is not None:
