@@ -258,7 +258,11 @@ class LLMEngine:
                     self._admit(r, len(batch))
                 except OutOfPages:
                     if not batch and not self.running:
-                        raise
+                        # the whole cache is free and the prompt still does not fit: this request can never run.  It
+                        # ends with finish reason "cache_full" (the server answers 400); the queue behind it goes on.
+                        self.waiting.pop(0)
+                        self._finish(r, "cache_full")
+                        return [StepOutput(r.rid, [], True, "cache_full", [] if r.params.wants_logprobs else None)]
                     break
                 self.waiting.pop(0)
                 batch.append(r)

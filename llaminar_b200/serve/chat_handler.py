@@ -22,6 +22,7 @@ from .tool_parser import parse_tool_calls
 
 SYSTEM_FINGERPRINT = "llaminar-b200"
 STOP_THINKING_TEXT = "\n\nConsidering the limited time by the user, I have to give the solution based on the thinking directly now.\n</think>\n\n"
+CACHE_FULL = "the prompt does not fit the KV cache of this server even when nothing else is running"
 _SAMPLING_FIELDS = ("temperature", "top_p", "top_k", "seed", "presence_penalty", "frequency_penalty",
                     "dry_multiplier", "dry_base", "dry_allowed_length")
 
@@ -228,6 +229,8 @@ class ChatCompletionHandler:
                                        "invalid_request_error" if (len(ev) > 2 and ev[2] == 400) else "server_error")
                 if ev[0] == "done":
                     finish = ev[1] or "stop"
+                    if finish == "cache_full":
+                        raise RequestError(CACHE_FULL, err_type="context_length_exceeded")
                     break
                 if stopper.hit:
                     continue                                  # tokens that were in flight when the stop sequence appeared
@@ -439,6 +442,8 @@ class ChatCompletionHandler:
                                        "invalid_request_error" if (len(ev) > 2 and ev[2] == 400) else "server_error")
                 if ev[0] == "done":
                     finish = ev[1] or "stop"
+                    if finish == "cache_full":
+                        raise RequestError(CACHE_FULL, err_type="context_length_exceeded")
                     break
                 if stopper.hit:
                     continue

@@ -172,3 +172,17 @@ def test_forward_batch_index_check_names_every_out_of_range_input():
     for name, fb in bad.items():
         errs = fb.index_errors(1024, 8, 4096)
         assert errs and any(name in e for e in errs), (name, errs)
+
+
+def test_a_prompt_larger_than_the_whole_cache_is_ended_and_the_queue_goes_on():
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=256, kv_pages=3)            # 2 usable pages: 128 tokens
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    big, small = eng.add_request(_prompt(200, seed=1), sp), eng.add_request(_prompt(30, seed=2), sp)
+    outs = []
+    while eng.has_unfinished():
+        outs += eng.step()
+    assert big.finish_reason == "cache_full" and big.output == []
+    assert any(o.rid == big.rid and o.finished and o.finish_reason == "cache_full" for o in outs)
+    assert small.finish_reason == "length" and len(small.output) == 4
+    assert eng.kv.allocator.n_free == eng.kv.n_pages - 1

@@ -436,3 +436,24 @@ def test_soak_under_kv_pressure_every_request_completes():
         assert all(r <= 1 for r in eng.kv.allocator.refs)
     finally:
         srv.stop()
+
+
+def test_prompt_that_cannot_fit_the_cache_gets_400_and_the_server_goes_on():
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=0)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, kv_pages=3)            # room for 128 tokens in all
+    tok = BPETokenizer.from_metadata(w.metadata)
+    loop = EngineLoop(eng)
+    chat = ChatCompletionHandler(loop, tok, ChatTemplate.resolve(None, tok.chat_template), "qwen3", 512, model_name="tiny", eos_ids=())
+    srv = Server(chat, "127.0.0.1", 0)
+    srv.start_background()
+    try:
+        long_msg = {"messages": [{"role": "user", "content": "word " * 60}], "max_tokens": 4}
+        for stream in (False, True):
+            st, body, _ = _post(srv, dict(long_msg, stream=stream))
+            assert st == 400 and json.loads(body)["error"]["type"] == "context_length_exceeded", body[:200]
+        st, body, _ = _post(srv, {"prompt": "word " * 150, "max_tokens": 4}, path="/v1/completions")
+        assert st == 400
+        st, body, _ = _post(srv, {"prompt": "hi", "max_tokens": 3, "temperature": 0}, path="/v1/completions")
+        assert st == 200 and loop.errors == 0
+    finally:
+        srv.stop()
