@@ -33,7 +33,9 @@ class EngineLoop:
         self.errors = 0
         # counters for /metrics (written by the engine thread only)
         self.counters = {"requests_submitted": 0, "requests_finished": 0, "requests_cancelled": 0, "requests_rejected": 0,
-                         "prompt_tokens": 0, "generated_tokens": 0, "prefix_hit_tokens": 0, "engine_steps": 0}
+                         "prompt_tokens": 0, "generated_tokens": 0, "prefix_hit_tokens": 0, "engine_steps": 0,
+                         # Prometheus summary pairs: mean = sum / count
+                         "ttft_seconds_sum": 0.0, "ttft_seconds_count": 0, "request_seconds_sum": 0.0, "request_seconds_count": 0}
         self._thread = threading.Thread(target=self._run, name="engine-loop", daemon=True)
         self._thread.start()
 
@@ -133,6 +135,12 @@ class EngineLoop:
                     t.events.put(("tokens", list(o.new_tokens), getattr(o, "logprobs", None)))
                 if o.finished:
                     self.counters["requests_finished"] += 1
+                    if req is not None and req.t_first_token is not None:
+                        import time
+                        self.counters["ttft_seconds_sum"] += req.t_first_token - req.t_arrival
+                        self.counters["ttft_seconds_count"] += 1
+                        self.counters["request_seconds_sum"] += time.perf_counter() - req.t_arrival
+                        self.counters["request_seconds_count"] += 1
                     self.counters["prefix_hit_tokens"] += int(t.prefix_hit_tokens or 0)
                     t.events.put(("done", o.finish_reason))
                     self._tickets.pop(o.rid, None)

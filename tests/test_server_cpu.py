@@ -245,6 +245,10 @@ def test_metrics_endpoint_counts_requests_and_tokens(server):
     assert after["llaminar_generated_tokens"] - before["llaminar_generated_tokens"] == used["completion_tokens"]
     assert after["llaminar_prompt_tokens"] - before["llaminar_prompt_tokens"] == used["prompt_tokens"]
     assert after["llaminar_requests_running"] == 0 and after["llaminar_kv_pages_free"] > 0
+    assert after["llaminar_ttft_seconds_count"] == before["llaminar_ttft_seconds_count"] + 1
+    d_ttft = after["llaminar_ttft_seconds_sum"] - before["llaminar_ttft_seconds_sum"]
+    d_req = after["llaminar_request_seconds_sum"] - before["llaminar_request_seconds_sum"]
+    assert 0 < d_ttft <= d_req < 120
 
 
 def test_n_choices_run_as_parallel_requests(server):
