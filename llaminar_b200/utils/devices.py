@@ -27,4 +27,10 @@ def describe_devices() -> dict:
                 g["power_limit_w"] = pynvml.nvmlDeviceGetEnforcedPowerLimit(h) / 1000.0
         except Exception:
             pass
+    try:                                            # is the compiled extension in place for the sources of this checkout?
+        from ..ops import build as ops_build
+        out["extension"] = {"path": str(ops_build.so_path()), "built_for_these_sources": bool(ops_build.is_built()),
+                            "arch": "sm_100a"}
+    except Exception as exc:
+        out["extension"] = {"error": f"{type(exc).__name__}: {exc}"}
     return out
