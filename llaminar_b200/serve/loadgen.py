@@ -34,8 +34,8 @@ def percentile(xs: list[float], p: float) -> float:
     return s[min(int(round(p / 100.0 * (len(s) - 1))), len(s) - 1)]
 
 
-def one_request(url, payload: dict, api_key: str | None, timeout: float) -> dict:
-    """Streams one chat completion; returns timings (seconds) and token counts, or {"error": ...}."""
+def one_request(url, payload: dict, api_key: str | None, timeout: float, path: str = "/v1/chat/completions") -> dict:
+    """Streams one chat (or text) completion; returns timings (seconds) and token counts, or {"error": ...}."""
     u = urlparse(url)
     conn_cls = http.client.HTTPSConnection if u.scheme == "https" else http.client.HTTPConnection
     conn = conn_cls(u.hostname, u.port or (443 if u.scheme == "https" else 80), timeout=timeout)
@@ -44,7 +44,7 @@ def one_request(url, payload: dict, api_key: str | None, timeout: float) -> dict
         headers["Authorization"] = f"Bearer {api_key}"
     t0 = time.perf_counter()
     try:
-        conn.request("POST", (u.path.rstrip("/") or "") + "/v1/chat/completions", body=json.dumps(payload).encode(), headers=headers)
+        conn.request("POST", (u.path.rstrip("/") or "") + path, body=json.dumps(payload).encode(), headers=headers)
         resp = conn.getresponse()
         if resp.status != 200:
             return {"error": f"HTTP {resp.status}: {resp.read()[:200].decode(errors='replace')}"}
@@ -56,8 +56,9 @@ def one_request(url, payload: dict, api_key: str | None, timeout: float) -> dict
             obj = json.loads(line[6:])
             if "error" in obj:
                 return {"error": obj["error"].get("message", "error")}
-            delta = obj["choices"][0].get("delta", {})
-            if delta.get("content") or delta.get("reasoning_content"):
+            choice = obj["choices"][0]
+            delta = choice.get("delta", {})
+            if delta.get("content") or delta.get("reasoning_content") or choice.get("text"):
                 stamps.append(time.perf_counter())
             usage = obj.get("usage") or usage
         t1 = time.perf_counter()
@@ -72,7 +73,7 @@ def one_request(url, payload: dict, api_key: str | None, timeout: float) -> dict
 
 
 def run(url: str, concurrency: int, requests: int, prompt_tokens: int, max_tokens: int, api_key: str | None = None,
-        shared_prefix: bool = False, temperature: float = 0.0, timeout: float = 600.0) -> dict:
+        shared_prefix: bool = False, temperature: float = 0.0, timeout: float = 600.0, endpoint: str = "chat") -> dict:
     results: list[dict] = []
     lock = threading.Lock()
     counter = iter(range(requests))
@@ -83,9 +84,14 @@ def run(url: str, concurrency: int, requests: int, prompt_tokens: int, max_token
                 i = next(counter, None)
             if i is None:
                 return
-            payload = {"messages": [{"role": "user", "content": make_prompt(i, prompt_tokens, shared_prefix)}],
-                       "max_tokens": max_tokens, "temperature": temperature, "stream": True}
-            r = one_request(url, payload, api_key, timeout)
+            prompt = make_prompt(i, prompt_tokens, shared_prefix)
+            payload = {"max_tokens": max_tokens, "temperature": temperature, "stream": True}
+            if endpoint == "completions":                      # raw prompt, no chat template
+                payload["prompt"] = prompt
+                r = one_request(url, payload, api_key, timeout, "/v1/completions")
+            else:
+                payload["messages"] = [{"role": "user", "content": prompt}]
+                r = one_request(url, payload, api_key, timeout)
             with lock:
                 results.append(r)
 
@@ -117,10 +123,12 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, default=128)
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--shared-prefix", action="store_true", help="all prompts share their beginning (measures the prefix cache)")
+    ap.add_argument("--endpoint", choices=("chat", "completions"), default="chat", help="/v1/chat/completions or /v1/completions")
     ap.add_argument("--api-key", default=None)
     ap.add_argument("--json", default=None, help="also write the summary to this file")
     a = ap.parse_args(argv)
-    summary = run(a.url, a.concurrency, a.requests, a.prompt_tokens, a.max_tokens, a.api_key, a.shared_prefix, a.temperature)
+    summary = run(a.url, a.concurrency, a.requests, a.prompt_tokens, a.max_tokens, a.api_key, a.shared_prefix, a.temperature,
+                  endpoint=a.endpoint)
     text = json.dumps(summary, indent=2)
     print(text)
     if a.json:

@@ -411,6 +411,8 @@ def test_load_generator_against_the_in_process_server(server, tmp_path):
     assert loadgen.main(["--url", f"http://127.0.0.1:{server.port}", "--concurrency", "2", "--requests", "2", "--prompt-tokens", "16",
                          "--max-tokens", "3", "--json", str(out)]) == 0
     assert json.loads(out.read_text())["succeeded"] == 2
+    t = loadgen.run(f"http://127.0.0.1:{server.port}", concurrency=2, requests=3, prompt_tokens=16, max_tokens=4, endpoint="completions")
+    assert t["succeeded"] == 3 and 3 <= t["output_tokens"] <= 12 and t["ttft_ms"]["p50"] > 0
     bad = loadgen.run("http://127.0.0.1:9", concurrency=1, requests=1, prompt_tokens=8, max_tokens=2, timeout=5)
     assert bad["failed"] == 1 and bad["errors"]
     assert loadgen.percentile([1.0, 2.0, 3.0, 4.0], 50) in (2.0, 3.0) and loadgen.percentile([], 99) == 0.0
