@@ -20,7 +20,7 @@ from .. import ops
 from ..gguf.constants import GGMLType
 from ..models.config import ModelConfig
 from ..models.weights import ModelWeights, QTensor
-from ..ops.layout import PackedWeight, can_pack, interleave_gate_up, pack_experts, pack_matrix
+from ..ops.layout import PackedWeight, can_pack, interleave_gate_up, pack_experts, pack_matrix, q4k_scales_in_range
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
 
@@ -33,6 +33,8 @@ def for_kernels(t: QTensor) -> QTensor:
     of a bf16 copy and the same kernels as every other layer.  Unquantised tensors, and matrices whose K is not a whole
     number of 256-column chunks, are left alone and run as dense bf16."""
     k = t.shape[-1]
+    if t.qtype == GGMLType.Q4_K and can_pack(t.qtype, k) and not q4k_scales_in_range(t.raw):
+        return t.transcoded(GGMLType.Q8_0)          # block scales beyond the Q4_K conversion's range (never seen in practice)
     if can_pack(t.qtype, k) or t.qtype in _FLOAT_TYPES or not can_pack(GGMLType.Q8_0, k):
         return t
     return t.transcoded(GGMLType.Q8_0)

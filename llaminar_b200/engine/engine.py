@@ -68,7 +68,7 @@ class LLMEngine:
     def __init__(self, weights: ModelWeights, device: str | torch.device | None = None, max_batch: int = 32,
                  max_context: int = 4096, kv_pages: int | None = None, max_prefill_tokens: int = 8192,
                  use_graphs: bool = True, prefix_cache=None, mtp=None, tp=None, eos_token_id: int | None = None,
-                 model=None, kv_memory_fraction: float = 0.85, kv_dtype: torch.dtype | None = None):
+                 model=None, kv_memory_fraction: float = 0.85, kv_dtype: torch.dtype | None = None, agree_group=None):
         self.cfg: ModelConfig = weights.config if weights is not None else model.cfg
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -97,6 +97,10 @@ class LLMEngine:
                 kv_pages = int(min(need * 2, max(need // 4, int(free * kv_memory_fraction) // per_page)))
             else:
                 kv_pages = need
+        # Every rank of a multi-process engine runs the same scheduler and must reach the same admission, eviction and
+        # preemption decisions, so all of them use the smallest page count any rank could afford (free memory differs
+        # between GPUs).  `agree_group`: the ranks that step together (default: the tensor-parallel group).
+        kv_pages = self._agree_kv_pages(kv_pages, agree_group if agree_group is not None else (tp.group if tp is not None and tp.size > 1 else None))
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
                                dtype=torch.bfloat16 if self.is_cuda else (kv_dtype or torch.float32))
         self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
@@ -122,6 +126,17 @@ class LLMEngine:
             self._init_static_buffers()
 
     # -- construction helpers ------------------------------------------------------------------
+    def _agree_kv_pages(self, kv_pages: int, group) -> int:
+        import torch.distributed as dist
+        if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return kv_pages
+        dev = self.device if dist.get_backend(group) == "nccl" else "cpu"
+        t = torch.tensor([kv_pages, -kv_pages], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+        lo, hi = int(t[0]), -int(t[1])
+        self.kv_pages_per_rank = (lo, hi)              # smallest and largest proposal, for the start-up log
+        return lo
+
     @staticmethod
     def from_gguf(path: str, **kw) -> "LLMEngine":
         dev = kw.get("device") or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -153,6 +168,12 @@ class LLMEngine:
         self._pairs_all = torch.zeros(ws, bmax * R, 2, dtype=torch.int32, device=self.device)
         # top-k / top-p sampling over a sharded head: every rank contributes its SAMPLE_CANDIDATES best entries per row
         # (the sampling kernel never looks beyond that many), 8 KB per row and rank instead of the logits
+        # presence / frequency penalties inside the captured step: per-lane penalty values and (allocated on first use) a
+        # dense table of token counts per lane over this rank's vocabulary shard, advanced on the device after sampling
+        self._pen_host = torch.zeros(2 * bmax, dtype=torch.float32).pin_memory()
+        self._pen_dev = torch.zeros(2 * bmax, dtype=torch.float32, device=self.device)
+        self._pen_counts = None
+        self._pen_lanes: list = [None] * bmax          # per lane: (request id, tokens of its history that the table holds)
         self._cand = self._cand_all = None
         if ws > 1 and self.is_cuda:
             kc = min(self.SAMPLE_CANDIDATES, self.model.vocab_local)
@@ -186,21 +207,58 @@ class LLMEngine:
         self.waiting.append(r)
         return r
 
-    def check_health(self) -> None:
-        """Raise if a kernel reported a bounded wait that ran out (a peer rank stalled); the scratch is reset first."""
+    def _status_words(self) -> list[torch.Tensor]:
+        """The device status words that kernels set when a bounded wait runs out (split-K scratch, fused TP arena)."""
+        words = []
+        sc = getattr(self.model, "scratch", None)
+        if sc is not None:
+            words.append(sc.status)
+        symm = getattr(self.tp, "symm", None) if self.tp is not None else None
+        if symm is not None:
+            words.append(symm.status)
+        return words
+
+    def _queue_health(self) -> None:
+        """Enqueue the copy of the status words into pinned memory behind the step's kernels; the step's own
+        synchronisation then makes them readable at no extra cost (`_finish_health`)."""
         if not self.is_cuda:
             return
+        if getattr(self, "_health_host", None) is None:
+            self._health_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        for i, w in enumerate(self._status_words()):
+            self._health_host[i:i + 1].copy_(w[:1], non_blocking=True)
+        self._health_queued = True
+
+    def _finish_health(self) -> None:
+        """After the step has synchronised: raise if any status word was set.  The scratch is reset first, the failure is
+        posted to the heartbeat (so that the other ranks stop too) and the caller fails the running requests."""
+        if not self.is_cuda:
+            return
+        if getattr(self, "_health_queued", False):
+            self._health_queued = False
+            vals = self._health_host[:len(self._status_words())].tolist()
+        else:
+            vals = [int(w[0]) for w in self._status_words()]
+        if not any(vals):
+            return
         sc = getattr(self.model, "scratch", None)
-        bad = sc is not None and int(sc.status[0]) != 0
+        if sc is not None:
+            sc.reset()
         symm = getattr(self.tp, "symm", None) if self.tp is not None else None
-        try:
-            if symm is not None:
-                symm.check_status()
-        finally:
-            if bad:
-                sc.reset()
-        if bad:
-            raise RuntimeError("a GEMM kernel gave up a bounded wait (status word set); scratch buffers were reset")
+        if symm is not None:
+            symm.status.zero_()
+        msg = f"a kernel gave up a bounded wait (status words {vals}); scratch buffers were reset"
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            hb.post_error(msg)
+        raise RuntimeError(msg)
+
+    def check_health(self) -> None:
+        """Raise if a kernel reported a bounded wait that ran out (a peer rank stalled); the scratch is reset first.
+        `step()` runs this check itself after every step; it is public for callers that drive `model.forward` directly."""
+        if self.is_cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        self._finish_health()
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
@@ -237,11 +295,14 @@ class LLMEngine:
     def step(self) -> list[StepOutput]:
         """One scheduler iteration: admit + prefill waiting requests if lanes are free, else one decode step."""
         if not self.perf.enabled:
-            return self._step()
+            outs = self._step()
+            self._finish_health()
+            return outs
         kind = "prefill" if self.waiting and len(self.running) < self.max_batch else "decode"
         self.perf.set_phase(kind)
         with self.perf.timer("engine", "step", device=str(self.device)), self.perf.cuda_timer("engine", "step_device", device=self.device):
             outs = self._step()
+        self._finish_health()
         self.perf.count("engine", "tokens", sum(len(o.new_tokens) for o in outs), device=str(self.device))
         return outs
 
@@ -297,12 +358,19 @@ class LLMEngine:
                 except OutOfPages:
                     self.kv.free_sequence(r.kv)
                     r.kv = SequenceKV()
-            hit_pages, hit_tokens = self.prefix_cache.lookup(r.prompt)
-        if hit_tokens >= len(r.prompt):               # keep at least one token to run for the logits
-            drop = (hit_tokens - len(r.prompt)) // PAGE_SIZE + 1
-            hit_pages = hit_pages[:len(hit_pages) - drop]
-            hit_tokens = len(hit_pages) * PAGE_SIZE
-        r.kv = self.kv.fork_prefix(hit_pages, hit_tokens) if hit_pages else SequenceKV()
+            held, hit_tokens = self.prefix_cache.lookup(r.prompt)      # `held`: one reference per page, dropped below
+            hit_pages = list(held)
+        else:
+            held = []
+        try:
+            if hit_tokens >= len(r.prompt):               # keep at least one token to run for the logits
+                drop = (hit_tokens - len(r.prompt)) // PAGE_SIZE + 1
+                hit_pages = hit_pages[:len(hit_pages) - drop]
+                hit_tokens = len(hit_pages) * PAGE_SIZE
+            r.kv = self.kv.fork_prefix(hit_pages, hit_tokens) if hit_pages else SequenceKV()
+        finally:
+            if held:
+                self.prefix_cache.release_pages(held)
         r.prefix_hit_tokens = hit_tokens
         try:
             self._ensure_pages(r, len(r.prompt) + 1)
@@ -551,7 +619,9 @@ class LLMEngine:
         reqs = self._reserve_decode_pages(reqs)
         if not reqs:
             return []
-        eager = (not self.use_graphs) or any(r.params.needs_penalties or r.forced or r.params.wants_logprobs for r in reqs)
+        # presence / frequency penalties run inside the graph (device-side count table); DRY, forced tokens and logprobs
+        # need the host and take the eager path
+        eager = (not self.use_graphs) or any(r.params.dry_multiplier > 0.0 or r.forced or r.params.wants_logprobs for r in reqs)
         if self.is_cuda:
             toks = self._decode_cuda(reqs, eager)
         else:
@@ -685,16 +755,23 @@ class LLMEngine:
         v = self._dec_views(bucket, 1)
         self._fill_decode_host(reqs, bucket, v)
         greedy = all(r.params.is_greedy for r in reqs)
+        pen = any(r.params.presence_penalty != 0.0 or r.params.frequency_penalty != 0.0 for r in reqs)
         n = v["n"]
         self._dec_dev[:n].copy_(self._dec_host[:n], non_blocking=True)
         if not greedy:
             self._fl_dev[:2 * bucket].copy_(self._fl_host[:2 * bucket], non_blocking=True)
             self._seed_dev[:bucket].copy_(self._seed_host[:bucket], non_blocking=True)
-        key = (bucket, greedy)
+        key = (bucket, greedy, pen)
         g = self._graphs.get(key)
         if g is None:
-            g = self._capture_decode(bucket, greedy, v)
+            if pen and self._pen_counts is None:
+                self._pen_counts = torch.zeros(self._bmax, self._vocab_window()[1], dtype=torch.int16, device=self.device)
+            g = self._capture_decode(bucket, greedy, v, pen)     # its warm-up runs dirty the count table: synced below
             self._graphs[key] = g
+        if pen:
+            self._sync_penalty_tables(reqs, bucket)
+            for i, r in enumerate(reqs):              # the graph counts the token it samples
+                self._pen_lanes[i] = (r.rid, r.n_tokens + 1)
         evp = self.step_events.pop() if self.step_events else None
         if evp:
             evp[0].record()
@@ -703,10 +780,43 @@ class LLMEngine:
             evp[1].record()
         self.stats["graph_replays"] += 1
         self._tok_host[:bucket].copy_(self._tok_dev[:bucket], non_blocking=True)
+        self._queue_health()
         torch.cuda.current_stream(self.device).synchronize()
         return self._tok_host[:B].tolist()
 
-    def _decode_body(self, bucket: int, greedy: bool, v: dict) -> None:
+    def _vocab_window(self) -> tuple[int, int]:
+        """[first token id, number of ids) of the logits rows this rank samples from."""
+        if self._sharded_vocab():
+            return self.model.plan.vocab_start, self.model.vocab_local
+        return 0, self._logits.shape[1]
+
+    def _sync_penalty_tables(self, reqs: list[Request], bucket: int) -> None:
+        """Bring the device-side count table in line with the lanes of this step.  A lane whose request changed, or whose
+        request took steps outside the graph since the table last saw it, is rebuilt from the request's tokens (one row
+        memset plus a small scatter); otherwise the table is already current, the previous graph replay has counted the
+        token it sampled."""
+        import numpy as np
+        v0, V = self._vocab_window()
+        if self._pen_counts is None:
+            self._pen_counts = torch.zeros(self._bmax, V, dtype=torch.int16, device=self.device)
+        ph, B = self._pen_host.numpy(), len(reqs)
+        ph[:bucket] = 0.0
+        ph[self._bmax:self._bmax + bucket] = 0.0
+        for i, r in enumerate(reqs):
+            ph[i], ph[self._bmax + i] = r.params.presence_penalty, r.params.frequency_penalty
+            if self._pen_lanes[i] != (r.rid, r.n_tokens):
+                toks = np.asarray(r.all_tokens, dtype=np.int64) - v0
+                u, c = np.unique(toks[(toks >= 0) & (toks < V)], return_counts=True)
+                row = self._pen_counts[i]
+                row.zero_()
+                if len(u):
+                    row.index_copy_(0, torch.from_numpy(u).to(self.device),
+                                    torch.from_numpy(np.minimum(c, 32767).astype(np.int16)).to(self.device))
+        for i in range(B, bucket):
+            self._pen_lanes[i] = None
+        self._pen_dev.copy_(self._pen_host, non_blocking=True)
+
+    def _decode_body(self, bucket: int, greedy: bool, v: dict, pen: bool = False) -> None:
         from .. import ops
         d = self._dec_dev
         P = self.max_pages_per_seq
@@ -714,33 +824,40 @@ class LLMEngine:
                           block_table=d[v["bt"]].view(bucket, P), seq_lens=d[v["len"]], rows_per_seq=1,
                           n_splits=self._splits_for(bucket))
         logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
+        tok = self._tok_dev[:bucket]
+        if pen:
+            ops.penalties_dense(logits, self._pen_counts[:bucket], self._pen_dev[:bucket], self._pen_dev[self._bmax:self._bmax + bucket])
         if greedy and self._sharded_vocab():
-            self._sharded_argmax(logits, bucket, self._tok_dev[:bucket])
-            return
-        if not greedy and self._sharded_vocab() and self._cand is not None:
+            self._sharded_argmax(logits, bucket, tok)
+        elif not greedy and self._sharded_vocab() and self._cand is not None:
             self._sharded_sample(logits, bucket, self._fl_dev[:bucket], d[v["topk"]], self._fl_dev[bucket:2 * bucket],
-                                 self._seed_dev[:bucket], d[v["step"]], self._tok_dev[:bucket])
-            return
-        logits = self._gather_vocab(logits)
-        if greedy:
-            ops.argmax(logits, self._tok_dev[:bucket])
+                                 self._seed_dev[:bucket], d[v["step"]], tok)
         else:
-            ops.sample(logits, self._fl_dev[:bucket], d[v["topk"]], self._fl_dev[bucket:2 * bucket],
-                       self._seed_dev[:bucket], d[v["step"]], self._tok_dev[:bucket])
+            logits = self._gather_vocab(logits)
+            if greedy:
+                ops.argmax(logits, tok)
+            else:
+                ops.sample(logits, self._fl_dev[:bucket], d[v["topk"]], self._fl_dev[bucket:2 * bucket],
+                           self._seed_dev[:bucket], d[v["step"]], tok)
+        if pen:
+            v0, V = self._vocab_window()
+            ops.count_tokens(self._pen_counts[:bucket], tok, v0, V)
 
-    def _capture_decode(self, bucket: int, greedy: bool, v: dict):
+    def _capture_decode(self, bucket: int, greedy: bool, v: dict, pen: bool = False):
         torch.cuda.synchronize(self.device)
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
             for _ in range(2):                          # warm-up: lazy initialisation must not happen in capture
-                self._decode_body(bucket, greedy, v)
+                self._decode_body(bucket, greedy, v, pen)
+            if pen:                                     # the warm-up runs counted tokens: every lane's table is rebuilt below
+                self._pen_lanes = [None] * self._bmax
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         from .. import ops
         n0 = ops.launch_count()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._decode_body(bucket, greedy, v)
-        self.launches_per_graph[(bucket, greedy)] = ops.launch_count() - n0
+            self._decode_body(bucket, greedy, v, pen)
+        self.launches_per_graph[(bucket, greedy, pen) if pen else (bucket, greedy)] = ops.launch_count() - n0
         return g

@@ -73,17 +73,26 @@ class PrefixCache:
         self.page_bytes = 0
         self._stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "inserted_blocks": 0, "evicted_to_ram": 0,
                        "evicted_to_disk": 0, "dropped": 0, "promoted": 0, "terminal_hits": 0, "terminal_stored": 0}
-        if self.cfg.disk_dir and self.cfg.disk_budget_mb > 0:
-            os.makedirs(self.cfg.disk_dir, exist_ok=True)
-            for name in sorted(os.listdir(self.cfg.disk_dir)):          # blocks persisted by an earlier process
-                if name.endswith(".kvblk") and name.startswith(self.salt.hex()[:8]):
-                    self.disk[bytes.fromhex(name[9:-6])] = os.path.getsize(os.path.join(self.cfg.disk_dir, name))
+        self.file_prefix = self.salt.hex()[:8]           # completed by attach(): the shard of the cache this process holds
 
     # -- wiring ---------------------------------------------------------------------------------------------
     def attach(self, engine) -> None:
         self.engine = engine
         kv = engine.kv
         self.page_bytes = kv.n_layers * 2 * kv.n_kv_heads * PAGE_SIZE * kv.head_dim * kv.layers[0].element_size()
+        # Disk-tier files are private to one shard of the cache: every rank of a multi-process engine holds other KV heads
+        # (tensor parallelism) or other layers (pipeline stages) of the same block hash.  The file prefix therefore names
+        # the model fingerprint AND this process's rank / world size and page geometry, so that a rank never reads a
+        # payload that another rank, or an earlier run with another layout, wrote.
+        import torch.distributed as dist
+        rank, world = (dist.get_rank(), dist.get_world_size()) if dist.is_available() and dist.is_initialized() else (0, 1)
+        shard = f"{rank}/{world}/{kv.n_layers}/{kv.n_kv_heads}/{kv.head_dim}/{kv.layers[0].dtype}"
+        self.file_prefix = self.salt.hex()[:8] + hashlib.blake2b(shard.encode(), digest_size=4).hexdigest()
+        if self.cfg.disk_dir and self.cfg.disk_budget_mb > 0:
+            os.makedirs(self.cfg.disk_dir, exist_ok=True)
+            for name in sorted(os.listdir(self.cfg.disk_dir)):          # blocks persisted by an earlier process
+                if name.endswith(".kvblk") and name.startswith(self.file_prefix + "_"):
+                    self.disk[bytes.fromhex(name[len(self.file_prefix) + 1:-6])] = os.path.getsize(os.path.join(self.cfg.disk_dir, name))
 
     @property
     def max_device_pages(self) -> int:
@@ -107,7 +116,12 @@ class PrefixCache:
 
     # -- lookup -----------------------------------------------------------------------------------------------
     def lookup(self, prompt: list[int]) -> tuple[list[int], int]:
-        """Longest cached chain of full blocks -> (page ids, tokens covered).  RAM / disk hits are re-imported."""
+        """Longest cached chain of full blocks -> (page ids, tokens covered).  RAM / disk hits are re-imported.
+
+        Every returned page carries one extra reference that belongs to the caller: promoting a later block of the chain
+        may have to evict, and a page that only the cache held could otherwise be evicted and handed straight back for
+        the new block while it is already part of this result.  The caller drops the references with `release_pages`
+        once the sequence has taken its own (`fork_prefix`)."""
         self._stats["lookups"] += 1
         kv = self.engine.kv
         pages: list[int] = []
@@ -126,11 +140,17 @@ class PrefixCache:
                 self._stats["promoted"] += 1
             else:
                 self.device.move_to_end(h)
+            kv.allocator.retain(page)
             pages.append(page)
         if pages:
             self._stats["hits"] += 1
             self._stats["hit_tokens"] += len(pages) * PAGE_SIZE
         return pages, len(pages) * PAGE_SIZE
+
+    def release_pages(self, pages: list[int]) -> None:
+        """Drop the references `lookup` took on the caller's behalf."""
+        for p in pages:
+            self.engine.kv.allocator.release(p)
 
     def lookup_terminal(self, prompt: list[int]) -> TerminalState | None:
         if self.cfg.terminal_state == "off":
@@ -193,17 +213,21 @@ class PrefixCache:
 
     def restore_terminal(self, engine, req, term: TerminalState) -> bool:
         """Rebuild the sequence's pages for an exact prompt repeat; False if the full blocks are gone."""
-        pages, covered = self.lookup(req.prompt)
+        held, covered = self.lookup(req.prompt)
         need_full = term.n_tokens - term.tail_tokens
         if covered < need_full:
+            self.release_pages(held)
             return False
-        pages = pages[:need_full // PAGE_SIZE]
-        req.kv = engine.kv.fork_prefix(pages, need_full) if pages else SequenceKV()
-        if term.tail_tokens:
-            page = self._alloc_page()
-            for i, l in enumerate(engine.kv.layers):
-                l[page].copy_(term.tail_payload[i])
-            req.kv.pages.append(page)
+        try:
+            pages = held[:need_full // PAGE_SIZE]
+            req.kv = engine.kv.fork_prefix(pages, need_full) if pages else SequenceKV()
+            if term.tail_tokens:
+                page = self._alloc_page()
+                for i, l in enumerate(engine.kv.layers):
+                    l[page].copy_(term.tail_payload[i])
+                req.kv.pages.append(page)
+        finally:
+            self.release_pages(held)
         req.kv.length = term.n_tokens
         self._stats["terminal_hits"] += 1
         return True
@@ -268,14 +292,16 @@ class PrefixCache:
             self._to_disk(h, payload)
 
     def _disk_path(self, h: bytes) -> str:
-        return os.path.join(self.cfg.disk_dir, f"{self.salt.hex()[:8]}_{h.hex()}.kvblk")
+        return os.path.join(self.cfg.disk_dir, f"{self.file_prefix}_{h.hex()}.kvblk")
 
     def _to_disk(self, h: bytes, payload: torch.Tensor) -> None:
         if not (self.cfg.disk_dir and self.cfg.disk_budget_mb > 0):
             self._stats["dropped"] += 1
             return
         path = self._disk_path(h)
-        torch.save(payload.cpu(), path)
+        tmp = f"{path}.{os.getpid()}.tmp"                # a reader never sees a half-written file
+        torch.save(payload.cpu(), tmp)
+        os.replace(tmp, path)
         self.disk[h] = os.path.getsize(path)
         self._stats["evicted_to_disk"] += 1
         budget = self.cfg.disk_budget_mb * (1 << 20)

@@ -264,8 +264,15 @@ def sample_merged(gathered, temperature, top_k, top_p, seeds, step, tokens) -> N
     _count()
 
 
-def penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency) -> None:
-    ext().penalties(logits, hist_tokens, hist_counts, hist_offsets, presence, frequency)
+def penalties_dense(logits, counts, presence, frequency) -> None:
+    """logits[row, t] -= presence[row] * (counts[row, t] > 0) + frequency[row] * counts[row, t] (int16 count table per lane)."""
+    ext().penalties_dense(logits, counts, presence, frequency)
+    _count()
+
+
+def count_tokens(counts, tokens, v0: int, vocab: int) -> None:
+    """counts[row, tokens[row] - v0] += 1 where the token falls into [v0, v0 + vocab): the sampled tokens join the history."""
+    ext().count_tokens(counts, tokens, v0, vocab)
     _count()
 
 

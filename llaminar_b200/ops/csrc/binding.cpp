@@ -305,13 +305,22 @@ static void sample_merged(const Tensor& gathered, const Tensor& temperature, con
     LLM_CUDA_CHECK(llm::launch_sample(p, cur_stream()));
 }
 
-static void penalties(Tensor logits, const Tensor& hist_tokens, const Tensor& hist_counts, const Tensor& hist_offsets,
-                      const Tensor& presence, const Tensor& frequency) {
+static void penalties_dense(Tensor logits, const Tensor& counts, const Tensor& presence, const Tensor& frequency) {
     const c10::cuda::CUDAGuard guard(logits.device());
-    LLM_CUDA_CHECK(llm::launch_penalties(static_cast<float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1), (int)logits.stride(0),
-                                         static_cast<const int*>(hist_tokens.data_ptr()), static_cast<const int*>(hist_counts.data_ptr()),
-                                         static_cast<const int*>(hist_offsets.data_ptr()), static_cast<const float*>(presence.data_ptr()),
-                                         static_cast<const float*>(frequency.data_ptr()), cur_stream()));
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && counts.scalar_type() == torch::kInt16 && logits.dim() == 2 && counts.dim() == 2);
+    TORCH_CHECK(counts.size(0) >= logits.size(0) && counts.size(1) >= logits.size(1), "count table smaller than the logits");
+    TORCH_CHECK(presence.numel() >= logits.size(0) && frequency.numel() >= logits.size(0));
+    LLM_CUDA_CHECK(llm::launch_penalties_dense(static_cast<float*>(logits.data_ptr()), (int)logits.size(0), (int)logits.size(1), (int)logits.stride(0),
+                                               static_cast<const unsigned short*>(counts.data_ptr()), (int)counts.stride(0),
+                                               static_cast<const float*>(presence.data_ptr()), static_cast<const float*>(frequency.data_ptr()), cur_stream()));
+}
+
+static void count_tokens(Tensor counts, const Tensor& tokens, int64_t v0, int64_t vocab) {
+    const c10::cuda::CUDAGuard guard(counts.device());
+    TORCH_CHECK(counts.scalar_type() == torch::kInt16 && tokens.scalar_type() == torch::kInt32 && counts.dim() == 2);
+    TORCH_CHECK(counts.size(0) >= tokens.numel() && counts.size(1) >= vocab);
+    LLM_CUDA_CHECK(llm::launch_count_tokens(static_cast<unsigned short*>(counts.data_ptr()), (int)counts.stride(0),
+                                            static_cast<const int*>(tokens.data_ptr()), (int)v0, (int)vocab, (int)tokens.numel(), cur_stream()));
 }
 
 static void nan_scan(const Tensor& x, Tensor counts) {
@@ -429,7 +438,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("sample", &sample);
     m.def("sample_candidates", &sample_candidates);
     m.def("sample_merged", &sample_merged);
-    m.def("penalties", &penalties);
+    m.def("penalties_dense", &penalties_dense);
+    m.def("count_tokens", &count_tokens);
     m.def("nan_scan", &nan_scan);
     m.def("spec_verify_greedy", &spec_verify_greedy);
     m.def("spec_verify_reject", &spec_verify_reject);

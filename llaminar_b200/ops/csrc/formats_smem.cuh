@@ -226,4 +226,69 @@ template <int A> struct DequantAtom<FMT_IQ3_S, A> {
     }
 };
 
+// ---- Q4_K to bf16, atom index at run time ------------------------------------------------------------------------------
+// A nibble q kept in the high half of its byte (0xq0) and widened to 16 bits with a zero high byte is the bf16 subnormal
+// 16 q * 2^-133 = q * 2^-129, exactly and with no magic offset to subtract afterwards.  One HFMA2 with the block's scale
+// times 2^129 and its (negated) minimum then yields two weights with a single rounding: bit for bit what
+// (128 + q - 128) * scale - min gives, for one half2 operation less per pair.  Per 8 weights: 3 logic ops, 4 byte permutes,
+// 4 HFMA2 (the generic path spends 3 + 4 + 8).  The scale times 2^129 must stay finite in bf16, i.e. d * sc < 0.5 (weights
+// up to about +-7); larger scales are clamped to the largest finite value, and the loader re-encodes such a tensor instead
+// of sending it here (ops/layout.py: q4k_scales_in_range).
+// The atom index is a run-time value so that the four warps of a scheduler (same row group, different atoms) share one
+// copy of the code.  The sink receives 16 consecutive columns per call: sink.emit16(c, r) -> columns 64*A + 16*c ...
+// (A fp16 variant through cvt.rn.f16x2.e4m3x2 was tried first: tcgen05.mma kind::f16 with an fp16 A and a bf16 B operand
+// raises "illegal instruction" on B200, although the two formats are separate fields of the instruction descriptor.)
+LLM_DEVICE uint32_t hfma2_bf16_u32(uint32_t a, __nv_bfloat162 s, __nv_bfloat162 b) {
+    const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&a), s, b);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+struct DequantAtomQ4KRt {
+    template <bool HI, class S>
+    LLM_DEVICE static void conv16(const uint4& q, __nv_bfloat162 s, __nv_bfloat162 nb, int c, S& sink) {
+        const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+        uint32_t r[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = (HI ? ws[i] : (ws[i] << 4)) & 0xf0f0f0f0u;
+            r[2 * i] = hfma2_bf16_u32(__byte_perm(w, 0u, 0x4140), s, nb);
+            r[2 * i + 1] = hfma2_bf16_u32(__byte_perm(w, 0u, 0x4342), s, nb);
+        }
+        sink.emit16(c, r);
+    }
+    // Everything this thread needs from the raw chunk, fetched and prepared before the operand slot is waited for: the two
+    // 16-byte units of packed nibbles and the scale / minimum pairs of sub-blocks 2A and 2A + 1.
+    struct Regs { uint4 q0, q1; __nv_bfloat162 s_lo, s_hi, b_lo, b_hi; };
+    LLM_DEVICE static Regs load(uint32_t raw, int g, int lane, int A) {
+        using T = FmtTraits<FMT_Q4_K>;
+        Regs r;
+        const uint32_t row16 = (uint32_t)((g << 5) + lane) << 4;
+        const uint4 meta = lds_v4(raw + T::P_META + row16);
+        const uint32_t qaddr = raw + T::P_QS + ((uint32_t)(g * 8 + 2 * A) << 9) + ((uint32_t)lane << 4);
+        r.q0 = lds_v4(qaddr);
+        r.q1 = lds_v4(qaddr + 512);
+        // 6-bit scales / minima of sub-blocks 2A and 2A + 1: bytes (2A & 3) and (2A & 3) + 1 of the three packed words
+        const int sh = (A & 1) << 4;
+        const uint32_t a2 = meta.y >> sh, b2 = meta.z >> sh, c2 = meta.w >> sh;
+        uint32_t sc2, mn2;
+        if (A < 2) { sc2 = a2 & 0x3f3fu; mn2 = b2 & 0x3f3fu; }
+        else { sc2 = (c2 & 0x0f0fu) | ((a2 >> 2) & 0x3030u); mn2 = ((c2 >> 4) & 0x0f0fu) | ((b2 >> 2) & 0x3030u); }
+        // d * 2^129 in two exact steps (2^129 is not an fp32 value)
+        const float BIG = 3.3895314e38f;                       // largest finite bf16
+        const float d = half_bits_to_float(meta.x & 0xffff) * 1.2676506e30f, ndmin = -half_bits_to_float(meta.x >> 16);   // 2^100
+        const float k29 = 536870912.0f;                         // 2^29
+        r.s_lo = __float2bfloat162_rn(fminf(d * ((float)(sc2 & 0xff) * k29), BIG));
+        r.s_hi = __float2bfloat162_rn(fminf(d * ((float)((sc2 >> 8) & 0xff) * k29), BIG));
+        r.b_lo = __float2bfloat162_rn(ndmin * (float)(mn2 & 0xff));
+        r.b_hi = __float2bfloat162_rn(ndmin * (float)((mn2 >> 8) & 0xff));
+        return r;
+    }
+    template <class S> LLM_DEVICE static void convert(const Regs& r, S& sink) {
+        conv16<false>(r.q0, r.s_lo, r.b_lo, 0, sink);
+        conv16<false>(r.q1, r.s_lo, r.b_lo, 1, sink);
+        conv16<true>(r.q0, r.s_hi, r.b_hi, 2, sink);
+        conv16<true>(r.q1, r.s_hi, r.b_hi, 3, sink);
+    }
+    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, int A, S& sink) { convert(load(raw, g, lane, A), sink); }
+};
+
 }  // namespace llm

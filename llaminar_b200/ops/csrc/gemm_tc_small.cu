@@ -28,6 +28,13 @@ namespace tcs {
 using namespace tc5;
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+#ifndef LLM_WAIT_MODE
+#define LLM_WAIT_MODE 0
+#endif
+#ifndef LLM_PREFETCH_PRE_PDL
+#define LLM_PREFETCH_PRE_PDL 1
+#endif
+constexpr unsigned long long WAIT_LIMIT_NS = 300ull * 1000 * 1000;      // 0.3 s: far beyond any wait inside one launch
 constexpr int N_DQ_WARPS = 16;
 constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activation producer, two MMA issuers
 
@@ -35,12 +42,30 @@ constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activatio
 // own bounded wait for a tensor-parallel peer; the pipeline behind it is legitimately stalled, so the count is held
 // meanwhile (the peer wait has its own limit and reports through the status word).
 LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 512) {
-            if (abort_flag[0]) return false;
-            if (abort_flag[1]) i = 513;
+    // try_wait parks the thread in hardware for a short, system-chosen time; after a few misses the warp also yields its
+    // issue slots (a suspend-time hint on try_wait made no measurable difference here, polling without the sleep cost
+    // the conversion-heavy formats 10 %).  The limit is a deadline on the global nanosecond timer, read every few attempts.
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+#if LLM_WAIT_MODE == 1
+        if (mbar_test_wait(bar, parity)) return true;
+        if (i >= 4096u) {
             __nanosleep(40);
+#elif LLM_WAIT_MODE == 2
+        if (mbar_test_wait(bar, parity)) return true;
+        if (i >= 8u) {
+            __nanosleep(20);
+#else
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i >= 16u) {
+            __nanosleep(40);
+#endif
+            if ((i & 63u) == 63u) {
+                if (abort_flag[0]) return false;
+                const unsigned long long now = global_timer_ns();
+                if (t0 == 0 || abort_flag[1]) t0 = now;
+                else if (now - t0 > WAIT_LIMIT_NS) break;
+            }
         }
     }
     abort_flag[0] = 1;
@@ -56,13 +81,19 @@ LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 template <int FMT, int BM> struct Cfg {
     static_assert(BM == 32, "the small-batch kernel is built for one 32-token tile");
     static constexpr int B_ATOM_BYTES = BM * 128;         // activation tile: BM tokens x 64 columns, 128B-swizzled
-    static constexpr int N_SETS = 3;                      // chunks in flight between the dequant warps and the MMA issuers
+    // Formats converted by two alternating sets of eight warps (see TWO_SETS below): each warp set owns one operand set and
+    // the raw ring has an even number of slots, so that every waiter meets each of its barriers on EVERY revolution.  A
+    // waiter that meets a barrier only every second revolution can be two phases ahead of it, and a 1-bit parity wait
+    // then passes on a stale phase (with three operand sets, or five raw slots, the alternating warp sets did exactly
+    // that: an "unspecified launch failure" of the Q8_0 kernel on a 10240 x 5120 matrix).
+    static constexpr bool TWO_SETS = (FMT == FMT_Q8_0 || FMT == FMT_IQ3_S);
+    static constexpr int N_SETS = TWO_SETS ? 2 : 3;       // chunks in flight between the dequant warps and the MMA issuers
     static constexpr int N_B_STAGES = 4 * N_SETS;         // per chunk four 64-column activation atoms
     static constexpr int RING_BYTES = N_B_STAGES * B_ATOM_BYTES;
     static constexpr int CHUNK = FmtTraits<FMT>::CHUNK;
     static constexpr int BUDGET = 218 * 1024 - RING_BYTES;
     static constexpr int RAW_SLOTS_ = BUDGET / CHUNK;
-    static constexpr int RAW_SLOTS = RAW_SLOTS_ > 8 ? 8 : RAW_SLOTS_;
+    static constexpr int RAW_SLOTS = (RAW_SLOTS_ > 8 ? 8 : RAW_SLOTS_) & ~1;
     static_assert(RAW_SLOTS >= 2, "not enough shared memory for the raw chunk ring");
     static constexpr int SMEM_BYTES = RING_BYTES + RAW_SLOTS * CHUNK + 1024;
     static constexpr int COLS_PER_WARP = BM / 4;          // epilogue: 4 column parts x 4 lane quarters
@@ -80,7 +111,6 @@ template <int FMT, int BM> struct Cfg {
     // Dequant warp organisation: formats whose conversion is light (Q8_0) or latency-heavy (IQ3_S grid lookups) run as two
     // sets of eight warps on alternate chunks (measured per-chunk period 1.59 -> 1.16 us and 2.20 -> 1.57 us); the
     // ALU-bound k-quants keep all sixteen warps on one chunk (two sets: 0.91 -> 1.10 us for Q4_K).
-    static constexpr bool TWO_SETS = (FMT == FMT_Q8_0 || FMT == FMT_IQ3_S);
     static constexpr int DQ_WARPS_PER_CHUNK = TWO_SETS ? N_DQ_WARPS / 2 : N_DQ_WARPS;
     static constexpr int N_ISSUERS = 2;
     static constexpr int ACC_PER_ISSUER = 1;
@@ -88,6 +118,8 @@ template <int FMT, int BM> struct Cfg {
     static constexpr int A_COLS_OFFSET = 2 * ACC_SET_COLS;
     static constexpr int A_CHUNK_COLS = 128;
     static constexpr int TMEM_COLS = 512;
+    // Q4_K has a conversion with the atom index at run time (one copy of the code for the four warps of a scheduler)
+    static constexpr bool RT_ATOM = (FMT == FMT_Q4_K);
     static_assert(A_COLS_OFFSET + N_SETS * A_CHUNK_COLS <= TMEM_COLS, "tensor memory map overflows");
 };
 
@@ -96,6 +128,16 @@ struct TmemSink {
     uint32_t taddr;         // lane quarter | first column of this atom in the current chunk's A region
     LLM_DEVICE void emit(int c, uint4 v) {
         asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr + c * 4), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+    // 16 values (eight packed pairs) -> 8 TMEM columns
+    LLM_DEVICE void emit16(int c, const uint32_t (&r)[8]) {
+#ifdef LLM_PROBE_SKIP_ST
+        uint32_t x = r[0] ^ r[1] ^ r[2] ^ r[3] ^ r[4] ^ r[5] ^ r[6] ^ r[7];
+        if (x == 0x12345678u) asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr + c * 8), "r"(x) : "memory");
+        return;
+#endif
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + c * 8), "r"(r[0]), "r"(r[1]),
+                     "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
     }
 };
 
@@ -152,7 +194,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
 
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
-        for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, C::DQ_WARPS_PER_CHUNK + 1); mbar_init(empty_bar + s * 8, 1); }
+        for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, C::DQ_WARPS_PER_CHUNK + 1); mbar_init(empty_bar + s * 8, C::N_ISSUERS); }
         for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
@@ -170,7 +212,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_wait();                     // everything above touched only this CTA's shared and tensor memory
+    // Everything above touched only this CTA's shared and tensor memory.  The weights are constants, so the raw-chunk producer
+    // starts filling its ring at once (under programmatic dependent launch that overlaps the tail of the previous kernel) and
+    // joins the wait only before its first wait on a ring slot; every other role waits here, before it reads activations or
+    // writes outputs and scratch.
+    if (!LLM_PREFETCH_PRE_PDL || warp != N_DQ_WARPS) pdl_wait();
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = s_abort;
     // optional timeline trace of CTA (flags >> 8): p.debug[role * 1024 + slot] = low 32 bits of the ns timer
@@ -227,13 +273,57 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         auto epilogue = [&](const Unit& u, int ui_, int cc0) -> bool {
             const int buf = ui_ & 1;
             if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 0);
+            const int c0 = part * CW;
+            // The finisher of a split tile (its first contributor) fetches the other contributors' parked partial sums BEFORE
+            // it waits for its own accumulator: they were parked long ago (the others compute their share of the tile at the
+            // start of their range), and both the counter round trip and the loads then run under the drain of this CTA's
+            // last MMAs instead of after it.  A tile of k_blocks chunks spread over CTAs of >= 1 chunk has at most MAX_C
+            // contributors in practice; more are handled one by one further down.
+            constexpr int MAX_C = 4;
+            float parked[MAX_C][CW];
+            const bool use_slots = p.partials != nullptr;
+            const int c_first = u.contributors > 1 ? it.cta_of(u.tile * k_blocks) : 0;
+            const int c_last = u.contributors > 1 ? it.cta_of(u.tile * k_blocks + k_blocks - 1) : 0;
+            const bool finisher = u.contributors > 1 && use_slots && (int)blockIdx.x == c_first;
+            if (finisher) {
+                const unsigned target = (unsigned)(N_DQ_WARPS * (u.contributors - 1));
+                int got = 1;
+                if (lane == 0) {
+                    got = 0;
+                    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                        if (ld_acquire_gpu(&p.tickets[u.tile]) >= target) { got = 1; break; }
+                        if (i > 64) { if (abort_flag[0]) break; __nanosleep(32); }
+                    }
+                    if (!got) abort_flag[0] = 1;
+                }
+                got = __shfl_sync(0xffffffffu, got, 0);
+                __syncwarp();
+                if (!got) return false;
+                // once every warp has seen the count, warp 0 puts the counter back for the next launch
+                if (lane == 0) mbar_arrive(epi_bar);
+                if (warp == 0) {
+                    if (!mbar_wait(epi_bar, epi_syncs & 1, abort_flag)) return false;
+                    if (lane == 0) p.tickets[u.tile] = 0u;
+                }
+                ++epi_syncs;
+                const int nc = c_last - c_first + 1;
+#pragma unroll
+                for (int j = 1; j < MAX_C; ++j) {
+                    const int c = c_first + j;
+                    if (j < nc) {
+                        const int c_pos = (int)(((long long)c * it.total) / it.G);
+                        const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) parked[j][i] = __ldcg(&theirs[(c0 + i) * 128 + row]);
+                    }
+                }
+            }
             if (!mbar_wait(accf_bar + buf * 8, (ui_ >> 1) & 1, abort_flag)) return false;
             if (warp == 0 && lane == 0) stamp(3, ui_ * 4 + 1);
             tc_fence_after();
             float v[CW];
-            const int c0 = part * CW;
             // issuer w worked on this unit iff the unit has a chunk of parity w
-            const bool has0 = u.nkb >= 2 || (cc0 & 1) == 0, has1 = u.nkb >= 2 || (cc0 & 1) == 1;
+            const bool has0 = true, has1 = true;      // both issuers work on every chunk (half of its K range each)
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = 0.f;
 #pragma unroll
@@ -258,12 +348,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 // slot (slot 0: the CTA's first unit, slot 1: any later one -- a CTA has at most one split unit at each end
                 // of its range) and the last arriver adds the slots up in CTA order; 4096 fp32 atomics per unit were
                 // measured to cost several microseconds when all CTAs reach their unit boundary together.
-                const bool use_slots = p.partials != nullptr;
-                if (use_slots) {
+                if (use_slots && !finisher) {
                     float* mine = p.partials + ((size_t)blockIdx.x * 2 + (ui_ > 0 ? 1 : 0)) * (128 * BM);
 #pragma unroll
                     for (int i = 0; i < CW; ++i) __stcg(&mine[(c0 + i) * 128 + row], v[i]);
-                } else {
+                } else if (!use_slots) {
 #pragma unroll
                     for (int i = 0; i < CW; ++i) {
                         const int m = c0 + i;
@@ -272,35 +361,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 }
                 if (use_slots) {
                     // The tile's first contributor finishes it: its part of the tile is the tail of its own chunk range and
-                    // therefore the last to be computed, so it hardly ever waits.  The others hand their slot to the signal
-                    // lane (in the activation producer's warp), which pays for the device-scope release (~2 us of waiting
-                    // for the stores to be acknowledged) while these warps go back to converting weights.
-                    const int c_first = it.cta_of(u.tile * k_blocks);
+                    // therefore the last to be computed (it has fetched the others' slots above).  The others hand their slot
+                    // to the signal lane (in the activation producer's warp), which pays for the device-scope release (~2 us
+                    // of waiting for the stores to be acknowledged) while these warps go back to converting weights.
                     __syncwarp();
-                    if ((int)blockIdx.x != c_first) {
+                    if (!finisher) {
                         if (lane == 0) mbar_arrive(sig_bar);
                         do_finish = false;
-                    } else {
-                        const unsigned target = (unsigned)(N_DQ_WARPS * (u.contributors - 1));
-                        int got = 1;
-                        if (lane == 0) {
-                            got = 0;
-                            for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-                                if (ld_acquire_gpu(&p.tickets[u.tile]) >= target) { got = 1; break; }
-                                if (i > 64) { if (abort_flag[0]) break; __nanosleep(32); }
-                            }
-                            if (!got) abort_flag[0] = 1;
-                        }
-                        got = __shfl_sync(0xffffffffu, got, 0);
-                        __syncwarp();
-                        if (!got) return false;
-                        // once every warp has seen the count, warp 0 puts the counter back for the next launch
-                        if (lane == 0) mbar_arrive(epi_bar);
-                        if (warp == 0) {
-                            if (!mbar_wait(epi_bar, epi_syncs & 1, abort_flag)) return false;
-                            if (lane == 0) p.tickets[u.tile] = 0u;
-                        }
-                        ++epi_syncs;
                     }
                 } else {
                 __threadfence();
@@ -325,36 +392,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     if (!use_slots) __threadfence();
                     if (use_slots) {
                         // contributors are the CTAs that own a chunk of this tile, in order; sum in that order (own registers
-                        // at this CTA's place) so that the result does not depend on who arrived last
-                        const int c_first = it.cta_of(u.tile * k_blocks), c_last = it.cta_of(u.tile * k_blocks + k_blocks - 1);
-                        // all slots are requested before any is consumed (one L2 round trip instead of one per contributor);
-                        // a tile of k_blocks chunks spread over CTAs of >= 1 chunk has at most MAX_C contributors in practice
-                        constexpr int MAX_C = 4;
-                        float part[MAX_C][CW];
+                        // first: the finisher is the first contributor) so that the result does not depend on who arrived last
                         const int nc = c_last - c_first + 1;
-#pragma unroll
-                        for (int j = 0; j < MAX_C; ++j) {
-                            const int c = c_first + j;
-                            if (j < nc && c != (int)blockIdx.x) {
-                                const int c_pos = (int)(((long long)c * it.total) / it.G);
-                                const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
-#pragma unroll
-                                for (int i = 0; i < CW; ++i) part[j][i] = __ldcg(&theirs[(c0 + i) * 128 + row]);
-                            }
-                        }
                         float sum[CW];
 #pragma unroll
-                        for (int i = 0; i < CW; ++i) sum[i] = 0.f;
+                        for (int i = 0; i < CW; ++i) sum[i] = v[i];
 #pragma unroll
-                        for (int j = 0; j < MAX_C; ++j) {
+                        for (int j = 1; j < MAX_C; ++j) {
                             if (j >= nc) break;
-                            if (c_first + j == (int)blockIdx.x) {
 #pragma unroll
-                                for (int i = 0; i < CW; ++i) sum[i] += v[i];
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < CW; ++i) sum[i] += part[j][i];
-                            }
+                            for (int i = 0; i < CW; ++i) sum[i] += parked[j][i];
                         }
                         for (int c = c_first + MAX_C; c <= c_last; ++c) {        // more contributors than that: one by one
                             if (c == (int)blockIdx.x) {
@@ -543,10 +590,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 const int set = set_of(cc);
                 ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
                 if (warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
+                // Q4_K: the packed bytes and the prepared scales go into registers now, so that the loads and the scale
+                // arithmetic run under the wait for the operand slot instead of after it
+                [[maybe_unused]] DequantAtomQ4KRt::Regs pre;
+                if constexpr (C::RT_ATOM) {
+                    if (ok) pre = DequantAtomQ4KRt::load(raw_base + slot * C::CHUNK, g, lane, a1);
+                }
                 if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
                 if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
                 if (!ok) return;
-                publish();
                 const uint32_t raw = raw_base + slot * C::CHUNK;
                 const uint32_t a_base = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
                 if constexpr (C::TWO_SETS) {
@@ -567,6 +619,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink);
                         }
                     }
+                } else if constexpr (C::RT_ATOM) {
+                    sink.taddr = a_base + a1 * 32;
+#ifndef LLM_PROBE_SKIP_DEQUANT
+                    DequantAtomQ4KRt::convert(pre, sink);
+#endif
                 } else {
                     sink.taddr = a_base + a1 * 32;
                     switch (a1) {
@@ -576,8 +633,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
                     }
                 }
+                // Published at once.  An operand set makes a round trip per chunk (conversion -> TMEM stores complete -> full
+                // -> MMAs issued and completed -> empty) and only N_SETS chunks are in flight, so every nanosecond between the
+                // last store and the arrival on `full` lengthens the period of all roles: a per-CTA timeline with the
+                // publication deferred to the next chunk (to hide the store latency) showed both the issuers and these warps
+                // waiting on each other, 0.9 us per chunk with neither side busier than 60 %.
                 pend_set = set;
                 pend_slot = slot;
+                publish();
                 if (warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
             }
         };
@@ -601,6 +664,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
             const uint8_t* wsrc = p.w + ((size_t)u.tile * k_blocks + u.kb0) * C::CHUNK;
             for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
                 const int slot = cc % R, rphase = (cc / R) & 1;
+                if (LLM_PREFETCH_PRE_PDL && cc == R) pdl_wait();   // the first R slots start out empty: no wait, hence no time limit, before this
                 ok = mbar_wait(rawe_bar + slot * 8, rphase ^ 1, abort_flag);
                 if (!ok) break;
                 const uint8_t* src = wsrc + (size_t)c * C::CHUNK + lane * 16;
@@ -663,7 +727,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 tc_fence_after();
                 bool first = true;
                 for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
-                    if ((cc & 1) != w) continue;
                     const int set = set_of(cc);
                     ok = mbar_wait(full_bar + set * 8, sphase_of(cc), abort_flag);
                     if (w == 0) stamp(2, cc * 2);
@@ -672,11 +735,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     const uint32_t acc_base = tmem_base + buf * C::ACC_SET_COLS + w * C::ACC_PER_ISSUER * BM;
                     const uint32_t a_tmem = tmem_base + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
+                    for (int a2 = 0; a2 < 2; ++a2) {
+                        const int a = 2 * w + a2;
                         const uint64_t bdesc = smem_desc_sw128(smem_base + (set * 4 + a) * C::B_ATOM_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)      // 16 columns of K = 8 TMEM columns of A, 32 bytes of the swizzled B row
-                            mma_f16_ts(acc_base, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc, (first && a == 0 && k4 == 0) ? 0u : 1u);
+#ifndef LLM_PROBE_SKIP_MMA
+                            mma_f16_ts(acc_base, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc, (first && a2 == 0 && k4 == 0) ? 0u : 1u);
+#else
+                            ;
+#endif
                     }
                     mma_commit(empty_bar + set * 8);
                     if (w == 0) stamp(2, cc * 2 + 1);

@@ -25,8 +25,7 @@ struct Scratch {
 static __device__ __align__(256) Scratch g_scratch;
 
 struct DeviceSlot {
-    std::atomic<int> ready{0};
-    Scratch* ptr = nullptr;
+    std::atomic<Scratch*> ptr{nullptr};      // published once per device; racing first callers store the same value
 };
 DeviceSlot g_slots[kMaxDevices];
 thread_local char g_error[256] = "";
@@ -55,15 +54,22 @@ extern "C" __attribute__((visibility("default"))) int llaminar_gemv_noalloc(cons
     if (e != cudaSuccess) return fail(6, "cudaGetDevice failed: ", cudaGetErrorString(e));
     if (dev < 0 || dev >= kMaxDevices) return fail(7, "device index out of range");
     DeviceSlot& slot = g_slots[dev];
-    if (!slot.ready.load(std::memory_order_acquire)) {
-        // one-time set-up for this device, with this device current: resolve the array's device address
+    Scratch* sc = slot.ptr.load(std::memory_order_acquire);
+    if (!sc) {
+        // one-time set-up for this device, with this device current: resolve the array's device address, and check that
+        // the caller's output buffer belongs to this device (a wrong current device would otherwise pair this device's
+        // scratch with another device's buffers)
+        cudaPointerAttributes attr{};
+        e = cudaPointerGetAttributes(&attr, out);
+        if (e != cudaSuccess) return fail(11, "cudaPointerGetAttributes(out) failed: ", cudaGetErrorString(e));
+        if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
+            return fail(12, "out belongs to another device than the current one (call cudaSetDevice first)");
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_scratch);
         if (e != cudaSuccess || !p) return fail(8, "cudaGetSymbolAddress failed: ", cudaGetErrorString(e));
-        slot.ptr = static_cast<Scratch*>(p);
-        slot.ready.store(1, std::memory_order_release);
+        sc = static_cast<Scratch*>(p);
+        slot.ptr.store(sc, std::memory_order_release);
     }
-    Scratch* sc = slot.ptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // the array keeps whatever the previous call left: start this call's part from zero

@@ -25,6 +25,8 @@ extern "C" {
 //
 // * The scratch is ~1 MiB of device memory (LLAMINAR_NOALLOC_MAX_ROWS x LLAMINAR_NOALLOC_MAX_N floats plus
 //   512 counters) that every GPU loading this library holds until the process exits.
+// * Call with the device that owns w, x, out and `stream` current (cudaSetDevice): the scratch used and the launch
+//   belong to the current device, and the first call checks that `out` lives there.
 // * The first call on each device looks up the device address of that array; make that first call
 //   before any stream capture begins on the device.
 // * All calls share the one array.  Each call clears the part it uses on `stream` before the kernel runs,

@@ -440,20 +440,41 @@ cudaError_t launch_sample(const SampleParams& p, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-__global__ void penalties_kernel(float* logits, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
-                                 const int* hist_offsets, const float* presence, const float* frequency) {
-    const int row = blockIdx.x;
-    const int b = hist_offsets[row], e = hist_offsets[row + 1];
-    const float pp = presence ? presence[row] : 0.f, fp = frequency ? frequency[row] : 0.f;
-    for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
-        const int tok = hist_tokens[i];
-        if (tok >= 0 && tok < vocab) logits[(size_t)row * stride + tok] -= pp + fp * hist_counts[i];
+// Presence / frequency penalties from a dense per-lane count table: counts[lane][t] = how often token t of this rank's
+// vocabulary shard occurs in the lane's prompt + output so far (16-bit, saturating).  logits[row][t] -= presence[row] *
+// (count > 0) + frequency[row] * count.  The table lives on the device and is advanced by count_tokens_kernel right after
+// sampling, so a decode step with penalties needs nothing from the host and replays as a CUDA graph (reference:
+// cuda_apply_logit_penalties_f32, src/v2/kernels/cuda/ops/CUDASamplingKernels.cu:5410, which takes the history per call).
+__global__ void penalties_dense_kernel(float* logits, int stride, int vocab, const unsigned short* counts, int counts_stride,
+                                       const float* presence, const float* frequency) {
+    const int row = blockIdx.y;
+    const float pp = presence[row], fp = frequency[row];
+    if (pp == 0.f && fp == 0.f) return;
+    const unsigned short* c = counts + (size_t)row * counts_stride;
+    float* l = logits + (size_t)row * stride;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        const unsigned n = c[i];
+        if (n) l[i] -= pp + fp * (float)n;
     }
 }
-cudaError_t launch_penalties(float* logits, int rows, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
-                             const int* hist_offsets, const float* presence, const float* frequency, cudaStream_t st) {
+cudaError_t launch_penalties_dense(float* logits, int rows, int vocab, int stride, const unsigned short* counts, int counts_stride,
+                                   const float* presence, const float* frequency, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    penalties_kernel<<<rows, 256, 0, st>>>(logits, vocab, stride, hist_tokens, hist_counts, hist_offsets, presence, frequency);
+    penalties_dense_kernel<<<dim3(32, rows), 256, 0, st>>>(logits, stride, vocab, counts, counts_stride, presence, frequency);
+    return cudaGetLastError();
+}
+// counts[row][tokens[row] - v0] += 1 for the tokens that fall into this shard (one thread per row; rows own their table rows)
+__global__ void count_tokens_kernel(unsigned short* counts, int counts_stride, const int* tokens, int v0, int vocab, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int t = tokens[r] - v0;
+    if (t < 0 || t >= vocab) return;
+    unsigned short* c = counts + (size_t)r * counts_stride + t;
+    if (*c < 32767) *c = *c + 1;
+}
+cudaError_t launch_count_tokens(unsigned short* counts, int counts_stride, const int* tokens, int v0, int vocab, int rows, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    count_tokens_kernel<<<(rows + 63) / 64, 64, 0, st>>>(counts, counts_stride, tokens, v0, vocab, rows);
     return cudaGetLastError();
 }
 

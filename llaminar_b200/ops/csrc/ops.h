@@ -79,8 +79,9 @@ struct SampleParams {
     const int* merge_pairs = nullptr; int merge_ranks = 0, merge_k = 0;
 };
 cudaError_t launch_sample(const SampleParams& p, cudaStream_t st);
-cudaError_t launch_penalties(float* logits, int rows, int vocab, int stride, const int* hist_tokens, const int* hist_counts,
-                             const int* hist_offsets, const float* presence, const float* frequency, cudaStream_t st);
+cudaError_t launch_penalties_dense(float* logits, int rows, int vocab, int stride, const unsigned short* counts, int counts_stride,
+                                   const float* presence, const float* frequency, cudaStream_t st);
+cudaError_t launch_count_tokens(unsigned short* counts, int counts_stride, const int* tokens, int v0, int vocab, int rows, cudaStream_t st);
 // counts[0] = #NaN, counts[1] = #Inf
 cudaError_t launch_nan_scan(const void* x, size_t n, int dtype /*0 f32, 1 bf16*/, int* counts, cudaStream_t st);
 

@@ -78,6 +78,18 @@ def _planes_of(qtype: GGMLType, blocks: torch.Tensor) -> list[torch.Tensor]:
     raise NotImplementedError(qtype)
 
 
+Q4K_MAX_D = 0.5 / 63          # the small-batch GEMM multiplies d * sc by 2^129 in bf16: d * sc must stay below 0.5
+
+
+def q4k_scales_in_range(raw: torch.Tensor) -> bool:
+    """Whether every super-block scale ``d`` of a Q4_K tensor is small enough for the small-batch GEMM's conversion
+    (csrc/formats_smem.cuh: DequantAtomQ4KRt).  Real checkpoints are two orders of magnitude below the limit (it allows
+    weights up to about +-7); a tensor that is not gets re-encoded by the loader instead of silently losing range."""
+    d = raw.reshape(-1, 144)[:, :2].contiguous().view(torch.float16).float().abs()
+    d = torch.nan_to_num(d, nan=float("inf"))
+    return bool((d.max() <= Q4K_MAX_D).item()) if d.numel() else True
+
+
 def can_pack(qtype: GGMLType, k: int) -> bool:
     return qtype in FMT_IDS and k % TILE_K == 0
 

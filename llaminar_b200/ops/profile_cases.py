@@ -20,7 +20,7 @@ def _rand_weight(ops, qt, n, k, dev, seed=1):
     e, b = BLOCK_GEOMETRY[qt]
     g = torch.Generator(device=dev).manual_seed(seed)
     raw = torch.randint(0, 256, (n * k // e * b,), dtype=torch.uint8, device=dev, generator=g)
-    raw.view(torch.int16).bitwise_and_(0x3FFF)            # keep every fp16 scale field finite
+    raw.view(torch.int16).bitwise_and_(0x1FFF)            # keep every fp16 scale field finite and small (|d| < 0.0079)
     return ops.pack_matrix(raw, qt, n, k), raw.numel()
 
 
@@ -108,7 +108,7 @@ def main() -> int:
 
         def slab(n, k):
             raw = torch.randint(0, 256, (E * n * k // e_ * b_,), dtype=torch.uint8, device=dev, generator=g)
-            raw.view(torch.int16).bitwise_and_(0x3FFF)
+            raw.view(torch.int16).bitwise_and_(0x1FFF)
             return pack_experts(raw, q3, E, n, k), raw.numel()
         (gate_up, b1), (down, b2) = slab(2 * ff, d), slab(d, ff)
         h = torch.randn(T, d, device=dev, generator=g)

@@ -138,7 +138,7 @@ def main() -> int:
                 pws = []
                 for c in range(max(2, min(16, int(300e6 // wb) + 1))):       # rotate copies so that weights come from HBM
                     raw = torch.randint(0, 256, (wb,), dtype=torch.uint8, device=dev)
-                    raw.view(torch.int16).bitwise_and_(0x3FFF)
+                    raw.view(torch.int16).bitwise_and_(0x1FFF)
                     pws.append(ops.pack_matrix(raw, qt, n, k))
                 for rows in (int(r) for r in args.rows.split(",")):
                     x = torch.randn(rows, k, device=dev)

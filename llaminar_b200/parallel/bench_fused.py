@@ -73,7 +73,7 @@ def main() -> int:
             wbytes = n * k // elems * bpb
             g = torch.Generator(device=dev).manual_seed(1 + rank)
             raw = torch.randint(0, 256, (wbytes,), dtype=torch.uint8, device=dev, generator=g)
-            raw.view(torch.int16).bitwise_and_(0x3FFF)
+            raw.view(torch.int16).bitwise_and_(0x1FFF)
             pw = ops.pack_matrix(raw, qt, n, k)
             for m_total in args.ag_rows:
                 rpr = (m_total + world - 1) // world
@@ -129,7 +129,7 @@ def main() -> int:
         # clear the exponent's top bit of every 16-bit word so all scales stay finite
         pws = []
         for r in raws:
-            r.view(torch.int16).bitwise_and_(0x3FFF)
+            r.view(torch.int16).bitwise_and_(0x1FFF)
             pws.append(ops.pack_matrix(r, qt, n, k))
         for rows in args.rows:
             x = (torch.randn(rows, k, device=dev, generator=g) * 0.1).to(torch.bfloat16)

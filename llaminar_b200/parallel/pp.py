@@ -133,6 +133,7 @@ def build_pipeline_engine(weights, layout: dict, rank: int, microbatch_tokens: i
     kw = dict(kw)
     kw["max_prefill_tokens"] = microbatch_tokens
     kw.setdefault("use_graphs", False)           # point-to-point transfers stay outside CUDA graphs
+    kw.setdefault("agree_group", dist.group.WORLD)   # all stages schedule in lock step: one KV page count for everybody
     eng = LLMEngine(weights, model=model, **kw)
     eng.pp_stage, eng.pp_size = stage, pp
     return eng

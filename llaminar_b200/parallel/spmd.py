@@ -30,45 +30,66 @@ class ReplicatedEngine:
 
     def __init__(self, engine, channel: ControlChannel):
         self._e, self._ch = engine, channel
+        self._n = 0                                   # commands sent so far; the workers count the same way
+
+    def _run(self, fn):
+        """Run one replicated command locally; its outcome goes on record for the cross-rank comparison of step errors
+        (`parallel.watchdog.Heartbeat.post_step_error`)."""
+        n, self._n = self._n, self._n + 1
+        hb = getattr(self._e, "heartbeat", None)
+        try:
+            out = fn()
+        except Exception as exc:
+            if hb is not None:
+                hb.post_step_error(n, f"{type(exc).__name__}: {exc}")
+            raise
+        if hb is not None:
+            hb.note_step_ok(n)
+        return out
 
     def __getattr__(self, name):
         return getattr(self._e, name)
 
     def add_request(self, prompt, params):
         self._ch.bcast((ADD, list(prompt), params))
-        return self._e.add_request(prompt, params)
+        return self._run(lambda: self._e.add_request(prompt, params))
 
     def step(self):
         self._ch.bcast((STEP,))
         wd = getattr(self._e, "step_watchdog", None)
         if wd is None:
-            return self._e.step()
+            return self._run(self._e.step)
         with wd("engine step"):
-            return self._e.step()
+            return self._run(self._e.step)
 
     def abort(self, rid):
         self._ch.bcast((ABORT, rid))
-        return self._e.abort(rid)
+        return self._run(lambda: self._e.abort(rid))
 
     def force_token(self, rid, token):
         self._ch.bcast((FORCE, rid, token))
-        return self._e.force_token(rid, token)
+        return self._run(lambda: self._e.force_token(rid, token))
 
     def clear_cache(self):
         self._ch.bcast((CLEAR,))
-        return self._e.clear_cache()
+        return self._run(self._e.clear_cache)
 
     def shutdown_workers(self):
         self._ch.bcast((SHUTDOWN,))
 
 
 def worker_loop(engine, channel: ControlChannel) -> None:
-    """Non-root ranks: replay the commands of rank 0 until told to stop."""
+    """Non-root ranks: replay the commands of rank 0 until told to stop.  A command that raises here is put on record
+    through the heartbeat: if rank 0 raised for the same command the ranks are still in step (rank 0 fails the affected
+    requests), otherwise the monitors report this rank as failed and the process group is torn down."""
+    n = -1
+    hb = getattr(engine, "heartbeat", None)
     while True:
         cmd = channel.bcast()
         op = cmd[0]
         if op == SHUTDOWN:
             return
+        n += 1
         try:
             if op == ADD:
                 engine.add_request(cmd[1], cmd[2])
@@ -88,7 +109,10 @@ def worker_loop(engine, channel: ControlChannel) -> None:
                 engine.force_token(cmd[1], cmd[2])
             elif op == CLEAR:
                 engine.clear_cache()
-        except Exception:
-            # rank 0 hits the same error in the same call and fails the affected requests; stay in lock step
+            if hb is not None:
+                hb.note_step_ok(n)
+        except Exception as exc:
             import traceback
             traceback.print_exc()
+            if hb is not None:
+                hb.post_step_error(n, f"{type(exc).__name__}: {exc}")

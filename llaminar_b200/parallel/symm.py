@@ -21,6 +21,26 @@ ROWS_CAP = 64
 TP_MAX_RANKS = 8
 
 
+def tp_fuse_blob(*, inbox, flags, epoch_ptr: int, status_ptr: int, rank: int, size: int, rows_cap: int, n_cap: int,
+                 spin_limit: int, two_phase_min_rows: int = 0, rs=None, ag=None, flags2=None, epoch2_ptr: int = 0) -> bytes:
+    """The bytes of a `TpFuse` descriptor (ops/csrc/tp_fuse.cuh) from explicit device addresses, one list entry per rank.
+    `SymmetricArena` fills it with the peers' symmetric-memory addresses; a single-GPU test can fill it with local
+    buffers standing in for a peer that never answers."""
+    def pad(xs):
+        xs = list(xs or [])
+        return xs + [0] * (TP_MAX_RANKS - len(xs))
+    # the kernels read epoch, epoch2 and status on every call, and inbox / flags of every rank below `size`
+    if not (epoch_ptr and epoch2_ptr and status_ptr) or len(inbox) < size or len(flags) < size or not all(inbox[:size]) or not all(flags[:size]):
+        raise ValueError("TpFuse descriptor with a null pointer the kernels dereference (epoch, epoch2, status, inbox, flags)")
+    if two_phase_min_rows > 0 and not (rs and ag and flags2 and all(rs[:size]) and all(ag[:size]) and all(flags2[:size])):
+        raise ValueError("two-phase TpFuse descriptor without its reduce-scatter / all-gather buffers")
+    # struct TpFuse { float* inbox[8]; unsigned* flags[8]; unsigned* epoch; int* status; int rank, size, rows_cap, n_cap;
+    #                 unsigned spin_limit; int two_phase_min_rows; float* rs_inbox[8]; float* ag_inbox[8]; unsigned* flags2[8];
+    #                 unsigned* epoch2; }
+    return struct.pack("<8Q8QQQiiiiIi8Q8Q8QQ", *pad(inbox), *pad(flags), epoch_ptr, status_ptr, rank, size, rows_cap, n_cap,
+                       spin_limit, two_phase_min_rows, *pad(rs), *pad(ag), *pad(flags2), epoch2_ptr)
+
+
 class SymmetricArena:
     def __init__(self, group, device, n_cap: int, rows_cap: int = ROWS_CAP, spin_limit: int | None = None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -44,21 +64,14 @@ class SymmetricArena:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.epoch = torch.zeros(2 * n_tiles, dtype=torch.int32, device=self.device)      # one-shot counters, then two-phase counters
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        pad = [0] * (TP_MAX_RANKS - self.size)
         o_inbox = 2 * self.flag_bytes
         o_rs, o_ag = o_inbox + self.inbox_bytes, o_inbox + self.inbox_bytes + self.rs_bytes
-        inbox = [p + o_inbox for p in ptrs] + pad
-        flags = ptrs + pad
-        rs = [p + o_rs for p in ptrs] + pad
-        ag = [p + o_ag for p in ptrs] + pad
-        flags2 = [p + self.flag_bytes for p in ptrs] + pad
         two_phase_min_rows = 16 if (self.size >= 4 and 128 % self.size == 0) else 0
-        # struct TpFuse { float* inbox[8]; unsigned* flags[8]; unsigned* epoch; int* status; int rank, size, rows_cap, n_cap;
-        #                 unsigned spin_limit; int two_phase_min_rows; float* rs_inbox[8]; float* ag_inbox[8]; unsigned* flags2[8];
-        #                 unsigned* epoch2; }
-        blob = struct.pack("<8Q8QQQiiiiIi8Q8Q8QQ", *inbox, *flags, self.epoch.data_ptr(), self.status.data_ptr(),
-                           self.rank, self.size, rows_cap, n_cap, spin_limit, two_phase_min_rows, *rs, *ag, *flags2,
-                           self.epoch.data_ptr() + n_tiles * 4)
+        blob = tp_fuse_blob(inbox=[p + o_inbox for p in ptrs], flags=ptrs, epoch_ptr=self.epoch.data_ptr(),
+                            status_ptr=self.status.data_ptr(), rank=self.rank, size=self.size, rows_cap=rows_cap, n_cap=n_cap,
+                            spin_limit=spin_limit, two_phase_min_rows=two_phase_min_rows, rs=[p + o_rs for p in ptrs],
+                            ag=[p + o_ag for p in ptrs], flags2=[p + self.flag_bytes for p in ptrs],
+                            epoch2_ptr=self.epoch.data_ptr() + n_tiles * 4)
         self.desc = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.device)
         dist.barrier(group=group)
 
@@ -87,6 +100,18 @@ class SymmetricArena:
         if s != 0:
             self.status.zero_()
             raise RuntimeError(f"a fused tensor-parallel kernel gave up waiting for a peer (status {s})")
+
+    def resync(self) -> None:
+        """Collective: bring the arrival counters and call counters of every rank back to zero.  After a wait that ran out
+        (or a call that one rank skipped) the ranks' epochs disagree and every later fused call would wait for arrivals
+        that were counted already or never come; all ranks call this between steps, with no fused kernel in flight."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.buf[:2 * self.flag_bytes].zero_()
+        self.epoch.zero_()
+        self.status.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
 
 
 class AllGatherArena:

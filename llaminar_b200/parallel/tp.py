@@ -36,6 +36,7 @@ class TPContext:
     moe_mode: str = "expert-parallel"   # --moe-expert-mode: expert-parallel | replicated
     skip_allreduce: bool = False        # debug switch LLAMINAR_SKIP_ALLREDUCE (isolates compute time; results are wrong)
     verify_checksums: bool = False      # debug switch LLAMINAR_VERIFY_COLLECTIVES: every rank must hold the same reduced values
+    allreduce_precision: str = "auto"   # LLAMINAR_ALLREDUCE_PRECISION: fp32 | bf16 | fp16 | auto (reference: LocalTPContext.cpp:835-989)
 
     @staticmethod
     def create(group=None, device=None, fused: bool | None = None) -> "TPContext":
@@ -45,6 +46,9 @@ class TPContext:
         ctx = TPContext(group, rank, size, device)
         ctx.skip_allreduce = debug_env().skip_allreduce
         ctx.verify_checksums = debug_env().verify_collectives
+        ctx.allreduce_precision = str(debug_env().allreduce_precision).lower()
+        if ctx.allreduce_precision not in ("auto", "fp32", "bf16", "fp16"):
+            raise ValueError(f"LLAMINAR_ALLREDUCE_PRECISION={ctx.allreduce_precision!r}: expected fp32, bf16, fp16 or auto")
         if debug_env().collective_order_check:
             from .collective_check import CollectiveOrderChecker
             ctx.order_check = CollectiveOrderChecker(None)
@@ -150,5 +154,21 @@ class TPContext:
             return
         part = model.ws_partial[:T]
         lin(x, part, scratch=model.scratch, xn=None if small else x)
-        self.all_reduce(part)
-        h += part
+        dt = self.payload_dtype(T)
+        if dt is torch.float32 or self.device.type != "cuda":
+            self.all_reduce(part)
+            h += part
+        else:
+            # reduced-precision payload: half the bytes on the wire for the bandwidth-bound prefill all-reduce; every rank
+            # receives the same reduced bits, so the residual streams stay identical
+            low = part.to(dt)
+            self.all_reduce(low)
+            h += low
+
+    def payload_dtype(self, rows: int) -> torch.dtype:
+        """Element type of the NCCL all-reduce payload for a call of ``rows`` activation rows (the policy the reference
+        sets per layer or through LLAMINAR_ALLREDUCE_PRECISION; reference: src/v2/collective/LocalTPContext.cpp:835-989)."""
+        p = self.allreduce_precision
+        if p == "auto":
+            p = "bf16" if rows > 32 else "fp32"
+        return {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[p]

@@ -48,6 +48,9 @@ class Heartbeat:
         self._seen: dict[int, tuple[int, float]] = {}
         self._thread: threading.Thread | None = None
         self.paused = False                       # test hook: stop beating without stopping the monitor
+        self._own_step_errors: dict[int, str] = {}
+        self._last_ok_step = -1
+        self._peer_step_seen: dict[int, str] = {}
 
     def _key(self, r: int, what: str) -> str:
         return f"{self.prefix}/{what}/{r}"
@@ -65,6 +68,20 @@ class Heartbeat:
 
     def post_error(self, reason: str) -> None:
         self.store.set(self._key(self.rank, "err"), reason[:2000])
+
+    def post_step_error(self, step: int, reason: str) -> None:
+        """Record that replicated command number ``step`` raised on this rank.  Ranks replay the same commands, so an
+        error that every rank raises for the same command is harmless (rank 0 fails the affected requests); one that
+        only some ranks raise leaves the engines out of step.  The monitor of every rank compares the peers' records
+        with its own (`poll_once`) and reports a rank whose record has no local counterpart as failed."""
+        self._own_step_errors[step] = reason[:200]
+        while len(self._own_step_errors) > 64:
+            self._own_step_errors.pop(next(iter(self._own_step_errors)))
+        self.store.set(self._key(self.rank, "steperr"), f"{step}|{reason[:500]}")
+
+    def note_step_ok(self, step: int) -> None:
+        """The command number ``step`` completed on this rank without an error (kept locally, nothing is sent)."""
+        self._last_ok_step = max(self._last_ok_step, step)
 
     def _write_beat(self) -> None:
         self._beat += 1
@@ -90,6 +107,17 @@ class Heartbeat:
             if err:
                 new[r] = err
                 continue
+            se = self._read(self._key(r, "steperr"))
+            if se and se != self._peer_step_seen.get(r):
+                step_s, _, why = se.partition("|")
+                step = int(step_s) if step_s.lstrip("-").isdigit() else -1
+                if step in self._own_step_errors:
+                    self._peer_step_seen[r] = se            # the same command failed here too: the ranks are still in step
+                elif step <= self._last_ok_step:
+                    self._peer_step_seen[r] = se
+                    new[r] = f"command {step} failed on rank {r} only: {why}"
+                    continue
+                # else: this rank has not run that command yet; look again at the next pass
             b = self._read(self._key(r, "beat"))
             beat = int(b) if b else 0
             last = self._seen.get(r)

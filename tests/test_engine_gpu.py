@@ -210,3 +210,22 @@ def test_logprobs_on_the_gpu_engine_are_self_consistent():
     for tok, lp, top in r.logprobs:
         assert lp <= 1e-6 and len(top) == 3 and abs(top[0][1] - lp) < 1e-5      # greedy: the likeliest token was emitted
         assert top[0][1] >= top[1][1] >= top[2][1]
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_penalties_run_inside_the_decode_graph_and_match_the_eager_path(temperature):
+    """Presence / frequency penalties no longer push a request off the captured decode step: the graph applies them from a
+    device-side count table that it advances itself.  The tokens equal the eager path's (host-side history per step), also
+    when requests finish at different times and lanes are reassigned."""
+    w = synthesize(SHAPES["tiny-qwen3"], "Q4_K_M", seed=2)
+    prompts = [_prompt(n, n) for n in (5, 70, 33, 130, 64)]
+    ps = [SamplingParams(temperature=temperature, top_k=20, top_p=0.95, seed=7 + i, presence_penalty=1.5 if i != 1 else 0.0,
+                         frequency_penalty=0.3 if i % 2 else 0.0, max_tokens=6 + 3 * i, ignore_eos=True) for i in range(5)]
+    e1 = LLMEngine(w, device="cuda", max_batch=4, max_context=256, use_graphs=True)
+    e2 = LLMEngine(w, device="cuda", max_batch=4, max_context=256, use_graphs=False)
+    o1, o2 = e1.generate(prompts, ps), e2.generate(prompts, ps)
+    assert o1 == o2
+    assert e1.stats["graph_replays"] > 0 and any(len(k) == 3 and k[2] for k in e1._graphs)
+    # the penalties matter for this model: without them the outputs differ
+    plain = [SamplingParams(temperature=temperature, top_k=20, top_p=0.95, seed=7 + i, max_tokens=6 + 3 * i, ignore_eos=True) for i in range(5)]
+    assert e2.generate(prompts, plain) != o2

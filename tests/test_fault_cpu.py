@@ -152,3 +152,118 @@ def test_server_answers_500_and_keeps_serving():
         assert st == 200 and body["choices"][0]["message"]["role"] == "assistant"
     finally:
         srv.stop()
+
+
+def test_step_errors_of_one_rank_only_are_reported_and_shared_ones_are_not():
+    """Ranks replay the same commands.  A command that raises on every rank keeps them in step; one that raises on a
+    single rank does not, and the other ranks' monitors report that rank."""
+    store = DictStore()
+    seen = []
+    a = Heartbeat(store, 0, 2, interval_s=0.05, timeout_s=10.0, on_failure=lambda r, why: seen.append((r, why)))
+    b = Heartbeat(store, 1, 2, interval_s=0.05, timeout_s=10.0)
+    a._write_beat(); b._write_beat()
+    # command 3 fails on both ranks (say, a prompt longer than the context window)
+    a.post_step_error(3, "ValueError: prompt too long")
+    b.post_step_error(3, "ValueError: prompt too long")
+    assert a.poll_once(now=1.0) == {}
+    # command 5 fails on rank 1 only; rank 0 has not finished it yet: no verdict so far
+    b.post_step_error(5, "RuntimeError: a kernel gave up a bounded wait")
+    a.note_step_ok(4)
+    assert a.poll_once(now=1.1) == {}
+    a.note_step_ok(5)
+    new = a.poll_once(now=1.2)
+    assert list(new) == [1] and "command 5 failed on rank 1 only" in new[1] and seen[0][0] == 1
+    assert a.poll_once(now=1.3) == {}                   # reported once
+
+
+def _worker_error_case(rank, world):
+    """The worker's engine raises in a step that rank 0 completes: rank 0's heartbeat monitor learns of it."""
+    import torch.distributed as dist
+    from llaminar_b200.parallel.spmd import ControlChannel, ReplicatedEngine, worker_loop
+    from llaminar_b200.parallel.watchdog import Heartbeat
+
+    class Eng:
+        def __init__(self, bad):
+            self.requests, self.bad, self.n = {}, bad, 0
+
+        def step(self):
+            self.n += 1
+            if self.bad and self.n == 2:
+                raise RuntimeError("status word set")
+            return []
+
+    failed = []
+    store = dist.distributed_c10d._get_default_store()
+    eng = Eng(bad=(rank == 1))
+    eng.heartbeat = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=30.0, on_failure=lambda r, why: failed.append((r, why))).start()
+    ch = ControlChannel()
+    if rank == 0:
+        drive = ReplicatedEngine(eng, ch)
+        for _ in range(3):
+            drive.step()
+        deadline = time.time() + 5.0
+        while not failed and time.time() < deadline:
+            time.sleep(0.05)
+        drive.shutdown_workers()
+    else:
+        worker_loop(eng, ch)
+    eng.heartbeat.stop()
+    return failed
+
+
+def test_worker_only_step_error_reaches_rank_zero():
+    out = run_ranks(_worker_error_case, 2)
+    assert out[0] and out[0][0][0] == 1 and "command 1 failed on rank 1 only" in out[0][0][1]
+    assert out[1] == []
+
+
+def _kv_pages_case(rank, world):
+    import dataclasses
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=1)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=256, tp=tp, kv_pages=40 + 7 * rank)
+    return eng.kv.n_pages, eng.kv_pages_per_rank
+
+
+def test_ranks_agree_on_the_smallest_kv_page_count():
+    out = run_ranks(_kv_pages_case, 2)
+    assert out[0] == out[1] == (40, (40, 47))
+
+
+def _shared_disk_dir_case(rank, world, path):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.prefix_cache import PrefixCache, PrefixCacheConfig
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    import torch.distributed as dist
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=1)
+    tp = TPContext.create(device="cpu")
+    greedy = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    cfg = PrefixCacheConfig(storage="tiered", vram_budget_mb=0, ram_budget_mb=0, disk_budget_mb=64, disk_dir=path, terminal_state="off")
+    pc = PrefixCache(cfg, "fp")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, tp=tp, prefix_cache=pc)
+    pc.cfg.vram_budget_mb = 0
+    g = torch.Generator().manual_seed(5)
+    ps = [torch.randint(0, 1024, (130,), generator=g).tolist() for _ in range(3)]
+    first = [eng.generate([p], greedy)[0] for p in ps]
+    again = [eng.generate([p], greedy)[0] for p in ps]          # blocks come back from this rank's own files
+    dist.barrier()
+    pc2 = PrefixCache(cfg, "fp")
+    LLMEngine(w, device="cpu", max_batch=2, max_context=512, tp=tp, prefix_cache=pc2)
+    return first == again, pc.stats()["promoted"], pc.file_prefix, len(pc2.disk)
+
+
+def test_ranks_sharing_a_disk_dir_keep_their_kv_shards_apart(tmp_path):
+    out = run_ranks(_shared_disk_dir_case, 2, str(tmp_path))
+    assert out[0][0] and out[1][0] and out[0][1] > 0 and out[1][1] > 0
+    assert out[0][2] != out[1][2]                       # one file prefix per rank
+    assert out[0][3] > 0 and out[1][3] > 0              # and a restart finds only its own files
+    import os
+    names = os.listdir(tmp_path)
+    assert all(n.startswith(out[0][2] + "_") or n.startswith(out[1][2] + "_") for n in names)

@@ -444,3 +444,53 @@ def test_moe_fused_route_gate_up_down_combine(tokens, qt_name):
         local_pairs = int(((ids >= e0) & (ids < e0 + n_local)).sum())
         assert int(counts.sum()) == local_pairs
         assert int(n_items) >= max(1, (local_pairs + 3) // 4) and int(ticket) == 0 and int(tile_tickets.sum()) == 0
+
+
+@pytest.mark.parametrize("rows", [2, 32])
+def test_fused_allreduce_wait_runs_out_and_reports(rows):
+    """The bounded wait of the fused tensor-parallel epilogue, made to run out on ONE GPU: a descriptor of two ranks whose
+    'peer' buffers are local memory that nothing ever signals.  The kernel must come back by itself with STATUS_TIMEOUT in
+    the status word, leave the residual rows alone, and the same engine-side check that runs after every step must raise
+    and reset the scratch; an ordinary call afterwards is clean."""
+    from llaminar_b200 import ops
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.parallel.symm import tp_fuse_blob
+    n, k, n_cap, rows_cap = 256, 1024, 256, 32
+    pw, wf = _weight(GGMLType.Q4_K, n, k, seed=3)
+    sc = ops.scratch_for(DEV)
+    sc.reset()
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    inbox = [z(2 * 2 * rows_cap * n_cap) for _ in range(2)]
+    flags = [z(64, dt=torch.int32) for _ in range(2)]
+    epoch, status = z(64, dt=torch.int32), z(4, dt=torch.int32)
+    blob = tp_fuse_blob(inbox=[t.data_ptr() for t in inbox], flags=[t.data_ptr() for t in flags], epoch_ptr=epoch.data_ptr(),
+                        status_ptr=status.data_ptr(), rank=0, size=2, rows_cap=rows_cap, n_cap=n_cap, spin_limit=20000,
+                        epoch2_ptr=epoch.data_ptr() + 32 * 4)
+    desc = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(DEV)
+    x = torch.randn(rows, k, device=DEV).to(torch.bfloat16)
+    h0 = torch.randn(rows, n, device=DEV)
+    h = h0.clone()
+    (ops.gemv if rows <= 4 else ops.gemm)(pw, x, h, epi=ops.EPI_RESID, scratch=sc, tp=desc)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 1                                   # STATUS_TIMEOUT
+    assert torch.equal(h, h0)                                    # no tile was added without its peer's share
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1       # this rank did signal both inboxes, once per tile
+
+    class _Model:                                                # the part of an engine that the health check reads
+        scratch = sc
+
+    class _Symm:
+        pass
+    eng = LLMEngine.__new__(LLMEngine)
+    eng.is_cuda, eng.device, eng.model = True, torch.device(DEV), _Model()
+    eng.tp = type("TP", (), {"symm": _Symm()})()
+    eng.tp.symm.status = status
+    sc.status.zero_()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        eng.check_health()
+    assert int(status[0]) == 0 and int(sc.tickets.abs().sum()) == 0 and float(sc.accum.abs().sum()) == 0.0
+    eng.check_health()                                           # nothing left to report
+    out = torch.zeros(rows, n, dtype=torch.bfloat16, device=DEV)
+    (ops.gemv if rows <= 4 else ops.gemm)(pw, x, out, scratch=sc)
+    torch.cuda.synchronize()
+    assert _rel(out.float(), x.float() @ wf.T) < 2e-2 and int(sc.status[0]) == 0

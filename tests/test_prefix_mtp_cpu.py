@@ -74,7 +74,11 @@ def test_eviction_spills_to_ram_and_disk_and_promotes(weights, tmp_path):
         assert eng.generate([p], GREEDY)[0] == r
     assert pc.stats()["promoted"] > 0
     pc2 = PrefixCache(PrefixCacheConfig(disk_budget_mb=64, disk_dir=str(tmp_path)), "fp")
+    LLMEngine(weights, device="cpu", max_batch=2, max_context=512, prefix_cache=pc2)   # the scan runs once the page geometry is known
     assert pc2.stats()["disk_blocks"] > 0           # a new process finds the persisted blocks
+    pc3 = PrefixCache(PrefixCacheConfig(disk_budget_mb=64, disk_dir=str(tmp_path)), "another model")
+    LLMEngine(weights, device="cpu", max_batch=2, max_context=512, prefix_cache=pc3)
+    assert pc3.stats()["disk_blocks"] == 0          # and nothing that another fingerprint wrote
     pc.clear()
     assert all(r <= 1 for r in eng.kv.allocator.refs)
 
@@ -194,3 +198,32 @@ def test_logprobs_under_speculative_decoding_fall_back_to_plain_steps(weights):
     assert b.output == a.output and [t for t, _, _ in b.logprobs] == b.output
     assert all(abs(x[1] - y[1]) < 1e-4 for x, y in zip(a.logprobs, b.logprobs))
     assert len(c.output) == 12 and c.logprobs == [] and eng.mtp.stats()["drafted"] > 0
+
+
+def test_lookup_keeps_its_pages_while_later_blocks_are_promoted(weights):
+    """A tight cache: promoting a block from the RAM tier must not evict (and hand back) a page that the same lookup
+    has already returned.  Every page of a lookup result is distinct and the prefix is restored bit for bit."""
+    base = LLMEngine(weights, device="cpu", max_batch=1, max_context=512)
+    g = torch.Generator().manual_seed(21)
+    p = torch.randint(0, 1024, (64 * 4 + 5,), generator=g).tolist()
+    ref = base.generate([p], GREEDY)[0]
+    pc = PrefixCache(PrefixCacheConfig(storage="tiered", vram_budget_mb=1, terminal_state="off"), "fp")
+    eng = LLMEngine(weights, device="cpu", max_batch=1, max_context=512, prefix_cache=pc, kv_pages=7)
+    assert eng.generate([p], GREEDY)[0] == ref
+    # move the two oldest blocks of the chain to the RAM tier, keep the others on the device
+    hs = chain_hashes(p, pc.salt)
+    for h in hs[:2]:
+        page = pc.device.pop(h)
+        pc._spill(h, eng.kv.export_page(page))
+        eng.kv.allocator.release(page)
+    # leave exactly one free page: promoting the second block has to evict
+    spare = [eng.kv.allocator.alloc() for _ in range(eng.kv.allocator.n_free - 1)]
+    held, covered = pc.lookup(p)
+    assert len(set(held)) == len(held) and covered == len(held) * 64
+    assert all(eng.kv.allocator.refs[pg] >= 1 for pg in held)
+    pc.release_pages(held)
+    for pg in spare:
+        eng.kv.allocator.release(pg)
+    assert eng.generate([p], GREEDY)[0] == ref
+    pc.clear()
+    assert all(r <= 1 for r in eng.kv.allocator.refs)

@@ -190,3 +190,52 @@ def test_fused_row_parallel_allreduce_4gpu_two_phase(qt_name, rows):
     _need(4)
     errs = run_ranks_gpu(_fused_kernels, 4, qt_name, rows)
     assert max(errs) < 2e-2
+
+
+def _skipped_call(rank, world):
+    """Rank 1 leaves out one fused call between steps: rank 0's bounded wait runs out and returns with a status (no rank
+    exits, nothing faults); after `resync()` the next fused call is correct on both ranks."""
+    import torch.distributed as dist
+    from llaminar_b200 import ops
+    from llaminar_b200.gguf import GGMLType, dequantize, quantize
+    from llaminar_b200.parallel.symm import SymmetricArena
+    dev = torch.device("cuda", rank)
+    arena = SymmetricArena(dist.group.WORLD, dev, n_cap=1024, spin_limit=200_000)     # a fraction of a second
+    qt = GGMLType.Q4_K
+    n, rows = 640, 8
+    g = torch.Generator(device=dev).manual_seed(1)
+    w = torch.randn(n, 1024 * world, device=dev, generator=g) * 0.05
+    x = torch.randn(rows, 1024 * world, device=dev, generator=g).to(torch.bfloat16)
+    h0 = torch.randn(rows, n, device=dev, generator=g)
+    ks = rank * 1024
+    pw = ops.pack_matrix(quantize(w[:, ks:ks + 1024].contiguous(), qt), qt, n, 1024)
+    wf = torch.cat([dequantize(quantize(w[:, r * 1024:(r + 1) * 1024].contiguous(), qt), qt, (n, 1024)) for r in range(world)], 1)
+    ref = h0 + x.float() @ wf.T
+    xs = x[:, ks:ks + 1024].contiguous()
+    sc = ops.scratch_for(dev)
+
+    def call():
+        h = h0.clone()
+        ops.gemm(pw, xs, h, epi=ops.EPI_RESID, scratch=sc, tp=arena.desc)
+        torch.cuda.synchronize()
+        return h
+    ok0 = ((call() - ref).norm() / ref.norm()).item()
+    dist.barrier()
+    timed_out = False
+    if rank == 0:                                   # rank 1 skips this call
+        h = call()
+        timed_out = int(arena.status[0]) == 1 and torch.equal(h, h0)
+    dist.barrier()
+    arena.resync()
+    sc.reset()
+    ok1 = ((call() - ref).norm() / ref.norm()).item()
+    return ok0, timed_out, ok1, int(arena.status[0])
+
+
+def test_skipped_fused_call_times_out_and_resync_recovers_2gpu(monkeypatch):
+    _need(2)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    res = run_ranks_gpu(_skipped_call, 2)
+    assert res[0][0] < 2e-2 and res[1][0] < 2e-2
+    assert res[0][1] is True                        # rank 0 gave up its wait and left the residual alone
+    assert res[0][2] < 2e-2 and res[1][2] < 2e-2 and res[0][3] == 0 and res[1][3] == 0
