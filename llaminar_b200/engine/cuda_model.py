@@ -123,6 +123,18 @@ class ForwardBatch:
         return errs
 
 
+class _HiddenRows:
+    """The hidden rows a sequence-sharded forward pass brought to every rank, indexed by their global row number (the
+    other rows of the residual stream live on their owners only)."""
+
+    def __init__(self, rows: torch.Tensor, values: torch.Tensor | None):
+        self._pos = {int(r): i for i, r in enumerate(rows.tolist())} if values is not None else {}
+        self._values = values
+
+    def __getitem__(self, row):
+        return self._values[self._pos[int(row)]]
+
+
 class QLinear:
     """A (possibly multi-part) quantised linear layer: parts may differ in block format."""
 
@@ -444,6 +456,78 @@ class CudaModel:
             self.head(xn, out, scratch=self.scratch, xn=xn)
         return out
 
+    # -- sequence-sharded tensor-parallel prefill: fused GEMM -> reduce-scatter and all-gather -> GEMM ---------------------
+    SEQ_SHARD_MIN_ROWS = 64          # per rank; below that the replicated path (small-batch kernels, fused all-reduce) is faster
+
+    def _seq_shard_arena(self, fb: ForwardBatch, T: int):
+        """The arena of the sequence-sharded path when this forward call can take it, else None.  It serves prefill chunks
+        of a dense model under fused tensor parallelism: every weight in a packed format, no pipeline input, no debug taps,
+        no consumer of the full hidden state (the engine turns ``seq_shard`` off when a NextN head needs all rows)."""
+        tp = self.tp
+        if (tp is None or tp.size == 1 or not tp.fused or not getattr(self, "seq_shard", True) or fb.is_decode or fb.embeds is not None
+                or self.cfg.is_moe or getattr(self, "taps", None) is not None or T < self.SEQ_SHARD_MIN_ROWS * tp.size
+                or self.cfg.d_model % 128 or self.cfg.d_model > 8192 or not isinstance(self.embed, PackedWeight)):
+            return None
+        if getattr(self, "_ss_ok", None) is None:
+            lins = [l for L in self.layers for l in (L.qkv, L.wo, L.gate_up, L.down)]
+            self._ss_ok = (all(isinstance(w, PackedWeight) for l in lins for w, _ in l.parts)
+                           and all(len(L.wo.parts) == 1 and len(L.down.parts) == 1 and L.gate_up.fused_swiglu for L in self.layers))
+        if not self._ss_ok:
+            return None
+        if getattr(self, "_ss_arena", None) is None:
+            from ..parallel.symm import SeqShardArena
+            rows_cap = (self.max_tokens + tp.size - 1) // tp.size
+            self._ss_arena = SeqShardArena(tp.group, self.device, rows_cap, self.cfg.d_model)
+        return self._ss_arena
+
+    def _column_parallel_gathered(self, lin: QLinear, arena, T: int, tw: int, out: torch.Tensor, epi=ops.EPI_STORE) -> None:
+        """out = gather(x) @ W_shard^T: the first part's launch pulls the rows from their owners while it multiplies; further
+        parts (another block format) read the staged copy."""
+        for i, (w, col) in enumerate(lin.parts):
+            o = out if epi == ops.EPI_SWIGLU else (out[:, col:col + w.n] if (col or w.n != out.shape[1]) else out)
+            b = lin.bias[col:col + w.n] if lin.bias is not None else None
+            if i == 0:
+                arena.ag.gemm(w, T, tw, o, epi=epi, bias=b)
+            else:
+                ops.gemm(w, arena.ag.gathered(T, lin.k), o, epi=epi, bias=b, scratch=self.scratch)
+
+    def _forward_seq_sharded(self, arena, fb: ForwardBatch, kv: PagedKVCache, T: int, logits_out, want_logits: bool, kv_layer_offset: int):
+        c, tp = self.cfg, self.tp
+        tw = arena.rows_per_rank(T)
+        r0, mine = arena.my_rows(T, tw)
+        h = self.ws_h[:mine]                                   # this rank's rows of the residual stream
+        if mine:
+            self.embed_tokens(fb.tokens[r0:r0 + mine], h)
+            ops.rmsnorm(h, self.layers[0].attn_norm, arena.ag.own_rows(tw, c.d_model)[:mine], c.rms_eps)
+        n_layers = len(self.layers)
+        for li, L in enumerate(self.layers):
+            qkv = self.ws_qkv[:T]
+            self._column_parallel_gathered(L.qkv, arena, T, tw, qkv)
+            o = self._attention(L, fb, kv.layers[kv_layer_offset + li], T)
+            arena.gemm_reduce_scatter(L.wo.parts[0][0], o, tw)
+            arena.reduce_norm(h, T, tw, c.d_model, L.ffn_norm, arena.ag.own_rows(tw, c.d_model)[:mine] if mine else None, c.rms_eps)
+            act = self.ws_act[:T, :self.ff_local]
+            self._column_parallel_gathered(L.gate_up, arena, T, tw, act, epi=ops.EPI_SWIGLU)
+            arena.gemm_reduce_scatter(L.down.parts[0][0], act, tw)
+            nxt = self.layers[li + 1].attn_norm if li + 1 < n_layers else None
+            arena.reduce_norm(h, T, tw, c.d_model, nxt, (arena.ag.own_rows(tw, c.d_model)[:mine] if mine else None) if nxt is not None else None,
+                              c.rms_eps)
+            tp.stats["fused_calls"] += 4
+        # the rows that get logits (and whose hidden state the caller keeps) are brought to every rank: each is owned by
+        # one rank, the others contribute zeros to a small all-reduce
+        rows = fb.logit_rows if fb.logit_rows is not None else torch.arange(T, dtype=torch.int32, device=self.device)
+        logits, sel = None, None
+        if want_logits and rows.numel():
+            idx = rows.long() - r0
+            ok = (idx >= 0) & (idx < mine)
+            sel = torch.zeros(rows.numel(), c.d_model, dtype=torch.float32, device=self.device)
+            if mine:
+                sel[ok] = h.index_select(0, idx.clamp(0, max(mine - 1, 0)))[ok]
+            tp.all_reduce(sel)
+            if self.head is not None:
+                logits = self._final_logits(sel, logits_out, self.out_norm)
+        return logits, _HiddenRows(rows, sel)
+
     @torch.no_grad()
     def forward(self, fb: ForwardBatch, kv: PagedKVCache, logits_out: torch.Tensor | None = None,
                 want_logits: bool = True, kv_layer_offset: int = 0):
@@ -451,6 +535,9 @@ class CudaModel:
         T = fb.tokens.shape[0] if fb.embeds is None else fb.embeds.shape[0]
         assert T <= self.max_tokens, f"{T} tokens exceed the workspace ({self.max_tokens})"
         debug = self._debug_hooks()
+        arena = self._seq_shard_arena(fb, T) if debug is None else None
+        if arena is not None:
+            return self._forward_seq_sharded(arena, fb, kv, T, logits_out, want_logits, kv_layer_offset)
         if debug is not None:
             errs = fb.index_errors(self.cfg.vocab_size, kv.n_pages, self.cfg.context_length)
             if errs:

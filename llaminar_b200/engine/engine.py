@@ -118,6 +118,7 @@ class LLMEngine:
         self.mtp = mtp
         if mtp is not None:
             mtp.attach(self)
+            self.model.seq_shard = False            # the NextN head reads the hidden state of every prompt row
         self._dropped: list[StepOutput] = []       # sequences that a decode step had to end because the cache is full
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
                       "prefix_hit_tokens": 0, "graph_replays": 0, "preemptions": 0}

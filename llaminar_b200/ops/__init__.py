@@ -167,6 +167,20 @@ def gemm_allgather(pw: PackedWeight, m_total: int, out: torch.Tensor, desc: torc
     _count()
 
 
+def gemm_reduce_scatter(pw: PackedWeight, x: torch.Tensor, desc: torch.Tensor, *, status: torch.Tensor | None = None) -> None:
+    """Row-parallel GEMM whose bf16 partial tiles go straight to the owners of their rows (see RsFuse in gemm_tc.h)."""
+    ext().gemm_tc_rs(pw.data, pw.fmt, pw.n, pw.k, x, status, desc)
+    _count()
+
+
+def rs_reduce_norm(inbox_ptr: int, flags_ptr: int, target: int, world: int, rows_per_rank: int, n_cap: int, block_m: int,
+                   h: torch.Tensor, norm_w: torch.Tensor | None, xn: torch.Tensor | None, eps: float, spin_limit: int,
+                   status: torch.Tensor | None) -> None:
+    """Owner side of the fused reduce-scatter: h[row] += sum of the ranks' partial rows; xn[row] = RMSNorm(h[row]) * norm_w."""
+    ext().rs_reduce_norm(inbox_ptr, flags_ptr, target, world, rows_per_rank, n_cap, block_m, h, norm_w, xn, eps, spin_limit, status)
+    _count()
+
+
 def dequant(pw: PackedWeight, out: torch.Tensor | None = None) -> torch.Tensor:
     if out is None:
         out = torch.empty(pw.n, pw.k, dtype=torch.bfloat16, device=pw.data.device)

@@ -417,6 +417,52 @@ static void gemm_tc_allgather(const Tensor& w, int64_t fmt, int64_t n, int64_t k
     LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
 }
 
+// Row-parallel GEMM whose partial tiles are reduce-scattered to the owners of their rows inside the launch (RsFuse in gemm_tc.h).
+// `desc` is a host int64 tensor: [inbox ptr x8, flags ptr x8, world, rank, rows_per_rank, n_cap, parity, flags_per_parity].
+static void gemm_tc_rs(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, const OptTensor& status, const Tensor& desc) {
+    check_cuda(w, "w"); check_cuda(x, "x");
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "gemm_tc_rs input must be contiguous bf16");
+    TORCH_CHECK(desc.device().is_cpu() && desc.scalar_type() == torch::kInt64 && desc.numel() >= 22);
+    const int64_t* d = desc.data_ptr<int64_t>();
+    llm::GemmTcParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr()); p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.m = (int)x.size(0);
+    p.x = static_cast<const __nv_bfloat16*>(x.data_ptr());
+    p.out = nullptr; p.epi = llm::EPI_STORE; p.status = mptr<int>(status); p.ksplit = 1;
+    p.rs_on = 1;
+    for (int i = 0; i < 8; ++i) {
+        p.rs.inbox[i] = reinterpret_cast<__nv_bfloat16*>(d[i]);
+        p.rs.flags[i] = reinterpret_cast<unsigned*>(d[8 + i]);
+    }
+    p.rs.world = (int)d[16]; p.rs.rank = (int)d[17]; p.rs.rows_per_rank = (int)d[18]; p.rs.n_cap = (int)d[19];
+    p.rs.parity = (int)d[20]; p.rs.flags_per_parity = (int)d[21];
+    TORCH_CHECK(p.rs.world >= 1 && p.rs.world <= 8 && p.rs.rank >= 0 && p.rs.rank < p.rs.world, "bad reduce-scatter group");
+    TORCH_CHECK(p.m <= (int64_t)p.rs.world * p.rs.rows_per_rank, "more rows than the ranks own");
+    TORCH_CHECK(n <= p.rs.n_cap && p.rs.n_cap % 8 == 0, "inbox rows narrower than the output");
+    for (int i = 0; i < p.rs.world; ++i) TORCH_CHECK(p.rs.inbox[i] && p.rs.flags[i], "null inbox / flags pointer");
+    TORCH_CHECK((p.rs.rows_per_rank / llm::gemm_tc_rs_block_m(p.m, p.rs.rows_per_rank)) <= p.rs.flags_per_parity, "too few arrival counters");
+    LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
+}
+
+static void rs_reduce_norm(int64_t inbox_ptr, int64_t flags_ptr, int64_t target, int64_t world, int64_t rows_per_rank, int64_t n_cap,
+                           int64_t block_m, Tensor h, const OptTensor& norm_w, const OptTensor& xn, double eps, int64_t spin_limit,
+                           const OptTensor& status) {
+    check_cuda(h, "h");
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.scalar_type() == torch::kFloat32 && h.is_contiguous() && h.dim() == 2, "h must be contiguous fp32 [rows, d]");
+    TORCH_CHECK(inbox_ptr != 0 && flags_ptr != 0, "null inbox / flags pointer");
+    TORCH_CHECK(h.size(1) <= n_cap, "inbox rows narrower than h");
+    if (norm_w.has_value()) {
+        TORCH_CHECK(xn.has_value() && xn->scalar_type() == torch::kBFloat16 && xn->is_contiguous() && xn->size(0) >= h.size(0) && xn->size(1) == h.size(1));
+        TORCH_CHECK(norm_w->scalar_type() == torch::kFloat32 && norm_w->numel() == h.size(1));
+    }
+    LLM_CUDA_CHECK(llm::launch_rs_reduce_norm(reinterpret_cast<const __nv_bfloat16*>(inbox_ptr), reinterpret_cast<const unsigned*>(flags_ptr),
+                                              (unsigned)target, (int)world, (int)rows_per_rank, (int)n_cap, (int)block_m,
+                                              static_cast<float*>(h.data_ptr()), cptr<float>(norm_w),
+                                              xn.has_value() ? static_cast<__nv_bfloat16*>(xn->data_ptr()) : nullptr, (int)h.size(0), (int)h.size(1),
+                                              (float)eps, (unsigned)spin_limit, mptr<int>(status), cur_stream()));
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_pdl", [](bool on) { llm::pdl_enabled() = on; });
     m.def("gemv", &gemv);
@@ -424,6 +470,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_gemv", &moe_gemv);
     m.def("gemm_tc", &gemm_tc);
     m.def("gemm_tc_allgather", &gemm_tc_allgather);
+    m.def("gemm_tc_rs", &gemm_tc_rs);
+    m.def("rs_reduce_norm", &rs_reduce_norm);
+    m.def("gemm_tc_rs_block_m", [](int64_t m_, int64_t rows_per_rank) { return (int64_t)llm::gemm_tc_rs_block_m((int)m_, (int)rows_per_rank); });
     m.def("dequant", &dequant);
     m.def("gather_rows", &gather_rows);
     m.def("rmsnorm", &rmsnorm);

@@ -403,7 +403,56 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         }
     };
 
-    if (warp < 8 && !split && live) {
+    if (p.rs_on) {
+        // ---- fused reduce-scatter (RsFuse in gemm_tc.h): the partial tile goes to the owner of its rows ----
+        // The operand ring is idle by now (every MMA has completed), so its first BM x 272 bytes serve as the transpose
+        // buffer: each thread holds one output column for 32 tokens at a time, the wire wants 16-byte pieces of a row.
+        constexpr int PITCH = 128 * 2 + 16;                   // bytes per token row of the tile (padded against bank conflicts)
+        static_assert(BM * PITCH <= C::STAGES * C::STAGE_BYTES, "transpose buffer exceeds the operand ring");
+        const RsFuse& rs = p.rs;
+        if (warp < 8 && live) {
+            auto stash = [&](int c0, const float (&v)[32]) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t a = smem_base + (c0 + i) * PITCH + row_in_tile * 2;
+                    const __nv_bfloat16 b = __float2bfloat16(v[i]);
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"(*reinterpret_cast<const unsigned short*>(&b)) : "memory");
+                }
+            };
+            if (n_it > 0) {
+                for_each_load([&](int c0, const uint32_t (&r)[32]) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    stash(c0, v);
+                });
+            } else {
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                for (int c = 0; c < LOADS; ++c) stash(half * HALF_COLS + c * 32, v);
+            }
+        }
+        if (warp < 8) asm volatile("bar.sync 1, 256;" ::: "memory");        // the eight epilogue warps only
+        const int m0 = tile_m * BM;
+        const int owner = m0 / rs.rows_per_rank;              // rows_per_rank is a multiple of BM: one owner per tile
+        if (warp < 8 && live && owner < rs.world) {
+            __nv_bfloat16* dst0 = rs.inbox[owner] + ((size_t)(rs.parity * rs.world + rs.rank) * rs.rows_per_rank + (m0 - owner * rs.rows_per_rank)) * rs.n_cap
+                                  + (size_t)tile_n * 128;
+            const int cols_ok = min(128, p.n - tile_n * 128);  // d_model is a multiple of 8
+            for (int u = tid; u < BM * 16; u += 256) {
+                const int t = u >> 4, c8 = (u & 15) * 8;
+                if (m0 + t < p.m && c8 < cols_ok) {
+                    uint4 v;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_base + t * PITCH + c8 * 2));
+                    *reinterpret_cast<uint4*>(dst0 + (size_t)t * rs.n_cap + c8) = v;
+                }
+            }
+        }
+        if (warp < 8) asm volatile("bar.sync 1, 256;" ::: "memory");        // every store of the tile precedes the one release below
+        if (tid == 0 && live && owner < rs.world)
+            red_release_sys_add(rs.flags[owner] + rs.parity * rs.flags_per_parity + (m0 - owner * rs.rows_per_rank) / BM, 1u);
+    } else if (warp < 8 && !split && live) {
         if (n_it > 0) {
             for_each_load([&](int c0, const uint32_t (&r)[32]) {
                 float v[32];
@@ -418,7 +467,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
             for (int c = 0; c < LOADS; ++c) finish(half * HALF_COLS + c * 32, v);
         }
     }
-    if (split) {
+    if (split && !p.rs_on) {
         if (warp < 8 && live && n_it > 0) {
             for_each_load([&](int c0, const uint32_t (&r)[32]) {
 #pragma unroll
@@ -546,6 +595,12 @@ void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* kspli
     *ksplit = ks;
 }
 
+int gemm_tc_rs_block_m(int m, int rows_per_rank) {
+    int bm = m <= 64 ? 64 : (m <= 128 ? 128 : 256);
+    while (rows_per_rank % bm) bm >>= 1;
+    return bm;
+}
+
 template <int FMT>
 static cudaError_t launch_fmt(const GemmTcParams& p, int bm, int ks, cudaStream_t st) {
     switch (bm) {
@@ -566,8 +621,15 @@ cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
         if (p.m <= 32) bm = 64;                    // the fused all-gather lives in the large-tile kernel
         if (p.ag.world < 1 || p.ag.world > 8 || p.ag.copy_ctas < 1 || p.ag.rows_per_rank < 1) return cudaErrorInvalidValue;
     }
+    if (p.rs_on) {
+        // one owner per tile: the tile height must divide the rows every rank owns; no split-K (partials leave the GPU)
+        if (p.rs.world < 1 || p.rs.world > 8 || p.rs.rows_per_rank < 64 || p.rs.rows_per_rank % 64 || p.bias || p.n % 8) return cudaErrorInvalidValue;
+        if (bm < 64) bm = 64;
+        while (p.rs.rows_per_rank % bm) bm >>= 1;
+        ks = 1;
+    }
     if (ks > 1 && (!p.accum || !p.tickets)) ks = 1;
-    if (bm == 32) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
+    if (bm == 32 && !p.rs_on) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
     switch (p.fmt) {
         case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(p, bm, ks, st);
         case FMT_Q5_K: return launch_fmt<FMT_Q5_K>(p, bm, ks, st);

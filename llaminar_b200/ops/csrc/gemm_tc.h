@@ -25,6 +25,23 @@ struct AgFuse {
     unsigned spin_limit;
 };
 
+// Reduce-scatter fused into the epilogue of the large-tile kernel (row-parallel attention-output / FFN-down projections
+// of a prefill chunk).  The residual stream is sharded by rows between the ranks: rank o owns rows [o * rows_per_rank,
+// (o + 1) * rows_per_rank).  Every CTA converts its finished partial tile to bf16, transposes it through shared memory
+// and writes it with 16-byte stores straight into the inbox of the rank that owns those rows (peer memory over NVLink, or
+// local memory for its own rows), then bumps that rank's arrival counter for the tile's row block.  The transfers of a
+// tile overlap the main loops of the CTAs that are still computing.  The owner sums the `world` partials of its rows,
+// adds the residual and applies the next RMSNorm in `rs_reduce_norm` (ops.h), which waits (bounded) on the counters.
+// No TMA touches peer memory and nothing is multicast.  The reference runs GEMM, ncclAllReduce and the add as three
+// stages (reference: src/v2/models/qwen/QwenGraphBase.cpp:2937-3014).
+struct RsFuse {
+    __nv_bfloat16* inbox[8];   // per owner: [2 parities][world sources][rows_per_rank][n_cap] bf16 (symmetric memory)
+    unsigned* flags[8];        // per owner: [2 parities][rows_per_rank / block_m] arrival counters (symmetric memory)
+    int world, rank, rows_per_rank, n_cap;
+    int parity;                // which half of inbox / flags this call uses (call counter & 1, identical on all ranks)
+    int flags_per_parity;
+};
+
 struct GemmTcParams {
     const uint8_t* w;          // weight chunks [n_tiles][k_blocks][chunk]
     int fmt;
@@ -48,11 +65,15 @@ struct GemmTcParams {
                                // the traced CTA of the small-batch kernel
     int ag_on;                 // large-tile kernel: x rows are gathered from the ranks of `ag` inside the launch
     AgFuse ag;
+    int rs_on;                 // large-tile kernel: partial tiles go to the owners of their rows (`rs`) instead of `out`
+    RsFuse rs;
 };
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);
 // small-batch kernel (block_m 32 or 64), implemented in gemm_tc_small.cu
 cudaError_t launch_gemm_tc_small(const GemmTcParams& p, int block_m, int ksplit, cudaStream_t st);
+// tile height the launcher uses for a fused reduce-scatter launch of m rows (the owners' counters are per tile of that height)
+int gemm_tc_rs_block_m(int m, int rows_per_rank);
 // tokens per CTA tile and split factor the launcher would use (for sizing scratch)
 void gemm_tc_plan(int m, int n, int k, int ksplit_hint, int* block_m, int* ksplit);
 

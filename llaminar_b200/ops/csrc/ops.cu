@@ -49,6 +49,89 @@ cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, i
 }
 
 // ------------------------------------------------------------------------------------------------
+// Owner side of the fused reduce-scatter (RsFuse, gemm_tc.h): one CTA per row this rank owns.  It waits (bounded) until every
+// rank's partial tiles of the row's block have arrived, adds them in rank order to the fp32 residual row, writes the row back
+// and, when a norm gain is given, the bf16 RMSNorm of the new row (the input of the next column-parallel projection, placed
+// where the all-gather reads it).  Replaces the reference's all-reduce + residual add + RMSNorm stages
+// (reference: src/v2/models/qwen/QwenGraphBase.cpp:2004-2023, :2937-3014).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const __nv_bfloat16* __restrict__ inbox, const unsigned* flags, unsigned target,
+                                                             int world, int rows_per_rank, int n_cap, int block_m, float* __restrict__ h,
+                                                             const float* __restrict__ norm_w, __nv_bfloat16* __restrict__ xn, int d, float eps,
+                                                             unsigned spin_limit, int* status) {
+    __shared__ float s_part[8];
+    __shared__ int s_ok;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    if (tid == 0) {
+        const unsigned* f = flags + row / block_m;
+        int ok = 0;
+        for (unsigned i = 0; i < spin_limit; ++i) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v >= target) { ok = 1; break; }
+            if (i > 1024) __nanosleep(100);
+        }
+        if (!ok && status) atomicExch(status, (int)STATUS_TIMEOUT);
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;                                   // the row keeps its old value; the host sees the status word
+    constexpr int MAXU = 4;                              // 8-column units per thread: d <= 8192
+    float acc[MAXU][8];
+    float ss = 0.f;
+    float* hrow = h + (size_t)row * d;
+    const int units = d >> 3;
+#pragma unroll
+    for (int j = 0; j < MAXU; ++j) {
+        const int u = tid + j * 256;
+        if (u < units) {
+            const float4 a = *reinterpret_cast<const float4*>(hrow + u * 8), b = *reinterpret_cast<const float4*>(hrow + u * 8 + 4);
+            acc[j][0] = a.x; acc[j][1] = a.y; acc[j][2] = a.z; acc[j][3] = a.w;
+            acc[j][4] = b.x; acc[j][5] = b.y; acc[j][6] = b.z; acc[j][7] = b.w;
+            for (int src = 0; src < world; ++src) {
+                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(inbox + ((size_t)src * rows_per_rank + row) * n_cap + u * 8));
+                acc[j][0] += bf16_lo(v.x); acc[j][1] += bf16_hi(v.x); acc[j][2] += bf16_lo(v.y); acc[j][3] += bf16_hi(v.y);
+                acc[j][4] += bf16_lo(v.z); acc[j][5] += bf16_hi(v.z); acc[j][6] += bf16_lo(v.w); acc[j][7] += bf16_hi(v.w);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += acc[j][i] * acc[j][i];
+            *reinterpret_cast<float4*>(hrow + u * 8) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+            *reinterpret_cast<float4*>(hrow + u * 8 + 4) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+        }
+    }
+    if (norm_w == nullptr) return;
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    const float r = rsqrtf(tot / d + eps);
+    __nv_bfloat16* xrow = xn + (size_t)row * d;
+#pragma unroll
+    for (int j = 0; j < MAXU; ++j) {
+        const int u = tid + j * 256;
+        if (u < units) {
+            const float4 g0 = *reinterpret_cast<const float4*>(norm_w + u * 8), g1 = *reinterpret_cast<const float4*>(norm_w + u * 8 + 4);
+            uint4 o;
+            o.x = pack_bf16(acc[j][0] * r * g0.x, acc[j][1] * r * g0.y);
+            o.y = pack_bf16(acc[j][2] * r * g0.z, acc[j][3] * r * g0.w);
+            o.z = pack_bf16(acc[j][4] * r * g1.x, acc[j][5] * r * g1.y);
+            o.w = pack_bf16(acc[j][6] * r * g1.z, acc[j][7] * r * g1.w);
+            *reinterpret_cast<uint4*>(xrow + u * 8) = o;
+        }
+    }
+}
+cudaError_t launch_rs_reduce_norm(const __nv_bfloat16* inbox, const unsigned* flags, unsigned target, int world, int rows_per_rank, int n_cap,
+                                  int block_m, float* h, const float* norm_w, __nv_bfloat16* xn, int rows, int d, float eps,
+                                  unsigned spin_limit, int* status, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    if (d % 8 || d > 8192 || rows > rows_per_rank || block_m < 1) return cudaErrorInvalidValue;
+    rs_reduce_norm_kernel<<<rows, 256, 0, st>>>(inbox, flags, target, world, rows_per_rank, n_cap, block_m, h, norm_w, xn, d, eps, spin_limit, status);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
 // Multi-token-prediction draft prologue: out[row] = [RMSNorm(embedding[row]; enorm) | RMSNorm(hidden[row]; hnorm)] as bf16,
 // the input of the NextN layer's eh_proj (reference: src/v2/kernels/cuda/ops/CUDARowSelectKernels.cu:74 mtpConcatFP32Kernel
 // after two RMSNorm stages, src/v2/models/qwen35/Qwen35Graph.cpp:403-507).  grid = (rows, 2): y selects the half.

@@ -51,6 +51,9 @@ struct RopeKVParams {
 cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st);
 
 // h (+= delta) ; out = RMSNorm(h) * w   (fp32 residual stream, bf16 normalised output)
+cudaError_t launch_rs_reduce_norm(const __nv_bfloat16* inbox, const unsigned* flags, unsigned target, int world, int rows_per_rank, int n_cap,
+                                  int block_m, float* h, const float* norm_w, __nv_bfloat16* xn, int rows, int d, float eps,
+                                  unsigned spin_limit, int* status, cudaStream_t st);
 cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st);
 cudaError_t launch_mtp_concat_norm(const float* emb, const float* hidden, const float* enorm, const float* hnorm,
                                    __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st);

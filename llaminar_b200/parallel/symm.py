@@ -173,3 +173,89 @@ class AllGatherArena:
         if int(self.status[0]) != 0:
             self.status.zero_()
             raise RuntimeError("the fused all-gather GEMM gave up waiting for a peer's rows")
+
+
+class SeqShardArena:
+    """Buffers of the sequence-sharded tensor-parallel prefill path: fused GEMM -> reduce-scatter and all-gather -> GEMM.
+
+    Between the row-parallel projections (attention output, FFN down) and the next column-parallel ones (QKV, gate|up) the
+    residual stream is sharded by rows: rank o owns rows ``[o * Tw, (o + 1) * Tw)`` of a chunk of T rows, ``Tw`` a multiple
+    of 64.  The row-parallel GEMM pushes bf16 partial tiles into the owners' inboxes from its epilogue
+    (`ops.gemm_reduce_scatter`), the owner sums them into its fp32 residual rows and writes the next RMSNorm as bf16 into
+    the all-gather arena (`ops.rs_reduce_norm`), and the column-parallel GEMM pulls all rows from their owners while it
+    already multiplies (`AllGatherArena.gemm`).  Per layer that is two reduce-scatters and two all-gathers of bf16 rows that
+    overlap the GEMMs tile by tile, instead of two fp32 all-reduces between kernels.
+
+    Symmetric memory per rank: two parities of arrival counters and of ``[world][rows_cap][d]`` bf16 inbox rows.  A call uses
+    parity ``calls & 1``; the owner clears the counters of a parity after it has consumed them.  A rank reaches call c + 2
+    only after every peer has finished call c + 1's reduce, which is stream-ordered after that peer's reduce of call c, so
+    two parities suffice.  The reference has no counterpart (its residual stream is replicated and all-reduced:
+    src/v2/models/qwen/QwenGraphBase.cpp:2937-3014).
+    """
+
+    FLAGS_PER_PARITY = 64
+
+    def __init__(self, group, device, rows_cap: int, d: int, spin_limit: int | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from ..utils.env import debug_env
+        self.group, self.device = group, torch.device(device)
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        if self.size > TP_MAX_RANKS:
+            raise ValueError(f"fused tensor parallelism supports at most {TP_MAX_RANKS} ranks")
+        self.rows_cap = (rows_cap + 63) // 64 * 64
+        self.d = d
+        self.spin_limit = debug_env().tp_spin_limit if spin_limit is None else spin_limit
+        self.flag_bytes = 2 * self.FLAGS_PER_PARITY * 4
+        self.inbox_bytes = 2 * self.size * self.rows_cap * d * 2
+        self.buf = symm_mem.empty(self.flag_bytes + self.inbox_bytes, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.flags_view = self.buf[:self.flag_bytes].view(torch.int32).view(2, self.FLAGS_PER_PARITY)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.ag = AllGatherArena(group, device, self.rows_cap, d, spin_limit=self.spin_limit)
+        self.calls = 0
+        dist.barrier(group=group)
+
+    def rows_per_rank(self, T: int) -> int:
+        """Rows every rank owns of a chunk of T rows (a multiple of 64; the last owners may hold fewer or none)."""
+        tw = ((T + self.size - 1) // self.size + 63) // 64 * 64
+        if tw > self.rows_cap:
+            raise ValueError(f"a chunk of {T} rows needs {tw} rows per rank, the arena holds {self.rows_cap}")
+        return tw
+
+    def my_rows(self, T: int, tw: int) -> tuple[int, int]:
+        """(first global row, number of rows) this rank owns."""
+        r0 = self.rank * tw
+        return r0, max(0, min(T - r0, tw))
+
+    def gemm_reduce_scatter(self, pw, x: torch.Tensor, tw: int) -> None:
+        """Partial x @ W_shard^T of all T rows, pushed to the owners of the rows from the GEMM's epilogue."""
+        from .. import ops
+        par = self.calls & 1
+        inbox = [p + self.flag_bytes for p in self.ptrs] + [0] * (TP_MAX_RANKS - self.size)
+        flags = list(self.ptrs) + [0] * (TP_MAX_RANKS - self.size)
+        desc = torch.tensor(inbox + flags + [self.size, self.rank, tw, self.d, par, self.FLAGS_PER_PARITY], dtype=torch.int64)
+        ops.gemm_reduce_scatter(pw, x, desc, status=self.status)
+
+    def reduce_norm(self, h_local: torch.Tensor, T: int, tw: int, n_out: int, norm_w, xn_out, eps: float) -> None:
+        """h_local[row] += the ranks' partial rows of this call (rank order); xn_out[row] = RMSNorm(h_local[row]) * norm_w."""
+        from .. import ops
+        par = self.calls & 1
+        rows = h_local.shape[0]
+        if rows:
+            bm = int(ops.ext().gemm_tc_rs_block_m(T, tw))
+            n_tiles = (n_out + 127) // 128
+            inbox_ptr = self.ptrs[self.rank] + self.flag_bytes + par * self.size * tw * self.d * 2
+            flags_ptr = self.ptrs[self.rank] + par * self.FLAGS_PER_PARITY * 4
+            ops.rs_reduce_norm(inbox_ptr, flags_ptr, n_tiles * self.size, self.size, tw, self.d, bm, h_local, norm_w, xn_out, eps,
+                               self.spin_limit, self.status)
+        self.flags_view[par].zero_()          # stream-ordered after the reduce; the next writers of this parity come a call later
+        self.calls += 1
+
+    def check_status(self) -> None:
+        if int(self.status[0]) != 0:
+            self.status.zero_()
+            raise RuntimeError("a fused reduce-scatter gave up waiting for a peer's partial rows")
+        self.ag.check_status()

@@ -239,3 +239,93 @@ def test_skipped_fused_call_times_out_and_resync_recovers_2gpu(monkeypatch):
     assert res[0][0] < 2e-2 and res[1][0] < 2e-2
     assert res[0][1] is True                        # rank 0 gave up its wait and left the residual alone
     assert res[0][2] < 2e-2 and res[1][2] < 2e-2 and res[0][3] == 0 and res[1][3] == 0
+
+
+def _reduce_scatter_layer(rank, world, qt_name, T, n, k_total):
+    """Row-parallel GEMM with the reduce-scatter in its epilogue, then the owner-side reduce + residual + RMSNorm, then the
+    all-gather GEMM on the normed rows: every stage against an fp32 reference, over several calls (parities alternate)."""
+    import torch.distributed as dist
+    from llaminar_b200 import ops
+    from llaminar_b200.gguf import GGMLType, dequantize, quantize
+    from llaminar_b200.parallel.symm import SeqShardArena
+    dev = torch.device("cuda", rank)
+    qt = GGMLType[qt_name]
+    kl = k_total // world
+    arena = SeqShardArena(dist.group.WORLD, dev, rows_cap=(T + world - 1) // world, d=n)
+    g = torch.Generator(device=dev).manual_seed(5)                   # same seed: every rank can build the reference
+    w = torch.randn(n, k_total, device=dev, generator=g) * 0.05
+    w2 = torch.randn(256, n, device=dev, generator=g) * 0.05         # the next column-parallel weight (replicated here)
+    x = (torch.randn(T, k_total, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    h0 = torch.randn(T, n, device=dev, generator=g)
+    gain = torch.rand(n, device=dev, generator=g) + 0.5
+    raws = [quantize(w[:, r * kl:(r + 1) * kl].contiguous(), qt) for r in range(world)]
+    pw = ops.pack_matrix(raws[rank], qt, n, kl)
+    wq = torch.cat([dequantize(raws[r], qt, (n, kl)) for r in range(world)], 1)
+    raw2 = quantize(w2, GGMLType.Q8_0)
+    pw2 = ops.pack_matrix(raw2, GGMLType.Q8_0, 256, n)
+    w2q = dequantize(raw2, GGMLType.Q8_0, (256, n))
+    tw = arena.rows_per_rank(T)
+    r0, mine = arena.my_rows(T, tw)
+    errs = []
+    for call in range(3):
+        xs = (x.float() * (1.0 + 0.5 * call)).to(torch.bfloat16)
+        ref_h = h0 + xs.float() @ wq.T
+        ref_xn = ref_h * torch.rsqrt((ref_h * ref_h).mean(-1, keepdim=True) + 1e-6) * gain
+        h = h0[r0:r0 + mine].clone()
+        arena.gemm_reduce_scatter(pw, xs[:, rank * kl:(rank + 1) * kl].contiguous(), tw)
+        arena.reduce_norm(h, T, tw, n, gain, arena.ag.own_rows(tw, n)[:mine] if mine else None, 1e-6)
+        out = torch.zeros(T, 256, device=dev)
+        arena.ag.gemm(pw2, T, tw, out)
+        torch.cuda.synchronize()
+        arena.check_status()
+        if mine:
+            errs.append(((h - ref_h[r0:r0 + mine]).norm() / ref_h[r0:r0 + mine].norm()).item())
+        ref_out = ref_xn.to(torch.bfloat16).float() @ w2q.T
+        errs.append(((out - ref_out).norm() / ref_out.norm()).item())
+    return max(errs)
+
+
+@pytest.mark.parametrize("qt_name,T,n,k_total", [("Q4_K", 512, 1024, 2048), ("Q6_K", 300, 512, 1024), ("Q4_K", 2048, 1024, 1024)])
+def test_fused_reduce_scatter_norm_allgather_2gpu(qt_name, T, n, k_total):
+    _need(2)
+    errs = run_ranks_gpu(_reduce_scatter_layer, 2, qt_name, T, n, k_total)
+    assert max(errs) < 2e-2
+
+
+@pytest.mark.parametrize("qt_name,T,n,k_total", [("Q4_K", 640, 1024, 2048), ("Q4_K", 2048, 1024, 4096)])
+def test_fused_reduce_scatter_norm_allgather_4gpu(qt_name, T, n, k_total):
+    _need(4)
+    errs = run_ranks_gpu(_reduce_scatter_layer, 4, qt_name, T, n, k_total)
+    assert max(errs) < 2e-2
+
+
+def _engine_prefill_tokens(rank, world, fused):
+    """Prompts long enough for the sequence-sharded prefill path (fused reduce-scatter / all-gather GEMMs)."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    dev = torch.device("cuda", rank)
+    cfg = SHAPES["tiny-qwen3"].with_(d_model=1024, n_heads=8, n_kv_heads=2, head_dim=128, d_ff=2048, n_layers=2)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    tp = TPContext.create(device=dev, fused=fused)
+    eng = LLMEngine(w, device=dev, max_batch=8, max_context=1024, tp=tp, max_prefill_tokens=1024)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (400, 190, 700, 333)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    eng.check_health()
+    arena = getattr(eng.model, "_ss_arena", None)
+    if arena is not None:
+        arena.check_status()
+    return outs, dict(tp.stats), arena is not None and arena.calls > 0
+
+
+def test_engine_tp2_sequence_sharded_prefill_equals_nccl_baseline():
+    _need(2)
+    fused = run_ranks_gpu(_engine_prefill_tokens, 2, True)
+    base = run_ranks_gpu(_engine_prefill_tokens, 2, False)
+    assert fused[0][0] == fused[1][0] and base[0][0] == base[1][0]
+    assert fused[0][2] and not base[0][2]                          # the fused run went through the reduce-scatter arena
+    agree = sum(a == b for fo, bo in zip(fused[0][0], base[0][0]) for a, b in zip(fo, bo))
+    assert agree >= 0.85 * 24            # bf16 partial sums and another summation order may flip a near-tie
