@@ -93,12 +93,182 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+REF_LIB = os.path.join(REPO, "baseline", "_ref", "libllaminar_ref_kernels.so")
+
+
 def reference_arm(args):
-    # The reference is a C++23/CMake project (no setup.py / pyproject.toml, so pip cannot install it) whose
-    # build needs OpenMPI, libnuma and network FetchContent of two libraries; none exist in this image.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference is a CMake/C++ binary needing OpenMPI + libnuma + network FetchContent; "
-                      "pip install of the reference tree fails: no setup.py or pyproject.toml"}))
+    """Kernels-only reference arm.
+
+    The reference binary cannot be built in this image (its CMake build needs OpenMPI, libnuma and two libraries fetched
+    over the network), but its CUDA kernels can: `baseline/build_ref_kernels.sh` compiles the reference's own GEMM / GEMV /
+    repack translation units, unmodified, into `baseline/_ref/libllaminar_ref_kernels.so`.  This arm repacks the same
+    synthetic GGUF blocks with the reference's GPU repacker and times the reference's quantised GEMM launcher
+    (`cudaNativeVNNIPrefill_fp32`, M = batch rows, int8 activations with per-32 scales as the reference uses) on every
+    weight matrix of one decode step of the same model shape, with an NCCL all-reduce after the row-parallel projections
+    when N > 1.  Attention, normalisation, RoPE and sampling are NOT included (the reference has no batched decode path to
+    take them from), so the number is an upper bound on what a full reference step could reach.
+    """
+    if not os.path.exists(REF_LIB):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref/libllaminar_ref_kernels.so is missing (built by baseline/build_ref_kernels.sh from the "
+                          "reference's CUDA sources; the reference binary itself needs OpenMPI + libnuma + network FetchContent)"}))
+        return 0
+    import ctypes
+    import datetime
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=600))
+    from llaminar_b200.models.config import SHAPES
+    model_name = args.model or "qwen3-32b"
+    cfg = SHAPES[model_name]
+    n_layers = args.layers or cfg.n_layers
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    lib = ctypes.CDLL(REF_LIB)
+    vp, i32, f32, u8 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_uint8
+    lib.cudaPrefillContext_create.restype = vp
+    lib.cudaPrefillContext_create.argtypes = [i32]
+    lib.cudaGemvContext_create.restype = vp
+    lib.cudaGemvContext_create.argtypes = [i32]
+    lib.ref_repack_to_vnni.restype = i32
+    lib.ref_repack_to_vnni.argtypes = [i32, vp, vp, vp, vp, i32, i32, vp]
+    lib.cudaNativeVNNIPrefill_fp32.restype = ctypes.c_bool
+    lib.cudaNativeVNNIPrefill_fp32.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32, vp, vp, u8, i32, vp, vp]
+    lib.cudaNativeVNNIGemvTuned_fp32.restype = ctypes.c_bool
+    lib.cudaNativeVNNIGemvTuned_fp32.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, vp, vp, u8, i32, vp, vp, vp]
+    lib.cudaPrefillContext_bindWorkspace.argtypes = [vp, vp, ctypes.c_size_t, vp, ctypes.c_size_t]
+    lib.cudaGemvContext_bindWorkspace.argtypes = [vp, vp, ctypes.c_size_t]
+    lib.cudaNativeVNNIPrefill_getWorkspacePlan.restype = ctypes.c_bool
+    lib.cudaNativeVNNIPrefill_getWorkspacePlan.argtypes = [u8, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t),
+                                                           ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    pctx, gctx = lib.cudaPrefillContext_create(local), lib.cudaGemvContext_create(local)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    gen = torch.Generator(device=dev).manual_seed(0)
+    D, hd = cfg.d_model, cfg.head_dim
+    q_dim, kv_dim, ff = cfg.n_heads * hd // world, max(cfg.n_kv_heads // world, 1) * hd, cfg.d_ff // world
+    # (name, N, K, all-reduce after it, GGUF block bytes per 256 columns, reference repack format, reference codebook id)
+    Q4K, Q6K = (144, 5, 5), (210, 7, 8)
+    shapes = [("qkv", q_dim + 2 * kv_dim, D, False, Q4K), ("wo", D, q_dim, True, Q4K), ("gate_up", 2 * ff, D, False, Q4K),
+              ("down", D, ff, True, Q4K)]
+    head = ("head", (cfg.vocab_size + world - 1) // world, D, False, Q6K)
+
+    def make_weight(n, k, fmt):
+        blk, rfmt, cb = fmt
+        raw = torch.randint(0, 256, (n * (k // 256) * blk,), dtype=torch.uint8, device=dev, generator=gen)
+        v = raw.view(n * (k // 256), blk)
+        if blk == 144:
+            v[:, :4].view(torch.int16).bitwise_and_(0x1FFF)          # d, dmin: small finite fp16
+        else:
+            v[:, 208:210].view(torch.int16).bitwise_and_(0x1FFF)     # Q6_K: d is the last field
+        payload = torch.empty(n * k * (4 if blk == 144 else 6) // 8, dtype=torch.uint8, device=dev)
+        scales = torch.empty(n * (k // (32 if blk == 144 else 16)), dtype=torch.int16, device=dev)
+        mins = torch.empty(n * (k // 32), dtype=torch.int16, device=dev)
+        ok = lib.ref_repack_to_vnni(rfmt, raw.data_ptr(), payload.data_ptr(), scales.data_ptr(), mins.data_ptr(), n, k, stream)
+        if not ok:
+            raise RuntimeError("the reference's repack launcher refused the format")
+        torch.cuda.synchronize(dev)
+        # the reference's GEMV keeps a row-major copy of a weight in a per-weight slot: every weight gets its own
+        return payload, scales, mins, cb, (ctypes.c_void_p * 1)()
+
+    def act(m, k):
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev, generator=gen)
+        sc = torch.rand(m, k // 32, device=dev, generator=gen) * 0.01
+        sums = a.view(m, k // 32, 32).to(torch.int32).sum(-1).contiguous()
+        return a, sc, sums
+
+    try:
+        layers = [[(nm, n, k, ar, make_weight(n, k, fmt)) for nm, n, k, ar, fmt in shapes] for _ in range(n_layers)]
+        hw = make_weight(head[1], head[2], head[4])
+    except Exception as exc:                             # an unsupported format or out of memory: no number rather than a wrong one
+        print(json.dumps({"impl": "reference", "unavailable": f"reference kernels arm could not set up its weights: {exc}"}))
+        return 0
+    # the reference's runtime binds its split-K / stream-K / GEMV workspaces from its own arena: do the same from the
+    # reference's workspace plan of every shape of the step
+    need_sk, need_fix = 1 << 20, 1 << 20
+    for nm, n, k, ar, fmt in shapes + [head]:
+        a, b, c_, d_ = ctypes.c_size_t(0), ctypes.c_size_t(0), i32(0), i32(0)
+        if lib.cudaNativeVNNIPrefill_getWorkspacePlan(fmt[2], B, n, k, local, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c_), ctypes.byref(d_)):
+            need_sk, need_fix = max(need_sk, a.value), max(need_fix, b.value)
+    ws_sk = torch.zeros(need_sk + 256, dtype=torch.uint8, device=dev)
+    ws_fix = torch.zeros(need_fix + 256, dtype=torch.uint8, device=dev)
+    ws_gemv = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
+    lib.cudaPrefillContext_bindWorkspace(pctx, ws_sk.data_ptr(), ws_sk.numel(), ws_fix.data_ptr(), ws_fix.numel())
+    lib.cudaGemvContext_bindWorkspace(gctx, ws_gemv.data_ptr(), ws_gemv.numel())
+    acts = {k: act(B, k) for k in {s[2] for s in shapes}}
+    acts1 = {k: act(1, k) for k in {s[2] for s in shapes}}
+    outs = {n: torch.empty(B, n, dtype=torch.float32, device=dev) for n in {s[1] for s in shapes} | {head[1]}}
+    def gemm(m, n, k, wt, acts_):
+        payload, scales, mins, cb, slot = wt
+        a, sc, sums = acts_[k]
+        o = outs[n]
+        if m == 1:
+            ok = lib.cudaNativeVNNIGemvTuned_fp32(a.data_ptr(), payload.data_ptr(), scales.data_ptr(), mins.data_ptr(), None, o.data_ptr(),
+                                                  sc.data_ptr(), n, k, 1.0, 0.0, None, None, cb, local, stream, gctx, ctypes.cast(slot, vp))
+        else:
+            ok = lib.cudaNativeVNNIPrefill_fp32(a.data_ptr(), payload.data_ptr(), scales.data_ptr(), mins.data_ptr(), None, o.data_ptr(),
+                                                sc.data_ptr(), sums.data_ptr(), m, n, k, 1.0, 0.0, None, None, cb, local, stream, pctx)
+        if not ok:
+            raise RuntimeError(f"the reference launcher returned false for m={m} n={n} k={k} codebook={cb}")
+        return o
+
+    def step(m, acts_):
+        for L in layers:
+            for nm, n, k, ar, wt in L:
+                o = gemm(m, n, k, wt, acts_)
+                if ar and world > 1:
+                    dist.all_reduce(o[:m])
+        gemm(m, head[1], head[2], hw, acts_)
+
+    def timed(m, acts_, steps):
+        for _ in range(W):
+            step(m, acts_)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step(m, acts_)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms
+
+    try:
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        ms = timed(B, acts, K)
+        clocks = sampler.stop() if rank == 0 else {}
+        ms1 = timed(1, acts1, K)
+    except Exception as exc:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference kernels arm failed: {exc}"}))
+        return 0
+    if rank == 0:
+        wbytes = sum(w[4][0].numel() + 2 * w[4][1].numel() + 2 * w[4][2].numel() for L in layers for w in L)
+        print(json.dumps({
+            "metric": "decode_tok_s_bs32", "value": round(B * K / (ms / 1e3), 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x 4-bit (fp32 accumulate)",
+            "data": "synthetic", "impl": "reference",
+            "reference_class": "kernels-only: the reference's own NativeVNNI quantised GEMM launcher on every weight matrix of a decode step "
+                               "(+ NCCL all-reduce after the row-parallel ones); attention, norms, RoPE and sampling are not included",
+            "config": {"model": f"{model_name} (Q4_K blocks of random bytes, repacked by the reference's GPU repacker)", "global_batch": B,
+                       "seq_len": args.prompt_len or 1024, "parallelism": f"tp{world}", "layers": n_layers, "weight_bytes_per_gpu": int(wbytes),
+                       "l2": "inputs larger than L2 (every layer has its own weights)"},
+            "clocks": clocks, "extras": {"decode_bs1_tok_s": round(K / (ms1 / 1e3), 2)}}))
+        sys.stdout.flush()
+    if world > 1:
+        dist.destroy_process_group()
     return 0
 
 

@@ -197,6 +197,11 @@ class QLinear:
                 ops.gemm(w, xn if xn is not None else x, o, epi=epi, bias=b, scratch=scratch)
 
 
+def _expert_view_for_tests(pw: PackedWeight, e: int) -> PackedWeight:
+    """Expert ``e`` of a packed expert slab as a matrix of its own (tests dequantise it for their fp32 references)."""
+    return PackedWeight(pw.fmt, pw.qtype, pw.n, pw.k, pw.n_tiles, pw.k_blocks, pw.data[e])
+
+
 def _f32(t: QTensor | None, device) -> torch.Tensor | None:
     return None if t is None else t.to_float().to(device=device, dtype=torch.float32).contiguous()
 

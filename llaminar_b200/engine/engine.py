@@ -248,6 +248,8 @@ class LLMEngine:
         symm = getattr(self.tp, "symm", None) if self.tp is not None else None
         if symm is not None:
             symm.status.zero_()
+            if getattr(self.tp, "verify_checksums", False) and hasattr(symm, "check_canaries"):
+                symm.check_canaries()
         msg = f"a kernel gave up a bounded wait (status words {vals}); scratch buffers were reset"
         hb = getattr(self, "heartbeat", None)
         if hb is not None:

@@ -95,12 +95,62 @@ def moe_forward_fused(model, L, h: torch.Tensor, T: int) -> None:
         model.tp.stats["fused_calls"] += 1
 
 
+def grouped_supported(model, L, T: int) -> bool:
+    c = model.cfg
+    return (hasattr(ops, "gemm_grouped") and getattr(model, "moe_grouped", True) and c.n_experts <= 256 and c.d_model % 256 == 0
+            and c.expert_ff % 256 == 0 and L.experts.n_local >= 1)
+
+
+def moe_forward_grouped(model, L, h: torch.Tensor, T: int) -> None:
+    """Prefill-sized batches, entirely on the device: route (RMSNorm + router + top-k, one launch), sort the (token, slot)
+    pairs by expert with device-side torch ops (no host round trip), ONE grouped tensor-core GEMM for gate|up + SwiGLU and
+    one for down over all local experts, and an ordered weighted combine.  The reference's grouped prefill path does the
+    same in its count / scan / scatter kernels, per-expert grouped GEMMs and ordered weighted scatter
+    (reference: src/v2/kernels/cuda/moe/CUDAMoEKernels.cu:1242, :1537, :1707, :1826)."""
+    c, sc, dev = model.cfg, model.scratch, model.device
+    k, slab = c.n_experts_used, L.experts
+    P = T * k
+    xn = model.ws_xn[:T]
+    ids = torch.empty(T, k, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, k, dtype=torch.float32, device=dev)
+    ops.moe_route_only(h, L.ffn_norm, c.rms_eps, L.router, k, c.norm_topk_prob, ids, wts, xn)
+    _record_routing(model, L, ids)
+    flat = ids.view(-1)
+    local = (flat >= slab.e0) & (flat < slab.e0 + slab.n_local)
+    key = torch.where(local, flat - slab.e0, torch.full_like(flat, slab.n_local)).long()
+    order = torch.argsort(key, stable=True)                  # pairs of other ranks' experts sort to the end and stay unused
+    counts = torch.zeros(slab.n_local + 1, dtype=torch.int32, device=dev).index_add_(0, key, torch.ones(P, dtype=torch.int32, device=dev))
+    avg = P // max(c.n_experts, 1)
+    bm = 256 if avg >= 192 else (128 if avg >= 96 else 64)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    row_off = torch.cat([zero, torch.cumsum(counts[:slab.n_local], 0, dtype=torch.int32)])
+    tile_off = torch.cat([zero, torch.cumsum((counts[:slab.n_local] + (bm - 1)) // bm, 0, dtype=torch.int32)])
+    xg = xn.index_select(0, order // k)                      # activation rows in expert order
+    act = torch.empty(P, c.expert_ff, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(P, c.d_model, dtype=torch.float32, device=dev)
+    ops.gemm_grouped(slab.gate_up, xg, act, row_off, tile_off, bm, epi=ops.EPI_SWIGLU, scratch=sc)
+    ops.gemm_grouped(slab.down, act, y, row_off, tile_off, bm, scratch=sc)
+    pos = torch.empty(P, dtype=torch.int32, device=dev)
+    pos[order] = torch.arange(P, dtype=torch.int32, device=dev)
+    w_eff = torch.where(local.view(T, k), wts, torch.zeros_like(wts))
+    ep = model.tp is not None and model.tp.size > 1 and getattr(model.tp, "moe_mode", "expert-parallel") != "replicated"
+    target = model.ws_partial[:T] if ep else h
+    if ep:
+        target.zero_()
+    ops.moe_combine_sorted(target, y, pos, w_eff, k)
+    if ep:
+        model.tp.all_reduce(target)
+        h += target
+
+
 def moe_forward(model, L, h: torch.Tensor, T: int) -> None:
     c, sc = model.cfg, model.scratch
     dev = model.device
     k = c.n_experts_used
     if T * k <= SMALL_SLOTS * 2 and fused_supported(model, L, T):
         return moe_forward_fused(model, L, h, T)
+    if T * k > SMALL_SLOTS and grouped_supported(model, L, T):
+        return moe_forward_grouped(model, L, h, T)
     xn = model.ws_xn[:T]
     ops.rmsnorm(h, L.ffn_norm, xn, c.rms_eps)
     logits = (xn @ L.router.T).float()

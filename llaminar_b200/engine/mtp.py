@@ -215,7 +215,8 @@ class MTPDecoder:
             fbv = ForwardBatch(tokens=it(vt), positions=it(vp), seq_ids=it([i for i in range(B) for _ in range(R)]), block_table=bt,
                                cu_q=it([i * R for i in range(B + 1)]), ctx_lens=it([n0[i] - 1 for i in range(B)]), max_q_len=R)
         raw_logits, h = engine.model.forward(fbv, engine.kv)
-        logits = engine._gather_vocab(raw_logits) if k > 0 else raw_logits
+        device_verify = (k > 0 and not sampling and engine.is_cuda and engine._sharded_vocab() and B * R <= engine._pairs.shape[0])
+        logits = raw_logits if (k == 0 or device_verify) else engine._gather_vocab(raw_logits)
         h = h[:B * R].clone()
 
         # 4. accept
@@ -225,17 +226,36 @@ class MTPDecoder:
         elif sampling:
             out_tokens, n_acc = self._verify_sampling(engine, logits.view(B, R, -1), torch.stack(p_draft, 1), drafts, reqs)
         else:
-            tgt = logits.argmax(-1).view(B, R).tolist()
+            if engine.is_cuda:
+                # greedy verification on the device: per-shard argmax of the B x R target rows (8 bytes per row and rank
+                # cross the wire instead of the logits), then one kernel compares drafts and targets and writes the
+                # accepted prefix; only the counts and the tokens come back to the host
+                from .. import ops
+                tgt_dev = torch.empty(B * R, dtype=torch.int32, device=dev)
+                if engine._sharded_vocab() and B * R <= engine._pairs.shape[0]:
+                    engine._sharded_argmax(raw_logits.contiguous(), B * R, tgt_dev)
+                else:
+                    ops.argmax(logits.contiguous(), tgt_dev)
+                n_acc_dev = torch.empty(B, dtype=torch.int32, device=dev)
+                out_dev = torch.empty(B, R, dtype=torch.int32, device=dev)
+                ops.spec_verify_greedy(it(drafts).view(B, k), tgt_dev.view(B, R), n_acc_dev, out_dev)
+                acc_host, out_host, tgt = n_acc_dev.tolist(), out_dev.tolist(), tgt_dev.view(B, R).tolist()
+            else:
+                tgt = logits.argmax(-1).view(B, R).tolist()
+                acc_host = out_host = None
             out_tokens, n_acc = [], []
             for i in range(B):
-                a = 0
-                while a < k and drafts[i][a] == tgt[i][a]:
-                    a += 1
+                if acc_host is not None:
+                    a = acc_host[i]
+                else:
+                    a = 0
+                    while a < k and drafts[i][a] == tgt[i][a]:
+                        a += 1
                 if self.cfg.force_accept:
                     a = k
                     out_tokens.append(drafts[i] + [tgt[i][k]])
                 else:
-                    out_tokens.append(tgt[i][:a + 1])
+                    out_tokens.append(out_host[i][:a + 1] if out_host is not None else tgt[i][:a + 1])
                 n_acc.append(a)
         outs = []
         for i, r in enumerate(reqs):
@@ -269,6 +289,10 @@ class MTPDecoder:
 
     # -- helpers --------------------------------------------------------------------------------------------------------
     def _draft_tokens(self, engine, logits, reqs, sampling: bool, p_draft: list, j: int) -> list[int]:
+        if not sampling and engine.is_cuda and engine._sharded_vocab() and logits.shape[0] <= engine._pairs.shape[0]:
+            tok = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+            engine._sharded_argmax(logits.contiguous(), logits.shape[0], tok)      # per-shard argmax + merge: no logits gather
+            return tok.tolist()
         logits = engine._gather_vocab(logits)
         if not sampling:
             return logits.argmax(-1).tolist()

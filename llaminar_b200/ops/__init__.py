@@ -33,6 +33,12 @@ def ext():
     return mod
 
 
+def bounds_status(reset: bool = True) -> int:
+    """Status word of the bounds-check build (LLAMINAR_BOUNDS_CHECK=1): non-zero after a kernel met an index outside its
+    table (it used index 0 instead and went on).  Always 0 in the production build."""
+    return int(ext().bounds_status(bool(reset)))
+
+
 def launch_count() -> int:
     return _launches
 
@@ -122,6 +128,28 @@ MOE_ITEM_INTS = 6          # struct MoeItem { int expert, m, slot[4]; }
 def moe_route(h, norm_w, eps, router, top_k, renorm, e0, n_local, ids, wts, items, n_items, ticket, counts=None) -> None:
     """Fused RMSNorm + router projection + softmax top-k + grouped work list of the local experts."""
     ext().moe_route(h, norm_w, eps, router, top_k, bool(renorm), e0, n_local, ids, wts, items, n_items, ticket, counts)
+    _count()
+
+
+def moe_route_only(h, norm_w, eps, router, top_k, renorm, ids, wts, xn_out=None) -> None:
+    """RMSNorm + router projection + softmax top-k for any number of tokens; ``xn_out`` receives the normalised rows (bf16)."""
+    ext().moe_route_only(h, norm_w, eps, router, top_k, bool(renorm), ids, wts, xn_out)
+    _count()
+
+
+def moe_combine_sorted(h, y, pos, wts, top_k: int) -> None:
+    """h[t] += sum_s wts[t, s] * y[pos[t, s]] (slot order; zero-weight slots skipped)."""
+    ext().moe_combine_sorted(h, y, pos, wts, top_k)
+    _count()
+
+
+def gemm_grouped(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, row_off: torch.Tensor, tile_off: torch.Tensor, block_m: int, *,
+                 epi: int = EPI_STORE, scratch: Scratch | None = None) -> None:
+    """Expert GEMMs of one chunk in one launch: rows of ``x`` / ``out`` are sorted by expert, ``row_off`` / ``tile_off``
+    (device int32 [experts + 1]) give every expert's first row and first m-tile of height ``block_m``."""
+    stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
+    ext().gemm_tc_grouped(pw.data, pw.fmt, pw.n, pw.k, pw.n_experts, stride, x, out, epi, row_off, tile_off, block_m,
+                          scratch.status if scratch is not None else None)
     _count()
 
 

@@ -22,6 +22,20 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 _module = None
 
 
+def _bounds_check() -> bool:
+    from ..utils.env import debug_env
+    return bool(debug_env().bounds_check)
+
+
+def _flags() -> list[str]:
+    return NVCC_FLAGS + (["-DLLM_BOUNDS_CHECK"] if _bounds_check() else [])
+
+
+def _build_dir() -> Path:
+    """The bounds-check variant is a build of its own (other flags, other directory), selected by LLAMINAR_BOUNDS_CHECK."""
+    return BUILD_DIR.with_name("_build_bc") if _bounds_check() else BUILD_DIR
+
+
 def _existing_sources() -> list[Path]:
     return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
 
@@ -32,16 +46,16 @@ def source_hash() -> str:
         if p.suffix in (".cu", ".cuh", ".cpp", ".h", ".inc"):
             h.update(p.name.encode())
             h.update(p.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     return h.hexdigest()
 
 
 def _so_path() -> Path:
-    return BUILD_DIR / f"{NAME}.so"
+    return _build_dir() / f"{NAME}.so"
 
 
 def is_built() -> bool:
-    hp = BUILD_DIR / f"{NAME}.hash"
+    hp = _build_dir() / f"{NAME}.hash"
     return _so_path().exists() and hp.exists() and hp.read_text().strip() == source_hash()
 
 
@@ -61,23 +75,32 @@ def build(verbose: bool = False, force: bool = False):
         _module = _import_so()
         return _module
     from torch.utils import cpp_extension
-    BUILD_DIR.mkdir(exist_ok=True)
+    _build_dir().mkdir(exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(max(1, (os.cpu_count() or 2))))
     cpp_extension.load(
         name=NAME,
         sources=[str(s) for s in _existing_sources()],
-        extra_cflags=["-O2", "-std=c++17"],
-        extra_cuda_cflags=NVCC_FLAGS,
+        extra_cflags=["-O2", "-std=c++17"] + (["-DLLM_BOUNDS_CHECK"] if _bounds_check() else []),
+        extra_cuda_cflags=_flags(),
         extra_include_paths=[str(CSRC)],
-        build_directory=str(BUILD_DIR),
+        build_directory=str(_build_dir()),
         with_cuda=True,
         verbose=verbose,
         is_python_module=True,
     )
-    (BUILD_DIR / f"{NAME}.hash").write_text(source_hash())
+    (_build_dir() / f"{NAME}.hash").write_text(source_hash())
     _module = sys.modules.get(NAME) or _import_so()
     return _module
+
+
+def build_bounds_check_variant() -> None:
+    """Compile the debug variant with explicit index checks (LLAMINAR_BOUNDS_CHECK=1 loads it) in a child process: the
+    variant is chosen by the environment before the extension is first imported."""
+    import subprocess
+    env = dict(os.environ, LLAMINAR_BOUNDS_CHECK="1")
+    code = "from llaminar_b200.ops import build as b; b.build()"
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, cwd=str(Path(__file__).resolve().parents[2]))
 
 
 def load():

@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
 
     auto issue = [&](int pg, int stage) {
         if (pg < pg1) {
-            const size_t page = (size_t)btab[pg];
+            const size_t page = (size_t)LLM_CHECK_INDEX(btab[pg], p.n_pages);
             const __nv_bfloat16* kp = p.kv + ((page * 2 + 0) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)warp * 16 * D;
             const __nv_bfloat16* vp = p.kv + ((page * 2 + 1) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)warp * 16 * D;
             const uint32_t kb = wbase + stage * 2 * SM::SUB, vb = kb + SM::SUB;
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(128) paged_attn_prefill_kernel(const AttnPrefi
 
     auto issue = [&](int pg, int stage) {
         if (pg < n_pages) {
-            const size_t page = (size_t)btab[pg];
+            const size_t page = (size_t)LLM_CHECK_INDEX(btab[pg], p.n_pages);
             const __nv_bfloat16* kp = p.kv + ((page * 2 + 0) * p.n_kv_heads + kvh) * (size_t)(PAGE * D);
             const __nv_bfloat16* vp = p.kv + ((page * 2 + 1) * p.n_kv_heads + kvh) * (size_t)(PAGE * D);
             const uint32_t kb = sbase + stage * 2 * TILE, vb = kb + TILE;
@@ -446,5 +446,7 @@ cudaError_t launch_attn_prefill(const AttnPrefillParams& p, int n_seqs, int max_
     }
     return cudaGetLastError();
 }
+
+LLM_DEFINE_BOUNDS_STATUS_READER(bounds_status_attention)
 
 }  // namespace llm

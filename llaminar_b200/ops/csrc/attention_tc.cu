@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             return r;
         };
         // a page past the end repeats the last one (its keys are masked)
-        auto page_of = [&](int pg) { return (size_t)btab[min(pg, n_pages - 1)]; };
+        auto page_of = [&](int pg) { return (size_t)LLM_CHECK_INDEX(btab[min(pg, n_pages - 1)], p.n_pages); };
         auto issue_k = [&](int j) {                // K tile j -> operand buffer j & 1 (one cp.async group, also when j >= nt)
             if (j < nt) {
 #pragma unroll
@@ -394,5 +394,7 @@ cudaError_t launch_attn_prefill_tc(const AttnPrefillParams& p, int n_seqs, int m
     atc::paged_attn_prefill_tc_kernel<<<grid, atc::THREADS, atc::SMEM_BYTES, st>>>(p, status);
     return cudaGetLastError();
 }
+
+LLM_DEFINE_BOUNDS_STATUS_READER(bounds_status_attention_tc)
 
 }  // namespace llm

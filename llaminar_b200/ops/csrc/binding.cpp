@@ -83,6 +83,59 @@ static void moe_route(const Tensor& h, const Tensor& norm_w, double eps, const T
     LLM_CUDA_CHECK(llm::launch_moe_route(p, cur_stream()));
 }
 
+// Routing only (any number of tokens): RMSNorm + router + softmax top-k; optionally the normalised rows as bf16.
+static void moe_route_only(const Tensor& h, const Tensor& norm_w, double eps, const Tensor& router, int64_t top_k, bool renorm,
+                           Tensor ids, Tensor wts, const OptTensor& xn_out) {
+    check_cuda(h, "h"); check_cuda(router, "router");
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.scalar_type() == torch::kFloat32 && router.scalar_type() == torch::kBFloat16 && router.is_contiguous());
+    TORCH_CHECK(ids.scalar_type() == torch::kInt32 && wts.scalar_type() == torch::kFloat32);
+    llm::MoeRouteParams p{};
+    p.h = static_cast<const float*>(h.data_ptr()); p.h_stride = (int)h.stride(0);
+    p.norm_w = static_cast<const float*>(norm_w.data_ptr()); p.eps = (float)eps;
+    p.router = static_cast<const __nv_bfloat16*>(router.data_ptr());
+    p.tokens = (int)h.size(0); p.d = (int)router.size(1); p.n_experts = (int)router.size(0);
+    p.top_k = (int)top_k; p.renorm = renorm ? 1 : 0;
+    TORCH_CHECK(ids.numel() >= (int64_t)p.tokens * p.top_k && wts.numel() >= (int64_t)p.tokens * p.top_k);
+    p.ids = static_cast<int*>(ids.data_ptr()); p.wts = static_cast<float*>(wts.data_ptr());
+    if (xn_out.has_value()) {
+        TORCH_CHECK(xn_out->scalar_type() == torch::kBFloat16 && xn_out->is_contiguous() && xn_out->size(0) >= p.tokens && xn_out->size(1) == p.d);
+        p.xn_out = static_cast<__nv_bfloat16*>(xn_out->data_ptr());
+    }
+    LLM_CUDA_CHECK(llm::launch_moe_route(p, cur_stream()));
+}
+
+static void moe_combine_sorted(Tensor h, const Tensor& y, const Tensor& pos, const Tensor& wts, int64_t top_k) {
+    check_cuda(h, "h"); check_cuda(y, "y");
+    const c10::cuda::CUDAGuard guard(h.device());
+    TORCH_CHECK(h.scalar_type() == torch::kFloat32 && y.scalar_type() == torch::kFloat32 && y.is_contiguous() && h.stride(1) == 1);
+    TORCH_CHECK(pos.scalar_type() == torch::kInt32 && wts.scalar_type() == torch::kFloat32 && pos.is_contiguous() && wts.is_contiguous());
+    TORCH_CHECK(pos.numel() >= h.size(0) * top_k && wts.numel() >= h.size(0) * top_k && y.size(1) == h.size(1));
+    LLM_CUDA_CHECK(llm::launch_moe_combine_sorted(static_cast<float*>(h.data_ptr()), (int)h.stride(0), static_cast<const float*>(y.data_ptr()),
+                                                  static_cast<const int*>(pos.data_ptr()), static_cast<const float*>(wts.data_ptr()),
+                                                  (int)h.size(0), (int)top_k, (int)h.size(1), cur_stream()));
+}
+
+// Grouped expert GEMM on the tensor cores: rows of x / out sorted by expert (see GemmTcParams::groups in gemm_tc.h).
+static void gemm_tc_grouped(const Tensor& w, int64_t fmt, int64_t n, int64_t k, int64_t groups, int64_t w_group_stride, const Tensor& x, Tensor out,
+                            int64_t epi, const Tensor& row_off, const Tensor& tile_off, int64_t bm, const OptTensor& status) {
+    check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "grouped GEMM input must be contiguous bf16");
+    TORCH_CHECK(row_off.scalar_type() == torch::kInt32 && tile_off.scalar_type() == torch::kInt32 && row_off.is_cuda() && tile_off.is_cuda());
+    TORCH_CHECK(row_off.numel() >= groups + 1 && tile_off.numel() >= groups + 1 && groups >= 1);
+    TORCH_CHECK(epi == llm::EPI_STORE || epi == llm::EPI_SWIGLU, "grouped GEMM: store or SwiGLU epilogue");
+    llm::GemmTcParams p{};
+    p.w = static_cast<const uint8_t*>(w.data_ptr()); p.fmt = (int)fmt; p.n = (int)n; p.k = (int)k; p.m = (int)x.size(0);
+    p.x = static_cast<const __nv_bfloat16*>(x.data_ptr());
+    p.out = out.data_ptr(); p.out_stride = (int)out.stride(0); p.out_f32 = out.scalar_type() == torch::kFloat32;
+    TORCH_CHECK(out.size(0) >= x.size(0), "grouped GEMM: out has fewer rows than x");
+    p.epi = (int)epi; p.status = mptr<int>(status); p.ksplit = 1;
+    p.groups = (int)groups; p.w_group_stride = (long long)w_group_stride; p.group_bm = (int)bm;
+    p.group_row_off = static_cast<const int*>(row_off.data_ptr()); p.group_tile_off = static_cast<const int*>(tile_off.data_ptr());
+    LLM_CUDA_CHECK(llm::launch_gemm_tc(p, cur_stream()));
+}
+
 // Grouped expert GEMV over the router's work list: epi = EPI_SWIGLU (gate|up) or EPI_MOE_COMBINE (down + combine [+ all-reduce]).
 static void moe_gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, int64_t expert_stride, const Tensor& x, const OptTensor& norm_w,
                      double eps, Tensor out, int64_t epi, const Tensor& items, const Tensor& n_items, int64_t x_div, int64_t z_max,
@@ -184,6 +237,7 @@ static void rope_kv(Tensor qkv, Tensor q_out, Tensor kv, const OptTensor& q_norm
     p.block_table = static_cast<const int*>(block_table.data_ptr());
     p.n_tokens = (int)qkv.size(0); p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim;
     p.max_pages = (int)block_table.size(1); p.theta = (float)theta; p.eps = (float)eps;
+    p.n_pages = (int)kv.size(0); p.n_seqs = (int)block_table.size(0);
     LLM_CUDA_CHECK(llm::launch_rope_kv(p, cur_stream()));
 }
 
@@ -200,6 +254,7 @@ static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Ten
     p.part_o = mptr<float>(part_o); p.part_ml = mptr<float>(part_ml); p.tickets = mptr<unsigned>(tickets);
     p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim; p.max_pages = (int)block_table.size(1);
     p.rows_per_seq = (int)rows_per_seq; p.scale = (float)scale;
+    p.n_pages = (int)kv.size(0);
     if (n_splits > 1) {
         TORCH_CHECK(part_o.has_value() && part_ml.has_value() && tickets.has_value(), "split decode needs scratch");
         TORCH_CHECK(part_o->numel() >= (int64_t)batch * n_kv_heads * n_splits * 16 * head_dim, "part_o too small");
@@ -220,7 +275,7 @@ static void attn_prefill(const Tensor& q, const Tensor& kv, Tensor out, const Te
     p.block_table = static_cast<const int*>(block_table.data_ptr()); p.cu_q = static_cast<const int*>(cu_q.data_ptr());
     p.ctx_lens = static_cast<const int*>(ctx_lens.data_ptr());
     p.n_heads = (int)n_heads; p.n_kv_heads = (int)n_kv_heads; p.head_dim = (int)head_dim; p.max_pages = (int)block_table.size(1);
-    p.scale = (float)scale;
+    p.scale = (float)scale; p.n_pages = (int)kv.size(0);
     if (tensor_core) {
         TORCH_CHECK(head_dim == 128, "the tcgen05 prefill attention is built for head_dim 128");
         LLM_CUDA_CHECK(llm::launch_attn_prefill_tc(p, (int)ctx_lens.numel(), (int)max_q_len, mptr<int>(status), cur_stream()));
@@ -465,9 +520,18 @@ static void rs_reduce_norm(int64_t inbox_ptr, int64_t flags_ptr, int64_t target,
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_pdl", [](bool on) { llm::pdl_enabled() = on; });
+    m.def("bounds_status", [](bool reset) { return llm::bounds_status_ops(reset) | llm::bounds_status_attention(reset) | llm::bounds_status_attention_tc(reset); });
+#ifdef LLM_BOUNDS_CHECK
+    m.attr("bounds_check_build") = true;
+#else
+    m.attr("bounds_check_build") = false;
+#endif
     m.def("gemv", &gemv);
     m.def("moe_route", &moe_route);
     m.def("moe_gemv", &moe_gemv);
+    m.def("moe_route_only", &moe_route_only);
+    m.def("moe_combine_sorted", &moe_combine_sorted);
+    m.def("gemm_tc_grouped", &gemm_tc_grouped);
     m.def("gemm_tc", &gemm_tc);
     m.def("gemm_tc_allgather", &gemm_tc_allgather);
     m.def("gemm_tc_rs", &gemm_tc_rs);

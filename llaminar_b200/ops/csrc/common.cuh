@@ -13,7 +13,33 @@ constexpr int TILE_N = 128;   // rows per weight chunk
 constexpr int TILE_K = 256;   // columns per weight chunk
 
 // Status codes a kernel may leave in a caller-provided status word (never traps).
-enum KernelStatus : int { STATUS_OK = 0, STATUS_TIMEOUT = 1, STATUS_BAD_ARG = 2 };
+enum KernelStatus : int { STATUS_OK = 0, STATUS_TIMEOUT = 1, STATUS_BAD_ARG = 2, STATUS_BAD_INDEX = 3 };
+
+// Debug build with explicit bounds checks (-DLLM_BOUNDS_CHECK; `LLAMINAR_BOUNDS_CHECK=1` builds it into its own directory).
+// Every index that a kernel takes from a device-side table (KV page ids, block-table rows) goes through LLM_CHECK_INDEX:
+// an index outside [0, hi) raises STATUS_BAD_INDEX in the translation unit's status word and is replaced by 0, so the
+// access stays inside the allocation and the host reads the word (`ops.bounds_status()`) instead of the GPU faulting.
+// The production build compiles the macro away.
+#ifdef LLM_BOUNDS_CHECK
+static __device__ int g_bounds_status;
+__device__ __forceinline__ bool llm_index_in_range(long long v, long long hi) {
+    const bool ok = v >= 0 && v < hi;
+    if (!ok) atomicExch(&g_bounds_status, (int)STATUS_BAD_INDEX);
+    return ok;
+}
+#define LLM_CHECK_INDEX(v, hi) (llm::llm_index_in_range((long long)(v), (long long)(hi)) ? (v) : 0)
+#define LLM_DEFINE_BOUNDS_STATUS_READER(fn)                                              \
+    int fn(bool reset) {                                                                 \
+        int v = 0;                                                                       \
+        cudaMemcpyFromSymbol(&v, g_bounds_status, sizeof(int));                          \
+        if (reset && v) { const int z = 0; cudaMemcpyToSymbol(g_bounds_status, &z, sizeof(int)); } \
+        return v;                                                                        \
+    }
+#else
+#define LLM_CHECK_INDEX(v, hi) (v)
+#define LLM_DEFINE_BOUNDS_STATUS_READER(fn) \
+    int fn(bool) { return 0; }
+#endif
 
 LLM_DEVICE float warp_sum(float v) {
 #pragma unroll

@@ -204,6 +204,23 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         tile_n = lin % n_tiles_grid;
         tile_m = (lin / n_tiles_grid + (p.ag.rank * p.ag.rows_per_rank) / BM) % m_tiles;
     }
+    // grouped mode: which group and which of its m-tiles this CTA has (surplus CTAs of the over-sized grid leave at once,
+    // before any barrier or tensor-memory allocation)
+    int row_lo = 0, row_hi = p.m;
+    const uint8_t* w_base = p.w;
+    if (p.groups > 0) {
+        const int j = blockIdx.y;
+        if (j >= __ldg(p.group_tile_off + p.groups)) return;
+        int lo = 0, hi = p.groups;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (__ldg(p.group_tile_off + mid) <= j) lo = mid; else hi = mid;
+        }
+        tile_m = j - __ldg(p.group_tile_off + lo);
+        row_lo = __ldg(p.group_row_off + lo);
+        row_hi = __ldg(p.group_row_off + lo + 1);
+        w_base += (long long)lo * p.w_group_stride;
+    }
     const int k_blocks = p.k / 256;
     const int per = (k_blocks + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * per, kb1 = min(k_blocks, kb0 + per);
@@ -260,7 +277,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
     if (warp < 8) {
         // ------------------------------ dequant producers ------------------------------
         const int g = warp & 3, set = warp >> 2;
-        const uint8_t* wtile = p.w + (size_t)tile_n * k_blocks * FmtTraits<FMT>::CHUNK;
+        const uint8_t* wtile = w_base + (size_t)tile_n * k_blocks * FmtTraits<FMT>::CHUNK;
         RingSink<C::STAGES> sink{smem_base, C::STAGE_BYTES, full_bar, empty_bar, 0, g * 32 + lane, lane, abort_flag, true};
         int kb = kb0 + set;
         typename DequantBlock<FMT>::Regs regs;
@@ -298,7 +315,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
                 ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
                 if (!ok) break;
                 mbar_arrive_expect_tx(full_bar + stage * 8, C::B_ATOM_BYTES);
-                tma_load_2d(smem_base + stage * C::STAGE_BYTES + A_ATOM_BYTES, &tmap_x, kb0 * 256 + it * 64, tile_m * BM,
+                tma_load_2d(smem_base + stage * C::STAGE_BYTES + A_ATOM_BYTES, &tmap_x, kb0 * 256 + it * 64, row_lo + tile_m * BM,
                             full_bar + stage * 8);
                 trace(3, it + 1);
             }
@@ -349,7 +366,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
 
     auto finish = [&](int c0, const float (&v)[32]) {
         // v[i]: value for token m0 + c0 + i, output row n_row
-        const int m_base = tile_m * BM + c0;
+        const int m_base = row_lo + tile_m * BM + c0;
         if (p.epi == EPI_SWIGLU) {
             // rows of a 32-row group: 16 gate rows then the 16 matching up rows.  Lanes l and l + 16 hold one output
             // column; the lower lane finishes the even tokens and the upper lane the odd ones, so one exchange serves two.
@@ -361,7 +378,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
             for (int j = 0; j < 16; ++j) {
                 const float got = __shfl_xor_sync(0xffffffffu, lower ? v[2 * j + 1] : v[2 * j], 16);
                 const float gate = lower ? v[2 * j] : got, up = lower ? got : v[2 * j + 1];
-                if (col_ok && m_base + 2 * j + (lower ? 0 : 1) < p.m) o[(size_t)(2 * j) * p.out_stride] = __float2bfloat16(silu(gate) * up);
+                if (col_ok && m_base + 2 * j + (lower ? 0 : 1) < row_hi) o[(size_t)(2 * j) * p.out_stride] = __float2bfloat16(silu(gate) * up);
             }
             return;
         }
@@ -371,16 +388,16 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
             float* h = static_cast<float*>(p.out) + (size_t)m_base * p.out_stride + n_row;
             float old[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) old[i] = (m_base + i < p.m) ? h[(size_t)i * p.out_stride] : 0.f;
+            for (int i = 0; i < 32; ++i) old[i] = (m_base + i < row_hi) ? h[(size_t)i * p.out_stride] : 0.f;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-                if (m_base + i < p.m) h[(size_t)i * p.out_stride] = old[i] + v[i] + b;
+                if (m_base + i < row_hi) h[(size_t)i * p.out_stride] = old[i] + v[i] + b;
             return;
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             const int m = m_base + i;
-            if (m >= p.m) continue;
+            if (m >= row_hi) continue;
             const size_t idx = (size_t)m * p.out_stride + n_row;
             if (p.out_f32) static_cast<float*>(p.out)[idx] = v[i] + b;
             else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(v[i] + b);
@@ -562,6 +579,7 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
         attr_set = true;
     }
     dim3 grid((p.n + 127) / 128, (p.m + BM - 1) / BM, ksplit);
+    if (p.groups > 0) grid = dim3(grid.x, (p.m + BM - 1) / BM + p.groups, 1);     // at most one ragged tile per group more than m / BM
     if (p.ag_on) {                                   // per-m-tile counters of staged slices start from zero in every launch
         cudaError_t e = cudaMemsetAsync(p.ag.staged, 0, sizeof(unsigned) * grid.y, st);
         if (e != cudaSuccess) return e;
@@ -621,6 +639,12 @@ cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
         if (p.m <= 32) bm = 64;                    // the fused all-gather lives in the large-tile kernel
         if (p.ag.world < 1 || p.ag.world > 8 || p.ag.copy_ctas < 1 || p.ag.rows_per_rank < 1) return cudaErrorInvalidValue;
     }
+    if (p.groups > 0) {
+        if (p.ag_on || p.rs_on || !p.group_row_off || !p.group_tile_off || p.epi == EPI_RESID) return cudaErrorInvalidValue;
+        bm = p.group_bm;
+        if (bm != 64 && bm != 128 && bm != 256) return cudaErrorInvalidValue;
+        ks = 1;
+    }
     if (p.rs_on) {
         // one owner per tile: the tile height must divide the rows every rank owns; no split-K (partials leave the GPU)
         if (p.rs.world < 1 || p.rs.world > 8 || p.rs.rows_per_rank < 64 || p.rs.rows_per_rank % 64 || p.bias || p.n % 8) return cudaErrorInvalidValue;
@@ -629,7 +653,7 @@ cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st) {
         ks = 1;
     }
     if (ks > 1 && (!p.accum || !p.tickets)) ks = 1;
-    if (bm == 32 && !p.rs_on) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
+    if (bm == 32 && !p.rs_on && p.groups == 0) return launch_gemm_tc_small(p, bm, (p.accum && p.tickets && p.ksplit != 1) ? 0 : 1, st);
     switch (p.fmt) {
         case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(p, bm, ks, st);
         case FMT_Q5_K: return launch_fmt<FMT_Q5_K>(p, bm, ks, st);

@@ -67,6 +67,15 @@ struct GemmTcParams {
     AgFuse ag;
     int rs_on;                 // large-tile kernel: partial tiles go to the owners of their rows (`rs`) instead of `out`
     RsFuse rs;
+    // Grouped mode of the large-tile kernel (expert GEMMs of a mixture-of-experts prefill chunk): `groups` weight matrices of the
+    // same shape, `w_group_stride` bytes apart; the rows of x / out that belong to group g are [group_row_off[g],
+    // group_row_off[g + 1]) (rows sorted by expert on the device).  blockIdx.y runs over the m-tiles of all groups,
+    // group_tile_off[g] = tiles of the groups before g; the grid is sized from a host-side upper bound and surplus CTAs exit.
+    int groups;
+    const int* group_row_off;  // device [groups + 1]
+    const int* group_tile_off; // device [groups + 1]
+    long long w_group_stride;
+    int group_bm;              // tile height the offsets were computed for
 };
 
 cudaError_t launch_gemm_tc(const GemmTcParams& p, cudaStream_t st);

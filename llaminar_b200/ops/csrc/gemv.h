@@ -77,7 +77,10 @@ struct MoeRouteParams {
     int max_items;
     unsigned* ticket;          // one counter, zero between calls
     int* counts;               // optional out [n_local] pairs per local expert
+    __nv_bfloat16* xn_out;     // optional out [tokens, d]: the normalised rows as bf16 (input of the grouped expert GEMMs)
 };
+cudaError_t launch_moe_combine_sorted(float* h, int h_stride, const float* y, const int* pos, const float* wts, int tokens, int top_k, int d,
+                                      cudaStream_t st);
 cudaError_t launch_moe_route(const MoeRouteParams& p, cudaStream_t st);
 
 cudaError_t launch_dequant(int fmt, const uint8_t* w, int n, int k, __nv_bfloat16* out, cudaStream_t st);

@@ -48,7 +48,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     for (int i = tid * 4; i < p.d; i += ROUTE_THREADS * 4) {
         const float4 v = *reinterpret_cast<const float4*>(hrow + i);
         const float4 g = *reinterpret_cast<const float4*>(p.norm_w + i);
-        *reinterpret_cast<float4*>(xn + i) = make_float4(v.x * rms * g.x, v.y * rms * g.y, v.z * rms * g.z, v.w * rms * g.w);
+        const float4 o = make_float4(v.x * rms * g.x, v.y * rms * g.y, v.z * rms * g.z, v.w * rms * g.w);
+        *reinterpret_cast<float4*>(xn + i) = o;
+        if (p.xn_out) *reinterpret_cast<uint2*>(p.xn_out + (size_t)t * p.d + i) = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
     }
     __syncthreads();
 
@@ -133,6 +135,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
             p.wts[(size_t)t * p.top_k + lane] = p.renorm ? my_w / wsum : my_w;
         }
     }
+    if (p.items == nullptr) return;                                  // route-only call (prefill chunks): the caller groups on its own
     // ---- last CTA: build the grouped work list of the local experts ----
     __threadfence();
     __syncthreads();
@@ -228,12 +231,40 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const MoeRoute
     }
 }
 
+// Weighted combine of the grouped expert outputs of a prefill chunk: h[t] += sum over the token's slots of wts[t, s] *
+// y[pos[t, s]], where y holds the down-projection rows sorted by expert and pos is the inverse of that sort.  Slots with
+// a zero weight (experts of another rank) are skipped.  One CTA per token; the slots are added in slot order, so the
+// result does not depend on timing (reference: the ordered weighted scatter of its grouped prefill path,
+// src/v2/kernels/cuda/moe/CUDAMoEKernels.cu:1826).
+__global__ void __launch_bounds__(256) moe_combine_sorted_kernel(float* __restrict__ h, int h_stride, const float* __restrict__ y,
+                                                                 const int* __restrict__ pos, const float* __restrict__ wts, int top_k, int d) {
+    const int t = blockIdx.x;
+    float* hrow = h + (size_t)t * h_stride;
+    for (int i = threadIdx.x * 4; i < d; i += 256 * 4) {
+        float4 acc = *reinterpret_cast<const float4*>(hrow + i);
+        for (int s = 0; s < top_k; ++s) {
+            const float w = wts[(size_t)t * top_k + s];
+            if (w == 0.f) continue;
+            const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos[(size_t)t * top_k + s] * d + i);
+            acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        }
+        *reinterpret_cast<float4*>(hrow + i) = acc;
+    }
+}
+cudaError_t launch_moe_combine_sorted(float* h, int h_stride, const float* y, const int* pos, const float* wts, int tokens, int top_k, int d,
+                                      cudaStream_t st) {
+    if (tokens == 0) return cudaSuccess;
+    if (d % 4) return cudaErrorInvalidValue;
+    moe_combine_sorted_kernel<<<tokens, 256, 0, st>>>(h, h_stride, y, pos, wts, top_k, d);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_moe_route(const MoeRouteParams& p, cudaStream_t st) {
     if (p.tokens == 0) return cudaSuccess;
     if (p.n_experts > ROUTE_MAX_EXPERTS || p.top_k > 32 || p.n_local > ROUTE_MAX_EXPERTS || (p.d & 255) != 0 ||
-        p.tokens * p.top_k > ROUTE_MAX_PAIRS)
+        (p.items != nullptr && p.tokens * p.top_k > ROUTE_MAX_PAIRS))
         return cudaErrorInvalidValue;
-    const size_t dyn = max((size_t)(p.d + ROUTE_MAX_EXPERTS) * sizeof(float), (size_t)p.tokens * p.top_k * sizeof(int));
+    const size_t dyn = max((size_t)(p.d + ROUTE_MAX_EXPERTS) * sizeof(float), p.items ? (size_t)p.tokens * p.top_k * sizeof(int) : (size_t)0);
     if (dyn > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
     return launch_pdl(moe_route_kernel, dim3(p.tokens), dim3(ROUTE_THREADS), dyn, st, p);
 }

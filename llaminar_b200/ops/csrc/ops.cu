@@ -42,6 +42,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
     }
 }
 
+LLM_DEFINE_BOUNDS_STATUS_READER(bounds_status_ops)
+
 cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
     if (d % 4) return cudaErrorInvalidValue;
@@ -222,8 +224,9 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKVParams p) {
         dst = p.q_out + ((size_t)t * p.n_heads + hh) * D;
     } else {
         const int kvh = is_k ? hh - p.n_heads : hh - p.n_heads - p.n_kv_heads;
-        const int seq = p.seq_ids[t];
-        const size_t page = (size_t)p.block_table[(size_t)seq * p.max_pages + pos / PAGE];
+        const int seq = LLM_CHECK_INDEX(p.seq_ids[t], p.n_seqs);
+        const int slot = LLM_CHECK_INDEX(pos / PAGE, p.max_pages);
+        const size_t page = (size_t)LLM_CHECK_INDEX(p.block_table[(size_t)seq * p.max_pages + slot], p.n_pages);
         dst = p.kv + ((page * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)(pos % PAGE) * D;
     }
 #pragma unroll

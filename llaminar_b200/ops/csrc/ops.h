@@ -17,6 +17,7 @@ struct AttnDecodeParams {
     unsigned* tickets;             // [batch * n_kv_heads], zero between calls
     int n_heads, n_kv_heads, head_dim, max_pages, rows_per_seq;
     float scale;
+    int n_pages;                   // pages of the cache (bounds-check build)
 };
 
 struct AttnPrefillParams {
@@ -28,6 +29,7 @@ struct AttnPrefillParams {
     const int* ctx_lens;           // [n_seqs] tokens already cached before this chunk
     int n_heads, n_kv_heads, head_dim, max_pages;
     float scale;
+    int n_pages;                   // pages of the cache (bounds-check build)
 };
 
 int attn_decode_pick_splits(int batch, int n_kv_heads, int max_pages_in_use);
@@ -47,7 +49,12 @@ struct RopeKVParams {
     const int* block_table;        // [n_seqs, max_pages]
     int n_tokens, n_heads, n_kv_heads, head_dim, max_pages;
     float theta, eps;
+    int n_pages, n_seqs;           // pages of the cache, rows of block_table (bounds-check build)
 };
+// status word of the bounds-check build, per translation unit (0 in the production build)
+int bounds_status_ops(bool reset);
+int bounds_status_attention(bool reset);
+int bounds_status_attention_tc(bool reset);
 cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st);
 
 // h (+= delta) ; out = RMSNorm(h) * w   (fp32 residual stream, bf16 normalised output)

@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 ROWS_CAP = 64
 TP_MAX_RANKS = 8
+CANARY_BYTE = 0xA5
 
 
 def tp_fuse_blob(*, inbox, flags, epoch_ptr: int, status_ptr: int, rank: int, size: int, rows_cap: int, n_cap: int,
@@ -56,7 +57,10 @@ class SymmetricArena:
         self.inbox_bytes = 2 * self.size * rows_cap * n_cap * 4
         self.rs_bytes = 2 * rows_cap * n_cap * 4          # [2][size][rows_cap][n_cap / size]
         self.ag_bytes = 2 * rows_cap * n_cap * 4          # [2][rows_cap][n_cap]
-        total = 2 * self.flag_bytes + self.inbox_bytes + self.rs_bytes + self.ag_bytes
+        # guard words behind every region that peers write into: a store that runs past its region lands on a canary
+        # and `check_canaries` (debug runs: LLAMINAR_VERIFY_COLLECTIVES) names the region instead of a later wrong sum
+        self.guard_bytes = 256
+        total = 2 * self.flag_bytes + self.inbox_bytes + self.rs_bytes + self.ag_bytes + 4 * self.guard_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
@@ -64,8 +68,14 @@ class SymmetricArena:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.epoch = torch.zeros(2 * n_tiles, dtype=torch.int32, device=self.device)      # one-shot counters, then two-phase counters
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        o_inbox = 2 * self.flag_bytes
-        o_rs, o_ag = o_inbox + self.inbox_bytes, o_inbox + self.inbox_bytes + self.rs_bytes
+        g = self.guard_bytes
+        o_inbox = 2 * self.flag_bytes + g
+        o_rs, o_ag = o_inbox + self.inbox_bytes + g, o_inbox + self.inbox_bytes + g + self.rs_bytes + g
+        self._guards = {"flags": 2 * self.flag_bytes, "inbox": o_inbox + self.inbox_bytes, "rs_inbox": o_rs + self.rs_bytes,
+                        "ag_inbox": o_ag + self.ag_bytes}
+        for off in self._guards.values():
+            self.buf[off:off + g].fill_(CANARY_BYTE)
+        torch.cuda.synchronize(self.device)
         two_phase_min_rows = 16 if (self.size >= 4 and 128 % self.size == 0) else 0
         blob = tp_fuse_blob(inbox=[p + o_inbox for p in ptrs], flags=ptrs, epoch_ptr=self.epoch.data_ptr(),
                             status_ptr=self.status.data_ptr(), rank=self.rank, size=self.size, rows_cap=rows_cap, n_cap=n_cap,
@@ -100,6 +110,12 @@ class SymmetricArena:
         if s != 0:
             self.status.zero_()
             raise RuntimeError(f"a fused tensor-parallel kernel gave up waiting for a peer (status {s})")
+
+    def check_canaries(self) -> None:
+        """Raise if a peer (or this rank) wrote past one of the arena's regions (debug aid; one small device read per region)."""
+        for name, off in self._guards.items():
+            if not bool((self.buf[off:off + self.guard_bytes] == CANARY_BYTE).all()):
+                raise RuntimeError(f"symmetric arena: the guard words behind '{name}' were overwritten on rank {self.rank}")
 
     def resync(self) -> None:
         """Collective: bring the arrival counters and call counters of every rank back to zero.  After a wait that ran out

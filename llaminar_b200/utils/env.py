@@ -40,6 +40,7 @@ REGISTRY: tuple[EnvVar, ...] = (
     EnvVar("LLAMINAR_WATCHDOG_TIMEOUT_S", float, 60.0, "a rank whose heartbeat is older than this is reported dead"),
     EnvVar("LLAMINAR_STEP_TIMEOUT_S", float, 0.0, "abort the process group when one engine step takes longer (0 = off)"),
     EnvVar("LLAMINAR_STAGE_DUMP_DIR", str, "", "dump per-layer hidden states of the next forward pass into this directory"),
+    EnvVar("LLAMINAR_BOUNDS_CHECK", bool, False, "build and load the kernels' debug variant with explicit index checks (status word instead of a fault)"),
     EnvVar("LLAMINAR_EXTENSION_REQUIRED", bool, True, "fail instead of falling back when the CUDA extension is missing on a GPU host"),
 )
 _BY_NAME = {e.name: e for e in REGISTRY}
