@@ -139,6 +139,17 @@ class QuantRecipe:
                 # Q4_K_M rule of thumb: a subset of the down projections is kept in Q6_K
                 if "ffn_down" in tensor_name and layer is not None and _more_bits(layer, n_layers):
                     return t
+            elif key == "ffn_down:first8th":
+                # Q4_K_S: the down projections of the first eighth of the layers get one more bit
+                if "ffn_down" in tensor_name and "_exps" not in tensor_name and layer is not None and layer < n_layers // 8:
+                    return t
+            elif key == "attn_v:first4":
+                if "attn_v" in tensor_name and layer is not None and layer < 4:
+                    return t
+            elif key == "output.weight":
+                # the LM head only: "blk.N.attn_output.weight" contains the same text and is an ordinary projection
+                if tensor_name == "output.weight":
+                    return t
             elif key in tensor_name:
                 return t
         return self.default
@@ -151,7 +162,10 @@ def _more_bits(i_layer: int, n_layers: int) -> bool:
 RECIPES = {
     "Q8_0": QuantRecipe(GGMLType.Q8_0, {}, "Q8_0"),
     "Q4_0": QuantRecipe(GGMLType.Q4_0, {}, "Q4_0"),
-    "Q4_K_S": QuantRecipe(GGMLType.Q4_K, {"output.weight": GGMLType.Q6_K, "token_embd": GGMLType.Q4_K}, "Q4_K_S"),
+    # llama.cpp's Q4_K_S mix: Q4_K everywhere, Q5_K for attn_v of the first four layers and ffn_down of the first eighth,
+    # Q6_K for the LM head
+    "Q4_K_S": QuantRecipe(GGMLType.Q4_K, {"output.weight": GGMLType.Q6_K, "token_embd": GGMLType.Q4_K, "attn_v:first4": GGMLType.Q5_K,
+                                          "ffn_down:first8th": GGMLType.Q5_K}, "Q4_K_S"),
     "Q4_K_M": QuantRecipe(GGMLType.Q4_K, {"output.weight": GGMLType.Q6_K, "attn_v": GGMLType.Q6_K,
                                           "ffn_down:some": GGMLType.Q6_K}, "Q4_K_M"),
     "Q5_K": QuantRecipe(GGMLType.Q5_K, {"output.weight": GGMLType.Q6_K}, "Q5_K"),

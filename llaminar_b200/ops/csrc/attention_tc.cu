@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             issue_v(j + 1);
         }
         cp_async_wait_all();
-    } else if (lane == 0) {
+    } else if (elect_one()) {
         // ------------------------------ MMA issue ------------------------------
         bool ok = true;
         auto issue_s = [&](int j) {

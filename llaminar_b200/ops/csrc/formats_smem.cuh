@@ -235,7 +235,7 @@ template <int A> struct DequantAtom<FMT_IQ3_S, A> {
 // up to about +-7); larger scales are clamped to the largest finite value, and the loader re-encodes such a tensor instead
 // of sending it here (ops/layout.py: q4k_scales_in_range).
 // The atom index is a run-time value so that the four warps of a scheduler (same row group, different atoms) share one
-// copy of the code.  The sink receives 16 consecutive columns per call: sink.emit16(c, r) -> columns 64*A + 16*c ...
+// copy of the code.  The sink receives the whole atom at once: sink.emit64(r) -> the 64 columns of atom A of this lane's row.
 // (A fp16 variant through cvt.rn.f16x2.e4m3x2 was tried first: tcgen05.mma kind::f16 with an fp16 A and a bf16 B operand
 // raises "illegal instruction" on B200, although the two formats are separate fields of the instruction descriptor.)
 LLM_DEVICE uint32_t hfma2_bf16_u32(uint32_t a, __nv_bfloat162 s, __nv_bfloat162 b) {
@@ -243,17 +243,15 @@ LLM_DEVICE uint32_t hfma2_bf16_u32(uint32_t a, __nv_bfloat162 s, __nv_bfloat162 
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 struct DequantAtomQ4KRt {
-    template <bool HI, class S>
-    LLM_DEVICE static void conv16(const uint4& q, __nv_bfloat162 s, __nv_bfloat162 nb, int c, S& sink) {
+    template <bool HI>
+    LLM_DEVICE static void conv16(const uint4& q, __nv_bfloat162 s, __nv_bfloat162 nb, uint32_t* r) {
         const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
-        uint32_t r[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t w = (HI ? ws[i] : (ws[i] << 4)) & 0xf0f0f0f0u;
             r[2 * i] = hfma2_bf16_u32(__byte_perm(w, 0u, 0x4140), s, nb);
             r[2 * i + 1] = hfma2_bf16_u32(__byte_perm(w, 0u, 0x4342), s, nb);
         }
-        sink.emit16(c, r);
     }
     // Everything this thread needs from the raw chunk, fetched and prepared before the operand slot is waited for: the two
     // 16-byte units of packed nibbles and the scale / minimum pairs of sub-blocks 2A and 2A + 1.
@@ -282,11 +280,14 @@ struct DequantAtomQ4KRt {
         r.b_hi = __float2bfloat162_rn(ndmin * (float)((mn2 >> 8) & 0xff));
         return r;
     }
+    // all 64 values into registers of their own, then one store: see TmemSink::emit64
     template <class S> LLM_DEVICE static void convert(const Regs& r, S& sink) {
-        conv16<false>(r.q0, r.s_lo, r.b_lo, 0, sink);
-        conv16<false>(r.q1, r.s_lo, r.b_lo, 1, sink);
-        conv16<true>(r.q0, r.s_hi, r.b_hi, 2, sink);
-        conv16<true>(r.q1, r.s_hi, r.b_hi, 3, sink);
+        uint32_t o[32];
+        conv16<false>(r.q0, r.s_lo, r.b_lo, o);
+        conv16<false>(r.q1, r.s_lo, r.b_lo, o + 8);
+        conv16<true>(r.q0, r.s_hi, r.b_hi, o + 16);
+        conv16<true>(r.q1, r.s_hi, r.b_hi, o + 24);
+        sink.emit64(o);
     }
     template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, int A, S& sink) { convert(load(raw, g, lane, A), sink); }
 };

@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         }
     } else {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        if (elect_one()) {
             constexpr uint32_t idesc = instr_desc(BM);
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {

@@ -1,19 +1,26 @@
-// Small-batch (5 <= M <= 64 rows) variant of the tcgen05 dequant GEMM: the weight-streaming, memory-bound regime
-// of batched decode.  out[M, N] = x[M, K] * dequant(W)[N, K]^T with weights in the MMA M dimension.
+// Small-batch (1 <= M <= 64 rows; the engine uses it for 5..64) variant of the tcgen05 dequant GEMM: the weight-streaming,
+// memory-bound regime of batched decode.  out[M, N] = x[M, K] * dequant(W)[N, K]^T with weights in the MMA M dimension.
 //
 // Differences from the large-tile kernel in gemm_tc.cu:
-//   * raw weight chunks are fetched by ONE bulk copy each (cp.async.bulk, ~14-34 KB) into a deep shared-memory
-//     ring, so HBM latency is hidden by bytes in flight rather than by warps waiting on global loads;
+//   * the packed weight chunks (128 rows x 256 columns, ~14-34 KB) are fetched by one producer warp with 16-byte cp.async
+//     into a deep shared-memory ring (an even number of slots), so HBM latency is hidden by bytes in flight rather than by
+//     warps waiting on global loads; weights are constants, so under programmatic dependent launch the producer fills the
+//     ring before the wait on the previous kernel;
 //   * 16 dequant warps cooperate on every chunk: warp (g, a) converts the 64-column atom `a` of row group `g`
 //     (lane == row), reading the packed bytes with ld.shared and storing the bf16 values straight into tensor
-//     memory (tcgen05.st), from where the MMA takes its A operand: no shared-memory round trip for the weights;
+//     memory (tcgen05.st), from where the MMA takes its A operand: no shared-memory round trip for the weights.
+//     The converted chunk lives in one of N_SETS operand sets (3; 2 for the formats whose warps alternate);
+//   * two MMA issuer warps each issue half of EVERY chunk (issuer w takes atoms 2w and 2w+1): tcgen05.mma costs ~180
+//     clocks to issue whatever its shape, and issue from different warps overlaps;
 //   * persistent CTAs (one per SM) walk a contiguous range of (tile, chunk) work ("stream-K"): every SM streams
 //     the same number of bytes, barriers / TMEM are set up once, and two TMEM accumulators let the MMAs of the
-//     next tile start while the previous tile's epilogue drains;
+//     next tile start while the previous tile's epilogue drains; the finisher of a split tile loads the parked partial
+//     sums before it waits for its own accumulator;
 //   * SwiGLU pairs gate and up rows inside one warp (16 + 16 rows), so the epilogue needs a shuffle only.
-// Warp roles: 0-15 dequant + epilogue, 16 raw-chunk bulk producer, 17 activation TMA producer, 18-19 MMA issuers
+// Warp roles: 0-15 dequant + epilogue, 16 raw-chunk producer, 17 activation TMA producer, 18-19 MMA issuers
 // (18 also owns the TMEM allocation).
-// Every stage and raw slot is visited once per revolution by each waiter, so 1-bit mbarrier parities are exact.
+// Every barrier is visited by each of its waiters on every revolution (set counts and slot counts are chosen for that), so
+// the 1-bit mbarrier parities are exact.
 #include <cuda.h>
 
 #include "formats_smem.cuh"
@@ -28,12 +35,6 @@ namespace tcs {
 using namespace tc5;
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-#ifndef LLM_WAIT_MODE
-#define LLM_WAIT_MODE 0
-#endif
-#ifndef LLM_PREFETCH_PRE_PDL
-#define LLM_PREFETCH_PRE_PDL 1
-#endif
 constexpr unsigned long long WAIT_LIMIT_NS = 300ull * 1000 * 1000;      // 0.3 s: far beyond any wait inside one launch
 constexpr int N_DQ_WARPS = 16;
 constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activation producer, two MMA issuers
@@ -41,35 +42,61 @@ constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activatio
 // Bounded wait.  abort_flag[0]: some wait of this CTA gave up (everybody leaves).  abort_flag[1]: the epilogue is inside its
 // own bounded wait for a tensor-parallel peer; the pipeline behind it is legitimately stalled, so the count is held
 // meanwhile (the peer wait has its own limit and reports through the status word).
-LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    // try_wait parks the thread in hardware for a short, system-chosen time; after a few misses the warp also yields its
-    // issue slots (a suspend-time hint on try_wait made no measurable difference here, polling without the sleep cost
-    // the conversion-heavy formats 10 %).  The limit is a deadline on the global nanosecond timer, read every few attempts.
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-#if LLM_WAIT_MODE == 1
-        if (mbar_test_wait(bar, parity)) return true;
-        if (i >= 4096u) {
-            __nanosleep(40);
-#elif LLM_WAIT_MODE == 2
-        if (mbar_test_wait(bar, parity)) return true;
-        if (i >= 8u) {
-            __nanosleep(20);
-#else
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i >= 16u) {
-            __nanosleep(40);
+// The timeline stamps are compiled in only for a tracing build (-DLLM_TRACE=1): a branch the compiler cannot prove
+// warp-uniform costs a reconvergence sequence even when it is never taken, and the hot loops are sensitive to that.
+#ifndef LLM_TRACE
+#define LLM_TRACE 0
 #endif
-            if ((i & 63u) == 63u) {
-                if (abort_flag[0]) return false;
-                const unsigned long long now = global_timer_ns();
-                if (t0 == 0 || abort_flag[1]) t0 = now;
-                else if (now - t0 > WAIT_LIMIT_NS) break;
-            }
-        }
+constexpr uint32_t WAIT_HINT_NS = 4000;       // suspend-time hint of one try_wait
+constexpr uint32_t WAIT_TRIES = 32;           // attempts inside one assembly loop, between two looks at the abort flag and the clock
+// `tries` attempts of mbarrier.try_wait in one assembly block.  The loop is invisible to the compiler, so it plants no
+// divergence bookkeeping around it; try_wait answers a whole warp at once, so the lanes leave together anyway.
+LLM_DEVICE uint32_t mbar_try_wait_loop(uint32_t bar, uint32_t parity, uint32_t tries) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\tmov.u32 n, %3;\n"
+        "WAIT_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %4;\n\t"
+        "@p bra WAIT_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\t"
+        "setp.ne.u32 p, n, 0;\n\t"
+        "@p bra WAIT_LOOP;\n"
+        "WAIT_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(tries), "r"(WAIT_HINT_NS) : "memory");
+    return ok;
+}
+// Bounded wait.  abort_flag[0]: some wait of this CTA gave up (everybody leaves).  abort_flag[1]: the epilogue is inside its
+// own bounded wait for a tensor-parallel peer; the pipeline behind it is legitimately stalled, so the clock is restarted
+// meanwhile (the peer wait has its own limit and reports through the status word).
+// WARP = true: called by all 32 lanes of a converged warp; the result is made warp-uniform by a vote, so the branches on it
+// are uniform branches.  WARP = false: called by a single elected lane.
+template <bool WARP>
+LLM_DEVICE bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    uint32_t ok = mbar_try_wait_loop(bar, parity, WAIT_TRIES);
+    if (WARP) ok = __all_sync(0xffffffffu, ok);
+    if (ok) return true;
+    unsigned long long t0 = 0;
+#pragma unroll 1
+    for (;;) {
+        int give_up = abort_flag[0];
+        const unsigned long long now = global_timer_ns();
+        if (t0 == 0 || abort_flag[1]) t0 = now;
+        else if (now - t0 > WAIT_LIMIT_NS) give_up = 1;
+        if (WARP) give_up = __any_sync(0xffffffffu, give_up);
+        if (give_up) break;
+        ok = mbar_try_wait_loop(bar, parity, WAIT_TRIES);
+        if (WARP) ok = __all_sync(0xffffffffu, ok);
+        if (ok) return true;
     }
     abort_flag[0] = 1;
     return false;
+}
+LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) { return mbar_wait_t<false>(bar, parity, abort_flag); }
+LLM_DEVICE bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) { return mbar_wait_t<true>(bar, parity, abort_flag); }
+// arrive from the lanes whose `pred` is set, without a branch the compiler would have to reconverge
+LLM_DEVICE void mbar_arrive_if(uint32_t bar, bool pred) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar), "r"((uint32_t)pred) : "memory");
 }
 LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -123,21 +150,31 @@ template <int FMT, int BM> struct Cfg {
     static_assert(A_COLS_OFFSET + N_SETS * A_CHUNK_COLS <= TMEM_COLS, "tensor memory map overflows");
 };
 
+// Sink that keeps a converted atom (64 bf16 of this lane's row, 32 packed pairs) in registers.
+struct RegSink {
+    uint32_t o[32];
+    LLM_DEVICE void emit(int c, uint4 v) { o[4 * c] = v.x; o[4 * c + 1] = v.y; o[4 * c + 2] = v.z; o[4 * c + 3] = v.w; }
+    LLM_DEVICE void emit64(const uint32_t (&r)[32]) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = r[i];
+    }
+};
+
 // Sink of a dequant warp: 8 bf16 (one uint4) -> 4 TMEM columns of this lane's row.
 struct TmemSink {
     uint32_t taddr;         // lane quarter | first column of this atom in the current chunk's A region
     LLM_DEVICE void emit(int c, uint4 v) {
         asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr + c * 4), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
     }
-    // 16 values (eight packed pairs) -> 8 TMEM columns
-    LLM_DEVICE void emit16(int c, const uint32_t (&r)[8]) {
-#ifdef LLM_PROBE_SKIP_ST
-        uint32_t x = r[0] ^ r[1] ^ r[2] ^ r[3] ^ r[4] ^ r[5] ^ r[6] ^ r[7];
-        if (x == 0x12345678u) asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr + c * 8), "r"(x) : "memory");
-        return;
-#endif
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + c * 8), "r"(r[0]), "r"(r[1]),
-                     "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+    // a whole 64-column atom of this lane's row (32 packed pairs) -> 32 TMEM columns, one instruction (measured alone, sixteen
+    // warps: 940 bytes per clock and SM with .x32, 790 with .x8)
+    LLM_DEVICE void emit64(const uint32_t (&r)[32]) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                     "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                     ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                     "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+                     "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+                     "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
     }
 };
 
@@ -195,7 +232,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
         for (int s = 0; s < C::N_SETS; ++s) { mbar_init(full_bar + s * 8, C::DQ_WARPS_PER_CHUNK + 1); mbar_init(empty_bar + s * 8, C::N_ISSUERS); }
-        for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 32); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
+        for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 1); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
         mbar_init(sig_bar, N_DQ_WARPS);
@@ -216,12 +253,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     // starts filling its ring at once (under programmatic dependent launch that overlaps the tail of the previous kernel) and
     // joins the wait only before its first wait on a ring slot; every other role waits here, before it reads activations or
     // writes outputs and scratch.
-    if (!LLM_PREFETCH_PRE_PDL || warp != N_DQ_WARPS) pdl_wait();
+    if (warp != N_DQ_WARPS) pdl_wait();
     const uint32_t tmem_base = s_tmem;
     volatile int* abort_flag = s_abort;
     // optional timeline trace of CTA (flags >> 8): p.debug[role * 1024 + slot] = low 32 bits of the ns timer
     auto stamp = [&](int role, int slot) {
-        if (p.debug && (int)blockIdx.x == (p.flags >> 8) && slot < 1024) {
+        if (LLM_TRACE && p.debug && (int)blockIdx.x == (p.flags >> 8) && slot < 1024) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             p.debug[role * 1024 + slot] = (int)(t & 0x7fffffff);
@@ -229,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     };
     // per-CTA start / end stamps: p.debug[4096 + 4 * cta + {0, 1, 2}] = start, end, end of dequant loop
     auto cta_stamp = [&](int slot) {
-        if (p.debug) {
+        if (LLM_TRACE && p.debug) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             p.debug[4096 + 4 * blockIdx.x + slot] = (int)(t & 0x7fffffff);
@@ -255,18 +292,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         TmemSink sink{0};
         int cc = 0, ui = 0, epi_syncs = 0;
         bool ok = true;
-        // A chunk is published to the MMA issuers one step late: its TMEM stores complete while this warp already waits
-        // for the next chunk's raw bytes and operand slot, instead of being waited for on their own.
+        // A chunk is published to the MMA issuers one step late (see the conversion loop): pend_* name the chunk that is owed.
         int pend_set = -1, pend_slot = -1;
         auto publish = [&]() {
             if (pend_set < 0) return;
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");      // warp-wide: every lane's stores are complete after it
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(full_bar + pend_set * 8);       // this warp's part of the chunk's weight operand is in TMEM
-                mbar_arrive(rawe_bar + pend_slot * 8);      // this warp no longer needs the raw chunk
-            }
+            mbar_arrive_if(full_bar + pend_set * 8, lane == 0);       // this warp's part of the chunk's weight operand is in TMEM
+            mbar_arrive_if(rawe_bar + pend_slot * 8, lane == 0);      // this warp no longer needs the raw chunk
             pend_set = -1;
         };
         // Epilogue of unit `ui_` (accumulator set ui_ & 1; its first chunk had counter cc0).  Returns false after a timeout.
@@ -588,16 +621,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 if (C::TWO_SETS && (cc & 1) != ws) continue;
                 const int slot = cc % R, rphase = (cc / R) & 1;
                 const int set = set_of(cc);
-                ok = mbar_wait(rawf_bar + slot * 8, rphase, abort_flag);
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
+                ok = mbar_wait_warp(rawf_bar + slot * 8, rphase, abort_flag);
+                if (LLM_TRACE && warp == 0 && lane == 0) stamp(0, cc * 4 + 0);
                 // Q4_K: the packed bytes and the prepared scales go into registers now, so that the loads and the scale
                 // arithmetic run under the wait for the operand slot instead of after it
                 [[maybe_unused]] DequantAtomQ4KRt::Regs pre;
                 if constexpr (C::RT_ATOM) {
                     if (ok) pre = DequantAtomQ4KRt::load(raw_base + slot * C::CHUNK, g, lane, a1);
                 }
-                if (ok) ok = mbar_wait(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
+                if (ok) ok = mbar_wait_warp(empty_bar + set * 8, sphase_of(cc) ^ 1, abort_flag);
+                if (LLM_TRACE && warp == 0 && lane == 0) stamp(0, cc * 4 + 1);
                 if (!ok) return;
                 const uint32_t raw = raw_base + slot * C::CHUNK;
                 const uint32_t a_base = tmem_base + ((uint32_t)(g * 32) << 16) + C::A_COLS_OFFSET + set * C::A_CHUNK_COLS;
@@ -619,29 +652,36 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             sink.taddr = a_base + 96; DequantAtom<FMT, 3>::run(raw, g, lane, sink);
                         }
                     }
-                } else if constexpr (C::RT_ATOM) {
-                    sink.taddr = a_base + a1 * 32;
-#ifndef LLM_PROBE_SKIP_DEQUANT
-                    DequantAtomQ4KRt::convert(pre, sink);
-#endif
                 } else {
-                    sink.taddr = a_base + a1 * 32;
-                    switch (a1) {
-                        case 0: DequantAtom<FMT, 0>::run(raw, g, lane, sink); break;
-                        case 1: DequantAtom<FMT, 1>::run(raw, g, lane, sink); break;
-                        case 2: DequantAtom<FMT, 2>::run(raw, g, lane, sink); break;
-                        default: DequantAtom<FMT, 3>::run(raw, g, lane, sink); break;
+                    // All sixteen warps on one chunk: the converted atom is built in registers, the PREVIOUS chunk is published
+                    // (its tensor-memory stores have had this whole iteration to complete), and only then this chunk's single
+                    // store is issued.  The MMA issue is cheap since it goes through elect.sync, and operand sets come free a
+                    // chunk ahead of need, so the extra iteration of latency costs nothing.
+                    RegSink rs;
+                    if constexpr (C::RT_ATOM) {
+                        DequantAtomQ4KRt::convert(pre, rs);
+                    } else {
+                        switch (a1) {
+                            case 0: DequantAtom<FMT, 0>::run(raw, g, lane, rs); break;
+                            case 1: DequantAtom<FMT, 1>::run(raw, g, lane, rs); break;
+                            case 2: DequantAtom<FMT, 2>::run(raw, g, lane, rs); break;
+                            default: DequantAtom<FMT, 3>::run(raw, g, lane, rs); break;
+                        }
                     }
+                    publish();
+                    sink.taddr = a_base + a1 * 32;
+                    sink.emit64(rs.o);
+                    pend_set = set;
+                    pend_slot = slot;
                 }
-                // Published at once.  An operand set makes a round trip per chunk (conversion -> TMEM stores complete -> full
-                // -> MMAs issued and completed -> empty) and only N_SETS chunks are in flight, so every nanosecond between the
-                // last store and the arrival on `full` lengthens the period of all roles: a per-CTA timeline with the
-                // publication deferred to the next chunk (to hide the store latency) showed both the issuers and these warps
-                // waiting on each other, 0.9 us per chunk with neither side busier than 60 %.
-                pend_set = set;
-                pend_slot = slot;
-                publish();
-                if (warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
+                // The alternating warp sets publish at once: a set owns one operand set, so its next chunk's operand set frees
+                // only after this chunk has been published and multiplied.
+                if constexpr (C::TWO_SETS) {
+                    pend_set = set;
+                    pend_slot = slot;
+                    publish();
+                }
+                if (LLM_TRACE && warp == 0 && lane == 0) stamp(0, cc * 4 + 2);
             }
         };
         while (ok && it.next(u)) {
@@ -656,33 +696,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         }
         if (ok) ok = flush();
     } else if (warp == N_DQ_WARPS) {
-        // ---------------- raw chunk producer: the whole warp streams each chunk with 16-byte cp.async ----------------
-        // (measured: one cp.async.bulk per chunk tops out near 10 GB/s per SM here, far below what LDGSTS sustains)
-        int cc = 0;
-        bool ok = true;
-        while (ok && it.next(u)) {
-            const uint8_t* wsrc = p.w + ((size_t)u.tile * k_blocks + u.kb0) * C::CHUNK;
-            for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
-                const int slot = cc % R, rphase = (cc / R) & 1;
-                if (LLM_PREFETCH_PRE_PDL && cc == R) pdl_wait();   // the first R slots start out empty: no wait, hence no time limit, before this
-                ok = mbar_wait(rawe_bar + slot * 8, rphase ^ 1, abort_flag);
-                if (!ok) break;
-                const uint8_t* src = wsrc + (size_t)c * C::CHUNK + lane * 16;
-                const uint32_t dst = raw_base + slot * C::CHUNK + lane * 16;
-#pragma unroll 4
-                for (int i = 0; i < C::CHUNK / 512; ++i)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 512), "l"(src + i * 512) : "memory");
-                if constexpr (C::CHUNK % 512 != 0) {
-                    constexpr int full = (C::CHUNK / 512) * 512;
-                    if (lane < (C::CHUNK % 512) / 16)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + full), "l"(src + full) : "memory");
+        // ---------------- raw chunk producer: one bulk copy per chunk ----------------
+        // Measured on a ring of this shape with nothing behind it (148 CTAs, 18 KB chunks, 8 slots): one cp.async.bulk per
+        // chunk streams 6.9 TB/s, a warp of 16-byte cp.async 4.0 TB/s (four such warps 6.7 TB/s), so the copy engine it is.
+        if (elect_one()) {
+            int cc = 0;
+            bool ok = true;
+            while (ok && it.next(u)) {
+                const uint8_t* wsrc = p.w + ((size_t)u.tile * k_blocks + u.kb0) * C::CHUNK;
+                for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
+                    const int slot = cc % R, rphase = (cc / R) & 1;
+                    if (cc == R) pdl_wait();   // the first R slots start out empty: no wait, hence no time limit, before this
+                    ok = mbar_wait(rawe_bar + slot * 8, rphase ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(rawf_bar + slot * 8, C::CHUNK);
+                    bulk_load(raw_base + slot * C::CHUNK, wsrc + (size_t)c * C::CHUNK, C::CHUNK, rawf_bar + slot * 8);
+                    stamp(1, cc);
                 }
-                // the barrier receives one arrival per lane once that lane's copies have landed
-                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(rawf_bar + slot * 8) : "memory");
-                if (lane == 0) stamp(1, cc);
             }
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == N_DQ_WARPS + 1) {
         // ---------------- activation tile producer (TMA): the four 64-column tiles of a chunk on one barrier ----------------
         if (lane == 16 && streamk && p.partials != nullptr) {
@@ -710,13 +742,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     for (int a = 0; a < 4; ++a)
                         tma_load_2d(smem_base + (set * 4 + a) * C::B_ATOM_BYTES, &tmap_x, (u.kb0 + c) * 256 + a * 64, 0,
                                     full_bar + set * 8);
+                    stamp(6, cc);
                 }
             }
         }
     } else {
         // ---------------- MMA issuers: warp w takes the chunks of parity w ----------------
         const int w = warp - (N_DQ_WARPS + 2);
-        if (lane == 0) {
+        if (elect_one()) {
             constexpr uint32_t idesc = instr_desc(BM);
             int cc = 0, ui = 0;
             bool ok = true;
@@ -729,7 +762,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 for (int c = 0; c < u.nkb && ok; ++c, ++cc) {
                     const int set = set_of(cc);
                     ok = mbar_wait(full_bar + set * 8, sphase_of(cc), abort_flag);
-                    if (w == 0) stamp(2, cc * 2);
+                    stamp(w == 0 ? 2 : 5, cc * 2);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t acc_base = tmem_base + buf * C::ACC_SET_COLS + w * C::ACC_PER_ISSUER * BM;
@@ -740,14 +773,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                         const uint64_t bdesc = smem_desc_sw128(smem_base + (set * 4 + a) * C::B_ATOM_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)      // 16 columns of K = 8 TMEM columns of A, 32 bytes of the swizzled B row
-#ifndef LLM_PROBE_SKIP_MMA
                             mma_f16_ts(acc_base, a_tmem + a * 32 + k4 * 8, bdesc + 2 * k4, idesc, (first && a2 == 0 && k4 == 0) ? 0u : 1u);
-#else
-                            ;
-#endif
                     }
                     mma_commit(empty_bar + set * 8);
-                    if (w == 0) stamp(2, cc * 2 + 1);
+                    stamp(w == 0 ? 2 : 5, cc * 2 + 1);
                     first = false;
                 }
                 if (ok) mma_commit(accf_bar + buf * 8);
@@ -791,6 +820,8 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     using C = Cfg<FMT, BM>;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
+    static_assert(C::CHUNK % 16 == 0 && C::RING_BYTES % 16 == 0, "bulk copies need 16-byte granularity");
+    if (reinterpret_cast<uintptr_t>(p.w) & 15) return cudaErrorInvalidValue;      // the chunks arrive by bulk copy
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
     const cuuint64_t strides[1] = {(cuuint64_t)p.k * 2};

@@ -25,17 +25,23 @@ LLM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// non-blocking test of a phase (test_wait never suspends the thread)
-LLM_DEVICE bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+// One lane of a converged warp, chosen by the hardware.  A single-lane region entered through elect.sync keeps its operands
+// in uniform registers; the same region behind `if (lane == 0)` issued tcgen05.mma at 53-140 clocks apiece (measured, one
+// warp, M=128 N=32 K=16), behind elect.sync at 16 clocks, which is the tensor pipe's own rate for that shape.
+LLM_DEVICE bool elect_one() {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok));
     return ok != 0;
 }
 LLM_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 LLM_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 LLM_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, size a multiple of 16 bytes
+LLM_DEVICE void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 // one tile of a 2-D tensor map into shared memory (no multicast: the tile is for this CTA only)
 LLM_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
