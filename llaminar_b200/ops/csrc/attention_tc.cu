@@ -37,17 +37,6 @@ constexpr int OFF_P = OFF_VT + 4 * ATOM;           // 2 atoms (key halves), rows
 constexpr int OFF_VS = OFF_P + 2 * ATOM;           // staging of the two V pages of a key tile: 128 keys x 256 bytes
 constexpr int SMEM_BYTES = OFF_VS + BK * D * 2 + 1024;
 
-LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 256) {
-            if (*abort_flag) return false;
-            __nanosleep(64);
-        }
-    }
-    *abort_flag = 1;
-    return false;
-}
 LLM_DEVICE void cp_async16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
 LLM_DEVICE void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 LLM_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -78,7 +67,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_bars[N_BARS];
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort;
+    __shared__ int s_abort[2];       // [1] stays 0 here (tc_common.cuh: restarts the wait clock when set)
     // [column half][row]: row maxima (and, at the end, sums) of a thread pair.  One copy is enough: a thread overwrites its
     // entry only after the O_FULL wait of the tile, which needs the partner's P_FULL arrival, which follows the partner's read.
     __shared__ float s_xchg[2][BQ];
@@ -100,7 +89,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
     auto bar = [&](int i) { return bars + i * 8; };
 
     if (tid == 0) {
-        s_abort = 0;
+        s_abort[0] = 0; s_abort[1] = 0;
         const int counts[N_BARS] = {3, 3, 1, 1, 3, 3, 1, 1, 1, 1, 8, 8, 8, 1, 8, 3, 2, 2, 2, 2};
         for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), counts[i]);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -114,7 +103,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    volatile int* abort_flag = &s_abort;
+    volatile int* abort_flag = s_abort;
 
     if (warp < 8) {
         // ------------------------------ softmax + output: two threads per query row (== TMEM lane), 64 columns each ------------------------------
@@ -134,8 +123,8 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
         int n_pair = 0;
         auto pair_meet = [&]() {                   // bounded rendezvous of the two warps that share these 32 rows
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(PAIR + q4));
-            const bool r = mbar_wait(bar(PAIR + q4), n_pair & 1, abort_flag);
+            mbar_arrive_if(bar(PAIR + q4), lane == 0);
+            const bool r = mbar_wait_warp(bar(PAIR + q4), n_pair & 1, abort_flag);
             ++n_pair;
             return r;
         };
@@ -144,7 +133,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
         // first pass over tile j: wait for S, row maximum over this thread's 64 columns, exchange with the partner thread
         auto pass1 = [&](int j) {
             const int b = j & 1;
-            if (!mbar_wait(bar(S_FULL + b), (j >> 1) & 1, abort_flag)) return false;
+            if (!mbar_wait_warp(bar(S_FULL + b), (j >> 1) & 1, abort_flag)) return false;
             tc_fence_after();
             const int key0 = j * BK + half * 64;
             const uint32_t t_s = t_lane + b * 128;
@@ -174,7 +163,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
         };
         // the tile's P V product is complete: fold it into the register copy of the output row
         auto fold = [&](int j) {
-            if (!mbar_wait(bar(O_FULL), j & 1, abort_flag)) return false;
+            if (!mbar_wait_warp(bar(O_FULL), j & 1, abort_flag)) return false;
             tc_fence_after();
             const uint32_t t_o = t_lane + 256;
             tmem_ld32_issue(t_o, ra);
@@ -188,7 +177,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(O_EMPTY));
+            mbar_arrive_if(bar(O_EMPTY), lane == 0);
             return true;
         };
         // Order per tile: first pass (row maxima; the P V MMAs of the previous tile run meanwhile) -> fold of the previous tile
@@ -237,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(bar(S_EMPTY + b)); mbar_arrive(bar(P_FULL)); }
+            mbar_arrive_if(bar(S_EMPTY + b), lane == 0); mbar_arrive_if(bar(P_FULL), lane == 0);
             l = l * alpha + sum;
             m = m_new;
             alpha_prev = alpha;
@@ -272,8 +261,8 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
         bool ok = true;
         auto loaders_meet = [&]() {               // bounded rendezvous of the loader warps
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(LD_SYNC));
-            const bool r = mbar_wait(bar(LD_SYNC), n_sync & 1, abort_flag);
+            mbar_arrive_if(bar(LD_SYNC), lane == 0);
+            const bool r = mbar_wait_warp(bar(LD_SYNC), n_sync & 1, abort_flag);
             ++n_sync;
             return r;
         };
@@ -314,12 +303,12 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             cp_async_wait_1();                     // K of tile j (and Q) has landed; V of tile j may still be in flight
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(K_FULL + b));
-            if (j + 1 < nt) ok = mbar_wait(bar(K_EMPTY + (b ^ 1)), (((j + 1) >> 1) & 1) ^ 1, abort_flag);
+            mbar_arrive_if(bar(K_FULL + b), lane == 0);
+            if (j + 1 < nt) ok = mbar_wait_warp(bar(K_EMPTY + (b ^ 1)), (((j + 1) >> 1) & 1) ^ 1, abort_flag);
             if (!ok) break;
             issue_k(j + 1);
             cp_async_wait_1();                     // V of tile j has landed (K of tile j + 1 may still be in flight)
-            ok = mbar_wait(bar(VT_EMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag) && loaders_meet();
+            ok = mbar_wait_warp(bar(VT_EMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag) && loaders_meet();
             if (!ok) break;
             // transpose 8x8 blocks: 16 key blocks x 4 groups of four d blocks
             for (int op = lw; op < 64; op += N_LOADERS / 32) {
@@ -331,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
             fence_proxy_async();
             ok = loaders_meet();                   // the staging tile may be overwritten
             if (!ok) break;
-            if (lane == 0) mbar_arrive(bar(VT_FULL + b));
+            mbar_arrive_if(bar(VT_FULL + b), lane == 0);
             issue_v(j + 1);
         }
         cp_async_wait_all();
@@ -371,7 +360,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_attn_prefill_tc_kernel(const
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
     __syncthreads();
-    if (s_abort) {
+    if (s_abort[0]) {
         if (tid == 0 && status) atomicExch(status, (int)STATUS_TIMEOUT);
         for (int i = 0; i < 2000; ++i) __nanosleep(100);      // let copies still in flight land before the memory is reused
         __syncthreads();

@@ -270,26 +270,28 @@ struct DequantAtomQ4KRt {
         uint32_t sc2, mn2;
         if (A < 2) { sc2 = a2 & 0x3f3fu; mn2 = b2 & 0x3f3fu; }
         else { sc2 = (c2 & 0x0f0fu) | ((a2 >> 2) & 0x3030u); mn2 = ((c2 >> 4) & 0x0f0fu) | ((b2 >> 2) & 0x3030u); }
-        // d * 2^129 in two exact steps (2^129 is not an fp32 value)
+        // d * 2^129 in two exact steps (2^129 is not an fp32 value).  The 6-bit integers become floats without the conversion
+        // unit: byte k under the exponent of 2^23 is 2^23 + k, and (2^23 + k) * f - 2^23 * f is one FMA.
         const float BIG = 3.3895314e38f;                       // largest finite bf16
-        const float d = half_bits_to_float(meta.x & 0xffff) * 1.2676506e30f, ndmin = -half_bits_to_float(meta.x >> 16);   // 2^100
+        const float d100 = half_bits_to_float(meta.x & 0xffff) * 1.2676506e30f;     // d * 2^100
+        const float ndmin = -half_bits_to_float(meta.x >> 16);
+        const float d100c = -8388608.0f * d100, ndminc = -8388608.0f * ndmin;
         const float k29 = 536870912.0f;                         // 2^29
-        r.s_lo = __float2bfloat162_rn(fminf(d * ((float)(sc2 & 0xff) * k29), BIG));
-        r.s_hi = __float2bfloat162_rn(fminf(d * ((float)((sc2 >> 8) & 0xff) * k29), BIG));
-        r.b_lo = __float2bfloat162_rn(ndmin * (float)(mn2 & 0xff));
-        r.b_hi = __float2bfloat162_rn(ndmin * (float)((mn2 >> 8) & 0xff));
+        const float sc_lo = __uint_as_float(__byte_perm(sc2, 0x4b000000u, 0x7650)), sc_hi = __uint_as_float(__byte_perm(sc2, 0x4b000000u, 0x7651));
+        const float mn_lo = __uint_as_float(__byte_perm(mn2, 0x4b000000u, 0x7650)), mn_hi = __uint_as_float(__byte_perm(mn2, 0x4b000000u, 0x7651));
+        r.s_lo = __float2bfloat162_rn(fminf(fmaf(sc_lo, d100, d100c) * k29, BIG));
+        r.s_hi = __float2bfloat162_rn(fminf(fmaf(sc_hi, d100, d100c) * k29, BIG));
+        r.b_lo = __float2bfloat162_rn(fmaf(mn_lo, ndmin, ndminc));
+        r.b_hi = __float2bfloat162_rn(fmaf(mn_hi, ndmin, ndminc));
         return r;
     }
-    // all 64 values into registers of their own, then one store: see TmemSink::emit64
-    template <class S> LLM_DEVICE static void convert(const Regs& r, S& sink) {
-        uint32_t o[32];
+    // all 64 values (32 packed pairs) of the atom into `o`, which the caller then hands to one tensor-memory store
+    LLM_DEVICE static void convert(const Regs& r, uint32_t (&o)[32]) {
         conv16<false>(r.q0, r.s_lo, r.b_lo, o);
         conv16<false>(r.q1, r.s_lo, r.b_lo, o + 8);
         conv16<true>(r.q0, r.s_hi, r.b_hi, o + 16);
         conv16<true>(r.q1, r.s_hi, r.b_hi, o + 24);
-        sink.emit64(o);
     }
-    template <class S> LLM_DEVICE static void run(uint32_t raw, int g, int lane, int A, S& sink) { convert(load(raw, g, lane, A), sink); }
 };
 
 }  // namespace llm

@@ -31,21 +31,8 @@ using namespace tc5;
 constexpr int A_ATOM_BYTES = 128 * 128;          // 128 weight rows x 64 bf16
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-// Bounded wait: returns false once the limit is hit or another thread has raised the abort flag.
-// abort_flag[1] holds the count while the TMA lane is inside its own bounded wait for staged rows (fused all-gather).
-LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 256) {
-            if (abort_flag[0]) return false;
-            if (abort_flag[1]) i = 257;
-            __nanosleep(64);
-        }
-    }
-    abort_flag[0] = 1;
-    return false;
-}
-
+// Bounded waits: tc_common.cuh (mbar_wait for one lane, mbar_wait_warp for a converged warp).  abort_flag[1] is set while the
+// TMA lane is inside its own bounded wait for staged rows (fused all-gather): the rest of the pipeline is legitimately stalled.
 template <int BM> struct Cfg {
     static constexpr int B_ATOM_BYTES = BM * 128;
     static constexpr int STAGE_BYTES = A_ATOM_BYTES + B_ATOM_BYTES;
@@ -84,7 +71,7 @@ struct RingSink {
         for (int i = 0; i < n; ++i) {
             int stage, phase;
             ring_slot<STAGES>(it0 + a + i, stage, phase);
-            if (ok) ok = mbar_wait(empty_bar + stage * 8, phase ^ 1, abort_flag);
+            if (ok) ok = mbar_wait_warp(empty_bar + stage * 8, phase ^ 1, abort_flag);
         }
     }
     LLM_DEVICE void emit(int kg, uint4 v) {
@@ -95,13 +82,11 @@ struct RingSink {
     }
     LLM_DEVICE void end(int a, int n) {
         fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-            for (int i = 0; i < n; ++i) {
-                int stage, phase;
-                ring_slot<STAGES>(it0 + a + i, stage, phase);
-                mbar_arrive(full_bar + stage * 8);
-            }
+        __syncwarp();                          // every lane's stores are fenced before lane 0 publishes the stage
+        for (int i = 0; i < n; ++i) {
+            int stage, phase;
+            ring_slot<STAGES>(it0 + a + i, stage, phase);
+            mbar_arrive_if(full_bar + stage * 8, lane == 0);
         }
     }
 };
@@ -292,7 +277,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const __grid_constant__
         }
     } else if (warp == 8) {
         // ------------------------------ TMA producer (activations) ------------------------------
-        if (lane == 0) {
+        if (elect_one()) {
             bool ok = true;
             if (p.ag_on) {
                 // wait (bounded) until the copier CTAs have staged this m-tile, then order their generic-proxy stores

@@ -35,7 +35,6 @@ namespace tcs {
 using namespace tc5;
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr unsigned long long WAIT_LIMIT_NS = 300ull * 1000 * 1000;      // 0.3 s: far beyond any wait inside one launch
 constexpr int N_DQ_WARPS = 16;
 constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activation producer, two MMA issuers
 
@@ -47,57 +46,6 @@ constexpr int THREADS = (N_DQ_WARPS + 4) * 32;      // + raw producer, activatio
 #ifndef LLM_TRACE
 #define LLM_TRACE 0
 #endif
-constexpr uint32_t WAIT_HINT_NS = 4000;       // suspend-time hint of one try_wait
-constexpr uint32_t WAIT_TRIES = 32;           // attempts inside one assembly loop, between two looks at the abort flag and the clock
-// `tries` attempts of mbarrier.try_wait in one assembly block.  The loop is invisible to the compiler, so it plants no
-// divergence bookkeeping around it; try_wait answers a whole warp at once, so the lanes leave together anyway.
-LLM_DEVICE uint32_t mbar_try_wait_loop(uint32_t bar, uint32_t parity, uint32_t tries) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\tmov.u32 n, %3;\n"
-        "WAIT_LOOP:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %4;\n\t"
-        "@p bra WAIT_DONE;\n\t"
-        "sub.u32 n, n, 1;\n\t"
-        "setp.ne.u32 p, n, 0;\n\t"
-        "@p bra WAIT_LOOP;\n"
-        "WAIT_DONE:\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(tries), "r"(WAIT_HINT_NS) : "memory");
-    return ok;
-}
-// Bounded wait.  abort_flag[0]: some wait of this CTA gave up (everybody leaves).  abort_flag[1]: the epilogue is inside its
-// own bounded wait for a tensor-parallel peer; the pipeline behind it is legitimately stalled, so the clock is restarted
-// meanwhile (the peer wait has its own limit and reports through the status word).
-// WARP = true: called by all 32 lanes of a converged warp; the result is made warp-uniform by a vote, so the branches on it
-// are uniform branches.  WARP = false: called by a single elected lane.
-template <bool WARP>
-LLM_DEVICE bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    uint32_t ok = mbar_try_wait_loop(bar, parity, WAIT_TRIES);
-    if (WARP) ok = __all_sync(0xffffffffu, ok);
-    if (ok) return true;
-    unsigned long long t0 = 0;
-#pragma unroll 1
-    for (;;) {
-        int give_up = abort_flag[0];
-        const unsigned long long now = global_timer_ns();
-        if (t0 == 0 || abort_flag[1]) t0 = now;
-        else if (now - t0 > WAIT_LIMIT_NS) give_up = 1;
-        if (WARP) give_up = __any_sync(0xffffffffu, give_up);
-        if (give_up) break;
-        ok = mbar_try_wait_loop(bar, parity, WAIT_TRIES);
-        if (WARP) ok = __all_sync(0xffffffffu, ok);
-        if (ok) return true;
-    }
-    abort_flag[0] = 1;
-    return false;
-}
-LLM_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) { return mbar_wait_t<false>(bar, parity, abort_flag); }
-LLM_DEVICE bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) { return mbar_wait_t<true>(bar, parity, abort_flag); }
-// arrive from the lanes whose `pred` is set, without a branch the compiler would have to reconverge
-LLM_DEVICE void mbar_arrive_if(uint32_t bar, bool pred) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar), "r"((uint32_t)pred) : "memory");
-}
 LLM_DEVICE void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
@@ -154,10 +102,6 @@ template <int FMT, int BM> struct Cfg {
 struct RegSink {
     uint32_t o[32];
     LLM_DEVICE void emit(int c, uint4 v) { o[4 * c] = v.x; o[4 * c + 1] = v.y; o[4 * c + 2] = v.z; o[4 * c + 3] = v.w; }
-    LLM_DEVICE void emit64(const uint32_t (&r)[32]) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = r[i];
-    }
 };
 
 // Sink of a dequant warp: 8 bf16 (one uint4) -> 4 TMEM columns of this lane's row.
@@ -659,7 +603,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     // chunk ahead of need, so the extra iteration of latency costs nothing.
                     RegSink rs;
                     if constexpr (C::RT_ATOM) {
-                        DequantAtomQ4KRt::convert(pre, rs);
+                        DequantAtomQ4KRt::convert(pre, rs.o);
                     } else {
                         switch (a1) {
                             case 0: DequantAtom<FMT, 0>::run(raw, g, lane, rs); break;
