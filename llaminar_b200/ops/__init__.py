@@ -95,8 +95,10 @@ def _accum_args(pw: PackedWeight, rows: int, sc: Scratch | None):
 
 def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
          epi: int = EPI_STORE, bias: torch.Tensor | None = None, scratch: Scratch | None = None, ksplit: int = 0,
-         tp: torch.Tensor | None = None, tuned: bool = True) -> None:
+         tp: torch.Tensor | None = None, tuned: bool = True, stream: bool = True) -> None:
     """out[m, :] (+)= x[m, :] @ W^T for m <= 4 rows.  x: fp32 residual rows when ``norm_w`` is given, else bf16.
+    Plain dense calls run the streaming kernel (persistent CTAs, chunks by bulk copy; ``stream=False`` keeps the
+    register-path kernel, which also serves the fused tensor-parallel epilogue and the expert work lists).
     ``tp``: device copy of the tensor-parallel descriptor; with EPI_RESID the epilogue all-reduces across ranks.
     ``ksplit`` 0 lets the tuning table (``ops/tuning.py``), then the kernel's heuristic, pick the split-K factor."""
     rows = x.shape[0]
@@ -105,7 +107,9 @@ def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.
         from .tuning import table
         ksplit = table().ksplit("gemv", pw.fmt, pw.n, pw.k, rows)
     accum, tickets = _accum_args(pw, rows, scratch)
-    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1, tp)
+    ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1, tp,
+               scratch.partials if scratch is not None else None, scratch.status if scratch is not None else None,
+               stream and tp is None)
     _count()
 
 
@@ -118,7 +122,7 @@ def gemv_experts(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, expert_id
         accum, tickets = None, None
     stride = pw.n_tiles * pw.k_blocks * pw.chunk_bytes
     ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, None, 0.0, out, epi, None, accum, tickets, 0, expert_ids, stride,
-               slots_per_row, 1, z, None)
+               slots_per_row, 1, z, None, None, None, False)
     _count()
 
 

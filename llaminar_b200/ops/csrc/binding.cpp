@@ -28,7 +28,7 @@ static void check_cuda(const Tensor& t, const char* name) {
 static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tensor& x, const OptTensor& norm_w, double eps,
                  Tensor out, int64_t epi, const OptTensor& bias, const OptTensor& accum, const OptTensor& tickets,
                  int64_t ksplit, const OptTensor& expert_ids, int64_t expert_stride, int64_t z_per_x, int64_t m_tile, int64_t z,
-                 const OptTensor& tp) {
+                 const OptTensor& tp, const OptTensor& partials, const OptTensor& status, bool stream) {
     check_cuda(w, "w"); check_cuda(x, "x"); check_cuda(out, "out");
     const c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(k % 256 == 0, "k must be a multiple of 256");
@@ -57,6 +57,12 @@ static void gemv(const Tensor& w, int64_t fmt, int64_t n, int64_t k, const Tenso
     p.bias = cptr<float>(bias);
     p.expert_ids = cptr<int>(expert_ids); p.expert_stride = (size_t)expert_stride;
     p.tp = tp.has_value() ? reinterpret_cast<const llm::TpFuse*>(tp->data_ptr()) : nullptr;
+    if (stream && z == 1 && partials.has_value() && partials->scalar_type() == torch::kFloat32 && tickets.has_value() &&
+        tickets->numel() >= p.n_tiles) {
+        const cudaError_t e = llm::launch_gemv_stream(p, (int)m_tile, mptr<float>(partials), (size_t)partials->numel(), mptr<unsigned>(tickets),
+                                                      status.has_value() ? static_cast<int*>(status->data_ptr()) : nullptr, cur_stream());
+        if (e != cudaErrorNotSupported) { LLM_CUDA_CHECK(e); return; }
+    }
     LLM_CUDA_CHECK(llm::launch_gemv(p, (int)m_tile, (int)z, cur_stream()));
 }
 

@@ -80,15 +80,46 @@ LLM_DEVICE int dp4a_s(uint32_t a, int b, int c) {   // both signed
     return r;
 }
 
-template <int F, int M> struct DotBlock;
+// Where a chunk is read from: global memory (read-only path, no L1 allocation) or a copy in shared memory (a generic
+// pointer into the CTA's shared window).  The dot products below are written once against this policy.
+struct LdGlobalNc {
+    LLM_DEVICE static uint4 v4(const void* p) { return ldg_nc_v4(p); }
+    LLM_DEVICE static uint2 v2(const void* p) { return ldg_nc_v2(p); }
+    LLM_DEVICE static uint32_t u32(const void* p) { return ldg_nc_u32(p); }
+    LLM_DEVICE static uint16_t u16(const void* p) { return ldg_nc_u16(p); }
+};
+struct LdShared {
+    LLM_DEVICE static uint32_t a(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+    LLM_DEVICE static uint4 v4(const void* p) {
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a(p)));
+        return v;
+    }
+    LLM_DEVICE static uint2 v2(const void* p) {
+        uint2 v;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a(p)));
+        return v;
+    }
+    LLM_DEVICE static uint32_t u32(const void* p) {
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a(p)));
+        return v;
+    }
+    LLM_DEVICE static uint16_t u16(const void* p) {
+        uint16_t v;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a(p)));
+        return v;
+    }
+};
+template <int F, int M, class L = LdGlobalNc> struct DotBlock;
 
-template <int M> struct DotBlock<FMT_Q4_K, M> {
+template <int M, class L> struct DotBlock<FMT_Q4_K, M, L> {
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q4_K>;
-        const uint4 meta = ldg_nc_v4(chunk + T::P_META + ((g * 32 + lane) << 4));
+        const uint4 meta = L::v4(chunk + T::P_META + ((g * 32 + lane) << 4));
         uint4 w[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) w[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
+        for (int u = 0; u < 8; ++u) w[u] = L::v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
         const float d = half_bits_to_float(meta.x & 0xffff), dmin = half_bits_to_float(meta.x >> 16);
         int sc[8], mn[8];
         unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
@@ -126,15 +157,15 @@ template <int M> struct DotBlock<FMT_Q4_K, M> {
     }
 };
 
-template <int M> struct DotBlock<FMT_Q5_K, M> {
+template <int M, class L> struct DotBlock<FMT_Q5_K, M, L> {
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q5_K>;
-        const uint4 meta = ldg_nc_v4(chunk + T::P_META + ((g * 32 + lane) << 4));
+        const uint4 meta = L::v4(chunk + T::P_META + ((g * 32 + lane) << 4));
         uint4 w[8], qh[2];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) w[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
+        for (int u = 0; u < 8; ++u) w[u] = L::v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
 #pragma unroll
-        for (int u = 0; u < 2; ++u) qh[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QH, 2, g, u, lane));
+        for (int u = 0; u < 2; ++u) qh[u] = L::v4(unit_ptr(chunk + T::P_QH, 2, g, u, lane));
         const float d = half_bits_to_float(meta.x & 0xffff), dmin = half_bits_to_float(meta.x >> 16);
         int sc[8], mn[8];
         unpack_k4_scales(meta.y, meta.z, meta.w, sc, mn);
@@ -175,17 +206,17 @@ template <int M> struct DotBlock<FMT_Q5_K, M> {
     }
 };
 
-template <int M> struct DotBlock<FMT_Q6_K, M> {
+template <int M, class L> struct DotBlock<FMT_Q6_K, M, L> {
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q6_K>;
         const int row = g * 32 + lane;
-        const uint4 scw = ldg_nc_v4(chunk + T::P_SC + (row << 4));
-        const float d = half_bits_to_float(ldg_nc_u16(chunk + T::P_D + (row << 1)));
+        const uint4 scw = L::v4(chunk + T::P_SC + (row << 4));
+        const float d = half_bits_to_float(L::u16(chunk + T::P_D + (row << 1)));
         uint4 ql[8], qh[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) ql[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QL, 8, g, u, lane));
+        for (int u = 0; u < 8; ++u) ql[u] = L::v4(unit_ptr(chunk + T::P_QL, 8, g, u, lane));
 #pragma unroll
-        for (int u = 0; u < 4; ++u) qh[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QH, 4, g, u, lane));
+        for (int u = 0; u < 4; ++u) qh[u] = L::v4(unit_ptr(chunk + T::P_QH, 4, g, u, lane));
         const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -230,15 +261,15 @@ template <int M> struct DotBlock<FMT_Q6_K, M> {
     }
 };
 
-template <int M> struct DotBlock<FMT_Q8_0, M> {
+template <int M, class L> struct DotBlock<FMT_Q8_0, M, L> {
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q8_0>;
-        const uint4 dw = ldg_nc_v4(chunk + T::P_D + ((g * 32 + lane) << 4));
+        const uint4 dw = L::v4(chunk + T::P_D + ((g * 32 + lane) << 4));
         const uint32_t ds[4] = {dw.x, dw.y, dw.z, dw.w};
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
-            const uint4 q0 = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 16, g, 2 * b, lane));
-            const uint4 q1 = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 16, g, 2 * b + 1, lane));
+            const uint4 q0 = L::v4(unit_ptr(chunk + T::P_QS, 16, g, 2 * b, lane));
+            const uint4 q1 = L::v4(unit_ptr(chunk + T::P_QS, 16, g, 2 * b + 1, lane));
             const float d = half_bits_to_float((ds[b >> 1] >> (16 * (b & 1))) & 0xffff);
 #pragma unroll
             for (int m = 0; m < M; ++m) {
@@ -254,14 +285,14 @@ template <int M> struct DotBlock<FMT_Q8_0, M> {
     }
 };
 
-template <int M> struct DotBlock<FMT_Q4_0, M> {
+template <int M, class L> struct DotBlock<FMT_Q4_0, M, L> {
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M]) {
         using T = FmtTraits<FMT_Q4_0>;
-        const uint4 dw = ldg_nc_v4(chunk + T::P_D + ((g * 32 + lane) << 4));
+        const uint4 dw = L::v4(chunk + T::P_D + ((g * 32 + lane) << 4));
         const uint32_t ds[4] = {dw.x, dw.y, dw.z, dw.w};
         uint4 w[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) w[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
+        for (int u = 0; u < 8; ++u) w[u] = L::v4(unit_ptr(chunk + T::P_QS, 8, g, u, lane));
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
             const uint32_t ws[4] = {w[b].x, w[b].y, w[b].z, w[b].w};
@@ -284,7 +315,7 @@ template <int M> struct DotBlock<FMT_Q4_0, M> {
     }
 };
 
-template <int M> struct DotBlock<FMT_IQ3_S, M> {
+template <int M, class L> struct DotBlock<FMT_IQ3_S, M, L> {
     // `grid` must point at a shared-memory copy of g_iq3s_grid.
     LLM_DEVICE static void run(const uint8_t* chunk, int g, int lane, const ActBlk* act, int act_stride, float (&acc)[M],
                                const uint32_t* grid) {
@@ -292,12 +323,12 @@ template <int M> struct DotBlock<FMT_IQ3_S, M> {
         const int row = g * 32 + lane;
         uint4 qs[4], sg[2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) qs[u] = ldg_nc_v4(unit_ptr(chunk + T::P_QS, 4, g, u, lane));
+        for (int u = 0; u < 4; ++u) qs[u] = L::v4(unit_ptr(chunk + T::P_QS, 4, g, u, lane));
 #pragma unroll
-        for (int u = 0; u < 2; ++u) sg[u] = ldg_nc_v4(unit_ptr(chunk + T::P_SIGNS, 2, g, u, lane));
-        const uint2 qh = ldg_nc_v2(chunk + T::P_QH + (row << 3));
-        const uint32_t scw = ldg_nc_u32(chunk + T::P_SC + (row << 2));
-        const float d = half_bits_to_float(ldg_nc_u16(chunk + T::P_D + (row << 1)));
+        for (int u = 0; u < 2; ++u) sg[u] = L::v4(unit_ptr(chunk + T::P_SIGNS, 2, g, u, lane));
+        const uint2 qh = L::v2(chunk + T::P_QH + (row << 3));
+        const uint32_t scw = L::u32(chunk + T::P_SC + (row << 2));
+        const float d = half_bits_to_float(L::u16(chunk + T::P_D + (row << 1)));
 #pragma unroll
         for (int ib = 0; ib < 8; ++ib) {
             const uint4 q4 = qs[ib >> 1];

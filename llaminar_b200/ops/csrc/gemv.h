@@ -60,6 +60,9 @@ struct GemvParams {
 };
 
 cudaError_t launch_gemv(const GemvParams& p, int m_tile, int z, cudaStream_t st);
+// Streaming kernel for plain dense calls (gemv_stream.cu): one persistent CTA per SM, chunks by bulk copy.  Returns
+// cudaErrorNotSupported for calls it does not take (grouped experts, fused tensor-parallel epilogue, missing scratch).
+cudaError_t launch_gemv_stream(const GemvParams& p, int m, float* partials, size_t partials_floats, unsigned* tickets, int* status, cudaStream_t st);
 int gemv_pick_ksplit(int n_tiles, int k_blocks, int z);
 
 struct MoeRouteParams {

@@ -49,18 +49,49 @@ def test_gemv_plain_and_norm(qt, m):
     xb = x.to(torch.bfloat16)
     out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
     bias = torch.randn(n, device=DEV)
-    for ks in (1, 0, 2):
-        ops.gemv(pw, xb, out, bias=bias, scratch=sc, ksplit=ks)
-        ref = xb.float() @ wf.T + bias
-        assert _rel(out, ref) < 2e-2, (qt, m, ks)
-    # fused RMSNorm prologue + residual epilogue
-    gain = torch.rand(k, device=DEV) + 0.5
-    h = torch.randn(m, n, device=DEV)
-    h0 = h.clone()
-    ops.gemv(pw, x, h, norm_w=gain, eps=1e-6, epi=ops.EPI_RESID, scratch=sc)
-    ref = h0 + ref_rmsnorm(x, gain, 1e-6) @ wf.T
-    assert _rel(h, ref) < 2e-2
+    sc.status.zero_()
+    for stream in (True, False):            # the streaming kernel (bulk-copy ring) and the register-path kernel
+        for ks in (1, 0, 2):
+            out.zero_()
+            ops.gemv(pw, xb, out, bias=bias, scratch=sc, ksplit=ks, stream=stream)
+            ref = xb.float() @ wf.T + bias
+            assert _rel(out, ref) < 2e-2, (qt, m, ks, stream)
+        # fused RMSNorm prologue + residual epilogue
+        gain = torch.rand(k, device=DEV) + 0.5
+        h = torch.randn(m, n, device=DEV)
+        h0 = h.clone()
+        ops.gemv(pw, x, h, norm_w=gain, eps=1e-6, epi=ops.EPI_RESID, scratch=sc, stream=stream)
+        ref = h0 + ref_rmsnorm(x, gain, 1e-6) @ wf.T
+        assert _rel(h, ref) < 2e-2, stream
+    assert int(sc.status[0]) == 0, "a bounded wait of the streaming kernel ran out"
     assert int(sc.tickets.abs().sum()) == 0 and float(sc.accum.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(5120, 8192), (1000, 25600), (10240, 5120), (128, 256), (384, 512)])
+@pytest.mark.parametrize("m", [1, 3])
+def test_gemv_streaming_split_tiles_match_the_register_path(shape, m):
+    """Shapes whose tiles are split between CTAs (long K), ranges that wrap over a tile end, a ragged last tile and problems
+    smaller than the grid: the streaming kernel equals the fp32 reference, repeats bit for bit, and leaves its counters at zero."""
+    from llaminar_b200 import ops
+    n, k = shape
+    pw, wf = _weight(GGMLType.Q4_K, n, k, seed=11)
+    sc = ops.scratch_for(DEV)
+    sc.status.zero_()
+    xb = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    ref = xb.float() @ wf.T
+    outs = []
+    for rep in range(3):
+        out = torch.zeros(m, n, dtype=torch.float32, device=DEV)
+        ops.gemv(pw, xb, out, scratch=sc)
+        outs.append(out)
+    old = torch.zeros(m, n, dtype=torch.float32, device=DEV)
+    ops.gemv(pw, xb, old, scratch=sc, stream=False)
+    torch.cuda.synchronize()
+    assert int(sc.status[0]) == 0
+    assert _rel(outs[0], ref) < 2e-2
+    assert _rel(outs[0], old) < 1e-4              # same int8 activations and dp4a sums, different summation order over chunks
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert int(sc.tickets.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("qt", [GGMLType.Q4_K, GGMLType.Q8_0])
@@ -76,10 +107,12 @@ def test_gemv_swiglu(qt):
     pw = ops.pack_matrix(raw, qt, n2, k)
     x = torch.randn(2, k, device=DEV).to(torch.bfloat16)
     out = torch.empty(2, d_ff, dtype=torch.bfloat16, device=DEV)
-    ops.gemv(pw, x, out, epi=ops.EPI_SWIGLU, scratch=ops.scratch_for(DEV))
     gf, uf = dequantize(rg, qt, (d_ff, k)), dequantize(ru, qt, (d_ff, k))
     ref = torch.nn.functional.silu(x.float() @ gf.T) * (x.float() @ uf.T)
-    assert _rel(out, ref) < 3e-2
+    for stream in (True, False):
+        out.zero_()
+        ops.gemv(pw, x, out, epi=ops.EPI_SWIGLU, scratch=ops.scratch_for(DEV), stream=stream)
+        assert _rel(out, ref) < 3e-2, stream
 
 
 @pytest.mark.parametrize("qt", FORMATS)
