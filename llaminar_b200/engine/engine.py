@@ -242,6 +242,11 @@ class LLMEngine:
             vals = [int(w[0]) for w in self._status_words()]
         if not any(vals):
             return
+        symm0 = getattr(self.tp, "symm", None) if self.tp is not None else None
+        detail = ""
+        if symm0 is not None and int(symm0.status[0]) != 0:
+            t, seen, want = (int(v) for v in symm0.status[1:4])
+            detail = f"; fused tensor-parallel wait: tile {t & 0xffff}{' (second phase)' if t & 0x10000 else ''} saw count {seen}, wanted {want}"
         sc = getattr(self.model, "scratch", None)
         if sc is not None:
             sc.reset()
@@ -250,7 +255,7 @@ class LLMEngine:
             symm.status.zero_()
             if getattr(self.tp, "verify_checksums", False) and hasattr(symm, "check_canaries"):
                 symm.check_canaries()
-        msg = f"a kernel gave up a bounded wait (status words {vals}); scratch buffers were reset"
+        msg = f"a kernel gave up a bounded wait (status words {vals}{detail}); scratch buffers were reset"
         hb = getattr(self, "heartbeat", None)
         if hb is not None:
             hb.post_error(msg)

@@ -107,6 +107,8 @@ def gemv(pw: PackedWeight, x: torch.Tensor, out: torch.Tensor, *, norm_w: torch.
         from .tuning import table
         ksplit = table().ksplit("gemv", pw.fmt, pw.n, pw.k, rows)
     accum, tickets = _accum_args(pw, rows, scratch)
+    if tickets is None and scratch is not None and pw.n_tiles <= scratch.tickets.numel():
+        tickets = scratch.tickets          # wider than the split-K accumulator (the LM head): the streaming kernel needs the counters only
     ext().gemv(pw.data, pw.fmt, pw.n, pw.k, x, norm_w, eps, out, epi, bias, accum, tickets, ksplit, None, 0, 1, rows, 1, tp,
                scratch.partials if scratch is not None else None, scratch.status if scratch is not None else None,
                stream and tp is None)

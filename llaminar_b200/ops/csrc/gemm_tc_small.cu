@@ -132,10 +132,11 @@ struct UnitIter {
     int pos, end;
     LLM_DEVICE void init(int kb, int nt, int grid, int cta, int sk) {
         k_blocks = kb; n_tiles = nt; total = kb * nt; G = grid; b = cta; streamk = sk;
-        if (streamk) { pos = (int)(((long long)b * total) / G); end = (int)(((long long)(b + 1) * total) / G); }
+        if (streamk) { pos = (int)(((unsigned)b * (unsigned)total) / (unsigned)G); end = (int)(((unsigned)(b + 1) * (unsigned)total) / (unsigned)G); }
         else { pos = b; end = n_tiles; }
     }
-    LLM_DEVICE int cta_of(int x) const { return (int)((((long long)(x + 1)) * G - 1) / total); }
+    // 32-bit arithmetic: the launcher refuses problems with (chunks + 1) * grid >= 2^32 (64-bit division costs ~100 instructions)
+    LLM_DEVICE int cta_of(int x) const { return (int)(((unsigned)(x + 1) * (unsigned)G - 1u) / (unsigned)total); }
     LLM_DEVICE bool next(Unit& u) {
         if (pos >= end) return false;
         if (streamk) {
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     using C = Cfg<FMT, BM>;
     constexpr int R = C::RAW_SLOTS;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi, s_sig;
+    __shared__ __align__(8) uint64_t s_full[C::N_SETS], s_empty[C::N_SETS], s_raw_full[R], s_raw_empty[R], s_acc_full[2], s_acc_empty[2], s_epi, s_sig, s_tick;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort[2], s_last, s_tp_ok;
     __shared__ unsigned s_tp_epoch, s_tp_epoch2;
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
     const uint32_t raw_base = smem_base + C::RING_BYTES;       // activation ring first, raw weight chunks behind it
     const uint32_t full_bar = smem_u32(s_full), empty_bar = smem_u32(s_empty);
     const uint32_t rawf_bar = smem_u32(s_raw_full), rawe_bar = smem_u32(s_raw_empty);
-    const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi), sig_bar = smem_u32(&s_sig);
+    const uint32_t accf_bar = smem_u32(s_acc_full), acce_bar = smem_u32(s_acc_empty), epi_bar = smem_u32(&s_epi), sig_bar = smem_u32(&s_sig), tick_bar = smem_u32(&s_tick);
 
     if (tid == 0) {
         s_abort[0] = 0; s_abort[1] = 0;
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         for (int s = 0; s < R; ++s) { mbar_init(rawf_bar + s * 8, 1); mbar_init(rawe_bar + s * 8, C::DQ_WARPS_PER_CHUNK); }
         for (int s = 0; s < 2; ++s) { mbar_init(accf_bar + s * 8, C::N_ISSUERS); mbar_init(acce_bar + s * 8, N_DQ_WARPS); }
         mbar_init(epi_bar, N_DQ_WARPS);
+        mbar_init(tick_bar, N_DQ_WARPS);
         mbar_init(sig_bar, N_DQ_WARPS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
         const int q = g, part = warp >> 2;                 // epilogue: TMEM lane quarter q, column part `part`
         constexpr int CW = C::COLS_PER_WARP;
         TmemSink sink{0};
-        int cc = 0, ui = 0, epi_syncs = 0;
+        int cc = 0, ui = 0, epi_syncs = 0, tick_syncs = 0;
         bool ok = true;
         // A chunk is published to the MMA issuers one step late (see the conversion loop): pend_* name the chunk that is owed.
         int pend_set = -1, pend_slot = -1;
@@ -276,19 +278,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                 got = __shfl_sync(0xffffffffu, got, 0);
                 __syncwarp();
                 if (!got) return false;
-                // once every warp has seen the count, warp 0 puts the counter back for the next launch
-                if (lane == 0) mbar_arrive(epi_bar);
+                // Once every warp has seen the count, warp 0 puts the counter back for the next launch.  Only warp 0 waits, so
+                // this rendezvous has a barrier of its own: on the barrier of the full rendezvous further down, the arrival of a
+                // warp that is already one phase on would complete this phase before a slow warp has read the counter, and
+                // that warp would then poll a counter that is back at zero until its limit (seen with tiles split between two
+                // CTAs that finish together: four ranks, attention output projection).
+                if (lane == 0) mbar_arrive(tick_bar);
                 if (warp == 0) {
-                    if (!mbar_wait(epi_bar, epi_syncs & 1, abort_flag)) return false;
+                    if (!mbar_wait(tick_bar, tick_syncs & 1, abort_flag)) return false;
                     if (lane == 0) p.tickets[u.tile] = 0u;
                 }
-                ++epi_syncs;
+                ++tick_syncs;
                 const int nc = c_last - c_first + 1;
 #pragma unroll
                 for (int j = 1; j < MAX_C; ++j) {
                     const int c = c_first + j;
                     if (j < nc) {
-                        const int c_pos = (int)(((long long)c * it.total) / it.G);
+                        const int c_pos = (int)(((unsigned)c * (unsigned)it.total) / (unsigned)it.G);
                         const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
 #pragma unroll
                         for (int i = 0; i < CW; ++i) parked[j][i] = __ldcg(&theirs[(c0 + i) * 128 + row]);
@@ -385,7 +391,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
 #pragma unroll
                                 for (int i = 0; i < CW; ++i) sum[i] += v[i];
                             } else {
-                                const int c_pos = (int)(((long long)c * it.total) / it.G);
+                                const int c_pos = (int)(((unsigned)c * (unsigned)it.total) / (unsigned)it.G);
                                 const float* theirs = p.partials + ((size_t)c * 2 + (c_pos / k_blocks == u.tile ? 0 : 1)) * (128 * BM);
 #pragma unroll
                                 for (int i = 0; i < CW; ++i) sum[i] += __ldcg(&theirs[(c0 + i) * 128 + row]);
@@ -480,11 +486,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                             const unsigned target = (e2 + 1u) * (unsigned)W;
                             const unsigned* f2 = tp.flags2[tp.rank] + u.tile;
                             int got = 0;
-                            for (unsigned it2 = 0; it2 < tp.spin_limit; ++it2) {
+                            const bool dead = tp.status && *reinterpret_cast<volatile int*>(tp.status) != 0;     // see tp_wait
+                            for (unsigned it2 = 0; it2 < tp.spin_limit && !dead; ++it2) {
                                 if ((int)(ld_acquire_sys(f2) - target) >= 0) { got = 1; break; }
                                 if (it2 > 4096) __nanosleep(64);
                             }
-                            if (!got && tp.status) atomicExch(tp.status, (int)STATUS_TIMEOUT);
+                            if (!got && tp.status) {
+                                tp.status[1] = u.tile | 0x10000; tp.status[2] = (int)ld_acquire_sys(f2); tp.status[3] = (int)target;
+                                atomicExch(tp.status, (int)STATUS_TIMEOUT);
+                            }
                             s_tp_ok = s_tp_ok && got;
                             abort_flag[1] = 0;
                             tp.epoch2[u.tile] = e2 + 1;
@@ -532,15 +542,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_small_kernel(const __grid_
                     }
                 } else if (n_row < p.n) {
                     const float b = p.bias ? p.bias[n_row] : 0.f;
+                    if (p.epi == EPI_RESID) {
+                        // residual add: all the loads first, then the stores (one L2 round trip instead of one per token)
+                        float* h = static_cast<float*>(p.out) + n_row;
+                        float hv[CW];
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) {
-                        const int m = c0 + i;
-                        if (m >= p.m) continue;
-                        const size_t idx = (size_t)m * p.out_stride + n_row;
-                        const float o = v[i] + b;
-                        if (p.epi == EPI_RESID) { float* h = static_cast<float*>(p.out); h[idx] += o; }
-                        else if (p.out_f32) static_cast<float*>(p.out)[idx] = o;
-                        else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(o);
+                        for (int i = 0; i < CW; ++i) hv[i] = (c0 + i < p.m) ? __ldcg(h + (size_t)(c0 + i) * p.out_stride) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < CW; ++i)
+                            if (c0 + i < p.m) h[(size_t)(c0 + i) * p.out_stride] = hv[i] + v[i] + b;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) {
+                            const int m = c0 + i;
+                            if (m >= p.m) continue;
+                            const size_t idx = (size_t)m * p.out_stride + n_row;
+                            const float o = v[i] + b;
+                            if (p.out_f32) static_cast<float*>(p.out)[idx] = o;
+                            else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16(o);
+                        }
                     }
                 }
             }
@@ -784,6 +804,7 @@ static cudaError_t launch_one(const GemmTcParams& p, int ksplit, cudaStream_t st
     // persistent: one CTA per SM (or fewer when there is less work than that)
     GemmTcParams q = p;
     const int n_tiles = (p.n + 127) / 128, k_blocks = p.k / 256;
+    if ((unsigned long long)(n_tiles * (long long)k_blocks + 1) * 148ull >= (1ull << 32)) return cudaErrorInvalidValue;   // 32-bit work indices
     const bool streamk = ksplit != 1 && p.accum && p.tickets;
     q.flags = (p.flags & ~2) | (streamk ? 2 : 0);
     const int units = streamk ? n_tiles * k_blocks : n_tiles;

@@ -49,10 +49,11 @@ struct Walk {
     int k_blocks, total, G, pos, end;
     LLM_DEVICE void init(int kb, int n_tiles, int grid, int cta) {
         k_blocks = kb; total = kb * n_tiles; G = grid;
-        pos = (int)(((long long)cta * total) / G);
-        end = (int)(((long long)(cta + 1) * total) / G);
+        pos = (int)(((unsigned)cta * (unsigned)total) / (unsigned)G);
+        end = (int)(((unsigned)(cta + 1) * (unsigned)total) / (unsigned)G);
     }
-    LLM_DEVICE int cta_of(int x) const { return (int)((((long long)(x + 1)) * G - 1) / total); }
+    // 32-bit arithmetic: the launcher refuses problems with (chunks + 1) * grid >= 2^32
+    LLM_DEVICE int cta_of(int x) const { return (int)(((unsigned)(x + 1) * (unsigned)G - 1u) / (unsigned)total); }
     LLM_DEVICE bool next(Unit& u) {
         if (pos >= end) return false;
         u.tile = pos / k_blocks;
@@ -329,6 +330,7 @@ cudaError_t launch_gemv_stream(const GemvParams& p, int m, float* partials, size
     if (p.epi != EPI_STORE && p.epi != EPI_RESID && p.epi != EPI_SWIGLU) return cudaErrorNotSupported;
     if (reinterpret_cast<uintptr_t>(p.w) & 15) return cudaErrorNotSupported;
     const int total = p.n_tiles * p.k_blocks;
+    if ((unsigned long long)((long long)total + 1) * 148ull >= (1ull << 32)) return cudaErrorNotSupported;      // 32-bit work indices
     static int cached_sms = 0;
     if (!cached_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev); }
     const int sms = cached_sms > 0 ? cached_sms : 148;

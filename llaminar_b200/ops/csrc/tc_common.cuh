@@ -34,8 +34,11 @@ LLM_DEVICE bool elect_one() {
     return ok != 0;
 }
 // ---- bounded mbarrier waits shared by the tcgen05 kernels ----
-constexpr unsigned long long WAIT_LIMIT_NS = 300ull * 1000 * 1000;      // 0.3 s: far beyond any wait inside one launch
-constexpr uint32_t WAIT_HINT_NS = 4000;       // suspend-time hint of one try_wait
+constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000 * 1000;     // 2 s: far beyond any wait inside one launch, and beyond a host hiccup of a peer rank
+#ifndef LLM_WAIT_HINT_NS
+#define LLM_WAIT_HINT_NS 4000
+#endif
+constexpr uint32_t WAIT_HINT_NS = LLM_WAIT_HINT_NS;       // suspend-time hint of one try_wait
 constexpr uint32_t WAIT_TRIES = 32;           // attempts inside one assembly loop, between two looks at the abort flag and the clock
 // `tries` attempts of mbarrier.try_wait in one assembly block.  The loop is invisible to the compiler, so it plants no
 // divergence bookkeeping around it; try_wait answers a whole warp at once, so the lanes leave together anyway.

@@ -76,12 +76,19 @@ LLM_DEVICE void tp_signal(const TpFuse& tp, int tile, int peer) { red_release_sy
 LLM_DEVICE bool tp_wait(const TpFuse& tp, int tile, unsigned epoch_val) {
     const unsigned target = (epoch_val + 1u) * (unsigned)tp.size;
     const unsigned* f = tp.flags[tp.rank] + tile;
+    // a wait of this rank has run out already: the counters of the ranks no longer agree until the host has resynchronised
+    // them, so the remaining calls of the step give up at once instead of waiting out the limit one after the other
+    if (tp.status && *reinterpret_cast<volatile int*>(tp.status) != 0) return false;
     for (unsigned i = 0; i < tp.spin_limit; ++i) {
         // wrap-safe comparison of monotone counters
         if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
         if (i > 4096) __nanosleep(64);       // the peer is normally a few microseconds away: poll hard first
     }
-    if (tp.status) atomicExch(tp.status, (int)STATUS_TIMEOUT);
+    if (tp.status) {
+        // status[1..3]: which tile gave up, the count it saw and the count it wanted (a host-side report names them)
+        tp.status[1] = tile; tp.status[2] = (int)ld_acquire_sys(f); tp.status[3] = (int)target;
+        atomicExch(tp.status, (int)STATUS_TIMEOUT);
+    }
     return false;
 }
 
