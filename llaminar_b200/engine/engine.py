@@ -481,6 +481,8 @@ class LLMEngine:
             return tok.tolist()
         logits = self._gather_vocab(logits)
         out = self._sample_full_rows(logits, reqs, all_greedy)
+        if getattr(self.model, "token_sync", False):
+            out = self.model.sync_sampled(out)            # pipeline stages: the last stage's draw is everybody's
         if want_lp:
             self._record_logprobs(logits, reqs, out)
         return out
@@ -551,9 +553,16 @@ class LLMEngine:
         return self.tp.all_gather_vocab(logits, self.cfg.vocab_size)
 
     # -- prefill ---------------------------------------------------------------------------------------
+    def _set_token_sync(self, reqs: list[Request]) -> None:
+        """Pipeline stages: whether only the sampled ids cross the stages in this pass (not with speculative decoding, which
+        verifies full rows on every rank, nor when a request wants log-probabilities from the rows)."""
+        if hasattr(self.model, "sync_sampled"):
+            self.model.token_sync = self.mtp is None and not any(r.params.wants_logprobs for r in reqs)
+
     def _prefill(self, batch: list[Request]) -> list[StepOutput]:
         t0 = time.perf_counter()
         dev = self.device
+        self._set_token_sync(batch)
         # split long prompts into chunks of at most max_prefill_tokens rows per forward
         pending = {r.rid: r.prefix_hit_tokens for r in batch}
         final_logits: dict[int, torch.Tensor] = {}
@@ -701,6 +710,7 @@ class LLMEngine:
         return min(s, max(1, self.max_pages_per_seq // 2))
 
     def _decode_eager(self, reqs: list[Request]) -> list[int]:
+        self._set_token_sync(reqs)
         fb = self._decode_batch_tensors(reqs)
         evp = self.step_events.pop() if self.step_events else None
         if evp:

@@ -3,8 +3,12 @@
 Every rank runs the same scheduler on the same requests (commands are replicated, `parallel.spmd`), so all
 ranks build identical batches and call `forward` in lock step.  A stage's `forward` receives the residual
 stream from the stage before it, runs its own layers and sends the result on; the last stage computes the
-logits, gathers the vocabulary shards inside its tensor-parallel group and broadcasts full rows to the other
-stages so that every rank samples the same token.  Sends and receives are stream-ordered NCCL point-to-point
+logits and gathers the vocabulary shards inside its tensor-parallel group.  Every rank runs the same sampler on the
+same request state, but only the last stage has real logits: it samples, and the chosen token ids (a few bytes, not
+the 19 MB of full-vocabulary rows of a 32-row step) are broadcast to the other stages, which drop what they drew
+from their placeholder rows (`sync_sampled`).  Full rows are still broadcast for the steps that need them on every
+rank (log-probabilities, speculative verification).  Between stages the residual stream travels as bf16 on GPUs
+(`LLAMINAR_PP_PAYLOAD`).  Sends and receives are stream-ordered NCCL point-to-point
 operations between ranks with the same tensor-parallel index, so a long prompt that the engine feeds in chunks
 of ``microbatch_tokens`` rows pipelines by itself: stage 0 starts chunk i+1 while stage 1 still works on chunk i
 (reference: src/v2/execution/pipeline/PipelineStageRunner.cpp, src/v2/execution/runner/OrchestrationRunner.cpp:850-922;
@@ -53,9 +57,19 @@ class PipelineStageModel:
         self.next = (stage + 1) * tp_size + tp_index
         self.last_rank = (n_stages - 1) * tp_size + tp_index
         self.scratch = getattr(inner, "scratch", None)
-        self.stats = {"sent_bytes": 0, "recv_bytes": 0, "bcast_bytes": 0}
+        self.stats = {"sent_bytes": 0, "recv_bytes": 0, "bcast_bytes": 0, "token_syncs": 0}
         d = self.cfg.d_model
-        self._recv = torch.empty(getattr(inner, "max_tokens", 4096), d, dtype=torch.float32, device=self.device)
+        from ..utils.env import debug_env
+        mode = str(debug_env().pp_payload).lower()
+        if mode not in ("auto", "bf16", "fp32"):
+            raise ValueError(f"LLAMINAR_PP_PAYLOAD={mode!r}: expected auto, bf16 or fp32")
+        self.payload_dtype = torch.bfloat16 if (mode == "bf16" or (mode == "auto" and self.device.type == "cuda")) else torch.float32
+        rows = getattr(inner, "max_tokens", 4096)
+        self._recv = torch.empty(rows, d, dtype=torch.float32, device=self.device)
+        self._wire = torch.empty(rows, d, dtype=self.payload_dtype, device=self.device) if self.payload_dtype != torch.float32 else None
+        # set by the engine before a forward pass whose rows will be sampled: True = only token ids cross the stages
+        self.token_sync = False
+        self._placeholder = None
 
     def weight_bytes(self) -> int:
         return self.inner.weight_bytes()
@@ -63,8 +77,23 @@ class PipelineStageModel:
     def _n_rows(self, fb: ForwardBatch) -> int:
         return fb.tokens.shape[0]
 
+    def sync_sampled(self, tokens: list[int]) -> list[int]:
+        """The last stage's draw is everybody's: one small broadcast per sampled step."""
+        t = torch.tensor(tokens, dtype=torch.int32, device=self.device)
+        dist.broadcast(t, src=self.last_rank, group=self.pp_group)
+        self.stats["token_syncs"] += 1
+        self.stats["bcast_bytes"] += t.numel() * 4
+        return t.tolist()
+
     def _bcast_logits(self, logits, n_rows: int, logits_out):
         V = self.cfg.vocab_size
+        if self.token_sync:
+            if self.last:
+                full = logits if self.tp is None or self.tp.size == 1 else self.tp.all_gather_vocab(logits, V)
+                return full.contiguous()
+            if self._placeholder is None:
+                self._placeholder = torch.zeros(1, V, dtype=torch.float32, device=self.device)
+            return self._placeholder.expand(n_rows, V)           # never read for its values: `sync_sampled` replaces the draw
         if self.last:
             full = logits if self.tp is None or self.tp.size == 1 else self.tp.all_gather_vocab(logits, V)
             full = full.contiguous()
@@ -82,15 +111,19 @@ class PipelineStageModel:
         T = self._n_rows(fb)
         if not self.first:
             buf = self._recv[:T]
-            dist.recv(buf, src=self.prev)
-            self.stats["recv_bytes"] += buf.numel() * 4
+            if self._wire is None:
+                dist.recv(buf, src=self.prev)
+            else:
+                dist.recv(self._wire[:T], src=self.prev)
+                buf.copy_(self._wire[:T])
+            self.stats["recv_bytes"] += buf.numel() * self.payload_dtype.itemsize
             fb = replace(fb, embeds=buf)
         # the vocabulary shard of the last stage goes through its own buffer; `logits_out` holds full rows
         logits, h = self.inner.forward(fb, kv, want_logits=want_logits and self.last)
         if not self.last:
-            out = h[:T].contiguous()
+            out = h[:T].contiguous() if self._wire is None else h[:T].to(self.payload_dtype)
             dist.send(out, dst=self.next)
-            self.stats["sent_bytes"] += out.numel() * 4
+            self.stats["sent_bytes"] += out.numel() * self.payload_dtype.itemsize
         if want_logits:
             n_rows = T if fb.logit_rows is None else fb.logit_rows.shape[0]
             logits = self._bcast_logits(logits, n_rows, logits_out)

@@ -27,6 +27,7 @@ REGISTRY: tuple[EnvVar, ...] = (
     EnvVar("LLAMINAR_PERF_STATS_FILTER", str, "", "only keep records whose domain/name contains this text"),
     EnvVar("LLAMINAR_TP_FUSED", bool, True, "fuse the row-parallel GEMM with its all-reduce over peer memory"),
     EnvVar("LLAMINAR_ALLREDUCE_PRECISION", str, "auto", "payload of the NCCL tensor-parallel all-reduce: fp32, bf16, fp16 or auto (bf16 for more than 32 rows, fp32 below)"),
+    EnvVar("LLAMINAR_PP_PAYLOAD", str, "auto", "residual stream between pipeline stages: bf16, fp32 or auto (bf16 on GPUs, fp32 on the CPU back end)"),
     EnvVar("LLAMINAR_TP_SPIN_LIMIT", int, 64_000_000, "iterations of the bounded in-kernel wait for a peer (64 ns apiece: about four seconds, so that a host hiccup of one rank does not end the step)"),
     EnvVar("LLAMINAR_COLLECTIVE_ORDER_CHECK", bool, False, "audit that all ranks issue the same collectives in the same order"),
     EnvVar("LLAMINAR_VERIFY_COLLECTIVES", bool, False, "after every all-reduce compare a checksum of the result across ranks (and count NaN/Inf)"),

@@ -13,8 +13,10 @@ def _prompts():
     return [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (17, 90)]
 
 
-def _pp_generate(rank, world, tp_size, mtp):
+def _pp_generate(rank, world, tp_size, mtp, payload="auto"):
+    import os
     import torch.distributed as dist
+    os.environ["LLAMINAR_PP_PAYLOAD"] = payload
     from llaminar_b200.engine.sampling import SamplingParams
     from llaminar_b200.models.synth import synthesize
     from llaminar_b200.parallel.pp import build_pipeline_engine
@@ -53,7 +55,18 @@ def test_pp2_matches_single_rank():
     res = run_ranks(_pp_generate, 2, 1, False)
     assert res[0][0] == ref and res[1][0] == ref
     assert res[0][1]["sent_bytes"] > 0 and res[1][1]["recv_bytes"] == res[0][1]["sent_bytes"]
+    # only token ids cross the stages after sampling: one 4-byte id per sampled row, no full-vocabulary rows
+    assert res[0][1]["token_syncs"] > 0 and res[0][1]["bcast_bytes"] == res[1][1]["bcast_bytes"] < 1024
     assert res[0][2] + res[1][2] == SHAPES["tiny-qwen3"].n_layers
+
+
+def test_pp2_bf16_payload_halves_the_bytes_and_ranks_agree():
+    """The residual stream between the stages as bf16: both stages emit the same tokens (the last stage's draw is
+    broadcast), half the bytes cross; the tokens may differ from the fp32 run by a rounding."""
+    fp32 = run_ranks(_pp_generate, 2, 1, False)
+    bf16 = run_ranks(_pp_generate, 2, 1, False, "bf16")
+    assert bf16[0][0] == bf16[1][0] and all(len(o) == 6 for o in bf16[0][0])
+    assert bf16[0][1]["sent_bytes"] * 2 == fp32[0][1]["sent_bytes"]
 
 
 def test_pp2_tp2_with_mtp_matches_single_rank():
