@@ -100,7 +100,8 @@ class LLMEngine:
         # Every rank of a multi-process engine runs the same scheduler and must reach the same admission, eviction and
         # preemption decisions, so all of them use the smallest page count any rank could afford (free memory differs
         # between GPUs).  `agree_group`: the ranks that step together (default: the tensor-parallel group).
-        kv_pages = self._agree_kv_pages(kv_pages, agree_group if agree_group is not None else (tp.group if tp is not None and tp.size > 1 else None))
+        self._agree_group = agree_group if agree_group is not None else (tp.group if tp is not None and tp.size > 1 else None)
+        kv_pages = self._agree_kv_pages(kv_pages, self._agree_group)
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
                                dtype=torch.bfloat16 if self.is_cuda else (kv_dtype or torch.float32))
         self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
@@ -137,6 +138,20 @@ class LLMEngine:
         lo, hi = int(t[0]), -int(t[1])
         self.kv_pages_per_rank = (lo, hi)              # smallest and largest proposal, for the start-up log
         return lo
+
+    def _agree_min(self, value: int) -> int:
+        """The smallest `value` over the ranks that step together.  Cache decisions go through it: what a prefix lookup finds
+        depends on each rank's own RAM / disk tiers and eviction history, and ranks that reuse different numbers of pages
+        build different batches and meet in different collectives (reference: PrefixCacheCoordinator.cpp:61-96)."""
+        import torch.distributed as dist
+        group = getattr(self, "_agree_group", None)
+        if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return value
+        dev = self.device if dist.get_backend(group) == "nccl" else "cpu"
+        t = torch.tensor([value], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+        self.stats["agreements"] = self.stats.get("agreements", 0) + 1
+        return int(t[0])
 
     @staticmethod
     def from_gguf(path: str, **kw) -> "LLMEngine":
@@ -356,6 +371,8 @@ class LLMEngine:
         hit_pages, hit_tokens = [], 0
         if self.prefix_cache is not None:
             term = self.prefix_cache.lookup_terminal(r.prompt)
+            if not self._agree_min(1 if term is not None else 0):
+                term = None                                   # some rank does not have it: nobody uses it
             if term is not None:
                 try:
                     if self.prefix_cache.restore_terminal(self, r, term):
@@ -367,7 +384,9 @@ class LLMEngine:
                     self.kv.free_sequence(r.kv)
                     r.kv = SequenceKV()
             held, hit_tokens = self.prefix_cache.lookup(r.prompt)      # `held`: one reference per page, dropped below
-            hit_pages = list(held)
+            agreed = self._agree_min(hit_tokens)                       # every rank reuses the same number of pages
+            hit_pages = list(held)[:agreed // PAGE_SIZE]
+            hit_tokens = len(hit_pages) * PAGE_SIZE if agreed < hit_tokens else hit_tokens
         else:
             held = []
         try:

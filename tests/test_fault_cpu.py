@@ -267,3 +267,37 @@ def test_ranks_sharing_a_disk_dir_keep_their_kv_shards_apart(tmp_path):
     import os
     names = os.listdir(tmp_path)
     assert all(n.startswith(out[0][2] + "_") or n.startswith(out[1][2] + "_") for n in names)
+
+
+def _prefix_agreement_case(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.prefix_cache import PrefixCache, PrefixCacheConfig
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=1)
+    tp = TPContext.create(device="cpu")
+    greedy = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    pc = PrefixCache(PrefixCacheConfig(storage="vram", terminal_state="off"), "fp")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, tp=tp, prefix_cache=pc)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, 1024, (200,), generator=g).tolist()
+    first = eng.generate([prompt], greedy)[0]
+    if rank == 1:                                      # this rank's cache loses the second block of the chain
+        from llaminar_b200.engine.prefix_cache import chain_hashes
+        hs = list(chain_hashes(prompt, pc.salt, pc.cfg.block_size))
+        page = pc.device.pop(hs[1])
+        eng.kv.allocator.release(page)
+    before = eng.stats["prefix_hit_tokens"]
+    again = eng.generate([prompt], greedy)[0]
+    return first == again, eng.stats["prefix_hit_tokens"] - before, eng.stats.get("agreements", 0)
+
+
+def test_ranks_agree_on_the_shortest_prefix_hit():
+    """Rank 1 has lost a block that rank 0 still holds: both reuse only what both have (one 64-token block), so both
+    prefill the same rows and stay in the same collectives; the tokens are unchanged."""
+    out = run_ranks(_prefix_agreement_case, 2)
+    assert out[0][0] and out[1][0]
+    assert out[0][1] == out[1][1] == 64
+    assert out[0][2] > 0 and out[0][2] == out[1][2]
