@@ -41,6 +41,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=0, help="0: the model's default (1024 for qwen3-32b, 2048 for qwen3-8b)")
     ap.add_argument("--watchdog-s", type=int, default=1500, help="dump stacks and exit if the run takes longer than this")
+    ap.add_argument("--kv-cache-precision", default="bf16", choices=["bf16", "q8_0"], help="bf16 is the benchmark's setting; q8_0 measures the 8-bit cache")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a valid bench)")
     ap.add_argument("--skip-extras", action="store_true", help="only the headline region (no bs1 / prefill / TTFT)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one instead of replaying a graph")
@@ -301,7 +302,7 @@ def measure(model_name: str, recipe: str, S: int, args, tp, dev, world: int, ran
     t_build = time.time() - t0
     log(f"weights ready in {t_build:.1f} s; building the engine")
     engine = LLMEngine(weights, device=dev, max_batch=B, max_context=S + K + W + 96, max_prefill_tokens=8192, tp=tp,
-                       use_graphs=not args.no_graphs)
+                       use_graphs=not args.no_graphs, kv_dtype="q8_0" if args.kv_cache_precision == "q8_0" else None)
     del weights
     torch.cuda.empty_cache()
     gen = torch.Generator().manual_seed(1)
@@ -456,7 +457,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": f"{model_name} ({recipe}, random-init N(0,0.02) seed 0)", "global_batch": res["B"],
                        "seq_len": res["S"], "decode_ctx_start": res["S"] + 1 + res["W"], "parallelism": f"tp{world}",
-                       "kv_cache": "paged bf16, 64-token pages", "l2": "inputs larger than L2 (weights stream from HBM every step)",
+                       "kv_cache": f"paged {args.kv_cache_precision}, 64-token pages", "l2": "inputs larger than L2 (weights stream from HBM every step)",
                        "layers": res["layers"], "weight_bytes_per_gpu": res["weight_bytes"],
                        "fused_tp_calls": res["fused_tp_calls"]},
             "e2e": {"value": round(res["e2e"], 2), "unit": "tok/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},

@@ -146,6 +146,9 @@ def build_engine(cfg: OrchestrationConfig):
               eos_token_id=eos)
     if torch.device(dev).type == "cpu" and "kv_cache_precision" in cfg.explicitly_set:
         kw["kv_dtype"] = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[v["kv_cache_precision"]]
+    elif v.get("kv_cache_precision") in ("q8_0", "q8_1"):
+        from .engine.kv_cache import Q8
+        kw["kv_dtype"] = Q8           # int8 values with an fp16 scale per 32 (the reference's q8_1 also stores block sums, which this layout does not need)
     if layout["pp"] > 1:
         from .parallel.pp import build_pipeline_engine
         engine = build_pipeline_engine(weights, layout, rank, **kw)

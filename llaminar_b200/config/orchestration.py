@@ -80,7 +80,7 @@ OPTIONS: list[OptionSpec] = [
        help="plan: find the smallest pp x tp placement on up to N GPUs that fits their memory and print its flags"),
     # -- precision ------------------------------------------------------------------------------------------
     _o("--activation-precision", default="bf16", choices=("bf16", "fp32", "fp16"), category="precision"),
-    _o("--kv-cache-precision", default="bf16", choices=("bf16", "fp16", "fp32", "q8_1", "tq4", "tq8"), category="precision"),
+    _o("--kv-cache-precision", default="bf16", choices=("bf16", "fp16", "fp32", "q8_0", "q8_1", "tq4", "tq8"), category="precision"),
     # -- MoE ------------------------------------------------------------------------------------------------
     _o("--moe-expert-mode", default="expert-parallel", choices=("expert-parallel", "tensor-parallel", "replicated"), category="moe"),
     _o("--moe-overlay", category="moe", unsupported="CPU/GPU expert overlay tiers are not built"),
@@ -463,8 +463,10 @@ def validate(cfg: OrchestrationConfig) -> list[str]:
         errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: the CUDA kernels keep the KV cache in bf16 (fp16 / fp32 are available with -d cpu)")
     if not on_cpu and v.get("activation_precision") in ("fp16", "fp32") and "activation_precision" in ex:
         errs.append(f"--activation-precision {v['activation_precision']}: the CUDA path uses bf16 GEMM operands with an fp32 residual stream (fp32 is available with -d cpu)")
-    if v.get("kv_cache_precision") in ("q8_1", "tq4", "tq8"):
-        errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: quantised KV caches are not built (bf16/fp16/fp32)")
+    if v.get("kv_cache_precision") in ("tq4", "tq8"):
+        errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: the turbo-quantised KV caches are not built (bf16 / q8_0 on GPUs, bf16 / fp16 / fp32 with -d cpu)")
+    if on_cpu and v.get("kv_cache_precision") in ("q8_0", "q8_1"):
+        errs.append(f"--kv-cache-precision {v['kv_cache_precision']}: the 8-bit KV cache is a CUDA feature (bf16 / fp16 / fp32 with -d cpu)")
     if not 1 <= int(v.get("mtp_draft_tokens") or 1) <= 3:
         errs.append("--mtp-draft-tokens must be between 1 and 3")
     if int(v.get("prefix_cache_block_size") or 64) % 64:

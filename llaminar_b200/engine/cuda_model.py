@@ -71,6 +71,7 @@ class ForwardBatch:
     # prefill-style attention
     cu_q: torch.Tensor | None = None         # [B + 1]
     ctx_lens: torch.Tensor | None = None     # [B]
+    max_kv_len: int = 0                      # prefill: longest context + chunk of the batch (0: unknown, assume the table width)
     max_q_len: int = 0
     # which hidden rows get logits (None: all rows)
     logit_rows: torch.Tensor | None = None
@@ -372,9 +373,34 @@ class CudaModel:
             ops.attn_decode(q, kv_layer, o3, fb.block_table, fb.seq_lens, self.n_heads_local, self.n_kv_local,
                             c.head_dim, fb.rows_per_seq, scale, fb.n_splits, self.scratch)
         else:
-            ops.attn_prefill(q, kv_layer, o3, fb.block_table, fb.cu_q, fb.ctx_lens, self.n_heads_local,
+            kv_bf16, btab = self._kv_for_prefill(fb, kv_layer)
+            ops.attn_prefill(q, kv_bf16, o3, btab, fb.cu_q, fb.ctx_lens, self.n_heads_local,
                              self.n_kv_local, c.head_dim, scale, fb.max_q_len, scratch=self.scratch)
         return o
+
+    def _kv_for_prefill(self, fb: ForwardBatch, kv_layer: torch.Tensor):
+        """The prefill kernels read bf16 pages.  With the 8-bit cache the pages of the chunk's sequences (context and the rows
+        just appended) are expanded into a staging pool that is reused layer after layer, and the kernels get a block table
+        into that pool.  Decode reads the 8-bit pages directly."""
+        if kv_layer.dtype != torch.uint8:
+            return kv_layer, fb.block_table
+        c = self.cfg
+        B, P = fb.block_table.shape
+        if fb.max_kv_len:
+            P = min(P, (fb.max_kv_len + 63) // 64)
+        st = getattr(self, "_q8_prefill", None)
+        if st is None or st["fb"] is not fb:
+            n_tok = (fb.ctx_lens + (fb.cu_q[1:] - fb.cu_q[:-1])).to(torch.int32)
+            st = {"fb": fb, "n_tok": n_tok, "bt": fb.block_table[:, :P].contiguous(),
+                  "bt2": torch.arange(B * P, dtype=torch.int32, device=self.device).view(B, P)}
+            self._q8_prefill = st
+        need = B * P
+        pool = getattr(self, "_q8_pool", None)
+        if pool is None or pool.shape[0] < need:
+            pool = torch.empty(need, 2, self.n_kv_local, 64, c.head_dim, dtype=torch.bfloat16, device=self.device)
+            self._q8_pool = pool
+        ops.kv_dequant_pages(kv_layer, st["bt"], st["n_tok"], self.n_kv_local, c.head_dim, pool)
+        return pool, st["bt2"]
 
     def _row_parallel_resid(self, lin: QLinear, x: torch.Tensor, h: torch.Tensor) -> None:
         """h += x @ W^T, summed over tensor-parallel ranks."""

@@ -19,6 +19,7 @@ from ..models.config import ModelConfig
 from ..models.weights import ModelWeights
 from .cuda_model import ForwardBatch
 from .kv_cache import PAGE_SIZE, OutOfPages, PagedKVCache, SequenceKV
+from .kv_cache import Q8 as KV_Q8
 from .sampling import SamplingParams, apply_penalties, sample_row
 from ..utils.env import debug_env
 from ..utils.perfstats import perf_stats
@@ -87,13 +88,15 @@ class LLMEngine:
         else:
             from .torch_model import TorchPagedModel
             self.model = TorchPagedModel(weights, self.device, tp=tp)
+        if kv_dtype == KV_Q8 and not self.is_cuda:
+            raise ValueError("the 8-bit KV cache is a CUDA feature (the CPU back end takes bf16 / fp16 / fp32)")
         self.max_pages_per_seq = (max_context + PAGE_SIZE - 1) // PAGE_SIZE + 1
         n_kv_layers = getattr(self.model, "n_kv_layers", c.n_layers + c.nextn_layers)
         if kv_pages is None:
             need = max_batch * self.max_pages_per_seq + 64
             if self.is_cuda:
                 free, _ = torch.cuda.mem_get_info(self.device)
-                per_page = PagedKVCache.bytes_per_page(n_kv_layers, self.model.n_kv_local, c.head_dim)
+                per_page = PagedKVCache.bytes_per_page(n_kv_layers, self.model.n_kv_local, c.head_dim, 17 / 16 if kv_dtype == KV_Q8 else 2)
                 kv_pages = int(min(need * 2, max(need // 4, int(free * kv_memory_fraction) // per_page)))
             else:
                 kv_pages = need
@@ -103,7 +106,7 @@ class LLMEngine:
         self._agree_group = agree_group if agree_group is not None else (tp.group if tp is not None and tp.size > 1 else None)
         kv_pages = self._agree_kv_pages(kv_pages, self._agree_group)
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
-                               dtype=torch.bfloat16 if self.is_cuda else (kv_dtype or torch.float32))
+                               dtype=(KV_Q8 if kv_dtype == KV_Q8 else torch.bfloat16) if self.is_cuda else (kv_dtype or torch.float32))
         self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
         self.perf = perf_stats()
         self._graphs: dict = {}
@@ -617,6 +620,7 @@ class LLMEngine:
             logit_rows = [row for _, row in rows_for if row is not None]
             fb = ForwardBatch(tokens=it(toks), positions=it(pos), seq_ids=it(sid), block_table=bt.to(dev), cu_q=it(cu),
                               ctx_lens=it(ctx), max_q_len=max(cu[i + 1] - cu[i] for i in range(len(ctx))),
+                              max_kv_len=max(ctx[i] + cu[i + 1] - cu[i] for i in range(len(ctx))),
                               logit_rows=it(logit_rows) if logit_rows else None)
             logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
             if self.mtp is not None:

@@ -60,18 +60,30 @@ class SequenceKV:
         return len(self.pages) * PAGE_SIZE
 
 
+Q8 = "q8_0"          # 8-bit cache: int8 values with one fp16 scale per 32 (CUDA back end; reference: CUDARingKVCache.cu:405)
+
+
 class PagedKVCache:
     def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, n_pages: int, device, dtype=torch.bfloat16):
         self.n_layers, self.n_kv_heads, self.head_dim, self.n_pages = n_layers, n_kv_heads, head_dim, n_pages
         self.device = torch.device(device)
-        # zero-filled: masked-out positions are multiplied by zero probabilities, so they must stay finite
-        self.layers = [torch.zeros(n_pages, 2, n_kv_heads, PAGE_SIZE, head_dim, dtype=dtype, device=device)
-                       for _ in range(n_layers)]
+        self.q8 = dtype == Q8
+        if self.q8:
+            # a page is [2][n_kv_heads][64][head_dim] int8 followed by [2][n_kv_heads][64][head_dim / 32] fp16 block scales;
+            # zero bytes decode to zeros, so untouched positions stay finite
+            if head_dim % 32:
+                raise ValueError("the 8-bit KV cache needs a head dimension that is a multiple of 32")
+            data = 2 * n_kv_heads * PAGE_SIZE * head_dim
+            self.layers = [torch.zeros(n_pages, data + data // 16, dtype=torch.uint8, device=device) for _ in range(n_layers)]
+        else:
+            # zero-filled: masked-out positions are multiplied by zero probabilities, so they must stay finite
+            self.layers = [torch.zeros(n_pages, 2, n_kv_heads, PAGE_SIZE, head_dim, dtype=dtype, device=device)
+                           for _ in range(n_layers)]
         self.allocator = PageAllocator(n_pages)
 
     @staticmethod
-    def bytes_per_page(n_layers: int, n_kv_heads: int, head_dim: int, itemsize: int = 2) -> int:
-        return n_layers * 2 * n_kv_heads * PAGE_SIZE * head_dim * itemsize
+    def bytes_per_page(n_layers: int, n_kv_heads: int, head_dim: int, itemsize: float = 2) -> int:
+        return int(n_layers * 2 * n_kv_heads * PAGE_SIZE * head_dim * itemsize)
 
     def ensure_capacity(self, seq: SequenceKV, n_tokens: int) -> None:
         """Grow the page table so that ``n_tokens`` positions fit."""

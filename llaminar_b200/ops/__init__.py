@@ -264,6 +264,14 @@ def attn_prefill(q, kv, out, block_table, cu_q, ctx_lens, n_heads, n_kv_heads, h
     _count()
 
 
+def kv_dequant_pages(kv8: torch.Tensor, block_table: torch.Tensor, n_tokens: torch.Tensor, n_kv_heads: int, head_dim: int,
+                     staging: torch.Tensor) -> None:
+    """8-bit KV pages of the sequences in ``block_table`` -> bf16 pages: page j of sequence s lands at staging page
+    ``s * block_table.shape[1] + j`` (only pages that hold one of the sequence's ``n_tokens[s]`` tokens are written)."""
+    ext().kv_dequant_pages(kv8, block_table, n_tokens, n_kv_heads, head_dim, staging)
+    _count()
+
+
 ATTN_TC_MIN_ROWS = 1536
 _ATTN_TC = None
 

@@ -41,6 +41,19 @@ LLM_DEVICE void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uin
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+LLM_DEVICE void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <bool F16> LLM_DEVICE void mma_16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (F16) mma_f16(c, a, b0, b1); else mma_bf16(c, a, b0, b1);
+}
+LLM_DEVICE uint32_t pack_f16(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // One 16-key x D sub-tile of K or V: row stride D*2 bytes, 16-byte units swizzled by (row & 7).
 template <int D>
 LLM_DEVICE uint32_t tile_addr(uint32_t base, int row, int unit) {
@@ -48,7 +61,7 @@ LLM_DEVICE uint32_t tile_addr(uint32_t base, int row, int unit) {
 }
 
 // S(16 x 16 keys) = Q(16 x D) K^T for one warp;  qa: the warp's Q fragments, kbase: 16 swizzled key rows
-template <int D>
+template <int D, bool F16 = false>
 LLM_DEVICE void qk_16keys(const uint32_t (&qa)[D / 16][4], uint32_t kbase, int lane, float (&s)[2][4]) {
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
@@ -60,13 +73,13 @@ LLM_DEVICE void qk_16keys(const uint32_t (&qa)[D / 16][4], uint32_t kbase, int l
     for (int ks = 0; ks < D / 16; ++ks) {
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(tile_addr<D>(kbase, key, 2 * ks + (mat & 1)), b0, b1, b2, b3);
-        mma_bf16(s[0], qa[ks], b0, b1);
-        mma_bf16(s[1], qa[ks], b2, b3);
+        mma_16<F16>(s[0], qa[ks], b0, b1);
+        mma_16<F16>(s[1], qa[ks], b2, b3);
     }
 }
 
 // O(16 x D) += P(16 x 16 keys) V(16 keys x D)
-template <int D>
+template <int D, bool F16 = false>
 LLM_DEVICE void pv_16keys(const uint32_t (&pa)[4], uint32_t vbase, int lane, float (&o)[D / 8][4]) {
     const int mat = lane >> 3, r = lane & 7;
     const int key = (mat & 1) * 8 + r;
@@ -74,23 +87,47 @@ LLM_DEVICE void pv_16keys(const uint32_t (&pa)[4], uint32_t vbase, int lane, flo
     for (int c = 0; c < D / 16; ++c) {
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(tile_addr<D>(vbase, key, 2 * c + (mat >> 1)), b0, b1, b2, b3);
-        mma_bf16(o[2 * c], pa, b0, b1);
-        mma_bf16(o[2 * c + 1], pa, b2, b3);
+        mma_16<F16>(o[2 * c], pa, b0, b1);
+        mma_16<F16>(o[2 * c + 1], pa, b2, b3);
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // decode
 // ------------------------------------------------------------------------------------------------
-template <int D>
+// Q8: the cache holds int8 rows + fp16 block scales (AttnDecodeParams).  The cp.async ring then carries the raw bytes (half
+// the traffic) and the warp expands each 16-key sub-tile into one 16-bit work tile of the layout the MMAs read (fp16: see
+// q8_unit_to_f16).
+template <int D, bool Q8>
 struct DecodeSmem {
-    static constexpr int STAGES = 3;
-    static constexpr int SUB = 16 * D * 2;                   // bytes of a 16-key K (or V) sub-tile
-    static constexpr int PER_WARP = STAGES * 2 * SUB;
-    static constexpr int BYTES = 4 * PER_WARP;
+    static constexpr int STAGES = Q8 ? 2 : 3;                // 8-bit: two raw stages keep the CTA small enough for three per SM
+    static constexpr int SUB = 16 * D * 2;                   // bytes of a 16-key K (or V) sub-tile in 16-bit form
+    static constexpr int RAW_SUB = 16 * D;                   // the same rows as int8
+    static constexpr int RAW_SC = 16 * (D / 32) * 2;         // their block scales
+    static constexpr int RAW_STAGE = 2 * (RAW_SUB + RAW_SC);
+    static constexpr int PER_WARP = Q8 ? STAGES * RAW_STAGE + 2 * SUB : STAGES * 2 * SUB;
+    static constexpr int MERGE = 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
+    static constexpr int BYTES = 4 * PER_WARP > MERGE ? 4 * PER_WARP : MERGE;
 };
 
-template <int D>
+// 16 int8 values (four words) times one scale -> 16 fp16 (eight packed pairs), one PRMT and one HFMA2 per pair: a byte
+// b ^ 0x80 under the high byte 0x64 is the fp16 number 1024 + 128 + x (fp16 carries 10 mantissa bits, so that is exact), and
+// (1152 + x) * s - 1152 * s = x * s: the FMA is exact inside and 1152 * s is an fp16 number because the scales are stored
+// with seven mantissa bits (rope_kv).  The 8-bit path therefore multiplies in fp16 (Q and the probabilities are converted
+// to fp16 as well); sums stay in fp32.
+LLM_DEVICE void q8_unit_to_f16(const uint4& w, __half2 sc2, __half2 off2, uint32_t (&o)[8]) {
+    const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = __byte_perm(ws[k], 0x64646464u, 0x4140), hi = __byte_perm(ws[k], 0x64646464u, 0x4342);
+        const __half2 r0 = __hfma2(*reinterpret_cast<const __half2*>(&lo), sc2, off2);
+        const __half2 r1 = __hfma2(*reinterpret_cast<const __half2*>(&hi), sc2, off2);
+        o[2 * k] = *reinterpret_cast<const uint32_t*>(&r0);
+        o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&r1);
+    }
+}
+
+template <int D, bool Q8>
 __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_trigger();
@@ -103,8 +140,9 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
     const int per = (n_pages + gridDim.y - 1) / gridDim.y;
     const int pg0 = split * per, pg1 = min(n_pages, pg0 + per);
     const int* btab = p.block_table + (size_t)seq * p.max_pages;
-    using SM = DecodeSmem<D>;
+    using SM = DecodeSmem<D, Q8>;
     const uint32_t wbase = smem_u32(smem) + warp * SM::PER_WARP;
+    const uint32_t work_k = wbase + SM::STAGES * SM::RAW_STAGE, work_v = work_k + SM::SUB;      // Q8 only: the expanded sub-tiles
 
     // Q fragments: MMA row i <-> (verify row r = i / G, q head g = i % G)
     uint32_t qa[D / 16][4];
@@ -124,6 +162,10 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
             qa[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + d0) : 0u;
             qa[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + d0 + 8) : 0u;
             qa[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + d0 + 8) : 0u;
+            if (Q8) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) qa[ks][j] = pack_f16(bf16_lo(qa[ks][j]), bf16_hi(qa[ks][j]));
+            }
         }
     }
     // causal limit per MMA row: verify row r sees keys < seq_len - (R - 1 - r)
@@ -139,6 +181,28 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
     const float sl2 = p.scale * 1.4426950408889634f;
 
     auto issue = [&](int pg, int stage) {
+        if (Q8) {
+            if (pg < pg1) {
+                const size_t page = (size_t)LLM_CHECK_INDEX(btab[pg], p.n_pages);
+                const uint8_t* pgp = reinterpret_cast<const uint8_t*>(p.kv) + page * p.page_bytes;
+                const size_t rk = ((size_t)0 * p.n_kv_heads + kvh) * PAGE + (size_t)warp * 16, rv = ((size_t)1 * p.n_kv_heads + kvh) * PAGE + (size_t)warp * 16;
+                const uint8_t *kp = pgp + rk * D, *vp = pgp + rv * D;
+                const uint8_t *ks = pgp + p.scale_off + rk * (D / 32) * 2, *vs = pgp + p.scale_off + rv * (D / 32) * 2;
+                const uint32_t rb = wbase + stage * SM::RAW_STAGE;        // [K rows][V rows][K scales][V scales]
+#pragma unroll
+                for (int t = 0; t < SM::RAW_SUB / 16 / 32; ++t) {
+                    const int idx = t * 32 + lane;
+                    cp_async16(rb + idx * 16, kp + idx * 16);
+                    cp_async16(rb + SM::RAW_SUB + idx * 16, vp + idx * 16);
+                }
+                if (lane < SM::RAW_SC / 16) {
+                    cp_async16(rb + 2 * SM::RAW_SUB + lane * 16, ks + lane * 16);
+                    cp_async16(rb + 2 * SM::RAW_SUB + SM::RAW_SC + lane * 16, vs + lane * 16);
+                }
+            }
+            cp_async_commit();
+            return;
+        }
         if (pg < pg1) {
             const size_t page = (size_t)LLM_CHECK_INDEX(btab[pg], p.n_pages);
             const __nv_bfloat16* kp = p.kv + ((page * 2 + 0) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)warp * 16 * D;
@@ -162,9 +226,42 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
         issue(pg + SM::STAGES - 1, (pg - pg0 + SM::STAGES - 1) % SM::STAGES);
         cp_async_wait<SM::STAGES - 1>();
         __syncwarp();
-        const uint32_t kb = wbase + stage * 2 * SM::SUB, vb = kb + SM::SUB;
+        uint32_t kb = wbase + stage * 2 * SM::SUB, vb = kb + SM::SUB;
+        if (Q8) {
+            // expand this stage's raw rows into the work tiles: unit idx = 16 consecutive values of row idx / (D / 16)
+            const uint32_t rb = wbase + stage * SM::RAW_STAGE;
+            constexpr int UPR8 = D / 16, NU = 16 * UPR8 / 32;
+            // all loads first (they pipeline in the shared-memory unit), then the arithmetic and the stores
+            uint4 w[2][NU];
+            uint16_t hs[2][NU];
+#pragma unroll
+            for (int t = 0; t < NU; ++t) {
+                const int idx = t * 32 + lane, row = idx / UPR8, u = idx % UPR8;
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[kv][t].x), "=r"(w[kv][t].y), "=r"(w[kv][t].z), "=r"(w[kv][t].w)
+                                 : "r"(rb + kv * SM::RAW_SUB + idx * 16));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(hs[kv][t]) : "r"(rb + 2 * SM::RAW_SUB + kv * SM::RAW_SC + (row * (D / 32) + (u >> 1)) * 2));
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < NU; ++t) {
+                const int idx = t * 32 + lane, row = idx / UPR8, u = idx % UPR8;
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    uint32_t o[8];
+                    const __half hsc = __ushort_as_half(hs[kv][t]);
+                    q8_unit_to_f16(w[kv][t], __half2half2(hsc), __half2half2(__hmul(hsc, __float2half_rn(-1152.0f))), o);
+                    const uint32_t dst = kv ? work_v : work_k;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr<D>(dst, row, 2 * u)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr<D>(dst, row, 2 * u + 1)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                }
+            }
+            __syncwarp();
+            kb = work_k; vb = work_v;
+        }
         float s[2][4];
-        qk_16keys<D>(qa, kb, lane, s);
+        qk_16keys<D, Q8>(qa, kb, lane, s);
         const int key0 = pg * PAGE + warp * 16 + (lane & 3) * 2;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -197,9 +294,14 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const AttnDecode
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
         uint32_t pa[4];
-        pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
-        pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
-        pv_16keys<D>(pa, vb, lane, o);
+        if (Q8) {
+            pa[0] = pack_f16(s[0][0], s[0][1]); pa[1] = pack_f16(s[0][2], s[0][3]);
+            pa[2] = pack_f16(s[1][0], s[1][1]); pa[3] = pack_f16(s[1][2], s[1][3]);
+        } else {
+            pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
+        }
+        pv_16keys<D, Q8>(pa, vb, lane, o);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -288,20 +390,28 @@ cudaError_t launch_attn_decode(const AttnDecodeParams& p, int batch, int n_split
     const int G = p.n_heads / p.n_kv_heads;
     if (G * p.rows_per_seq > 16 || p.n_heads % p.n_kv_heads) return cudaErrorInvalidValue;
     dim3 grid(p.n_kv_heads, n_splits, batch);
+    if (p.kv_q8 && (p.page_bytes % 16 || p.scale_off % 16)) return cudaErrorInvalidValue;     // 16-byte cp.async units
+    auto go = [&](auto kernel, int smem) -> cudaError_t {
+        static const void* done[8] = {};                     // kernels whose shared-memory limit has been raised
+        const void* key = reinterpret_cast<const void*>(kernel);
+        bool seen = false;
+        for (const void* d : done) seen = seen || d == key;
+        if (!seen) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return e;
+            for (const void*& d : done) if (!d) { d = key; break; }
+        }
+        return launch_pdl(kernel, grid, dim3(128), smem, st, p);
+    };
+    constexpr int SLACK = 1024;
     if (p.head_dim == 128) {
-        constexpr int smem = DecodeSmem<128>::BYTES;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(paged_attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
-        return launch_pdl(paged_attn_decode_kernel<128>, grid, dim3(128), smem, st, p);
+        if (p.kv_q8) return go(paged_attn_decode_kernel<128, true>, DecodeSmem<128, true>::BYTES + SLACK);
+        return go(paged_attn_decode_kernel<128, false>, DecodeSmem<128, false>::BYTES + SLACK);
     } else if (p.head_dim == 64) {
-        constexpr int smem = DecodeSmem<64>::BYTES < 4 * 16 * 64 * 4 + 1024 ? 4 * 16 * 64 * 4 + 1024 : DecodeSmem<64>::BYTES;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(paged_attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
-        return launch_pdl(paged_attn_decode_kernel<64>, grid, dim3(128), smem, st, p);
-    } else {
-        return cudaErrorInvalidValue;
+        if (p.kv_q8) return go(paged_attn_decode_kernel<64, true>, DecodeSmem<64, true>::BYTES + SLACK);
+        return go(paged_attn_decode_kernel<64, false>, DecodeSmem<64, false>::BYTES + SLACK);
     }
-    return cudaGetLastError();
+    return cudaErrorInvalidValue;
 }
 
 // ------------------------------------------------------------------------------------------------

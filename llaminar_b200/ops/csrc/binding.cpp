@@ -238,6 +238,13 @@ static void rope_kv(Tensor qkv, Tensor q_out, Tensor kv, const OptTensor& q_norm
     llm::RopeKVParams p{};
     p.qkv = static_cast<__nv_bfloat16*>(qkv.data_ptr()); p.q_out = static_cast<__nv_bfloat16*>(q_out.data_ptr());
     p.kv = static_cast<__nv_bfloat16*>(kv.data_ptr());
+    if (kv.scalar_type() == torch::kUInt8) {           // 8-bit cache: [n_pages, page_bytes]
+        TORCH_CHECK(kv.dim() == 2, "an 8-bit KV layer is [n_pages, page_bytes]");
+        p.kv_q8 = 1; p.page_bytes = (size_t)kv.size(1); p.scale_off = (size_t)2 * n_kv_heads * 64 * head_dim;
+        TORCH_CHECK(p.page_bytes == p.scale_off + p.scale_off / 16, "8-bit KV page size does not match heads x head_dim");
+    } else {
+        TORCH_CHECK(kv.scalar_type() == torch::kBFloat16, "KV cache must be bf16 or 8-bit");
+    }
     p.q_norm = cptr<float>(q_norm); p.k_norm = cptr<float>(k_norm);
     p.positions = static_cast<const int*>(positions.data_ptr()); p.seq_ids = static_cast<const int*>(seq_ids.data_ptr());
     p.block_table = static_cast<const int*>(block_table.data_ptr());
@@ -245,6 +252,24 @@ static void rope_kv(Tensor qkv, Tensor q_out, Tensor kv, const OptTensor& q_norm
     p.max_pages = (int)block_table.size(1); p.theta = (float)theta; p.eps = (float)eps;
     p.n_pages = (int)kv.size(0); p.n_seqs = (int)block_table.size(0);
     LLM_CUDA_CHECK(llm::launch_rope_kv(p, cur_stream()));
+}
+
+// 8-bit KV pages of the sequences in `block_table` -> bf16 staging pages (page j of sequence s at staging[s * max_pages + j])
+static void kv_dequant_pages(const Tensor& kv8, const Tensor& block_table, const Tensor& n_tokens, int64_t n_kv_heads, int64_t head_dim,
+                             Tensor staging) {
+    check_cuda(kv8, "kv8"); check_cuda(staging, "staging");
+    const c10::cuda::CUDAGuard guard(kv8.device());
+    TORCH_CHECK(kv8.scalar_type() == torch::kUInt8 && kv8.dim() == 2 && kv8.is_contiguous());
+    TORCH_CHECK(block_table.scalar_type() == torch::kInt32 && block_table.dim() == 2 && block_table.is_contiguous());
+    TORCH_CHECK(n_tokens.scalar_type() == torch::kInt32 && n_tokens.numel() == block_table.size(0));
+    TORCH_CHECK(staging.scalar_type() == torch::kBFloat16 && staging.is_contiguous());
+    const size_t scale_off = (size_t)2 * n_kv_heads * 64 * head_dim;
+    TORCH_CHECK((size_t)kv8.size(1) == scale_off + scale_off / 16, "8-bit KV page size does not match heads x head_dim");
+    TORCH_CHECK(staging.numel() >= block_table.numel() * (int64_t)scale_off, "staging pool too small");
+    LLM_CUDA_CHECK(llm::launch_kv_dequant_pages(static_cast<const uint8_t*>(kv8.data_ptr()), (size_t)kv8.size(1), scale_off,
+                                                static_cast<const int*>(block_table.data_ptr()), static_cast<const int*>(n_tokens.data_ptr()),
+                                                (int)block_table.size(0), (int)block_table.size(1), (int)n_kv_heads, (int)head_dim, (int)kv8.size(0),
+                                                static_cast<__nv_bfloat16*>(staging.data_ptr()), cur_stream()));
 }
 
 static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Tensor& block_table, const Tensor& seq_lens,
@@ -255,6 +280,13 @@ static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Ten
     const int batch = (int)seq_lens.numel();
     llm::AttnDecodeParams p{};
     p.q = static_cast<const __nv_bfloat16*>(q.data_ptr()); p.kv = static_cast<const __nv_bfloat16*>(kv.data_ptr());
+    if (kv.scalar_type() == torch::kUInt8) {
+        TORCH_CHECK(kv.dim() == 2, "an 8-bit KV layer is [n_pages, page_bytes]");
+        p.kv_q8 = 1; p.page_bytes = (size_t)kv.size(1); p.scale_off = (size_t)2 * n_kv_heads * 64 * head_dim;
+        TORCH_CHECK(p.page_bytes == p.scale_off + p.scale_off / 16, "8-bit KV page size does not match heads x head_dim");
+    } else {
+        TORCH_CHECK(kv.scalar_type() == torch::kBFloat16, "KV cache must be bf16 or 8-bit");
+    }
     p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
     p.block_table = static_cast<const int*>(block_table.data_ptr()); p.seq_lens = static_cast<const int*>(seq_lens.data_ptr());
     p.part_o = mptr<float>(part_o); p.part_ml = mptr<float>(part_ml); p.tickets = mptr<unsigned>(tickets);
@@ -533,6 +565,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("bounds_check_build") = false;
 #endif
     m.def("gemv", &gemv);
+    m.def("kv_dequant_pages", &kv_dequant_pages);
     m.def("moe_route", &moe_route);
     m.def("moe_gemv", &moe_gemv);
     m.def("moe_route_only", &moe_route_only);

@@ -227,6 +227,44 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKVParams p) {
         const int seq = LLM_CHECK_INDEX(p.seq_ids[t], p.n_seqs);
         const int slot = LLM_CHECK_INDEX(pos / PAGE, p.max_pages);
         const size_t page = (size_t)LLM_CHECK_INDEX(p.block_table[(size_t)seq * p.max_pages + slot], p.n_pages);
+        if (p.kv_q8) {
+            // 8-bit cache: one fp16 scale per 32 values (amax / 127), values rounded to nearest.  This lane's values sit in
+            // blocks (lane * EPL) / 32 of the first half and the same block of the second half; the lanes of a block are
+            // 32 / EPL neighbours.
+            constexpr int GROUP = 32 / EPL;
+            float ma = 0.f, mb = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { ma = fmaxf(ma, fabsf(a[e])); mb = fmaxf(mb, fabsf(b[e])); }
+#pragma unroll
+            for (int o = 1; o < GROUP; o <<= 1) {
+                ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+                mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+            }
+            // The stored scale is amax / 127 rounded UP to seven mantissa bits (no value clips; the values are quantised with
+            // the stored scale).  Seven bits because the decode kernel expands a byte as (1152 + x) * s - 1152 * s in one fp16
+            // FMA, and 1152 * s = 9 * s * 2^7 is exact in fp16 only if s carries at most seven bits.
+            auto scale7 = [](float amax) {
+                const uint32_t b = (__float_as_uint(amax * (1.0f / 127.0f)) + 0xFFFFu) & 0xFFFF0000u;
+                return __uint_as_float(b);
+            };
+            const __half ha = __float2half_rn(scale7(ma)), hb = __float2half_rn(scale7(mb));
+            const float da = __half2float(ha), db = __half2float(hb);
+            const float ia = da > 0.f ? 1.0f / da : 0.f, ib = db > 0.f ? 1.0f / db : 0.f;
+            uint8_t* pg = reinterpret_cast<uint8_t*>(p.kv) + page * p.page_bytes;
+            const size_t row = ((size_t)(is_k ? 0 : 1) * p.n_kv_heads + kvh) * PAGE + (size_t)(pos % PAGE);
+            int8_t* d8 = reinterpret_cast<int8_t*>(pg + row * D);
+            __half* sc = reinterpret_cast<__half*>(pg + p.scale_off + row * (D / 32) * 2);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                d8[lane * EPL + e] = (int8_t)max(-127, min(127, __float2int_rn(a[e] * ia)));
+                d8[D / 2 + lane * EPL + e] = (int8_t)max(-127, min(127, __float2int_rn(b[e] * ib)));
+            }
+            if ((lane & (GROUP - 1)) == 0) {
+                sc[(lane * EPL) / 32] = ha;
+                sc[(D / 2 + lane * EPL) / 32] = hb;
+            }
+            return;
+        }
         dst = p.kv + ((page * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh) * (size_t)(PAGE * D) + (size_t)(pos % PAGE) * D;
     }
 #pragma unroll
@@ -244,6 +282,46 @@ cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st) {
     else if (p.head_dim == 64) return launch_pdl(rope_kv_kernel<64>, dim3(grid), dim3(128), 0, st, p);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// 8-bit KV pages -> bf16 pages (the prefill kernels read bf16): one CTA per (page slot, sequence), one 16-byte unit of
+// 16 values per thread and step
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) kv_dequant_pages_kernel(const uint8_t* __restrict__ kv8, size_t page_bytes, size_t scale_off,
+                                                               const int* __restrict__ block_table, const int* __restrict__ n_tokens, int max_pages,
+                                                               int n_kv_heads, int head_dim, int n_pages, __nv_bfloat16* __restrict__ staging) {
+    pdl_trigger();
+    pdl_wait();
+    const int j = blockIdx.x, s = blockIdx.y;
+    if (j * PAGE >= n_tokens[s]) return;
+    const size_t page = (size_t)LLM_CHECK_INDEX(block_table[(size_t)s * max_pages + j], n_pages);
+    const uint8_t* pg = kv8 + page * page_bytes;
+    const int rows = 2 * n_kv_heads * PAGE, upr = head_dim / 16;           // 16-value units per row
+    __nv_bfloat16* out = staging + ((size_t)s * max_pages + j) * (size_t)rows * head_dim;
+    for (int idx = threadIdx.x; idx < rows * upr; idx += blockDim.x) {
+        const int row = idx / upr, u = idx - row * upr;
+        const uint4 w = *reinterpret_cast<const uint4*>(pg + (size_t)row * head_dim + u * 16);
+        const float sc = __half2float(*reinterpret_cast<const __half*>(pg + scale_off + ((size_t)row * (head_dim / 32) + (u >> 1)) * 2));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int8_t b0 = (int8_t)(ws[k] & 0xff), b1 = (int8_t)((ws[k] >> 8) & 0xff), b2 = (int8_t)((ws[k] >> 16) & 0xff), b3 = (int8_t)(ws[k] >> 24);
+            o[2 * k] = pack_bf16(sc * b0, sc * b1);
+            o[2 * k + 1] = pack_bf16(sc * b2, sc * b3);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * head_dim + u * 16);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+cudaError_t launch_kv_dequant_pages(const uint8_t* kv8, size_t page_bytes, size_t scale_off, const int* block_table, const int* n_tokens,
+                                    int n_seqs, int max_pages, int n_kv_heads, int head_dim, int n_pages, __nv_bfloat16* staging, cudaStream_t st) {
+    if (n_seqs == 0 || max_pages == 0) return cudaSuccess;
+    if (head_dim % 32 != 0) return cudaErrorInvalidValue;
+    return launch_pdl(kv_dequant_pages_kernel, dim3(max_pages, n_seqs), dim3(256), 0, st, kv8, page_bytes, scale_off, block_table, n_tokens,
+                      max_pages, n_kv_heads, head_dim, n_pages, staging);
 }
 
 // ------------------------------------------------------------------------------------------------

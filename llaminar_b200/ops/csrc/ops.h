@@ -18,6 +18,10 @@ struct AttnDecodeParams {
     int n_heads, n_kv_heads, head_dim, max_pages, rows_per_seq;
     float scale;
     int n_pages;                   // pages of the cache (bounds-check build)
+    // 8-bit cache (`kv` then points at bytes): a page is [2][n_kv_heads][64][head_dim] int8 followed by
+    // [2][n_kv_heads][64][head_dim / 32] fp16 block scales (value = scale * int8)
+    int kv_q8;
+    size_t page_bytes, scale_off;
 };
 
 struct AttnPrefillParams {
@@ -50,7 +54,12 @@ struct RopeKVParams {
     int n_tokens, n_heads, n_kv_heads, head_dim, max_pages;
     float theta, eps;
     int n_pages, n_seqs;           // pages of the cache, rows of block_table (bounds-check build)
+    int kv_q8;                     // 8-bit cache: rows are quantised per 32 values on the way in (layout: AttnDecodeParams)
+    size_t page_bytes, scale_off;
 };
+// 8-bit cache -> bf16 pages for the prefill kernels: page j of sequence s (j < pages_of[s]) goes to staging page s * max_pages + j
+cudaError_t launch_kv_dequant_pages(const uint8_t* kv8, size_t page_bytes, size_t scale_off, const int* block_table, const int* n_tokens,
+                                    int n_seqs, int max_pages, int n_kv_heads, int head_dim, int n_pages, __nv_bfloat16* staging, cudaStream_t st);
 // status word of the bounds-check build, per translation unit (0 in the production build)
 int bounds_status_ops(bool reset);
 int bounds_status_attention(bool reset);

@@ -49,7 +49,11 @@ def test_pp_layout_and_rules():
 def test_unsupported_and_bad_values_are_named():
     with pytest.raises(ConfigError) as e:
         parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--kv-cache-precision", "tq4"])
-    assert "quantised KV" in str(e.value)
+    assert "turbo-quantised KV" in str(e.value)
+    with pytest.raises(ConfigError) as e:
+        parse_args(["oneshot", "--synthetic", "tiny-qwen3", "-d", "cpu", "--kv-cache-precision", "q8_0"])
+    assert "CUDA feature" in str(e.value)
+    parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--kv-cache-precision", "q8_0"])       # accepted for GPUs
     with pytest.raises(ConfigError):
         parse_args(["oneshot", "--synthetic", "tiny-qwen3", "--tp-devices", "rocm:0,rocm:1"])
     with pytest.raises(ConfigError):

@@ -229,3 +229,25 @@ def test_penalties_run_inside_the_decode_graph_and_match_the_eager_path(temperat
     # the penalties matter for this model: without them the outputs differ
     plain = [SamplingParams(temperature=temperature, top_k=20, top_p=0.95, seed=7 + i, max_tokens=6 + 3 * i, ignore_eos=True) for i in range(5)]
     assert e2.generate(prompts, plain) != o2
+
+
+def test_8bit_kv_cache_engine_matches_the_bf16_cache():
+    """`--kv-cache-precision q8_0`: prefill (through the bf16 staging pool), chunked prefill over a cached context and graph
+    decode straight from the 8-bit pages give mostly the same greedy tokens as the bf16 cache (a random-weight model has
+    near-ties, so a few may flip), and the cache takes 17/32 of the memory."""
+    from llaminar_b200.engine.kv_cache import Q8
+    w = synthesize(SHAPES["tiny-qwen3"], "Q4_K_M", seed=4)
+    prompts = [_prompt(n, n) for n in (5, 70, 200, 33)]
+    ps = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    outs, nbytes = {}, {}
+    for name, dt in (("bf16", None), ("q8", Q8)):
+        eng = LLMEngine(w, device="cuda", max_batch=4, max_context=512, max_prefill_tokens=128, kv_dtype=dt, kv_pages=64)
+        assert eng.kv.q8 == (dt == Q8)
+        outs[name] = eng.generate(prompts, ps)
+        eng.check_health()
+        assert eng.stats["graph_replays"] > 0
+        nbytes[name] = sum(l.numel() * l.element_size() for l in eng.kv.layers)
+    assert all(len(o) == 10 for o in outs["q8"])
+    agree = sum(a == b for oa, ob in zip(outs["bf16"], outs["q8"]) for a, b in zip(oa, ob))
+    assert agree >= 0.8 * 40, (outs["bf16"], outs["q8"])
+    assert nbytes["q8"] * 32 == nbytes["bf16"] * 17

@@ -265,6 +265,65 @@ def test_rope_kv_and_attention(D, nq, nkv):
         assert int(ops.scratch_for(DEV).attn_tickets.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("D,nq,nkv", [(128, 32, 8), (64, 4, 2)])
+def test_kv_cache_8bit_against_the_bf16_cache(D, nq, nkv):
+    """8-bit KV pages (int8 + one fp16 scale per 32 values): the quantising append, the expansion into bf16 staging pages that
+    the prefill kernels read, and decode attention straight from the 8-bit pages, each against the bf16 cache."""
+    from llaminar_b200 import ops
+    torch.manual_seed(1)
+    B, q_lens = 3, [70, 129, 5]
+    kv, btab, max_pages = _paged_setup(B, [l + 3 for l in q_lens], nkv, D)
+    data = 2 * nkv * 64 * D
+    kv8 = torch.zeros(kv.shape[0], data + data // 16, dtype=torch.uint8, device=DEV)
+    T = sum(q_lens)
+    qkv = (torch.randn(T, (nq + 2 * nkv) * D, device=DEV) * 0.5).to(torch.bfloat16)
+    qn, kn = torch.rand(D, device=DEV) + 0.5, torch.rand(D, device=DEV) + 0.5
+    pos = torch.cat([torch.arange(l) for l in q_lens]).to(torch.int32).to(DEV)
+    sid = torch.cat([torch.full((l,), i) for i, l in enumerate(q_lens)]).to(torch.int32).to(DEV)
+    q_a = torch.empty(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    q_b = torch.empty_like(q_a)
+    ops.rope_kv(qkv.clone(), q_a, kv, qn, kn, pos, sid, btab, nq, nkv, D, 1e6, 1e-6)
+    ops.rope_kv(qkv.clone(), q_b, kv8, qn, kn, pos, sid, btab, nq, nkv, D, 1e6, 1e-6)
+    assert torch.equal(q_a, q_b)
+    # expansion of the sequences' pages: staging page s * max_pages + j holds page btab[s, j]
+    n_tok = torch.tensor(q_lens, dtype=torch.int32, device=DEV)
+    staging = torch.zeros(B * max_pages, 2, nkv, 64, D, dtype=torch.bfloat16, device=DEV)
+    ops.kv_dequant_pages(kv8, btab, n_tok, nkv, D, staging)
+    for b, L in enumerate(q_lens):
+        for j in range((L + 63) // 64):
+            ref = kv[int(btab[b, j])].float()
+            got = staging[b * max_pages + j].float()
+            assert _rel(got, ref) < 8e-3, (b, j)                     # half a step of 1/127 of each block's largest value
+    # prefill attention over the staging pool against the bf16 cache
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ctx = torch.zeros(B, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    o_a = torch.empty(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    o_b = torch.empty_like(o_a)
+    bt2 = torch.arange(B * max_pages, dtype=torch.int32, device=DEV).view(B, max_pages)
+    ops.attn_prefill(q_a, kv, o_a, btab, cu, ctx, nq, nkv, D, scale, max(q_lens))
+    ops.attn_prefill(q_a, staging, o_b, bt2, cu, ctx, nq, nkv, D, scale, max(q_lens))
+    assert _rel(o_b, o_a.float()) < 1.5e-2
+    # decode straight from the 8-bit pages, one and two rows per sequence, with and without splits
+    g = nq // nkv
+    for R in (1, 2 if g * 2 <= 16 else 1):
+        newq = (torch.randn(B * R, (nq + 2 * nkv) * D, device=DEV) * 0.5).to(torch.bfloat16)
+        pos2 = torch.cat([torch.arange(L, L + R) for L in q_lens]).to(torch.int32).to(DEV)
+        sid2 = torch.arange(B).repeat_interleave(R).to(torch.int32).to(DEV)
+        kv_a, kv_b = kv.clone(), kv8.clone()
+        qd = torch.empty(B * R, nq, D, dtype=torch.bfloat16, device=DEV)
+        ops.rope_kv(newq.clone(), qd, kv_a, qn, kn, pos2, sid2, btab, nq, nkv, D, 1e6, 1e-6)
+        ops.rope_kv(newq.clone(), qd, kv_b, qn, kn, pos2, sid2, btab, nq, nkv, D, 1e6, 1e-6)
+        seq_lens = torch.tensor([L + R for L in q_lens], dtype=torch.int32, device=DEV)
+        for splits in (1, 3):
+            od_a = torch.empty(B * R, nq, D, dtype=torch.bfloat16, device=DEV)
+            od_b = torch.empty_like(od_a)
+            ops.attn_decode(qd, kv_a, od_a, btab, seq_lens, nq, nkv, D, R, scale, splits, ops.scratch_for(DEV))
+            ops.attn_decode(qd, kv_b, od_b, btab, seq_lens, nq, nkv, D, R, scale, splits, ops.scratch_for(DEV))
+            assert _rel(od_b, od_a.float()) < 1.5e-2, (R, splits)
+    assert int(ops.scratch_for(DEV).attn_tickets.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("nq,nkv,q_lens,ctx_lens", [(8, 2, [70, 129, 5], [0, 0, 0]), (4, 4, [300, 128], [0, 64]),
                                                      (16, 2, [257, 40, 1], [200, 131, 513])])
 def test_prefill_attention_tcgen05(nq, nkv, q_lens, ctx_lens):

@@ -16,7 +16,7 @@ def _prompts():
 def _pp_generate(rank, world, tp_size, mtp, payload="auto"):
     import os
     import torch.distributed as dist
-    os.environ["LLAMINAR_PP_PAYLOAD"] = payload
+    os.environ.update({"LLAMINAR_PP_PAYLOAD": payload})       # a child process of its own: set before the stage model reads it
     from llaminar_b200.engine.sampling import SamplingParams
     from llaminar_b200.models.synth import synthesize
     from llaminar_b200.parallel.pp import build_pipeline_engine
