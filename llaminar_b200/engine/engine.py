@@ -244,9 +244,23 @@ class LLMEngine:
             return
         if getattr(self, "_health_host", None) is None:
             self._health_host = torch.zeros(8, dtype=torch.int32).pin_memory()
-        for i, w in enumerate(self._status_words()):
+        words = self._status_words()
+        for i, w in enumerate(words):
             self._health_host[i:i + 1].copy_(w[:1], non_blocking=True)
+        self._health_host[7:8].copy_(self._group_failed(words), non_blocking=True)
         self._health_queued = True
+
+    def _group_failed(self, words: list[torch.Tensor]) -> torch.Tensor:
+        """Device word: 1 if ANY rank of the tensor-parallel group has a status word set after this step (MAX over the group,
+        enqueued behind the step's kernels).  A wait that runs out on one rank (its peer stalled) leaves the arrival counters
+        of the fused kernels out of step on every rank, so all of them have to see the failure and resynchronise together;
+        the rank that caused it may have nothing in its own words."""
+        flag = torch.stack([w[0] for w in words]).ne(0).any().to(torch.int32).view(1) if words else torch.zeros(1, dtype=torch.int32, device=self.device)
+        tp = self.tp
+        if tp is not None and tp.size > 1 and getattr(tp, "symm", None) is not None:
+            import torch.distributed as dist
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=tp.group)
+        return flag
 
     def _finish_health(self) -> None:
         """After the step has synchronised: raise if any status word was set.  The scratch is reset first, the failure is
@@ -256,9 +270,12 @@ class LLMEngine:
         if getattr(self, "_health_queued", False):
             self._health_queued = False
             vals = self._health_host[:len(self._status_words())].tolist()
+            group_failed = bool(self._health_host[7])
         else:
-            vals = [int(w[0]) for w in self._status_words()]
-        if not any(vals):
+            words = self._status_words()
+            group_failed = bool(int(self._group_failed(words)[0]))       # every rank calls check_health at the same point
+            vals = [int(w[0]) for w in words]
+        if not any(vals) and not group_failed:
             return
         symm0 = getattr(self.tp, "symm", None) if self.tp is not None else None
         detail = ""
@@ -273,6 +290,12 @@ class LLMEngine:
             symm.status.zero_()
             if getattr(self.tp, "verify_checksums", False) and hasattr(symm, "check_canaries"):
                 symm.check_canaries()
+            if group_failed and self.tp.size > 1 and hasattr(symm, "resync"):
+                # all ranks of the group are here (the flag was agreed): bring the fused kernels' counters back in step, so that
+                # the next step can run instead of timing out again on the counts this step left behind
+                symm.resync()
+        if not any(vals):
+            detail += "; reported by another rank of the tensor-parallel group"
         msg = f"a kernel gave up a bounded wait (status words {vals}{detail}); scratch buffers were reset"
         hb = getattr(self, "heartbeat", None)
         if hb is not None:

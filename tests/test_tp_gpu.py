@@ -329,3 +329,41 @@ def test_engine_tp2_sequence_sharded_prefill_equals_nccl_baseline():
     assert fused[0][2] and not base[0][2]                          # the fused run went through the reduce-scatter arena
     agree = sum(a == b for fo, bo in zip(fused[0][0], base[0][0]) for a, b in zip(fo, bo))
     assert agree >= 0.85 * 24            # bf16 partial sums and another summation order may flip a near-tie
+
+
+def _group_failure_case(rank, world):
+    """A status word set on ONE rank: every rank's health check raises in the same step (MAX over the group), the arrival
+    counters are resynchronised by all of them together, and the next requests run through the fused kernels again."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.tp import TPContext
+    dev = torch.device("cuda", rank)
+    cfg = SHAPES["tiny-qwen3"].with_(d_model=1024, n_heads=8, n_kv_heads=2, head_dim=128, d_ff=2048, n_layers=2)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    tp = TPContext.create(device=dev, fused=True)
+    eng = LLMEngine(w, device=dev, max_batch=4, max_context=256, tp=tp)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9)]
+    ps = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    first = eng.generate(prompts, ps)
+    if rank == 0:
+        tp.symm.status[0] = 1                      # as a wait of this rank that ran out would leave it
+    raised, text = False, ""
+    try:
+        eng.check_health()
+    except RuntimeError as e:
+        raised, text = True, str(e)
+    again = eng.generate(prompts, ps)
+    eng.check_health()
+    return raised, "another rank" in text, first == again, int(tp.symm.status[0])
+
+
+def test_a_failure_on_one_rank_is_seen_and_resynchronised_by_all():
+    _need(2)
+    out = run_ranks_gpu(_group_failure_case, 2)
+    assert out[0][0] and out[1][0]                  # both ranks raised
+    assert not out[0][1] and out[1][1]              # rank 1 had nothing in its own words
+    assert out[0][2] and out[1][2]                  # the fused path works again afterwards, same tokens
+    assert out[0][3] == 0 and out[1][3] == 0
