@@ -367,3 +367,34 @@ def test_a_failure_on_one_rank_is_seen_and_resynchronised_by_all():
     assert not out[0][1] and out[1][1]              # rank 1 had nothing in its own words
     assert out[0][2] and out[1][2]                  # the fused path works again afterwards, same tokens
     assert out[0][3] == 0 and out[1][3] == 0
+
+
+def _pp2_gpu_case(rank, world):
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    from llaminar_b200.parallel.pp import build_pipeline_engine
+    dev = torch.device("cuda", rank)
+    cfg = SHAPES["tiny-qwen3"].with_(d_model=1024, n_heads=8, n_kv_heads=2, head_dim=128, d_ff=2048, n_layers=4)
+    w = synthesize(cfg, "Q4_K_M", seed=0)
+    layout = {"pp": 2, "tp": 1, "world": 2, "stages": [(f"s{i}", [f"cuda:{i}"], None, None) for i in range(2)]}
+    eng = build_pipeline_engine(w, layout, rank, microbatch_tokens=64, device=dev, max_batch=4, max_context=256)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 130, 9)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    sampled = eng.generate(prompts[:2], SamplingParams(temperature=0.8, top_k=20, seed=5, max_tokens=6, ignore_eos=True))
+    eng.check_health()
+    return outs, sampled, dict(eng.model.stats), str(eng.model.payload_dtype)
+
+
+def test_pipeline_stages_on_two_gpus_exchange_bf16_rows_and_token_ids():
+    """PP = 2 on GPUs: the residual stream crosses as bf16, only sampled token ids come back (no full-vocabulary rows), both
+    stages end up with the same tokens for greedy and for sampled requests."""
+    _need(2)
+    out = run_ranks_gpu(_pp2_gpu_case, 2)
+    assert out[0][0] == out[1][0] and out[0][1] == out[1][1]
+    assert all(len(o) == 8 for o in out[0][0]) and all(len(o) == 6 for o in out[0][1])
+    assert out[0][3] == "torch.bfloat16"
+    s0, s1 = out[0][2], out[1][2]
+    assert s0["sent_bytes"] > 0 and s0["sent_bytes"] == s1["recv_bytes"]
+    assert s0["token_syncs"] > 0 and s0["bcast_bytes"] == s1["bcast_bytes"] < 4096
