@@ -82,7 +82,7 @@ OPTIONS: list[OptionSpec] = [
     _o("--activation-precision", default="bf16", choices=("bf16", "fp32", "fp16"), category="precision"),
     _o("--kv-cache-precision", default="bf16", choices=("bf16", "fp16", "fp32", "q8_0", "q8_1", "tq4", "tq8"), category="precision"),
     # -- MoE ------------------------------------------------------------------------------------------------
-    _o("--moe-expert-mode", default="expert-parallel", choices=("expert-parallel", "tensor-parallel", "replicated"), category="moe"),
+    _o("--moe-expert-mode", default="expert-parallel", choices=("expert-parallel", "expert-parallel-a2a", "tensor-parallel", "replicated"), category="moe"),
     _o("--moe-overlay", category="moe", unsupported="CPU/GPU expert overlay tiers are not built"),
     _o("--moe-rebalance", action="store_true", category="moe",
        unsupported="experts are not moved while serving; measure with --moe-stats-out and place them with --moe-expert-placement"),

@@ -143,10 +143,90 @@ def moe_forward_grouped(model, L, h: torch.Tensor, T: int) -> None:
         h += target
 
 
+def a2a_supported(model, L, T: int) -> bool:
+    tp = model.tp
+    # prefill-sized batches only: the split sizes of the exchange are read on the host, which a captured decode step cannot do
+    return (tp is not None and tp.size > 1 and getattr(tp, "moe_mode", "") == "expert-parallel-a2a" and grouped_supported(model, L, T)
+            and model.cfg.n_experts == L.experts.n_local * tp.size and T * model.cfg.n_experts_used > FUSED_MAX_PAIRS
+            and not torch.cuda.is_current_stream_capturing())
+
+
+def moe_forward_a2a(model, L, h: torch.Tensor, T: int) -> None:
+    """Token-sharded expert parallelism through NCCL all-to-all (`--moe-expert-mode expert-parallel-a2a`), prefill-sized batches.
+
+    Rank r routes only its own T / W tokens, sends every (token, slot) row to the rank that owns the expert
+    (`all_to_all_single`, rows sorted by expert so that they arrive grouped), runs the grouped tensor-core expert GEMMs on what
+    it received, sends the results back, combines them with the routing weights for its own tokens and all-gathers the token
+    rows (the residual stream stays replicated for the tensor-parallel attention).  This is the dispatch / return form of the
+    reference (reference: src/v2/execution/moe/MoEOverlaySparseCollective.cpp) and the baseline that the default mode is
+    measured against: with a replicated residual it moves top_k * d per token and direction (bf16 out, fp32 back) where the
+    default mode's dense all-reduce moves about 2 * d fp32, and NCCL's variable split sizes cost one host synchronisation per
+    layer, so it is not the default."""
+    import torch.distributed as dist
+    c, sc, dev, tp = model.cfg, model.scratch, model.device, model.tp
+    W, r, k, slab, d = tp.size, tp.rank, c.n_experts_used, L.experts, c.d_model
+    nl = slab.n_local
+    t0, t1 = T * r // W, T * (r + 1) // W
+    To = t1 - t0
+    xn = model.ws_xn[:To]
+    ids = torch.empty(To, k, dtype=torch.int32, device=dev)
+    wts = torch.empty(To, k, dtype=torch.float32, device=dev)
+    ops.moe_route_only(h[t0:t1], L.ffn_norm, c.rms_eps, L.router, k, c.norm_topk_prob, ids, wts, xn)
+    flat = ids.view(-1).long()
+    order = torch.argsort(flat, stable=True)                 # by expert, hence by destination rank
+    sorted_e = flat[order]
+    send_counts = torch.bincount(sorted_e // nl, minlength=W)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=tp.group)
+    sc_l, rc_l = send_counts.tolist(), recv_counts.tolist()  # NCCL wants the split sizes on the host
+    R = sum(rc_l)
+    send_rows = xn.index_select(0, order // k)
+    send_eid = (sorted_e % nl).to(torch.int32)
+    recv_rows = torch.empty(R, d, dtype=torch.bfloat16, device=dev)
+    recv_eid = torch.empty(R, dtype=torch.int32, device=dev)
+    dist.all_to_all_single(recv_rows, send_rows, rc_l, sc_l, group=tp.group)
+    dist.all_to_all_single(recv_eid, send_eid, rc_l, sc_l, group=tp.group)
+    y_arr = torch.empty(R, d, dtype=torch.float32, device=dev)
+    if R > 0:
+        key = recv_eid.long()
+        order2 = torch.argsort(key, stable=True)             # arrival order is by source rank; the GEMMs want it by expert
+        counts = torch.bincount(key, minlength=nl).to(torch.int32)
+        avg = R // max(nl, 1)
+        bm = 256 if avg >= 192 else (128 if avg >= 96 else 64)
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        row_off = torch.cat([zero, torch.cumsum(counts, 0, dtype=torch.int32)])
+        tile_off = torch.cat([zero, torch.cumsum((counts + (bm - 1)) // bm, 0, dtype=torch.int32)])
+        xg = recv_rows.index_select(0, order2)
+        act = torch.empty(R, c.expert_ff, dtype=torch.bfloat16, device=dev)
+        y = torch.empty(R, d, dtype=torch.float32, device=dev)
+        ops.gemm_grouped(slab.gate_up, xg, act, row_off, tile_off, bm, epi=ops.EPI_SWIGLU, scratch=sc)
+        ops.gemm_grouped(slab.down, act, y, row_off, tile_off, bm, scratch=sc)
+        y_arr[order2] = y                                    # back to arrival order
+    back = torch.empty(To * k, d, dtype=torch.float32, device=dev)
+    dist.all_to_all_single(back, y_arr, sc_l, rc_l, group=tp.group)
+    # `back` is in this rank's by-expert order of its own pairs
+    Tmax = (T + W - 1) // W
+    own = torch.zeros(Tmax, d, dtype=torch.float32, device=dev)
+    if To > 0:
+        pos = torch.empty(To * k, dtype=torch.int32, device=dev)
+        pos[order] = torch.arange(To * k, dtype=torch.int32, device=dev)
+        ops.moe_combine_sorted(own[:To], back, pos, wts, k)
+    full = torch.empty(W, Tmax, d, dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(full, own, group=tp.group)
+    for q in range(W):
+        q0, q1 = T * q // W, T * (q + 1) // W
+        if q1 > q0:
+            h[q0:q1] += full[q, :q1 - q0]
+    tp.stats["a2a_calls"] = tp.stats.get("a2a_calls", 0) + 1
+    tp.stats["a2a_bytes"] = tp.stats.get("a2a_bytes", 0) + sum(sc_l) * d * 2 + R * d * 4
+
+
 def moe_forward(model, L, h: torch.Tensor, T: int) -> None:
     c, sc = model.cfg, model.scratch
     dev = model.device
     k = c.n_experts_used
+    if a2a_supported(model, L, T):
+        return moe_forward_a2a(model, L, h, T)
     if T * k <= SMALL_SLOTS * 2 and fused_supported(model, L, T):
         return moe_forward_fused(model, L, h, T)
     if T * k > SMALL_SLOTS and grouped_supported(model, L, T):

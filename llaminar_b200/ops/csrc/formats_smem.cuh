@@ -239,14 +239,8 @@ template <int A> struct DequantAtom<FMT_IQ3_S, A> {
 // (A fp16 variant through cvt.rn.f16x2.e4m3x2 was tried first: tcgen05.mma kind::f16 with an fp16 A and a bf16 B operand
 // raises "illegal instruction" on B200, although the two formats are separate fields of the instruction descriptor.)
 LLM_DEVICE uint32_t hfma2_bf16_u32(uint32_t a, __nv_bfloat162 s, __nv_bfloat162 b) {
-#ifdef LLM_ASM_FMA
-    uint32_t r;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(*reinterpret_cast<const uint32_t*>(&s)), "r"(*reinterpret_cast<const uint32_t*>(&b)));
-    return r;
-#else
     const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&a), s, b);
     return *reinterpret_cast<const uint32_t*>(&r);
-#endif
 }
 struct DequantAtomQ4KRt {
     template <bool HI>

@@ -116,7 +116,7 @@ def test_engine_tp2_sampled_decode_uses_candidate_merge():
     assert all(0 <= t < res[0][2] for o in res[0][0] for t in o) and all(len(o) == 12 for o in res[0][0])
 
 
-def _moe_engine_tokens(rank, world, fused):
+def _moe_engine_tokens(rank, world, fused, moe_mode="expert-parallel", lens=(40, 9, 70, 21, 64, 5)):
     from llaminar_b200.engine.engine import LLMEngine
     from llaminar_b200.engine.sampling import SamplingParams
     from llaminar_b200.models.config import SHAPES
@@ -127,12 +127,26 @@ def _moe_engine_tokens(rank, world, fused):
                                         n_experts_used=4, n_layers=2)
     w = synthesize(cfg, "Q4_K_M", seed=0)
     tp = TPContext.create(device=dev, fused=fused)
-    eng = LLMEngine(w, device=dev, max_batch=8, max_context=256, tp=tp)
+    tp.moe_mode = moe_mode
+    eng = LLMEngine(w, device=dev, max_batch=8, max_context=max(256, max(lens) + 64), max_prefill_tokens=4096, tp=tp)
     g = torch.Generator().manual_seed(3)
-    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9, 70, 21, 64, 5)]
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
     outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     eng.check_health()
     return outs, dict(tp.stats)
+
+
+def test_engine_moe_all_to_all_dispatch_matches_the_dense_all_reduce_2gpu():
+    """`--moe-expert-mode expert-parallel-a2a`: token-sharded routing, NCCL all-to-all dispatch and return, grouped expert
+    GEMMs on the received rows; the tokens agree with the default expert-parallel mode (dense all-reduce of partial rows)."""
+    _need(2)
+    lens = (400, 90, 700, 210)                       # 1400 prompt rows x top-4 = 5600 pairs in one prefill chunk: above the threshold
+    a2a = run_ranks_gpu(_moe_engine_tokens, 2, False, "expert-parallel-a2a", lens)
+    base = run_ranks_gpu(_moe_engine_tokens, 2, False, "expert-parallel", lens)
+    assert a2a[0][0] == a2a[1][0]
+    assert a2a[0][1].get("a2a_calls", 0) > 0 and base[0][1].get("a2a_calls", 0) == 0
+    agree = sum(x == y for fo, bo in zip(a2a[0][0], base[0][0]) for x, y in zip(fo, bo))
+    assert agree >= 0.85 * 32
 
 
 def test_engine_moe_expert_parallel_fused_combine_2gpu():
