@@ -121,6 +121,9 @@ def reference_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device on this host (the reference's kernels are CUDA kernels)"}))
+        return 0
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -412,8 +415,18 @@ def measure(model_name: str, recipe: str, S: int, args, tp, dev, world: int, ran
     return res
 
 
+def _keep_stdout_for_the_result() -> None:
+    """The contract is ONE JSON line on stdout.  Libraries print banners there from C (NCCL's version line, for one), so the
+    process-level stdout is pointed at stderr and Python's `sys.stdout` keeps the original descriptor for the result line."""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(keep, "w", buffering=1)
+
+
 def main():
     args = parse_args()
+    _keep_stdout_for_the_result()
     if args.impl == "reference":
         return reference_arm(args)
     import datetime
