@@ -257,7 +257,7 @@ class LLMEngine:
         the rank that caused it may have nothing in its own words."""
         flag = torch.stack([w[0] for w in words]).ne(0).any().to(torch.int32).view(1) if words else torch.zeros(1, dtype=torch.int32, device=self.device)
         tp = self.tp
-        if tp is not None and tp.size > 1 and getattr(tp, "symm", None) is not None:
+        if tp is not None and getattr(tp, "size", 1) > 1 and getattr(tp, "symm", None) is not None:
             import torch.distributed as dist
             dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=tp.group)
         return flag
@@ -290,7 +290,7 @@ class LLMEngine:
             symm.status.zero_()
             if getattr(self.tp, "verify_checksums", False) and hasattr(symm, "check_canaries"):
                 symm.check_canaries()
-            if group_failed and self.tp.size > 1 and hasattr(symm, "resync"):
+            if group_failed and getattr(self.tp, "size", 1) > 1 and hasattr(symm, "resync"):
                 # all ranks of the group are here (the flag was agreed): bring the fused kernels' counters back in step, so that
                 # the next step can run instead of timing out again on the counts this step left behind
                 symm.resync()

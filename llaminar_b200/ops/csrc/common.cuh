@@ -84,6 +84,11 @@ LLM_DEVICE uint16_t ldg_nc_u16(const void* p) {
 
 // Programmatic dependent launch (see launch.h): trigger lets the next kernel of the stream start its prologue, wait blocks
 // until the previous kernel has completed and its memory is visible.  Both are no-ops for an ordinary launch.
+// A kernel launched that way becomes resident while its predecessor still runs, so whatever
+// the predecessor writes is NOT read-only for this kernel's lifetime: after `pdl_wait()` read it with ordinary or `__ldcg`
+// loads, never through the read-only path (`ld.global.nc`, `__ldg`, or a `const __restrict__` parameter, which lets the
+// compiler pick that path).  A line that another CTA on the same SM brought into the read-only cache while the predecessor had
+// not yet written it would be served stale.  Weights and other constants may use it.
 LLM_DEVICE void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 LLM_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     // rows of this CTA: consecutive ones, or the (token, slot) pairs of a grouped-expert work item
     int xr[M], orow[M], n_valid = M, expert = -1;
     if (p.items) {
-        if ((int)blockIdx.z >= __ldg(p.n_items)) return;
+        if ((int)blockIdx.z >= __ldcg(p.n_items)) return;
         const MoeItem it = p.items[blockIdx.z];
         expert = it.expert;
         n_valid = min(it.m, M);
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         __syncthreads();
         if (tid == 0) {
             const unsigned t = atomicAdd(&mc.tile_tickets[tile], 1u);
-            s_last2 = (t == (unsigned)__ldg(p.n_items) - 1u);
+            s_last2 = (t == (unsigned)__ldcg(p.n_items) - 1u);
             if (s_last2 && p.tp) s_epoch2 = p.tp->epoch[tile];
         }
         __syncthreads();

@@ -72,6 +72,26 @@ template <int M, int NORM>
 LLM_DEVICE void quantise_acts(const GemvParams& p, int kb_first, int n_act, int act_cap, ActBlk* acts, float* s_red) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float rms[M];
+    // One activation row with a fused RMSNorm (decode at batch 1): the values this CTA will quantise and their gains are
+    // loaded together with the full-row pass, before the reduction, and stay in registers across it, so the prologue has one
+    // memory round trip on its critical path instead of two.
+    constexpr int QPT = 4;                      // quads a thread may keep
+    const int n_quads_all = n_act * 64;
+    const bool in_regs = NORM && M == 1 && n_quads_all <= QPT * N_COMPUTE;
+    float4 keep_v[QPT], keep_g[QPT];
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < QPT; ++j) {
+            const int qd = tid + j * N_COMPUTE;
+            if (qd < n_quads_all) {
+                int kb = kb_first + (qd >> 6);
+                if (kb >= p.k_blocks) kb -= p.k_blocks;
+                const int col = kb * 256 + (qd & 63) * 4;
+                keep_v[j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + col);
+                keep_g[j] = *reinterpret_cast<const float4*>(p.norm_w + col);
+            }
+        }
+    }
     if (NORM) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -94,37 +114,49 @@ LLM_DEVICE void quantise_acts(const GemvParams& p, int kb_first, int n_act, int 
         bar_compute();                          // s_red is reused by the main loop
     }
     const int n_quads = n_act * 64;             // 4 consecutive columns per thread, 8 threads per 32-column block
-    for (int m = 0; m < M; ++m) {
-        for (int qd = tid; qd < n_quads; qd += N_COMPUTE) {
-            const int i = qd >> 6;
-            int kb = kb_first + i;
-            if (kb >= p.k_blocks) kb -= p.k_blocks;
-            const int col = kb * 256 + (qd & 63) * 4;
-            float v0, v1, v2, v3;
-            if (NORM) {
-                const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)m * p.x_stride + col);
-                const float4 g = *reinterpret_cast<const float4*>(p.norm_w + col);
-                v0 = v.x * rms[m] * g.x; v1 = v.y * rms[m] * g.y; v2 = v.z * rms[m] * g.z; v3 = v.w * rms[m] * g.w;
-            } else {
-                const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)m * p.x_stride + col);
-                v0 = bf16_lo(v.x); v1 = bf16_hi(v.x); v2 = bf16_lo(v.y); v3 = bf16_hi(v.y);
+    // quantise one quad (its 32-column block is shared by 8 neighbouring lanes) and store it
+    auto emit = [&](int m, int qd, float v0, float v1, float v2, float v3) {
+        float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float d = amax * (1.0f / 127.0f);
+        const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+        const int q0 = __float2int_rn(v0 * inv), q1 = __float2int_rn(v1 * inv);
+        const int q2 = __float2int_rn(v2 * inv), q3 = __float2int_rn(v3 * inv);
+        int s = q0 + q1 + q2 + q3;
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        ActBlk& ab = acts[m * act_cap + (qd >> 6)];
+        const int qi = qd & 63;
+        ab.a[qi] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        if ((qi & 7) == 0) ab.d[qi >> 3] = d;
+        if ((qi & 3) == 0) ab.ds16[qi >> 2] = d * s;
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < QPT; ++j) {
+            const int qd = tid + j * N_COMPUTE;  // whole warps are in or out: n_quads is a multiple of 64
+            if (qd < n_quads) {
+                const float4 v = keep_v[j], g = keep_g[j];
+                emit(0, qd, v.x * rms[0] * g.x, v.y * rms[0] * g.y, v.z * rms[0] * g.z, v.w * rms[0] * g.w);
             }
-            float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            const float d = amax * (1.0f / 127.0f);
-            const float inv = amax > 0.f ? 127.0f / amax : 0.f;
-            const int q0 = __float2int_rn(v0 * inv), q1 = __float2int_rn(v1 * inv);
-            const int q2 = __float2int_rn(v2 * inv), q3 = __float2int_rn(v3 * inv);
-            int s = q0 + q1 + q2 + q3;
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            ActBlk& ab = acts[m * act_cap + i];
-            const int qi = qd & 63;
-            ab.a[qi] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
-            if ((qi & 7) == 0) ab.d[qi >> 3] = d;
-            if ((qi & 3) == 0) ab.ds16[qi >> 2] = d * s;
+        }
+    } else {
+        for (int m = 0; m < M; ++m) {
+            for (int qd = tid; qd < n_quads; qd += N_COMPUTE) {
+                int kb = kb_first + (qd >> 6);
+                if (kb >= p.k_blocks) kb -= p.k_blocks;
+                const int col = kb * 256 + (qd & 63) * 4;
+                if (NORM) {
+                    const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + (size_t)m * p.x_stride + col);
+                    const float4 g = *reinterpret_cast<const float4*>(p.norm_w + col);
+                    emit(m, qd, v.x * rms[m] * g.x, v.y * rms[m] * g.y, v.z * rms[m] * g.z, v.w * rms[m] * g.w);
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)m * p.x_stride + col);
+                    emit(m, qd, bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+                }
+            }
         }
     }
     bar_compute();

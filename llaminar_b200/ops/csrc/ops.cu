@@ -15,17 +15,36 @@ constexpr int PAGE = 64;
 // ------------------------------------------------------------------------------------------------
 // RMSNorm: fp32 residual stream in, bf16 out
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ h, const float* __restrict__ w,
+// One CTA per row.  For rows of up to 8192 values the row and the gain are read once, together, and stay in registers across
+// the reduction (one memory round trip on the critical path of a decode step instead of two); longer rows are re-read.
+// `h` is written by the kernel before this one, which may still be running when this kernel's CTAs become resident
+// (programmatic dependent launch): it is read with L2-coherent loads (`__ldcg`), never through the read-only path.
+template <bool IN_REGS>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* h, const float* __restrict__ w,
                                                       __nv_bfloat16* __restrict__ out, int d, float eps) {
     __shared__ float s_part[8];
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float4* x4 = reinterpret_cast<const float4*>(h + (size_t)row * d);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    constexpr int MAXV = 8;
+    float4 xv[MAXV], gv[MAXV];
     float ss = 0.f;
-    for (int i = tid; i < d / 4; i += 256) {
-        const float4 v = x4[i];
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (IN_REGS) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int i = tid + j * 256;
+            if (i < d / 4) { xv[j] = __ldcg(x4 + i); gv[j] = w4[i]; }
+            else { xv[j] = make_float4(0.f, 0.f, 0.f, 0.f); gv[j] = xv[j]; }
+        }
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    } else {
+        for (int i = tid; i < d / 4; i += 256) {
+            const float4 v = __ldcg(x4 + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
     }
     ss = warp_sum(ss);
     if ((tid & 31) == 0) s_part[tid >> 5] = ss;
@@ -34,11 +53,19 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += s_part[i];
     const float r = rsqrtf(tot / d + eps);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
     uint2* o2 = reinterpret_cast<uint2*>(out + (size_t)row * d);
-    for (int i = tid; i < d / 4; i += 256) {
-        const float4 v = x4[i], g = w4[i];
-        o2[i] = make_uint2(pack_bf16(v.x * r * g.x, v.y * r * g.y), pack_bf16(v.z * r * g.z, v.w * r * g.w));
+    if (IN_REGS) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int i = tid + j * 256;
+            if (i < d / 4)
+                o2[i] = make_uint2(pack_bf16(xv[j].x * r * gv[j].x, xv[j].y * r * gv[j].y), pack_bf16(xv[j].z * r * gv[j].z, xv[j].w * r * gv[j].w));
+        }
+    } else {
+        for (int i = tid; i < d / 4; i += 256) {
+            const float4 v = __ldcg(x4 + i), g = w4[i];
+            o2[i] = make_uint2(pack_bf16(v.x * r * g.x, v.y * r * g.y), pack_bf16(v.z * r * g.z, v.w * r * g.w));
+        }
     }
 }
 
@@ -47,7 +74,8 @@ LLM_DEFINE_BOUNDS_STATUS_READER(bounds_status_ops)
 cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
     if (d % 4) return cudaErrorInvalidValue;
-    return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, st, h, w, out, d, eps);
+    if (d <= 8 * 256 * 4) return launch_pdl(rmsnorm_kernel<true>, dim3(rows), dim3(256), 0, st, h, w, out, d, eps);
+    return launch_pdl(rmsnorm_kernel<false>, dim3(rows), dim3(256), 0, st, h, w, out, d, eps);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -288,8 +316,8 @@ cudaError_t launch_rope_kv(const RopeKVParams& p, cudaStream_t st) {
 // 8-bit KV pages -> bf16 pages (the prefill kernels read bf16): one CTA per (page slot, sequence), one 16-byte unit of
 // 16 values per thread and step
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) kv_dequant_pages_kernel(const uint8_t* __restrict__ kv8, size_t page_bytes, size_t scale_off,
-                                                               const int* __restrict__ block_table, const int* __restrict__ n_tokens, int max_pages,
+__global__ void __launch_bounds__(256) kv_dequant_pages_kernel(const uint8_t* kv8, size_t page_bytes, size_t scale_off,
+                                                               const int* block_table, const int* n_tokens, int max_pages,
                                                                int n_kv_heads, int head_dim, int n_pages, __nv_bfloat16* __restrict__ staging) {
     pdl_trigger();
     pdl_wait();
@@ -301,8 +329,8 @@ __global__ void __launch_bounds__(256) kv_dequant_pages_kernel(const uint8_t* __
     __nv_bfloat16* out = staging + ((size_t)s * max_pages + j) * (size_t)rows * head_dim;
     for (int idx = threadIdx.x; idx < rows * upr; idx += blockDim.x) {
         const int row = idx / upr, u = idx - row * upr;
-        const uint4 w = *reinterpret_cast<const uint4*>(pg + (size_t)row * head_dim + u * 16);
-        const float sc = __half2float(*reinterpret_cast<const __half*>(pg + scale_off + ((size_t)row * (head_dim / 32) + (u >> 1)) * 2));
+        const uint4 w = __ldcg(reinterpret_cast<const uint4*>(pg + (size_t)row * head_dim + u * 16));   // written by the kernel before (see rmsnorm_kernel)
+        const float sc = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(pg + scale_off + ((size_t)row * (head_dim / 32) + (u >> 1)) * 2))));
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
         uint32_t o[8];
 #pragma unroll
@@ -382,7 +410,7 @@ LLM_DEVICE float uniform01(uint64_t seed, uint64_t ctr) {
     return (splitmix64(seed ^ splitmix64(ctr)) >> 40) * (1.0f / 16777216.0f);
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int vocab, int stride, int* __restrict__ tokens,
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int vocab, int stride, int* __restrict__ tokens,
                                                       int* __restrict__ pairs, int idx_offset) {
     __shared__ float s_v[32];
     __shared__ int s_i[32];
@@ -392,7 +420,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += 1024) {
-        const float v = row[i];
+        const float v = __ldcg(row + i);             // the head's output: L2-coherent load (see rmsnorm_kernel)
         if (v > best || (v == best && i < bi)) { best = v; bi = i; }
     }
 #pragma unroll

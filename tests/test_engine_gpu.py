@@ -76,6 +76,17 @@ def test_engine_sampling_graph_and_seed_determinism():
     assert a == b and len(set(a)) > 1
 
 
+def test_repeated_prefill_and_decode_give_one_answer_with_kernels_queued_deep():
+    """The same request, 200 times, back to back: with programmatic dependent launch three kernels of the chain can be
+    resident at once, and a kernel that read its predecessor's output through the read-only cache path (RMSNorm once did)
+    was served, now and then, a stale line that an earlier kernel on the same SM had fetched.  One distinct output only."""
+    w = synthesize(SHAPES["tiny-qwen3"], "Q8_0", seed=4)
+    p = SamplingParams(temperature=0.9, top_k=50, top_p=0.95, seed=11, max_tokens=3, ignore_eos=True)
+    e = LLMEngine(w, device="cuda", max_batch=2, max_context=256)
+    outs = {tuple(e.generate([_prompt(20, 1)], p)[0]) for _ in range(200)}
+    assert len(outs) == 1, outs
+
+
 def test_moe_engine_matches_oracle():
     w = synthesize(SHAPES["tiny-qwen3moe"], "Q8_0", seed=5)
     eng = LLMEngine(w, device="cuda", max_batch=2, max_context=256)

@@ -575,7 +575,7 @@ def test_fused_allreduce_wait_runs_out_and_reports(rows):
         pass
     eng = LLMEngine.__new__(LLMEngine)
     eng.is_cuda, eng.device, eng.model = True, torch.device(DEV), _Model()
-    eng.tp = type("TP", (), {"symm": _Symm()})()
+    eng.tp = type("TP", (), {"symm": _Symm(), "size": 1, "group": None})()
     eng.tp.symm.status = status
     sc.status.zero_()
     with pytest.raises(RuntimeError, match="bounded wait"):
