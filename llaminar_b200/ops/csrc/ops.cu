@@ -85,7 +85,7 @@ cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, i
 // where the all-gather reads it).  Replaces the reference's all-reduce + residual add + RMSNorm stages
 // (reference: src/v2/models/qwen/QwenGraphBase.cpp:2004-2023, :2937-3014).
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const __nv_bfloat16* __restrict__ inbox, const unsigned* flags, unsigned target,
+__global__ void __launch_bounds__(256) rs_reduce_norm_kernel(const __nv_bfloat16* inbox, const unsigned* flags, unsigned target,
                                                              int world, int rows_per_rank, int n_cap, int block_m, float* __restrict__ h,
                                                              const float* __restrict__ norm_w, __nv_bfloat16* __restrict__ xn, int d, float eps,
                                                              unsigned spin_limit, int* status) {
