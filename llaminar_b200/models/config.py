@@ -11,7 +11,7 @@ from dataclasses import asdict, dataclass, field, replace
 
 from ..gguf.constants import GGMLType
 
-SUPPORTED_ARCHS = ("qwen2", "qwen3", "qwen3moe")
+SUPPORTED_ARCHS = ("qwen2", "qwen3", "qwen3moe", "qwen35")
 
 
 @dataclass
@@ -37,11 +37,57 @@ class ModelConfig:
     norm_topk_prob: bool = True
     # multi-token prediction (NextN) head: number of extra decoder layers stored after the trunk
     nextn_layers: int = 0
+    # hybrid layout (qwen35): every `full_attention_interval`-th layer is softmax attention over the KV cache, the others are
+    # Gated-DeltaNet linear attention (short causal convolution + one recurrent d_k x d_v state per value head)
+    # (reference: src/v2/models/qwen35/Qwen35GraphConfigBuilder.cpp:56-137)
+    full_attention_interval: int = 0     # 0: every layer is full attention
+    ssm_conv_kernel: int = 4
+    ssm_state: int = 0                   # d_k = d_v of the linear-attention heads
+    ssm_k_heads: int = 0
+    ssm_v_heads: int = 0
+    rope_dim: int = 0                    # leading dims of each head that are rotated (0: all of head_dim)
+    attn_gate: bool = False              # attn_q holds [q | gate] per head; the attention output is scaled by sigmoid(gate)
     name: str = "tiny-qwen3"
 
     @property
     def is_moe(self) -> bool:
         return self.n_experts > 0
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.full_attention_interval > 0
+
+    def is_gdn_layer(self, i: int) -> bool:
+        """Trunk layer i is linear attention (NextN layers, i >= n_layers, are always full attention)."""
+        return self.is_hybrid and i < self.n_layers and (i + 1) % self.full_attention_interval != 0
+
+    def kv_layers(self, layer_ids) -> list[int]:
+        """Of the given layers, the ones that own a KV-cache layer (all but the linear-attention ones)."""
+        return [i for i in layer_ids if not self.is_gdn_layer(i)]
+
+    def gdn_layers(self, layer_ids) -> list[int]:
+        return [i for i in layer_ids if self.is_gdn_layer(i)]
+
+    @property
+    def gdn_key_dim(self) -> int:
+        return self.ssm_k_heads * self.ssm_state
+
+    @property
+    def gdn_value_dim(self) -> int:
+        return self.ssm_v_heads * self.ssm_state
+
+    @property
+    def gdn_conv_dim(self) -> int:
+        return 2 * self.gdn_key_dim + self.gdn_value_dim
+
+    @property
+    def rotary_dim(self) -> int:
+        return self.rope_dim or self.head_dim
+
+    @property
+    def ffn_norm_name(self) -> str:
+        """GGUF name of the second norm of a block: qwen35 files call it post_attention_norm."""
+        return "post_attention_norm.weight" if self.arch.startswith("qwen35") else "ffn_norm.weight"
 
     @property
     def q_dim(self) -> int:
@@ -63,7 +109,7 @@ class ModelConfig:
         arch = gf.architecture
         if arch not in SUPPORTED_ARCHS:
             raise ValueError(f"unsupported GGUF architecture '{arch}' (supported: {', '.join(SUPPORTED_ARCHS)}; "
-                             "the hybrid Gated-DeltaNet families qwen35/qwen35moe are not built here)")
+                             "of the hybrid Gated-DeltaNet families the dense qwen35 is built, qwen35moe is not)")
         a = gf.arch_key
         d_model = int(a("embedding_length"))
         n_heads = int(a("attention.head_count"))
@@ -78,6 +124,17 @@ class ModelConfig:
             vocab = int(a("vocab_size"))
         nextn = int(a("nextn_predict_layers", 0))
         n_blocks = int(a("block_count"))
+        hybrid = {}
+        first_attn = 0                                  # first block with softmax attention (QK-norm / bias probes look there)
+        if arch == "qwen35":
+            interval = int(a("full_attention_interval", 4))
+            first_attn = interval - 1
+            hybrid = dict(full_attention_interval=interval, ssm_conv_kernel=int(a("ssm.conv_kernel", 4)),
+                          ssm_state=int(a("ssm.state_size")), ssm_k_heads=int(a("ssm.group_count")),
+                          ssm_v_heads=int(a("ssm.time_step_rank")), rope_dim=int(a("rope.dimension_count", 0) or 0),
+                          attn_gate=True)
+            if int(a("ssm.inner_size", hybrid["ssm_v_heads"] * hybrid["ssm_state"])) != hybrid["ssm_v_heads"] * hybrid["ssm_state"]:
+                raise ValueError("qwen35: ssm.inner_size is not ssm.time_step_rank x ssm.state_size")
         return ModelConfig(
             arch=arch,
             n_layers=n_blocks - nextn,
@@ -90,8 +147,8 @@ class ModelConfig:
             rope_theta=float(a("rope.freq_base", 10000.0)),
             rms_eps=float(a("attention.layer_norm_rms_epsilon", 1e-6)),
             context_length=int(a("context_length", 4096)),
-            qk_norm="blk.0.attn_q_norm.weight" in gf,
-            qkv_bias="blk.0.attn_q.bias" in gf,
+            qk_norm=f"blk.{first_attn}.attn_q_norm.weight" in gf,
+            qkv_bias=f"blk.{first_attn}.attn_q.bias" in gf,
             tie_embeddings="output.weight" not in gf,
             n_experts=int(a("expert_count", 0) or 0),
             n_experts_used=int(a("expert_used_count", 0) or 0),
@@ -99,6 +156,7 @@ class ModelConfig:
             norm_topk_prob=True,
             nextn_layers=nextn,
             name=str(gf.get("general.name", arch)),
+            **hybrid,
         )
 
     def gguf_metadata(self) -> dict:
@@ -123,6 +181,15 @@ class ModelConfig:
             md[f"{a}.expert_feed_forward_length"] = self.expert_ff
         if self.nextn_layers:
             md[f"{a}.nextn_predict_layers"] = self.nextn_layers
+        if self.is_hybrid:
+            md[f"{a}.full_attention_interval"] = self.full_attention_interval
+            md[f"{a}.ssm.conv_kernel"] = self.ssm_conv_kernel
+            md[f"{a}.ssm.state_size"] = self.ssm_state
+            md[f"{a}.ssm.group_count"] = self.ssm_k_heads
+            md[f"{a}.ssm.time_step_rank"] = self.ssm_v_heads
+            md[f"{a}.ssm.inner_size"] = self.gdn_value_dim
+            if self.rope_dim:
+                md[f"{a}.rope.dimension_count"] = self.rope_dim
         return md
 
 
@@ -182,6 +249,14 @@ SHAPES = {
     "tiny-qwen2": ModelConfig(name="tiny-qwen2", arch="qwen2", qk_norm=False, qkv_bias=True),
     "tiny-qwen3moe": ModelConfig(name="tiny-qwen3moe", arch="qwen3moe", n_experts=8, n_experts_used=2,
                                  expert_ff=256, d_ff=0),
+    # hybrid: layers 0-2 and 4-6 linear attention, 3 and 7 softmax attention with an output gate and partial RoPE;
+    # twice as many value heads as key heads (the 4B / 27B ratio)
+    "tiny-qwen35": ModelConfig(name="tiny-qwen35", arch="qwen35", n_layers=8, head_dim=64, rope_dim=16, attn_gate=True,
+                               full_attention_interval=4, ssm_state=32, ssm_k_heads=2, ssm_v_heads=4, rope_theta=1e7),
+    "qwen3.5-27b": ModelConfig(name="qwen3.5-27b", arch="qwen35", n_layers=64, d_model=5120, n_heads=24, n_kv_heads=4,
+                               head_dim=256, rope_dim=64, attn_gate=True, d_ff=17408, vocab_size=248320,
+                               tie_embeddings=False, full_attention_interval=4, ssm_state=128, ssm_k_heads=16,
+                               ssm_v_heads=48, rope_theta=1e7, context_length=262144),
     "qwen3-8b": ModelConfig(name="qwen3-8b", n_layers=36, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128,
                             d_ff=12288, vocab_size=151936, tie_embeddings=False, context_length=40960),
     "qwen3-32b": ModelConfig(name="qwen3-32b", n_layers=64, d_model=5120, n_heads=64, n_kv_heads=8, head_dim=128,

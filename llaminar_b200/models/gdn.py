@@ -1,0 +1,114 @@
+"""Gated-DeltaNet linear attention in plain PyTorch: the pieces of the hybrid (qwen35) blocks.
+
+A linear-attention block keeps, per sequence, the last ``K - 1`` inputs of a short causal convolution and one
+``d_k x d_v`` matrix per value head.  Per token t and head:
+
+    a_t = exp(g_t)                      g_t = ssm_a * softplus(alpha_t + dt_bias)        (ssm_a = -exp(A_log) < 0)
+    S   = a_t * S                       decay
+    u_t = beta_t * (v_t - S^T k_t)      delta-rule correction, beta_t = sigmoid(b_t)
+    S   = S + k_t u_t^T
+    o_t = S^T q_t                       q, k L2-normalised, q scaled by d_k^-1/2
+
+(reference: the recurrence and chunk kernels of src/v2/kernels/cuda/gdn/CUDAGatedDeltaNetKernels.cu and the stage that
+drives them, src/v2/execution/compute_stages/stages/GDNRecurrenceStage.cpp; value head j reads key head j mod n_k, the
+tiled order GGUF files store).  Two evaluators of the same recurrence are given: token by token (decode, and the oracle of
+the other), and chunk-parallel for prefill, which turns a chunk of C tokens into one unit-lower-triangular solve and three
+matrix products per head.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def causal_conv_silu(x: torch.Tensor, state: torch.Tensor, w: torch.Tensor):
+    """Depth-wise causal convolution + SiLU over one sequence.  x: [T, C] new inputs, state: [C, K-1] the inputs before
+    them (zeros at the start of a sequence), w: [C, K] taps (tap K-1 multiplies the newest input).  Returns
+    (y [T, C], new state [C, K-1])."""
+    T, C = x.shape
+    K = w.shape[1]
+    xp = torch.cat([state.t().to(x.dtype), x], dim=0)                    # [K-1+T, C]
+    y = torch.zeros(T, C, dtype=x.dtype, device=x.device)
+    for j in range(K):
+        y += xp[j:j + T] * w[:, j]
+    return F.silu(y), xp[T:].t().contiguous()
+
+
+def gates(alpha: torch.Tensor, b: torch.Tensor, ssm_a: torch.Tensor, dt_bias: torch.Tensor):
+    """Log-decay g (<= 0) and write strength beta of every (token, value head).  alpha, b: [T, H]."""
+    return ssm_a.float() * F.softplus(alpha.float() + dt_bias.float()), torch.sigmoid(b.float())
+
+
+def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(dim=-1, keepdim=True) + eps)
+
+
+def expand_key_heads(x: torch.Tensor, n_v: int, v_head_offset: int = 0) -> torch.Tensor:
+    """[T, n_k, d] -> [T, n_v, d]: value head j (global index j + v_head_offset) reads key head (j + offset) mod n_k."""
+    n_k = x.shape[1]
+    idx = (torch.arange(n_v, device=x.device) + v_head_offset) % n_k
+    return x.index_select(1, idx)
+
+
+def delta_rule_recurrent(q, k, v, g, beta, S):
+    """Token-by-token evaluation.  q, k: [T, H, dk] (already normalised / scaled), v: [T, H, dv], g, beta: [T, H],
+    S: [H, dk, dv] float32 (updated in place).  Returns o [T, H, dv]."""
+    T = q.shape[0]
+    o = torch.empty_like(v, dtype=torch.float32)
+    for t in range(T):
+        S.mul_(torch.exp(g[t])[:, None, None])
+        u = (v[t] - torch.einsum("hkv,hk->hv", S, k[t])) * beta[t][:, None]
+        S.add_(torch.einsum("hk,hv->hkv", k[t], u))
+        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return o
+
+
+def delta_rule_chunked(q, k, v, g, beta, S, chunk: int = 64):
+    """Chunk-parallel evaluation of the same recurrence (same arguments and result as `delta_rule_recurrent`).
+
+    Inside a chunk let G_t be the running sum of g and M[t, i] = exp(G_t - G_i) for i <= t (0 above the diagonal).  The
+    corrections solve (I + A) U = beta * (V - exp(G) * K S0) with A[t, i] = beta_t M[t, i] (k_t . k_i) for i < t; then
+    O = exp(G) * Q S0 + (M * Q K^T) U and S_C = exp(G_C) S0 + K^T (exp(G_C - G) * U).  Every exponent is <= 0."""
+    T, H, dk = q.shape
+    o = torch.empty(T, H, v.shape[-1], dtype=torch.float32, device=q.device)
+    for c0 in range(0, T, chunk):
+        c1 = min(T, c0 + chunk)
+        C = c1 - c0
+        qc, kc, vc = (x[c0:c1].float().transpose(0, 1) for x in (q, k, v))          # [H, C, d]
+        gc, bc = g[c0:c1].float().t(), beta[c0:c1].float().t()                      # [H, C]
+        G = torch.cumsum(gc, dim=1)
+        low = torch.tril(torch.ones(C, C, dtype=torch.bool, device=q.device))
+        M = torch.exp((G[:, :, None] - G[:, None, :]).masked_fill(~low, float("-inf")))       # [H, C, C], 0 above the diagonal
+        eG = torch.exp(G)[:, :, None]
+        A = (kc @ kc.transpose(1, 2)) * M * bc[:, :, None]
+        A = A.masked_fill(torch.eye(C, dtype=torch.bool, device=q.device), 0.0)               # strictly lower
+        rhs = (vc - eG * (kc @ S)) * bc[:, :, None]
+        U = torch.linalg.solve_triangular(A + torch.eye(C, device=q.device), rhs, upper=False, unitriangular=True)
+        o[c0:c1] = (eG * (qc @ S) + ((qc @ kc.transpose(1, 2)) * M) @ U).transpose(0, 1)
+        last = torch.exp(G[:, -1:, None] - G[:, :, None])                                     # [H, C, 1]
+        S.mul_(torch.exp(G[:, -1])[:, None, None]).add_(kc.transpose(1, 2) @ (last * U))
+    return o
+
+
+def gated_rmsnorm(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over each head's d_v values, then * SiLU(z).  o, z: [T, H, dv]; w: [dv]."""
+    of = o.float()
+    return of * torch.rsqrt(of.pow(2).mean(dim=-1, keepdim=True) + eps) * w.float() * F.silu(z.float())
+
+
+def gdn_mix(qkv: torch.Tensor, z: torch.Tensor, alpha: torch.Tensor, b: torch.Tensor, conv_w, ssm_a, dt_bias, norm_w,
+            conv_state: torch.Tensor, S: torch.Tensor, n_k: int, n_v: int, d: int, eps: float,
+            v_head_offset: int = 0, chunk: int = 64) -> tuple[torch.Tensor, torch.Tensor]:
+    """Everything between the input projections and the output projection of one linear-attention block, for the new
+    tokens of ONE sequence.  qkv: [T, 2 n_k d + n_v d], z: [T, n_v d], alpha, b: [T, n_v]; conv_state [C, K-1] and
+    S [n_v, d, d] are the sequence's state before these tokens.  Returns (rows [T, n_v d] for the output projection,
+    new conv state); S is updated in place."""
+    T = qkv.shape[0]
+    y, conv_state = causal_conv_silu(qkv.float(), conv_state, conv_w.float())
+    q, k, v = torch.split(y, [n_k * d, n_k * d, n_v * d], dim=-1)
+    q = expand_key_heads(l2norm(q.view(T, n_k, d)) * d ** -0.5, n_v, v_head_offset)
+    k = expand_key_heads(l2norm(k.view(T, n_k, d)), n_v, v_head_offset)
+    g, beta = gates(alpha, b, ssm_a, dt_bias)
+    run = delta_rule_recurrent if T <= 4 else delta_rule_chunked
+    o = run(q, k, v.view(T, n_v, d), g, beta, S) if T <= 4 else run(q, k, v.view(T, n_v, d), g, beta, S, chunk)
+    return gated_rmsnorm(o, z.view(T, n_v, d), norm_w, eps).reshape(T, n_v * d), conv_state

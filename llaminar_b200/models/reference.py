@@ -4,13 +4,16 @@ Implements the block order the reference builds for qwen2 / qwen3 (RMSNorm -> QK
 per-head QK RMSNorm -> split-half RoPE -> causal GQA attention -> Wo; RMSNorm -> SwiGLU FFN or
 softmax-top-k MoE; reference: src/v2/models/qwen/QwenStandardGraph.cpp:103-203,
 src/v2/models/qwen/QwenGraphBase.cpp:1974-2176) and the NextN multi-token-prediction head
-(src/v2/models/qwen35/Qwen35Graph.cpp:403-610) on dequantised weights.
+(src/v2/models/qwen35/Qwen35Graph.cpp:403-610) on dequantised weights.  The hybrid qwen35 family adds linear-attention
+blocks (models/gdn.py) and, in its softmax blocks, a per-head output gate and partial rotation
+(src/v2/models/qwen35/Qwen35Graph.cpp:980-990).
 """
 from __future__ import annotations
 
 import torch
 import torch.nn.functional as F
 
+from . import gdn
 from .config import ModelConfig
 from .weights import ModelWeights
 
@@ -20,8 +23,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps) * w
 
 
-def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
-    """x: [T, H, D]; rotates pairs (i, i + D/2) by pos * theta^(-2i/D)."""
+def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float, rotary_dim: int = 0) -> torch.Tensor:
+    """x: [T, H, D]; rotates pairs (i, i + R/2) of the first R = rotary_dim (default D) values by pos * theta^(-2i/R); the
+    rest of each head passes through."""
+    if rotary_dim and rotary_dim < x.shape[-1]:
+        return torch.cat([rope_split_half(x[..., :rotary_dim], positions, theta), x[..., rotary_dim:]], dim=-1)
     D = x.shape[-1]
     half = D // 2
     inv = theta ** (-torch.arange(half, device=x.device, dtype=torch.float32) * 2.0 / D)
@@ -48,6 +54,9 @@ class KVState:
     def __init__(self, n_layers: int):
         self.k = [None] * n_layers
         self.v = [None] * n_layers
+        self.conv = {}                  # linear-attention layers: last K-1 convolution inputs [C, K-1]
+        self.rec = {}                   # ... and the recurrent matrices [n_v, d, d]
+        self.seen = 0                   # tokens fed so far
 
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor):
         self.k[layer] = k if self.k[layer] is None else torch.cat([self.k[layer], k], dim=0)
@@ -55,9 +64,12 @@ class KVState:
         return self.k[layer], self.v[layer]
 
     def length(self) -> int:
-        return 0 if self.k[0] is None else self.k[0].shape[0]
+        return self.seen
 
     def truncate(self, n: int) -> None:
+        if self.rec and n != self.seen:
+            raise ValueError("a recurrent state cannot be rolled back")
+        self.seen = n
         for i in range(len(self.k)):
             if self.k[i] is not None:
                 self.k[i], self.v[i] = self.k[i][:n], self.v[i][:n]
@@ -87,14 +99,18 @@ class ReferenceModel:
         v = x @ w[p + "attn_v.weight"].T
         if c.qkv_bias:
             q, k, v = q + w[p + "attn_q.bias"], k + w[p + "attn_k.bias"], v + w[p + "attn_v.bias"]
-        q = q.view(T, c.n_heads, c.head_dim)
+        gate = None
+        if c.attn_gate:                 # every head's rows are [query | gate]
+            q, gate = q.view(T, c.n_heads, 2, c.head_dim).unbind(dim=2)
+            gate = gate.reshape(T, c.q_dim)
+        q = q.reshape(T, c.n_heads, c.head_dim)
         k = k.view(T, c.n_kv_heads, c.head_dim)
         v = v.view(T, c.n_kv_heads, c.head_dim)
         if c.qk_norm:
             q = rmsnorm(q, w[p + "attn_q_norm.weight"], c.rms_eps)
             k = rmsnorm(k, w[p + "attn_k_norm.weight"], c.rms_eps)
-        q = rope_split_half(q, positions, c.rope_theta)
-        k = rope_split_half(k, positions, c.rope_theta)
+        q = rope_split_half(q, positions, c.rope_theta, c.rotary_dim)
+        k = rope_split_half(k, positions, c.rope_theta, c.rotary_dim)
         K, V = kv.append(kv_layer, k, v)
         S = K.shape[0]
         past = S - T
@@ -106,7 +122,20 @@ class ReferenceModel:
         qry_pos = (past + torch.arange(T, device=x.device))[:, None]
         scores = scores.masked_fill((key_pos > qry_pos)[None], float("-inf"))
         o = torch.einsum("hts,shd->thd", torch.softmax(scores, dim=-1), Vh).reshape(T, c.q_dim)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
         return o @ w[p + "attn_output.weight"].T
+
+    def linear_attention(self, i: int, x: torch.Tensor, kv: KVState) -> torch.Tensor:
+        c, w, p = self.cfg, self.w, f"blk.{i}."
+        if i not in kv.rec:
+            kv.conv[i] = torch.zeros(c.gdn_conv_dim, c.ssm_conv_kernel - 1, device=x.device)
+            kv.rec[i] = torch.zeros(c.ssm_v_heads, c.ssm_state, c.ssm_state, device=x.device)
+        rows, kv.conv[i] = gdn.gdn_mix(x @ w[p + "attn_qkv.weight"].T, x @ w[p + "attn_gate.weight"].T,
+                                       x @ w[p + "ssm_alpha.weight"].T, x @ w[p + "ssm_beta.weight"].T,
+                                       w[p + "ssm_conv1d.weight"], w[p + "ssm_a"], w[p + "ssm_dt.bias"], w[p + "ssm_norm.weight"],
+                                       kv.conv[i], kv.rec[i], c.ssm_k_heads, c.ssm_v_heads, c.ssm_state, c.rms_eps)
+        return rows @ w[p + "ssm_out.weight"].T
 
     def ffn(self, i: int, x: torch.Tensor) -> torch.Tensor:
         c, w, p = self.cfg, self.w, f"blk.{i}."
@@ -128,8 +157,9 @@ class ReferenceModel:
     def layer(self, i: int, h: torch.Tensor, positions: torch.Tensor, kv: KVState, kv_layer: int | None = None):
         c, w, p = self.cfg, self.w, f"blk.{i}."
         kv_layer = i if kv_layer is None else kv_layer
-        h = h + self.attention(i, rmsnorm(h, w[p + "attn_norm.weight"], c.rms_eps), positions, kv, kv_layer)
-        h = h + self.ffn(i, rmsnorm(h, w[p + "ffn_norm.weight"], c.rms_eps))
+        x = rmsnorm(h, w[p + "attn_norm.weight"], c.rms_eps)
+        h = h + (self.linear_attention(i, x, kv) if c.is_gdn_layer(i) else self.attention(i, x, positions, kv, kv_layer))
+        h = h + self.ffn(i, rmsnorm(h, w[p + c.ffn_norm_name], c.rms_eps))
         return h
 
     # -- full passes -------------------------------------------------------------------------
@@ -145,6 +175,7 @@ class ReferenceModel:
             h = self.layer(i, h, pos, kv)
             if taps is not None:
                 taps[f"layer{i}"] = h.clone()
+        kv.seen += tokens.shape[0]
         return self.lm_head(h), h, kv
 
     @torch.no_grad()
@@ -160,6 +191,7 @@ class ReferenceModel:
         x = torch.cat([e, hn], dim=-1) @ w[p + "eh_proj.weight"].T
         pos = kv.length() + torch.arange(x.shape[0], device=self.device)
         h = self.layer(i, x, pos, kv, kv_layer=0)
+        kv.seen += x.shape[0]
         return self.lm_head(h, p + "shared_head_norm.weight"), h, kv
 
     @torch.no_grad()

@@ -63,10 +63,37 @@ def synthesize(cfg: ModelConfig, recipe: QuantRecipe | str = "Q8_0", seed: int =
     if not cfg.tie_embeddings:
         mat("output.weight", cfg.vocab_size, d)
 
-    def decoder_layer(i: int) -> None:
+    def rand_vec(name: str, n: int, lo: float, hi: float, sign: float = 1.0) -> None:
+        x = (torch.rand(n, generator=gen, device=dev, dtype=torch.float32) * (hi - lo) + lo) * sign
+        tensors[name] = qtensor_from_float(x, GGMLType.F32)
+
+    def gdn_layer(i: int) -> None:
+        """Linear-attention block of the hybrid family (names: src/v2/models/qwen35/Qwen35Schema.h:107-134 of the reference).
+        ssm_a holds -exp(A_log); the convolution taps are a [channels, kernel] matrix; value heads are in tiled order
+        (value head j reads key head j mod n_k)."""
         p = f"blk.{i}."
         vec(p + "attn_norm.weight", d)
-        mat(p + "attn_q.weight", qd, d, layer=i)
+        mat(p + "attn_qkv.weight", cfg.gdn_conv_dim, d, layer=i)
+        mat(p + "attn_gate.weight", cfg.gdn_value_dim, d, layer=i)
+        mat(p + "ssm_alpha.weight", cfg.ssm_v_heads, d, layer=i)
+        mat(p + "ssm_beta.weight", cfg.ssm_v_heads, d, layer=i)
+        x = torch.randn(cfg.gdn_conv_dim, cfg.ssm_conv_kernel, generator=gen, device=dev, dtype=torch.float32) * 0.3
+        tensors[p + "ssm_conv1d.weight"] = qtensor_from_float(x, GGMLType.F32)
+        rand_vec(p + "ssm_dt.bias", cfg.ssm_v_heads, -1.0, 1.0)
+        rand_vec(p + "ssm_a", cfg.ssm_v_heads, 0.5, 8.0, sign=-1.0)
+        vec(p + "ssm_norm.weight", cfg.ssm_state)
+        mat(p + "ssm_out.weight", d, cfg.gdn_value_dim, layer=i)
+        vec(p + cfg.ffn_norm_name, d)
+        mat(p + "ffn_gate.weight", cfg.d_ff, d, layer=i)
+        mat(p + "ffn_up.weight", cfg.d_ff, d, layer=i)
+        mat(p + "ffn_down.weight", d, cfg.d_ff, layer=i)
+
+    def decoder_layer(i: int) -> None:
+        if cfg.is_gdn_layer(i):
+            return gdn_layer(i)
+        p = f"blk.{i}."
+        vec(p + "attn_norm.weight", d)
+        mat(p + "attn_q.weight", qd * (2 if cfg.attn_gate else 1), d, layer=i)
         mat(p + "attn_k.weight", kvd, d, layer=i)
         mat(p + "attn_v.weight", kvd, d, layer=i)
         mat(p + "attn_output.weight", d, qd, layer=i)
@@ -77,7 +104,7 @@ def synthesize(cfg: ModelConfig, recipe: QuantRecipe | str = "Q8_0", seed: int =
         if cfg.qk_norm:
             vec(p + "attn_q_norm.weight", cfg.head_dim)
             vec(p + "attn_k_norm.weight", cfg.head_dim)
-        vec(p + "ffn_norm.weight", d)
+        vec(p + cfg.ffn_norm_name, d)
         if cfg.is_moe:
             mat(p + "ffn_gate_inp.weight", cfg.n_experts, d, layer=i)
             mat(p + "ffn_gate_exps.weight", cfg.n_experts, cfg.expert_ff, d, layer=i)

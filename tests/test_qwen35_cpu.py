@@ -1,0 +1,144 @@
+"""The hybrid Gated-DeltaNet family (qwen35) on the CPU: the chunk-parallel delta rule against the token-by-token form, the
+fp32 oracle against the `transformers` implementation of the architecture (weights converted the way GGUF files store them:
+norm gains as 1 + w, ssm_a = -exp(A_log), value heads in tiled order), and the engine's runner against the oracle."""
+import pytest
+import torch
+
+from llaminar_b200.gguf import GGMLType
+from llaminar_b200.models import gdn
+from llaminar_b200.models.config import SHAPES, ModelConfig
+from llaminar_b200.models.reference import ReferenceModel
+from llaminar_b200.models.synth import synthesize
+from llaminar_b200.models.weights import ModelWeights, qtensor_from_float
+
+
+def test_chunked_delta_rule_matches_token_by_token():
+    torch.manual_seed(0)
+    T, H, d = 150, 4, 32
+    q = gdn.l2norm(torch.randn(T, H, d)) * d ** -0.5
+    k = gdn.l2norm(torch.randn(T, H, d))
+    v = torch.randn(T, H, d)
+    g, beta = -torch.rand(T, H) * 3, torch.rand(T, H)
+    S0 = torch.randn(H, d, d) * 0.1
+    S1, S2 = S0.clone(), S0.clone()
+    o1 = gdn.delta_rule_recurrent(q, k, v, g, beta, S1)
+    o2 = gdn.delta_rule_chunked(q, k, v, g, beta, S2, chunk=64)
+    assert (o1 - o2).abs().max() < 1e-5 and (S1 - S2).abs().max() < 1e-5
+
+
+def test_convolution_state_carries_across_calls():
+    torch.manual_seed(1)
+    x, w = torch.randn(11, 6), torch.randn(6, 4)
+    y, _ = gdn.causal_conv_silu(x, torch.zeros(6, 3), w)
+    y1, st = gdn.causal_conv_silu(x[:5], torch.zeros(6, 3), w)
+    y2, _ = gdn.causal_conv_silu(x[5:], st, w)
+    assert torch.allclose(y, torch.cat([y1, y2]), atol=1e-6)
+
+
+def _hf_model():
+    tf = pytest.importorskip("transformers")
+    try:
+        from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM, Qwen3_5TextConfig
+    except Exception as e:                                    # an older transformers without the family
+        pytest.skip(f"transformers has no qwen3_5: {e}")
+    cfg = Qwen3_5TextConfig(hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                            intermediate_size=128, vocab_size=128, rms_norm_eps=1e-6, max_position_embeddings=512,
+                            layer_types=["linear_attention"] * 3 + ["full_attention"], full_attention_interval=4,
+                            linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+                            linear_conv_kernel_dim=4, tie_word_embeddings=False,
+                            rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                                             "mrope_section": [2, 1, 1]})
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(3)
+    m = Qwen3_5ForCausalLM(cfg).float().eval()
+    with torch.no_grad():                                      # make every learned vector non-trivial
+        for n, p in m.named_parameters():
+            if p.dim() == 1:
+                p.copy_(torch.randn_like(p) * 0.3)
+            if n.endswith("A_log"):
+                p.copy_(torch.log(torch.rand_like(p) * 6 + 0.5))
+            if n.endswith("linear_attn.norm.weight"):
+                p.copy_(torch.rand_like(p) + 0.5)
+    return cfg, m
+
+
+def _tiled_value_heads(n_k: int, n_v: int) -> list[int]:
+    """GGUF value head i = r * n_k + kh holds the transformers value head kh * rep + r (so that head i reads key head
+    i mod n_k where transformers reads key head j div rep)."""
+    rep = n_v // n_k
+    return [(i % n_k) * rep + i // n_k for i in range(n_v)]
+
+
+def _convert(cfg, m) -> ModelWeights:
+    n_k, n_v, d = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim
+    ours = ModelConfig(name="hf-tiny-qwen35", arch="qwen35", n_layers=cfg.num_hidden_layers, d_model=cfg.hidden_size,
+                       n_heads=cfg.num_attention_heads, n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+                       d_ff=cfg.intermediate_size, vocab_size=cfg.vocab_size, rope_theta=10000.0, rms_eps=cfg.rms_norm_eps,
+                       tie_embeddings=False, full_attention_interval=4, ssm_conv_kernel=4, ssm_state=d, ssm_k_heads=n_k,
+                       ssm_v_heads=n_v, rope_dim=int(cfg.head_dim * 0.25), attn_gate=True)
+    sd = {k: v.detach().float() for k, v in m.state_dict().items()}
+    perm = torch.tensor(_tiled_value_heads(n_k, n_v))
+    rows = (perm[:, None] * d + torch.arange(d)[None, :]).reshape(-1)           # value-head blocks of d rows
+    t = {}
+    put = lambda name, x: t.__setitem__(name, qtensor_from_float(x.contiguous(), GGMLType.F32))
+    put("token_embd.weight", sd["model.embed_tokens.weight"])
+    put("output.weight", sd["lm_head.weight"])
+    put("output_norm.weight", 1 + sd["model.norm.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, p = f"model.layers.{i}.", f"blk.{i}."
+        put(p + "attn_norm.weight", 1 + sd[s + "input_layernorm.weight"])
+        put(p + "post_attention_norm.weight", 1 + sd[s + "post_attention_layernorm.weight"])
+        for a, b in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")):
+            put(p + f"ffn_{a}.weight", sd[s + f"mlp.{b}.weight"])
+        if cfg.layer_types[i] == "linear_attention":
+            la = s + "linear_attn."
+            kd = n_k * d
+            qkv = sd[la + "in_proj_qkv.weight"]
+            put(p + "attn_qkv.weight", torch.cat([qkv[:2 * kd], qkv[2 * kd:][rows]]))
+            put(p + "attn_gate.weight", sd[la + "in_proj_z.weight"][rows])
+            put(p + "ssm_alpha.weight", sd[la + "in_proj_a.weight"][perm])
+            put(p + "ssm_beta.weight", sd[la + "in_proj_b.weight"][perm])
+            conv = sd[la + "conv1d.weight"].squeeze(1)
+            put(p + "ssm_conv1d.weight", torch.cat([conv[:2 * kd], conv[2 * kd:][rows]]))
+            put(p + "ssm_dt.bias", sd[la + "dt_bias"][perm])
+            put(p + "ssm_a", -torch.exp(sd[la + "A_log"][perm]))
+            put(p + "ssm_norm.weight", sd[la + "norm.weight"])
+            put(p + "ssm_out.weight", sd[la + "out_proj.weight"][:, rows])
+        else:
+            sa = s + "self_attn."
+            put(p + "attn_q.weight", sd[sa + "q_proj.weight"])
+            put(p + "attn_k.weight", sd[sa + "k_proj.weight"])
+            put(p + "attn_v.weight", sd[sa + "v_proj.weight"])
+            put(p + "attn_output.weight", sd[sa + "o_proj.weight"])
+            put(p + "attn_q_norm.weight", 1 + sd[sa + "q_norm.weight"])
+            put(p + "attn_k_norm.weight", 1 + sd[sa + "k_norm.weight"])
+    return ModelWeights(ours, t)
+
+
+def test_oracle_matches_the_transformers_model():
+    cfg, m = _hf_model()
+    w = _convert(cfg, m)
+    toks = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = m(input_ids=toks[None]).logits[0]
+    ref = ReferenceModel(w)
+    got, _, kv = ref.forward(toks)
+    assert (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+    # the same rows fed in pieces (prefill chunk, second chunk, single tokens): the carried state must give the same logits
+    a, _, kv = ref.forward(toks[:20])
+    b, _, kv = ref.forward(toks[20:33], kv)
+    rest = [ref.forward(toks[i:i + 1], kv)[0] for i in range(33, 37)]
+    assert (torch.cat([a, b] + rest) - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_gguf_round_trip_keeps_the_hybrid_configuration(tmp_path):
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=2)
+    path = str(tmp_path / "h.gguf")
+    w.save_gguf(path)
+    back = ModelWeights.from_gguf(path)
+    c0, c1 = w.config, back.config
+    for f in ("arch", "n_layers", "full_attention_interval", "ssm_conv_kernel", "ssm_state", "ssm_k_heads", "ssm_v_heads",
+              "rope_dim", "attn_gate", "qk_norm", "head_dim"):
+        assert getattr(c0, f) == getattr(c1, f), f
+    assert [c1.is_gdn_layer(i) for i in range(8)] == [True, True, True, False] * 2
+    assert back["blk.0.ssm_conv1d.weight"].shape == (c0.gdn_conv_dim, 4)
