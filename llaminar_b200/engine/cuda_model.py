@@ -76,6 +76,7 @@ class ForwardBatch:
     # which hidden rows get logits (None: all rows)
     logit_rows: torch.Tensor | None = None
     embeds: torch.Tensor | None = None       # optional fp32 [T, d] input instead of token embeddings
+    state_slots: torch.Tensor | None = None  # [B] hybrid models: the state slot of every sequence (row of block_table)
 
     @property
     def is_decode(self) -> bool:
@@ -243,10 +244,21 @@ class CudaModel:
             v0, v1 = pl.vocab_start, pl.vocab_stop
             self.head = QLinear.from_qtensors([head_t.rows(v0, v1)], dev)
             self.vocab_local = v1 - v0
+        self._kv_ids, self._gdn_ids = c.kv_layers(self.layer_ids), c.gdn_layers(self.layer_ids)
+        self.gdn_v_local = pl.gdn_v_stop - pl.gdn_v_start
+        self.gdn_conv_local = 2 * c.gdn_key_dim + self.gdn_v_local * c.ssm_state
+        # hybrid models whose softmax blocks have a head size without an attention kernel here (qwen3.5 checkpoints use 256)
+        # run those blocks on PyTorch ops, which CUDA graphs cannot capture (host-side loop over the sequences)
+        self.torch_attention = c.is_hybrid and c.head_dim not in (64, 128)
+        self.graph_safe = not self.torch_attention
         self.layers = [self._build_layer(weights, i) for i in self.layer_ids]
         self.mtp_layers = []
-        self.mtp_kv_base = len(self.layer_ids)          # the NextN layers' K/V follow this stage's own layers in the cache
-        self.n_kv_layers = len(self.layer_ids) + (c.nextn_layers if with_mtp else 0)
+        self.mtp_kv_base = len(self._kv_ids)            # the NextN layers' K/V follow this stage's own layers in the cache
+        self.n_kv_layers = len(self._kv_ids) + (c.nextn_layers if with_mtp else 0)
+        self.hybrid_dims = None
+        if self._gdn_ids:
+            self.hybrid_dims = dict(n_layers=len(self._gdn_ids), conv_dim=self.gdn_conv_local, conv_kernel=c.ssm_conv_kernel,
+                                    n_v_heads=self.gdn_v_local, d=c.ssm_state)
         for j in range(c.nextn_layers if with_mtp else 0):
             i = c.n_layers + j
             lay = self._build_layer(weights, i)
@@ -272,9 +284,16 @@ class CudaModel:
         L = CudaLayer()
         L.index = i
         L.attn_norm = _f32(w[p + "attn_norm.weight"], dev)
-        L.ffn_norm = _f32(w[p + "ffn_norm.weight"], dev)
+        L.ffn_norm = _f32(w[p + c.ffn_norm_name], dev)
+        L.is_gdn = c.is_gdn_layer(i)
+        L.kv_index = self._kv_ids.index(i) if i in self._kv_ids else (self.mtp_kv_base + i - c.n_layers if i >= c.n_layers else None)
+        if L.is_gdn:
+            self._build_gdn(L, w, p)
+            self._build_ffn(L, w, p)
+            return L
         D = c.head_dim
-        q = w[p + "attn_q.weight"].rows(pl.q_head_start * D, pl.q_head_stop * D)
+        qw = 2 if c.attn_gate else 1                            # rows of a head: [query | gate]
+        q = w[p + "attn_q.weight"].rows(pl.q_head_start * D * qw, pl.q_head_stop * D * qw)
         k = w[p + "attn_k.weight"].rows(pl.kv_head_start * D, pl.kv_head_stop * D)
         v = w[p + "attn_v.weight"].rows(pl.kv_head_start * D, pl.kv_head_stop * D)
         bias = None
@@ -287,6 +306,11 @@ class CudaModel:
         L.q_norm = _f32(w.get(p + "attn_q_norm.weight"), dev) if c.qk_norm else None
         L.k_norm = _f32(w.get(p + "attn_k_norm.weight"), dev) if c.qk_norm else None
         L.wo = QLinear.from_qtensors([w[p + "attn_output.weight"].cols(pl.q_head_start * D, pl.q_head_stop * D)], dev)
+        self._build_ffn(L, w, p)
+        return L
+
+    def _build_ffn(self, L: CudaLayer, w: ModelWeights, p: str) -> None:
+        c, dev, pl = self.cfg, self.device, self.plan
         if c.is_moe:
             L.router = w[p + "ffn_gate_inp.weight"].to_float().to(dev).to(torch.bfloat16).contiguous()
             e0, e1 = pl.expert_start, pl.expert_stop
@@ -298,7 +322,26 @@ class CudaModel:
             u = w[p + "ffn_up.weight"].rows(f0, f1)
             L.gate_up = self._pack_gate_up(g, u)
             L.down = QLinear.from_qtensors([w[p + "ffn_down.weight"].cols(f0, f1)], dev)
-        return L
+
+    def _build_gdn(self, L: CudaLayer, w: ModelWeights, p: str) -> None:
+        """Linear-attention block.  One input projection produces q | k (all key heads) | v (this rank's value heads) | z |
+        alpha | b in one launch; `wo` is the row-parallel output projection over this rank's value heads
+        (sharding as in the reference: src/v2/models/qwen35/Qwen35Schema.h:107-134)."""
+        c, dev, pl = self.cfg, self.device, self.plan
+        d, kd = c.ssm_state, c.gdn_key_dim
+        v0, v1 = pl.gdn_v_start, pl.gdn_v_stop
+        qkv, z = w[p + "attn_qkv.weight"], w[p + "attn_gate.weight"]
+        L.gdn_index = self._gdn_ids.index(L.index)
+        L.qkv = QLinear.from_qtensors([qkv.rows(0, 2 * kd), qkv.rows(2 * kd + v0 * d, 2 * kd + v1 * d), z.rows(v0 * d, v1 * d),
+                                       w[p + "ssm_alpha.weight"].rows(v0, v1), w[p + "ssm_beta.weight"].rows(v0, v1)], dev)
+        L.z_off = self.gdn_conv_local
+        L.ab_off = L.z_off + (v1 - v0) * d
+        rows = torch.cat([torch.arange(2 * kd), 2 * kd + torch.arange(v0 * d, v1 * d)])
+        L.conv_w = _f32(w[p + "ssm_conv1d.weight"], dev)[rows.to(dev)].contiguous()
+        L.ssm_a = _f32(w[p + "ssm_a"], dev)[v0:v1].contiguous()
+        L.dt_bias = _f32(w[p + "ssm_dt.bias"], dev)[v0:v1].contiguous()
+        L.ssm_norm = _f32(w[p + "ssm_norm.weight"], dev)
+        L.wo = QLinear.from_qtensors([w[p + "ssm_out.weight"].cols(v0 * d, v1 * d)], dev)
 
     def _pack_gate_up(self, g: QTensor, u: QTensor) -> QLinear:
         dev = self.device
@@ -347,9 +390,12 @@ class CudaModel:
         e = lambda *s, dt=bf: torch.empty(*s, dtype=dt, device=dev)
         self.ws_h = e(T, c.d_model, dt=f32)
         self.ws_xn = e(T, c.d_model)
-        self.ws_qkv = e(T, self.qkv_dim)
+        gdn_in = self.gdn_conv_local + self.gdn_v_local * c.ssm_state + 2 * self.gdn_v_local if self._gdn_ids else 0
+        self.ws_qkv = e(T, max(self.qkv_dim + (self.q_dim if c.attn_gate else 0), (gdn_in + 63) // 64 * 64))
         self.ws_q = e(T, self.n_heads_local, c.head_dim)
         self.ws_o = e(T, self.q_dim)
+        self.ws_gdn_o = e(T, self.gdn_v_local * c.ssm_state) if self._gdn_ids else None      # input of the block's output projection
+        self.ws_gdn_y = e(T, self.gdn_conv_local, dt=f32) if self._gdn_ids else None
         ff = max(self.ff_local, c.expert_ff if c.is_moe else 0)
         self.ws_act = e(T, ff)
         self.ws_gu = e(T, 2 * ff) if any(getattr(L.gate_up, "fused_swiglu", True) is False for L in self.layers if L.gate_up) else None
@@ -377,6 +423,89 @@ class CudaModel:
             ops.attn_prefill(q, kv_bf16, o3, btab, fb.cu_q, fb.ctx_lens, self.n_heads_local,
                              self.n_kv_local, c.head_dim, scale, fb.max_q_len, scratch=self.scratch)
         return o
+
+    def _linear_attention(self, L: CudaLayer, fb: ForwardBatch, inp: torch.Tensor, T: int) -> torch.Tensor:
+        """Between the input and output projections of a Gated-DeltaNet block.  Decode steps (one row per sequence) run
+        the two step kernels on the sequences' state slots; prefill chunks run the chunk-parallel form on PyTorch ops,
+        sequence by sequence (one host synchronisation per forward pass for the row ranges)."""
+        c, hs = self.cfg, self._kv.hybrid
+        d, nv = c.ssm_state, self.gdn_v_local
+        o = self.ws_gdn_o[:T]
+        conv, rec = hs.conv[L.gdn_index], hs.rec[L.gdn_index]
+        if fb.is_decode and fb.rows_per_seq == 1:
+            ops.gdn_step(inp, self.gdn_conv_local, L.z_off, L.ab_off, L.conv_w, L.ssm_a, L.dt_bias, L.ssm_norm, conv, rec,
+                         fb.state_slots, self.ws_gdn_y[:T], o, c.ssm_k_heads, self.plan.gdn_v_start, c.rms_eps)
+            return o
+        from ..models import gdn
+        seqs = getattr(fb, "_gdn_seqs", None)
+        if seqs is None:
+            seqs = fb._gdn_seqs = gdn.batch_sequences(fb.seq_ids, fb.positions, fb.state_slots)
+        C = self.gdn_conv_local
+        x = inp.float()
+        rows = gdn.gdn_block_rows(x[:, :C], x[:, L.z_off:L.z_off + nv * d], x[:, L.ab_off:L.ab_off + nv],
+                                  x[:, L.ab_off + nv:L.ab_off + 2 * nv], seqs, conv, rec, L.conv_w, L.ssm_a, L.dt_bias, L.ssm_norm,
+                                  c.ssm_k_heads, nv, d, c.rms_eps, self.plan.gdn_v_start)
+        o.copy_(rows)
+        return o
+
+    def _attention_gated(self, L: CudaLayer, fb: ForwardBatch, kv_layer: torch.Tensor, qkv: torch.Tensor, T: int) -> torch.Tensor:
+        """Softmax block of the hybrid family: every head's projection rows are [query | gate], only the first `rotary_dim`
+        values of a head are rotated, and the attention output is scaled by sigmoid(gate) before the output projection.
+        The split, QK-norm, rotation and cache append are PyTorch ops (a dozen small launches per block, one block in
+        four); attention itself runs the paged kernels for head sizes 64 and 128 and PyTorch otherwise."""
+        from ..models.reference import rmsnorm, rope_split_half
+        c = self.cfg
+        H, Hk, D = self.n_heads_local, self.n_kv_local, c.head_dim
+        if kv_layer.dtype == torch.uint8:
+            raise NotImplementedError("the 8-bit KV cache is not available for the gated-attention blocks of hybrid models")
+        qw = 2 if c.attn_gate else 1
+        qg = qkv[:, :H * D * qw].view(T, H, qw, D)
+        q = qg[:, :, 0].float()
+        gate = qg[:, :, 1].reshape(T, H * D).float() if c.attn_gate else None
+        k = qkv[:, H * D * qw:H * D * qw + Hk * D].view(T, Hk, D).float()
+        v = qkv[:, H * D * qw + Hk * D:H * D * qw + 2 * Hk * D].view(T, Hk, D)
+        if L.q_norm is not None:
+            q, k = rmsnorm(q, L.q_norm, c.rms_eps), rmsnorm(k, L.k_norm, c.rms_eps)
+        pos = fb.positions.long()
+        q = rope_split_half(q, pos, c.rope_theta, c.rotary_dim)
+        k = rope_split_half(k, pos, c.rope_theta, c.rotary_dim)
+        page = fb.block_table.long()[fb.seq_ids.long(), pos // 64]
+        off = pos % 64
+        kv_layer[page, 0, :, off] = k.to(kv_layer.dtype)
+        kv_layer[page, 1, :, off] = v.to(kv_layer.dtype)
+        o = self.ws_o[:T]
+        o3 = o.view(T, H, D)
+        scale = 1.0 / math.sqrt(D)
+        if self.torch_attention:
+            o3.copy_(self._attention_torch(q, fb, kv_layer, scale))
+        else:
+            qb = self.ws_q[:T]
+            qb.copy_(q)
+            if fb.is_decode:
+                ops.attn_decode(qb, kv_layer, o3, fb.block_table, fb.seq_lens, H, Hk, D, fb.rows_per_seq, scale, fb.n_splits, self.scratch)
+            else:
+                ops.attn_prefill(qb, kv_layer, o3, fb.block_table, fb.cu_q, fb.ctx_lens, H, Hk, D, scale, fb.max_q_len, scratch=self.scratch)
+        if gate is not None:
+            o.copy_(o.float() * torch.sigmoid(gate))
+        return o
+
+    def _attention_torch(self, q: torch.Tensor, fb: ForwardBatch, kv_layer: torch.Tensor, scale: float) -> torch.Tensor:
+        """Causal GQA attention over the paged cache on PyTorch ops, one sequence at a time (any head size)."""
+        H, Hk, D = self.n_heads_local, self.n_kv_local, self.cfg.head_dim
+        pos, sid = fb.positions.long(), fb.seq_ids.long()
+        out = torch.empty(q.shape[0], H, D, dtype=torch.float32, device=q.device)
+        g = H // Hk
+        for b in sid.unique().tolist():
+            rows = (sid == b).nonzero(as_tuple=True)[0]
+            last = int(pos[rows].max())
+            n_pages = last // 64 + 1
+            pages = fb.block_table.long()[b, :n_pages]
+            K = kv_layer[pages, 0].permute(1, 0, 2, 3).reshape(Hk, n_pages * 64, D)[:, :last + 1].float().repeat_interleave(g, 0)
+            V = kv_layer[pages, 1].permute(1, 0, 2, 3).reshape(Hk, n_pages * 64, D)[:, :last + 1].float().repeat_interleave(g, 0)
+            s = torch.einsum("thd,hsd->hts", q[rows], K) * scale
+            mask = torch.arange(last + 1, device=q.device)[None, :] > pos[rows][:, None]
+            out[rows] = torch.einsum("hts,hsd->thd", torch.softmax(s.masked_fill(mask[None], float("-inf")), -1), V)
+        return out
 
     def _kv_for_prefill(self, fb: ForwardBatch, kv_layer: torch.Tensor):
         """The prefill kernels read bf16 pages.  With the 8-bit cache the pages of the chunk's sequences (context and the rows
@@ -416,14 +545,19 @@ class CudaModel:
         c, sc = self.cfg, self.scratch
         h = self.ws_h[:T]
         small = T <= ops.GEMV_MAX_ROWS
-        qkv = self.ws_qkv[:T]
+        qkv = self.ws_qkv[:T, :L.qkv.n_out]
         if small:
             L.qkv(h, qkv, norm_w=L.attn_norm, eps=c.rms_eps, scratch=sc)
         else:
             xn = self.ws_xn[:T]
             ops.rmsnorm(h, L.attn_norm, xn, c.rms_eps)
             L.qkv(xn, qkv, scratch=sc, xn=xn)
-        o = self._attention(L, fb, kv_layer, T)
+        if getattr(L, "is_gdn", False):
+            o = self._linear_attention(L, fb, qkv, T)
+        elif c.attn_gate or c.rotary_dim != c.head_dim or self.torch_attention:
+            o = self._attention_gated(L, fb, kv_layer, qkv, T)
+        else:
+            o = self._attention(L, fb, kv_layer, T)
         self._row_parallel_resid(L.wo, o, h)
         if c.is_moe:
             self._moe(L, h, T)
@@ -496,7 +630,7 @@ class CudaModel:
         no consumer of the full hidden state (the engine turns ``seq_shard`` off when a NextN head needs all rows)."""
         tp = self.tp
         if (tp is None or tp.size == 1 or not tp.fused or not getattr(self, "seq_shard", True) or fb.is_decode or fb.embeds is not None
-                or self.cfg.is_moe or getattr(self, "taps", None) is not None or T < self.SEQ_SHARD_MIN_ROWS * tp.size
+                or self.cfg.is_moe or self.cfg.is_hybrid or getattr(self, "taps", None) is not None or T < self.SEQ_SHARD_MIN_ROWS * tp.size
                 or self.cfg.d_model % 128 or self.cfg.d_model > 8192 or not isinstance(self.embed, PackedWeight)):
             return None
         if getattr(self, "_ss_ok", None) is None:
@@ -578,8 +712,9 @@ class CudaModel:
             h.copy_(fb.embeds)
         else:
             self.embed_tokens(fb.tokens, h)
+        self._kv = kv
         for li, L in enumerate(self.layers):
-            self._layer(L, fb, kv.layers[kv_layer_offset + li], T)
+            self._layer(L, fb, kv.layers[kv_layer_offset + L.kv_index] if L.kv_index is not None else None, T)
             if debug is not None:
                 debug(self.layer_ids[li], h)
             if getattr(self, "taps", None) is not None:       # per-layer hidden states for the parity report

@@ -18,7 +18,7 @@ import torch
 from ..models.config import ModelConfig
 from ..models.weights import ModelWeights
 from .cuda_model import ForwardBatch
-from .kv_cache import PAGE_SIZE, OutOfPages, PagedKVCache, SequenceKV
+from .kv_cache import HybridState, PAGE_SIZE, OutOfPages, PagedKVCache, SequenceKV
 from .kv_cache import Q8 as KV_Q8
 from .sampling import SamplingParams, apply_penalties, sample_row
 from ..utils.env import debug_env
@@ -46,6 +46,7 @@ class Request:
     terminal: object = None                               # prefix-cache terminal state: the forward pass is skipped
     logprobs: list = field(default_factory=list)          # one (token, logprob, [(token, logprob), ...]) per output token
     n_folded: int = 0                                     # leading output tokens that a preemption appended to `prompt`
+    slot: int = -1                                        # hybrid models: state slot held from admission to the end
 
     @property
     def all_tokens(self) -> list[int]:
@@ -91,6 +92,18 @@ class LLMEngine:
         if kv_dtype == KV_Q8 and not self.is_cuda:
             raise ValueError("the 8-bit KV cache is a CUDA feature (the CPU back end takes bf16 / fp16 / fp32)")
         self.max_pages_per_seq = (max_context + PAGE_SIZE - 1) // PAGE_SIZE + 1
+        # hybrid models: one state slot per lane for the linear-attention layers, allocated before the KV cache is sized so
+        # that the page count is taken from what is left
+        hybrid = None
+        hd = getattr(self.model, "hybrid_dims", None)
+        if hd:
+            if prefix_cache is not None:
+                raise ValueError("--prefix-cache is not available for hybrid (linear-attention) models: a cached prefix would "
+                                 "need the recurrent state at its end, which this build does not store")
+            if mtp is not None:
+                raise ValueError("--mtp is not available for hybrid (linear-attention) models: a rejected draft would need "
+                                 "the recurrent state rolled back, which this build does not do")
+            hybrid = HybridState(n_slots=max(1, max_batch), device=self.device, **hd)
         n_kv_layers = getattr(self.model, "n_kv_layers", c.n_layers + c.nextn_layers)
         if kv_pages is None:
             need = max_batch * self.max_pages_per_seq + 64
@@ -107,7 +120,8 @@ class LLMEngine:
         kv_pages = self._agree_kv_pages(kv_pages, self._agree_group)
         self.kv = PagedKVCache(n_kv_layers, self.model.n_kv_local, c.head_dim, kv_pages, self.device,
                                dtype=(KV_Q8 if kv_dtype == KV_Q8 else torch.bfloat16) if self.is_cuda else (kv_dtype or torch.float32))
-        self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs
+        self.kv.hybrid = hybrid
+        self.use_graphs = use_graphs and self.is_cuda and not debug_env().no_cuda_graphs and getattr(self.model, "graph_safe", True)
         self.perf = perf_stats()
         self._graphs: dict = {}
         self.launches_per_graph: dict = {}      # kernels of this package inside each captured decode graph
@@ -170,7 +184,7 @@ class LLMEngine:
         bmax = next(b for b in BUCKETS if b >= B) if B <= BUCKETS[-1] else B
         self._bmax = bmax
         R = 4                                   # up to 4 rows per sequence (speculative verify)
-        n_int = bmax * R * 2 + bmax + bmax * P + bmax * 3
+        n_int = bmax * R * 2 + bmax + bmax * P + bmax * 3 * R + bmax
         self._dec_host = torch.zeros(n_int, dtype=torch.int32).pin_memory()
         self._dec_dev = torch.zeros(n_int, dtype=torch.int32, device=self.device)
         self._fl_host = torch.zeros(bmax * R * 2, dtype=torch.float32).pin_memory()
@@ -212,7 +226,9 @@ class LLMEngine:
             return s
         s_tok, s_pos, s_len, s_bt = take(T), take(T), take(bucket), take(bucket * P)
         s_topk, s_step, s_sid = take(T), take(T), take(T)
-        return {"tok": s_tok, "pos": s_pos, "len": s_len, "bt": s_bt, "topk": s_topk, "step": s_step, "sid": s_sid, "n": o}
+        s_slot = take(bucket)                           # hybrid models: state slot per lane
+        return {"tok": s_tok, "pos": s_pos, "len": s_len, "bt": s_bt, "topk": s_topk, "step": s_step, "sid": s_sid,
+                "slot": s_slot, "n": o}
 
     # -- public API ---------------------------------------------------------------------------------
     def add_request(self, prompt: list[int], params: SamplingParams | None = None) -> Request:
@@ -375,6 +391,8 @@ class LLMEngine:
                         return [StepOutput(r.rid, [], True, "cache_full", [] if r.params.wants_logprobs else None)]
                     break
                 self.waiting.pop(0)
+                if self.kv.hybrid is not None:
+                    r.slot = self.kv.hybrid.alloc()            # at most max_batch sequences are admitted: a slot is free
                 batch.append(r)
                 budget -= cost
             if batch:
@@ -454,6 +472,11 @@ class LLMEngine:
                 raise
             self.kv.ensure_capacity(r.kv, n_tokens)
 
+    def _release_slot(self, r: Request) -> None:
+        if r.slot >= 0:
+            self.kv.hybrid.release(r.slot)
+            r.slot = -1
+
     def _finish(self, r: Request, reason: str) -> None:
         if r.state == "finished":
             return
@@ -463,6 +486,7 @@ class LLMEngine:
         if r in self.running:
             self.running.remove(r)
         self.kv.free_sequence(r.kv)
+        self._release_slot(r)
         if self.prefix_cache is not None:
             self.prefix_cache.trim()                  # pages the request pinned can now leave the device tier
         if self.mtp is not None:
@@ -644,7 +668,8 @@ class LLMEngine:
             fb = ForwardBatch(tokens=it(toks), positions=it(pos), seq_ids=it(sid), block_table=bt.to(dev), cu_q=it(cu),
                               ctx_lens=it(ctx), max_q_len=max(cu[i + 1] - cu[i] for i in range(len(ctx))),
                               max_kv_len=max(ctx[i] + cu[i + 1] - cu[i] for i in range(len(ctx))),
-                              logit_rows=it(logit_rows) if logit_rows else None)
+                              logit_rows=it(logit_rows) if logit_rows else None,
+                              state_slots=it([r.slot for r, _, _ in chunks]) if self.kv.hybrid is not None else None)
             logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
             if self.mtp is not None:
                 keep = {r.rid: h[row].clone() for r, row in rows_for if row is not None}
@@ -727,6 +752,7 @@ class LLMEngine:
         if self.prefix_cache is not None:
             self.prefix_cache.insert(self, r)          # its full pages stay reusable until someone needs the space
         self.kv.free_sequence(r.kv)
+        self._release_slot(r)                          # the next prefill starts from position 0 and so from a zero state
         if self.mtp is not None:
             self.mtp.release(r)
         r.kv = SequenceKV()
@@ -747,7 +773,8 @@ class LLMEngine:
             bt[i, :len(r.kv.pages)] = torch.tensor(r.kv.pages, dtype=torch.int32)
         return ForwardBatch(tokens=it([r.output[-1] for r in reqs]), positions=it([r.n_tokens - 1 for r in reqs]),
                             seq_ids=it(list(range(B))), block_table=bt.to(dev), seq_lens=it([r.n_tokens for r in reqs]),
-                            rows_per_seq=1, n_splits=self._splits_for(B))
+                            rows_per_seq=1, n_splits=self._splits_for(B),
+                            state_slots=it([r.slot for r in reqs]) if self.kv.hybrid is not None else None)
 
     def _splits_for(self, bucket: int) -> int:
         if not self.is_cuda:
@@ -788,6 +815,10 @@ class LLMEngine:
         pos[:B] = n_tok - 1
         ln[:B] = n_tok
         h[v["step"]][:B] = np.fromiter((len(r.output) for r in reqs), dtype=np.int32, count=B)
+        if self.kv.hybrid is not None:                  # padded lanes work on the scratch slot
+            sl = h[v["slot"]]
+            sl[:B] = np.fromiter((r.slot for r in reqs), dtype=np.int32, count=B)
+            sl[B:bucket] = self.kv.hybrid.scratch_slot
         sig = (bucket, tuple(r.rid for r in reqs))
         if sig != self._lane_sig:
             self._lane_sig = sig
@@ -886,7 +917,8 @@ class LLMEngine:
         P = self.max_pages_per_seq
         fb = ForwardBatch(tokens=d[v["tok"]], positions=d[v["pos"]], seq_ids=d[v["sid"]],
                           block_table=d[v["bt"]].view(bucket, P), seq_lens=d[v["len"]], rows_per_seq=1,
-                          n_splits=self._splits_for(bucket))
+                          n_splits=self._splits_for(bucket),
+                          state_slots=d[v["slot"]] if self.kv.hybrid is not None else None)
         logits, _ = self.model.forward(fb, self.kv, logits_out=self._logits[:bucket])
         tok = self._tok_dev[:bucket]
         if pen:
@@ -909,6 +941,10 @@ class LLMEngine:
 
     def _capture_decode(self, bucket: int, greedy: bool, v: dict, pen: bool = False):
         torch.cuda.synchronize(self.device)
+        if self.kv.hybrid is not None:
+            # the warm-up runs are real steps, and a recurrent state (unlike a K/V row) is not the same after being advanced
+            # twice with one token: they work on the scratch slot, the lanes' own slots come back with the staged inputs
+            self._dec_dev[v["slot"]].fill_(self.kv.hybrid.scratch_slot)
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
@@ -924,4 +960,6 @@ class LLMEngine:
         with torch.cuda.graph(g):
             self._decode_body(bucket, greedy, v, pen)
         self.launches_per_graph[(bucket, greedy, pen) if pen else (bucket, greedy)] = ops.launch_count() - n0
+        if self.kv.hybrid is not None:
+            self._dec_dev[:v["n"]].copy_(self._dec_host[:v["n"]], non_blocking=True)
         return g

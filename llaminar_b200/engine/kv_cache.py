@@ -60,6 +60,32 @@ class SequenceKV:
         return len(self.pages) * PAGE_SIZE
 
 
+class HybridState:
+    """Per-sequence state of the linear-attention layers of a hybrid model: for every such layer and every state slot the
+    last K-1 inputs of the short convolution and one d x d matrix per value head (fp32).  A running sequence owns one slot
+    from admission to its end; slot ``n_slots`` is scratch for the padded lanes of a captured decode step.  (The
+    reference keeps these beside its ring KV cache: src/v2/kernels/cuda/kvcache/CUDAHybridRingKVCache.h.)"""
+
+    def __init__(self, n_layers: int, n_slots: int, conv_dim: int, conv_kernel: int, n_v_heads: int, d: int, device):
+        self.n_slots, self.scratch_slot = n_slots, n_slots
+        self.conv = torch.zeros(n_layers, n_slots + 1, conv_dim, conv_kernel - 1, dtype=torch.float32, device=device)
+        self.rec = torch.zeros(n_layers, n_slots + 1, n_v_heads, d, d, dtype=torch.float32, device=device)
+        self.free = list(range(n_slots - 1, -1, -1))
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise OutOfPages("no free state slot")
+        return self.free.pop()
+
+    def release(self, slot: int) -> None:
+        assert 0 <= slot < self.n_slots and slot not in self.free
+        self.free.append(slot)
+
+    @staticmethod
+    def bytes_per_slot(n_layers: int, conv_dim: int, conv_kernel: int, n_v_heads: int, d: int) -> int:
+        return 4 * n_layers * (conv_dim * (conv_kernel - 1) + n_v_heads * d * d)
+
+
 Q8 = "q8_0"          # 8-bit cache: int8 values with one fp16 scale per 32 (CUDA back end; reference: CUDARingKVCache.cu:405)
 
 
@@ -80,6 +106,7 @@ class PagedKVCache:
             self.layers = [torch.zeros(n_pages, 2, n_kv_heads, PAGE_SIZE, head_dim, dtype=dtype, device=device)
                            for _ in range(n_layers)]
         self.allocator = PageAllocator(n_pages)
+        self.hybrid: HybridState | None = None          # set by the engine for models with linear-attention layers
 
     @staticmethod
     def bytes_per_page(n_layers: int, n_kv_heads: int, head_dim: int, itemsize: float = 2) -> int:

@@ -12,6 +12,7 @@ import math
 import torch
 import torch.nn.functional as F
 
+from ..models import gdn
 from ..models.config import ModelConfig
 from ..models.reference import moe_route, rmsnorm, rope_split_half
 from ..models.weights import ModelWeights
@@ -41,11 +42,40 @@ class TorchPagedModel:
             self.head = head.rows(pl.vocab_start, pl.vocab_stop).to_float().to(self.device)
             self.vocab_local = pl.vocab_stop - pl.vocab_start
 
-        def layer(i):
+        kv_ids, gdn_ids = c.kv_layers(self.layer_ids), c.gdn_layers(self.layer_ids)
+
+        def ffn(L, p):
+            L["wg"] = f(p + "ffn_gate.weight")[pl.ff_start:pl.ff_stop]
+            L["wu"] = f(p + "ffn_up.weight")[pl.ff_start:pl.ff_stop]
+            L["wd"] = f(p + "ffn_down.weight")[:, pl.ff_start:pl.ff_stop]
+
+        def gdn_layer(i):
+            """Linear-attention block: all key heads (q and k rows) plus this rank's value heads."""
             p = f"blk.{i}."
-            L = {"attn_norm": f(p + "attn_norm.weight"), "ffn_norm": f(p + "ffn_norm.weight"), "index": i}
+            L = {"attn_norm": f(p + "attn_norm.weight"), "ffn_norm": f(p + c.ffn_norm_name), "index": i,
+                 "gdn_index": gdn_ids.index(i)}
+            d, kd = c.ssm_state, c.gdn_key_dim
+            v0, v1 = pl.gdn_v_start, pl.gdn_v_stop
+            rows = torch.cat([torch.arange(2 * kd), 2 * kd + torch.arange(v0 * d, v1 * d)])
+            L["wqkv"] = f(p + "attn_qkv.weight")[rows]
+            L["conv_w"] = f(p + "ssm_conv1d.weight")[rows]
+            L["wz"] = f(p + "attn_gate.weight")[v0 * d:v1 * d]
+            L["walpha"], L["wbeta"] = f(p + "ssm_alpha.weight")[v0:v1], f(p + "ssm_beta.weight")[v0:v1]
+            L["ssm_a"], L["dt_bias"] = f(p + "ssm_a")[v0:v1], f(p + "ssm_dt.bias")[v0:v1]
+            L["ssm_norm"] = f(p + "ssm_norm.weight")
+            L["wout"] = f(p + "ssm_out.weight")[:, v0 * d:v1 * d]
+            ffn(L, p)
+            return L
+
+        def layer(i):
+            if c.is_gdn_layer(i):
+                return gdn_layer(i)
+            p = f"blk.{i}."
+            L = {"attn_norm": f(p + "attn_norm.weight"), "ffn_norm": f(p + c.ffn_norm_name), "index": i,
+                 "kv_index": kv_ids.index(i) if i in kv_ids else None}
             qs, qe, ks, ke = pl.q_head_start * D, pl.q_head_stop * D, pl.kv_head_start * D, pl.kv_head_stop * D
-            L["wq"], L["wk"], L["wv"] = f(p + "attn_q.weight")[qs:qe], f(p + "attn_k.weight")[ks:ke], f(p + "attn_v.weight")[ks:ke]
+            qw = 2 if c.attn_gate else 1                       # rows of a head: [query | gate]
+            L["wq"], L["wk"], L["wv"] = f(p + "attn_q.weight")[qs * qw:qe * qw], f(p + "attn_k.weight")[ks:ke], f(p + "attn_v.weight")[ks:ke]
             L["wo"] = f(p + "attn_output.weight")[:, qs:qe]
             if c.qkv_bias:
                 L["bq"], L["bk"], L["bv"] = f(p + "attn_q.bias")[qs:qe], f(p + "attn_k.bias")[ks:ke], f(p + "attn_v.bias")[ks:ke]
@@ -59,15 +89,19 @@ class TorchPagedModel:
                 L["wu"] = f(p + "ffn_up_exps.weight")[e0:e1]
                 L["wd"] = f(p + "ffn_down_exps.weight")[e0:e1]
             else:
-                L["wg"] = f(p + "ffn_gate.weight")[pl.ff_start:pl.ff_stop]
-                L["wu"] = f(p + "ffn_up.weight")[pl.ff_start:pl.ff_stop]
-                L["wd"] = f(p + "ffn_down.weight")[:, pl.ff_start:pl.ff_stop]
+                ffn(L, p)
             return L
 
         self.layers = [layer(i) for i in self.layer_ids]
         self.mtp_layers = []
-        self.mtp_kv_base = len(self.layer_ids)          # the NextN layers' K/V follow this stage's own layers in the cache
-        self.n_kv_layers = len(self.layer_ids) + (c.nextn_layers if with_mtp else 0)
+        self.mtp_kv_base = len(kv_ids)                  # the NextN layers' K/V follow this stage's own layers in the cache
+        self.n_kv_layers = len(kv_ids) + (c.nextn_layers if with_mtp else 0)
+        # what the engine needs to size the linear-attention state pools of this stage (None: no such layers)
+        self.hybrid_dims = None
+        if gdn_ids:
+            nv = pl.gdn_v_stop - pl.gdn_v_start
+            self.hybrid_dims = dict(n_layers=len(gdn_ids), conv_dim=2 * c.gdn_key_dim + nv * c.ssm_state,
+                                    conv_kernel=c.ssm_conv_kernel, n_v_heads=nv, d=c.ssm_state)
         for j in range(c.nextn_layers if with_mtp else 0):
             i = c.n_layers + j
             L = layer(i)
@@ -91,13 +125,17 @@ class TorchPagedModel:
         q, k, v = x @ L["wq"].T, x @ L["wk"].T, x @ L["wv"].T
         if c.qkv_bias:
             q, k, v = q + L["bq"], k + L["bk"], v + L["bv"]
-        q = q.view(T, self.n_heads_local, D)
+        gate = None
+        if c.attn_gate:
+            q, gate = q.view(T, self.n_heads_local, 2, D).unbind(dim=2)
+            gate = gate.reshape(T, -1)
+        q = q.reshape(T, self.n_heads_local, D)
         k = k.view(T, self.n_kv_local, D)
         v = v.view(T, self.n_kv_local, D)
         if c.qk_norm:
             q, k = rmsnorm(q, L["qn"], c.rms_eps), rmsnorm(k, L["kn"], c.rms_eps)
         pos = fb.positions.long()
-        q, k = rope_split_half(q, pos, c.rope_theta), rope_split_half(k, pos, c.rope_theta)
+        q, k = rope_split_half(q, pos, c.rope_theta, c.rotary_dim), rope_split_half(k, pos, c.rope_theta, c.rotary_dim)
         sid = fb.seq_ids.long()
         page = fb.block_table.long()[sid, pos // PAGE_SIZE]
         off = pos % PAGE_SIZE
@@ -118,7 +156,19 @@ class TorchPagedModel:
             mask = torch.arange(last + 1, device=x.device)[None, :] > pos[rows][:, None]
             s = s.masked_fill(mask[None], float("-inf"))
             out[rows] = torch.einsum("hts,hsd->thd", torch.softmax(s, -1), V)
-        return out.reshape(T, -1) @ L["wo"].T
+        out = out.reshape(T, -1)
+        if gate is not None:
+            out = out * torch.sigmoid(gate)
+        return out @ L["wo"].T
+
+    def _linear_attention(self, L, x, fb: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
+        c, hs, gi = self.cfg, kv.hybrid, L["gdn_index"]
+        seqs = gdn.batch_sequences(fb.seq_ids, fb.positions, fb.state_slots)
+        rows = gdn.gdn_block_rows(x @ L["wqkv"].T, x @ L["wz"].T, x @ L["walpha"].T, x @ L["wbeta"].T, seqs,
+                                  hs.conv[gi], hs.rec[gi], L["conv_w"], L["ssm_a"], L["dt_bias"], L["ssm_norm"],
+                                  c.ssm_k_heads, self.plan.gdn_v_stop - self.plan.gdn_v_start, c.ssm_state, c.rms_eps,
+                                  self.plan.gdn_v_start)
+        return rows @ L["wout"].T
 
     def _ffn(self, L, x: torch.Tensor) -> torch.Tensor:
         c = self.cfg
@@ -138,9 +188,10 @@ class TorchPagedModel:
             out.index_add_(0, tok, ye * wt[tok, slot].unsqueeze(-1))
         return out
 
-    def _layer(self, L, h, fb, kvl):
+    def _layer(self, L, h, fb, kvl, kv=None):
         c = self.cfg
-        h = h + self._sum_ranks(self._attention(L, rmsnorm(h, L["attn_norm"], c.rms_eps), fb, kvl))
+        x = rmsnorm(h, L["attn_norm"], c.rms_eps)
+        h = h + self._sum_ranks(self._linear_attention(L, x, fb, kv) if "gdn_index" in L else self._attention(L, x, fb, kvl))
         y = self._ffn(L, rmsnorm(h, L["ffn_norm"], c.rms_eps))
         if not (c.is_moe and getattr(self.tp, "moe_mode", "expert-parallel") == "replicated"):
             y = self._sum_ranks(y)               # replicated experts: every rank already has the full sum
@@ -157,7 +208,8 @@ class TorchPagedModel:
     def forward(self, fb: ForwardBatch, kv: PagedKVCache, logits_out=None, want_logits=True, kv_layer_offset: int = 0):
         h = fb.embeds.float() if fb.embeds is not None else self.embed[fb.tokens.long()].float()
         for li, L in enumerate(self.layers):
-            h = self._layer(L, h, fb, kv.layers[kv_layer_offset + li])
+            kvl = kv.layers[kv_layer_offset + L["kv_index"]] if L.get("kv_index") is not None else None
+            h = self._layer(L, h, fb, kvl, kv)
             if getattr(self, "taps", None) is not None:       # per-layer hidden states for the parity report
                 self.taps[f"layer{li}"] = h.float().clone()
         logits = None

@@ -109,6 +109,34 @@ def gdn_mix(qkv: torch.Tensor, z: torch.Tensor, alpha: torch.Tensor, b: torch.Te
     q = expand_key_heads(l2norm(q.view(T, n_k, d)) * d ** -0.5, n_v, v_head_offset)
     k = expand_key_heads(l2norm(k.view(T, n_k, d)), n_v, v_head_offset)
     g, beta = gates(alpha, b, ssm_a, dt_bias)
-    run = delta_rule_recurrent if T <= 4 else delta_rule_chunked
-    o = run(q, k, v.view(T, n_v, d), g, beta, S) if T <= 4 else run(q, k, v.view(T, n_v, d), g, beta, S, chunk)
+    if T <= 4:
+        o = delta_rule_recurrent(q, k, v.view(T, n_v, d), g, beta, S)
+    else:
+        o = delta_rule_chunked(q, k, v.view(T, n_v, d), g, beta, S, chunk)
     return gated_rmsnorm(o, z.view(T, n_v, d), norm_w, eps).reshape(T, n_v * d), conv_state
+
+
+def gdn_block_rows(qkv, z, alpha, b, seqs, conv_pool, rec_pool, conv_w, ssm_a, dt_bias, norm_w, n_k: int, n_v: int, d: int,
+                   eps: float, v_head_offset: int = 0) -> torch.Tensor:
+    """The linear-attention mix for a packed batch.  ``seqs``: (first row, end row, state slot, fresh) per sequence, rows of
+    a sequence being consecutive; ``fresh`` sequences start from a zero state.  conv_pool [slots, C, K-1] and
+    rec_pool [slots, n_v, d, d] are one layer's state pools and are updated.  Returns fp32 rows [T, n_v d]."""
+    out = torch.empty(qkv.shape[0], n_v * d, dtype=torch.float32, device=qkv.device)
+    for r0, r1, slot, fresh in seqs:
+        if fresh:
+            conv_pool[slot].zero_()
+            rec_pool[slot].zero_()
+        out[r0:r1], conv_pool[slot] = gdn_mix(qkv[r0:r1], z[r0:r1], alpha[r0:r1], b[r0:r1], conv_w, ssm_a, dt_bias, norm_w,
+                                             conv_pool[slot], rec_pool[slot], n_k, n_v, d, eps, v_head_offset)
+    return out
+
+
+def batch_sequences(seq_ids, positions, state_slots) -> list[tuple[int, int, int, bool]]:
+    """(first row, end row, slot, fresh) of every sequence of a packed batch (host lists; one synchronisation on a GPU)."""
+    sid, pos, slots = seq_ids.tolist(), positions.tolist(), state_slots.tolist()
+    out, r0 = [], 0
+    for r in range(1, len(sid) + 1):
+        if r == len(sid) or sid[r] != sid[r0]:
+            out.append((r0, r, slots[sid[r0]], pos[r0] == 0))
+            r0 = r
+    return out

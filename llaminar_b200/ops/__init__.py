@@ -272,6 +272,18 @@ def kv_dequant_pages(kv8: torch.Tensor, block_table: torch.Tensor, n_tokens: tor
     _count()
 
 
+def gdn_step(inp: torch.Tensor, C: int, z_off: int, ab_off: int, conv_w: torch.Tensor, ssm_a: torch.Tensor, dt_bias: torch.Tensor,
+             norm_w: torch.Tensor, conv_state: torch.Tensor, rec: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
+             out: torch.Tensor, n_k: int, v_head_offset: int, eps: float) -> None:
+    """One new token per row of a Gated-DeltaNet block, between its input and output projections (two launches).
+    ``inp`` [rows, >= C + ...] bf16 is the input projection's output: q | k | v in columns [0, C), the gate z from
+    ``z_off``, (alpha | b) from ``ab_off``.  conv_state [slots, C, K-1] and rec [slots, n_v, d, d] are the layer's fp32 state
+    pools, ``slots`` [rows] int32 picks each row's slot; y [rows, C] fp32 is scratch; out [rows, n_v * d] bf16."""
+    ext().gdn_conv_step(inp, conv_w, conv_state, slots, y)
+    ext().gdn_recurrent_step(y, inp, z_off, ab_off, ssm_a, dt_bias, norm_w, rec, slots, out, n_k, v_head_offset, eps)
+    _count(2)
+
+
 ATTN_TC_MIN_ROWS = 1536
 _ATTN_TC = None
 

@@ -15,7 +15,7 @@ from pathlib import Path
 NAME = "llaminar_b200_ops"
 CSRC = Path(__file__).resolve().parent / "csrc"
 BUILD_DIR = Path(__file__).resolve().parent / "_build"
-SOURCES = ["binding.cpp", "gemv.cu", "gemv_stream.cu", "gemm_tc.cu", "gemm_tc_small.cu", "attention.cu", "attention_tc.cu", "ops.cu", "moe_ep.cu", "no_alloc.cu"]
+SOURCES = ["binding.cpp", "gemv.cu", "gemv_stream.cu", "gemm_tc.cu", "gemm_tc_small.cu", "attention.cu", "attention_tc.cu", "ops.cu", "gdn.cu", "moe_ep.cu", "no_alloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

@@ -272,6 +272,48 @@ static void kv_dequant_pages(const Tensor& kv8, const Tensor& block_table, const
                                                 static_cast<__nv_bfloat16*>(staging.data_ptr()), cur_stream()));
 }
 
+// Linear-attention decode step, first launch: y = SiLU(conv(window | in[:, :C])), windows shifted (gdn.cu)
+static void gdn_conv_step(const Tensor& in, const Tensor& conv_w, Tensor conv_state, const Tensor& slots, Tensor y) {
+    check_cuda(in, "in"); check_cuda(conv_state, "conv_state");
+    const c10::cuda::CUDAGuard guard(in.device());
+    const int rows = (int)in.size(0), C = (int)conv_w.size(0), K = (int)conv_w.size(1);
+    TORCH_CHECK(in.scalar_type() == torch::kBFloat16 && in.dim() == 2 && in.stride(1) == 1 && in.size(1) >= C);
+    TORCH_CHECK(conv_w.scalar_type() == torch::kFloat32 && conv_w.is_contiguous());
+    TORCH_CHECK(conv_state.scalar_type() == torch::kFloat32 && conv_state.is_contiguous() && conv_state.dim() == 3 &&
+                conv_state.size(1) == C && conv_state.size(2) == K - 1);
+    TORCH_CHECK(slots.scalar_type() == torch::kInt32 && slots.numel() >= rows);
+    TORCH_CHECK(y.scalar_type() == torch::kFloat32 && y.is_contiguous() && y.size(0) >= rows && y.size(1) == C);
+    LLM_CUDA_CHECK(llm::launch_gdn_conv_step(static_cast<const __nv_bfloat16*>(in.data_ptr()), (int)in.stride(0),
+                                             static_cast<const float*>(conv_w.data_ptr()), static_cast<float*>(conv_state.data_ptr()),
+                                             static_cast<const int*>(slots.data_ptr()), static_cast<float*>(y.data_ptr()), rows, C, K, cur_stream()));
+}
+
+// ... second launch: delta rule on every (row, value head) + gated RMSNorm -> out[rows, n_v * d] bf16
+static void gdn_recurrent_step(const Tensor& y, const Tensor& in, int64_t z_off, int64_t ab_off, const Tensor& ssm_a, const Tensor& dt_bias,
+                               const Tensor& norm_w, Tensor rec, const Tensor& slots, Tensor out, int64_t n_k, int64_t v_head_offset,
+                               double eps) {
+    check_cuda(y, "y"); check_cuda(rec, "rec");
+    const c10::cuda::CUDAGuard guard(y.device());
+    const int rows = (int)in.size(0), n_v = (int)rec.size(1), d = (int)rec.size(2);
+    TORCH_CHECK(rec.scalar_type() == torch::kFloat32 && rec.is_contiguous() && rec.dim() == 4 && rec.size(3) == d);
+    TORCH_CHECK(y.scalar_type() == torch::kFloat32 && y.is_contiguous() && y.size(0) >= rows && y.size(1) == 2 * n_k * d + n_v * d);
+    TORCH_CHECK(in.scalar_type() == torch::kBFloat16 && in.dim() == 2 && in.stride(1) == 1);
+    TORCH_CHECK(z_off + n_v * d <= in.size(1) && ab_off + 2 * n_v <= in.size(1));
+    TORCH_CHECK(ssm_a.scalar_type() == torch::kFloat32 && ssm_a.numel() == n_v && dt_bias.scalar_type() == torch::kFloat32 && dt_bias.numel() == n_v);
+    TORCH_CHECK(norm_w.scalar_type() == torch::kFloat32 && norm_w.numel() == d);
+    TORCH_CHECK(slots.scalar_type() == torch::kInt32 && slots.numel() >= rows);
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.dim() == 2 && out.stride(1) == 1 && out.size(0) >= rows && out.size(1) >= n_v * d);
+    llm::GdnStepParams p{};
+    p.y = static_cast<const float*>(y.data_ptr()); p.C = (int)y.size(1);
+    p.in = static_cast<const __nv_bfloat16*>(in.data_ptr()); p.in_stride = (int)in.stride(0); p.z_off = (int)z_off; p.ab_off = (int)ab_off;
+    p.ssm_a = static_cast<const float*>(ssm_a.data_ptr()); p.dt_bias = static_cast<const float*>(dt_bias.data_ptr());
+    p.norm_w = static_cast<const float*>(norm_w.data_ptr());
+    p.rec = static_cast<float*>(rec.data_ptr()); p.slots = static_cast<const int*>(slots.data_ptr());
+    p.out = static_cast<__nv_bfloat16*>(out.data_ptr()); p.out_stride = (int)out.stride(0);
+    p.n_k = (int)n_k; p.n_v = n_v; p.v_head_offset = (int)v_head_offset; p.eps = (float)eps;
+    LLM_CUDA_CHECK(llm::launch_gdn_recurrent_step(p, rows, d, cur_stream()));
+}
+
 static void attn_decode(const Tensor& q, const Tensor& kv, Tensor out, const Tensor& block_table, const Tensor& seq_lens,
                         const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& tickets, int64_t n_heads,
                         int64_t n_kv_heads, int64_t head_dim, int64_t rows_per_seq, double scale, int64_t n_splits) {
@@ -566,6 +608,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
     m.def("gemv", &gemv);
     m.def("kv_dequant_pages", &kv_dequant_pages);
+    m.def("gdn_conv_step", &gdn_conv_step);
+    m.def("gdn_recurrent_step", &gdn_recurrent_step);
     m.def("moe_route", &moe_route);
     m.def("moe_gemv", &moe_gemv);
     m.def("moe_route_only", &moe_route_only);

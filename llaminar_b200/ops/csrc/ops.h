@@ -60,6 +60,24 @@ struct RopeKVParams {
 // 8-bit cache -> bf16 pages for the prefill kernels: page j of sequence s (j < pages_of[s]) goes to staging page s * max_pages + j
 cudaError_t launch_kv_dequant_pages(const uint8_t* kv8, size_t page_bytes, size_t scale_off, const int* block_table, const int* n_tokens,
                                     int n_seqs, int max_pages, int n_kv_heads, int head_dim, int n_pages, __nv_bfloat16* staging, cudaStream_t st);
+// Gated-DeltaNet decode step (gdn.cu).  `in` is the row-major output of the block's input projection: columns [0, C) hold
+// q | k | v, z_off / ab_off give the first column of the gate z and of the (alpha | b) pair; y = conv + SiLU of the q | k | v part.
+struct GdnStepParams {
+    const float* y;                 // [rows, C] fp32
+    int C;
+    const __nv_bfloat16* in;        // [rows, in_stride]
+    int in_stride, z_off, ab_off;
+    const float *ssm_a, *dt_bias, *norm_w;
+    float* rec;                     // [slots, n_v, d, d]
+    const int* slots;               // [rows]
+    __nv_bfloat16* out;             // [rows, out_stride]
+    int out_stride;
+    int n_k, n_v, v_head_offset;
+    float eps;
+};
+cudaError_t launch_gdn_conv_step(const __nv_bfloat16* in, int in_stride, const float* w, float* conv_state, const int* slots, float* y,
+                                 int rows, int C, int K, cudaStream_t st);
+cudaError_t launch_gdn_recurrent_step(const GdnStepParams& p, int rows, int d, cudaStream_t st);
 // status word of the bounds-check build, per translation unit (0 in the production build)
 int bounds_status_ops(bool reset);
 int bounds_status_attention(bool reset);

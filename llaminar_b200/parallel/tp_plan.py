@@ -36,6 +36,11 @@ class TPPlan:
     vocab_stop: int
     expert_start: int
     expert_stop: int
+    # linear-attention value heads of a hybrid model (key heads stay replicated: value head j reads key head j mod n_k, and
+    # the q / k work is a small share of the block; reference: the head mapping comment in
+    # src/v2/models/qwen35/Qwen35Graph.cpp:888-900)
+    gdn_v_start: int = 0
+    gdn_v_stop: int = 0
 
     @property
     def n_heads_local(self) -> int:
@@ -63,6 +68,8 @@ class TPPlan:
             errs.append(f"d_ff={cfg.d_ff} has fewer than tp={tp} blocks of {FF_UNIT} columns")
         if cfg.is_moe and cfg.n_experts < tp:
             errs.append(f"n_experts={cfg.n_experts} < tp={tp}")
+        if getattr(cfg, "is_hybrid", False) and cfg.ssm_v_heads % tp:
+            errs.append(f"ssm value heads={cfg.ssm_v_heads} are not divisible by tp={tp}")
         if (cfg.q_dim // tp) % 32 and tp > 1:
             errs.append(f"per-rank attention width {cfg.q_dim // tp} is not a multiple of 32 (smallest quantisation block)")
         return errs
@@ -99,7 +106,8 @@ class TPPlan:
             es, ee = 0, cfg.n_experts           # every rank holds and computes all experts: no exchange after the MoE block
         else:
             es, ee = _split(cfg.n_experts, tp, rank) if cfg.is_moe else (0, 0)
-        return TPPlan(tp, rank, qs, qe, ks, ke, rep, fs, fe, vs, ve, es, ee)
+        gs, ge = _split(cfg.ssm_v_heads, tp, rank) if getattr(cfg, "is_hybrid", False) else (0, 0)
+        return TPPlan(tp, rank, qs, qe, ks, ke, rep, fs, fe, vs, ve, es, ee, gs, ge)
 
     def describe(self) -> str:
         return (f"rank {self.rank}/{self.tp}: q heads [{self.q_head_start},{self.q_head_stop}) "

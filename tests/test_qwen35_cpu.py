@@ -142,3 +142,35 @@ def test_gguf_round_trip_keeps_the_hybrid_configuration(tmp_path):
         assert getattr(c0, f) == getattr(c1, f), f
     assert [c1.is_gdn_layer(i) for i in range(8)] == [True, True, True, False] * 2
     assert back["blk.0.ssm_conv1d.weight"].shape == (c0.gdn_conv_dim, 4)
+
+
+def _prompt(n, seed, vocab=1024):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def test_engine_on_the_hybrid_model_matches_the_oracle_with_batching_and_chunked_prefill():
+    """Continuous batching over state slots: three prompts of different lengths, prefill split into chunks (the recurrent
+    state carries from chunk to chunk), decode steps batched; every sequence must emit the oracle's greedy tokens."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    ref = ReferenceModel(w)
+    prompts = [_prompt(70, 1), _prompt(9, 2), _prompt(33, 3)]
+    want = [ref.generate_greedy(torch.tensor(p), 8)[0] for p in prompts]
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=256, max_prefill_tokens=48)
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert got == want
+    assert sorted(eng.kv.hybrid.free) == [0, 1]                       # every slot came back
+    assert eng.kv.allocator.n_free == eng.kv.n_pages - 1
+
+
+def test_hybrid_model_rejects_prefix_cache_and_speculation_by_name():
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.mtp import MTPDecoder
+    from llaminar_b200.engine.prefix_cache import PrefixCache
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    with pytest.raises(ValueError, match="prefix-cache"):
+        LLMEngine(w, device="cpu", max_batch=2, max_context=128, prefix_cache=PrefixCache())
+    with pytest.raises(ValueError, match="mtp"):
+        LLMEngine(w, device="cpu", max_batch=2, max_context=128, mtp=MTPDecoder())
