@@ -103,13 +103,16 @@ class LLMEngine:
             if mtp is not None:
                 raise ValueError("--mtp is not available for hybrid (linear-attention) models: a rejected draft would need "
                                  "the recurrent state rolled back, which this build does not do")
+            if kv_dtype == KV_Q8:
+                raise ValueError("the 8-bit KV cache is not available for hybrid (linear-attention) models: their gated "
+                                 "attention blocks append to a bf16 cache")
             hybrid = HybridState(n_slots=max(1, max_batch), device=self.device, **hd)
         n_kv_layers = getattr(self.model, "n_kv_layers", c.n_layers + c.nextn_layers)
         if kv_pages is None:
             need = max_batch * self.max_pages_per_seq + 64
             if self.is_cuda:
                 free, _ = torch.cuda.mem_get_info(self.device)
-                per_page = PagedKVCache.bytes_per_page(n_kv_layers, self.model.n_kv_local, c.head_dim, 17 / 16 if kv_dtype == KV_Q8 else 2)
+                per_page = max(1, PagedKVCache.bytes_per_page(n_kv_layers, self.model.n_kv_local, c.head_dim, 17 / 16 if kv_dtype == KV_Q8 else 2))
                 kv_pages = int(min(need * 2, max(need // 4, int(free * kv_memory_fraction) // per_page)))
             else:
                 kv_pages = need

@@ -50,6 +50,8 @@ class PipelineStageModel:
         self.cfg, self.device, self.tp = inner.cfg, inner.device, tp
         self.n_kv_local, self.n_heads_local = inner.n_kv_local, inner.n_heads_local
         self.n_kv_layers = inner.n_kv_layers
+        self.hybrid_dims = getattr(inner, "hybrid_dims", None)     # linear-attention state of this stage's layers (or None)
+        self.graph_safe = getattr(inner, "graph_safe", True)
         self.vocab_local = inner.cfg.vocab_size
         self.mtp_layers = [object()] * inner.cfg.nextn_layers        # only their count is read outside the last stage
         self.pp_group = pp_group                                       # ranks with this tensor-parallel index, one per stage

@@ -59,6 +59,11 @@ def compare(weights, device: str, prompt_tokens: int = 96, decode_steps: int = 4
     pages = (total + 63) // 64
     kv = PagedKVCache(getattr(model, "n_kv_layers", cfg.n_layers + cfg.nextn_layers), model.n_kv_local, cfg.head_dim, pages + 2, dev,
                       dtype=kv_dtype)
+    slots = None
+    if getattr(model, "hybrid_dims", None):                  # linear-attention layers: one state slot for the one sequence
+        from .engine.kv_cache import HybridState
+        kv.hybrid = HybridState(n_slots=1, device=dev, **model.hybrid_dims)
+        slots = torch.zeros(1, dtype=torch.int32, device=dev)
     g = torch.Generator().manual_seed(seed)
     prompt = torch.randint(0, cfg.vocab_size, (prompt_tokens,), generator=g)
     it = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)
@@ -86,12 +91,13 @@ def compare(weights, device: str, prompt_tokens: int = 96, decode_steps: int = 4
 
     n = prompt_tokens
     fb = ForwardBatch(tokens=it(prompt.tolist()), positions=it(list(range(n))), seq_ids=it([0] * n), block_table=bt,
-                      cu_q=it([0, n]), ctx_lens=it([0]), max_q_len=n)
+                      cu_q=it([0, n]), ctx_lens=it([0]), max_q_len=n, state_slots=slots)
     ref_logits, ref_kv = one_pass("prefill", prompt, fb, None)
     nxt = int(ref_logits[-1].argmax())
     for step in range(decode_steps):                     # teacher-forced with the oracle's greedy tokens
         pos = n + step
-        fb = ForwardBatch(tokens=it([nxt]), positions=it([pos]), seq_ids=it([0]), block_table=bt, seq_lens=it([pos + 1]))
+        fb = ForwardBatch(tokens=it([nxt]), positions=it([pos]), seq_ids=it([0]), block_table=bt, seq_lens=it([pos + 1]),
+                          state_slots=slots)
         ref_logits, ref_kv = one_pass(f"decode{step}", torch.tensor([nxt]), fb, ref_kv)
         nxt = int(ref_logits[-1].argmax())
     return rows, failed

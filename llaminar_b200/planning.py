@@ -100,8 +100,15 @@ class ExecutionPlan:
 def layer_weight_bytes(cfg: ModelConfig, recipe: QuantRecipe, layer: int, tp: TPPlan) -> float:
     d, D = cfg.d_model, cfg.head_dim
     t = lambda name: recipe.for_tensor(f"blk.{layer}.{name}.weight", layer, cfg.n_layers)
-    tot = _bytes(t("attn_q"), tp.n_heads_local * D * d) + 2 * _bytes(t("attn_k"), tp.n_kv_local * D * d)
-    tot += _bytes(t("attn_output"), d * tp.n_heads_local * D)
+    if cfg.is_gdn_layer(layer):
+        # linear-attention block: q | k of every key head, this rank's value heads of v and z, alpha / b, output projection
+        nv, ds = tp.gdn_v_stop - tp.gdn_v_start, cfg.ssm_state
+        tot = _bytes(t("attn_qkv"), (2 * cfg.gdn_key_dim + nv * ds) * d) + _bytes(t("attn_gate"), nv * ds * d)
+        tot += 2 * _bytes(t("ssm_alpha"), nv * d) + _bytes(t("ssm_out"), d * nv * ds)
+        tot += 4 * (2 * cfg.gdn_key_dim + nv * ds) * cfg.ssm_conv_kernel
+    else:
+        tot = _bytes(t("attn_q"), tp.n_heads_local * D * d * (2 if cfg.attn_gate else 1)) + 2 * _bytes(t("attn_k"), tp.n_kv_local * D * d)
+        tot += _bytes(t("attn_output"), d * tp.n_heads_local * D)
     if cfg.is_moe:
         n_e = tp.expert_stop - tp.expert_start
         tot += n_e * (2 * _bytes(t("ffn_gate_exps"), cfg.expert_ff * d, True) + _bytes(t("ffn_down_exps"), cfg.expert_ff * d, True))
@@ -143,7 +150,14 @@ def build_plan(cfg: ModelConfig, layout: dict, recipe: QuantRecipe | str = "Q4_K
                 w += _bytes(recipe.for_tensor("output.weight"), (tp.vocab_stop - tp.vocab_start) * cfg.d_model)
             rp.weight_bytes = int(w)
             pages = batch_size * ((ctx_size + 63) // 64 + 1) + 64
-            rp.kv_bytes = int(pages * (last - first + 1) * 2 * tp.n_kv_local * 64 * cfg.head_dim * 2)
+            stage_layers = range(first, last + 1)
+            rp.kv_bytes = int(pages * len(cfg.kv_layers(stage_layers)) * 2 * tp.n_kv_local * 64 * cfg.head_dim * 2)
+            if cfg.is_hybrid:
+                # one fp32 state slot per batch lane (+1 scratch) for every linear-attention layer of the stage
+                from .engine.kv_cache import HybridState
+                nv = tp.gdn_v_stop - tp.gdn_v_start
+                rp.kv_bytes += (batch_size + 1) * HybridState.bytes_per_slot(len(cfg.gdn_layers(stage_layers)), 2 * cfg.gdn_key_dim + nv * cfg.ssm_state,
+                                                                             cfg.ssm_conv_kernel, nv, cfg.ssm_state)
             T = max(max_prefill_tokens, batch_size * 4)
             ff = (tp.ff_stop - tp.ff_start) if not cfg.is_moe else cfg.expert_ff
             rp.activation_bytes = int(T * (cfg.d_model * (4 + 2) + (tp.n_heads_local + 2 * tp.n_kv_local) * cfg.head_dim * 2

@@ -174,3 +174,51 @@ def test_hybrid_model_rejects_prefix_cache_and_speculation_by_name():
         LLMEngine(w, device="cpu", max_batch=2, max_context=128, prefix_cache=PrefixCache())
     with pytest.raises(ValueError, match="mtp"):
         LLMEngine(w, device="cpu", max_batch=2, max_context=128, mtp=MTPDecoder())
+
+
+def _tp_generate(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=0)
+    tp = TPContext.create(device="cpu")
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=tp, max_prefill_tokens=32)
+    outs = eng.generate([_prompt(17, 5), _prompt(40, 6)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    return outs, eng.model.hybrid_dims
+
+
+def test_tp2_shards_the_value_heads_and_matches_a_single_rank():
+    """Two gloo ranks: each holds two of the four value heads (with all key heads, read in tiled order from the rank's
+    first global head), the output projection is row-parallel; tokens must equal the single-rank engine's."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from tests.mp_utils import run_ranks
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=0)
+    ref = LLMEngine(w, device="cpu", max_batch=2, max_context=128, max_prefill_tokens=32).generate(
+        [_prompt(17, 5), _prompt(40, 6)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    res = run_ranks(_tp_generate, 2)
+    assert res[0][0] == ref and res[1][0] == ref
+    assert res[0][1]["n_v_heads"] == 2 and res[0][1]["conv_dim"] == 2 * 64 + 2 * 32
+
+
+def _pp_generate(rank, world):
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.parallel.pp import build_pipeline_engine
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=0)
+    layout = {"pp": 2, "tp": 1, "world": 2, "stages": [("s0", ["cpu"], 0, 2), ("s1", ["cpu"], 3, 7)]}
+    eng = build_pipeline_engine(w, layout, rank, microbatch_tokens=32, device="cpu", max_batch=2, max_context=256)
+    outs = eng.generate([_prompt(17, 5), _prompt(90, 6)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    return outs, eng.model.n_kv_layers, eng.model.hybrid_dims["n_layers"]
+
+
+def test_pp2_with_a_stage_of_linear_attention_only_matches_a_single_rank():
+    """Stage 0 holds layers 0-2 (no softmax block, hence no KV layer at all), stage 1 the rest."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from tests.mp_utils import run_ranks
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=0)
+    ref = LLMEngine(w, device="cpu", max_batch=2, max_context=256).generate(
+        [_prompt(17, 5), _prompt(90, 6)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    res = run_ranks(_pp_generate, 2)
+    assert res[0][0] == ref and res[1][0] == ref
+    assert (res[0][1], res[0][2]) == (0, 3) and (res[1][1], res[1][2]) == (2, 3)
