@@ -316,6 +316,15 @@ class CudaModel:
             e0, e1 = pl.expert_start, pl.expert_stop
             L.experts = self._pack_expert_slab(w, p, e0, e1)
             L.gate_up = L.down = None
+            L.shared = None
+            if c.shared_expert_ff:
+                # the always-on expert of the hybrid MoE family: replicated on every rank and added after the routed experts'
+                # sum (its width is one or two K blocks, too narrow to shard)
+                sh = CudaLayer()
+                sh.gate_up = self._pack_gate_up(w[p + "ffn_gate_shexp.weight"], w[p + "ffn_up_shexp.weight"])
+                sh.down = QLinear.from_qtensors([w[p + "ffn_down_shexp.weight"]], dev)
+                sh.gate_w = w[p + "ffn_gate_inp_shexp.weight"].to_float().to(dev).reshape(-1, 1).to(torch.bfloat16).contiguous()
+                L.shared = sh
         else:
             f0, f1 = pl.ff_start, pl.ff_stop
             g = w[p + "ffn_gate.weight"].rows(f0, f1)
@@ -380,6 +389,8 @@ class CudaModel:
                 tot += L.gate_up.nbytes() + L.down.nbytes()
             else:
                 tot += L.experts.gate_up.nbytes() + L.experts.down.nbytes()
+                if getattr(L, "shared", None) is not None:
+                    tot += L.shared.gate_up.nbytes() + L.shared.down.nbytes()
         if self.head is not None:
             tot += self.head.nbytes()
         return tot
@@ -398,6 +409,9 @@ class CudaModel:
         self.ws_gdn_y = e(T, self.gdn_conv_local, dt=f32) if self._gdn_ids else None
         ff = max(self.ff_local, c.expert_ff if c.is_moe else 0)
         self.ws_act = e(T, ff)
+        self.ws_shared = e(T, c.d_model, dt=f32) if c.shared_expert_ff else None
+        self.ws_sh_gu = e(T, 2 * c.shared_expert_ff) if c.shared_expert_ff else None
+        self.ws_sh_act = e(T, c.shared_expert_ff) if c.shared_expert_ff else None
         self.ws_gu = e(T, 2 * ff) if any(getattr(L.gate_up, "fused_swiglu", True) is False for L in self.layers if L.gate_up) else None
         self.ws_partial = e(T, c.d_model, dt=f32) if self.tp is not None else None
 
@@ -607,7 +621,30 @@ class CudaModel:
 
     def _moe(self, L: CudaLayer, h: torch.Tensor, T: int) -> None:
         from .moe import moe_forward
+        shared = self._shared_expert(L, h, T) if getattr(L, "shared", None) is not None else None
         moe_forward(self, L, h, T)
+        if shared is not None:
+            h += shared
+
+    def _shared_expert(self, L: CudaLayer, h: torch.Tensor, T: int) -> torch.Tensor:
+        """sigmoid(x . g) * FFN_shared(x) for the normed rows x of `h`, as fp32 rows in a workspace (read before the routed
+        experts update `h` in place)."""
+        c, sc, sh = self.cfg, self.scratch, L.shared
+        xn = self.ws_xn[:T]
+        ops.rmsnorm(h, L.ffn_norm, xn, c.rms_eps)
+        big = xn if T > ops.GEMV_MAX_ROWS else None
+        act = self.ws_sh_act[:T]
+        if sh.gate_up.fused_swiglu:
+            sh.gate_up(xn, act, epi=ops.EPI_SWIGLU, scratch=sc, xn=big)
+        else:
+            gu = self.ws_sh_gu[:T]
+            sh.gate_up(xn, gu, scratch=sc, xn=big)
+            f = c.shared_expert_ff
+            act.copy_((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(act.dtype))
+        y = self.ws_shared[:T]
+        sh.down(act, y, scratch=sc, xn=act if T > ops.GEMV_MAX_ROWS else None)
+        y.mul_(torch.sigmoid((xn @ sh.gate_w).float()))
+        return y
 
     def _final_logits(self, h_rows: torch.Tensor, out: torch.Tensor | None, norm_w: torch.Tensor) -> torch.Tensor:
         rows = h_rows.shape[0]

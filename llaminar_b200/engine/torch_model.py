@@ -45,6 +45,17 @@ class TorchPagedModel:
         kv_ids, gdn_ids = c.kv_layers(self.layer_ids), c.gdn_layers(self.layer_ids)
 
         def ffn(L, p):
+            if c.is_moe:
+                L["router"] = f(p + "ffn_gate_inp.weight")
+                e0, e1 = pl.expert_start, pl.expert_stop
+                L["e0"], L["e1"] = e0, e1
+                L["wg"] = f(p + "ffn_gate_exps.weight")[e0:e1]
+                L["wu"] = f(p + "ffn_up_exps.weight")[e0:e1]
+                L["wd"] = f(p + "ffn_down_exps.weight")[e0:e1]
+                if c.shared_expert_ff:                      # replicated on every rank, added after the experts' sum
+                    L["sh"] = (f(p + "ffn_gate_shexp.weight"), f(p + "ffn_up_shexp.weight"), f(p + "ffn_down_shexp.weight"),
+                               f(p + "ffn_gate_inp_shexp.weight").reshape(-1, 1))
+                return
             L["wg"] = f(p + "ffn_gate.weight")[pl.ff_start:pl.ff_stop]
             L["wu"] = f(p + "ffn_up.weight")[pl.ff_start:pl.ff_stop]
             L["wd"] = f(p + "ffn_down.weight")[:, pl.ff_start:pl.ff_stop]
@@ -81,15 +92,7 @@ class TorchPagedModel:
                 L["bq"], L["bk"], L["bv"] = f(p + "attn_q.bias")[qs:qe], f(p + "attn_k.bias")[ks:ke], f(p + "attn_v.bias")[ks:ke]
             if c.qk_norm:
                 L["qn"], L["kn"] = f(p + "attn_q_norm.weight"), f(p + "attn_k_norm.weight")
-            if c.is_moe:
-                L["router"] = f(p + "ffn_gate_inp.weight")
-                e0, e1 = pl.expert_start, pl.expert_stop
-                L["e0"], L["e1"] = e0, e1
-                L["wg"] = f(p + "ffn_gate_exps.weight")[e0:e1]
-                L["wu"] = f(p + "ffn_up_exps.weight")[e0:e1]
-                L["wd"] = f(p + "ffn_down_exps.weight")[e0:e1]
-            else:
-                ffn(L, p)
+            ffn(L, p)
             return L
 
         self.layers = [layer(i) for i in self.layer_ids]
@@ -192,9 +195,13 @@ class TorchPagedModel:
         c = self.cfg
         x = rmsnorm(h, L["attn_norm"], c.rms_eps)
         h = h + self._sum_ranks(self._linear_attention(L, x, fb, kv) if "gdn_index" in L else self._attention(L, x, fb, kvl))
-        y = self._ffn(L, rmsnorm(h, L["ffn_norm"], c.rms_eps))
+        xn = rmsnorm(h, L["ffn_norm"], c.rms_eps)
+        y = self._ffn(L, xn)
         if not (c.is_moe and getattr(self.tp, "moe_mode", "expert-parallel") == "replicated"):
             y = self._sum_ranks(y)               # replicated experts: every rank already has the full sum
+        if "sh" in L:
+            wg, wu, wd, gate = L["sh"]
+            y = y + torch.sigmoid(xn @ gate) * ((F.silu(xn @ wg.T) * (xn @ wu.T)) @ wd.T)
         return h + y
 
     def _logits(self, h_rows, norm_w, out):

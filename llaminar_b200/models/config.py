@@ -11,7 +11,7 @@ from dataclasses import asdict, dataclass, field, replace
 
 from ..gguf.constants import GGMLType
 
-SUPPORTED_ARCHS = ("qwen2", "qwen3", "qwen3moe", "qwen35")
+SUPPORTED_ARCHS = ("qwen2", "qwen3", "qwen3moe", "qwen35", "qwen35moe")
 
 
 @dataclass
@@ -35,6 +35,7 @@ class ModelConfig:
     n_experts_used: int = 0
     expert_ff: int = 0
     norm_topk_prob: bool = True
+    shared_expert_ff: int = 0       # qwen35moe: one always-on expert of this width, scaled by sigmoid(x . ffn_gate_inp_shexp)
     # multi-token prediction (NextN) head: number of extra decoder layers stored after the trunk
     nextn_layers: int = 0
     # hybrid layout (qwen35): every `full_attention_interval`-th layer is softmax attention over the KV cache, the others are
@@ -109,7 +110,7 @@ class ModelConfig:
         arch = gf.architecture
         if arch not in SUPPORTED_ARCHS:
             raise ValueError(f"unsupported GGUF architecture '{arch}' (supported: {', '.join(SUPPORTED_ARCHS)}; "
-                             "of the hybrid Gated-DeltaNet families the dense qwen35 is built, qwen35moe is not)")
+                             "qwen35 / qwen35moe are the hybrid Gated-DeltaNet families)")
         a = gf.arch_key
         d_model = int(a("embedding_length"))
         n_heads = int(a("attention.head_count"))
@@ -126,7 +127,7 @@ class ModelConfig:
         n_blocks = int(a("block_count"))
         hybrid = {}
         first_attn = 0                                  # first block with softmax attention (QK-norm / bias probes look there)
-        if arch == "qwen35":
+        if arch in ("qwen35", "qwen35moe"):
             interval = int(a("full_attention_interval", 4))
             first_attn = interval - 1
             hybrid = dict(full_attention_interval=interval, ssm_conv_kernel=int(a("ssm.conv_kernel", 4)),
@@ -154,6 +155,7 @@ class ModelConfig:
             n_experts_used=int(a("expert_used_count", 0) or 0),
             expert_ff=int(a("expert_feed_forward_length", 0) or 0),
             norm_topk_prob=True,
+            shared_expert_ff=(gf["blk.0.ffn_gate_shexp.weight"].shape[0] if "blk.0.ffn_gate_shexp.weight" in gf else 0),
             nextn_layers=nextn,
             name=str(gf.get("general.name", arch)),
             **hybrid,
@@ -179,6 +181,8 @@ class ModelConfig:
             md[f"{a}.expert_count"] = self.n_experts
             md[f"{a}.expert_used_count"] = self.n_experts_used
             md[f"{a}.expert_feed_forward_length"] = self.expert_ff
+            if self.shared_expert_ff:
+                md[f"{a}.expert_shared_count"] = 1
         if self.nextn_layers:
             md[f"{a}.nextn_predict_layers"] = self.nextn_layers
         if self.is_hybrid:
@@ -253,6 +257,13 @@ SHAPES = {
     # twice as many value heads as key heads (the 4B / 27B ratio)
     "tiny-qwen35": ModelConfig(name="tiny-qwen35", arch="qwen35", n_layers=8, head_dim=64, rope_dim=16, attn_gate=True,
                                full_attention_interval=4, ssm_state=32, ssm_k_heads=2, ssm_v_heads=4, rope_theta=1e7),
+    "tiny-qwen35moe": ModelConfig(name="tiny-qwen35moe", arch="qwen35moe", n_layers=4, head_dim=64, rope_dim=16, attn_gate=True,
+                                  full_attention_interval=4, ssm_state=32, ssm_k_heads=2, ssm_v_heads=4, rope_theta=1e7,
+                                  n_experts=8, n_experts_used=2, expert_ff=256, shared_expert_ff=256, d_ff=0),
+    "qwen3.5-35b-a3b": ModelConfig(name="qwen3.5-35b-a3b", arch="qwen35moe", n_layers=40, d_model=2048, n_heads=16, n_kv_heads=2,
+                                   head_dim=256, rope_dim=64, attn_gate=True, d_ff=0, vocab_size=248320, tie_embeddings=False,
+                                   full_attention_interval=4, ssm_state=128, ssm_k_heads=16, ssm_v_heads=32, rope_theta=1e7,
+                                   n_experts=256, n_experts_used=8, expert_ff=512, shared_expert_ff=512, context_length=262144),
     "qwen3.5-27b": ModelConfig(name="qwen3.5-27b", arch="qwen35", n_layers=64, d_model=5120, n_heads=24, n_kv_heads=4,
                                head_dim=256, rope_dim=64, attn_gate=True, d_ff=17408, vocab_size=248320,
                                tie_embeddings=False, full_attention_interval=4, ssm_state=128, ssm_k_heads=16,

@@ -152,6 +152,9 @@ class ReferenceModel:
             xe = x[tok]
             ye = (F.silu(xe @ Wg[e].T) * (xe @ Wu[e].T)) @ Wd[e].T
             out.index_add_(0, tok, ye * wt[tok, slot].unsqueeze(-1))
+        if c.shared_expert_ff:          # always-on expert, scaled per token by sigmoid(x . gate vector)
+            sh = (F.silu(x @ w[p + "ffn_gate_shexp.weight"].T) * (x @ w[p + "ffn_up_shexp.weight"].T)) @ w[p + "ffn_down_shexp.weight"].T
+            out = out + torch.sigmoid(x @ w[p + "ffn_gate_inp_shexp.weight"].reshape(-1, 1)) * sh
         return out
 
     def layer(self, i: int, h: torch.Tensor, positions: torch.Tensor, kv: KVState, kv_layer: int | None = None):

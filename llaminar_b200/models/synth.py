@@ -84,9 +84,25 @@ def synthesize(cfg: ModelConfig, recipe: QuantRecipe | str = "Q8_0", seed: int =
         vec(p + "ssm_norm.weight", cfg.ssm_state)
         mat(p + "ssm_out.weight", d, cfg.gdn_value_dim, layer=i)
         vec(p + cfg.ffn_norm_name, d)
-        mat(p + "ffn_gate.weight", cfg.d_ff, d, layer=i)
-        mat(p + "ffn_up.weight", cfg.d_ff, d, layer=i)
-        mat(p + "ffn_down.weight", d, cfg.d_ff, layer=i)
+        ffn(i)
+
+    def ffn(i: int) -> None:
+        p = f"blk.{i}."
+        if cfg.is_moe:
+            mat(p + "ffn_gate_inp.weight", cfg.n_experts, d, layer=i)
+            mat(p + "ffn_gate_exps.weight", cfg.n_experts, cfg.expert_ff, d, layer=i)
+            mat(p + "ffn_up_exps.weight", cfg.n_experts, cfg.expert_ff, d, layer=i)
+            mat(p + "ffn_down_exps.weight", cfg.n_experts, d, cfg.expert_ff, layer=i)
+            if cfg.shared_expert_ff:
+                mat(p + "ffn_gate_shexp.weight", cfg.shared_expert_ff, d, layer=i)
+                mat(p + "ffn_up_shexp.weight", cfg.shared_expert_ff, d, layer=i)
+                mat(p + "ffn_down_shexp.weight", d, cfg.shared_expert_ff, layer=i)
+                x = torch.randn(d, generator=gen, device=dev, dtype=torch.float32) * 0.2
+                tensors[p + "ffn_gate_inp_shexp.weight"] = qtensor_from_float(x, GGMLType.F32)
+        else:
+            mat(p + "ffn_gate.weight", cfg.d_ff, d, layer=i)
+            mat(p + "ffn_up.weight", cfg.d_ff, d, layer=i)
+            mat(p + "ffn_down.weight", d, cfg.d_ff, layer=i)
 
     def decoder_layer(i: int) -> None:
         if cfg.is_gdn_layer(i):
@@ -105,15 +121,7 @@ def synthesize(cfg: ModelConfig, recipe: QuantRecipe | str = "Q8_0", seed: int =
             vec(p + "attn_q_norm.weight", cfg.head_dim)
             vec(p + "attn_k_norm.weight", cfg.head_dim)
         vec(p + cfg.ffn_norm_name, d)
-        if cfg.is_moe:
-            mat(p + "ffn_gate_inp.weight", cfg.n_experts, d, layer=i)
-            mat(p + "ffn_gate_exps.weight", cfg.n_experts, cfg.expert_ff, d, layer=i)
-            mat(p + "ffn_up_exps.weight", cfg.n_experts, cfg.expert_ff, d, layer=i)
-            mat(p + "ffn_down_exps.weight", cfg.n_experts, d, cfg.expert_ff, layer=i)
-        else:
-            mat(p + "ffn_gate.weight", cfg.d_ff, d, layer=i)
-            mat(p + "ffn_up.weight", cfg.d_ff, d, layer=i)
-            mat(p + "ffn_down.weight", d, cfg.d_ff, layer=i)
+        ffn(i)
 
     for i in range(cfg.n_layers):
         decoder_layer(i)

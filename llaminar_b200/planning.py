@@ -113,6 +113,8 @@ def layer_weight_bytes(cfg: ModelConfig, recipe: QuantRecipe, layer: int, tp: TP
         n_e = tp.expert_stop - tp.expert_start
         tot += n_e * (2 * _bytes(t("ffn_gate_exps"), cfg.expert_ff * d, True) + _bytes(t("ffn_down_exps"), cfg.expert_ff * d, True))
         tot += 2 * cfg.n_experts * d
+        if cfg.shared_expert_ff:            # replicated on every rank
+            tot += 2 * _bytes(t("ffn_gate_shexp"), cfg.shared_expert_ff * d) + _bytes(t("ffn_down_shexp"), cfg.shared_expert_ff * d)
     else:
         ff = tp.ff_stop - tp.ff_start
         tot += 2 * _bytes(t("ffn_gate"), ff * d) + _bytes(t("ffn_down"), ff * d)

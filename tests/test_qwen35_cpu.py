@@ -35,13 +35,18 @@ def test_convolution_state_carries_across_calls():
     assert torch.allclose(y, torch.cat([y1, y2]), atol=1e-6)
 
 
-def _hf_model():
+def _hf_model(moe: bool = False):
     tf = pytest.importorskip("transformers")
     try:
-        from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM, Qwen3_5TextConfig
+        if moe:
+            from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM as Qwen3_5ForCausalLM
+            from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeTextConfig as Qwen3_5TextConfig
+        else:
+            from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM, Qwen3_5TextConfig
     except Exception as e:                                    # an older transformers without the family
         pytest.skip(f"transformers has no qwen3_5: {e}")
-    cfg = Qwen3_5TextConfig(hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+    extra = dict(num_experts=6, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48) if moe else {}
+    cfg = Qwen3_5TextConfig(**extra, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
                             intermediate_size=128, vocab_size=128, rms_norm_eps=1e-6, max_position_embeddings=512,
                             layer_types=["linear_attention"] * 3 + ["full_attention"], full_attention_interval=4,
                             linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
@@ -59,6 +64,8 @@ def _hf_model():
                 p.copy_(torch.log(torch.rand_like(p) * 6 + 0.5))
             if n.endswith("linear_attn.norm.weight"):
                 p.copy_(torch.rand_like(p) + 0.5)
+            if "experts." in n or "mlp.gate.weight" in n or "shared_expert_gate" in n:
+                p.copy_(torch.randn_like(p) * 0.2)           # left uninitialised / zero by the constructor
     return cfg, m
 
 
@@ -71,9 +78,12 @@ def _tiled_value_heads(n_k: int, n_v: int) -> list[int]:
 
 def _convert(cfg, m) -> ModelWeights:
     n_k, n_v, d = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim
-    ours = ModelConfig(name="hf-tiny-qwen35", arch="qwen35", n_layers=cfg.num_hidden_layers, d_model=cfg.hidden_size,
-                       n_heads=cfg.num_attention_heads, n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
-                       d_ff=cfg.intermediate_size, vocab_size=cfg.vocab_size, rope_theta=10000.0, rms_eps=cfg.rms_norm_eps,
+    moe = hasattr(cfg, "num_experts")
+    moe_kw = dict(n_experts=cfg.num_experts, n_experts_used=cfg.num_experts_per_tok, expert_ff=cfg.moe_intermediate_size,
+                  shared_expert_ff=cfg.shared_expert_intermediate_size) if moe else {}
+    ours = ModelConfig(name="hf-tiny-qwen35", arch="qwen35moe" if moe else "qwen35", n_layers=cfg.num_hidden_layers, d_model=cfg.hidden_size,
+                       n_heads=cfg.num_attention_heads, n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, **moe_kw,
+                       d_ff=0 if moe else cfg.intermediate_size, vocab_size=cfg.vocab_size, rope_theta=10000.0, rms_eps=cfg.rms_norm_eps,
                        tie_embeddings=False, full_attention_interval=4, ssm_conv_kernel=4, ssm_state=d, ssm_k_heads=n_k,
                        ssm_v_heads=n_v, rope_dim=int(cfg.head_dim * 0.25), attn_gate=True)
     sd = {k: v.detach().float() for k, v in m.state_dict().items()}
@@ -88,8 +98,18 @@ def _convert(cfg, m) -> ModelWeights:
         s, p = f"model.layers.{i}.", f"blk.{i}."
         put(p + "attn_norm.weight", 1 + sd[s + "input_layernorm.weight"])
         put(p + "post_attention_norm.weight", 1 + sd[s + "post_attention_layernorm.weight"])
-        for a, b in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")):
-            put(p + f"ffn_{a}.weight", sd[s + f"mlp.{b}.weight"])
+        if moe:
+            ff = cfg.moe_intermediate_size
+            put(p + "ffn_gate_inp.weight", sd[s + "mlp.gate.weight"])
+            put(p + "ffn_gate_exps.weight", sd[s + "mlp.experts.gate_up_proj"][:, :ff])
+            put(p + "ffn_up_exps.weight", sd[s + "mlp.experts.gate_up_proj"][:, ff:])
+            put(p + "ffn_down_exps.weight", sd[s + "mlp.experts.down_proj"])
+            for a, b in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")):
+                put(p + f"ffn_{a}_shexp.weight", sd[s + f"mlp.shared_expert.{b}.weight"])
+            put(p + "ffn_gate_inp_shexp.weight", sd[s + "mlp.shared_expert_gate.weight"].reshape(-1))
+        else:
+            for a, b in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")):
+                put(p + f"ffn_{a}.weight", sd[s + f"mlp.{b}.weight"])
         if cfg.layer_types[i] == "linear_attention":
             la = s + "linear_attn."
             kd = n_k * d
@@ -115,8 +135,9 @@ def _convert(cfg, m) -> ModelWeights:
     return ModelWeights(ours, t)
 
 
-def test_oracle_matches_the_transformers_model():
-    cfg, m = _hf_model()
+@pytest.mark.parametrize("moe", [False, True], ids=["dense", "moe-with-shared-expert"])
+def test_oracle_matches_the_transformers_model(moe):
+    cfg, m = _hf_model(moe)
     w = _convert(cfg, m)
     toks = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(5))
     with torch.no_grad():
@@ -222,3 +243,32 @@ def test_pp2_with_a_stage_of_linear_attention_only_matches_a_single_rank():
     res = run_ranks(_pp_generate, 2)
     assert res[0][0] == ref and res[1][0] == ref
     assert (res[0][1], res[0][2]) == (0, 3) and (res[1][1], res[1][2]) == (2, 3)
+
+
+def _moe_tp_generate(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen35moe"], "Q8_0", seed=11, std=0.05)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=128, tp=TPContext.create(device="cpu"))
+    return eng.generate([_prompt(17, 5), _prompt(40, 6)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+
+
+def test_hybrid_moe_engine_matches_the_oracle_and_expert_parallel_ranks_agree():
+    """qwen35moe: linear-attention blocks, routed experts and the always-on shared expert with its sigmoid gate.  Single
+    rank against the oracle; two expert-parallel ranks (the shared expert replicated, added after the experts' sum)
+    against the single rank."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from tests.mp_utils import run_ranks
+    w = synthesize(SHAPES["tiny-qwen35moe"], "Q8_0", seed=11, std=0.05)
+    assert "blk.0.ffn_gate_inp_shexp.weight" in w and w.config.shared_expert_ff == 256
+    ref = ReferenceModel(w)
+    prompts = [_prompt(17, 5), _prompt(40, 6)]
+    want = [ref.generate_greedy(torch.tensor(p), 6)[0] for p in prompts]
+    got = LLMEngine(w, device="cpu", max_batch=2, max_context=128).generate(
+        prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert got == want
+    assert any(len(set(o)) > 1 for o in got)                   # not a degenerate repeat
+    res = run_ranks(_moe_tp_generate, 2)
+    assert res[0] == got and res[1] == got

@@ -117,3 +117,27 @@ def test_hybrid_engine_graph_decode_equals_eager_and_tracks_the_oracle():
         for i, t in enumerate(out):
             row = full[len(pr) - 1 + i]
             assert row[t] >= row.max() - 0.05 * (row.max() - row.min())
+
+
+def test_hybrid_moe_with_shared_expert_tracks_the_oracle_graph_and_eager():
+    """qwen35moe on the GPU runner: fused MoE decode (route, grouped expert GEMVs, combine) plus the shared expert's FFN
+    scaled by its sigmoid gate, on top of the linear-attention blocks.  Layer by layer against the oracle, teacher-forced
+    (a router near-tie that flips an expert moves single rows, so the gates are on whole-layer cosine and on the logits'
+    top-1 / KL, not on every token); captured and eager decode agree."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.parity import compare
+    w = synthesize(SHAPES["tiny-qwen35moe"], "Q8_0", seed=0)
+    rows, _ = compare(w, DEV, prompt_tokens=90, decode_steps=3)
+    for r in rows:
+        if r["stage"] == "logits":
+            assert r["top1"] >= 0.9 and r["kl"] < 0.05, r
+        else:
+            assert r["cosine"] > 0.98, r
+    prompts = [_prompt(n, n) for n in (40, 7, 90)]
+    p = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    e1 = LLMEngine(w, device=DEV, max_batch=4, max_context=256, use_graphs=True)
+    e2 = LLMEngine(w, device=DEV, max_batch=4, max_context=256, use_graphs=False)
+    o1, o2 = e1.generate(prompts, p), e2.generate(prompts, p)
+    assert e1.stats["graph_replays"] > 0
+    assert sum(a == b for x, y in zip(o1, o2) for a, b in zip(x, y)) >= 20
