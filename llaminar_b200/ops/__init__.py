@@ -296,11 +296,6 @@ def _attn_tc_default() -> bool:
     return _ATTN_TC
 
 
-def swiglu_tiled(gu, out) -> None:
-    ext().swiglu_tiled(gu, out)
-    _count()
-
-
 def argmax(logits: torch.Tensor, tokens: torch.Tensor | None, pairs: torch.Tensor | None = None, idx_offset: int = 0) -> None:
     """Row argmax (ties -> lower index).  ``pairs`` [rows, 2] int32 receives (value bits, idx_offset + index) for the
     cross-rank merge of a vocabulary-sharded head."""

@@ -364,19 +364,6 @@ static void attn_prefill(const Tensor& q, const Tensor& kv, Tensor out, const Te
     }
 }
 
-static void swiglu_tiled(const Tensor& gu, Tensor out) {
-    const c10::cuda::CUDAGuard guard(gu.device());
-    TORCH_CHECK(gu.is_contiguous() && out.is_contiguous() && gu.size(1) == 2 * out.size(1) && out.size(1) % 64 == 0);
-    LLM_CUDA_CHECK(llm::launch_swiglu_tiled(static_cast<const __nv_bfloat16*>(gu.data_ptr()), static_cast<__nv_bfloat16*>(out.data_ptr()),
-                                            (int)out.size(0), (int)out.size(1), cur_stream()));
-}
-
-static void add_bf16_to_f32(Tensor h, const Tensor& x) {
-    const c10::cuda::CUDAGuard guard(h.device());
-    TORCH_CHECK(h.is_contiguous() && x.is_contiguous() && h.numel() == x.numel());
-    LLM_CUDA_CHECK(llm::launch_add_bf16_to_f32(static_cast<float*>(h.data_ptr()), static_cast<const __nv_bfloat16*>(x.data_ptr()),
-                                               (size_t)h.numel(), cur_stream()));
-}
 
 static void argmax(const Tensor& logits, const OptTensor& tokens, const OptTensor& pairs, int64_t idx_offset) {
     check_cuda(logits, "logits");
@@ -627,8 +614,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("rope_kv", &rope_kv);
     m.def("attn_decode", &attn_decode);
     m.def("attn_prefill", &attn_prefill);
-    m.def("swiglu_tiled", &swiglu_tiled);
-    m.def("add_bf16_to_f32", &add_bf16_to_f32);
     m.def("argmax", &argmax);
     m.def("argmax_merge", &argmax_merge);
     m.def("sample", &sample);

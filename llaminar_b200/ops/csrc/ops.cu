@@ -353,44 +353,6 @@ cudaError_t launch_kv_dequant_pages(const uint8_t* kv8, size_t page_bytes, size_
 }
 
 // ------------------------------------------------------------------------------------------------
-// SwiGLU over the 16-column-interleaved gate|up GEMM output; residual add
-// ------------------------------------------------------------------------------------------------
-__global__ void swiglu_tiled_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int d_ff) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;     // one thread per 2 output columns
-    const int half = d_ff / 2;
-    if (i >= (size_t)rows * half) return;
-    const int r = i / half, c = (i % half) * 2;
-    const int grp = c / 16, off = c % 16;                 // 32 fused columns = 16 gate + 16 up
-    const __nv_bfloat16* base = gu + (size_t)r * 2 * d_ff + grp * 32;
-    const uint32_t g = *reinterpret_cast<const uint32_t*>(base + off);
-    const uint32_t u = *reinterpret_cast<const uint32_t*>(base + 16 + off);
-    *reinterpret_cast<uint32_t*>(out + (size_t)r * d_ff + c) = pack_bf16(silu(bf16_lo(g)) * bf16_lo(u), silu(bf16_hi(g)) * bf16_hi(u));
-}
-cudaError_t launch_swiglu_tiled(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int d_ff, cudaStream_t st) {
-    const size_t n = (size_t)rows * d_ff / 2;
-    if (n == 0) return cudaSuccess;
-    swiglu_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(gu, out, rows, d_ff);
-    return cudaGetLastError();
-}
-
-__global__ void add_bf16_to_f32_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ x, size_t n) {
-    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
-    if (i + 1 < n) {
-        const uint32_t v = *reinterpret_cast<const uint32_t*>(x + i);
-        float2 a = *reinterpret_cast<float2*>(h + i);
-        a.x += bf16_lo(v); a.y += bf16_hi(v);
-        *reinterpret_cast<float2*>(h + i) = a;
-    } else if (i < n) {
-        h[i] += __bfloat162float(x[i]);
-    }
-}
-cudaError_t launch_add_bf16_to_f32(float* h, const __nv_bfloat16* x, size_t n, cudaStream_t st) {
-    if (n == 0) return cudaSuccess;
-    add_bf16_to_f32_kernel<<<(unsigned)((n / 2 + 256) / 256), 256, 0, st>>>(h, x, n);
-    return cudaGetLastError();
-}
-
-// ------------------------------------------------------------------------------------------------
 // sampling
 // ------------------------------------------------------------------------------------------------
 LLM_DEVICE uint32_t order_key(float f) {                 // monotone float -> uint map

@@ -92,8 +92,6 @@ cudaError_t launch_rmsnorm(const float* h, const float* w, __nv_bfloat16* out, i
 cudaError_t launch_mtp_concat_norm(const float* emb, const float* hidden, const float* enorm, const float* hnorm,
                                    __nv_bfloat16* out, int rows, int d, float eps, cudaStream_t st);
 // out[t, c] = silu(gate) * up, reading a gate|up GEMM output whose 32-column groups hold 16 gate + 16 up columns
-cudaError_t launch_swiglu_tiled(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int d_ff, cudaStream_t st);
-cudaError_t launch_add_bf16_to_f32(float* h, const __nv_bfloat16* x, size_t n, cudaStream_t st);
 
 // greedy: argmax of each row -> tokens[row]
 cudaError_t launch_argmax(const float* logits, int rows, int vocab, int stride, int* tokens, int* pairs, int idx_offset,

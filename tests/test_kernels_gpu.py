@@ -176,19 +176,15 @@ def test_gemm_tc_swiglu_large_k(m):
     assert _rel(out, ref) < 2e-2
 
 
-def test_rmsnorm_and_swiglu():
+@pytest.mark.parametrize("rows,d", [(37, 1024), (3, 5120), (5, 12288)])
+def test_rmsnorm(rows, d):
+    """Rows up to 8192 values stay in registers across the reduction; longer rows are read twice."""
     from llaminar_b200 import ops
-    h = torch.randn(37, 1024, device=DEV)
-    w = torch.rand(1024, device=DEV) + 0.5
-    out = torch.empty(37, 1024, dtype=torch.bfloat16, device=DEV)
+    h = torch.randn(rows, d, device=DEV)
+    w = torch.rand(d, device=DEV) + 0.5
+    out = torch.empty(rows, d, dtype=torch.bfloat16, device=DEV)
     ops.rmsnorm(h, w, out, 1e-6)
     assert _rel(out, ref_rmsnorm(h, w, 1e-6)) < 5e-3
-    gu = torch.randn(9, 256, device=DEV).to(torch.bfloat16)
-    o = torch.empty(9, 128, dtype=torch.bfloat16, device=DEV)
-    ops.swiglu_tiled(gu, o)
-    t = gu.float().view(9, 8, 2, 16)
-    ref = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(9, 128)
-    assert _rel(o, ref) < 1e-2
 
 
 def _paged_setup(B, ctx_lens, n_kv, D, extra_pages=3):
