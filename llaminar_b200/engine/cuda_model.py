@@ -212,6 +212,25 @@ class CudaLayer:
     pass
 
 
+def paged_decode_attention_torch(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                                 scale: float) -> torch.Tensor:
+    """One query row per sequence against the paged cache, any head size, as one batched expression with static shapes
+    (every sequence's whole page-table row is gathered and the positions past its length are masked), so a CUDA graph can
+    capture it.  q: [B, H, D]; kv_layer: [n_pages, 2, Hk, 64, D]; block_table: [B, P]; seq_lens: [B] (>= 1, the new
+    token included).  Returns fp32 [B, H, D].  The gather reads P x 64 positions per sequence whatever its length: a
+    stand-in for head sizes without a decode kernel, not a fast path."""
+    B, H, D = q.shape
+    P, Hk = block_table.shape[1], kv_layer.shape[2]
+    pages = kv_layer[block_table.long()]                                        # [B, P, 2, Hk, 64, D]
+    K = pages[:, :, 0].permute(0, 2, 1, 3, 4).reshape(B, Hk, P * 64, D)
+    V = pages[:, :, 1].permute(0, 2, 1, 3, 4).reshape(B, Hk, P * 64, D)
+    qg = q.reshape(B, Hk, H // Hk, D).to(K.dtype)
+    s = torch.einsum("bkgd,bkld->bkgl", qg, K).float() * scale
+    dead = torch.arange(P * 64, device=q.device)[None, :] >= seq_lens.long()[:, None]
+    p = torch.softmax(s.masked_fill(dead[:, None, None, :], float("-inf")), dim=-1)
+    return torch.einsum("bkgl,bkld->bkgd", p.to(V.dtype), V).float().reshape(B, H, D)
+
+
 class CudaModel:
     def __init__(self, weights: ModelWeights, device="cuda", max_tokens: int = 4096, tp=None, layer_range=None,
                  with_head: bool = True, with_embed: bool = True, with_mtp: bool = True):
@@ -248,9 +267,10 @@ class CudaModel:
         self.gdn_v_local = pl.gdn_v_stop - pl.gdn_v_start
         self.gdn_conv_local = 2 * c.gdn_key_dim + self.gdn_v_local * c.ssm_state
         # hybrid models whose softmax blocks have a head size without an attention kernel here (qwen3.5 checkpoints use 256)
-        # run those blocks on PyTorch ops, which CUDA graphs cannot capture (host-side loop over the sequences)
+        # run attention on PyTorch ops: decode steps as one batched, shape-static expression that CUDA graphs capture,
+        # prefill chunks sequence by sequence
         self.torch_attention = c.is_hybrid and c.head_dim not in (64, 128)
-        self.graph_safe = not self.torch_attention
+        self.graph_safe = True
         self.layers = [self._build_layer(weights, i) for i in self.layer_ids]
         self.mtp_layers = []
         self.mtp_kv_base = len(self._kv_ids)            # the NextN layers' K/V follow this stage's own layers in the cache
@@ -490,7 +510,9 @@ class CudaModel:
         o = self.ws_o[:T]
         o3 = o.view(T, H, D)
         scale = 1.0 / math.sqrt(D)
-        if self.torch_attention:
+        if self.torch_attention and fb.is_decode and fb.rows_per_seq == 1:
+            o3.copy_(paged_decode_attention_torch(q, kv_layer, fb.block_table, fb.seq_lens, scale))
+        elif self.torch_attention:
             o3.copy_(self._attention_torch(q, fb, kv_layer, scale))
         else:
             qb = self.ws_q[:T]

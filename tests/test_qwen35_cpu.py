@@ -272,3 +272,22 @@ def test_hybrid_moe_engine_matches_the_oracle_and_expert_parallel_ranks_agree():
     assert any(len(set(o)) > 1 for o in got)                   # not a degenerate repeat
     res = run_ranks(_moe_tp_generate, 2)
     assert res[0] == got and res[1] == got
+
+
+def test_batched_paged_decode_attention_matches_a_per_sequence_loop():
+    """The shape-static decode attention used for head sizes without a kernel (256 in the published hybrid checkpoints):
+    three sequences of different lengths on shuffled pages, GQA 4:2, against plain attention over each sequence's rows."""
+    from llaminar_b200.engine.cuda_model import paged_decode_attention_torch
+    torch.manual_seed(2)
+    B, H, Hk, D, P = 3, 4, 2, 256, 3
+    kv = torch.randn(12, 2, Hk, 64, D)
+    bt = torch.tensor([[5, 2, 9], [1, 7, 0], [3, 11, 4]], dtype=torch.int32)
+    lens = torch.tensor([130, 1, 64], dtype=torch.int32)
+    q = torch.randn(B, H, D)
+    got = paged_decode_attention_torch(q, kv, bt, lens, D ** -0.5)
+    for b in range(B):
+        n = int(lens[b])
+        K = kv[bt[b].long(), 0].permute(1, 0, 2, 3).reshape(Hk, P * 64, D)[:, :n].repeat_interleave(H // Hk, 0)
+        V = kv[bt[b].long(), 1].permute(1, 0, 2, 3).reshape(Hk, P * 64, D)[:, :n].repeat_interleave(H // Hk, 0)
+        p = torch.softmax(torch.einsum("hd,hld->hl", q[b], K) * D ** -0.5, -1)
+        assert torch.allclose(got[b], torch.einsum("hl,hld->hd", p, V), atol=1e-5)
