@@ -470,8 +470,11 @@ def cmd_describe(cfg: OrchestrationConfig) -> int:
         from .utils.env import debug_env
         print(debug_env().describe())
         return 0
-    from .utils.devices import describe_devices
-    print(json.dumps(describe_devices(), indent=2))
+    from .utils.devices import benchmark_devices, describe_devices
+    out = describe_devices()
+    if cfg.values.get("device_benchmark"):
+        out["benchmark"] = benchmark_devices()
+    print(json.dumps(out, indent=2))
     return 0
 
 

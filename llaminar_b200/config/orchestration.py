@@ -75,6 +75,8 @@ OPTIONS: list[OptionSpec] = [
     _o("--dry-run", action="store_true", help="plan and validate, then exit", category="devices"),
     _o("--explain-placement", action="store_true", category="devices"),
     _o("--env", action="store_true", category="debug", help="describe: list the LLAMINAR_* environment switches instead of the devices"),
+    _o("--device-benchmark", action="store_true", category="debug",
+       help="describe: also measure every device (copy bandwidth, bf16 matrix throughput, peer-to-peer copy bandwidth)"),
     _o("--validate-only", action="store_true", category="devices"),
     _o("--suggest-layout", type=int, default=None, category="devices",
        help="plan: find the smallest pp x tp placement on up to N GPUs that fits their memory and print its flags"),

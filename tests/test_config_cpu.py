@@ -268,3 +268,14 @@ def test_plan_of_a_checkpoint_budgets_the_formats_in_the_file(tmp_path, capsys):
     assert sizes["Q8_0"] > 1.5 * sizes["Q4_K_M"]
     assert main(["plan", "-m", str(tmp_path / "Q8_0.gguf"), "-d", "cuda:0"]) == 0
     assert "weight" in capsys.readouterr().out
+
+
+def test_describe_device_benchmark_reports_copy_and_matrix_rates(capsys):
+    """`describe --device-benchmark`: on a host without GPUs the CPU is measured (small sizes), the JSON keeps its shape."""
+    import json
+    from llaminar_b200.app import main
+    assert main(["describe", "--device-benchmark"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    d = out["benchmark"]["devices"][0]
+    assert d["copy_gbs"] > 0 and d["matmul_tflops"] > 0 and d["matmul_dtype"] in ("float32", "bfloat16")
+    assert isinstance(out["benchmark"]["p2p"], list)
