@@ -132,9 +132,8 @@ def build_engine(cfg: OrchestrationConfig):
                  mcfg.n_heads, mcfg.n_kv_heads, mcfg.vocab_size)
         log.info("placement\n%s", plan.table())
     if mcfg.is_hybrid:
-        # linear-attention state is neither stored with cached prefixes nor rolled back after a rejected draft here
-        bad = [f for f, on in (("--prefix-cache", v.get("prefix_cache")), ("--mtp", v.get("mtp")),
-                               ("--kv-cache-precision q8_0", v.get("kv_cache_precision") in ("q8_0", "q8_1"))) if on]
+        # the gated attention blocks append bf16 K/V
+        bad = [f for f, on in (("--kv-cache-precision q8_0", v.get("kv_cache_precision") in ("q8_0", "q8_1"))) if on]
         if bad:
             raise ConfigError([f"{f} is not available for hybrid (linear-attention) models such as {mcfg.arch}" for f in bad])
     prefix = None

@@ -77,6 +77,8 @@ class ForwardBatch:
     logit_rows: torch.Tensor | None = None
     embeds: torch.Tensor | None = None       # optional fp32 [T, d] input instead of token embeddings
     state_slots: torch.Tensor | None = None  # [B] hybrid models: the state slot of every sequence (row of block_table)
+    defer_state: bool = False                # hybrid models, speculative verification: equal rows per sequence, the recurrent
+                                             # state is advanced later by `HybridState.commit` for the accepted rows only
 
     @property
     def is_decode(self) -> bool:
@@ -466,11 +468,22 @@ class CudaModel:
         d, nv = c.ssm_state, self.gdn_v_local
         o = self.ws_gdn_o[:T]
         conv, rec = hs.conv[L.gdn_index], hs.rec[L.gdn_index]
+        from ..models import gdn
+        if fb.defer_state:
+            B = fb.state_slots.shape[0]
+            x = inp.float().view(B, T // B, -1)
+            C = self.gdn_conv_local
+            rows, hs.stash[L.gdn_index] = gdn.gdn_rows_deferred(
+                x[..., :C], x[..., L.z_off:L.z_off + nv * d], x[..., L.ab_off:L.ab_off + nv], x[..., L.ab_off + nv:L.ab_off + 2 * nv],
+                L.conv_w, L.ssm_a, L.dt_bias, L.ssm_norm, conv, rec, fb.state_slots.long(), c.ssm_k_heads, nv, d, c.rms_eps,
+                self.plan.gdn_v_start)
+            hs.stash_slots = fb.state_slots.long()
+            o.copy_(rows)
+            return o
         if fb.is_decode and fb.rows_per_seq == 1:
             ops.gdn_step(inp, self.gdn_conv_local, L.z_off, L.ab_off, L.conv_w, L.ssm_a, L.dt_bias, L.ssm_norm, conv, rec,
                          fb.state_slots, self.ws_gdn_y[:T], o, c.ssm_k_heads, self.plan.gdn_v_start, c.rms_eps)
             return o
-        from ..models import gdn
         seqs = getattr(fb, "_gdn_seqs", None)
         if seqs is None:
             seqs = fb._gdn_seqs = gdn.batch_sequences(fb.seq_ids, fb.positions, fb.state_slots)

@@ -97,12 +97,6 @@ class LLMEngine:
         hybrid = None
         hd = getattr(self.model, "hybrid_dims", None)
         if hd:
-            if prefix_cache is not None:
-                raise ValueError("--prefix-cache is not available for hybrid (linear-attention) models: a cached prefix would "
-                                 "need the recurrent state at its end, which this build does not store")
-            if mtp is not None:
-                raise ValueError("--mtp is not available for hybrid (linear-attention) models: a rejected draft would need "
-                                 "the recurrent state rolled back, which this build does not do")
             if kv_dtype == KV_Q8:
                 raise ValueError("the 8-bit KV cache is not available for hybrid (linear-attention) models: their gated "
                                  "attention blocks append to a bf16 cache")
@@ -383,9 +377,12 @@ class LLMEngine:
                 cost = len(r.prompt)
                 if batch and cost > budget:
                     break
+                if self.kv.hybrid is not None:
+                    r.slot = self.kv.hybrid.alloc()            # at most max_batch sequences are admitted: a slot is free
                 try:
                     self._admit(r, len(batch))
                 except OutOfPages:
+                    self._release_slot(r)
                     if not batch and not self.running:
                         # the whole cache is free and the prompt still does not fit: this request can never run.  It
                         # ends with finish reason "cache_full" (the server answers 400); the queue behind it goes on.
@@ -394,8 +391,6 @@ class LLMEngine:
                         return [StepOutput(r.rid, [], True, "cache_full", [] if r.params.wants_logprobs else None)]
                     break
                 self.waiting.pop(0)
-                if self.kv.hybrid is not None:
-                    r.slot = self.kv.hybrid.alloc()            # at most max_batch sequences are admitted: a slot is free
                 batch.append(r)
                 budget -= cost
             if batch:
@@ -416,8 +411,9 @@ class LLMEngine:
             if self._available_pages() < need:
                 raise OutOfPages("waiting for pages after a preemption")
         hit_pages, hit_tokens = [], 0
+        hybrid = self.cfg.is_hybrid                          # a model property: every rank takes the same branches below
         if self.prefix_cache is not None:
-            term = self.prefix_cache.lookup_terminal(r.prompt)
+            term = None if hybrid else self.prefix_cache.lookup_terminal(r.prompt)
             if not self._agree_min(1 if term is not None else 0):
                 term = None                                   # some rank does not have it: nobody uses it
             if term is not None:
@@ -432,6 +428,16 @@ class LLMEngine:
                     r.kv = SequenceKV()
             held, hit_tokens = self.prefix_cache.lookup(r.prompt)      # `held`: one reference per page, dropped below
             agreed = self._agree_min(hit_tokens)                       # every rank reuses the same number of pages
+            if hybrid:
+                # a linear-attention state can only be resumed where a snapshot of it is held: cut the hit back to the
+                # longest such boundary that leaves a token to run, the same one on every rank
+                limit = min(agreed, len(r.prompt) - 1) // PAGE_SIZE * PAGE_SIZE
+                local = self.kv.hybrid is not None           # a pipeline stage may hold softmax blocks only
+                b = self._agree_min(self.prefix_cache.state_boundary(r.prompt, limit) if local else limit)
+                have = b == 0 or not local or self.prefix_cache.state_at(r.prompt, b) is not None
+                agreed = b if self._agree_min(1 if have else 0) else 0
+                if agreed and local:
+                    self.kv.hybrid.restore(r.slot, self.prefix_cache.state_at(r.prompt, agreed))
             hit_pages = list(held)[:agreed // PAGE_SIZE]
             hit_tokens = len(hit_pages) * PAGE_SIZE if agreed < hit_tokens else hit_tokens
         else:
@@ -642,6 +648,12 @@ class LLMEngine:
         for r in batch:
             if r.terminal is not None:            # exact repeat of a cached prompt: logits and hidden row come from the cache
                 final_logits[r.rid], final_hidden[r.rid] = r.terminal.logits, r.terminal.hidden
+        # hybrid models with a prefix cache: one snapshot of the linear-attention state per prompt, at the last block boundary
+        # that leaves a token to run (where a follow-up prompt that extends this one can resume)
+        snap_at = {}
+        if self.prefix_cache is not None and self.kv.hybrid is not None:
+            snap_at = {r.rid: (len(r.prompt) - 1) // PAGE_SIZE * PAGE_SIZE for r in batch}
+            snap_at = {rid: b for rid, b in snap_at.items() if b > pending[rid]}
         while any(pending[r.rid] < len(r.prompt) for r in batch):
             toks, pos, sid, cu, ctx, rows_for, chunks = [], [], [], [0], [], [], []
             budget = self.max_prefill_tokens
@@ -651,6 +663,8 @@ class LLMEngine:
                 if done >= len(r.prompt) or budget <= 0:
                     continue
                 n = min(len(r.prompt) - done, budget)
+                if snap_at.get(r.rid, 0) > done:            # a chunk ends where the prefix cache wants the recurrent state
+                    n = min(n, snap_at[r.rid] - done)
                 budget -= n
                 b = len(ctx)
                 toks.extend(r.prompt[done:done + n])
@@ -674,6 +688,9 @@ class LLMEngine:
                               logit_rows=it(logit_rows) if logit_rows else None,
                               state_slots=it([r.slot for r, _, _ in chunks]) if self.kv.hybrid is not None else None)
             logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
+            for r, done, n in chunks:
+                if snap_at.get(r.rid) == done + n:
+                    self.prefix_cache.store_state(r.prompt[:done + n], self.kv.hybrid.snapshot(r.slot))
             if self.mtp is not None:
                 keep = {r.rid: h[row].clone() for r, row in rows_for if row is not None}
                 self.mtp.on_prefill_chunk(self, fb, h, chunks)
@@ -694,7 +711,7 @@ class LLMEngine:
             self.running.append(r)
             if self.prefix_cache is not None:
                 self.prefix_cache.insert(self, r)
-                if r.terminal is None:
+                if r.terminal is None and not self.cfg.is_hybrid:
                     self.prefix_cache.store_terminal(self, r, final_logits[r.rid], final_hidden[r.rid])
             if self.mtp is not None:
                 self.mtp.on_prefill_done(self, r, t, final_hidden[r.rid])

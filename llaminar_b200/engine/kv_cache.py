@@ -71,6 +71,18 @@ class HybridState:
         self.conv = torch.zeros(n_layers, n_slots + 1, conv_dim, conv_kernel - 1, dtype=torch.float32, device=device)
         self.rec = torch.zeros(n_layers, n_slots + 1, n_v_heads, d, d, dtype=torch.float32, device=device)
         self.free = list(range(n_slots - 1, -1, -1))
+        self.stash: dict = {}                  # layer -> what a deferred (speculative) pass left for `commit`
+        self.stash_slots = None
+
+    def commit(self, n_rows: list[int]) -> None:
+        """After a deferred pass over R rows per sequence: advance every layer's state of sequence i by its first
+        ``n_rows[i]`` rows (the accepted ones) and drop the stash."""
+        from ..models.gdn import commit_rows
+        n = torch.tensor(n_rows, dtype=torch.int64)
+        for layer, st in self.stash.items():
+            commit_rows(st, self.conv[layer], self.rec[layer], self.stash_slots, n)
+        self.stash.clear()
+        self.stash_slots = None
 
     def alloc(self) -> int:
         if not self.free:
@@ -80,6 +92,18 @@ class HybridState:
     def release(self, slot: int) -> None:
         assert 0 <= slot < self.n_slots and slot not in self.free
         self.free.append(slot)
+
+    def snapshot(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Copy of one slot's state over all layers (kept by the prefix cache at a block boundary of a prompt)."""
+        return self.conv[:, slot].clone(), self.rec[:, slot].clone()
+
+    def restore(self, slot: int, snap: tuple[torch.Tensor, torch.Tensor]) -> None:
+        self.conv[:, slot].copy_(snap[0])
+        self.rec[:, slot].copy_(snap[1])
+
+    @property
+    def slot_bytes(self) -> int:
+        return 4 * (self.conv[:, 0].numel() + self.rec[:, 0].numel())
 
     @staticmethod
     def bytes_per_slot(n_layers: int, conv_dim: int, conv_kernel: int, n_v_heads: int, d: int) -> int:

@@ -214,6 +214,12 @@ class MTPDecoder:
         else:
             fbv = ForwardBatch(tokens=it(vt), positions=it(vp), seq_ids=it([i for i in range(B) for _ in range(R)]), block_table=bt,
                                cu_q=it([i * R for i in range(B + 1)]), ctx_lens=it([n0[i] - 1 for i in range(B)]), max_q_len=R)
+        hybrid = engine.kv.hybrid
+        if hybrid is not None:
+            # linear-attention layers: with drafts in flight the pass leaves the recurrent state alone and a stash behind;
+            # the state is advanced below by the accepted rows only
+            fbv.state_slots = it([r.slot for r in reqs])
+            fbv.defer_state = k > 0
         raw_logits, h = engine.model.forward(fbv, engine.kv)
         device_verify = (k > 0 and not sampling and engine.is_cuda and engine._sharded_vocab() and B * R <= engine._pairs.shape[0])
         logits = raw_logits if (k == 0 or device_verify) else engine._gather_vocab(raw_logits)
@@ -257,6 +263,8 @@ class MTPDecoder:
                 else:
                     out_tokens.append(out_host[i][:a + 1] if out_host is not None else tgt[i][:a + 1])
                 n_acc.append(a)
+        if hybrid is not None and k > 0:
+            hybrid.commit([a + 1 for a in n_acc])
         outs = []
         for i, r in enumerate(reqs):
             a = n_acc[i]

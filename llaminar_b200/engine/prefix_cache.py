@@ -9,6 +9,12 @@ page ids to the new sequence's page table and bumps reference counts.  Evicted p
 memory and optionally to disk, and are re-imported on a later hit.  A *terminal state* (first-token logits,
 final hidden row and a copy of the partial tail page) lets an exact repeat of a prompt skip the forward pass
 (reference: src/v2/execution/runner/OrchestrationRunner.cpp:1207-1214).
+
+Hybrid models (linear-attention layers with a recurrent state) can resume a cached prefix only where that state is
+known.  The engine snapshots it once per prompt, at the last block boundary that leaves a token to run, and a hit is cut
+back to the longest cached chain that ends at a boundary with a snapshot (`store_state`, `state_boundary`; the reference
+stores the hybrid state in its block payloads: src/v2/execution/prefix_cache/PrefixPayloadLayout.h).  A follow-up prompt
+that extends an earlier one (a chat turn) therefore reuses the earlier prompt up to that boundary.
 """
 from __future__ import annotations
 
@@ -69,24 +75,31 @@ class PrefixCache:
         self.ram: "OrderedDict[bytes, torch.Tensor]" = OrderedDict()    # hash -> pinned host payload
         self.disk: "OrderedDict[bytes, int]" = OrderedDict()            # hash -> bytes on disk
         self.terminal: "OrderedDict[bytes, TerminalState]" = OrderedDict()
+        self.states: "OrderedDict[bytes, tuple]" = OrderedDict()        # hash of the block that ends at a boundary -> state snapshot
+        self.max_states = 0
         self.engine = None
         self.page_bytes = 0
         self._stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "inserted_blocks": 0, "evicted_to_ram": 0,
-                       "evicted_to_disk": 0, "dropped": 0, "promoted": 0, "terminal_hits": 0, "terminal_stored": 0}
+                       "evicted_to_disk": 0, "dropped": 0, "promoted": 0, "terminal_hits": 0, "terminal_stored": 0,
+                       "state_snapshots": 0}
         self.file_prefix = self.salt.hex()[:8]           # completed by attach(): the shard of the cache this process holds
 
     # -- wiring ---------------------------------------------------------------------------------------------
     def attach(self, engine) -> None:
         self.engine = engine
         kv = engine.kv
-        self.page_bytes = kv.n_layers * 2 * kv.n_kv_heads * PAGE_SIZE * kv.head_dim * kv.layers[0].element_size()
+        el = kv.layers[0].element_size() if kv.layers else 2
+        self.page_bytes = kv.n_layers * 2 * kv.n_kv_heads * PAGE_SIZE * kv.head_dim * el
+        if kv.hybrid is not None:
+            # state snapshots live on the device; between 1 and 16 of them, within the device budget of the cache
+            self.max_states = max(1, min(16, self.cfg.vram_budget_mb * (1 << 20) // max(kv.hybrid.slot_bytes, 1)))
         # Disk-tier files are private to one shard of the cache: every rank of a multi-process engine holds other KV heads
         # (tensor parallelism) or other layers (pipeline stages) of the same block hash.  The file prefix therefore names
         # the model fingerprint AND this process's rank / world size and page geometry, so that a rank never reads a
         # payload that another rank, or an earlier run with another layout, wrote.
         import torch.distributed as dist
         rank, world = (dist.get_rank(), dist.get_world_size()) if dist.is_available() and dist.is_initialized() else (0, 1)
-        shard = f"{rank}/{world}/{kv.n_layers}/{kv.n_kv_heads}/{kv.head_dim}/{kv.layers[0].dtype}"
+        shard = f"{rank}/{world}/{kv.n_layers}/{kv.n_kv_heads}/{kv.head_dim}/{kv.layers[0].dtype if kv.layers else None}"
         self.file_prefix = self.salt.hex()[:8] + hashlib.blake2b(shard.encode(), digest_size=4).hexdigest()
         if self.cfg.disk_dir and self.cfg.disk_budget_mb > 0:
             os.makedirs(self.cfg.disk_dir, exist_ok=True)
@@ -113,6 +126,7 @@ class PrefixCache:
         self.device.clear()
         self.ram.clear()
         self.terminal.clear()
+        self.states.clear()
 
     # -- lookup -----------------------------------------------------------------------------------------------
     def lookup(self, prompt: list[int]) -> tuple[list[int], int]:
@@ -146,6 +160,33 @@ class PrefixCache:
             self._stats["hits"] += 1
             self._stats["hit_tokens"] += len(pages) * PAGE_SIZE
         return pages, len(pages) * PAGE_SIZE
+
+    # -- recurrent-state snapshots of hybrid models ----------------------------------------------------------
+    def store_state(self, prompt_prefix: list[int], snap: tuple) -> None:
+        """Keep the state a sequence has after exactly ``prompt_prefix`` (a whole number of blocks)."""
+        hs = chain_hashes(prompt_prefix, self.salt, self.cfg.block_size)
+        if not hs or len(prompt_prefix) % self.cfg.block_size or self.max_states == 0:
+            return
+        self.states[hs[-1]] = snap
+        self.states.move_to_end(hs[-1])
+        self._stats["state_snapshots"] += 1
+        while len(self.states) > self.max_states:
+            self.states.popitem(last=False)
+
+    def state_boundary(self, prompt: list[int], limit_tokens: int) -> int:
+        """Largest block boundary <= ``limit_tokens`` at which a snapshot of this prompt's state is held (0: none)."""
+        hs = chain_hashes(prompt[:limit_tokens - limit_tokens % self.cfg.block_size], self.salt, self.cfg.block_size)
+        for i in range(len(hs), 0, -1):
+            if hs[i - 1] in self.states:
+                return i * self.cfg.block_size
+        return 0
+
+    def state_at(self, prompt: list[int], n_tokens: int):
+        hs = chain_hashes(prompt[:n_tokens], self.salt, self.cfg.block_size)
+        snap = self.states.get(hs[-1]) if hs and n_tokens % self.cfg.block_size == 0 else None
+        if snap is not None:
+            self.states.move_to_end(hs[-1])
+        return snap
 
     def release_pages(self, pages: list[int]) -> None:
         """Drop the references `lookup` took on the caller's behalf."""

@@ -166,6 +166,16 @@ class TorchPagedModel:
 
     def _linear_attention(self, L, x, fb: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
         c, hs, gi = self.cfg, kv.hybrid, L["gdn_index"]
+        nv = self.plan.gdn_v_stop - self.plan.gdn_v_start
+        if fb.defer_state:                       # speculative verification: R rows per sequence, state committed afterwards
+            B = fb.state_slots.shape[0]
+            sh = lambda t: t.view(B, x.shape[0] // B, -1)
+            rows, hs.stash[gi] = gdn.gdn_rows_deferred(sh(x @ L["wqkv"].T), sh(x @ L["wz"].T), sh(x @ L["walpha"].T), sh(x @ L["wbeta"].T),
+                                                       L["conv_w"], L["ssm_a"], L["dt_bias"], L["ssm_norm"], hs.conv[gi], hs.rec[gi],
+                                                       fb.state_slots.long(), c.ssm_k_heads, nv, c.ssm_state, c.rms_eps,
+                                                       self.plan.gdn_v_start)
+            hs.stash_slots = fb.state_slots.long()
+            return rows @ L["wout"].T
         seqs = gdn.batch_sequences(fb.seq_ids, fb.positions, fb.state_slots)
         rows = gdn.gdn_block_rows(x @ L["wqkv"].T, x @ L["wz"].T, x @ L["walpha"].T, x @ L["wbeta"].T, seqs,
                                   hs.conv[gi], hs.rec[gi], L["conv_w"], L["ssm_a"], L["dt_bias"], L["ssm_norm"],

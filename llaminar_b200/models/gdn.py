@@ -140,3 +140,53 @@ def batch_sequences(seq_ids, positions, state_slots) -> list[tuple[int, int, int
             out.append((r0, r, slots[sid[r0]], pos[r0] == 0))
             r0 = r
     return out
+
+
+def gdn_rows_deferred(qkv, z, alpha, b, conv_w, ssm_a, dt_bias, norm_w, conv_pool, rec_pool, slots, n_k: int, n_v: int, d: int,
+                      eps: float, v_head_offset: int = 0):
+    """R new rows for each of B sequences (speculative verification) WITHOUT touching the state pools: the outputs are what
+    feeding the rows one by one would give, and the returned stash holds what `commit_rows` needs to advance each
+    sequence's state by however many of its rows are accepted afterwards (the per-row decay, key and correction, and the
+    convolution inputs), a few KB per row instead of a copy of the state per row.
+    qkv: [B, R, C], z: [B, R, n_v d], alpha, b: [B, R, n_v]; slots: [B] int64.  Returns (rows [B * R, n_v d] fp32, stash).
+    (reference: the verifier's state capture rows, src/v2/models/qwen35/Qwen35Graph.cpp:886-887.)"""
+    B, R, C = qkv.shape
+    K = conv_w.shape[1]
+    xp = torch.cat([conv_pool[slots].transpose(1, 2), qkv.float()], dim=1)                     # [B, K-1+R, C]
+    y = torch.zeros(B, R, C, dtype=torch.float32, device=qkv.device)
+    for j in range(K):
+        y += xp[:, j:j + R] * conv_w.float()[:, j]
+    y = F.silu(y)
+    q, k, v = torch.split(y, [n_k * d, n_k * d, n_v * d], dim=-1)
+    idx = (torch.arange(n_v, device=qkv.device) + v_head_offset) % n_k
+    q = (l2norm(q.view(B, R, n_k, d)) * d ** -0.5).index_select(2, idx)
+    k = l2norm(k.view(B, R, n_k, d)).index_select(2, idx)
+    v = v.view(B, R, n_v, d)
+    g, beta = gates(alpha, b, ssm_a, dt_bias)                                                 # [B, R, n_v]
+    S = rec_pool[slots].clone()                                                               # [B, n_v, d, d]
+    o = torch.empty(B, R, n_v, d, dtype=torch.float32, device=qkv.device)
+    u_all = torch.empty_like(o)
+    for j in range(R):
+        S = S * torch.exp(g[:, j])[:, :, None, None]
+        u = (v[:, j] - torch.einsum("bhkv,bhk->bhv", S, k[:, j])) * beta[:, j][..., None]
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, j], u)
+        o[:, j] = torch.einsum("bhkv,bhk->bhv", S, q[:, j])
+        u_all[:, j] = u
+    rows = gated_rmsnorm(o.view(B * R, n_v, d), z.reshape(B * R, n_v, d), norm_w, eps).reshape(B * R, n_v * d)
+    return rows, (g, k, u_all, xp)
+
+
+def commit_rows(stash, conv_pool, rec_pool, slots, n_rows) -> None:
+    """Advance the state of sequence i (slot ``slots[i]``) by its first ``n_rows[i]`` stashed rows (>= 1)."""
+    g, k, u, xp = stash
+    B, R = g.shape[:2]
+    Km1 = conv_pool.shape[-1]
+    S = rec_pool[slots]
+    n_rows = n_rows.to(g.device)
+    for j in range(R):
+        live = (n_rows > j)[:, None, None, None]
+        S = torch.where(live, S * torch.exp(g[:, j])[:, :, None, None] + torch.einsum("bhk,bhv->bhkv", k[:, j], u[:, j]), S)
+    rec_pool[slots] = S
+    # the convolution window ends at the last accepted row: inputs n .. n + K - 2 of xp (xp starts with the old window)
+    win = torch.stack([xp[i, int(n):int(n) + Km1] for i, n in enumerate(n_rows.tolist())])    # [B, K-1, C]
+    conv_pool[slots] = win.transpose(1, 2)

@@ -186,15 +186,57 @@ def test_engine_on_the_hybrid_model_matches_the_oracle_with_batching_and_chunked
     assert eng.kv.allocator.n_free == eng.kv.n_pages - 1
 
 
-def test_hybrid_model_rejects_prefix_cache_and_speculation_by_name():
+def test_hybrid_model_rejects_speculation_and_the_8bit_cache_by_name():
     from llaminar_b200.engine.engine import LLMEngine
     from llaminar_b200.engine.mtp import MTPDecoder
-    from llaminar_b200.engine.prefix_cache import PrefixCache
     w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
-    with pytest.raises(ValueError, match="prefix-cache"):
-        LLMEngine(w, device="cpu", max_batch=2, max_context=128, prefix_cache=PrefixCache())
     with pytest.raises(ValueError, match="mtp"):
         LLMEngine(w, device="cpu", max_batch=2, max_context=128, mtp=MTPDecoder())
+
+
+def _chat_turns(eng):
+    """Two 'turns': the second prompt extends the first prompt and its answer.  Returns both outputs."""
+    from llaminar_b200.engine.sampling import SamplingParams
+    p = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    first = _prompt(150, 21)
+    a = eng.generate([first], p)[0]
+    second = first + a + _prompt(40, 22)
+    return a, eng.generate([second], p)[0]
+
+
+def test_prefix_cache_resumes_a_hybrid_model_from_a_state_snapshot():
+    """The second prompt shares 156 tokens with the first request; the cached chain is cut back to the boundary where the
+    first prompt's recurrent state was snapshotted (128 = the last block boundary that left a token to run), the state
+    slot is restored from it, and the answers equal those of an engine without a cache."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.prefix_cache import PrefixCache
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    plain = _chat_turns(LLMEngine(w, device="cpu", max_batch=2, max_context=512, max_prefill_tokens=96))
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, max_prefill_tokens=96, prefix_cache=PrefixCache())
+    cached = _chat_turns(eng)
+    assert cached == plain
+    assert eng.stats["prefix_hit_tokens"] == 128
+    st = eng.prefix_cache.stats()
+    assert st["state_snapshots"] == 2 and st["terminal_stored"] == 0      # one per prompt (at 128 and at 192)
+    assert sorted(eng.kv.hybrid.free) == [0, 1]
+
+
+def _tp_chat(rank, world):
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.prefix_cache import PrefixCache
+    from llaminar_b200.parallel.tp import TPContext
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, tp=TPContext.create(device="cpu"), prefix_cache=PrefixCache())
+    return _chat_turns(eng), eng.stats["prefix_hit_tokens"]
+
+
+def test_tp2_ranks_agree_on_the_snapshot_boundary():
+    from llaminar_b200.engine.engine import LLMEngine
+    from tests.mp_utils import run_ranks
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    plain = _chat_turns(LLMEngine(w, device="cpu", max_batch=2, max_context=512))
+    res = run_ranks(_tp_chat, 2)
+    assert res[0] == (plain, 128) and res[1] == (plain, 128)
 
 
 def _tp_generate(rank, world):
@@ -291,3 +333,51 @@ def test_batched_paged_decode_attention_matches_a_per_sequence_loop():
         V = kv[bt[b].long(), 1].permute(1, 0, 2, 3).reshape(Hk, P * 64, D)[:, :n].repeat_interleave(H // Hk, 0)
         p = torch.softmax(torch.einsum("hd,hld->hl", q[b], K) * D ** -0.5, -1)
         assert torch.allclose(got[b], torch.einsum("hl,hld->hd", p, V), atol=1e-5)
+
+
+def test_deferred_rows_and_commit_equal_feeding_the_accepted_rows_one_by_one():
+    torch.manual_seed(0)
+    B, R, n_k, n_v, d, K = 3, 4, 2, 4, 16, 4
+    C = 2 * n_k * d + n_v * d
+    conv_w, ssm_a, dt, nw = torch.randn(C, K) * 0.4, -(torch.rand(n_v) * 3 + 0.2), torch.rand(n_v) * 2 - 1, torch.rand(d) + 0.5
+    conv, rec = torch.randn(6, C, K - 1) * 0.5, torch.randn(6, n_v, d, d) * 0.1
+    slots, acc = torch.tensor([4, 1, 2]), torch.tensor([1, 4, 2])
+    qkv, z, al, bb = torch.randn(B, R, C), torch.randn(B, R, n_v * d), torch.randn(B, R, n_v), torch.randn(B, R, n_v)
+    c2, r2 = conv.clone(), rec.clone()
+    rows, stash = gdn.gdn_rows_deferred(qkv, z, al, bb, conv_w, ssm_a, dt, nw, c2, r2, slots, n_k, n_v, d, 1e-6, 1)
+    assert torch.equal(c2, conv) and torch.equal(r2, rec)              # nothing committed yet
+    gdn.commit_rows(stash, c2, r2, slots, acc)
+    c3, r3 = conv.clone(), rec.clone()
+    for i in range(B):
+        s = int(slots[i])
+        for j in range(int(acc[i])):
+            o, c3[s] = gdn.gdn_mix(qkv[i, j:j + 1], z[i, j:j + 1], al[i, j:j + 1], bb[i, j:j + 1], conv_w, ssm_a, dt, nw,
+                                   c3[s], r3[s], n_k, n_v, d, 1e-6, 1)
+            assert torch.allclose(o[0], rows[i * R + j], atol=1e-5)
+    assert torch.allclose(c2, c3, atol=1e-6) and torch.allclose(r2, r3, atol=1e-6)
+
+
+@pytest.mark.parametrize("force", [False, True], ids=["verified", "all-drafts-accepted"])
+def test_speculative_decoding_on_the_hybrid_model(force):
+    """NextN drafts verified by the hybrid trunk: the verification pass leaves the recurrent state alone and it is advanced
+    by the accepted rows only.  Verified drafts must reproduce plain greedy decoding token for token; with every draft
+    force-accepted (a throughput switch, not lossless) the state must still advance by all rows, which the run's length
+    and the returned slots show."""
+    import dataclasses
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.mtp import MTPConfig, MTPDecoder
+    from llaminar_b200.engine.sampling import SamplingParams
+    cfg = dataclasses.replace(SHAPES["tiny-qwen35"], nextn_layers=1, name="tiny-qwen35-mtp")
+    w = synthesize(cfg, "Q8_0", seed=9)
+    prompts = [_prompt(40, 3), _prompt(70, 4)]
+    p = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = LLMEngine(w, device="cpu", max_batch=2, max_context=256).generate(prompts, p)
+    dec = MTPDecoder(MTPConfig(draft_tokens=2, force_accept=force))
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=256, mtp=dec)
+    got = eng.generate(prompts, p)
+    assert all(len(o) == 12 for o in got)
+    if not force:
+        assert got == plain
+    st = dec.stats()
+    assert st["drafted"] > 0 and (st["accepted"] == st["drafted"] if force else True)
+    assert sorted(eng.kv.hybrid.free) == [0, 1] and not eng.kv.hybrid.stash
