@@ -112,9 +112,17 @@ class ModelConfig:
             raise ValueError(f"unsupported GGUF architecture '{arch}' (supported: {', '.join(SUPPORTED_ARCHS)}; "
                              "qwen35 / qwen35moe are the hybrid Gated-DeltaNet families)")
         a = gf.arch_key
+
+        def scalar(v):
+            """Hybrid checkpoints may store per-layer arrays (0 for the linear-attention layers): the softmax blocks' value."""
+            if isinstance(v, (list, tuple)):
+                vals = [int(x) for x in v if int(x) > 0]
+                return max(vals) if vals else 0
+            return v
+
         d_model = int(a("embedding_length"))
-        n_heads = int(a("attention.head_count"))
-        n_kv = int(a("attention.head_count_kv", n_heads))
+        n_heads = int(scalar(a("attention.head_count")))
+        n_kv = int(scalar(a("attention.head_count_kv", n_heads)))
         head_dim = int(a("attention.key_length", d_model // n_heads))
         tokens = gf.get("tokenizer.ggml.tokens")
         if tokens is not None:
@@ -143,7 +151,7 @@ class ModelConfig:
             n_heads=n_heads,
             n_kv_heads=n_kv,
             head_dim=head_dim,
-            d_ff=int(a("feed_forward_length", 0) or 0),
+            d_ff=int(scalar(a("feed_forward_length", 0)) or 0),
             vocab_size=vocab,
             rope_theta=float(a("rope.freq_base", 10000.0)),
             rms_eps=float(a("attention.layer_norm_rms_epsilon", 1e-6)),

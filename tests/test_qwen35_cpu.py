@@ -381,3 +381,16 @@ def test_speculative_decoding_on_the_hybrid_model(force):
     st = dec.stats()
     assert st["drafted"] > 0 and (st["accepted"] == st["drafted"] if force else True)
     assert sorted(eng.kv.hybrid.free) == [0, 1] and not eng.kv.hybrid.stash
+
+
+def test_per_layer_head_count_arrays_in_gguf_metadata_are_accepted(tmp_path):
+    """Converters of hybrid checkpoints may write `attention.head_count_kv` (and the FFN width) as one entry per layer, with
+    0 for the linear-attention layers; the configuration takes the softmax blocks' value."""
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=2)
+    path = str(tmp_path / "arr.gguf")
+    c = w.config
+    per_layer = [0 if c.is_gdn_layer(i) else c.n_kv_heads for i in range(c.n_layers)]
+    w.save_gguf(path, extra_metadata={"qwen35.attention.head_count_kv": per_layer,
+                                      "qwen35.feed_forward_length": [c.d_ff] * c.n_layers})
+    back = ModelWeights.from_gguf(path).config
+    assert back.n_kv_heads == c.n_kv_heads and back.d_ff == c.d_ff and back.full_attention_interval == 4
