@@ -133,9 +133,8 @@ def build_engine(cfg: OrchestrationConfig):
         log.info("placement\n%s", plan.table())
     if mcfg.is_hybrid:
         # the gated attention blocks append bf16 K/V
-        bad = [f for f, on in (("--kv-cache-precision q8_0", v.get("kv_cache_precision") in ("q8_0", "q8_1"))) if on]
-        if bad:
-            raise ConfigError([f"{f} is not available for hybrid (linear-attention) models such as {mcfg.arch}" for f in bad])
+        if v.get("kv_cache_precision") in ("q8_0", "q8_1"):
+            raise ConfigError([f"--kv-cache-precision q8_0 is not available for hybrid (linear-attention) models such as {mcfg.arch}"])
     prefix = None
     if v.get("prefix_cache"):
         prefix = PrefixCache(PrefixCacheConfig.from_values(v), fingerprint=_fingerprint(mcfg, layout, v))

@@ -139,10 +139,12 @@ def test_text_completion_endpoint(server):
     assert st == 400
 
 
-def test_serve_process_end_to_end(tmp_path):
+@pytest.mark.parametrize("shape,flags", [("tiny-qwen3", []), ("tiny-qwen35", ["--prefix-cache"])], ids=["dense", "hybrid-with-prefix-cache"])
+def test_serve_process_end_to_end(tmp_path, shape, flags):
     """The `serve` command as a separate process: wait for /health, one chat completion, one streamed completion, a
     long prompt, then SIGTERM and a clean exit (the reference drives its server the same way from a shell script:
-    tests/v2/e2e/server/test_server_e2e.sh)."""
+    tests/v2/e2e/server/test_server_e2e.sh).  Once for a dense model, once for a hybrid linear-attention model with the
+    prefix cache on (state slots and snapshots behind the same API)."""
     import http.client
     import json
     import signal
@@ -155,8 +157,8 @@ def test_serve_process_end_to_end(tmp_path):
     port = s.getsockname()[1]
     s.close()
     log = open(tmp_path / "serve.log", "w")
-    proc = subprocess.Popen([sys.executable, "-m", "llaminar_b200", "serve", "--synthetic", "tiny-qwen3", "--synthetic-recipe", "Q8_0",
-                             "-d", "cpu", "--host", "127.0.0.1", "--port", str(port), "-c", "512"], stdout=log, stderr=subprocess.STDOUT)
+    proc = subprocess.Popen([sys.executable, "-m", "llaminar_b200", "serve", "--synthetic", shape, "--synthetic-recipe", "Q8_0",
+                             "-d", "cpu", "--host", "127.0.0.1", "--port", str(port), "-c", "512"] + flags, stdout=log, stderr=subprocess.STDOUT)
     try:
         deadline = time.time() + 120
         ready = False
