@@ -394,3 +394,22 @@ def test_per_layer_head_count_arrays_in_gguf_metadata_are_accepted(tmp_path):
                                       "qwen35.feed_forward_length": [c.d_ff] * c.n_layers})
     back = ModelWeights.from_gguf(path).config
     assert back.n_kv_heads == c.n_kv_heads and back.d_ff == c.d_ff and back.full_attention_interval == 4
+
+
+def test_preemption_on_the_hybrid_model_gives_the_slot_back_and_recomputes_the_state():
+    """A cache that holds about half of three long generations: preempted sequences return their pages and their state slot,
+    come back with their tokens folded into the prompt, and the prefill that rebuilds their K/V rebuilds the recurrent
+    state from position 0; outputs equal those of an engine with room for everything."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    prompts = [_prompt(60, s) for s in (1, 2, 3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=120, ignore_eos=True)
+    want = LLMEngine(w, device="cpu", max_batch=3, max_context=256).generate(prompts, sp)
+    small = LLMEngine(w, device="cpu", max_batch=3, max_context=256, kv_pages=7)          # 6 usable pages of 64 tokens
+    reqs = [small.add_request(p, sp) for p in prompts]
+    while small.has_unfinished():
+        small.step()
+    assert small.stats["preemptions"] >= 1
+    assert [r.output for r in reqs] == want
+    assert small.kv.allocator.n_free == small.kv.n_pages - 1 and sorted(small.kv.hybrid.free) == [0, 1, 2]
