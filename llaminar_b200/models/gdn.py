@@ -120,14 +120,45 @@ def gdn_block_rows(qkv, z, alpha, b, seqs, conv_pool, rec_pool, conv_w, ssm_a, d
                    eps: float, v_head_offset: int = 0) -> torch.Tensor:
     """The linear-attention mix for a packed batch.  ``seqs``: (first row, end row, state slot, fresh) per sequence, rows of
     a sequence being consecutive; ``fresh`` sequences start from a zero state.  conv_pool [slots, C, K-1] and
-    rec_pool [slots, n_v, d, d] are one layer's state pools and are updated.  Returns fp32 rows [T, n_v d]."""
+    rec_pool [slots, n_v, d, d] are one layer's state pools and are updated.  Returns fp32 rows [T, n_v d].
+    Sequences with the same number of rows (the usual prefill batch of equal prompts or equal chunks) are evaluated
+    together, their heads stacked into one batch axis, so the number of small launches does not grow with the batch."""
     out = torch.empty(qkv.shape[0], n_v * d, dtype=torch.float32, device=qkv.device)
-    for r0, r1, slot, fresh in seqs:
-        if fresh:
-            conv_pool[slot].zero_()
-            rec_pool[slot].zero_()
-        out[r0:r1], conv_pool[slot] = gdn_mix(qkv[r0:r1], z[r0:r1], alpha[r0:r1], b[r0:r1], conv_w, ssm_a, dt_bias, norm_w,
-                                             conv_pool[slot], rec_pool[slot], n_k, n_v, d, eps, v_head_offset)
+    by_len: dict[int, list] = {}
+    for sq in seqs:
+        if sq[3]:
+            conv_pool[sq[2]].zero_()
+            rec_pool[sq[2]].zero_()
+        by_len.setdefault(sq[1] - sq[0], []).append(sq)
+    for T, group in by_len.items():
+        if len(group) == 1 or T <= 4:
+            for r0, r1, slot, _ in group:
+                out[r0:r1], conv_pool[slot] = gdn_mix(qkv[r0:r1], z[r0:r1], alpha[r0:r1], b[r0:r1], conv_w, ssm_a, dt_bias, norm_w,
+                                                     conv_pool[slot], rec_pool[slot], n_k, n_v, d, eps, v_head_offset)
+            continue
+        G = len(group)
+        rows = torch.cat([torch.arange(r0, r1, device=qkv.device) for r0, r1, _, _ in group])
+        slots = torch.tensor([sq[2] for sq in group], device=qkv.device)
+        pick = lambda t: t.index_select(0, rows).float().view(G, T, -1)
+        x, K = pick(qkv), conv_w.shape[1]
+        xp = torch.cat([conv_pool[slots].transpose(1, 2), x], dim=1)                          # [G, K-1+T, C]
+        y = torch.zeros_like(x)
+        for j in range(K):
+            y += xp[:, j:j + T] * conv_w.float()[:, j]
+        conv_pool[slots] = xp[:, T:].transpose(1, 2)
+        q, k, v = torch.split(F.silu(y), [n_k * d, n_k * d, n_v * d], dim=-1)
+        idx = (torch.arange(n_v, device=qkv.device) + v_head_offset) % n_k
+        # [G, T, heads, d] -> [T, G * n_v, d]: every (sequence, value head) is one row of the batch axis of the chunk form
+        fold = lambda t: t.permute(1, 0, 2, 3).reshape(T, G * n_v, d)
+        q = fold((l2norm(q.view(G, T, n_k, d)) * d ** -0.5).index_select(2, idx))
+        k = fold(l2norm(k.view(G, T, n_k, d)).index_select(2, idx))
+        g, beta = gates(pick(alpha), pick(b), ssm_a, dt_bias)                                 # [G, T, n_v]
+        S = rec_pool[slots].reshape(G * n_v, d, d)
+        o = delta_rule_chunked(q, k, fold(v.view(G, T, n_v, d)), g.permute(1, 0, 2).reshape(T, G * n_v),
+                               beta.permute(1, 0, 2).reshape(T, G * n_v), S)
+        rec_pool[slots] = S.view(G, n_v, d, d)
+        o = o.view(T, G, n_v, d).permute(1, 0, 2, 3).reshape(G * T, n_v, d)
+        out[rows] = gated_rmsnorm(o, pick(z).reshape(G * T, n_v, d), norm_w, eps).reshape(G * T, n_v * d)
     return out
 
 

@@ -413,3 +413,27 @@ def test_preemption_on_the_hybrid_model_gives_the_slot_back_and_recomputes_the_s
     assert small.stats["preemptions"] >= 1
     assert [r.output for r in reqs] == want
     assert small.kv.allocator.n_free == small.kv.n_pages - 1 and sorted(small.kv.hybrid.free) == [0, 1, 2]
+
+
+def test_equal_length_sequences_evaluated_together_match_one_at_a_time():
+    """A packed prefill batch with three 70-row sequences (one of them continuing from an earlier state), one 9-row and one
+    3-row sequence: the grouped evaluation must equal running every sequence alone."""
+    torch.manual_seed(4)
+    n_k, n_v, d, K = 2, 4, 16, 4
+    C = 2 * n_k * d + n_v * d
+    conv_w, ssm_a, dt, nw = torch.randn(C, K) * 0.4, -(torch.rand(n_v) * 3 + 0.2), torch.rand(n_v) * 2 - 1, torch.rand(d) + 0.5
+    conv, rec = torch.randn(7, C, K - 1) * 0.5, torch.randn(7, n_v, d, d) * 0.1
+    lens, slots, fresh = [70, 9, 70, 3, 70], [5, 0, 2, 6, 1], [True, True, False, False, True]
+    T = sum(lens)
+    qkv, z, al, bb = torch.randn(T, C), torch.randn(T, n_v * d), torch.randn(T, n_v), torch.randn(T, n_v)
+    seqs, r0 = [], 0
+    for n, s, f in zip(lens, slots, fresh):
+        seqs.append((r0, r0 + n, s, f))
+        r0 += n
+    c1, r1 = conv.clone(), rec.clone()
+    got = gdn.gdn_block_rows(qkv, z, al, bb, seqs, c1, r1, conv_w, ssm_a, dt, nw, n_k, n_v, d, 1e-6, 1)
+    c2, r2 = conv.clone(), rec.clone()
+    want = torch.cat([gdn.gdn_block_rows(qkv[a:b_], z[a:b_], al[a:b_], bb[a:b_], [(0, b_ - a, s, f)], c2, r2, conv_w, ssm_a, dt, nw,
+                                         n_k, n_v, d, 1e-6, 1) for a, b_, s, f in seqs])
+    assert torch.allclose(got, want, atol=2e-5)
+    assert torch.allclose(c1, c2, atol=1e-6) and torch.allclose(r1, r2, atol=2e-5)
