@@ -437,3 +437,24 @@ def test_equal_length_sequences_evaluated_together_match_one_at_a_time():
                                          n_k, n_v, d, 1e-6, 1) for a, b_, s, f in seqs])
     assert torch.allclose(got, want, atol=2e-5)
     assert torch.allclose(c1, c2, atol=1e-6) and torch.allclose(r1, r2, atol=2e-5)
+
+
+def test_parity_report_and_memory_plan_cover_hybrid_models():
+    """The layer-by-layer parity tool runs a hybrid model (it owns one state slot), and the memory planner counts the
+    recurrent state of every batch lane and KV pages for the softmax blocks only."""
+    from llaminar_b200.parity import compare
+    from llaminar_b200.planning import build_plan
+    rows, failed = compare(synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=1), "cpu", prompt_tokens=40, decode_steps=2)
+    assert not failed and sum(r["stage"] == "logits" for r in rows) == 3
+    lay = {"pp": 1, "tp": 2, "world": 2, "stages": [("s0", ["cuda:0", "cuda:1"], 0, -1)]}
+    cfg = SHAPES["qwen3.5-27b"]
+    plan = build_plan(cfg, lay, "Q4_K_M", ctx_size=8192, batch_size=32)
+    assert not plan.errors
+    r0 = plan.ranks[0]
+    pages = 32 * (8192 // 64 + 1) + 64
+    kv_only = pages * 16 * 2 * 2 * 64 * 256 * 2                       # 16 softmax blocks, 2 of 4 KV heads per rank
+    state = 33 * 4 * 48 * ((2 * 2048 + 24 * 128) * 3 + 24 * 128 * 128)  # 33 slots, 48 blocks, 24 value heads per rank
+    assert r0.kv_bytes == kv_only + state
+    # the dense 32B shape at the same settings holds four times the KV layers
+    dense = build_plan(SHAPES["qwen3-32b"], lay, "Q4_K_M", ctx_size=8192, batch_size=32).ranks[0]
+    assert dense.kv_bytes > r0.kv_bytes - state
