@@ -46,6 +46,9 @@ MODEL_DEFAULTS = {
     "qwen3": dict(temperature=0.6, top_p=0.95, top_k=20, presence_penalty=1.5),
     "qwen3moe": dict(temperature=0.6, top_p=0.95, top_k=20, presence_penalty=1.5),
     "qwen2": dict(temperature=0.7, top_p=0.8, top_k=20, presence_penalty=0.0),
+    # the hybrid families' recommended values (reference: src/v2/models/qwen35/Qwen35Schema.h:64-67)
+    "qwen35": dict(temperature=0.6, top_p=0.95, top_k=20, presence_penalty=1.5),
+    "qwen35moe": dict(temperature=0.6, top_p=0.95, top_k=20, presence_penalty=1.5),
 }
 
 
