@@ -283,7 +283,8 @@ def log(msg: str) -> None:
 
 
 T_START = time.time()
-MODEL_DEFAULTS = {"qwen3-8b": ("Q4_K_M", 2048), "qwen3-32b": ("Q4_K_S", 1024)}
+MODEL_DEFAULTS = {"qwen3-8b": ("Q4_K_M", 2048), "qwen3-32b": ("Q4_K_S", 1024),
+                  "qwen3.5-27b": ("Q4_K_M", 512), "qwen3.5-35b-a3b": ("Q4_K_M", 512)}      # the hybrid shapes (--model ...)
 
 
 def measure(model_name: str, recipe: str, S: int, args, tp, dev, world: int, rank: int, local: int, extras_on: bool) -> dict:
