@@ -1,0 +1,95 @@
+"""Hugging Face checkpoint -> GGUF conversion: for every family the engine runs, a tiny random model saved with
+`save_pretrained` is converted, loaded back from the GGUF file and run through the fp32 oracle; logits must equal the
+`transformers` model's.  Plus the tokenizer carry-over."""
+import json
+
+import pytest
+import torch
+
+from llaminar_b200.models.convert_hf import config_from_hf, convert_directory, tokenizer_metadata
+from llaminar_b200.models.reference import ReferenceModel
+from llaminar_b200.models.weights import ModelWeights
+
+tf = pytest.importorskip("transformers")
+
+
+def _tiny(family: str):
+    common = dict(hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, vocab_size=128,
+                  max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    hybrid = dict(head_dim=32, layer_types=["linear_attention"] * 3 + ["full_attention"], full_attention_interval=4,
+                  linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+                  linear_conv_kernel_dim=4,
+                  rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25, "mrope_section": [2, 1, 1]})
+    try:
+        if family == "qwen2":
+            from transformers import Qwen2Config, Qwen2ForCausalLM
+            return Qwen2ForCausalLM(Qwen2Config(**common, intermediate_size=128))
+        if family == "qwen3":
+            from transformers import Qwen3Config, Qwen3ForCausalLM
+            return Qwen3ForCausalLM(Qwen3Config(**common, head_dim=16, intermediate_size=128))
+        if family == "qwen3_moe":
+            from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+            return Qwen3MoeForCausalLM(Qwen3MoeConfig(**common, head_dim=16, intermediate_size=128, moe_intermediate_size=32, num_experts=6,
+                                                      num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]))
+        if family == "qwen3_5":
+            from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM, Qwen3_5TextConfig
+            return Qwen3_5ForCausalLM(Qwen3_5TextConfig(**common, **hybrid, intermediate_size=128))
+        from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM, Qwen3_5MoeTextConfig
+        return Qwen3_5MoeForCausalLM(Qwen3_5MoeTextConfig(**common, **hybrid, num_experts=6, num_experts_per_tok=2,
+                                                          moe_intermediate_size=32, shared_expert_intermediate_size=48))
+    except ImportError as e:
+        pytest.skip(f"this transformers has no {family}: {e}")
+
+
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe"])
+def test_converted_checkpoint_reproduces_the_transformers_logits(family, tmp_path):
+    torch.manual_seed(7)
+    m = _tiny(family).float().eval()
+    m.config._attn_implementation = "eager"
+    with torch.no_grad():
+        for n, p in m.named_parameters():                       # nothing left at its constructor value (zeros, ones, empty)
+            p.copy_(torch.randn_like(p) * (0.3 if p.dim() == 1 else 0.08))
+            if n.endswith("A_log"):
+                p.copy_(torch.log(torch.rand_like(p) * 6 + 0.5))
+    src, out = tmp_path / "hf", str(tmp_path / "m.gguf")
+    m.save_pretrained(src, safe_serialization=True)
+    convert_directory(str(src), out, "F32")
+    w = ModelWeights.from_gguf(out)
+    assert w.config.arch == {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe", "qwen3_5": "qwen35", "qwen3_5_moe": "qwen35moe"}[family]
+    toks = torch.randint(0, 128, (33,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = m(input_ids=toks[None]).logits[0]
+    got, _, _ = ReferenceModel(w).forward(toks)
+    assert (got - want).abs().max() < 3e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_quantised_recipe_and_config_mapping(tmp_path):
+    m = _tiny("qwen3_5").float().eval()
+    src, out = tmp_path / "hf", str(tmp_path / "q.gguf")
+    m.save_pretrained(src, safe_serialization=True)
+    w = convert_directory(str(src), out, "Q8_0")
+    assert w["blk.0.attn_qkv.weight"].qtype.name == "Q8_0" and w["blk.0.ssm_a"].qtype.name == "F32"
+    c = config_from_hf(json.load(open(src / "config.json")))
+    assert (c.full_attention_interval, c.ssm_k_heads, c.ssm_v_heads, c.ssm_state, c.rope_dim, c.attn_gate) == (4, 2, 4, 16, 8, True)
+    with pytest.raises(ValueError, match="model_type"):
+        config_from_hf({"model_type": "llama"})
+
+
+def test_tokenizer_files_become_gguf_tokenizer_metadata(tmp_path):
+    from llaminar_b200.tokenizer.bpe import BPETokenizer, byte_alphabet
+    alpha = byte_alphabet()
+    vocab = {alpha[b]: b for b in range(256)}
+    he = alpha[ord("h")] + alpha[ord("e")]
+    vocab[he] = 256
+    tj = {"model": {"type": "BPE", "vocab": vocab, "merges": [[alpha[ord("h")], alpha[ord("e")]]]},
+          "added_tokens": [{"id": 257, "content": "<|im_end|>", "special": True}, {"id": 259, "content": "<tool>", "special": False}]}
+    json.dump(tj, open(tmp_path / "tokenizer.json", "w"))
+    json.dump({"eos_token": {"content": "<|im_end|>"}, "chat_template": "{{ messages }}"}, open(tmp_path / "tokenizer_config.json", "w"))
+    md = tokenizer_metadata(str(tmp_path))
+    assert len(md["tokenizer.ggml.tokens"]) == 260 and md["tokenizer.ggml.token_type"][257] == 3
+    assert md["tokenizer.ggml.token_type"][258] == 5 and md["tokenizer.ggml.token_type"][259] == 4
+    assert md["tokenizer.ggml.eos_token_id"] == 257 and md["tokenizer.chat_template"] == "{{ messages }}"
+    tok = BPETokenizer.from_metadata(md)
+    ids = tok.encode("hehe<|im_end|>")
+    assert ids == [256, 256, 257] and tok.decode(ids[:2]) == "hehe"
+    assert tokenizer_metadata(str(tmp_path / "nowhere")) == {}
