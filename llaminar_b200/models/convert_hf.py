@@ -1,6 +1,7 @@
 """Hugging Face checkpoint (config.json + *.safetensors) -> GGUF, for the families this engine runs.
 
     python -m llaminar_b200.models.convert_hf <model directory> <out.gguf> [--recipe Q4_K_M]
+    python -m llaminar_b200.models.convert_hf <in.gguf> <out.gguf> --recipe Q4_K_M        # re-encode an existing GGUF file
 
 Tensor names, metadata keys and storage conventions are the ones GGUF files of these families use (and the loader here and
 the reference expect: src/v2/models/qwen/Qwen2Schema.h, src/v2/models/qwen35/Qwen35Schema.h:107-134,
@@ -209,6 +210,21 @@ def load_checkpoint(model_dir: str) -> tuple[dict, dict]:
     return hf, sd
 
 
+def requantize(w: ModelWeights, recipe: QuantRecipe | str) -> ModelWeights:
+    """The same checkpoint with every matrix re-encoded to ``recipe`` (decode, then encode; vectors and metadata are kept).
+    Going from a coarser to a finer format does not bring precision back."""
+    if isinstance(recipe, str):
+        recipe = RECIPES[recipe]
+    cfg, out = w.config, {}
+    for name, t in w.tensors.items():
+        layer = int(name.split(".")[1]) if name.startswith("blk.") else None
+        if len(t.shape) < 2 or "ssm_conv1d" in name:
+            out[name] = t
+        else:
+            out[name] = t.transcoded(_fit(recipe.for_tensor(name, layer, cfg.n_layers), t.shape[-1]))
+    return ModelWeights(cfg, out, dict(w.metadata))
+
+
 def convert_directory(model_dir: str, out_path: str, recipe: str = "Q8_0") -> ModelWeights:
     hf, sd = load_checkpoint(model_dir)
     cfg = config_from_hf(hf)
@@ -224,7 +240,11 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("out")
     ap.add_argument("--recipe", default="Q8_0", choices=sorted(RECIPES))
     a = ap.parse_args(argv)
-    w = convert_directory(a.model_dir, a.out, a.recipe)
+    if os.path.isfile(a.model_dir):
+        w = requantize(ModelWeights.from_gguf(a.model_dir), a.recipe)
+        w.save_gguf(a.out)
+    else:
+        w = convert_directory(a.model_dir, a.out, a.recipe)
     c = w.config
     print(f"{a.out}: {c.arch}, {c.n_layers} layers, d={c.d_model}, {len(w.tensors)} tensors, {w.nbytes() / 1e9:.2f} GB ({a.recipe})")
     return 0

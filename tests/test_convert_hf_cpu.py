@@ -93,3 +93,20 @@ def test_tokenizer_files_become_gguf_tokenizer_metadata(tmp_path):
     ids = tok.encode("hehe<|im_end|>")
     assert ids == [256, 256, 257] and tok.decode(ids[:2]) == "hehe"
     assert tokenizer_metadata(str(tmp_path / "nowhere")) == {}
+
+
+def test_requantising_a_gguf_file_keeps_the_model_function(tmp_path):
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.convert_hf import main
+    from llaminar_b200.models.synth import synthesize
+    src, dst = str(tmp_path / "a.gguf"), str(tmp_path / "b.gguf")
+    w = synthesize(SHAPES["tiny-qwen35"], "F32", seed=3)
+    w.save_gguf(src)
+    assert main([src, dst, "--recipe", "Q8_0"]) == 0
+    back = ModelWeights.from_gguf(dst)
+    assert back["blk.0.attn_qkv.weight"].qtype.name == "Q8_0" and back["blk.0.ssm_conv1d.weight"].qtype.name == "F32"
+    assert back.metadata.get("tokenizer.ggml.model") == "gpt2"
+    toks = torch.randint(0, 1024, (24,), generator=torch.Generator().manual_seed(2))
+    a, _, _ = ReferenceModel(w).forward(toks)
+    b, _, _ = ReferenceModel(back).forward(toks)
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.995      # Q8_0 rounding through eight blocks
