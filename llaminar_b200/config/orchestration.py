@@ -100,6 +100,9 @@ OPTIONS: list[OptionSpec] = [
     _o("--prefix-cache-disk-budget-mb", type=int, default=0, category="prefix-cache"),
     _o("--prefix-cache-disk-dir", category="prefix-cache"),
     _o("--prefix-cache-terminal-state", default="auto", choices=("off", "auto", "always"), category="prefix-cache"),
+    _o("--prefix-cache-state-stride", type=int, default=0, category="prefix-cache",
+       help="hybrid models: also snapshot the recurrent state every N prompt tokens (a multiple of the block size; 0 = only at "
+            "the last block boundary of a prompt), so that prompts sharing a shorter prefix can resume from it"),
     _o("--prefix-cache-moe-policy", default="placement-fingerprint",
        choices=("disabled", "placement-fingerprint", "invalidate-on-rebalance"), category="prefix-cache"),
     # -- MTP / speculative decode -----------------------------------------------------------------------------

@@ -650,10 +650,9 @@ class LLMEngine:
                 final_logits[r.rid], final_hidden[r.rid] = r.terminal.logits, r.terminal.hidden
         # hybrid models with a prefix cache: one snapshot of the linear-attention state per prompt, at the last block boundary
         # that leaves a token to run (where a follow-up prompt that extends this one can resume)
-        snap_at = {}
+        snap_at: dict[int, list[int]] = {}
         if self.prefix_cache is not None and self.kv.hybrid is not None:
-            snap_at = {r.rid: (len(r.prompt) - 1) // PAGE_SIZE * PAGE_SIZE for r in batch}
-            snap_at = {rid: b for rid, b in snap_at.items() if b > pending[rid]}
+            snap_at = {r.rid: self.prefix_cache.snapshot_points(len(r.prompt), pending[r.rid]) for r in batch}
         while any(pending[r.rid] < len(r.prompt) for r in batch):
             toks, pos, sid, cu, ctx, rows_for, chunks = [], [], [], [0], [], [], []
             budget = self.max_prefill_tokens
@@ -663,8 +662,9 @@ class LLMEngine:
                 if done >= len(r.prompt) or budget <= 0:
                     continue
                 n = min(len(r.prompt) - done, budget)
-                if snap_at.get(r.rid, 0) > done:            # a chunk ends where the prefix cache wants the recurrent state
-                    n = min(n, snap_at[r.rid] - done)
+                nxt = next((b for b in snap_at.get(r.rid, ()) if b > done), None)
+                if nxt is not None:                          # a chunk ends where the prefix cache wants the recurrent state
+                    n = min(n, nxt - done)
                 budget -= n
                 b = len(ctx)
                 toks.extend(r.prompt[done:done + n])
@@ -689,7 +689,7 @@ class LLMEngine:
                               state_slots=it([r.slot for r, _, _ in chunks]) if self.kv.hybrid is not None else None)
             logits, h = self.model.forward(fb, self.kv, want_logits=bool(logit_rows))
             for r, done, n in chunks:
-                if snap_at.get(r.rid) == done + n:
+                if done + n in snap_at.get(r.rid, ()):
                     self.prefix_cache.store_state(r.prompt[:done + n], self.kv.hybrid.snapshot(r.slot))
             if self.mtp is not None:
                 keep = {r.rid: h[row].clone() for r, row in rows_for if row is not None}

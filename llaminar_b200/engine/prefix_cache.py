@@ -39,13 +39,15 @@ class PrefixCacheConfig:
     disk_dir: str | None = None
     terminal_state: str = "auto"         # off | auto | always
     moe_policy: str = "placement-fingerprint"
+    state_stride: int = 0                # hybrid models: extra recurrent-state snapshots every this many prompt tokens (0: none)
 
     @staticmethod
     def from_values(v: dict) -> "PrefixCacheConfig":
         return PrefixCacheConfig(v.get("prefix_cache_storage", "tiered"), int(v.get("prefix_cache_block_size", 64)),
                                  int(v.get("prefix_cache_vram_budget_mb", 256)), int(v.get("prefix_cache_ram_budget_mb", 4096)),
                                  int(v.get("prefix_cache_disk_budget_mb", 0)), v.get("prefix_cache_disk_dir"),
-                                 v.get("prefix_cache_terminal_state", "auto"), v.get("prefix_cache_moe_policy", "placement-fingerprint"))
+                                 v.get("prefix_cache_terminal_state", "auto"), v.get("prefix_cache_moe_policy", "placement-fingerprint"),
+                                 int(v.get("prefix_cache_state_stride") or 0))
 
 
 def chain_hashes(tokens: list[int], salt: bytes, block: int = PAGE_SIZE) -> list[bytes]:
@@ -91,8 +93,8 @@ class PrefixCache:
         el = kv.layers[0].element_size() if kv.layers else 2
         self.page_bytes = kv.n_layers * 2 * kv.n_kv_heads * PAGE_SIZE * kv.head_dim * el
         if kv.hybrid is not None:
-            # state snapshots live on the device; between 1 and 16 of them, within the device budget of the cache
-            self.max_states = max(1, min(16, self.cfg.vram_budget_mb * (1 << 20) // max(kv.hybrid.slot_bytes, 1)))
+            # state snapshots live on the device; between 1 and 64 of them, within the device budget of the cache
+            self.max_states = max(1, min(64, self.cfg.vram_budget_mb * (1 << 20) // max(kv.hybrid.slot_bytes, 1)))
         # Disk-tier files are private to one shard of the cache: every rank of a multi-process engine holds other KV heads
         # (tensor parallelism) or other layers (pipeline stages) of the same block hash.  The file prefix therefore names
         # the model fingerprint AND this process's rank / world size and page geometry, so that a rank never reads a
@@ -172,6 +174,18 @@ class PrefixCache:
         self._stats["state_snapshots"] += 1
         while len(self.states) > self.max_states:
             self.states.popitem(last=False)
+
+    def snapshot_points(self, n_prompt: int, done: int) -> list[int]:
+        """Where prefill of an ``n_prompt``-token prompt, ``done`` tokens of which are cached already, should leave a snapshot:
+        the last block boundary that leaves a token to run, and every `state_stride` tokens before it."""
+        if self.max_states == 0:
+            return []
+        blk = self.cfg.block_size
+        last = (n_prompt - 1) // blk * blk
+        stride = self.cfg.state_stride // blk * blk
+        pts = set(range(stride, last + 1, stride)) if stride > 0 else set()
+        pts.add(last)
+        return sorted(p for p in pts if p > done)
 
     def state_boundary(self, prompt: list[int], limit_tokens: int) -> int:
         """Largest block boundary <= ``limit_tokens`` at which a snapshot of this prompt's state is held (0: none)."""

@@ -458,3 +458,20 @@ def test_parity_report_and_memory_plan_cover_hybrid_models():
     # the dense 32B shape at the same settings holds four times the KV layers
     dense = build_plan(SHAPES["qwen3-32b"], lay, "Q4_K_M", ctx_size=8192, batch_size=32).ranks[0]
     assert dense.kv_bytes > r0.kv_bytes - state
+
+
+def test_state_stride_lets_prompts_with_a_shorter_common_prefix_resume():
+    """Two different prompts that share their first 130 tokens: with a snapshot every 64 tokens the second one resumes at
+    128; with the default (one snapshot at the end of a prompt) it finds pages but no state and starts over."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.prefix_cache import PrefixCache, PrefixCacheConfig
+    from llaminar_b200.engine.sampling import SamplingParams
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    shared = _prompt(130, 31)
+    prompts = [shared + _prompt(90, 32), shared + _prompt(70, 33)]
+    p = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    plain = [LLMEngine(w, device="cpu", max_batch=2, max_context=512).generate([q], p)[0] for q in prompts]
+    for stride, want_hit in ((64, 128), (0, 0)):
+        eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, prefix_cache=PrefixCache(PrefixCacheConfig(state_stride=stride)))
+        got = [eng.generate([q], p)[0] for q in prompts]
+        assert got == plain and eng.stats["prefix_hit_tokens"] == want_hit, stride
