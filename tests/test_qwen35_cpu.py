@@ -475,3 +475,18 @@ def test_state_stride_lets_prompts_with_a_shorter_common_prefix_resume():
         eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, prefix_cache=PrefixCache(PrefixCacheConfig(state_stride=stride)))
         got = [eng.generate([q], p)[0] for q in prompts]
         assert got == plain and eng.stats["prefix_hit_tokens"] == want_hit, stride
+
+
+def test_prefix_cache_and_speculation_together_on_the_hybrid_model():
+    """Chat turns with both switches on: the second turn resumes from the first prompt's snapshot and decodes with NextN
+    drafts; answers equal those of a plain engine."""
+    import dataclasses
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.mtp import MTPConfig, MTPDecoder
+    from llaminar_b200.engine.prefix_cache import PrefixCache
+    cfg = dataclasses.replace(SHAPES["tiny-qwen35"], nextn_layers=1, name="tiny-qwen35-mtp")
+    w = synthesize(cfg, "Q8_0", seed=9)
+    plain = _chat_turns(LLMEngine(w, device="cpu", max_batch=2, max_context=512))
+    eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, prefix_cache=PrefixCache(), mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
+    assert _chat_turns(eng) == plain
+    assert eng.stats["prefix_hit_tokens"] == 128 and eng.mtp.stats()["drafted"] > 0
