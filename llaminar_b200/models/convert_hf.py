@@ -114,8 +114,9 @@ def convert_state_dict(cfg: ModelConfig, sd: Mapping[str, torch.Tensor], recipe:
     if hybrid:
         perm = torch.tensor(tiled_value_heads(n_k, n_v))
         vrows = (perm[:, None] * d + torch.arange(d)[None, :]).reshape(-1)
-    for i in range(cfg.n_layers):
-        s, p = f"{root}layers.{i}.", f"blk.{i}."
+    def block(s: str, i: int) -> None:
+        """One decoder block: checkpoint prefix ``s`` -> GGUF block ``i``."""
+        p = f"blk.{i}."
         vec(p + "attn_norm.weight", gain(get(s + "input_layernorm.weight")))
         vec(p + cfg.ffn_norm_name, gain(get(s + "post_attention_layernorm.weight")))
         if cfg.is_gdn_layer(i):
@@ -158,6 +159,21 @@ def convert_state_dict(cfg: ModelConfig, sd: Mapping[str, torch.Tensor], recipe:
         else:
             for g in ("gate", "up", "down"):
                 mat(p + f"ffn_{g}.weight", get(m + f"{g}_proj.weight"), i)
+
+    for i in range(cfg.n_layers):
+        block(f"{root}layers.{i}.", i)
+    # multi-token-prediction (NextN) blocks, kept by checkpoints under `mtp.`: every GGUF NextN block carries the shared
+    # projection and norms beside its own decoder block (names: src/v2/execution/mtp/MTPWeightManifest.cpp:55-100 of the reference)
+    n_mtp = len({k.split(".")[2] for k in sd if k.startswith("mtp.layers.")})
+    for j in range(n_mtp):
+        i = cfg.n_layers + j
+        block(f"mtp.layers.{j}.", i)
+        mat(f"blk.{i}.nextn.eh_proj.weight", get("mtp.fc.weight"), i)
+        vec(f"blk.{i}.nextn.enorm.weight", gain(get("mtp.pre_fc_norm_embedding.weight")))
+        vec(f"blk.{i}.nextn.hnorm.weight", gain(get("mtp.pre_fc_norm_hidden.weight")))
+        vec(f"blk.{i}.nextn.shared_head_norm.weight", gain(get("mtp.norm.weight")))
+    if n_mtp:
+        cfg = cfg.with_(nextn_layers=n_mtp)
     return ModelWeights(cfg, out)
 
 

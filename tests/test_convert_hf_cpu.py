@@ -23,17 +23,17 @@ def _tiny(family: str):
     try:
         if family == "qwen2":
             from transformers import Qwen2Config, Qwen2ForCausalLM
-            return Qwen2ForCausalLM(Qwen2Config(**common, intermediate_size=128))
+            return Qwen2ForCausalLM(Qwen2Config(**common, intermediate_size=256))
         if family == "qwen3":
             from transformers import Qwen3Config, Qwen3ForCausalLM
-            return Qwen3ForCausalLM(Qwen3Config(**common, head_dim=16, intermediate_size=128))
+            return Qwen3ForCausalLM(Qwen3Config(**common, head_dim=16, intermediate_size=256))
         if family == "qwen3_moe":
             from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
-            return Qwen3MoeForCausalLM(Qwen3MoeConfig(**common, head_dim=16, intermediate_size=128, moe_intermediate_size=32, num_experts=6,
+            return Qwen3MoeForCausalLM(Qwen3MoeConfig(**common, head_dim=16, intermediate_size=256, moe_intermediate_size=32, num_experts=6,
                                                       num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]))
         if family == "qwen3_5":
             from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM, Qwen3_5TextConfig
-            return Qwen3_5ForCausalLM(Qwen3_5TextConfig(**common, **hybrid, intermediate_size=128))
+            return Qwen3_5ForCausalLM(Qwen3_5TextConfig(**common, **hybrid, intermediate_size=256))
         from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM, Qwen3_5MoeTextConfig
         return Qwen3_5MoeForCausalLM(Qwen3_5MoeTextConfig(**common, **hybrid, num_experts=6, num_experts_per_tok=2,
                                                           moe_intermediate_size=32, shared_expert_intermediate_size=48))
@@ -110,3 +110,32 @@ def test_requantising_a_gguf_file_keeps_the_model_function(tmp_path):
     a, _, _ = ReferenceModel(w).forward(toks)
     b, _, _ = ReferenceModel(back).forward(toks)
     assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.995      # Q8_0 rounding through eight blocks
+
+
+def test_multi_token_prediction_blocks_of_a_checkpoint_become_nextn_blocks():
+    """Checkpoints keep the NextN head under `mtp.` (shared projection and norms + one decoder block per depth); the library
+    model drops it on load, so the tensors are fabricated here from block 3 of a tiny hybrid model.  The converted file
+    must describe one NextN layer, and an engine that drafts with it must decode exactly like one that does not."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.mtp import MTPConfig, MTPDecoder
+    from llaminar_b200.engine.sampling import SamplingParams
+    from llaminar_b200.models.convert_hf import convert_state_dict
+    torch.manual_seed(5)
+    m = _tiny("qwen3_5").float().eval()
+    sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    for k in [k for k in sd if k.startswith("model.layers.3.")]:
+        sd["mtp.layers.0." + k[len("model.layers.3."):]] = torch.randn_like(sd[k]) * 0.05
+    d = m.config.hidden_size
+    sd.update({"mtp.fc.weight": torch.randn(d, 2 * d) * 0.05, "mtp.norm.weight": torch.zeros(d),
+               "mtp.pre_fc_norm_embedding.weight": torch.zeros(d), "mtp.pre_fc_norm_hidden.weight": torch.randn(d) * 0.1})
+    w = convert_state_dict(config_from_hf(m.config.to_dict()), sd, "F32")
+    c = w.config
+    assert c.nextn_layers == 1 and w["blk.4.nextn.eh_proj.weight"].shape == (d, 2 * d)
+    assert torch.equal(w["blk.4.nextn.enorm.weight"].to_float(), torch.ones(d))            # zero-centred gain stored as 1 + w
+    assert "blk.4.attn_q.weight" in w and "blk.4.post_attention_norm.weight" in w and "blk.4.attn_qkv.weight" not in w
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 128, (n,), generator=g).tolist() for n in (30, 50)]
+    p = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    plain = LLMEngine(w, device="cpu", max_batch=2, max_context=128).generate(prompts, p)
+    spec = LLMEngine(w, device="cpu", max_batch=2, max_context=128, mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
+    assert spec.generate(prompts, p) == plain and spec.mtp.stats()["drafted"] > 0
