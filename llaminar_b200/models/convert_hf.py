@@ -211,19 +211,36 @@ def tokenizer_metadata(model_dir: str) -> dict:
     return md
 
 
-def load_checkpoint(model_dir: str) -> tuple[dict, dict]:
-    """(config.json as a dict, {tensor name: tensor}) of a directory with one or several `.safetensors` files."""
-    from safetensors import safe_open
-    hf = json.load(open(os.path.join(model_dir, "config.json"), encoding="utf-8"))
-    sd = {}
-    for name in sorted(os.listdir(model_dir)):
-        if name.endswith(".safetensors"):
-            with safe_open(os.path.join(model_dir, name), framework="pt") as f:
+class _LazyTensors(Mapping):
+    """Tensor name -> tensor over the `.safetensors` files of a directory; a tensor is read when it is asked for, so a
+    conversion never holds the whole unquantised checkpoint."""
+
+    def __init__(self, model_dir: str):
+        from safetensors import safe_open
+        self._files, self._where = {}, {}
+        for name in sorted(os.listdir(model_dir)):
+            if name.endswith(".safetensors"):
+                f = safe_open(os.path.join(model_dir, name), framework="pt")
+                self._files[name] = f
                 for k in f.keys():
-                    sd[k] = f.get_tensor(k)
-    if not sd:
-        raise FileNotFoundError(f"no .safetensors file in {model_dir}")
-    return hf, sd
+                    self._where[k] = name
+        if not self._where:
+            raise FileNotFoundError(f"no .safetensors file in {model_dir}")
+
+    def __getitem__(self, key: str) -> torch.Tensor:
+        return self._files[self._where[key]].get_tensor(key)
+
+    def __iter__(self):
+        return iter(self._where)
+
+    def __len__(self) -> int:
+        return len(self._where)
+
+
+def load_checkpoint(model_dir: str) -> tuple[dict, Mapping]:
+    """(config.json as a dict, {tensor name: tensor}, read lazily) of a directory with one or several `.safetensors` files."""
+    hf = json.load(open(os.path.join(model_dir, "config.json"), encoding="utf-8"))
+    return hf, _LazyTensors(model_dir)
 
 
 def requantize(w: ModelWeights, recipe: QuantRecipe | str) -> ModelWeights:
