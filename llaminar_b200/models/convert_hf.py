@@ -198,6 +198,15 @@ def tokenizer_metadata(model_dir: str) -> dict:
     merges = [m if isinstance(m, str) else " ".join(m) for m in model.get("merges", [])]
     md = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.pre": "qwen2", "tokenizer.ggml.tokens": tokens,
           "tokenizer.ggml.token_type": types, "tokenizer.ggml.merges": merges}
+    # the pre-tokeniser's expression itself, when the file states one: exact for any byte-level BPE vocabulary
+    pre = tj.get("pre_tokenizer") or {}
+    for part in (pre.get("pretokenizers") or [pre]):
+        rx = (part.get("pattern") or {}).get("Regex") if part.get("type") == "Split" else None
+        if rx:
+            md["tokenizer.llaminar.split_regex"] = rx
+            if "\\p{M}" in rx:
+                md["tokenizer.ggml.pre"] = "qwen35"
+            break
     cfg_path = os.path.join(model_dir, "tokenizer_config.json")
     if os.path.exists(cfg_path):
         tc = json.load(open(cfg_path, encoding="utf-8"))

@@ -15,9 +15,17 @@ try:
     import regex as _re
     _QWEN_SPLIT = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*"
                    r"|\s*[\r\n]+|\s+(?!\S)|\s+")
+    # the hybrid families' vocabulary was built with combining marks counted as letters
+    _QWEN35_SPLIT = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?[\p{L}\p{M}]+|\p{N}| ?[^\s\p{L}\p{M}\p{N}]+[\r\n]*"
+                     r"|\s*[\r\n]+|\s+(?!\S)|\s+")
 except ImportError:                                        # pragma: no cover
     import re as _re
     _QWEN_SPLIT = r"'s|'t|'re|'ve|'m|'ll|'d| ?[A-Za-z]+| ?[0-9]| ?[^\sA-Za-z0-9]+|\s+(?!\S)|\s+"
+    _QWEN35_SPLIT = _QWEN_SPLIT
+
+# pre-tokeniser by the name in `tokenizer.ggml.pre`; a file may also carry the expression itself
+# (`tokenizer.llaminar.split_regex`, written by models/convert_hf.py from the checkpoint's tokenizer.json)
+SPLIT_BY_NAME = {"qwen2": _QWEN_SPLIT, "qwen35": _QWEN35_SPLIT}
 
 TOKEN_NORMAL, TOKEN_UNKNOWN, TOKEN_CONTROL, TOKEN_USER_DEFINED, TOKEN_UNUSED, TOKEN_BYTE = 1, 2, 3, 4, 5, 6
 
@@ -39,7 +47,7 @@ def byte_alphabet() -> tuple[str, ...]:
 class BPETokenizer:
     def __init__(self, tokens: list[str], merges: Iterable[str] = (), token_types: list[int] | None = None,
                  bos_id: int | None = None, eos_id: int | None = None, pad_id: int | None = None,
-                 chat_template: str | None = None, add_bos: bool = False):
+                 chat_template: str | None = None, add_bos: bool = False, split_regex: str | None = None):
         self.tokens = list(tokens)
         self.vocab = {}
         for i, t in enumerate(self.tokens):
@@ -60,7 +68,7 @@ class BPETokenizer:
         if self.special:
             alts = sorted(self.special, key=len, reverse=True)
             self._special_re = _re.compile("|".join(_re.escape(a) for a in alts))
-        self._split_re = _re.compile(_QWEN_SPLIT)
+        self._split_re = _re.compile(split_regex or _QWEN_SPLIT)
         self._cache: dict[str, list[int]] = {}
         self._native = None
         try:
@@ -79,7 +87,8 @@ class BPETokenizer:
                             md.get("tokenizer.ggml.token_type"),
                             md.get("tokenizer.ggml.bos_token_id"), md.get("tokenizer.ggml.eos_token_id"),
                             md.get("tokenizer.ggml.padding_token_id"), md.get("tokenizer.chat_template"),
-                            bool(md.get("tokenizer.ggml.add_bos_token", False)))
+                            bool(md.get("tokenizer.ggml.add_bos_token", False)),
+                            md.get("tokenizer.llaminar.split_regex") or SPLIT_BY_NAME.get(str(md.get("tokenizer.ggml.pre", "qwen2"))))
 
     @property
     def vocab_size(self) -> int:

@@ -81,7 +81,10 @@ def test_tokenizer_files_become_gguf_tokenizer_metadata(tmp_path):
     vocab = {alpha[b]: b for b in range(256)}
     he = alpha[ord("h")] + alpha[ord("e")]
     vocab[he] = 256
+    rx = r"[\p{L}\p{M}]+|\p{N}|\s+|[^\s\p{L}\p{M}\p{N}]+"
     tj = {"model": {"type": "BPE", "vocab": vocab, "merges": [[alpha[ord("h")], alpha[ord("e")]]]},
+          "pre_tokenizer": {"type": "Sequence", "pretokenizers": [{"type": "Split", "pattern": {"Regex": rx}, "behavior": "Isolated"},
+                                                                  {"type": "ByteLevel", "add_prefix_space": False}]},
           "added_tokens": [{"id": 257, "content": "<|im_end|>", "special": True}, {"id": 259, "content": "<tool>", "special": False}]}
     json.dump(tj, open(tmp_path / "tokenizer.json", "w"))
     json.dump({"eos_token": {"content": "<|im_end|>"}, "chat_template": "{{ messages }}"}, open(tmp_path / "tokenizer_config.json", "w"))
@@ -89,7 +92,9 @@ def test_tokenizer_files_become_gguf_tokenizer_metadata(tmp_path):
     assert len(md["tokenizer.ggml.tokens"]) == 260 and md["tokenizer.ggml.token_type"][257] == 3
     assert md["tokenizer.ggml.token_type"][258] == 5 and md["tokenizer.ggml.token_type"][259] == 4
     assert md["tokenizer.ggml.eos_token_id"] == 257 and md["tokenizer.chat_template"] == "{{ messages }}"
+    assert md["tokenizer.llaminar.split_regex"] == rx and md["tokenizer.ggml.pre"] == "qwen35"      # the file's own expression
     tok = BPETokenizer.from_metadata(md)
+    assert tok._split_re.pattern == rx
     ids = tok.encode("hehe<|im_end|>")
     assert ids == [256, 256, 257] and tok.decode(ids[:2]) == "hehe"
     assert tokenizer_metadata(str(tmp_path / "nowhere")) == {}
