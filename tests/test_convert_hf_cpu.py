@@ -144,3 +144,30 @@ def test_multi_token_prediction_blocks_of_a_checkpoint_become_nextn_blocks():
     plain = LLMEngine(w, device="cpu", max_batch=2, max_context=128).generate(prompts, p)
     spec = LLMEngine(w, device="cpu", max_batch=2, max_context=128, mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
     assert spec.generate(prompts, p) == plain and spec.mtp.stats()["drafted"] > 0
+
+
+def test_converted_tokenizer_encodes_like_the_tokenizers_library(tmp_path):
+    """A byte-level BPE vocabulary trained with the `tokenizers` library (Qwen-style pre-tokeniser with combining marks
+    counted as letters, two special tokens), written as tokenizer.json, carried into GGUF metadata: this package's tokenizer
+    must give the library's ids on mixed text, and decode them back."""
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    from llaminar_b200.tokenizer.bpe import BPETokenizer, SPLIT_BY_NAME
+    t = Tokenizer(models.BPE())
+    t.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(SPLIT_BY_NAME["qwen35"]), behavior="isolated"),
+                                               pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    t.decoder = decoders.ByteLevel()
+    corpus = ["The quick brown fox jumps over the lazy dog. " * 3, "def add(a, b):\\n    return a + b\\n", "Zwölf Boxkämpfer jagen Viktor quer",
+              "über den großen Sylter Deich 12345 67890", "naïve café déjà vu — “quotes” and… ellipses", "它们是中文字符，日本語のテキスト",
+              "I'm sure they've said we'll go; it's what he'd do.", "été with combining marks"] * 4
+    t.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=420, special_tokens=["<|im_start|>", "<|im_end|>"],
+                                                      initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False))
+    t.save(str(tmp_path / "tokenizer.json"))
+    ours = BPETokenizer.from_metadata(tokenizer_metadata(str(tmp_path)))
+    samples = ["Hello, world! It's 2026.", "<|im_start|>user\\nZwölf   Boxkämpfer\\n\\n<|im_end|>", "  leading and trailing  ", "tabs\\tand\\r\\nnewlines",
+               "été naïve 中文 12 345", "x = {'a': [1, 2, 3]}  # comment"]
+    for text in samples:
+        want = t.encode(text, add_special_tokens=False).ids
+        got = ours.encode(text)
+        assert got == want, text
+        assert ours.decode(got) == text
