@@ -163,6 +163,8 @@ class PagedKVCache:
 
     # -- page payload movement for the RAM / disk prefix tiers -------------------------------
     def export_page(self, page: int) -> torch.Tensor:
+        if not self.layers:                      # a pipeline stage of linear-attention blocks only: pages carry no bytes here
+            return torch.empty(0)
         return torch.stack([l[page] for l in self.layers]).to("cpu", non_blocking=False)
 
     def import_page(self, page: int, payload: torch.Tensor) -> None:

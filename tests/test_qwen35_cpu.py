@@ -490,3 +490,23 @@ def test_prefix_cache_and_speculation_together_on_the_hybrid_model():
     eng = LLMEngine(w, device="cpu", max_batch=2, max_context=512, prefix_cache=PrefixCache(), mtp=MTPDecoder(MTPConfig(draft_tokens=2)))
     assert _chat_turns(eng) == plain
     assert eng.stats["prefix_hit_tokens"] == 128 and eng.mtp.stats()["drafted"] > 0
+
+
+def _pp_chat(rank, world):
+    from llaminar_b200.engine.prefix_cache import PrefixCache
+    from llaminar_b200.parallel.pp import build_pipeline_engine
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    layout = {"pp": 2, "tp": 1, "world": 2, "stages": [("s0", ["cpu"], 0, 2), ("s1", ["cpu"], 3, 7)]}
+    eng = build_pipeline_engine(w, layout, rank, microbatch_tokens=64, device="cpu", max_batch=2, max_context=512, prefix_cache=PrefixCache())
+    return _chat_turns(eng), eng.stats["prefix_hit_tokens"]
+
+
+def test_pipeline_stages_agree_on_the_snapshot_boundary_of_a_hybrid_model():
+    """Stage 0 holds linear-attention blocks only (no KV layer, three state layers), stage 1 the rest: both must cut the
+    second turn's prefix hit back to the same snapshot boundary."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from tests.mp_utils import run_ranks
+    w = synthesize(SHAPES["tiny-qwen35"], "Q8_0", seed=7)
+    plain = _chat_turns(LLMEngine(w, device="cpu", max_batch=2, max_context=512))
+    res = run_ranks(_pp_chat, 2)
+    assert res[0] == (plain, 128) and res[1] == (plain, 128)
