@@ -1,4 +1,6 @@
 """Byte-level BPE from GGUF metadata: merges, special tokens, streaming decode of split UTF-8."""
+import pytest
+
 from llaminar_b200.tokenizer.bpe import BPETokenizer, StreamDecoder, byte_alphabet
 
 
@@ -45,3 +47,44 @@ def test_from_metadata_of_a_synthetic_model():
     t = BPETokenizer.from_metadata(w.metadata)
     assert t.vocab_size == SHAPES["tiny-qwen3"].vocab_size and t.chat_template
     assert t.decode(t.encode("plain ascii text")) == "plain ascii text"
+
+
+def test_chat_template_rendering_matches_the_transformers_renderer():
+    """The same Jinja source rendered here and by `transformers` (its sandbox, filters and whitespace options): a Qwen3-style
+    template with tool definitions, tool calls, tool results, thinking content and the generation prompt."""
+    cu = pytest.importorskip("transformers.utils.chat_template_utils")
+    from llaminar_b200.models.synth import CHATML_TEMPLATE
+    from llaminar_b200.tokenizer.chat_template import ChatTemplate
+    qwen3_like = (
+        "{%- if tools %}{{- '<|im_start|>system\\n' }}{%- if messages[0].role == 'system' %}{{- messages[0].content + '\\n\\n' }}{%- endif %}"
+        "{{- '# Tools\\n<tools>' }}{%- for tool in tools %}{{- '\\n' }}{{- tool | tojson }}{%- endfor %}{{- '\\n</tools><|im_end|>\\n' }}"
+        "{%- elif messages[0].role == 'system' %}{{- '<|im_start|>system\\n' + messages[0].content + '<|im_end|>\\n' }}{%- endif %}"
+        "{%- set ns = namespace(last_user=-1) %}"
+        "{%- for m in messages %}{%- if m.role == 'user' %}{%- set ns.last_user = loop.index0 %}{%- endif %}{%- endfor %}"
+        "{%- for message in messages %}"
+        "{%- if message.role == 'user' or (message.role == 'system' and not loop.first) %}"
+        "{{- '<|im_start|>' + message.role + '\\n' + message.content + '<|im_end|>\\n' }}"
+        "{%- elif message.role == 'assistant' %}"
+        "{%- set content = message.content or '' %}"
+        "{%- if '</think>' in content %}{%- set content = content.split('</think>')[-1].lstrip('\\n') %}{%- endif %}"
+        "{{- '<|im_start|>assistant\\n' + content }}"
+        "{%- for tc in message.tool_calls or [] %}{{- '\\n<tool_call>\\n{\"name\": \"' + tc.function.name + '\", \"arguments\": ' }}"
+        "{{- tc.function.arguments | tojson }}{{- '}\\n</tool_call>' }}{%- endfor %}{{- '<|im_end|>\\n' }}"
+        "{%- elif message.role == 'tool' %}{{- '<|im_start|>user\\n<tool_response>\\n' + message.content + '\\n</tool_response><|im_end|>\\n' }}"
+        "{%- endif %}{%- endfor %}"
+        "{%- if add_generation_prompt %}{{- '<|im_start|>assistant\\n' }}"
+        "{%- if enable_thinking is defined and enable_thinking is false %}{{- '<think>\\n\\n</think>\\n\\n' }}{%- endif %}{%- endif %}")
+    tools = [{"type": "function", "function": {"name": "get_weather", "description": 'Weather for a <city> & country — "now"',
+                                               "parameters": {"type": "object", "properties": {"city": {"type": "string"}}, "required": ["city"]}}}]
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "Wetter in Köln?"},
+            {"role": "assistant", "content": "<think>\nneed a tool\n</think>\n\nLet me check.",
+             "tool_calls": [{"type": "function", "function": {"name": "get_weather", "arguments": {"city": "Köln", "n": 2}}}]},
+            {"role": "tool", "content": '{"temp": 7}'}, {"role": "user", "content": "thanks"}]
+    for source in (CHATML_TEMPLATE, qwen3_like):
+        for tl in (None, tools):
+            for think in (True, False):
+                want = cu.render_jinja_template([msgs], tools=tl, chat_template=source, add_generation_prompt=True, enable_thinking=think)[0]
+                if isinstance(want, list):
+                    want = want[0]
+                got = ChatTemplate(source).render(msgs, tools=tl, add_generation_prompt=True, enable_thinking=think)
+                assert got == want
