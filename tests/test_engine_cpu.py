@@ -186,3 +186,26 @@ def test_a_prompt_larger_than_the_whole_cache_is_ended_and_the_queue_goes_on():
     assert any(o.rid == big.rid and o.finished and o.finish_reason == "cache_full" for o in outs)
     assert small.finish_reason == "length" and len(small.output) == 4
     assert eng.kv.allocator.n_free == eng.kv.n_pages - 1
+
+
+def test_filtered_sampling_distribution_matches_the_transformers_logits_warpers():
+    """temperature -> top-k -> top-p as `transformers` applies them (its warpers, then softmax) against `filtered_probs`, the
+    distribution the samplers here draw from (the GPU kernel is tested against the same function)."""
+    pytest = __import__("pytest")
+    tf = pytest.importorskip("transformers")
+    from transformers import TemperatureLogitsWarper, TopKLogitsWarper, TopPLogitsWarper
+    from llaminar_b200.engine.sampling import filtered_probs
+    g = torch.Generator().manual_seed(0)
+    for temp, k, p in ((0.7, 40, 0.9), (1.3, 5, 0.5), (0.6, 20, 0.95), (1.0, 200, 1.0), (0.8, 0, 0.3)):
+        logits = torch.randn(1, 2000, generator=g) * 3
+        x = TemperatureLogitsWarper(temp)(None, logits.clone())
+        if k:
+            x = TopKLogitsWarper(k)(None, x)
+        else:
+            x = TopKLogitsWarper(1024)(None, x)                  # top_k = 0 means "the best 1024" here
+        if p < 1.0:
+            x = TopPLogitsWarper(p)(None, x)
+        want = torch.softmax(x, dim=-1)[0]
+        got = filtered_probs(logits[0], SamplingParams(temperature=temp, top_k=k, top_p=p))
+        assert torch.equal(got > 0, want > 0), (temp, k, p)
+        assert torch.allclose(got, want, atol=1e-6)
