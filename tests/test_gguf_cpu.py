@@ -200,3 +200,46 @@ def test_block_formats_without_a_packed_layout_are_reencoded_for_the_dense_kerne
     assert for_kernels(narrow) is narrow                                    # K is not a whole 256-column chunk: dense path
     lin = QLinear.from_qtensors([packed, low], "cpu")
     assert len(lin.parts) == 2 and all(isinstance(p, PackedWeight) for p, _ in lin.parts) and lin.n_out == 256
+
+
+def test_files_written_here_are_read_by_the_gguf_package_and_its_files_by_us(tmp_path):
+    """Interoperability of the container format in both directions: a checkpoint written by this package is opened with the
+    `gguf` package's reader (metadata values, tensor names, shapes, types, bytes), and a file written with the `gguf`
+    package's writer is opened with the reader here."""
+    gguf = pytest.importorskip("gguf")
+    import numpy as np
+    from llaminar_b200.gguf import GGUFFile
+    from llaminar_b200.models.config import SHAPES
+    from llaminar_b200.models.synth import synthesize
+    w = synthesize(SHAPES["tiny-qwen35"], "Q4_K_M", seed=1)
+    path = str(tmp_path / "ours.gguf")
+    w.save_gguf(path)
+    r = gguf.GGUFReader(path)
+    field = lambda k: r.fields[k]
+    assert bytes(field("general.architecture").parts[-1]).decode() == "qwen35"
+    assert int(field("qwen35.ssm.state_size").parts[-1][0]) == 32 and int(field("qwen35.full_attention_interval").parts[-1][0]) == 4
+    assert len(field("tokenizer.ggml.tokens").data) == 1024
+    names = {t.name: t for t in r.tensors}
+    assert set(names) == set(w.tensors)
+    for name in ("blk.0.attn_qkv.weight", "blk.3.attn_q.weight", "blk.0.ssm_a", "blk.0.ssm_conv1d.weight", "token_embd.weight"):
+        t, ours = names[name], w[name]
+        assert t.tensor_type.name == ours.qtype.name
+        assert list(reversed([int(x) for x in t.shape])) == list(ours.shape)            # GGUF lists the fastest dimension first
+        assert np.array_equal(np.asarray(t.data).reshape(-1).view(np.uint8), ours.raw.numpy())
+    # the other direction
+    theirs = str(tmp_path / "theirs.gguf")
+    wr = gguf.GGUFWriter(theirs, "qwen3")
+    wr.add_uint32("qwen3.block_count", 2)
+    wr.add_float32("qwen3.rope.freq_base", 1e6)
+    wr.add_array("tokenizer.ggml.tokens", ["a", "b", "c"])
+    x = np.arange(24, dtype=np.float32).reshape(4, 6)
+    wr.add_tensor("blk.0.ffn_norm.weight", x)
+    wr.write_header_to_file()
+    wr.write_kv_data_to_file()
+    wr.write_tensors_to_file()
+    wr.close()
+    gf = GGUFFile(theirs)
+    assert gf.architecture == "qwen3" and gf.get("qwen3.block_count") == 2 and gf.get("tokenizer.ggml.tokens") == ["a", "b", "c"]
+    t = gf["blk.0.ffn_norm.weight"]
+    assert tuple(t.shape) == (4, 6) and torch.equal(torch.frombuffer(bytearray(t.raw().numpy().tobytes()), dtype=torch.float32).view(4, 6), torch.from_numpy(x))
+    gf.close()
