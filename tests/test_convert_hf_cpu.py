@@ -171,3 +171,30 @@ def test_converted_tokenizer_encodes_like_the_tokenizers_library(tmp_path):
         got = ours.encode(text)
         assert got == want, text
         assert ours.decode(got) == text
+
+
+@pytest.mark.parametrize("family", ["qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe"])
+def test_engine_on_a_converted_checkpoint_generates_what_transformers_generates(family, tmp_path):
+    """End to end: converter, GGUF file, loader, CPU runner, paged cache (and state slots for the hybrid families), scheduler
+    and greedy sampler against `generate(do_sample=False)` of the library model, two prompts batched."""
+    from llaminar_b200.engine.engine import LLMEngine
+    from llaminar_b200.engine.sampling import SamplingParams
+    torch.manual_seed(11)
+    m = _tiny(family).float().eval()
+    m.config._attn_implementation = "eager"
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(torch.randn_like(p) * (0.3 if p.dim() == 1 else 0.1))
+            if n.endswith("A_log"):
+                p.copy_(torch.log(torch.rand_like(p) * 6 + 0.5))
+    src, out = tmp_path / "hf", str(tmp_path / "m.gguf")
+    m.save_pretrained(src, safe_serialization=True)
+    convert_directory(str(src), out, "F32")
+    eng = LLMEngine(ModelWeights.from_gguf(out), device="cpu", max_batch=2, max_context=128, max_prefill_tokens=24)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 128, (n,), generator=g).tolist() for n in (19, 40)]
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for pr, o in zip(prompts, got):
+        with torch.no_grad():
+            want = m.generate(torch.tensor([pr]), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(pr):].tolist()
+        assert o == want
