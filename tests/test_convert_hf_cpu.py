@@ -173,7 +173,7 @@ def test_converted_tokenizer_encodes_like_the_tokenizers_library(tmp_path):
         assert ours.decode(got) == text
 
 
-@pytest.mark.parametrize("family", ["qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe"])
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe"])
 def test_engine_on_a_converted_checkpoint_generates_what_transformers_generates(family, tmp_path):
     """End to end: converter, GGUF file, loader, CPU runner, paged cache (and state slots for the hybrid families), scheduler
     and greedy sampler against `generate(do_sample=False)` of the library model, two prompts batched."""
