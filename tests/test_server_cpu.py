@@ -465,3 +465,35 @@ def test_prompt_that_cannot_fit_the_cache_gets_400_and_the_server_goes_on():
         assert st == 200 and loop.errors == 0
     finally:
         srv.stop()
+
+
+def test_the_official_openai_client_talks_to_the_server(server):
+    """The `openai` Python client (which validates every response against its typed schema) against the in-process server:
+    model list, chat completion, streamed chat completion with usage, `n` choices with log-probabilities, a stop sequence, a
+    text completion, and the error shape for a bad request."""
+    openai = pytest.importorskip("openai")
+    client = openai.OpenAI(base_url=f"http://127.0.0.1:{server.port}/v1", api_key="unused", max_retries=0, timeout=120)
+    assert [m.id for m in client.models.list().data] == ["tiny"]
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "hello there"}]
+    r = client.chat.completions.create(model="tiny", messages=msgs, max_tokens=6, temperature=0)
+    assert r.object == "chat.completion" and r.choices[0].message.role == "assistant" and r.choices[0].finish_reason in ("length", "stop")
+    assert r.usage.completion_tokens <= 6 and r.usage.total_tokens == r.usage.prompt_tokens + r.usage.completion_tokens
+    chunks = list(client.chat.completions.create(model="tiny", messages=msgs, max_tokens=6, temperature=0, stream=True,
+                                                 stream_options={"include_usage": True}))
+    assert chunks and all(c.object == "chat.completion.chunk" for c in chunks)
+    streamed = "".join(c.choices[0].delta.content or "" for c in chunks if c.choices)
+    assert streamed == (r.choices[0].message.content or "")                     # greedy: the stream carries the same text
+    assert any(c.choices and c.choices[0].finish_reason for c in chunks)
+    r = client.chat.completions.create(model="tiny", messages=msgs, max_tokens=4, temperature=0.8, seed=3, n=2, logprobs=True, top_logprobs=2)
+    assert len(r.choices) == 2 and [c.index for c in r.choices] == [0, 1]
+    lp = r.choices[0].logprobs.content
+    assert lp and all(len(t.top_logprobs) == 2 and t.logprob <= 0.0 for t in lp)
+    full = client.chat.completions.create(model="tiny", messages=msgs, max_tokens=12, temperature=0).choices[0].message.content or ""
+    if len(full) > 3:
+        cut = client.chat.completions.create(model="tiny", messages=msgs, max_tokens=12, temperature=0, stop=[full[2:4]])
+        assert cut.choices[0].finish_reason == "stop" and cut.choices[0].message.content == full[:2]
+    t = client.completions.create(model="tiny", prompt="Once upon", max_tokens=5, temperature=0)
+    assert t.object == "text_completion" and t.choices[0].finish_reason in ("length", "stop") and t.usage.completion_tokens <= 5
+    with pytest.raises(openai.BadRequestError) as e:
+        client.chat.completions.create(model="tiny", messages=[], max_tokens=1)
+    assert e.value.status_code == 400
