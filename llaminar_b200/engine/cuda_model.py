@@ -214,6 +214,46 @@ class CudaLayer:
     pass
 
 
+def paged_attention_torch(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_ids: torch.Tensor,
+                          positions: torch.Tensor, scale: float) -> torch.Tensor:
+    """Causal GQA attention of a packed batch over the paged cache, any head size, one sequence at a time through
+    `scaled_dot_product_attention` (no [rows x keys] score matrix in memory, whatever the context length).  Rows of a
+    sequence are consecutive with consecutive positions; its keys are positions 0 .. last row's position.
+    q: [T, H, D]; kv_layer: [n_pages, 2, Hk, 64, D]; returns fp32 [T, H, D].  (One host synchronisation for the row ranges:
+    this is the prefill path of head sizes without an attention kernel.)"""
+    T, H, D = q.shape
+    Hk = kv_layer.shape[2]
+    sid, pos = seq_ids.tolist(), positions.tolist()
+    out = torch.empty(T, H, D, dtype=torch.float32, device=q.device)
+    r0 = 0
+    for r in range(1, T + 1):
+        if r < T and sid[r] == sid[r0]:
+            continue
+        n_keys = pos[r - 1] + 1
+        n_pages = (n_keys + 63) // 64
+        pages = block_table[sid[r0], :n_pages].long()
+        K = kv_layer[pages, 0].permute(1, 0, 2, 3).reshape(1, Hk, n_pages * 64, D)[:, :, :n_keys]
+        V = kv_layer[pages, 1].permute(1, 0, 2, 3).reshape(1, Hk, n_pages * 64, D)[:, :, :n_keys]
+        qs = q[r0:r].to(K.dtype).transpose(0, 1).unsqueeze(0)                       # [1, H, rows, D]
+        allowed = None
+        if pos[r0] != 0:                                                            # rows behind cached context: explicit mask
+            allowed = torch.arange(n_keys, device=q.device)[None, :] <= positions[r0:r].long()[:, None]
+        try:
+            o = torch.nn.functional.scaled_dot_product_attention(qs, K, V, attn_mask=allowed, is_causal=allowed is None, scale=scale,
+                                                                 enable_gqa=H != Hk)[0]
+        except RuntimeError:
+            # no fused backend took the shape: the same attention written out (materialises the rows x keys scores)
+            g = H // Hk
+            sc = torch.einsum("htd,hsd->hts", qs[0].float(), K[0].float().repeat_interleave(g, 0)) * scale
+            if allowed is None:
+                allowed = torch.arange(n_keys, device=q.device)[None, :] <= positions[r0:r].long()[:, None]
+            o = torch.einsum("hts,hsd->htd", torch.softmax(sc.masked_fill(~allowed[None], float("-inf")), -1),
+                             V[0].float().repeat_interleave(g, 0))
+        out[r0:r] = o.transpose(0, 1).float()
+        r0 = r
+    return out
+
+
 def paged_decode_attention_torch(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                                  scale: float) -> torch.Tensor:
     """One query row per sequence against the paged cache, any head size, as one batched expression with static shapes
@@ -539,22 +579,7 @@ class CudaModel:
         return o
 
     def _attention_torch(self, q: torch.Tensor, fb: ForwardBatch, kv_layer: torch.Tensor, scale: float) -> torch.Tensor:
-        """Causal GQA attention over the paged cache on PyTorch ops, one sequence at a time (any head size)."""
-        H, Hk, D = self.n_heads_local, self.n_kv_local, self.cfg.head_dim
-        pos, sid = fb.positions.long(), fb.seq_ids.long()
-        out = torch.empty(q.shape[0], H, D, dtype=torch.float32, device=q.device)
-        g = H // Hk
-        for b in sid.unique().tolist():
-            rows = (sid == b).nonzero(as_tuple=True)[0]
-            last = int(pos[rows].max())
-            n_pages = last // 64 + 1
-            pages = fb.block_table.long()[b, :n_pages]
-            K = kv_layer[pages, 0].permute(1, 0, 2, 3).reshape(Hk, n_pages * 64, D)[:, :last + 1].float().repeat_interleave(g, 0)
-            V = kv_layer[pages, 1].permute(1, 0, 2, 3).reshape(Hk, n_pages * 64, D)[:, :last + 1].float().repeat_interleave(g, 0)
-            s = torch.einsum("thd,hsd->hts", q[rows], K) * scale
-            mask = torch.arange(last + 1, device=q.device)[None, :] > pos[rows][:, None]
-            out[rows] = torch.einsum("hts,hsd->thd", torch.softmax(s.masked_fill(mask[None], float("-inf")), -1), V)
-        return out
+        return paged_attention_torch(q, kv_layer, fb.block_table, fb.seq_ids, fb.positions, scale)
 
     def _kv_for_prefill(self, fb: ForwardBatch, kv_layer: torch.Tensor):
         """The prefill kernels read bf16 pages.  With the 8-bit cache the pages of the chunk's sequences (context and the rows

@@ -510,3 +510,24 @@ def test_pipeline_stages_agree_on_the_snapshot_boundary_of_a_hybrid_model():
     plain = _chat_turns(LLMEngine(w, device="cpu", max_batch=2, max_context=512))
     res = run_ranks(_pp_chat, 2)
     assert res[0] == (plain, 128) and res[1] == (plain, 128)
+
+
+def test_packed_prefill_attention_over_pages_matches_plain_attention():
+    """Two sequences in one packed batch, head size 256, GQA 4:2: a fresh 70-row prompt and a 30-row chunk behind 100 cached
+    positions, pages shuffled; against softmax attention written out per sequence."""
+    from llaminar_b200.engine.cuda_model import paged_attention_torch
+    torch.manual_seed(6)
+    H, Hk, D = 4, 2, 256
+    kv = torch.randn(9, 2, Hk, 64, D)
+    bt = torch.tensor([[4, 1, 0], [7, 2, 5]], dtype=torch.int32)
+    sid = torch.tensor([0] * 70 + [1] * 30, dtype=torch.int32)
+    pos = torch.tensor(list(range(70)) + list(range(100, 130)), dtype=torch.int32)
+    q = torch.randn(100, H, D)
+    got = paged_attention_torch(q, kv, bt, sid, pos, D ** -0.5)
+    for b, rows in ((0, range(0, 70)), (1, range(70, 100))):
+        K = kv[bt[b].long(), 0].permute(1, 0, 2, 3).reshape(Hk, 192, D).repeat_interleave(H // Hk, 0)
+        V = kv[bt[b].long(), 1].permute(1, 0, 2, 3).reshape(Hk, 192, D).repeat_interleave(H // Hk, 0)
+        for r in rows:
+            n = int(pos[r]) + 1
+            p = torch.softmax(torch.einsum("hd,hld->hl", q[r], K[:, :n]) * D ** -0.5, -1)
+            assert torch.allclose(got[r], torch.einsum("hl,hld->hd", p, V[:, :n]), atol=2e-5), r
